@@ -1,0 +1,195 @@
+// Exact (bit-for-bit) decoders for the raw checkpoint encodings.
+//
+// Every encoding is cut into "parts": the unit one thread decodes at a time.
+// A part yields 4*G consecutive-in-groups weights: group g covers the four
+// logical elements [xoff(part, g), xoff(part, g) + 4) of its block. Products
+// and sums are formed with __fmul_rn / __fadd_rn so that the compiler cannot
+// contract them into an FMA: the reference rounds the multiply and the add
+// separately (arith.mulf then arith.addf,
+// crates/dyninfer-quantization/src/quantizations/gguf_codegen.rs:464-465,
+// mlx_affine.rs:596-597).
+#pragma once
+
+#include "common.cuh"
+
+namespace dyn {
+
+struct RowPtr {  // one weight row
+  const uint8_t* data;
+  const uint8_t* sc;  // MLX: this row's scales
+  const uint8_t* bi;  // MLX: this row's biases
+  int aux, group;
+};
+
+__device__ __forceinline__ RowPtr row_ptr(const WRef& w, int64_t row) {
+  RowPtr r;
+  r.data = w.data + row * w.row_bytes();
+  r.aux = w.aux;
+  r.group = w.group;
+  if (w.enc == E_MLX_U4) {
+    int64_t per_row = (w.cols / w.group) * (w.aux == E_F32 ? 4 : 2);
+    r.sc = w.scales + row * per_row;
+    r.bi = w.biases + row * per_row;
+  } else {
+    r.sc = r.bi = nullptr;
+  }
+  return r;
+}
+
+template <int ENC>
+struct Codec;
+
+// Q4_0: f16 d @0, 16 bytes @2; byte l: low nibble = element l, high = l+16;
+// w = f32(q - 8) * f32(d). gguf_codegen.rs:412-472.
+template <>
+struct Codec<E_Q4_0> {
+  static constexpr int BLOCK = 32, BYTES = 18, PARTS = 4, G = 2;
+  __device__ static __forceinline__ int xoff(int part, int g) { return g * 16 + 4 * part; }
+  __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int part, float* w) {
+    const uint8_t* b = r.data + blk * BYTES;
+    const float d = f16_bits_to_f32(ld_u16(b));
+    const uint32_t q = ld_u32_a2(b + 2 + 4 * part);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint32_t byte = (q >> (8 * i)) & 0xffu;
+      w[i] = __fmul_rn((float)((int)(byte & 15u) - 8), d);
+      w[4 + i] = __fmul_rn((float)((int)(byte >> 4) - 8), d);
+    }
+  }
+};
+
+// Q4_1: f16 d @0, f16 m @2, 16 bytes @4; w = f32(q)*d + m. gguf_codegen.rs:373-375,425-465.
+template <>
+struct Codec<E_Q4_1> {
+  static constexpr int BLOCK = 32, BYTES = 20, PARTS = 4, G = 2;
+  __device__ static __forceinline__ int xoff(int part, int g) { return g * 16 + 4 * part; }
+  __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int part, float* w) {
+    const uint8_t* b = r.data + blk * BYTES;
+    const float d = f16_bits_to_f32(ld_u16(b));
+    const float m = f16_bits_to_f32(ld_u16(b + 2));
+    const uint32_t q = *reinterpret_cast<const uint32_t*>(b + 4 + 4 * part);  // 20*blk is 4-aligned
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint32_t byte = (q >> (8 * i)) & 0xffu;
+      w[i] = __fadd_rn(__fmul_rn((float)(byte & 15u), d), m);
+      w[4 + i] = __fadd_rn(__fmul_rn((float)(byte >> 4), d), m);
+    }
+  }
+};
+
+// Q8_0: f16 d @0, 32 int8 @2; w = f32(q) * d. gguf_codegen.rs:382-410.
+template <>
+struct Codec<E_Q8_0> {
+  static constexpr int BLOCK = 32, BYTES = 34, PARTS = 8, G = 1;
+  __device__ static __forceinline__ int xoff(int part, int) { return 4 * part; }
+  __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int part, float* w) {
+    const uint8_t* b = r.data + blk * BYTES;
+    const float d = f16_bits_to_f32(ld_u16(b));
+    const uint32_t q = ld_u32_a2(b + 2 + 4 * part);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int v = (int)(int8_t)((q >> (8 * i)) & 0xffu);
+      w[i] = __fmul_rn((float)v, d);
+    }
+  }
+};
+
+// Q6_K: ql 128 B @0, qh 64 B @128, 16 int8 scales @192, f16 d @208.
+// element e = n*128 + h*64 + p*32 + j: ql byte n*64+p*32+j nibble h, qh byte
+// n*32+j field h*2+p, scale n*8+h*4+p*2+j/16; w = (f32(q-32)*f32(sc))*f32(d).
+// gguf_codegen.rs:474-526. A part is (n, 4 consecutive j); group g = (h, p).
+template <>
+struct Codec<E_Q6_K> {
+  static constexpr int BLOCK = 256, BYTES = 210, PARTS = 16, G = 4;
+  __device__ static __forceinline__ int xoff(int part, int g) {
+    return (part >> 3) * 128 + (g >> 1) * 64 + (g & 1) * 32 + 4 * (part & 7);
+  }
+  __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int part, float* w) {
+    const uint8_t* b = r.data + blk * BYTES;
+    const int n = part >> 3, j4 = part & 7;
+    const float d = f16_bits_to_f32(ld_u16(b + 208));
+    const uint32_t ql0 = ld_u32_a2(b + n * 64 + 4 * j4);
+    const uint32_t ql1 = ld_u32_a2(b + n * 64 + 32 + 4 * j4);
+    const uint32_t qh = ld_u32_a2(b + 128 + n * 32 + 4 * j4);
+    const int8_t* sc = reinterpret_cast<const int8_t*>(b + 192) + n * 8 + (j4 >> 2);
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+      const int h = g >> 1, p = g & 1;
+      const uint32_t ql = p ? ql1 : ql0;
+      const float s = (float)sc[h * 4 + p * 2];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const int lo = (int)((ql >> (8 * i + 4 * h)) & 15u);
+        const int hi = (int)((qh >> (8 * i + 2 * (h * 2 + p))) & 3u);
+        w[4 * g + i] = __fmul_rn(__fmul_rn((float)(lo + 16 * hi - 32), s), d);
+      }
+    }
+  }
+};
+
+// MLX affine U4: ui32[N, K/8], lane k of a word = bits [4k, 4k+4); per group:
+// w = f32(q)*scale + bias. mlx_affine.rs:284-290,590-600. One word is one "block".
+template <>
+struct Codec<E_MLX_U4> {
+  static constexpr int BLOCK = 8, BYTES = 4, PARTS = 1, G = 2;
+  __device__ static __forceinline__ int xoff(int, int g) { return 4 * g; }
+  __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int, float* w) {
+    const uint32_t q = reinterpret_cast<const uint32_t*>(r.data)[blk];
+    const int64_t gi = (blk * 8) / r.group;
+    const float s = aux_load(r.sc, r.aux, gi);
+    const float bb = aux_load(r.bi, r.aux, gi);
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+      w[i] = __fadd_rn(__fmul_rn((float)((q >> (4 * i)) & 15u), s), bb);
+  }
+};
+
+// Plain element types: exact widening (arith.extf,
+// crates/dyninfer-compiler/src/lowering/kernels.rs:1157-1173). Block = 4 elements.
+template <>
+struct Codec<E_F32> {
+  static constexpr int BLOCK = 4, BYTES = 16, PARTS = 1, G = 1;
+  __device__ static __forceinline__ int xoff(int, int) { return 0; }
+  __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int, float* w) {
+    const float4 v = reinterpret_cast<const float4*>(r.data)[blk];
+    w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
+  }
+};
+template <>
+struct Codec<E_F16> {
+  static constexpr int BLOCK = 4, BYTES = 8, PARTS = 1, G = 1;
+  __device__ static __forceinline__ int xoff(int, int) { return 0; }
+  __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int, float* w) {
+    const uint2 v = reinterpret_cast<const uint2*>(r.data)[blk];
+    w[0] = f16_bits_to_f32(v.x & 0xffffu), w[1] = f16_bits_to_f32(v.x >> 16);
+    w[2] = f16_bits_to_f32(v.y & 0xffffu), w[3] = f16_bits_to_f32(v.y >> 16);
+  }
+};
+template <>
+struct Codec<E_BF16> {
+  static constexpr int BLOCK = 4, BYTES = 8, PARTS = 1, G = 1;
+  __device__ static __forceinline__ int xoff(int, int) { return 0; }
+  __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int, float* w) {
+    const uint2 v = reinterpret_cast<const uint2*>(r.data)[blk];
+    w[0] = bf16_bits_to_f32(v.x & 0xffffu), w[1] = bf16_bits_to_f32(v.x >> 16);
+    w[2] = bf16_bits_to_f32(v.y & 0xffffu), w[3] = bf16_bits_to_f32(v.y >> 16);
+  }
+};
+
+// Dispatch a functor templated on the encoding.
+#define DYN_ENC_SWITCH(enc, ...)                        \
+  switch (enc) {                                        \
+    case E_F32: { constexpr int ENC = E_F32; __VA_ARGS__; } break;       \
+    case E_F16: { constexpr int ENC = E_F16; __VA_ARGS__; } break;       \
+    case E_BF16: { constexpr int ENC = E_BF16; __VA_ARGS__; } break;     \
+    case E_Q4_0: { constexpr int ENC = E_Q4_0; __VA_ARGS__; } break;     \
+    case E_Q4_1: { constexpr int ENC = E_Q4_1; __VA_ARGS__; } break;     \
+    case E_Q8_0: { constexpr int ENC = E_Q8_0; __VA_ARGS__; } break;     \
+    case E_Q6_K: { constexpr int ENC = E_Q6_K; __VA_ARGS__; } break;     \
+    case E_MLX_U4: { constexpr int ENC = E_MLX_U4; __VA_ARGS__; } break; \
+    default:                                            \
+      dyn::set_error("unknown encoding %d", (int)(enc)); \
+      return 1;                                         \
+  }
+
+}  // namespace dyn

@@ -1,0 +1,188 @@
+// Shared declarations for libdyninfer_cuda (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/dyninfer_cuda.h"
+
+namespace dyn {
+
+// ---- error channel: int rc + thread-local message ---------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
+
+#define DYN_CUDA(expr)                                                      \
+  do {                                                                      \
+    cudaError_t _e = (expr);                                                \
+    if (_e != cudaSuccess) return dyn::cuda_fail(_e, #expr, __FILE__, __LINE__); \
+  } while (0)
+
+#define DYN_CHECK(cond, ...)       \
+  do {                             \
+    if (!(cond)) {                 \
+      dyn::set_error(__VA_ARGS__); \
+      return 1;                    \
+    }                              \
+  } while (0)
+
+// Counts kernels launched by this library (per thread-attached counter).
+void count_launch(int n = 1);
+uint64_t* launch_counter_slot();  // where count_launch accumulates (thread-local pointer)
+
+// ---- encodings ----------------------------------------------------------------
+enum : int {
+  E_F32 = DYNINFER_ENC_F32,
+  E_F16 = DYNINFER_ENC_F16,
+  E_BF16 = DYNINFER_ENC_BF16,
+  E_Q4_0 = DYNINFER_ENC_Q4_0,
+  E_Q4_1 = DYNINFER_ENC_Q4_1,
+  E_Q8_0 = DYNINFER_ENC_Q8_0,
+  E_Q6_K = DYNINFER_ENC_Q6_K,
+  E_MLX_U4 = DYNINFER_ENC_MLX_U4,
+};
+
+__host__ __device__ inline int enc_block_elems(int enc) {
+  switch (enc) {
+    case E_Q4_0:
+    case E_Q4_1:
+    case E_Q8_0:
+      return 32;
+    case E_Q6_K:
+      return 256;
+    case E_MLX_U4:
+      return 8;
+    default:
+      return 1;
+  }
+}
+__host__ __device__ inline int enc_block_bytes(int enc) {
+  switch (enc) {
+    case E_F32:
+      return 4;
+    case E_F16:
+    case E_BF16:
+      return 2;
+    case E_Q4_0:
+      return 18;
+    case E_Q4_1:
+      return 20;
+    case E_Q8_0:
+      return 34;
+    case E_Q6_K:
+      return 210;
+    case E_MLX_U4:
+      return 4;
+    default:
+      return 0;
+  }
+}
+__host__ __device__ inline int64_t enc_row_bytes(int enc, int64_t cols) {
+  int be = enc_block_elems(enc);
+  return (cols % be) ? 0 : cols / be * enc_block_bytes(enc);
+}
+inline int aux_elem_bytes(int t) { return t == E_F32 ? 4 : 2; }
+
+// A weight as the kernels see it.
+struct WRef {
+  const uint8_t* data = nullptr;
+  const uint8_t* scales = nullptr;
+  const uint8_t* biases = nullptr;
+  int enc = 0, aux = E_BF16, group = 64;
+  int64_t rows = 0, cols = 0;
+  __host__ __device__ int64_t row_bytes() const { return enc_row_bytes(enc, cols); }
+  uint64_t total_bytes() const {
+    uint64_t b = (uint64_t)rows * (uint64_t)enc_row_bytes(enc, cols);
+    if (enc == E_MLX_U4) b += 2ull * rows * (cols / group) * aux_elem_bytes(aux);
+    return b;
+  }
+};
+
+int wref_from_api(const dyninfer_cuda_weight_t* w, WRef* out);
+
+// ---- small device helpers -------------------------------------------------------
+__device__ __forceinline__ uint32_t ld_u16(const uint8_t* p) {
+  return *reinterpret_cast<const uint16_t*>(p);
+}
+__device__ __forceinline__ uint32_t ld_u32_a2(const uint8_t* p) {  // 2-byte aligned 32-bit load
+  return ld_u16(p) | (ld_u16(p + 2) << 16);
+}
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t b) {
+  return __half2float(__ushort_as_half((unsigned short)b));
+}
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+__device__ __forceinline__ float aux_load(const uint8_t* base, int type, int64_t idx) {
+  if (type == E_F32) return reinterpret_cast<const float*>(base)[idx];
+  uint32_t b = reinterpret_cast<const uint16_t*>(base)[idx];
+  return type == E_F16 ? f16_bits_to_f32(b) : bf16_bits_to_f32(b);
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+struct FreqTable {  // inverse RoPE frequencies, one per rotated pair (head_dim <= 256)
+  float f[128];
+};
+void fill_freq_table(FreqTable* t, int64_t d, float theta);
+
+// ---- launchers (one per kernel family) -------------------------------------------
+int launch_dequant(const WRef& w, float* out, cudaStream_t s);
+int launch_gather(const WRef& w, const int64_t* tokens, int64_t count, float* out, cudaStream_t s);
+
+// y[m, N] = x[m, K] * W^T ; optional residual (added to result) ; x f32 or bf16.
+int launch_linear(const WRef& w, const void* x, int x_type, int64_t m, float* y,
+                  const float* residual, cudaStream_t s);
+// y = silu(x Wg^T) * (x Wu^T)
+int launch_linear_swiglu(const WRef& wg, const WRef& wu, const float* x, int64_t m, float* y,
+                         cudaStream_t s);
+
+int launch_rms_norm(const float* x, const void* w, int w_type, int64_t rows, int64_t width,
+                    float eps, float* y, cudaStream_t s);
+int launch_rope(float* x, int64_t s_rows, int64_t heads, int64_t d, int64_t start_pos,
+                const FreqTable& ft, cudaStream_t s);
+int launch_silu_mul(const float* gate, const float* up, int64_t n, float* y, cudaStream_t s);
+
+struct QkvPrepArgs {
+  float* q;        // [rows, nh, d]   normalised + rotated in place
+  const float* k;  // [rows, nkv, d]
+  const float* v;  // [rows, nkv, d]
+  void* kcache;    // layer base: [seq][nkv][cap][d]
+  void* vcache;
+  const void* q_norm_w;  // nullable
+  const void* k_norm_w;
+  int norm_w_type;
+  const int64_t* row_pos;  // [rows] absolute position of each row; NULL: base_pos + row
+  const int64_t* row_seq;  // [rows] cache slot of each row; NULL: slot 0
+  int64_t base_pos;
+  int64_t rows, nh, nkv, d, cap;
+  int kv_type, has_norm, has_rope;
+  float eps;
+};
+int launch_qkv_prepare(const QkvPrepArgs& a, const FreqTable& ft, cudaStream_t s);
+
+struct AttnArgs {
+  const float* q;  // [rows, nh, d]
+  const void* kcache;
+  const void* vcache;
+  const int64_t* row_pos;  // NULL: base_pos + row
+  const int64_t* row_seq;  // NULL: slot 0
+  int64_t base_pos;
+  float* ctx;  // [rows, nh*d]
+  int64_t rows, nh, nkv, d, cap;
+  int kv_type;
+};
+int launch_attention(const AttnArgs& a, cudaStream_t s);
+
+size_t argmax_scratch_bytes(int64_t n);
+int launch_argmax(const float* v, int64_t n, int64_t* out, void* scratch, cudaStream_t s);
+
+}  // namespace dyn

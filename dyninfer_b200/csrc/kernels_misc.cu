@@ -1,0 +1,373 @@
+// RMSNorm, RoPE, QK-norm + RoPE + KV write, GQA attention, SiLU*up, argmax.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace dyn {
+
+void fill_freq_table(FreqTable* t, int64_t d, float theta) {
+  // den = powf(theta, (2*i)/d); freq = 1/den, all in f32
+  // (crates/dyninfer-compiler/src/lowering/kernels.rs:1047-1052). Computed on the host
+  // once per call, like the reference's static variants which bake the table
+  // at compile time (kernels.rs:936-960).
+  const int64_t half = d / 2;
+  for (int64_t i = 0; i < 128; i++) {
+    if (i < half) {
+      float exponent = (2.0f * (float)i) / (float)d;
+      float den = powf(theta, exponent);
+      t->f[i] = 1.0f / den;
+    } else {
+      t->f[i] = 0.f;
+    }
+  }
+}
+
+__device__ __forceinline__ float block_sum(float v, float* smem) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; i++) t += smem[i];
+  return t;
+}
+
+// y = (x * inv) * w with inv = 1 / sqrt(sum(x^2)/H + eps)  (kernels.rs:817-829)
+__global__ void __launch_bounds__(256)
+rms_norm_kernel(const float* x, const void* __restrict__ w, int w_type, int64_t width, float eps,
+                float* y) {
+  __shared__ float red[32];
+  const float* xr = x + (int64_t)blockIdx.x * width;
+  float* yr = y + (int64_t)blockIdx.x * width;
+  float ss = 0.f;
+  for (int64_t i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+  ss = block_sum(ss, red);
+  const float ms = ss / (float)width;
+  const float inv = 1.0f / sqrtf(ms + eps);
+  for (int64_t i = threadIdx.x; i < width; i += blockDim.x) {
+    const float wv = aux_load(reinterpret_cast<const uint8_t*>(w), w_type, i);
+    yr[i] = __fmul_rn(__fmul_rn(xr[i], inv), wv);
+  }
+}
+
+int launch_rms_norm(const float* x, const void* w, int w_type, int64_t rows, int64_t width,
+                    float eps, float* y, cudaStream_t s) {
+  if (rows == 0) return 0;
+  const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 32);
+  rms_norm_kernel<<<(unsigned)rows, threads, 0, s>>>(x, w, w_type, width, eps, y);
+  count_launch();
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Rotate-half RoPE (kernels.rs:1053-1064): pair (i, i + d/2).
+__device__ __forceinline__ void rope_pair(float x1, float x2, float pos, float freq, float* lo,
+                                          float* hi) {
+  const float angle = __fmul_rn(pos, freq);
+  float sv, cv;
+  sincosf(angle, &sv, &cv);
+  *lo = __fsub_rn(__fmul_rn(x1, cv), __fmul_rn(x2, sv));
+  *hi = __fadd_rn(__fmul_rn(x1, sv), __fmul_rn(x2, cv));
+}
+
+__global__ void rope_kernel(float* x, int64_t heads, int64_t d, int64_t start_pos, FreqTable ft) {
+  const int64_t p = blockIdx.x, h = blockIdx.y, half = d / 2;
+  float* v = x + (p * heads + h) * d;
+  const float pos = (float)(start_pos + p);
+  for (int64_t i = threadIdx.x; i < half; i += blockDim.x) {
+    float lo, hi;
+    rope_pair(v[i], v[i + half], pos, ft.f[i], &lo, &hi);
+    v[i] = lo;
+    v[i + half] = hi;
+  }
+}
+
+int launch_rope(float* x, int64_t s_rows, int64_t heads, int64_t d, int64_t start_pos,
+                const FreqTable& ft, cudaStream_t s) {
+  if (s_rows == 0) return 0;
+  dim3 grid((unsigned)s_rows, (unsigned)heads);
+  rope_kernel<<<grid, 64, 0, s>>>(x, heads, d, start_pos, ft);
+  count_launch();
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
+__global__ void silu_mul_kernel(const float* __restrict__ g, const float* __restrict__ u, int64_t n,
+                                float* __restrict__ y) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const float gv = g[i];
+    y[i] = (gv / (1.0f + expf(-gv))) * u[i];
+  }
+}
+
+int launch_silu_mul(const float* gate, const float* up, int64_t n, float* y, cudaStream_t s) {
+  if (n == 0) return 0;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  silu_mul_kernel<<<(unsigned)blocks, 256, 0, s>>>(gate, up, n, y);
+  count_launch();
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ---- KV element store / load ---------------------------------------------------
+template <int KV>
+struct KvT;
+template <>
+struct KvT<E_F32> {
+  using T = float;
+  __device__ static __forceinline__ T enc(float v) { return v; }
+  __device__ static __forceinline__ float dec(T v) { return v; }
+};
+template <>
+struct KvT<E_F16> {
+  using T = __half;
+  __device__ static __forceinline__ T enc(float v) { return __float2half_rn(v); }
+  __device__ static __forceinline__ float dec(T v) { return __half2float(v); }
+};
+template <>
+struct KvT<E_BF16> {
+  using T = __nv_bfloat16;
+  __device__ static __forceinline__ T enc(float v) { return __float2bfloat16_rn(v); }
+  __device__ static __forceinline__ float dec(T v) { return __bfloat162float(v); }
+};
+
+// One block per (row, head). Heads [0, nh) are query heads (per-head RMSNorm then
+// RoPE, written back in place); [nh, nh+nkv) key heads (norm, RoPE, stored into the
+// cache at the row's position); [nh+nkv, nh+2nkv) value heads (stored unchanged).
+// Order norm -> rope follows crates/dyninfer-compiler/src/lowering/dense_decoder.rs:2431-2452,
+// the write follows dense_decoder.rs:1115-1197.
+template <int KV>
+__global__ void __launch_bounds__(128) qkv_prepare_kernel(QkvPrepArgs a, FreqTable ft) {
+  using T = typename KvT<KV>::T;
+  __shared__ float red[32];
+  const int64_t r = blockIdx.x, hh = blockIdx.y, d = a.d, half = d / 2;
+  const int64_t pos = a.row_pos ? a.row_pos[r] : a.base_pos + r;
+  const int64_t seq = a.row_seq ? a.row_seq[r] : 0;
+  const int kind = hh < a.nh ? 0 : (hh < a.nh + a.nkv ? 1 : 2);
+  const int64_t head = kind == 0 ? hh : (kind == 1 ? hh - a.nh : hh - a.nh - a.nkv);
+  if (kind == 2) {
+    const float* src = a.v + (r * a.nkv + head) * d;
+    T* dst = reinterpret_cast<T*>(a.vcache) + ((seq * a.nkv + head) * a.cap + pos) * d;
+    for (int64_t i = threadIdx.x; i < d; i += blockDim.x) dst[i] = KvT<KV>::enc(src[i]);
+    return;
+  }
+  float* qv = a.q + (r * a.nh + head) * d;
+  const float* src = kind == 0 ? qv : a.k + (r * a.nkv + head) * d;
+  const void* nw = kind == 0 ? a.q_norm_w : a.k_norm_w;
+  float inv = 1.f;
+  if (a.has_norm) {
+    float ss = 0.f;
+    for (int64_t i = threadIdx.x; i < d; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+    ss = block_sum(ss, red);
+    inv = 1.0f / sqrtf(ss / (float)d + a.eps);
+  }
+  T* kdst = kind == 1 ? reinterpret_cast<T*>(a.kcache) + ((seq * a.nkv + head) * a.cap + pos) * d
+                      : nullptr;
+  for (int64_t i = threadIdx.x; i < half; i += blockDim.x) {
+    float x1 = src[i], x2 = src[i + half];
+    if (a.has_norm) {
+      const uint8_t* nwb = reinterpret_cast<const uint8_t*>(nw);
+      x1 = __fmul_rn(__fmul_rn(x1, inv), aux_load(nwb, a.norm_w_type, i));
+      x2 = __fmul_rn(__fmul_rn(x2, inv), aux_load(nwb, a.norm_w_type, i + half));
+    }
+    float lo = x1, hi = x2;
+    if (a.has_rope) rope_pair(x1, x2, (float)pos, ft.f[i], &lo, &hi);
+    if (kind == 0) {
+      qv[i] = lo;
+      qv[i + half] = hi;
+    } else {
+      kdst[i] = KvT<KV>::enc(lo);
+      kdst[i + half] = KvT<KV>::enc(hi);
+    }
+  }
+}
+
+int launch_qkv_prepare(const QkvPrepArgs& a, const FreqTable& ft, cudaStream_t s) {
+  if (a.rows == 0) return 0;
+  DYN_CHECK(a.d % 2 == 0 && a.d <= 256, "head_dim %lld unsupported (even, <= 256)", (long long)a.d);
+  dim3 grid((unsigned)a.rows, (unsigned)(a.nh + 2 * a.nkv));
+  const int threads = a.d >= 128 ? 64 : 32;
+  if (a.kv_type == E_F32)
+    qkv_prepare_kernel<E_F32><<<grid, threads, 0, s>>>(a, ft);
+  else if (a.kv_type == E_F16)
+    qkv_prepare_kernel<E_F16><<<grid, threads, 0, s>>>(a, ft);
+  else if (a.kv_type == E_BF16)
+    qkv_prepare_kernel<E_BF16><<<grid, threads, 0, s>>>(a, ft);
+  else
+    DYN_CHECK(false, "kv_type %d unsupported", a.kv_type);
+  count_launch();
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ---- attention -------------------------------------------------------------------
+// One block per (query head, row). Keys 0..pos of the row's sequence are visible
+// (causal mask kernels.rs:460-506; every key <= pos has been written). Warps take
+// keys round-robin, keep an online (max, sum, acc) state (merge rule kernels.rs
+// :375-454), and the four states are merged through shared memory; the result is
+// acc / sum (dense_decoder.rs:1317-1328). scale = 1/sqrt(d).
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_DPL = 8;  // dims per lane, head_dim <= 256
+
+template <int KV>
+__global__ void __launch_bounds__(ATT_WARPS * 32) attention_kernel(AttnArgs a) {
+  using T = typename KvT<KV>::T;
+  __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS];
+  __shared__ float s_acc[ATT_WARPS][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t h = blockIdx.x, r = blockIdx.y, d = a.d;
+  const int64_t kvh = h / (a.nh / a.nkv);
+  const int64_t pos = a.row_pos ? a.row_pos[r] : a.base_pos + r;
+  const int64_t seq = a.row_seq ? a.row_seq[r] : 0;
+  const float scale = 1.0f / sqrtf((float)d);
+  const float* qv = a.q + (r * a.nh + h) * d;
+  const T* kb = reinterpret_cast<const T*>(a.kcache) + (seq * a.nkv + kvh) * a.cap * d;
+  const T* vb = reinterpret_cast<const T*>(a.vcache) + (seq * a.nkv + kvh) * a.cap * d;
+  float qreg[ATT_DPL], acc[ATT_DPL];
+#pragma unroll
+  for (int j = 0; j < ATT_DPL; j++) {
+    const int64_t idx = lane + 32 * j;
+    qreg[j] = idx < d ? qv[idx] : 0.f;
+    acc[j] = 0.f;
+  }
+  float m = -3.40282347e38f, l = 0.f;
+  for (int64_t key = warp; key <= pos; key += ATT_WARPS) {
+    const T* kr = kb + key * d;
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < ATT_DPL; j++) {
+      const int64_t idx = lane + 32 * j;
+      if (idx < d) dot = fmaf(qreg[j], KvT<KV>::dec(kr[idx]), dot);
+    }
+    dot = warp_sum(dot);
+    const float sc = dot * scale;
+    const float mn = fmaxf(m, sc);
+    const float factor = expf(m - mn);
+    const float p = expf(sc - mn);
+    l = l * factor + p;
+    const T* vr = vb + key * d;
+#pragma unroll
+    for (int j = 0; j < ATT_DPL; j++) {
+      const int64_t idx = lane + 32 * j;
+      if (idx < d) acc[j] = acc[j] * factor + p * KvT<KV>::dec(vr[idx]);
+    }
+    m = mn;
+  }
+  if (lane == 0) {
+    s_m[warp] = m;
+    s_l[warp] = l;
+  }
+#pragma unroll
+  for (int j = 0; j < ATT_DPL; j++) {
+    const int idx = lane + 32 * j;
+    if (idx < d) s_acc[warp][idx] = acc[j];
+  }
+  __syncthreads();
+  float gm = s_m[0];
+  for (int w = 1; w < ATT_WARPS; w++) gm = fmaxf(gm, s_m[w]);
+  float gl = 0.f;
+  for (int w = 0; w < ATT_WARPS; w++) gl += s_l[w] * expf(s_m[w] - gm);
+  for (int64_t idx = threadIdx.x; idx < d; idx += blockDim.x) {
+    float o = 0.f;
+    for (int w = 0; w < ATT_WARPS; w++) o += s_acc[w][idx] * expf(s_m[w] - gm);
+    a.ctx[r * a.nh * d + h * d + idx] = o / gl;
+  }
+}
+
+int launch_attention(const AttnArgs& a, cudaStream_t s) {
+  if (a.rows == 0) return 0;
+  DYN_CHECK(a.d <= 256, "head_dim %lld unsupported (<= 256)", (long long)a.d);
+  DYN_CHECK(a.nkv > 0 && a.nh % a.nkv == 0, "heads %lld not a multiple of kv heads %lld",
+            (long long)a.nh, (long long)a.nkv);
+  dim3 grid((unsigned)a.nh, (unsigned)a.rows);
+  if (a.kv_type == E_F32)
+    attention_kernel<E_F32><<<grid, ATT_WARPS * 32, 0, s>>>(a);
+  else if (a.kv_type == E_F16)
+    attention_kernel<E_F16><<<grid, ATT_WARPS * 32, 0, s>>>(a);
+  else if (a.kv_type == E_BF16)
+    attention_kernel<E_BF16><<<grid, ATT_WARPS * 32, 0, s>>>(a);
+  else
+    DYN_CHECK(false, "kv_type %d unsupported", a.kv_type);
+  count_launch();
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ---- argmax: first strict maximum (dense_decoder.rs:885-893) ---------------------
+struct ArgPair {
+  float v;
+  int pad;
+  long long i;
+};
+__device__ __forceinline__ bool arg_better(float v, long long i, float bv, long long bi) {
+  return v > bv || (v == bv && i < bi);
+}
+constexpr int ARGMAX_BLOCKS = 296;
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ v, int64_t n, ArgPair* part) {
+  __shared__ float sv[256];
+  __shared__ long long si[256];
+  float bv = -INFINITY;
+  long long bi = 0x7fffffffffffffffLL;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const float x = v[i];
+    if (x > -INFINITY && arg_better(x, i, bv, bi)) bv = x, bi = i;
+  }
+  sv[threadIdx.x] = bv;
+  si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o && arg_better(sv[threadIdx.x + o], si[threadIdx.x + o],
+                                           sv[threadIdx.x], si[threadIdx.x])) {
+      sv[threadIdx.x] = sv[threadIdx.x + o];
+      si[threadIdx.x] = si[threadIdx.x + o];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    part[blockIdx.x].v = sv[0];
+    part[blockIdx.x].i = si[0];
+  }
+}
+
+__global__ void __launch_bounds__(512)
+argmax_final_kernel(const ArgPair* part, int count, int64_t* out) {
+  __shared__ float sv[512];
+  __shared__ long long si[512];
+  float bv = -INFINITY;
+  long long bi = 0x7fffffffffffffffLL;
+  if ((int)threadIdx.x < count) bv = part[threadIdx.x].v, bi = part[threadIdx.x].i;
+  sv[threadIdx.x] = bv;
+  si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int o = 256; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o && arg_better(sv[threadIdx.x + o], si[threadIdx.x + o],
+                                           sv[threadIdx.x], si[threadIdx.x])) {
+      sv[threadIdx.x] = sv[threadIdx.x + o];
+      si[threadIdx.x] = si[threadIdx.x + o];
+    }
+    __syncthreads();
+  }
+  // all values NaN or -inf: the scan never moves off index 0 (generate.rs:16-26)
+  if (threadIdx.x == 0) out[0] = si[0] == 0x7fffffffffffffffLL ? 0 : si[0];
+}
+
+size_t argmax_scratch_bytes(int64_t) { return sizeof(ArgPair) * ARGMAX_BLOCKS; }
+
+int launch_argmax(const float* v, int64_t n, int64_t* out, void* scratch, cudaStream_t s) {
+  DYN_CHECK(n >= 1, "argmax: n must be >= 1");
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > ARGMAX_BLOCKS) blocks = ARGMAX_BLOCKS;
+  argmax_partial_kernel<<<blocks, 256, 0, s>>>(v, n, reinterpret_cast<ArgPair*>(scratch));
+  argmax_final_kernel<<<1, 512, 0, s>>>(reinterpret_cast<const ArgPair*>(scratch), blocks, out);
+  count_launch(2);
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace dyn

@@ -1,0 +1,831 @@
+// Session: owns the uploaded parameters (verbatim byte ranges), the paged KV pool,
+// the activation scratch and the captured decode graph. Shape and conventions follow
+// the reference's native session, third_party/iree_runtime_c_api/wrapper.c:914-1303.
+#include <errno.h>
+#include <fcntl.h>
+#include <string.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "json_min.h"
+
+namespace dyn {
+void set_launch_counter(uint64_t* p);
+
+struct NormW {
+  const void* ptr = nullptr;
+  int type = E_F32;
+  uint64_t bytes = 0;
+};
+
+struct LayerW {
+  NormW attn_norm, ffn_norm, q_norm, k_norm;
+  WRef q, k, v, o, gate, up, down;
+};
+
+struct ModelCfg {
+  int layers = 0, hidden = 0, inter = 0, heads = 0, kv_heads = 0, head_dim = 0, vocab = 0;
+  float eps = 1e-6f, theta = 10000.f;
+  bool qk_norm = true, rope = true;
+  int batch = 1;
+  int kv2_type = E_BF16;  // element type used when the KV cache is configured with 2 bytes
+};
+
+}  // namespace dyn
+
+using namespace dyn;
+
+struct dyninfer_cuda_session_t {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  ModelCfg cfg;
+  FreqTable freq;
+  // parameters
+  uint8_t* arena = nullptr;
+  uint64_t arena_bytes = 0;
+  uint64_t weight_bytes = 0;         // sum of uploaded range lengths
+  uint64_t decode_weight_bytes = 0;  // linears + lm_head + norm vectors
+  WRef embed, lm_head;
+  NormW out_norm;
+  std::vector<LayerW> layers;
+  // KV pool
+  bool kv_configured = false;
+  size_t page_size = 0, chunk_size = 0, kv_elem = 0, pages = 0;
+  int kv_type = E_F32;
+  uint8_t* kcache = nullptr;  // [layer][seq][nkv][cap][d]
+  uint8_t* vcache = nullptr;
+  size_t kv_bytes_each = 0;
+  // scratch
+  int64_t max_rows = 0;
+  float *hidden = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ctx = nullptr,
+        *act = nullptr, *logits = nullptr;
+  int64_t *tokens_dev = nullptr, *row_pos_dev = nullptr, *row_seq_dev = nullptr,
+          *out_token_dev = nullptr, *hist_dev = nullptr, *hist_count_dev = nullptr;
+  size_t hist_cap = 0;
+  void* argmax_scratch = nullptr;
+  // pinned host staging
+  float* logits_host = nullptr;
+  int64_t* stage_host = nullptr;  // [0]=token [1]=pos [2]=seq [3]=out token, then chunk arrays
+  // graphs
+  cudaGraphExec_t decode_graph = nullptr;  // H2D token/pos + forward + D2H token
+  cudaGraphExec_t loop_graph = nullptr;    // forward + device-side advance
+  uint64_t graph_nodes = 0, loop_nodes = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  // statistics
+  dyninfer_cuda_allocator_statistics_t stats{};
+  uint64_t launches = 0;
+};
+
+namespace {
+
+typedef dyninfer_cuda_session_t Session;
+
+int dev_alloc(Session* s, void** out, size_t bytes) {
+  DYN_CUDA(cudaMalloc(out, bytes ? bytes : 16));
+  s->stats.device_bytes_allocated += bytes;
+  uint64_t live = s->stats.device_bytes_allocated - s->stats.device_bytes_freed;
+  s->stats.device_bytes_peak = std::max(s->stats.device_bytes_peak, live);
+  return 0;
+}
+void dev_free(Session* s, void* p, size_t bytes) {
+  if (!p) return;
+  cudaFree(p);
+  s->stats.device_bytes_freed += bytes;
+}
+int host_alloc(Session* s, void** out, size_t bytes) {
+  DYN_CUDA(cudaMallocHost(out, bytes ? bytes : 16));
+  s->stats.host_bytes_allocated += bytes;
+  uint64_t live = s->stats.host_bytes_allocated - s->stats.host_bytes_freed;
+  s->stats.host_bytes_peak = std::max(s->stats.host_bytes_peak, live);
+  return 0;
+}
+
+int enc_from_name(const std::string& n) {
+  if (n == "plain.f32") return E_F32;
+  if (n == "plain.f16") return E_F16;
+  if (n == "plain.bf16") return E_BF16;
+  if (n == "gguf.q4_0") return E_Q4_0;
+  if (n == "gguf.q4_1") return E_Q4_1;
+  if (n == "gguf.q8_0") return E_Q8_0;
+  if (n == "gguf.q6_k") return E_Q6_K;
+  if (n == "mlx.affine.u4") return E_MLX_U4;
+  return -1;
+}
+
+struct Upload {  // one byte range placed in the arena
+  uint64_t arena_off = 0, length = 0;
+  size_t file = 0;
+  uint64_t file_off = 0;
+};
+
+struct ParamDesc {
+  int enc = -1, aux = E_BF16, group = 0;
+  std::vector<int64_t> shape;
+  std::map<std::string, Upload> comps;  // component name -> upload
+};
+
+int read_range(int fd, uint64_t off, uint64_t len, uint8_t* dst_dev, uint8_t* staging,
+               size_t staging_bytes, const char* path) {
+  uint64_t done = 0;
+  while (done < len) {
+    size_t n = (size_t)std::min<uint64_t>(staging_bytes, len - done);
+    size_t got = 0;
+    while (got < n) {
+      ssize_t r = pread(fd, staging + got, n - got, (off_t)(off + done + got));
+      if (r < 0 && errno == EINTR) continue;
+      DYN_CHECK(r > 0, "short read of %s at offset %llu (%s)", path,
+                (unsigned long long)(off + done + got), r == 0 ? "end of file" : strerror(errno));
+      got += (size_t)r;
+    }
+    DYN_CUDA(cudaMemcpy(dst_dev + done, staging, n, cudaMemcpyHostToDevice));
+    done += n;
+  }
+  return 0;
+}
+
+int bind_linear(const std::map<std::string, ParamDesc>& params, const uint8_t* arena,
+                const std::string& name, int64_t rows, int64_t cols, WRef* out) {
+  auto it = params.find(name);
+  DYN_CHECK(it != params.end(), "model descriptor lacks parameter `%s`", name.c_str());
+  const ParamDesc& p = it->second;
+  DYN_CHECK(p.shape.size() == 2 && p.shape[0] == rows && p.shape[1] == cols,
+            "parameter `%s` has the wrong logical shape (expected [%lld, %lld])", name.c_str(),
+            (long long)rows, (long long)cols);
+  out->enc = p.enc;
+  out->rows = rows;
+  out->cols = cols;
+  int unit = std::max(4, enc_block_elems(p.enc));
+  DYN_CHECK(cols % unit == 0, "parameter `%s`: cols %lld not a multiple of %d", name.c_str(),
+            (long long)cols, unit);
+  const char* main_comp = p.enc == E_MLX_U4 ? "packed" : "data";
+  auto c = p.comps.find(main_comp);
+  DYN_CHECK(c != p.comps.end(), "no byte range given for `weights::%s::%s`", name.c_str(), main_comp);
+  const uint64_t expect = (uint64_t)rows * (uint64_t)enc_row_bytes(p.enc, cols);
+  DYN_CHECK(c->second.length == expect,
+            "byte range of `%s` is %llu bytes, encoding and shape need %llu", name.c_str(),
+            (unsigned long long)c->second.length, (unsigned long long)expect);
+  out->data = arena + c->second.arena_off;
+  if (p.enc == E_MLX_U4) {
+    DYN_CHECK(p.group >= 8 && p.group % 8 == 0 && cols % p.group == 0,
+              "parameter `%s`: MLX group %d does not divide cols", name.c_str(), p.group);
+    auto sc = p.comps.find("scales"), bi = p.comps.find("biases");
+    DYN_CHECK(sc != p.comps.end() && bi != p.comps.end(),
+              "parameter `%s` lacks scales/biases ranges", name.c_str());
+    const uint64_t aux_expect = (uint64_t)rows * (cols / p.group) * aux_elem_bytes(p.aux);
+    DYN_CHECK(sc->second.length == aux_expect && bi->second.length == aux_expect,
+              "parameter `%s`: scales/biases byte length mismatch", name.c_str());
+    out->scales = arena + sc->second.arena_off;
+    out->biases = arena + bi->second.arena_off;
+    out->aux = p.aux;
+    out->group = p.group;
+  }
+  return 0;
+}
+
+int bind_norm(const std::map<std::string, ParamDesc>& params, const uint8_t* arena,
+              const std::string& name, int64_t width, bool required, NormW* out) {
+  auto it = params.find(name);
+  if (it == params.end()) {
+    DYN_CHECK(!required, "model descriptor lacks parameter `%s`", name.c_str());
+    return 0;
+  }
+  const ParamDesc& p = it->second;
+  DYN_CHECK(p.enc == E_F32 || p.enc == E_F16 || p.enc == E_BF16,
+            "norm weight `%s` must be a plain float type", name.c_str());
+  DYN_CHECK(p.shape.size() == 1 && p.shape[0] == width, "norm weight `%s` has the wrong shape",
+            name.c_str());
+  auto c = p.comps.find("data");
+  DYN_CHECK(c != p.comps.end(), "no byte range given for `weights::%s::data`", name.c_str());
+  DYN_CHECK(c->second.length == (uint64_t)width * aux_elem_bytes(p.enc),
+            "norm weight `%s` byte length mismatch", name.c_str());
+  out->ptr = arena + c->second.arena_off;
+  out->type = p.enc;
+  out->bytes = c->second.length;
+  return 0;
+}
+
+void destroy_graphs(Session* s) {
+  if (s->decode_graph) cudaGraphExecDestroy(s->decode_graph);
+  if (s->loop_graph) cudaGraphExecDestroy(s->loop_graph);
+  s->decode_graph = s->loop_graph = nullptr;
+}
+
+// Device-side greedy feedback: the produced token becomes the next input, the
+// position advances, and the token is appended to the history buffer.
+__global__ void advance_kernel(int64_t* tokens, int64_t* row_pos, const int64_t* out_token,
+                               int64_t* hist, int64_t* hist_count, int64_t hist_cap) {
+  const int64_t t = out_token[0];
+  tokens[0] = t;
+  row_pos[0] += 1;
+  const int64_t c = hist_count[0];
+  if (c < hist_cap) hist[c] = t;
+  hist_count[0] = c + 1;
+}
+
+// Enqueue the whole decoder for `rows` rows whose tokens / positions / slots are
+// already in device memory; logits and argmax come from row `logits_row`.
+int enqueue_forward(Session* s, int64_t rows, int64_t logits_row) {
+  const ModelCfg& c = s->cfg;
+  cudaStream_t st = s->stream;
+  const int64_t H = c.hidden, qd = (int64_t)c.heads * c.head_dim,
+                kvd = (int64_t)c.kv_heads * c.head_dim;
+  const int64_t cap = (int64_t)(s->pages * s->page_size);
+  const size_t layer_stride = (size_t)c.batch * c.kv_heads * cap * c.head_dim * s->kv_elem;
+  if (launch_gather(s->embed, s->tokens_dev, rows, s->hidden, st)) return 1;
+  for (int l = 0; l < c.layers; l++) {
+    const LayerW& L = s->layers[l];
+    if (launch_rms_norm(s->hidden, L.attn_norm.ptr, L.attn_norm.type, rows, H, c.eps, s->xn, st))
+      return 1;
+    if (launch_linear(L.q, s->xn, E_F32, rows, s->q, nullptr, st)) return 1;
+    if (launch_linear(L.k, s->xn, E_F32, rows, s->k, nullptr, st)) return 1;
+    if (launch_linear(L.v, s->xn, E_F32, rows, s->v, nullptr, st)) return 1;
+    QkvPrepArgs pa{};
+    pa.q = s->q, pa.k = s->k, pa.v = s->v;
+    pa.kcache = s->kcache + (size_t)l * layer_stride;
+    pa.vcache = s->vcache + (size_t)l * layer_stride;
+    pa.q_norm_w = L.q_norm.ptr, pa.k_norm_w = L.k_norm.ptr, pa.norm_w_type = L.q_norm.type;
+    pa.row_pos = s->row_pos_dev, pa.row_seq = s->row_seq_dev, pa.base_pos = 0;
+    pa.rows = rows, pa.nh = c.heads, pa.nkv = c.kv_heads, pa.d = c.head_dim, pa.cap = cap;
+    pa.kv_type = s->kv_type, pa.has_norm = c.qk_norm ? 1 : 0, pa.has_rope = c.rope ? 1 : 0;
+    pa.eps = c.eps;
+    if (launch_qkv_prepare(pa, s->freq, st)) return 1;
+    AttnArgs aa{};
+    aa.q = s->q, aa.kcache = pa.kcache, aa.vcache = pa.vcache;
+    aa.row_pos = s->row_pos_dev, aa.row_seq = s->row_seq_dev, aa.base_pos = 0;
+    aa.ctx = s->ctx;
+    aa.rows = rows, aa.nh = c.heads, aa.nkv = c.kv_heads, aa.d = c.head_dim, aa.cap = cap;
+    aa.kv_type = s->kv_type;
+    if (launch_attention(aa, st)) return 1;
+    if (launch_linear(L.o, s->ctx, E_F32, rows, s->hidden, s->hidden, st)) return 1;
+    if (launch_rms_norm(s->hidden, L.ffn_norm.ptr, L.ffn_norm.type, rows, H, c.eps, s->xn, st))
+      return 1;
+    if (L.gate.enc == L.up.enc) {
+      if (launch_linear_swiglu(L.gate, L.up, s->xn, rows, s->act, st)) return 1;
+    } else {
+      // mixed encodings: two products, then the activation (q and ctx are free here)
+      if (launch_linear(L.gate, s->xn, E_F32, rows, s->act, nullptr, st)) return 1;
+      float* up_tmp = s->ctx;  // ctx holds rows*qd floats; only used when inter <= qd
+      DYN_CHECK((int64_t)c.inter <= qd, "gate/up with different encodings need inter <= heads*head_dim");
+      if (launch_linear(L.up, s->xn, E_F32, rows, up_tmp, nullptr, st)) return 1;
+      if (launch_silu_mul(s->act, up_tmp, rows * c.inter, s->act, st)) return 1;
+    }
+    if (launch_linear(L.down, s->act, E_F32, rows, s->hidden, s->hidden, st)) return 1;
+  }
+  // final norm of the one row that feeds the lm_head (dense_decoder.rs:1573-1615)
+  if (launch_rms_norm(s->hidden + logits_row * H, s->out_norm.ptr, s->out_norm.type, 1, H, c.eps,
+                      s->xn, st))
+    return 1;
+  if (launch_linear(s->lm_head, s->xn, E_F32, 1, s->logits, nullptr, st)) return 1;
+  if (launch_argmax(s->logits, c.vocab, s->out_token_dev, s->argmax_scratch, st)) return 1;
+  (void)kvd;
+  return 0;
+}
+
+int capture(Session* s, bool loop, cudaGraphExec_t* out, uint64_t* nodes) {
+  cudaGraph_t g = nullptr;
+  uint64_t before = s->launches;
+  DYN_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+  int rc = 0;
+  if (!loop) {
+    if (cudaMemcpyAsync(s->tokens_dev, s->stage_host, 8, cudaMemcpyHostToDevice, s->stream) !=
+            cudaSuccess ||
+        cudaMemcpyAsync(s->row_pos_dev, s->stage_host + 1, 8, cudaMemcpyHostToDevice, s->stream) !=
+            cudaSuccess ||
+        cudaMemcpyAsync(s->row_seq_dev, s->stage_host + 2, 8, cudaMemcpyHostToDevice, s->stream) !=
+            cudaSuccess)
+      rc = 1;
+  }
+  if (!rc) rc = enqueue_forward(s, 1, 0);
+  if (!rc) {
+    if (loop) {
+      advance_kernel<<<1, 1, 0, s->stream>>>(s->tokens_dev, s->row_pos_dev, s->out_token_dev,
+                                             s->hist_dev, s->hist_count_dev, (int64_t)s->hist_cap);
+      count_launch();
+    } else if (cudaMemcpyAsync(s->stage_host + 3, s->out_token_dev, 8, cudaMemcpyDeviceToHost,
+                               s->stream) != cudaSuccess) {
+      rc = 1;
+    }
+  }
+  cudaError_t e = cudaStreamEndCapture(s->stream, &g);
+  if (rc) {
+    if (g) cudaGraphDestroy(g);
+    std::string keep = dyninfer_cuda_last_error();
+    set_error("graph capture failed: %s", keep.c_str());
+    return 1;
+  }
+  DYN_CUDA(e);
+  *nodes = s->launches - before;
+  s->launches = before;  // capture enqueues nothing; replays are counted per launch
+  cudaError_t ie = cudaGraphInstantiate(out, g, 0);
+  cudaGraphDestroy(g);
+  DYN_CUDA(ie);
+  return 0;
+}
+
+int ensure_hist(Session* s, size_t steps) {
+  if (steps <= s->hist_cap) return 0;
+  if (s->hist_dev) dev_free(s, s->hist_dev, s->hist_cap * 8);
+  s->hist_dev = nullptr;
+  size_t cap = std::max<size_t>(steps, 4096);
+  if (dev_alloc(s, (void**)&s->hist_dev, cap * 8)) return 1;
+  s->hist_cap = cap;
+  if (s->loop_graph) {
+    cudaGraphExecDestroy(s->loop_graph);
+    s->loop_graph = nullptr;
+  }
+  return 0;
+}
+
+struct CounterScope {  // routes count_launch() to this session for the duration of a call
+  explicit CounterScope(Session* s) { set_launch_counter(&s->launches); }
+  ~CounterScope() { set_launch_counter(nullptr); }
+};
+
+}  // namespace
+
+extern "C" {
+
+int dyninfer_cuda_session_create_with_file_params(
+    const char* device_uri, const char* model_desc_json,
+    const dyninfer_cuda_parameter_file_t* files, size_t file_count,
+    const dyninfer_cuda_file_param_t* params, size_t param_count,
+    dyninfer_cuda_session_t** out_session) {
+  DYN_CHECK(out_session != nullptr, "out_session is NULL");
+  *out_session = nullptr;
+  DYN_CHECK(model_desc_json != nullptr, "model_desc_json is NULL");
+  DYN_CHECK(file_count == 0 || files != nullptr, "files is NULL");
+  DYN_CHECK(param_count == 0 || params != nullptr, "params is NULL");
+
+  int device = 0;
+  {
+    std::string uri = device_uri ? device_uri : "cuda";
+    if (uri.empty()) uri = "cuda";
+    DYN_CHECK(uri.compare(0, 4, "cuda") == 0,
+              "device `%s` is not a cuda device; this library has no other backend and no CPU fallback",
+              uri.c_str());
+    if (uri.size() > 4) {
+      DYN_CHECK(uri[4] == ':' && uri.size() > 5, "malformed device uri `%s`", uri.c_str());
+      char* end = nullptr;
+      long v = strtol(uri.c_str() + 5, &end, 10);
+      DYN_CHECK(end && *end == 0 && v >= 0, "malformed device ordinal in `%s`", uri.c_str());
+      device = (int)v;
+    }
+  }
+
+  Json desc;
+  {
+    std::string err;
+    JsonParser jp(model_desc_json);
+    DYN_CHECK(jp.parse(&desc, &err) && desc.kind == Json::Obj, "model descriptor: %s", err.c_str());
+  }
+  ModelCfg cfg;
+  cfg.layers = (int)desc.number("layers", 0);
+  cfg.hidden = (int)desc.number("hidden", 0);
+  cfg.inter = (int)desc.number("intermediate", 0);
+  cfg.heads = (int)desc.number("heads", 0);
+  cfg.kv_heads = (int)desc.number("kv_heads", cfg.heads);
+  cfg.head_dim = (int)desc.number("head_dim", cfg.heads ? cfg.hidden / cfg.heads : 0);
+  cfg.vocab = (int)desc.number("vocab", 0);
+  cfg.eps = (float)desc.number("eps", 1e-6);
+  cfg.theta = (float)desc.number("theta", 10000.0);
+  cfg.qk_norm = desc.number("qk_norm", 1) != 0;
+  cfg.rope = desc.number("rope", 1) != 0;
+  cfg.batch = (int)desc.number("batch", 1);
+  {
+    std::string kvd = desc.string("kv_dtype", "bf16");
+    DYN_CHECK(kvd == "bf16" || kvd == "f16" || kvd == "f32", "kv_dtype `%s` unsupported",
+              kvd.c_str());
+    cfg.kv2_type = kvd == "f16" ? E_F16 : E_BF16;
+  }
+  DYN_CHECK(cfg.layers > 0 && cfg.hidden > 0 && cfg.inter > 0 && cfg.heads > 0 &&
+                cfg.kv_heads > 0 && cfg.head_dim > 0 && cfg.vocab > 0 && cfg.batch > 0,
+            "model descriptor lacks geometry (layers/hidden/intermediate/heads/kv_heads/head_dim/vocab)");
+  DYN_CHECK(cfg.heads % cfg.kv_heads == 0, "heads %d is not a multiple of kv_heads %d", cfg.heads,
+            cfg.kv_heads);
+  DYN_CHECK(cfg.head_dim % 2 == 0 && cfg.head_dim <= 256, "head_dim %d unsupported", cfg.head_dim);
+  DYN_CHECK(cfg.hidden % 4 == 0 && cfg.inter % 4 == 0, "hidden and intermediate must be multiples of 4");
+
+  // parameters: descriptor entries joined with their byte ranges
+  std::map<std::string, ParamDesc> pd;
+  const Json* jparams = desc.get("params");
+  DYN_CHECK(jparams && jparams->kind == Json::Obj, "model descriptor lacks `params`");
+  for (auto& kv : jparams->obj) {
+    ParamDesc p;
+    std::string en = kv.second.string("encoding", "");
+    p.enc = enc_from_name(en);
+    // strict rejection: an encoding without a registered cuda kernel is an error, never a fallback
+    DYN_CHECK(p.enc >= 0, "E_KERNEL_COVERAGE: no cuda kernel for encoding `%s` (parameter `%s`)",
+              en.c_str(), kv.first.c_str());
+    p.group = (int)kv.second.number("group", 0);
+    std::string aux = kv.second.string("aux", "");
+    p.aux = aux == "plain.f32" ? E_F32 : (aux == "plain.f16" ? E_F16 : E_BF16);
+    const Json* sh = kv.second.get("shape");
+    DYN_CHECK(sh && sh->kind == Json::Arr, "parameter `%s` lacks a shape", kv.first.c_str());
+    for (auto& d : sh->arr) p.shape.push_back((int64_t)d.num);
+    pd.emplace(kv.first, std::move(p));
+  }
+
+  // open files, validate ranges (crates/iree-runtime/src/lib.rs:139-206)
+  std::vector<int> fds(file_count, -1);
+  std::vector<uint64_t> fsize(file_count, 0);
+  auto close_all = [&]() {
+    for (int fd : fds)
+      if (fd >= 0) close(fd);
+  };
+  for (size_t i = 0; i < file_count; i++) {
+    if (!files[i].path || (fds[i] = open(files[i].path, O_RDONLY)) < 0) {
+      set_error("cannot open parameter file `%s`: %s", files[i].path ? files[i].path : "(null)",
+                strerror(errno));
+      close_all();
+      return 1;
+    }
+    struct stat stt;
+    fstat(fds[i], &stt);
+    fsize[i] = (uint64_t)stt.st_size;
+  }
+  uint64_t arena_bytes = 0, weight_bytes = 0;
+  int rc = 0;
+  for (size_t i = 0; i < param_count && !rc; i++) {
+    const dyninfer_cuda_file_param_t& fp = params[i];
+    std::string key = fp.key ? fp.key : "";
+    size_t a = key.find("::"), b = key.rfind("::");
+    if (a == std::string::npos || b == a) {
+      set_error("parameter key `%s` is not `<scope>::<name>::<component>`", key.c_str());
+      rc = 1;
+      break;
+    }
+    std::string name = key.substr(a + 2, b - a - 2), comp = key.substr(b + 2);
+    auto it = pd.find(name);
+    if (it == pd.end()) {
+      set_error("byte range `%s` has no entry in the model descriptor", key.c_str());
+      rc = 1;
+    } else if (fp.source_file_index >= file_count) {
+      set_error("parameter `%s`: source_file_index %zu out of range", key.c_str(),
+                fp.source_file_index);
+      rc = 1;
+    } else if (fp.length == 0 || fp.offset + fp.length < fp.offset ||
+               fp.offset + fp.length > fsize[fp.source_file_index]) {
+      set_error("parameter `%s`: byte range [%llu, +%llu) exceeds file size %llu", key.c_str(),
+                (unsigned long long)fp.offset, (unsigned long long)fp.length,
+                (unsigned long long)fsize[fp.source_file_index]);
+      rc = 1;
+    } else if (it->second.comps.count(comp)) {
+      set_error("duplicate parameter key `%s`", key.c_str());
+      rc = 1;
+    } else {
+      Upload u;
+      u.arena_off = arena_bytes;
+      u.length = fp.length;
+      u.file = fp.source_file_index;
+      u.file_off = fp.offset;
+      it->second.comps.emplace(comp, u);
+      arena_bytes += (fp.length + 64 + 255) / 256 * 256;  // 64 B of readable slack per range
+      weight_bytes += fp.length;
+    }
+  }
+  if (rc) {
+    close_all();
+    return 1;
+  }
+
+  {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0 || device >= n) {
+      set_error("cuda device %d is not available (%s); there is no CPU fallback", device,
+                e != cudaSuccess ? cudaGetErrorString(e) : "ordinal out of range");
+      close_all();
+      return 1;
+    }
+  }
+  Session* s = new Session();
+  s->device = device;
+  s->cfg = cfg;
+  CounterScope scope(s);
+  auto fail = [&]() {
+    close_all();
+    std::string keep = dyninfer_cuda_last_error();
+    dyninfer_cuda_session_destroy(s);
+    set_error("%s", keep.c_str());
+    return 1;
+  };
+  if (cudaSetDevice(device) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking) != cudaSuccess) {
+    set_error("cannot initialise cuda device %d: %s", device, cudaGetErrorString(cudaGetLastError()));
+    return fail();
+  }
+  cudaEventCreate(&s->ev0);
+  cudaEventCreate(&s->ev1);
+  fill_freq_table(&s->freq, cfg.head_dim, cfg.theta);
+  if (dev_alloc(s, (void**)&s->arena, arena_bytes)) return fail();
+  s->arena_bytes = arena_bytes;
+  if (cudaMemset(s->arena, 0, arena_bytes) != cudaSuccess) {
+    set_error("cudaMemset of the parameter arena failed");
+    return fail();
+  }
+  {
+    const size_t staging_bytes = 32u << 20;
+    uint8_t* staging = nullptr;
+    if (host_alloc(s, (void**)&staging, staging_bytes)) return fail();
+    for (auto& p : pd)
+      for (auto& c : p.second.comps) {
+        const Upload& u = c.second;
+        if (read_range(fds[u.file], u.file_off, u.length, s->arena + u.arena_off, staging,
+                       staging_bytes, files[u.file].path)) {
+          cudaFreeHost(staging);
+          return fail();
+        }
+      }
+    cudaFreeHost(staging);
+    s->stats.host_bytes_freed += staging_bytes;
+  }
+  close_all();
+  for (int& fd : fds) fd = -1;
+  s->weight_bytes = weight_bytes;
+
+  // bind tensors to roles
+  const int64_t H = cfg.hidden, qd = (int64_t)cfg.heads * cfg.head_dim,
+                kvd = (int64_t)cfg.kv_heads * cfg.head_dim, I = cfg.inter;
+  if (bind_linear(pd, s->arena, "token_embd.weight", cfg.vocab, H, &s->embed)) return fail();
+  if (pd.count("output.weight")) {
+    if (bind_linear(pd, s->arena, "output.weight", cfg.vocab, H, &s->lm_head)) return fail();
+  } else {
+    s->lm_head = s->embed;  // tied: same bytes (crates/dyninfer-architecture/src/naming.rs:70-96)
+  }
+  if (bind_norm(pd, s->arena, "output_norm.weight", H, true, &s->out_norm)) return fail();
+  s->layers.resize(cfg.layers);
+  uint64_t dwb = s->lm_head.total_bytes() + s->out_norm.bytes;
+  for (int l = 0; l < cfg.layers; l++) {
+    LayerW& L = s->layers[l];
+    std::string p = "blk." + std::to_string(l) + ".";
+    if (bind_norm(pd, s->arena, p + "attn_norm.weight", H, true, &L.attn_norm) ||
+        bind_norm(pd, s->arena, p + "ffn_norm.weight", H, true, &L.ffn_norm) ||
+        bind_norm(pd, s->arena, p + "attn_q_norm.weight", cfg.head_dim, cfg.qk_norm, &L.q_norm) ||
+        bind_norm(pd, s->arena, p + "attn_k_norm.weight", cfg.head_dim, cfg.qk_norm, &L.k_norm) ||
+        bind_linear(pd, s->arena, p + "attn_q.weight", qd, H, &L.q) ||
+        bind_linear(pd, s->arena, p + "attn_k.weight", kvd, H, &L.k) ||
+        bind_linear(pd, s->arena, p + "attn_v.weight", kvd, H, &L.v) ||
+        bind_linear(pd, s->arena, p + "attn_output.weight", H, qd, &L.o) ||
+        bind_linear(pd, s->arena, p + "ffn_gate.weight", I, H, &L.gate) ||
+        bind_linear(pd, s->arena, p + "ffn_up.weight", I, H, &L.up) ||
+        bind_linear(pd, s->arena, p + "ffn_down.weight", H, I, &L.down))
+      return fail();
+    if (cfg.qk_norm && L.q_norm.type != L.k_norm.type) {
+      set_error("q_norm and k_norm weights of layer %d differ in type", l);
+      return fail();
+    }
+    dwb += L.q.total_bytes() + L.k.total_bytes() + L.v.total_bytes() + L.o.total_bytes() +
+           L.gate.total_bytes() + L.up.total_bytes() + L.down.total_bytes() + L.attn_norm.bytes +
+           L.ffn_norm.bytes + L.q_norm.bytes + L.k_norm.bytes;
+  }
+  s->decode_weight_bytes = dwb;
+
+  if (host_alloc(s, (void**)&s->logits_host, (size_t)cfg.vocab * 4)) return fail();
+  if (dev_alloc(s, (void**)&s->logits, (size_t)cfg.vocab * 4) ||
+      dev_alloc(s, (void**)&s->out_token_dev, 64) ||
+      dev_alloc(s, (void**)&s->hist_count_dev, 64) ||
+      dev_alloc(s, &s->argmax_scratch, argmax_scratch_bytes(cfg.vocab)))
+    return fail();
+  *out_session = s;
+  return 0;
+}
+
+void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
+  if (!s) return;
+  cudaSetDevice(s->device);
+  if (s->stream) cudaStreamSynchronize(s->stream);
+  destroy_graphs(s);
+  void* dev[] = {s->arena, s->kcache, s->vcache, s->hidden, s->xn, s->q, s->k, s->v, s->ctx, s->act,
+                 s->logits, s->tokens_dev, s->row_pos_dev, s->row_seq_dev, s->out_token_dev,
+                 s->hist_dev, s->hist_count_dev, s->argmax_scratch};
+  for (void* p : dev)
+    if (p) cudaFree(p);
+  if (s->logits_host) cudaFreeHost(s->logits_host);
+  if (s->stage_host) cudaFreeHost(s->stage_host);
+  if (s->ev0) cudaEventDestroy(s->ev0);
+  if (s->ev1) cudaEventDestroy(s->ev1);
+  if (s->stream) cudaStreamDestroy(s->stream);
+  delete s;
+}
+
+int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t layer_count,
+                                             size_t page_size, size_t kv_head_count,
+                                             size_t head_dim, size_t kv_element_byte_count,
+                                             size_t chunk_size, size_t vocab_size) {
+  DYN_CHECK(s != nullptr, "session is NULL");
+  // reconfiguring after allocation is an error (wrapper.c:927-930)
+  DYN_CHECK(s->pages == 0, "paged KV is already allocated; it cannot be reconfigured");
+  DYN_CHECK(layer_count == (size_t)s->cfg.layers && kv_head_count == (size_t)s->cfg.kv_heads &&
+                head_dim == (size_t)s->cfg.head_dim && vocab_size == (size_t)s->cfg.vocab,
+            "paged KV geometry (layers %zu, kv heads %zu, head_dim %zu, vocab %zu) does not match the model",
+            layer_count, kv_head_count, head_dim, vocab_size);
+  DYN_CHECK(page_size > 0 && chunk_size > 0, "page_size and chunk_size must be positive");
+  DYN_CHECK(kv_element_byte_count == 4 || kv_element_byte_count == 2,
+            "kv_element_byte_count %zu unsupported (4 = f32, 2 = bf16/f16)", kv_element_byte_count);
+  CounterScope scope(s);
+  DYN_CUDA(cudaSetDevice(s->device));
+  s->page_size = page_size;
+  s->chunk_size = chunk_size;
+  s->kv_elem = kv_element_byte_count;
+  s->kv_type = kv_element_byte_count == 4 ? E_F32 : s->cfg.kv2_type;
+  // activation scratch for the widest call: one prefill chunk or one batched step
+  const ModelCfg& c = s->cfg;
+  const int64_t rows = std::max<int64_t>((int64_t)chunk_size, c.batch);
+  const int64_t qd = (int64_t)c.heads * c.head_dim, kvd = (int64_t)c.kv_heads * c.head_dim;
+  if (!s->kv_configured) {
+    if (dev_alloc(s, (void**)&s->hidden, (size_t)rows * c.hidden * 4) ||
+        dev_alloc(s, (void**)&s->xn, (size_t)rows * c.hidden * 4) ||
+        dev_alloc(s, (void**)&s->q, (size_t)rows * qd * 4) ||
+        dev_alloc(s, (void**)&s->k, (size_t)rows * kvd * 4) ||
+        dev_alloc(s, (void**)&s->v, (size_t)rows * kvd * 4) ||
+        dev_alloc(s, (void**)&s->ctx, (size_t)rows * qd * 4) ||
+        dev_alloc(s, (void**)&s->act, (size_t)rows * c.inter * 4) ||
+        dev_alloc(s, (void**)&s->tokens_dev, (size_t)rows * 8) ||
+        dev_alloc(s, (void**)&s->row_pos_dev, (size_t)rows * 8) ||
+        dev_alloc(s, (void**)&s->row_seq_dev, (size_t)rows * 8) ||
+        host_alloc(s, (void**)&s->stage_host, (size_t)(4 + 3 * rows) * 8))
+      return 1;
+    s->max_rows = rows;
+  } else {
+    DYN_CHECK(rows <= s->max_rows, "chunk_size %zu exceeds the scratch sized at first configuration",
+              chunk_size);
+  }
+  s->kv_configured = true;
+  destroy_graphs(s);
+  return 0;
+}
+
+int dyninfer_cuda_session_ensure_kv_pages(dyninfer_cuda_session_t* s, size_t page_count) {
+  DYN_CHECK(s != nullptr, "session is NULL");
+  DYN_CHECK(s->kv_configured, "paged KV is not configured");
+  if (page_count <= s->pages) return 0;
+  CounterScope scope(s);
+  DYN_CUDA(cudaSetDevice(s->device));
+  const ModelCfg& c = s->cfg;
+  const size_t planes = (size_t)c.layers * c.batch * c.kv_heads;
+  const size_t new_row = page_count * s->page_size * c.head_dim * s->kv_elem;  // bytes per plane
+  const size_t old_row = s->pages * s->page_size * c.head_dim * s->kv_elem;
+  const size_t bytes = planes * new_row;
+  uint8_t *nk = nullptr, *nv = nullptr;
+  if (dev_alloc(s, (void**)&nk, bytes)) return 1;
+  if (dev_alloc(s, (void**)&nv, bytes)) {
+    dev_free(s, nk, bytes);
+    return 1;
+  }
+  DYN_CUDA(cudaMemsetAsync(nk, 0, bytes, s->stream));
+  DYN_CUDA(cudaMemsetAsync(nv, 0, bytes, s->stream));
+  if (s->pages) {  // grow: keep what is already cached, plane by plane
+    DYN_CUDA(cudaMemcpy2DAsync(nk, new_row, s->kcache, old_row, old_row, planes,
+                               cudaMemcpyDeviceToDevice, s->stream));
+    DYN_CUDA(cudaMemcpy2DAsync(nv, new_row, s->vcache, old_row, old_row, planes,
+                               cudaMemcpyDeviceToDevice, s->stream));
+  }
+  DYN_CUDA(cudaStreamSynchronize(s->stream));
+  dev_free(s, s->kcache, s->kv_bytes_each);
+  dev_free(s, s->vcache, s->kv_bytes_each);
+  s->kcache = nk;
+  s->vcache = nv;
+  s->kv_bytes_each = bytes;
+  s->pages = page_count;
+  destroy_graphs(s);
+  return 0;
+}
+
+int dyninfer_cuda_session_reset_paged_kv(dyninfer_cuda_session_t* s) {
+  DYN_CHECK(s != nullptr, "session is NULL");
+  DYN_CHECK(s->kv_configured, "paged KV is not configured");
+  if (!s->pages) return 0;
+  DYN_CUDA(cudaSetDevice(s->device));
+  // zero-fill in place, the pool is kept (wrapper.c:1273-1303)
+  DYN_CUDA(cudaMemsetAsync(s->kcache, 0, s->kv_bytes_each, s->stream));
+  DYN_CUDA(cudaMemsetAsync(s->vcache, 0, s->kv_bytes_each, s->stream));
+  DYN_CUDA(cudaStreamSynchronize(s->stream));
+  return 0;
+}
+
+size_t dyninfer_cuda_session_kv_page_count(const dyninfer_cuda_session_t* s) {
+  return s ? s->pages : 0;
+}
+size_t dyninfer_cuda_session_kv_allocated_bytes(const dyninfer_cuda_session_t* s) {
+  return s ? 2 * s->kv_bytes_each : 0;
+}
+
+int dyninfer_cuda_session_allocator_statistics(const dyninfer_cuda_session_t* s,
+                                               dyninfer_cuda_allocator_statistics_t* out) {
+  DYN_CHECK(s != nullptr && out != nullptr, "session or out_stats is NULL");
+  *out = s->stats;
+  return 0;
+}
+
+uint64_t dyninfer_cuda_session_weight_bytes(const dyninfer_cuda_session_t* s) {
+  return s ? s->weight_bytes : 0;
+}
+uint64_t dyninfer_cuda_session_decode_weight_bytes(const dyninfer_cuda_session_t* s) {
+  return s ? s->decode_weight_bytes : 0;
+}
+uint64_t dyninfer_cuda_session_launch_count(const dyninfer_cuda_session_t* s) {
+  return s ? s->launches : 0;
+}
+
+int dyninfer_cuda_session_invoke_paged_chunk(dyninfer_cuda_session_t* s, const int64_t* tokens,
+                                             size_t token_count, int64_t last, int64_t start_pos,
+                                             float** out_logits, size_t* out_count,
+                                             int64_t* out_token, int want_logits) {
+  DYN_CHECK(s != nullptr, "session is NULL");
+  DYN_CHECK(s->kv_configured && s->pages > 0, "paged KV is not configured or has no pages");
+  DYN_CHECK(tokens != nullptr, "tokens is NULL");
+  // wrapper.c:1230-1235
+  DYN_CHECK(token_count == 1 || token_count == s->chunk_size,
+            "token_count %zu must be 1 or the chunk size %zu", token_count, s->chunk_size);
+  DYN_CHECK(last >= 0 && (size_t)last < token_count, "last %lld out of range [0, %zu)",
+            (long long)last, token_count);
+  DYN_CHECK(start_pos >= 0, "start_pos must be >= 0");
+  DYN_CHECK(!want_logits || (out_logits && out_count), "want_logits needs out_logits and out_count");
+  const int64_t rows = last + 1;
+  const int64_t cap = (int64_t)(s->pages * s->page_size);
+  DYN_CHECK(start_pos + rows <= cap, "positions [%lld, %lld) exceed the KV capacity %lld",
+            (long long)start_pos, (long long)(start_pos + rows), (long long)cap);
+  for (int64_t i = 0; i < rows; i++)
+    DYN_CHECK(tokens[i] >= 0 && tokens[i] < s->cfg.vocab, "token id %lld at %lld outside [0, %d)",
+              (long long)tokens[i], (long long)i, s->cfg.vocab);
+  CounterScope scope(s);
+  DYN_CUDA(cudaSetDevice(s->device));
+  if (rows == 1) {
+    if (!s->decode_graph && capture(s, false, &s->decode_graph, &s->graph_nodes)) return 1;
+    s->stage_host[0] = tokens[0];
+    s->stage_host[1] = start_pos;
+    s->stage_host[2] = 0;
+    DYN_CUDA(cudaGraphLaunch(s->decode_graph, s->stream));
+    s->launches += s->graph_nodes;
+  } else {
+    int64_t* st = s->stage_host + 4;
+    for (int64_t i = 0; i < rows; i++) {
+      st[i] = tokens[i];
+      st[rows + i] = start_pos + i;
+      st[2 * rows + i] = 0;
+    }
+    DYN_CUDA(cudaMemcpyAsync(s->tokens_dev, st, rows * 8, cudaMemcpyHostToDevice, s->stream));
+    DYN_CUDA(cudaMemcpyAsync(s->row_pos_dev, st + rows, rows * 8, cudaMemcpyHostToDevice, s->stream));
+    DYN_CUDA(cudaMemcpyAsync(s->row_seq_dev, st + 2 * rows, rows * 8, cudaMemcpyHostToDevice,
+                             s->stream));
+    if (enqueue_forward(s, rows, last)) return 1;
+    DYN_CUDA(cudaMemcpyAsync(s->stage_host + 3, s->out_token_dev, 8, cudaMemcpyDeviceToHost,
+                             s->stream));
+  }
+  if (want_logits)
+    DYN_CUDA(cudaMemcpyAsync(s->logits_host, s->logits, (size_t)s->cfg.vocab * 4,
+                             cudaMemcpyDeviceToHost, s->stream));
+  DYN_CUDA(cudaStreamSynchronize(s->stream));
+  if (out_token) *out_token = s->stage_host[3];
+  if (want_logits) {
+    *out_logits = s->logits_host;  // session scratch, borrowed until the next invoke
+    *out_count = (size_t)s->cfg.vocab;
+  } else {
+    if (out_logits) *out_logits = nullptr;
+    if (out_count) *out_count = 0;
+  }
+  return 0;
+}
+
+int dyninfer_cuda_session_decode_loop(dyninfer_cuda_session_t* s, int64_t first_token,
+                                      int64_t start_pos, size_t steps, int64_t* out_tokens,
+                                      float* out_device_ms) {
+  DYN_CHECK(s != nullptr, "session is NULL");
+  DYN_CHECK(s->kv_configured && s->pages > 0, "paged KV is not configured or has no pages");
+  DYN_CHECK(first_token >= 0 && first_token < s->cfg.vocab, "token id %lld outside [0, %d)",
+            (long long)first_token, s->cfg.vocab);
+  const int64_t cap = (int64_t)(s->pages * s->page_size);
+  DYN_CHECK(start_pos >= 0 && start_pos + (int64_t)steps <= cap,
+            "positions [%lld, %lld) exceed the KV capacity %lld", (long long)start_pos,
+            (long long)(start_pos + (int64_t)steps), (long long)cap);
+  if (out_device_ms) *out_device_ms = 0.f;
+  if (steps == 0) return 0;
+  CounterScope scope(s);
+  DYN_CUDA(cudaSetDevice(s->device));
+  if (ensure_hist(s, steps)) return 1;
+  if (!s->loop_graph && capture(s, true, &s->loop_graph, &s->loop_nodes)) return 1;
+  s->stage_host[0] = first_token;
+  s->stage_host[1] = start_pos;
+  s->stage_host[2] = 0;
+  DYN_CUDA(cudaMemcpyAsync(s->tokens_dev, s->stage_host, 8, cudaMemcpyHostToDevice, s->stream));
+  DYN_CUDA(cudaMemcpyAsync(s->row_pos_dev, s->stage_host + 1, 8, cudaMemcpyHostToDevice, s->stream));
+  DYN_CUDA(cudaMemcpyAsync(s->row_seq_dev, s->stage_host + 2, 8, cudaMemcpyHostToDevice, s->stream));
+  DYN_CUDA(cudaMemsetAsync(s->hist_count_dev, 0, 8, s->stream));
+  DYN_CUDA(cudaEventRecord(s->ev0, s->stream));
+  for (size_t i = 0; i < steps; i++) DYN_CUDA(cudaGraphLaunch(s->loop_graph, s->stream));
+  DYN_CUDA(cudaEventRecord(s->ev1, s->stream));
+  s->launches += s->loop_nodes * steps;
+  DYN_CUDA(cudaStreamSynchronize(s->stream));
+  if (out_device_ms) DYN_CUDA(cudaEventElapsedTime(out_device_ms, s->ev0, s->ev1));
+  if (out_tokens)
+    DYN_CUDA(cudaMemcpy(out_tokens, s->hist_dev, steps * 8, cudaMemcpyDeviceToHost));
+  return 0;
+}
+
+}  // extern "C"

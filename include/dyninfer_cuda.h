@@ -1,0 +1,220 @@
+/*
+ * libdyninfer_cuda — C ABI of the B200 (sm_100a) `cuda` target for dyninfer's
+ * direct quantized decoder path.
+ *
+ * The session half of this header is modelled one to one on the reference's
+ * native session boundary, third_party/iree_runtime_c_api/wrapper.h:14-122
+ * (bound from Rust by crates/iree-runtime-sys/src/lib.rs:53-145). Each entry
+ * point names the reference declaration it replaces. The per-operation half
+ * (dequant / linear / norm / rope / attention / argmax) has no counterpart in
+ * the reference ABI, where single operators are only reachable through a
+ * compiled module; it exists so that each kernel can be checked alone.
+ *
+ * Conventions kept from the reference (wrapper.h:38, wrapper.c:82-109):
+ *   - every call returns 0 on success and non-zero on failure;
+ *   - after a failure dyninfer_cuda_last_error() returns a human-readable
+ *     message; the message is thread-local, so independent sessions may be
+ *     driven from different threads;
+ *   - a session is thread-compatible, not thread-safe: the caller serialises
+ *     calls on one session (the Rust side holds it in a Mutex,
+ *     crates/iree-runtime/src/lib.rs:110-121);
+ *   - there is no CPU fallback: if no CUDA device is usable the call fails.
+ *
+ * All `*_dev` pointers are device pointers on the current CUDA device.
+ * `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ * stream).
+ */
+#ifndef DYNINFER_CUDA_H_
+#define DYNINFER_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DYNINFER_CUDA_ABI_VERSION 1
+
+/* ---- physical encodings (crates/dyninfer-core/src/types.rs:108-149) ------ */
+enum {
+  DYNINFER_ENC_F32 = 0,    /* plain.f32  */
+  DYNINFER_ENC_F16 = 1,    /* plain.f16  */
+  DYNINFER_ENC_BF16 = 2,   /* plain.bf16 */
+  DYNINFER_ENC_Q4_0 = 3,   /* gguf.q4_0:  32 el / 18 B */
+  DYNINFER_ENC_Q4_1 = 4,   /* gguf.q4_1:  32 el / 20 B */
+  DYNINFER_ENC_Q8_0 = 5,   /* gguf.q8_0:  32 el / 34 B */
+  DYNINFER_ENC_Q6_K = 6,   /* gguf.q6_k: 256 el / 210 B */
+  DYNINFER_ENC_MLX_U4 = 7  /* mlx.affine.u4: u32 words + scales + biases */
+};
+
+/* One [rows, cols] parameter as the verbatim checkpoint bytes, resident in
+ * device memory. rows = output features N, cols = input features K; storage is
+ * row-major [N, K] (crates/dyninfer-quantization/src/quantizations/
+ * gguf_codegen.rs:144-149). For MLX `data` is ui32[N, K/8], `scales`/`biases`
+ * are [N, K/group] of `aux_type` (F32, F16 or BF16). */
+typedef struct dyninfer_cuda_weight_t {
+  int32_t encoding;
+  int32_t aux_type;
+  int32_t group;
+  int32_t reserved;
+  int64_t rows;
+  int64_t cols;
+  const void* data;
+  const void* scales;
+  const void* biases;
+} dyninfer_cuda_weight_t;
+
+/* ---- library -------------------------------------------------------------- */
+
+int dyninfer_cuda_abi_version(void);
+/* replaces dyninfer_iree_last_error (wrapper.h:63) */
+const char* dyninfer_cuda_last_error(void);
+/* Number of usable CUDA devices; fails when the driver reports none. */
+int dyninfer_cuda_device_count(int* out_count);
+/* Bytes per row of an encoded [*, cols] tensor; 0 if cols is not a whole number of blocks. */
+uint64_t dyninfer_cuda_row_bytes(int encoding, int64_t cols);
+
+/* ---- single operators (device pointers) ----------------------------------- */
+
+/* Bit-exact dequantisation to f32 [rows, cols]
+ * (gguf_codegen.rs:350-526, mlx_affine.rs:590-600). */
+int dyninfer_cuda_dequant(const dyninfer_cuda_weight_t* w, float* out_dev, void* stream);
+
+/* out[i, :] = dequant(row tokens[i]) — the embedding lookup
+ * (gguf_codegen.rs:316-348, mlx_affine.rs:628-675). */
+int dyninfer_cuda_embedding_gather(const dyninfer_cuda_weight_t* w, const int64_t* tokens_dev,
+                                   int64_t count, float* out_dev, void* stream);
+
+/* y[m, n] = sum_k x[m, k] * w[n, k], f32 accumulation, fused dequantisation
+ * (gguf_codegen.rs:268-314, mlx_affine.rs:557-626). x_type is DYNINFER_ENC_F32
+ * or DYNINFER_ENC_BF16; y is f32 [m, rows]. Any m >= 1. */
+int dyninfer_cuda_linear(const dyninfer_cuda_weight_t* w, const void* x_dev, int x_type,
+                         int64_t m, float* y_dev, void* stream);
+
+/* y = (x * rsqrt(mean(x^2) + eps)) * w over the last dim
+ * (crates/dyninfer-compiler/src/lowering/kernels.rs:774-903). w_type gives the
+ * element type of the weight vector (F32 / F16 / BF16). In place allowed. */
+int dyninfer_cuda_rms_norm(const float* x_dev, const void* w_dev, int w_type, int64_t rows,
+                           int64_t width, float eps, float* y_dev, void* stream);
+
+/* Rotate-half RoPE on x [s, heads, d] in place, positions start_pos + row
+ * (kernels.rs:1007-1070). */
+int dyninfer_cuda_rope(float* x_dev, int64_t s, int64_t heads, int64_t d, int64_t start_pos,
+                       float theta, void* stream);
+
+/* y = silu(gate) * up (crates/dyninfer-compiler/src/lowering/dense_decoder.rs:1379-1385). */
+int dyninfer_cuda_silu_mul(const float* gate_dev, const float* up_dev, int64_t n, float* y_dev,
+                           void* stream);
+
+/* GQA causal attention of q [s, heads, d] against caches [kv_heads, kv_cap, d]
+ * holding keys/values for positions < start_pos + s; ctx is f32 [s, heads*d]
+ * (kernels.rs:310-506, dense_decoder.rs:1317-1328,2454-2456). kv_type is F32, F16 or BF16. */
+int dyninfer_cuda_attention(const float* q_dev, const void* k_cache_dev, const void* v_cache_dev,
+                            int kv_type, int64_t s, int64_t heads, int64_t kv_heads, int64_t d,
+                            int64_t kv_cap, int64_t start_pos, float* ctx_dev, void* stream);
+
+/* First strict maximum of v[0..n) (dense_decoder.rs:885-893). scratch_dev must hold
+ * dyninfer_cuda_argmax_scratch_bytes(n) bytes. */
+size_t dyninfer_cuda_argmax_scratch_bytes(int64_t n);
+int dyninfer_cuda_argmax(const float* v_dev, int64_t n, int64_t* out_index_dev, void* scratch_dev,
+                         void* stream);
+
+/* ---- session (paged-KV ABI) ----------------------------------------------- */
+
+typedef struct dyninfer_cuda_session_t dyninfer_cuda_session_t;
+
+/* replaces dyninfer_iree_parameter_file_t (wrapper.h:18-20) */
+typedef struct dyninfer_cuda_parameter_file_t {
+  const char* path;
+} dyninfer_cuda_parameter_file_t;
+
+/* replaces dyninfer_iree_file_param_t (wrapper.h:24-29): one stable external
+ * key "weights::<canonical>::<component>" backed by one contiguous byte range
+ * of an original checkpoint file. */
+typedef struct dyninfer_cuda_file_param_t {
+  const char* key;
+  size_t source_file_index;
+  uint64_t offset;
+  uint64_t length;
+} dyninfer_cuda_file_param_t;
+
+/* replaces dyninfer_iree_session_create_with_file_params (wrapper.h:46-50).
+ * `device_uri` is "cuda", "cuda:<ordinal>" or NULL (= "cuda:0"). `model_desc_json`
+ * stands where the reference passes a compiled module path: it carries the
+ * model geometry and, per parameter, encoding and logical shape. Every byte
+ * range is read from its file and uploaded unchanged. */
+int dyninfer_cuda_session_create_with_file_params(
+    const char* device_uri, const char* model_desc_json,
+    const dyninfer_cuda_parameter_file_t* files, size_t file_count,
+    const dyninfer_cuda_file_param_t* params, size_t param_count,
+    dyninfer_cuda_session_t** out_session);
+
+/* replaces dyninfer_iree_session_destroy (wrapper.h:60) */
+void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* session);
+
+/* replaces dyninfer_iree_free (wrapper.h:67): logits are session scratch, so this is a no-op. */
+void dyninfer_cuda_free(void* p);
+
+/* replaces dyninfer_iree_session_configure_paged_kv (wrapper.h:90-94).
+ * kv_element_byte_count 4 selects an f32 cache, 2 selects the 2-byte type the
+ * descriptor names ("kv_dtype": "bf16" default, or "f16"). Fails once pages exist. */
+int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* session, size_t layer_count,
+                                             size_t page_size, size_t kv_head_count,
+                                             size_t head_dim, size_t kv_element_byte_count,
+                                             size_t chunk_size, size_t vocab_size);
+/* replaces dyninfer_iree_session_ensure_kv_pages (wrapper.h:95-96) */
+int dyninfer_cuda_session_ensure_kv_pages(dyninfer_cuda_session_t* session, size_t page_count);
+
+/* replaces dyninfer_iree_session_invoke_paged_chunk (wrapper.h:97-100).
+ * token_count must be 1 or chunk_size; 0 <= last < token_count; start_pos >= 0.
+ * *out_logits is session-owned scratch valid until the next invoke. With
+ * want_logits = 0 the logits pointers may be NULL and only *out_token is produced. */
+int dyninfer_cuda_session_invoke_paged_chunk(dyninfer_cuda_session_t* session,
+                                             const int64_t* tokens, size_t token_count,
+                                             int64_t last, int64_t start_pos, float** out_logits,
+                                             size_t* out_count, int64_t* out_token,
+                                             int want_logits);
+/* replaces dyninfer_iree_session_reset_paged_kv (wrapper.h:101) */
+int dyninfer_cuda_session_reset_paged_kv(dyninfer_cuda_session_t* session);
+/* replace dyninfer_iree_session_kv_page_count / _kv_allocated_bytes (wrapper.h:102-105) */
+size_t dyninfer_cuda_session_kv_page_count(const dyninfer_cuda_session_t* session);
+size_t dyninfer_cuda_session_kv_allocated_bytes(const dyninfer_cuda_session_t* session);
+
+/* replaces dyninfer_iree_allocator_statistics_t (wrapper.h:109-116) */
+typedef struct dyninfer_cuda_allocator_statistics_t {
+  uint64_t host_bytes_peak;
+  uint64_t host_bytes_allocated;
+  uint64_t host_bytes_freed;
+  uint64_t device_bytes_peak;
+  uint64_t device_bytes_allocated;
+  uint64_t device_bytes_freed;
+} dyninfer_cuda_allocator_statistics_t;
+/* replaces dyninfer_iree_session_allocator_statistics (wrapper.h:120-122) */
+int dyninfer_cuda_session_allocator_statistics(const dyninfer_cuda_session_t* session,
+                                               dyninfer_cuda_allocator_statistics_t* out_stats);
+
+/* ---- session extensions (no reference precedent) --------------------------- */
+
+/* Total bytes of uploaded parameters (the reference's schema total_bytes used by
+ * eff_weight_bw_gbs, crates/dyninfer-runtime/src/perf.rs:298-305). */
+uint64_t dyninfer_cuda_session_weight_bytes(const dyninfer_cuda_session_t* session);
+/* Bytes of parameters one decode step reads (embedding counted as one row unless tied). */
+uint64_t dyninfer_cuda_session_decode_weight_bytes(const dyninfer_cuda_session_t* session);
+
+/* Device-resident greedy loop: feeds each argmax back as the next token without a
+ * host round trip; `steps` decode steps starting from `first_token` at `start_pos`.
+ * out_tokens (host, `steps` entries) may be NULL. *out_device_ms receives the
+ * CUDA-event time of the loop on the session stream. */
+int dyninfer_cuda_session_decode_loop(dyninfer_cuda_session_t* session, int64_t first_token,
+                                      int64_t start_pos, size_t steps, int64_t* out_tokens,
+                                      float* out_device_ms);
+
+/* Number of kernels this library has launched on behalf of `session` since creation. */
+uint64_t dyninfer_cuda_session_launch_count(const dyninfer_cuda_session_t* session);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DYNINFER_CUDA_H_ */

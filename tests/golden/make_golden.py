@@ -1,0 +1,48 @@
+"""Generates tests/golden/dequant_golden.npz.
+
+Raw blocks come from a fixed numpy seed; the expected values come from the
+third-party `gguf` Python package (gguf.quants.dequantize), the GGML ground
+truth whose block order the reference states it follows
+(crates/dyninfer-checkpoint-gguf/src/q4.rs:34-42). Run from the repo root:
+
+    python tests/golden/make_golden.py
+"""
+import os
+import sys
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+import gguf  # noqa: E402
+from gguf import quants  # noqa: E402
+
+from dyninfer_b200 import synth  # noqa: E402
+
+QT = {"gguf.q4_0": gguf.GGMLQuantizationType.Q4_0, "gguf.q4_1": gguf.GGMLQuantizationType.Q4_1,
+      "gguf.q8_0": gguf.GGMLQuantizationType.Q8_0, "gguf.q6_k": gguf.GGMLQuantizationType.Q6_K}
+
+
+def main():
+    out = {}
+    for i, (enc, qt) in enumerate(QT.items()):
+        rows, cols = 6, 512
+        raw = synth.random_weight(enc, rows, cols, 1234 + i)["data"]
+        # edge blocks: zero scale, extreme nibbles, negative scale, f16 subnormal scale
+        bsz = {"gguf.q4_0": 18, "gguf.q4_1": 20, "gguf.q8_0": 34, "gguf.q6_k": 210}[enc]
+        blk = raw.reshape(-1, bsz).copy()
+        doff = 208 if enc == "gguf.q6_k" else 0
+        blk[0, doff:doff + 2] = 0
+        blk[1, doff:doff + 2] = np.array([0x8400], np.uint16).view(np.uint8)   # -6.1e-5
+        blk[2, doff:doff + 2] = np.array([0x0001], np.uint16).view(np.uint8)   # smallest subnormal
+        blk[3, (2 if doff == 0 else 0):(2 if doff == 0 else 0) + 16] = 0xFF
+        blk[4, (2 if doff == 0 else 0):(2 if doff == 0 else 0) + 16] = 0x00
+        raw = blk.reshape(-1)
+        ref = quants.dequantize(raw.reshape(rows, -1), qt).astype(np.float32)
+        out[enc + ":raw"] = raw
+        out[enc + ":f32"] = ref.reshape(rows, cols)
+    np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "dequant_golden.npz"), **out)
+    print({k: v.shape for k, v in out.items()})
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,301 @@
+#!/usr/bin/env python
+"""Headline benchmark: batch-1 greedy decode of the Qwen3-0.6B-shape Q4_0 model.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one decode step (one generated token) of the seeded synthetic
+checkpoint (all linears Q4_0, tied Q6_K embedding / lm_head, GGUF v3), after a
+16-token prompt. Prints ONE JSON line on rank 0.
+
+  value     decode tok/s with everything resident in HBM: K replays of the captured
+            decode graph with the argmax fed back on the device, timed with CUDA
+            events on the session stream (max over ranks).
+  e2e       the same K steps through the public session call `decode_argmax`
+            (C ABI `dyninfer_cuda_session_invoke_paged_chunk`): host token in from
+            pinned memory, argmax token out, every step.
+  roofline  the lm_head product (151936 x 1024 Q6_K, the largest single launch),
+            timed alone with CUDA events, L2 flushed between launches.
+  cpu_baseline  the CPU restatement of the reference's direct path (oracle/) on the
+            host cores, on a bounded sample of the same workload.
+
+With N > 1 every rank runs an independent replica of the model on its own GPU
+(the 0.6B path does not shard; there is no data-path collective), so the value is
+N x the per-replica rate over the slowest rank: weak scaling.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = "qwen3-0.6b-shape q4_0 (tied q6_k lm_head), batch 1, prompt 16, greedy decode"
+PROMPT_LEN = 16
+SEED = 20240
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx = max(mx, float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6),
+                              ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def checkpoint_path():
+    d = os.environ.get("DYNINFER_BENCH_DIR") or os.path.join(tempfile.gettempdir(), "dyninfer_b200_bench")
+    os.makedirs(d, exist_ok=True)
+    return os.path.join(d, f"qwen3_0_6b_q4_0_seed{SEED}.gguf")
+
+
+def ensure_checkpoint():
+    from dyninfer_b200 import synth
+    path = checkpoint_path()
+    if not os.path.exists(path):
+        tmp = path + f".tmp{os.getpid()}"
+        synth.write_qwen3_gguf(tmp, synth.QWEN3_0_6B, seed=SEED)
+        os.replace(tmp, path)
+    return path
+
+
+def prompt_ids():
+    from dyninfer_b200 import synth
+    return np.random.default_rng(SEED).integers(0, synth.QWEN3_0_6B["vocab"], size=PROMPT_LEN).tolist()
+
+
+# ------------------------------------------------------------------ CPU restatement
+
+def cpu_decode_rate(path, steps, prompt_tokens=4):
+    """Decode tok/s of the CPU restatement (all host threads) on a bounded sample."""
+    from oracle import oracle as orc
+    from dyninfer_b200 import checkpoint as ck
+    orc.build()
+    cat = ck.open_catalog(path)
+    m = orc.Model(cat.config, orc.weights_from_catalog(cat), kv_cap=prompt_tokens + steps + 2, fast=True)
+    _, tok = m.forward(prompt_ids()[:prompt_tokens])
+    _, tok = m.forward([tok])                      # one untimed step
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        _, tok = m.forward([tok])
+    dt = time.perf_counter() - t0
+    return steps / dt, orc.num_threads(), dt
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    path = ensure_checkpoint()
+    steps = max(1, min(args.steps, 48))
+    tps, cores, dt = cpu_decode_rate(path, steps)
+    sample = (f"{steps} greedy decode steps of the full 28-layer model after a 4-token prompt, "
+              f"CPU restatement of the reference's direct path (the reference's own IREE llvm-cpu "
+              f"build cannot run here), {cores} OpenMP threads")
+    print(json.dumps({
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": tps, "unit": "tok/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": 1e3 * dt / steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD},
+        "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+# ------------------------------------------------------------------------- GPU arm
+
+def time_lm_head(path, iters=20):
+    """Average device time of the lm_head launch alone (CUDA events on the launching stream,
+    a 512 MB write between launches evicts L2)."""
+    import torch
+    from dyninfer_b200 import checkpoint as ck, ops
+    cat = ck.open_catalog(path)
+    p = cat.parameters["token_embd.weight"]
+    c = p.components[0]
+    raw = np.fromfile(path, dtype=np.uint8, count=c.length, offset=c.offset)
+    w = ops.DeviceWeight(p.encoding, p.shape[0], p.shape[1], raw)
+    x = torch.randn(1, p.shape[1], device="cuda")
+    y = torch.empty(1, p.shape[0], device="cuda")
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(3):
+        ops.linear(w, x, out=y)
+    times = []
+    for _ in range(iters):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.linear(w, x, out=y)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.mean(times), c.length, p.encoding
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "f16", "f32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the cuda target has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from dyninfer_b200 import build
+    from dyninfer_b200.runtime import ModelLoader, SessionConfig
+    build.build()
+    if rank == 0:
+        ensure_checkpoint()
+    if world > 1:
+        dist.barrier()
+    path = checkpoint_path()
+    model = ModelLoader().load(path, target=f"cuda:{local_rank}", max_kv=2048, kv_dtype=args.kv_dtype)
+    prompt = prompt_ids()
+    K, W = args.steps, args.warmup
+    max_seq = max(2048, PROMPT_LEN + 2 * (K + W) + 8)
+    model.max_kv = max_seq
+    session = model.create_session(SessionConfig(max_sequence_length=max_seq))
+    first = session.prefill_argmax(prompt)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident arm
+    toks_w, _ = session.decode_loop(first, W)
+    barrier()
+    launches0 = session.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        toks, ms = session.decode_loop(int(toks_w[-1]), K)
+        barrier()
+        gpu_launches = session.launch_count() - launches0
+        # ---- end-to-end arm through the public per-token call
+        nxt = int(toks[-1])
+        for _ in range(W):
+            nxt = session.decode_argmax(nxt)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            nxt = session.decode_argmax(nxt)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1]) / 1e3
+    weight_bytes = session.decode_weight_bytes()
+
+    if rank == 0:
+        hbm_peak, peak_kind = peaks()
+        lm_ms, lm_bytes, lm_enc = time_lm_head(path)
+        achieved = lm_bytes / (lm_ms * 1e-3) / 1e9
+        out = {
+            "metric": "decode_tokens_per_s", "value": world * K / (ms * 1e-3), "unit": "tok/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "kv_dtype": args.kv_dtype, "parallelism": f"replicas x{world}",
+                       "l2": "inputs larger than L2: each step streams %.1f MB of weights" % (weight_bytes / 1e6),
+                       "weight_bytes_per_step": weight_bytes},
+            "weight_gbs": world * weight_bytes * K / (ms * 1e-3) / 1e9,
+            "weight_hbm_frac_of_%s" % peak_kind: weight_bytes * K / (ms * 1e-3) / 1e9 / hbm_peak,
+            "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 24,
+                    "d2h_bytes_per_step": 8},
+            "gpu_launches": int(gpu_launches),
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "hbm", "kernel": f"linear_rows_kernel<{lm_enc}> lm_head 151936x1024, M=1",
+                         "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "peak_source": peak_kind,
+                         "bytes_per_launch": lm_bytes, "ms_per_launch": lm_ms, "traffic": None},
+        }
+        if not args.no_cpu_baseline:
+            steps = 24
+            tps, cores, dt = cpu_decode_rate(path, steps)
+            out["cpu_baseline"] = {
+                "value": tps, "unit": "tok/s", "cores": cores, "kind": "port",
+                "sample": f"{steps} decode steps of the same model after a 4-token prompt ({dt:.1f} s), "
+                          "CPU restatement of the reference's direct path"}
+        print(json.dumps(out), flush=True)
+    session.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -231,3 +231,27 @@ class Model:
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def weights_from_catalog(cat) -> dict:
+    """Oracle weights built from a checkpoint catalog's byte ranges — the same bytes the
+    GPU session uploads. Norm vectors are widened exactly to f32."""
+    blobs = [np.fromfile(p, dtype=np.uint8) for p in cat.files]
+    out = {}
+    for name, p in cat.parameters.items():
+        comp = {c.name: blobs[c.source_file_index][c.offset:c.offset + c.length] for c in p.components}
+        shape = p.shape
+        rows, cols = (shape if len(shape) == 2 else (1, shape[0]))
+        if p.encoding == "mlx.affine.u4":
+            out[name] = Weight(p.encoding, rows, cols, comp["packed"], comp["scales"], comp["biases"],
+                               p.components[1].type_name, p.group)
+            continue
+        enc, data = p.encoding, comp["data"]
+        if len(shape) == 1 and enc != "plain.f32":
+            if enc == "plain.bf16":
+                data = (data.view(np.uint16).astype(np.uint32) << 16).view(np.float32).view(np.uint8)
+            else:
+                data = data.view(np.float16).astype(np.float32).view(np.uint8)
+            enc = "plain.f32"
+        out[name] = Weight(enc, rows, cols, data)
+    return out

@@ -21,24 +21,7 @@ def oracle_weights(orc, tensors):
 
 def catalog_weights(orc, cat):
     """Oracle weights straight from a checkpoint file's byte ranges (what the GPU uploads)."""
-    blobs = [np.fromfile(p, dtype=np.uint8) for p in cat.files]
-    out = {}
-    for name, p in cat.parameters.items():
-        comp = {c.name: blobs[c.source_file_index][c.offset:c.offset + c.length] for c in p.components}
-        shape = p.shape
-        rows, cols = (shape if len(shape) == 2 else (1, shape[0]))
-        if p.encoding == "mlx.affine.u4":
-            out[name] = orc.Weight(p.encoding, rows, cols, comp["packed"], comp["scales"], comp["biases"],
-                                   p.components[1].type_name, p.group)
-        else:
-            enc, data = p.encoding, comp["data"]
-            if len(shape) == 1 and enc != "plain.f32":   # norm vectors: exact widening to f32
-                u = data.view(np.uint16).astype(np.uint32)
-                data = ((u << 16).view(np.float32) if enc == "plain.bf16"
-                        else data.view(np.float16).astype(np.float32)).view(np.uint8)
-                enc = "plain.f32"
-            out[name] = orc.Weight(enc, rows, cols, data)
-    return out
+    return orc.weights_from_catalog(cat)
 
 
 def write_fixture_gguf(path, cfg, tensors, arch="qwen3"):
@@ -101,3 +84,13 @@ def rel_err(a, b):
 def cosine(a, b):
     a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
     return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300))
+
+
+def bits_equal(a, b):
+    """Bit-for-bit equality of two f32 arrays; NaNs must sit in the same places but their
+    payload bits are not compared (a NaN scale in a block makes x86 and the GPU pick
+    different, equally valid, quiet-NaN encodings)."""
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    na, nb = np.isnan(a), np.isnan(b)
+    return a.shape == b.shape and np.array_equal(na, nb) and \
+        np.array_equal(a.view(np.uint32)[~na], b.view(np.uint32)[~nb])

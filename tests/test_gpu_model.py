@@ -1,0 +1,194 @@
+"""Whole-decoder parity through the session ABI: logits, greedy tokens, prefill vs decode."""
+import numpy as np
+import pytest
+
+import fixtures_ref as fx
+import helpers
+from dyninfer_b200 import DynInferError, checkpoint as ck, synth
+from dyninfer_b200.runtime import GenerateConfig, ModelLoader, PerfConfig, SessionConfig, generate_greedy, run_perf
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def greedy_match(got, want_tokens, margins, tie=1e-3):
+    """Identical greedy tokens except where the oracle's top-2 margin is a near-tie (< 1e-3)."""
+    for i, (g, w) in enumerate(zip(got, want_tokens)):
+        if g != w:
+            assert margins[i] < tie, f"step {i}: token {g} != {w} with margin {margins[i]}"
+            return i
+    return len(want_tokens)
+
+
+def oracle_run(oracle, cat, prompt, steps, kv_round=0, kv_cap=512, cfg_over=None):
+    cfg = dict(cat.config, **(cfg_over or {}))
+    m = oracle.Model(cfg, helpers.catalog_weights(oracle, cat), kv_cap=kv_cap, kv_round=kv_round, fast=True)
+    logits, tok = m.forward(prompt)
+    all_logits, toks, margins = [logits], [tok], []
+    for _ in range(steps):
+        top2 = np.partition(all_logits[-1], -2)[-2:]
+        margins.append(float(top2[1] - top2[0]))
+        logits, tok = m.forward([toks[-1]])
+        all_logits.append(logits)
+        toks.append(tok)
+    top2 = np.partition(all_logits[-1], -2)[-2:]
+    margins.append(float(top2[1] - top2[0]))
+    return all_logits, toks, margins
+
+
+@pytest.mark.parametrize("kind", ["f32", "gguf_mixed", "mlx_u4"])
+def test_reference_tiny_fixtures(native_lib, oracle, tmp_path, kind):
+    """The reference's differential e2e: logits within 1e-3 of reference.rs, tokens [1,2,3,0]
+    (crates/dyninfer-runtime/src/e2e.rs:43-140,245-306,364-409)."""
+    tens = fx.encoded_tensors(fx.TINY, kind)
+    if kind == "mlx_u4":
+        path = helpers.write_fixture_mlx(str(tmp_path / "m"), fx.TINY, tens)
+    else:
+        path = helpers.write_fixture_gguf(str(tmp_path / "t.gguf"), fx.TINY, tens, arch="llama")
+    model = ModelLoader().load(path, max_kv=128, chunk_size=4)
+    model.catalog.config.update(qk_norm=False, rope=False)     # the M1 fixture has neither
+    want = fx.reference_rs_forward(fx.roundtrip_weights(fx.TINY, kind), [1, 2, 3, 0])
+    with model.create_session(SessionConfig(max_sequence_length=128)) as s:
+        got = s.prefill([1, 2, 3, 0]).values
+        assert np.abs(got - want).max() < 1e-3
+        assert s.position() == 4
+        s.reset()
+        s.prefill([1, 2, 3])
+        step = s.decode(0).values                               # prefill(3) + decode(1) == prefill(4)
+        assert np.abs(step - got).max() < 1e-3
+        assert s.prefill_argmax([1, 2, 3, 0]) == int(np.argmax(want))
+
+
+def test_gqa_rope_qknorm_prefill_vs_decode(native_lib, oracle, tmp_path):
+    """e2e.rs:412-464,509-552: GQA + RoPE + QK-norm, prefill vs step decode < 1e-2 (here 1e-4)."""
+    tens = fx.encoded_tensors(fx.GQA, "f32")
+    path = helpers.write_fixture_gguf(str(tmp_path / "g.gguf"), fx.GQA, tens)
+    model = ModelLoader().load(path, max_kv=8, chunk_size=4)
+    cat = ck.open_catalog(path)
+    want, _, _ = oracle_run(oracle, cat, [5, 17, 3, 41], 0, kv_cap=8)
+    with model.create_session(SessionConfig(max_sequence_length=8)) as s:
+        full = s.prefill([5, 17, 3, 41]).values
+        assert np.abs(full - want[0]).max() < 1e-4
+        s.reset()
+        lg = s.prefill([5]).values
+        for t in [17, 3, 41]:
+            lg = s.decode(t).values
+        assert np.abs(lg - full).max() < 1e-4
+        for _ in range(4):
+            lg = s.decode(1).values
+        with pytest.raises(DynInferError, match="exceeds session/KV limit"):
+            s.decode(1)
+
+
+@pytest.mark.parametrize("flavor", ["gguf_q4_0", "gguf_mixed", "mlx_u4"])
+@pytest.mark.parametrize("kv", ["f32", "bf16"])
+def test_tiny_qwen3_logits_and_greedy(native_lib, oracle, tmp_path, flavor, kv):
+    """Seeded Qwen3-shaped model (2 layers): prompt of 16 ids, 32 greedy steps.
+    logits max-abs <= 1e-2, cosine >= 0.9999, identical greedy tokens except near-ties."""
+    if flavor == "mlx_u4":
+        path = synth.write_qwen3_mlx(str(tmp_path / "mlx"), synth.TINY, seed=11)
+    else:
+        encs = {"attn_v": "gguf.q4_1", "ffn_down": "gguf.q8_0"} if flavor == "gguf_mixed" else None
+        path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), synth.TINY, seed=11, encodings=encs,
+                                      output="gguf.q6_k" if flavor == "gguf_mixed" else None)
+    model = ModelLoader().load(path, max_kv=512, kv_dtype=kv, chunk_size=16)
+    cat = ck.open_catalog(path)
+    prompt = np.random.default_rng(5).integers(0, synth.TINY["vocab"], size=16).tolist()
+    steps = 32
+    want_logits, want_toks, margins = oracle_run(oracle, cat, prompt, steps, kv_round=2 if kv == "bf16" else 0)
+    with model.create_session(SessionConfig(max_sequence_length=512)) as s:
+        lg = s.prefill(prompt).values
+        assert np.abs(lg - want_logits[0]).max() <= 1e-2 and helpers.cosine(lg, want_logits[0]) >= 0.9999
+        toks = [int(np.argmax(lg))]
+        agree = 1
+        for i in range(steps):
+            # teacher-forced with the oracle's token so that every step is comparable
+            lg = s.decode(want_toks[i]).values
+            assert np.abs(lg - want_logits[i + 1]).max() <= 1e-2
+            assert helpers.cosine(lg, want_logits[i + 1]) >= 0.9999
+            toks.append(int(np.argmax(lg)))
+        greedy_match(toks, want_toks, margins)
+        # free-running greedy through the argmax entry points and the device-side loop
+        first = s.prefill_argmax(prompt)
+        run = [first]
+        for _ in range(8):
+            run.append(s.decode_argmax(run[-1]))
+        n_ok = greedy_match(run, want_toks[:9], margins[:9])
+        first2 = s.prefill_argmax(prompt)
+        loop, ms = s.decode_loop(first2, 8)
+        assert ms > 0 and [first2] + loop.tolist() == run
+        assert n_ok >= 1 and s.launch_count() > 0
+
+
+def test_chunked_prefill_padding_and_limits(native_lib, oracle, tmp_path):
+    path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), synth.TINY, seed=2)
+    cat = ck.open_catalog(path)
+    prompt = np.random.default_rng(1).integers(0, 512, size=21).tolist()
+    want, _, _ = oracle_run(oracle, cat, prompt, 0)
+    model = ModelLoader().load(path, max_kv=300, chunk_size=8)       # 21 tokens = chunks 8 + 8 + 5 (right padded)
+    with model.create_session(SessionConfig(max_sequence_length=300)) as s:
+        lg = s.prefill(prompt).values
+        assert np.abs(lg - want[0]).max() <= 1e-3
+        m = s.kv_cache_metrics()
+        assert m.page_count == 2 and m.paged and m.chunk_size == 8 and m.filled_tokens == 21
+        assert m.allocated_bytes == 2 * 2 * 2 * 512 * 64 * 4        # K+V x layers x kv heads x cap x d x 4
+        a = s.allocator_metrics()
+        assert a.device_live_bytes() >= m.allocated_bytes + s.weight_bytes()
+        s.reset()
+        assert s.position() == 0 and s.kv_cache_metrics().page_count == 2   # reset keeps the pool
+        assert np.abs(s.prefill(prompt).values - lg).max() == 0.0            # and is deterministic
+        with pytest.raises(DynInferError, match="non-empty"):
+            s.prefill([])
+        with pytest.raises(DynInferError, match="exceeds session/KV limit"):
+            s.prefill([1] * 301)
+        with pytest.raises(DynInferError, match="token id"):
+            s.prefill([1, 99999])
+    with pytest.raises(DynInferError, match="only batch_size=1"):
+        model.create_session(SessionConfig(batch_size=2)).prefill([1])
+
+
+def test_abi_misuse_is_reported(native_lib, tmp_path):
+    import ctypes as C
+    from dyninfer_b200 import _lib
+    path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), synth.TINY, seed=2)
+    model = ModelLoader().load(path, max_kv=256, chunk_size=8)
+    with model.create_session() as s:
+        L, h = _lib.lib(), s._h
+        tok = (C.c_int64 * 8)(*range(8))
+        out = C.c_int64()
+        assert L.dyninfer_cuda_session_invoke_paged_chunk(h, tok, 8, 0, 0, None, None, C.byref(out), 0) != 0
+        assert "no pages" in _lib.last_error()
+        assert L.dyninfer_cuda_session_ensure_kv_pages(h, 1) == 0
+        assert L.dyninfer_cuda_session_invoke_paged_chunk(h, tok, 3, 0, 0, None, None, C.byref(out), 0) != 0
+        assert "must be 1 or the chunk size" in _lib.last_error()
+        assert L.dyninfer_cuda_session_invoke_paged_chunk(h, tok, 8, 8, 0, None, None, C.byref(out), 0) != 0
+        assert L.dyninfer_cuda_session_invoke_paged_chunk(h, tok, 8, 0, -1, None, None, C.byref(out), 0) != 0
+        assert L.dyninfer_cuda_session_invoke_paged_chunk(h, tok, 8, 7, 250, None, None, C.byref(out), 0) != 0
+        assert "exceed the KV capacity" in _lib.last_error()
+        # want_logits = 0 with NULL logits pointers still yields the argmax token (wrapper.c:1172-1215)
+        assert L.dyninfer_cuda_session_invoke_paged_chunk(h, tok, 8, 7, 0, None, None, C.byref(out), 0) == 0
+        assert 0 <= out.value < 512
+        # reconfiguring after allocation is an error (wrapper.c:927-930)
+        assert L.dyninfer_cuda_session_configure_paged_kv(h, 2, 256, 2, 64, 4, 8, 512) != 0
+        assert "cannot be reconfigured" in _lib.last_error()
+    bad = ck.open_catalog(path)
+    plan = ck.build_runtime_provider_plan(bad)
+    plan.parameters[0].length -= 18                                   # short byte range
+    model.plan = plan
+    with pytest.raises(DynInferError, match="byte range"):
+        model.create_session()
+
+
+def test_generate_and_perf_report(native_lib, tmp_path):
+    path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), synth.TINY, seed=4)
+    model = ModelLoader().load(path, max_kv=256, chunk_size=16)
+    ids, stats = generate_greedy(model, [3, 1, 4, 1, 5], GenerateConfig(max_new_tokens=12), SessionConfig(256))
+    assert len(ids) == 17 and stats.generated_tokens == 12 and stats.decode_tps() > 0
+    ids2, _ = generate_greedy(model, [3, 1, 4, 1, 5], GenerateConfig(max_new_tokens=12, repetition_penalty=1.0 + 1e-9),
+                              SessionConfig(256))
+    assert ids2 == ids
+    stop = ids[7]
+    ids3, st3 = generate_greedy(model, [3, 1, 4, 1, 5], GenerateConfig(max_new_tokens=12, eos_token_id=stop), SessionConfig(256))
+    assert stop not in ids3[5:] and st3.generated_tokens <= 2 + ids[5:].index(stop)
+    rep = run_perf(model, PerfConfig(prefill_tokens=20, tg=4, warmup=1, iters=2, weight_bytes=1000), SessionConfig(256))
+    assert rep["decode"]["tokens"] == 4 and rep["decode"]["eff_weight_bw_gbs"] > 0 and rep["prefill"]["tps"] > 0

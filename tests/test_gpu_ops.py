@@ -1,0 +1,172 @@
+"""Parity of every single operator against the CPU oracle, through the C ABI, on a GPU."""
+import os
+
+import numpy as np
+import pytest
+
+import helpers
+from dyninfer_b200 import synth
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+ENCS = ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "mlx.affine.u4", "plain.bf16", "plain.f16", "plain.f32"]
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "dequant_golden.npz")
+
+
+def make_pair(oracle, enc, rows, cols, seed, aux="plain.bf16"):
+    from dyninfer_b200 import ops
+    t = synth.random_weight(enc, rows, cols, seed)
+    if enc == "mlx.affine.u4":
+        sc, bi = t["scales"], t["biases"]
+        if aux == "plain.f32":
+            sc, bi = synth.bf16_bits_to_f32(sc), synth.bf16_bits_to_f32(bi)
+        dw = ops.DeviceWeight(enc, rows, cols, t["packed"], sc, bi, aux, 64)
+        ow = oracle.Weight(enc, rows, cols, t["packed"], sc, bi, aux, 64)
+    else:
+        dw = ops.DeviceWeight(enc, rows, cols, t["data"])
+        ow = oracle.Weight(enc, rows, cols, t["data"])
+    return dw, ow
+
+
+@pytest.mark.parametrize("enc", ENCS)
+@pytest.mark.parametrize("shape", [(1, 256), (33, 512), (257, 1024)])
+def test_dequant_bit_exact(native_lib, oracle, enc, shape):
+    from dyninfer_b200 import ops
+    dw, ow = make_pair(oracle, enc, *shape, seed=shape[0])
+    got = ops.dequant(dw).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), oracle.dequant(ow).view(np.uint32))
+
+
+def test_dequant_golden_and_mlx_f32_aux(native_lib, oracle):
+    from dyninfer_b200 import ops
+    g = np.load(GOLD)
+    for enc in ENCS[:4]:
+        want = g[enc + ":f32"]
+        dw = ops.DeviceWeight(enc, want.shape[0], want.shape[1], g[enc + ":raw"])
+        assert helpers.bits_equal(ops.dequant(dw).cpu().numpy(), want), enc
+    dw, ow = make_pair(oracle, "mlx.affine.u4", 17, 512, 3, aux="plain.f32")
+    assert np.array_equal(ops.dequant(dw).cpu().numpy().view(np.uint32), oracle.dequant(ow).view(np.uint32))
+
+
+def test_dequant_full_size_q4_0_checksum(native_lib, oracle):
+    """Full-size tensor (3072 x 1024): a sampled-row comparison plus a linearity property
+    (sum over the tensor equals the sum of block scale x integer sums)."""
+    from dyninfer_b200 import ops
+    dw, ow = make_pair(oracle, "gguf.q4_0", 3072, 1024, 7)
+    got = ops.dequant(dw).cpu().numpy()
+    for r in (0, 1, 1535, 3071):
+        assert np.array_equal(got[r].view(np.uint32), oracle.dequant_row(ow, r).view(np.uint32))
+    blk = ow.data.reshape(-1, 18)
+    d = blk[:, :2].copy().view(np.float16).astype(np.float64)[:, 0]
+    q = blk[:, 2:]
+    isum = ((q & 15).astype(np.int64) - 8).sum(axis=1) + ((q >> 4).astype(np.int64) - 8).sum(axis=1)
+    assert abs(got.astype(np.float64).sum() - float((d * isum).sum())) < 1e-6 * max(1.0, np.abs(d * isum).sum())
+
+
+@pytest.mark.parametrize("enc", ENCS)
+def test_embedding_gather(native_lib, oracle, enc):
+    from dyninfer_b200 import ops
+    dw, ow = make_pair(oracle, enc, 64, 512, 9)
+    ids = np.array([0, 63, 5, 5, 31], dtype=np.int64)
+    got = ops.embedding_gather(dw, torch.from_numpy(ids)).cpu().numpy()
+    for i, t in enumerate(ids):
+        assert np.array_equal(got[i].view(np.uint32), oracle.dequant_row(ow, int(t)).view(np.uint32))
+    assert ops.embedding_gather(dw, torch.zeros(0, dtype=torch.int64)).shape == (0, 512)
+
+
+@pytest.mark.parametrize("enc", ENCS)
+@pytest.mark.parametrize("m", [1, 2, 3, 8, 17])
+def test_linear_vs_oracle(native_lib, oracle, enc, m):
+    """GEMV / skinny GEMM: rel <= 1e-3 with f32 accumulation (bf16 activations ~N(0,1))."""
+    from dyninfer_b200 import ops
+    n, k = 96, 1024
+    dw, ow = make_pair(oracle, enc, n, k, seed=m)
+    xb = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(torch.bfloat16)
+    want = oracle.linear(ow, xb.float().numpy())
+    got_bf16 = ops.linear(dw, xb.cuda()).cpu().numpy()
+    got_f32 = ops.linear(dw, xb.float().cuda()).cpu().numpy()
+    assert helpers.rel_err(got_bf16, want) < 1e-3 and helpers.rel_err(got_f32, want) < 1e-3
+    assert helpers.rel_err(got_f32, want) < 2e-5          # exact weights, f32 sums: only the order differs
+
+
+@pytest.mark.parametrize("enc,n,k", [("gguf.q4_0", 1, 32), ("gguf.q4_0", 5, 64), ("gguf.q8_0", 33, 96),
+                                     ("gguf.q6_k", 3, 256), ("mlx.affine.u4", 7, 64), ("plain.f32", 2, 4),
+                                     ("gguf.q4_1", 1024, 3072), ("gguf.q4_0", 3072, 1024)])
+def test_linear_ragged_and_full_shapes(native_lib, oracle, enc, n, k):
+    from dyninfer_b200 import ops
+    dw, ow = make_pair(oracle, enc, n, k, seed=n + k)
+    x = np.random.default_rng(n).normal(size=(2, k)).astype(np.float32)
+    got = ops.linear(dw, torch.from_numpy(x).cuda()).cpu().numpy()
+    assert helpers.rel_err(got, oracle.linear(ow, x, fast=True)) < 1e-4
+
+
+def test_linear_linearity_full_size_lm_head(native_lib, oracle):
+    """Size-independent property at the lm_head's full size (151936 x 1024, Q6_K):
+    W(a*x + y) == a*W(x) + W(y), and sampled rows against the oracle."""
+    from dyninfer_b200 import ops
+    n, k = 151936, 1024
+    dw, ow = make_pair(oracle, "gguf.q6_k", n, k, seed=2)
+    g = torch.Generator().manual_seed(0)
+    x, y = torch.randn(1, k, generator=g).cuda(), torch.randn(1, k, generator=g).cuda()
+    wx, wy, wxy = ops.linear(dw, x), ops.linear(dw, y), ops.linear(dw, 2.0 * x + y)
+    assert helpers.rel_err((2.0 * wx + wy).cpu().numpy(), wxy.cpu().numpy()) < 1e-5
+    xr = x.cpu().numpy()[0]
+    for r in (0, 77777, n - 1):
+        want = float(oracle.dequant_row(ow, r).astype(np.float64) @ xr.astype(np.float64))
+        assert abs(float(wx[0, r]) - want) < 1e-4 * max(1.0, abs(want))
+
+
+def test_rms_norm_rope_silu(native_lib, oracle):
+    from dyninfer_b200 import ops
+    rng = np.random.default_rng(0)
+    x = rng.normal(size=(5, 1024)).astype(np.float32) * 3
+    w = rng.normal(size=1024).astype(np.float32)
+    got = ops.rms_norm(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), 1e-6).cpu().numpy()
+    assert np.abs(got - oracle.rms_norm(x, w, 1e-6)).max() < 1e-5
+    wb = torch.from_numpy(w).to(torch.bfloat16)
+    got = ops.rms_norm(torch.from_numpy(x).cuda(), wb.cuda(), 1e-6).cpu().numpy()
+    assert np.abs(got - oracle.rms_norm(x, wb.float().numpy(), 1e-6)).max() < 1e-5
+    h = rng.normal(size=(3 * 16, 128)).astype(np.float32)      # per-head norm over d = 128
+    wd = rng.normal(size=128).astype(np.float32)
+    got = ops.rms_norm(torch.from_numpy(h).cuda(), torch.from_numpy(wd).cuda(), 1e-6).cpu().numpy()
+    assert np.abs(got - oracle.rms_norm(h, wd, 1e-6)).max() < 1e-5
+    for d, theta, start in ((128, 1e6, 0), (128, 1e6, 4090), (8, 1e4, 3)):
+        q = rng.normal(size=(4, 6, d)).astype(np.float32)
+        got = ops.rope(torch.from_numpy(q).cuda(), start, theta).cpu().numpy()
+        assert np.abs(got - oracle.rope(q, start, theta)).max() < 2e-5
+    g, u = rng.normal(size=4096).astype(np.float32) * 4, rng.normal(size=4096).astype(np.float32)
+    got = ops.silu_mul(torch.from_numpy(g).cuda(), torch.from_numpy(u).cuda()).cpu().numpy()
+    assert np.abs(got - oracle.silu_mul(g, u)).max() < 1e-5
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("s,start,d,nh,nkv", [(1, 0, 128, 16, 8), (1, 300, 128, 16, 8), (5, 7, 128, 4, 2),
+                                              (4, 0, 8, 4, 2), (3, 255, 64, 4, 4)])
+def test_attention_vs_oracle(native_lib, oracle, dtype, s, start, d, nh, nkv):
+    from dyninfer_b200 import ops
+    rng = np.random.default_rng(start + s)
+    cap = 512
+    q = rng.normal(size=(s, nh, d)).astype(np.float32)
+    k = rng.normal(size=(nkv, cap, d)).astype(np.float32)
+    v = rng.normal(size=(nkv, cap, d)).astype(np.float32)
+    tt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[dtype]
+    kt, vt = torch.from_numpy(k).to(tt), torch.from_numpy(v).to(tt)
+    want = oracle.attention(q, kt.float().numpy(), vt.float().numpy(), start, s)
+    got = ops.attention(torch.from_numpy(q).cuda(), kt.cuda(), vt.cuda(), start).cpu().numpy()
+    assert np.abs(got - want).max() < 2e-5
+
+
+def test_argmax_first_maximum(native_lib, oracle):
+    from dyninfer_b200 import ops
+    rng = np.random.default_rng(3)
+    v = rng.normal(size=151936).astype(np.float32)
+    assert ops.argmax(torch.from_numpy(v).cuda()) == oracle.argmax(v)
+    v[[1000, 90000, 151935]] = 50.0                        # ties: the lowest index wins
+    assert ops.argmax(torch.from_numpy(v).cuda()) == 1000
+    v[:] = -np.inf
+    assert ops.argmax(torch.from_numpy(v).cuda()) == 0
+    v[7] = np.nan
+    v[9] = -3.0
+    assert ops.argmax(torch.from_numpy(v).cuda()) == 9
+    assert ops.argmax(torch.tensor([2.0]).cuda()) == 0

@@ -19,8 +19,8 @@ def test_dequant_matches_golden_bit_exact(oracle, enc):
     raw, want = g[enc + ":raw"], g[enc + ":f32"]
     w = oracle.Weight(enc, want.shape[0], want.shape[1], raw)
     got = oracle.dequant(w)
-    assert got.view(np.uint32).tolist() == want.view(np.uint32).tolist()
-    assert np_ref.dequant(enc, raw, *want.shape).view(np.uint32).tolist() == want.view(np.uint32).tolist()
+    assert helpers.bits_equal(got, want)
+    assert helpers.bits_equal(np_ref.dequant(enc, raw, *want.shape), want)
 
 
 @pytest.mark.parametrize("enc", GGUF_ENCS)

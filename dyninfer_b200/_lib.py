@@ -76,6 +76,7 @@ PROTOTYPES = {
     "dyninfer_cuda_session_decode_loop": (C.c_int, [_P, _I64, _I64, C.c_size_t, C.POINTER(_I64),
                                                     C.POINTER(C.c_float)]),
     "dyninfer_cuda_session_launch_count": (C.c_uint64, [_P]),
+    "dyninfer_cuda_session_decode_phase_profile": (C.c_int, [_P, C.POINTER(C.c_double), C.c_size_t]),
 }
 
 _lib = None

@@ -116,6 +116,7 @@ int dyninfer_cuda_embedding_gather(const dyninfer_cuda_weight_t* w, const int64_
   if (wref_from_api(w, &r)) return 1;
   DYN_CHECK(count >= 0, "count must be >= 0");
   DYN_CHECK(count == 0 || tokens_dev, "tokens is NULL");
+  if (count == 0) return 0;
   DYN_CHECK(out_dev && aligned(out_dev, 16), "out must be a 16-byte aligned device pointer");
   if (require_device()) return 1;
   return launch_gather(r, tokens_dev, count, out_dev, (cudaStream_t)stream);

@@ -141,6 +141,10 @@ int launch_gather(const WRef& w, const int64_t* tokens, int64_t count, float* ou
 // y[m, N] = x[m, K] * W^T ; optional residual (added to result) ; x f32 or bf16.
 int launch_linear(const WRef& w, const void* x, int x_type, int64_t m, float* y,
                   const float* residual, cudaStream_t s);
+// Tensor-core GEMV for few activation rows (gemv_mma.cu); *handled tells whether it ran.
+size_t gemv_mma_workspace_bytes(const WRef& w, int x_type, int M);
+int launch_gemv_mma(const WRef& w, const void* x, int x_type, int M, float* y, const float* residual,
+                    void* workspace, cudaStream_t s, bool* handled);
 // y = silu(x Wg^T) * (x Wu^T)
 int launch_linear_swiglu(const WRef& wg, const WRef& wu, const float* x, int64_t m, float* y,
                          cudaStream_t s);

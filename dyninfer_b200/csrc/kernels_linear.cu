@@ -123,6 +123,28 @@ int launch_linear(const WRef& w, const void* x, int x_type, int64_t m, float* y,
   DYN_CHECK(x_type == E_F32 || x_type == E_BF16, "linear: x_type must be f32 or bf16, got %d",
             x_type);
   DYN_CHECK(m >= 1, "linear: m must be >= 1");
+  {
+    // few rows: tensor-core GEMV, 4 (f32) or 8 (bf16) activation rows per pass over the weights
+    const int64_t step = x_type == E_BF16 ? 8 : 4;
+    const size_t xe = x_type == E_BF16 ? 2 : 4;
+    int64_t m0 = 0;
+    for (; m0 < m && m <= 16; m0 += step) {
+      const int mv = (int)((m - m0) < step ? (m - m0) : step);
+      bool handled = false;
+      if (launch_gemv_mma(w, reinterpret_cast<const uint8_t*>(x) + (size_t)m0 * w.cols * xe, x_type, mv,
+                          y + m0 * w.rows, residual ? residual + m0 * w.rows : nullptr, nullptr, s,
+                          &handled))
+        return 1;
+      if (!handled) break;
+    }
+    if (m0 >= m) return 0;
+    if (m0 > 0) {  // cannot happen: the first chunk decides for the whole shape
+      x = reinterpret_cast<const uint8_t*>(x) + (size_t)m0 * w.cols * xe;
+      y += m0 * w.rows;
+      if (residual) residual += m0 * w.rows;
+      m -= m0;
+    }
+  }
   if (x_type == E_BF16) {
     DYN_ENC_SWITCH(w.enc, return (run_linear<ENC, true>(w, x, m, y, residual, s)));
   } else {

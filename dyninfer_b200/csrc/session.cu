@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "decode_mega.cuh"
 #include "json_min.h"
 
 namespace dyn {
@@ -35,6 +36,7 @@ struct ModelCfg {
   bool qk_norm = true, rope = true;
   int batch = 1;
   int kv2_type = E_BF16;  // element type used when the KV cache is configured with 2 bytes
+  bool persistent = true;  // single-token steps run as the persistent decode kernel
 };
 
 }  // namespace dyn
@@ -72,6 +74,17 @@ struct dyninfer_cuda_session_t {
   // pinned host staging
   float* logits_host = nullptr;
   int64_t* stage_host = nullptr;  // [0]=token [1]=pos [2]=seq [3]=out token, then chunk arrays
+  // persistent decode kernel
+  bool mega = false;
+  int mega_grid = 0, mega_nslot = 0, mega_xs = 0, mega_max_split = 1;
+  size_t mega_smem = 0;
+  MegaLayer* mega_layers = nullptr;
+  int64_t* io_dev = nullptr;  // [0] token [1] position [2] slot [3] produced token [4] error word
+  unsigned long long* bar_dev = nullptr;
+  float* attn_part = nullptr;
+  float* amax_val = nullptr;
+  long long* amax_idx = nullptr;
+  unsigned long long* prof_dev = nullptr;
   // graphs
   cudaGraphExec_t decode_graph = nullptr;  // H2D token/pos + forward + D2H token
   cudaGraphExec_t loop_graph = nullptr;    // forward + device-side advance
@@ -342,6 +355,44 @@ int ensure_hist(Session* s, size_t steps) {
   return 0;
 }
 
+void fill_mega_args(Session* s, MegaArgs* a, int advance) {
+  const ModelCfg& c = s->cfg;
+  a->layers = c.layers, a->H = c.hidden, a->I = c.inter, a->V = c.vocab;
+  a->nh = c.heads, a->nkv = c.kv_heads, a->d = c.head_dim;
+  a->eps = c.eps;
+  a->has_norm = c.qk_norm ? 1 : 0, a->has_rope = c.rope ? 1 : 0;
+  a->L = s->mega_layers;
+  a->embed = s->embed, a->lm_head = s->lm_head;
+  a->out_norm = s->out_norm.ptr, a->out_norm_type = s->out_norm.type;
+  a->hidden = s->hidden, a->q = s->q, a->k = s->k, a->v = s->v, a->ctx = s->ctx, a->act = s->act;
+  a->logits = s->logits;
+  a->kcache = s->kcache, a->vcache = s->vcache;
+  a->cap = (int64_t)(s->pages * s->page_size);
+  a->layer_stride = (uint64_t)c.batch * c.kv_heads * (uint64_t)a->cap * c.head_dim * s->kv_elem;
+  a->kv_type = s->kv_type;
+  a->io = s->io_dev;
+  a->hist = s->hist_dev, a->hist_count = s->hist_count_dev, a->hist_cap = (int64_t)s->hist_cap;
+  a->advance = advance;
+  a->bar = s->bar_dev;
+  a->error = reinterpret_cast<int*>(s->io_dev + 4);
+  a->attn_part = s->attn_part, a->max_split = s->mega_max_split;
+  a->argmax_val = s->amax_val, a->argmax_idx = s->amax_idx;
+  a->prof = s->prof_dev;
+  a->nslot = s->mega_nslot, a->xs_floats = s->mega_xs;
+  a->ft = s->freq;
+}
+
+// A bounded wait inside the kernel gave up: report it and put the barrier words back to zero.
+int mega_check_error(Session* s, int64_t word) {
+  if ((int)word == 0) return 0;
+  cudaMemsetAsync(s->bar_dev, 0, 64, s->stream);
+  cudaMemsetAsync(s->io_dev + 4, 0, 8, s->stream);
+  cudaStreamSynchronize(s->stream);
+  set_error("persistent decode kernel: a bounded wait expired (code %d: 2 grid barrier, 3 weight "
+            "ring full-wait, 4 ring empty-wait)", (int)word);
+  return 1;
+}
+
 struct CounterScope {  // routes count_launch() to this session for the duration of a call
   explicit CounterScope(Session* s) { set_launch_counter(&s->launches); }
   ~CounterScope() { set_launch_counter(nullptr); }
@@ -402,6 +453,10 @@ int dyninfer_cuda_session_create_with_file_params(
     DYN_CHECK(kvd == "bf16" || kvd == "f16" || kvd == "f32", "kv_dtype `%s` unsupported",
               kvd.c_str());
     cfg.kv2_type = kvd == "f16" ? E_F16 : E_BF16;
+    std::string dk = desc.string("decode_kernel", "persistent");
+    DYN_CHECK(dk == "persistent" || dk == "graph", "decode_kernel `%s` unknown (persistent | graph)",
+              dk.c_str());
+    cfg.persistent = dk == "persistent";
   }
   DYN_CHECK(cfg.layers > 0 && cfg.hidden > 0 && cfg.inter > 0 && cfg.heads > 0 &&
                 cfg.kv_heads > 0 && cfg.head_dim > 0 && cfg.vocab > 0 && cfg.batch > 0,
@@ -586,6 +641,40 @@ int dyninfer_cuda_session_create_with_file_params(
   }
   s->decode_weight_bytes = dwb;
 
+  if (cfg.persistent &&
+      mega_plan(cfg.hidden, cfg.inter, (int)qd, cfg.head_dim, &s->mega_nslot, &s->mega_xs,
+                &s->mega_smem)) {
+    if (mega_grid_size(device, s->mega_smem, &s->mega_grid)) return fail();
+    std::vector<MegaLayer> ml(cfg.layers);
+    for (int l = 0; l < cfg.layers; l++) {
+      const LayerW& L = s->layers[l];
+      ml[l].q = L.q, ml[l].k = L.k, ml[l].v = L.v, ml[l].o = L.o;
+      ml[l].gate = L.gate, ml[l].up = L.up, ml[l].down = L.down;
+      ml[l].attn_norm = L.attn_norm.ptr, ml[l].ffn_norm = L.ffn_norm.ptr;
+      ml[l].q_norm = L.q_norm.ptr, ml[l].k_norm = L.k_norm.ptr;
+      ml[l].norm_type = L.attn_norm.type, ml[l].qk_norm_type = L.q_norm.type;
+      if (L.attn_norm.type != L.ffn_norm.type || L.gate.enc != L.up.enc) s->mega_grid = 0;
+    }
+    s->mega_max_split = std::max(1, std::min(16, s->mega_grid / std::max(1, cfg.heads)));
+    if (s->mega_grid > 0) {
+      const size_t part_bytes = (size_t)cfg.heads * s->mega_max_split * (cfg.head_dim + 2) * 4;
+      if (dev_alloc(s, (void**)&s->mega_layers, ml.size() * sizeof(MegaLayer)) ||
+          dev_alloc(s, (void**)&s->io_dev, 64) || dev_alloc(s, (void**)&s->bar_dev, 64) ||
+          dev_alloc(s, (void**)&s->attn_part, part_bytes) ||
+          dev_alloc(s, (void**)&s->amax_val, (size_t)s->mega_grid * 4) ||
+          dev_alloc(s, (void**)&s->amax_idx, (size_t)s->mega_grid * 8) ||
+          dev_alloc(s, (void**)&s->prof_dev, 128))
+        return fail();
+      if (cudaMemcpy(s->mega_layers, ml.data(), ml.size() * sizeof(MegaLayer),
+                     cudaMemcpyHostToDevice) != cudaSuccess ||
+          cudaMemset(s->io_dev, 0, 64) != cudaSuccess ||
+          cudaMemset(s->bar_dev, 0, 64) != cudaSuccess) {
+        set_error("initialising the persistent decode kernel state failed");
+        return fail();
+      }
+      s->mega = true;
+    }
+  }
   if (host_alloc(s, (void**)&s->logits_host, (size_t)cfg.vocab * 4)) return fail();
   if (dev_alloc(s, (void**)&s->logits, (size_t)cfg.vocab * 4) ||
       dev_alloc(s, (void**)&s->out_token_dev, 64) ||
@@ -603,7 +692,8 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
   destroy_graphs(s);
   void* dev[] = {s->arena, s->kcache, s->vcache, s->hidden, s->xn, s->q, s->k, s->v, s->ctx, s->act,
                  s->logits, s->tokens_dev, s->row_pos_dev, s->row_seq_dev, s->out_token_dev,
-                 s->hist_dev, s->hist_count_dev, s->argmax_scratch};
+                 s->hist_dev, s->hist_count_dev, s->argmax_scratch, s->mega_layers, s->io_dev,
+                 s->bar_dev, s->attn_part, s->amax_val, s->amax_idx, s->prof_dev};
   for (void* p : dev)
     if (p) cudaFree(p);
   if (s->logits_host) cudaFreeHost(s->logits_host);
@@ -649,7 +739,7 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
         dev_alloc(s, (void**)&s->tokens_dev, (size_t)rows * 8) ||
         dev_alloc(s, (void**)&s->row_pos_dev, (size_t)rows * 8) ||
         dev_alloc(s, (void**)&s->row_seq_dev, (size_t)rows * 8) ||
-        host_alloc(s, (void**)&s->stage_host, (size_t)(4 + 3 * rows) * 8))
+        host_alloc(s, (void**)&s->stage_host, (size_t)(8 + 3 * rows) * 8))
       return 1;
     s->max_rows = rows;
   } else {
@@ -729,6 +819,18 @@ uint64_t dyninfer_cuda_session_weight_bytes(const dyninfer_cuda_session_t* s) {
 uint64_t dyninfer_cuda_session_decode_weight_bytes(const dyninfer_cuda_session_t* s) {
   return s ? s->decode_weight_bytes : 0;
 }
+int dyninfer_cuda_session_decode_phase_profile(dyninfer_cuda_session_t* s, double* out_us,
+                                               size_t count) {
+  DYN_CHECK(s != nullptr && out_us != nullptr, "session or out_us is NULL");
+  DYN_CHECK(s->mega && s->prof_dev, "the persistent decode kernel is not in use");
+  unsigned long long ns[16] = {0};
+  DYN_CUDA(cudaSetDevice(s->device));
+  DYN_CUDA(cudaStreamSynchronize(s->stream));
+  DYN_CUDA(cudaMemcpy(ns, s->prof_dev, sizeof ns, cudaMemcpyDeviceToHost));
+  for (size_t i = 0; i < count && i < 16; i++) out_us[i] = (double)ns[i] * 1e-3;
+  return 0;
+}
+
 uint64_t dyninfer_cuda_session_launch_count(const dyninfer_cuda_session_t* s) {
   return s ? s->launches : 0;
 }
@@ -756,7 +858,16 @@ int dyninfer_cuda_session_invoke_paged_chunk(dyninfer_cuda_session_t* s, const i
               (long long)tokens[i], (long long)i, s->cfg.vocab);
   CounterScope scope(s);
   DYN_CUDA(cudaSetDevice(s->device));
-  if (rows == 1) {
+  if (rows == 1 && s->mega) {
+    s->stage_host[0] = tokens[0];
+    s->stage_host[1] = start_pos;
+    s->stage_host[2] = 0;
+    MegaArgs ma;
+    fill_mega_args(s, &ma, 0);
+    DYN_CUDA(cudaMemcpyAsync(s->io_dev, s->stage_host, 24, cudaMemcpyHostToDevice, s->stream));
+    if (launch_decode_mega(ma, s->mega_grid, s->mega_smem, s->stream)) return 1;
+    DYN_CUDA(cudaMemcpyAsync(s->stage_host + 3, s->io_dev + 3, 16, cudaMemcpyDeviceToHost, s->stream));
+  } else if (rows == 1) {
     if (!s->decode_graph && capture(s, false, &s->decode_graph, &s->graph_nodes)) return 1;
     s->stage_host[0] = tokens[0];
     s->stage_host[1] = start_pos;
@@ -764,7 +875,7 @@ int dyninfer_cuda_session_invoke_paged_chunk(dyninfer_cuda_session_t* s, const i
     DYN_CUDA(cudaGraphLaunch(s->decode_graph, s->stream));
     s->launches += s->graph_nodes;
   } else {
-    int64_t* st = s->stage_host + 4;
+    int64_t* st = s->stage_host + 8;
     for (int64_t i = 0; i < rows; i++) {
       st[i] = tokens[i];
       st[rows + i] = start_pos + i;
@@ -782,6 +893,7 @@ int dyninfer_cuda_session_invoke_paged_chunk(dyninfer_cuda_session_t* s, const i
     DYN_CUDA(cudaMemcpyAsync(s->logits_host, s->logits, (size_t)s->cfg.vocab * 4,
                              cudaMemcpyDeviceToHost, s->stream));
   DYN_CUDA(cudaStreamSynchronize(s->stream));
+  if (rows == 1 && s->mega && mega_check_error(s, s->stage_host[4])) return 1;
   if (out_token) *out_token = s->stage_host[3];
   if (want_logits) {
     *out_logits = s->logits_host;  // session scratch, borrowed until the next invoke
@@ -809,6 +921,26 @@ int dyninfer_cuda_session_decode_loop(dyninfer_cuda_session_t* s, int64_t first_
   CounterScope scope(s);
   DYN_CUDA(cudaSetDevice(s->device));
   if (ensure_hist(s, steps)) return 1;
+  if (s->mega) {
+    s->stage_host[0] = first_token;
+    s->stage_host[1] = start_pos;
+    s->stage_host[2] = 0;
+    MegaArgs ma;
+    fill_mega_args(s, &ma, 1);
+    DYN_CUDA(cudaMemcpyAsync(s->io_dev, s->stage_host, 24, cudaMemcpyHostToDevice, s->stream));
+    DYN_CUDA(cudaMemsetAsync(s->hist_count_dev, 0, 8, s->stream));
+    DYN_CUDA(cudaEventRecord(s->ev0, s->stream));
+    for (size_t i = 0; i < steps; i++)
+      if (launch_decode_mega(ma, s->mega_grid, s->mega_smem, s->stream)) return 1;
+    DYN_CUDA(cudaEventRecord(s->ev1, s->stream));
+    DYN_CUDA(cudaMemcpyAsync(s->stage_host + 3, s->io_dev + 3, 16, cudaMemcpyDeviceToHost, s->stream));
+    DYN_CUDA(cudaStreamSynchronize(s->stream));
+    if (mega_check_error(s, s->stage_host[4])) return 1;
+    if (out_device_ms) DYN_CUDA(cudaEventElapsedTime(out_device_ms, s->ev0, s->ev1));
+    if (out_tokens)
+      DYN_CUDA(cudaMemcpy(out_tokens, s->hist_dev, steps * 8, cudaMemcpyDeviceToHost));
+    return 0;
+  }
   if (!s->loop_graph && capture(s, true, &s->loop_graph, &s->loop_nodes)) return 1;
   s->stage_host[0] = first_token;
   s->stage_host[1] = start_pos;

@@ -99,7 +99,7 @@ class CudaSession:
         self.kv_dtype = model.kv_dtype
         self.kv_elem = 4 if self.kv_dtype == "f32" else 2
         self.max_kv = int(model.max_kv)
-        desc = ck.model_descriptor(model.catalog, kv_dtype=self.kv_dtype)
+        desc = ck.model_descriptor(model.catalog, kv_dtype=self.kv_dtype, decode_kernel=model.decode_kernel)
         files = (_lib.ParameterFile * len(model.plan.file_paths))(
             *[_lib.ParameterFile(p.encode()) for p in model.plan.file_paths])
         self._keys = [p.external_key.encode() for p in model.plan.parameters]
@@ -260,6 +260,14 @@ class CudaSession:
         self.position_ += steps
         return out, float(ms.value)
 
+    def decode_phase_profile(self) -> dict:
+        """Microseconds per phase kind in the last persistent-kernel launch (CTA 0's view)."""
+        out = (C.c_double * 16)()
+        check(lib().dyninfer_cuda_session_decode_phase_profile(self._h, out, 16))
+        names = ("embed", "qkv", "attention", "o_proj", "gate_up", "down", "lm_head", "argmax", "total",
+                 "t_stage", "t_wait_weights", "t_rows", "t_grid_barrier")
+        return dict(zip(names, [float(v) for v in out]))
+
     def weight_bytes(self) -> int:
         return int(lib().dyninfer_cuda_session_weight_bytes(self._h))
 
@@ -275,9 +283,12 @@ class LoadedModel:
 
     def __init__(self, catalog: ck.Catalog, plan: ck.ProviderPlan, target: reg.TargetProfile,
                  device_uri: str, coverage: reg.CoverageReport, max_kv: int, kv_dtype: str,
-                 chunk_size: int):
+                 chunk_size: int, decode_kernel: str = "persistent"):
         self.catalog, self.plan, self.target, self.device_uri = catalog, plan, target, device_uri
         self.coverage, self.max_kv, self.kv_dtype, self.chunk_size = coverage, max_kv, kv_dtype, chunk_size
+        # "persistent": one cooperative kernel per decoded token; "graph": a captured graph of
+        # per-operator kernels (the path multi-row chunks always take)
+        self.decode_kernel = decode_kernel
         c = catalog.config
         self.metadata = {"architecture": c.get("model_type", "qwen3"), "vocabulary_size": c["vocab"],
                          "context_length": c.get("context_length", 0), "pad_token_id": 0}
@@ -314,12 +325,12 @@ class ModelLoader:
         return reg.dry_run_coverage(catalog.config, params, target, self.registry)
 
     def load(self, path: str, target: str = "cuda", max_kv: int = 2048, kv_dtype: str = "f32",
-             chunk_size: int = CHUNK_SIZE) -> LoadedModel:
+             chunk_size: int = CHUNK_SIZE, decode_kernel: str = "persistent") -> LoadedModel:
         profile, uri = self.resolve_target(target)
         catalog = self.bind(path)
         coverage = self.kernel_coverage(catalog, profile).require_complete()
         plan = ck.build_runtime_provider_plan(catalog)
-        return LoadedModel(catalog, plan, profile, uri, coverage, max_kv, kv_dtype, chunk_size)
+        return LoadedModel(catalog, plan, profile, uri, coverage, max_kv, kv_dtype, chunk_size, decode_kernel)
 
 
 # ----------------------------------------------------------------------- generation

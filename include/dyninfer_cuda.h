@@ -210,6 +210,13 @@ int dyninfer_cuda_session_decode_loop(dyninfer_cuda_session_t* session, int64_t 
                                       int64_t start_pos, size_t steps, int64_t* out_tokens,
                                       float* out_device_ms);
 
+/* Time CTA 0 of the persistent decode kernel spent per phase kind during its most recent
+ * launch, microseconds (device global timer): [0] embedding, [1] norm+QKV, [2] attention,
+ * [3] o_proj, [4] gate/up, [5] down, [6] lm_head, [7] argmax, [8] whole kernel. Each phase
+ * includes the grid barrier that ends it. Fails when the session uses the graph path. */
+int dyninfer_cuda_session_decode_phase_profile(dyninfer_cuda_session_t* session, double* out_us,
+                                               size_t count);
+
 /* Number of kernels this library has launched on behalf of `session` since creation. */
 uint64_t dyninfer_cuda_session_launch_count(const dyninfer_cuda_session_t* session);
 

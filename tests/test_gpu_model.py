@@ -82,7 +82,8 @@ def test_gqa_rope_qknorm_prefill_vs_decode(native_lib, oracle, tmp_path):
 
 @pytest.mark.parametrize("flavor", ["gguf_q4_0", "gguf_mixed", "mlx_u4"])
 @pytest.mark.parametrize("kv", ["f32", "bf16"])
-def test_tiny_qwen3_logits_and_greedy(native_lib, oracle, tmp_path, flavor, kv):
+@pytest.mark.parametrize("kernel", ["persistent", "graph"])
+def test_tiny_qwen3_logits_and_greedy(native_lib, oracle, tmp_path, flavor, kv, kernel):
     """Seeded Qwen3-shaped model (2 layers): prompt of 16 ids, 32 greedy steps.
     logits max-abs <= 1e-2, cosine >= 0.9999, identical greedy tokens except near-ties."""
     if flavor == "mlx_u4":
@@ -91,7 +92,7 @@ def test_tiny_qwen3_logits_and_greedy(native_lib, oracle, tmp_path, flavor, kv):
         encs = {"attn_v": "gguf.q4_1", "ffn_down": "gguf.q8_0"} if flavor == "gguf_mixed" else None
         path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), synth.TINY, seed=11, encodings=encs,
                                       output="gguf.q6_k" if flavor == "gguf_mixed" else None)
-    model = ModelLoader().load(path, max_kv=512, kv_dtype=kv, chunk_size=16)
+    model = ModelLoader().load(path, max_kv=512, kv_dtype=kv, chunk_size=16, decode_kernel=kernel)
     cat = ck.open_catalog(path)
     prompt = np.random.default_rng(5).integers(0, synth.TINY["vocab"], size=16).tolist()
     steps = 32
@@ -192,3 +193,27 @@ def test_generate_and_perf_report(native_lib, tmp_path):
     assert stop not in ids3[5:] and st3.generated_tokens <= 2 + ids[5:].index(stop)
     rep = run_perf(model, PerfConfig(prefill_tokens=20, tg=4, warmup=1, iters=2, weight_bytes=1000), SessionConfig(256))
     assert rep["decode"]["tokens"] == 4 and rep["decode"]["eff_weight_bw_gbs"] > 0 and rep["prefill"]["tps"] > 0
+
+
+@pytest.mark.parametrize("kv", ["f32", "bf16", "f16"])
+def test_persistent_kernel_long_context_split_kv(native_lib, oracle, tmp_path, kv):
+    """Context past 256 keys makes the persistent kernel split each head's keys over several
+    CTAs; its logits must track both the oracle and the per-operator graph path."""
+    path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), synth.TINY, seed=21)
+    cat = ck.open_catalog(path)
+    prompt = np.random.default_rng(2).integers(0, 512, size=600).tolist()
+    rnd = {"f32": 0, "f16": 1, "bf16": 2}[kv]
+    want, toks, margins = oracle_run(oracle, cat, prompt, 3, kv_round=rnd, kv_cap=1024)
+    outs = {}
+    for kernel in ("persistent", "graph"):
+        model = ModelLoader().load(path, max_kv=1024, kv_dtype=kv, chunk_size=128, decode_kernel=kernel)
+        with model.create_session(SessionConfig(max_sequence_length=1024)) as s:
+            lg = [s.prefill(prompt).values]
+            for i in range(3):
+                lg.append(s.decode(toks[i]).values)
+            outs[kernel] = lg
+    for i in range(4):
+        for kernel in outs:
+            assert np.abs(outs[kernel][i] - want[i]).max() <= 1e-2
+            assert helpers.cosine(outs[kernel][i], want[i]) >= 0.9999
+        assert np.abs(outs["persistent"][i] - outs["graph"][i]).max() <= 1e-3

@@ -1,222 +1,39 @@
 // Persistent single-token decode kernel: one launch per generated token.
 //
-// One CTA per SM, launched cooperatively so that all CTAs are co-resident. Each
-// CTA owns a fixed, balanced slice of the rows of every weight matrix. A producer
-// warp streams that slice — the verbatim checkpoint bytes — from HBM into a
-// shared-memory ring with 1-D bulk async copies (cp.async.bulk + mbarrier
-// transaction counts), running as far ahead of the math as the ring allows:
-// weight traffic never waits for the activation dependency chain. Eight consumer
-// warps decode rows straight out of shared memory (exact f32 weights, f32
-// accumulation) against the activation vector staged in shared memory, and the
+// One CTA per SM, launched cooperatively so that all CTAs are co-resident. Each CTA owns a
+// fixed, balanced slice of the rows of every weight matrix, cut into tiles of 16 rows (x
+// K-slices). A producer warp streams the tiles — the verbatim checkpoint bytes, one 1-D bulk
+// async copy per row segment (cp.async.bulk + mbarrier transaction counts) — from HBM into a
+// shared-memory ring, running as far ahead of the math as the ring allows: weight traffic never
+// waits for the activation dependency chain. Rows land PITCH bytes apart with PITCH/4 = 4
+// (mod 8), so the tensor-core fragment loads are bank-conflict free. Sixteen consumer warps
+// split each tile's K range, run the tile steps of gemv_core.cuh against the activation vector
+// staged in shared memory in fragment order, and reduce their partial sums in a fixed order.
 // CTAs meet at a grid barrier between dependent phases:
 //
 //   embed | per layer: norm+QKV | qk-norm+RoPE+KV-write+attention | o_proj+res |
 //   norm+gate/up+SwiGLU | down+res | final: norm+lm_head+argmax partials | argmax
 //
-// Every wait (mbarrier, grid barrier) is bounded: when it gives up it raises the
-// error word, the remaining phases are skipped in lockstep and the kernel ends.
-#include <cooperative_groups.h>
+// Every wait (mbarrier, grid barrier) is bounded: when it gives up it raises the error word,
+// the remaining phases are skipped in lockstep and the kernel ends.
+#include <algorithm>
 
 #include "codec.cuh"
 #include "decode_mega.cuh"
+#include "gemv_core.cuh"
+#include "ring.cuh"
 
 namespace dyn {
 
 namespace {
 
-constexpr int MK_CW = 16;               // consumer warps
-constexpr int MK_CT = MK_CW * 32;       // consumer threads
-constexpr int MK_THREADS = MK_CT + 32;  // + one producer warp
-constexpr int MK_SLOT = 16384;          // bytes per ring slot
-constexpr int MK_MISC_FLOATS = 6144;    // per-CTA scratch (attention state, reductions)
-constexpr int MK_MAX_COPIES = 6;
-constexpr long long MK_MBAR_SPINS = 1LL << 22;
-constexpr long long MK_GRID_SPINS = 1LL << 22;
-
-enum { PH_QKV = 0, PH_O, PH_GATEUP, PH_DOWN, PH_HEAD };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// 1-D bulk copy global -> this CTA's shared memory, completion counted on `bar`.
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-          smem_u32(dst)),
-      "l"(src), "r"(bytes), "r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(MK_CT) : "memory"); }
-
-struct Smem {
-  float* xs;
-  float* misc;
-  uint8_t* ring;
-  uint64_t* full;
-  uint64_t* empty;
-  volatile int* abort;
-  int nslot;
-};
-
-struct Chunk {
-  int ncopy;
-  const uint8_t* g[MK_MAX_COPIES];
-  uint32_t bytes[MK_MAX_COPIES];
-  uint32_t soff[MK_MAX_COPIES];  // slot offset of each copy
-  uint32_t doff[MK_MAX_COPIES];  // slot offset of the first row's bytes of each component
-  int64_t r0;
-  int n;
-  int tag;
-};
-
-__device__ __forceinline__ int aux_row_bytes(const WRef& w) {
-  return (int)(w.cols / w.group) * (w.aux == E_F32 ? 4 : 2);
-}
-__device__ __forceinline__ int rows_per_region(const WRef& w, int region) {
-  const int rb = (int)w.row_bytes();
-  if (w.enc == E_MLX_U4) return (region - 96) / (rb + 2 * aux_row_bytes(w));
-  return (region - 32) / rb;
-}
-__device__ __forceinline__ void add_copy(Chunk& c, const uint8_t* base, int64_t r0, int n, int rb,
-                                         uint32_t& cursor) {
-  const uint8_t* start = base + r0 * rb;
-  const uintptr_t s = reinterpret_cast<uintptr_t>(start);
-  const uint32_t off = (uint32_t)(s & 15);
-  const int i = c.ncopy++;
-  c.g[i] = start - off;
-  c.bytes[i] = (off + (uint32_t)(n * rb) + 15u) & ~15u;
-  c.soff[i] = cursor;
-  c.doff[i] = cursor + off;
-  cursor += c.bytes[i];
-}
-__device__ __forceinline__ void add_tensor(Chunk& c, const WRef& w, int64_t r0, int n,
-                                           uint32_t region_off) {
-  uint32_t cursor = region_off;
-  add_copy(c, w.data, r0, n, (int)w.row_bytes(), cursor);
-  if (w.enc == E_MLX_U4) {
-    add_copy(c, w.scales, r0, n, aux_row_bytes(w), cursor);
-    add_copy(c, w.biases, r0, n, aux_row_bytes(w), cursor);
-  }
-}
-
-// Chunks of rows [s0, s1) of one tensor (or of a gate/up pair sharing row indices).
-template <typename F>
-__device__ __forceinline__ void chunks_of(const WRef& w, const WRef* pair, int64_t s0, int64_t s1,
-                                          int tag, F&& f) {
-  if (s1 <= s0) return;
-  const int region = pair ? MK_SLOT / 2 : MK_SLOT;
-  int rpc = rows_per_region(w, region);
-  if (pair) {
-    const int r2 = rows_per_region(*pair, region);
-    rpc = r2 < rpc ? r2 : rpc;
-  }
-  if (rpc < 1) rpc = 1;  // excluded by mega_plan on the host
-  if (rpc > MK_CW) rpc -= rpc % MK_CW;  // whole rounds of the consumer warps
-  for (int64_t r = s0; r < s1; r += rpc) {
-    Chunk c;
-    c.ncopy = 0;
-    c.r0 = r;
-    c.n = (int)((s1 - r) < rpc ? (s1 - r) : rpc);
-    c.tag = tag;
-    add_tensor(c, w, r, c.n, 0);
-    if (pair) add_tensor(c, *pair, r, c.n, MK_SLOT / 2);
-    f(c);
-  }
-}
-
-// The fixed per-CTA program of one phase: both roles enumerate exactly this sequence.
-template <typename F>
-__device__ __forceinline__ void enum_phase(const MegaArgs& a, const MegaLayer* L, int phase, int cta,
-                                           int G, F&& f) {
-  const int64_t qd = (int64_t)a.nh * a.d, kvd = (int64_t)a.nkv * a.d;
-  if (phase == PH_QKV) {
-    const int64_t R = qd + 2 * kvd;
-    const int64_t a0 = R * cta / G, a1 = R * (cta + 1) / G;
-    const int64_t offs[3] = {0, qd, qd + kvd};
-    const int64_t lens[3] = {qd, kvd, kvd};
-    const WRef* ws[3] = {&L->q, &L->k, &L->v};
-#pragma unroll
-    for (int t = 0; t < 3; t++) {
-      const int64_t lo = (a0 > offs[t] ? a0 : offs[t]) - offs[t];
-      const int64_t hi = (a1 < offs[t] + lens[t] ? a1 : offs[t] + lens[t]) - offs[t];
-      chunks_of(*ws[t], nullptr, lo, hi, t, f);
-    }
-  } else if (phase == PH_O) {
-    chunks_of(L->o, nullptr, (int64_t)a.H * cta / G, (int64_t)a.H * (cta + 1) / G, 0, f);
-  } else if (phase == PH_GATEUP) {
-    chunks_of(L->gate, &L->up, (int64_t)a.I * cta / G, (int64_t)a.I * (cta + 1) / G, 0, f);
-  } else if (phase == PH_DOWN) {
-    chunks_of(L->down, nullptr, (int64_t)a.H * cta / G, (int64_t)a.H * (cta + 1) / G, 0, f);
-  } else {
-    chunks_of(a.lm_head, nullptr, (int64_t)a.V * cta / G, (int64_t)a.V * (cta + 1) / G, 0, f);
-  }
-}
-
-// ---- math on one row held in shared memory ------------------------------------------
+// Embedding row through the exact scalar decoders (one row per token: not performance relevant).
 template <int ENC>
-__device__ __forceinline__ float dot_row_t(const RowPtr& rp, int64_t K, const float* xs, int lane) {
-  using C = Codec<ENC>;
-  const int nparts = (int)(K / C::BLOCK) * C::PARTS;
-  float acc = 0.f;
-#pragma unroll 4
-  for (int it = lane; it < nparts; it += 32) {
-    const int blk = it / C::PARTS, part = it - blk * C::PARTS;
-    float wv[4 * C::G];
-    C::decode(rp, blk, part, wv);
-#pragma unroll
-    for (int g = 0; g < C::G; g++) {
-      const float4 xv = *reinterpret_cast<const float4*>(xs + blk * C::BLOCK + C::xoff(part, g));
-      acc = fmaf(wv[4 * g + 0], xv.x, acc);
-      acc = fmaf(wv[4 * g + 1], xv.y, acc);
-      acc = fmaf(wv[4 * g + 2], xv.z, acc);
-      acc = fmaf(wv[4 * g + 3], xv.w, acc);
-    }
-  }
-  return warp_sum(acc);
-}
-
-__device__ __forceinline__ float dot_row(int enc, const RowPtr& rp, int64_t K, const float* xs,
-                                         int lane) {
-  switch (enc) {
-    case E_Q4_0: return dot_row_t<E_Q4_0>(rp, K, xs, lane);
-    case E_Q4_1: return dot_row_t<E_Q4_1>(rp, K, xs, lane);
-    case E_Q8_0: return dot_row_t<E_Q8_0>(rp, K, xs, lane);
-    case E_Q6_K: return dot_row_t<E_Q6_K>(rp, K, xs, lane);
-    case E_MLX_U4: return dot_row_t<E_MLX_U4>(rp, K, xs, lane);
-    case E_BF16: return dot_row_t<E_BF16>(rp, K, xs, lane);
-    case E_F16: return dot_row_t<E_F16>(rp, K, xs, lane);
-    default: return dot_row_t<E_F32>(rp, K, xs, lane);
-  }
-}
-
-template <int ENC>
-__device__ __forceinline__ void gather_row_t(const WRef& w, int64_t row, float* out, int tid) {
+__device__ __forceinline__ void gather_row_t(const WRef& w, int64_t row, float* out, int tid, int nthreads) {
   using C = Codec<ENC>;
   const RowPtr rp = row_ptr(w, row);
   const int nparts = (int)(w.cols / C::BLOCK) * C::PARTS;
-  for (int it = tid; it < nparts; it += MK_CT) {
+  for (int it = tid; it < nparts; it += nthreads) {
     const int blk = it / C::PARTS, part = it - blk * C::PARTS;
     float v[4 * C::G];
     C::decode(rp, blk, part, v);
@@ -226,36 +43,99 @@ __device__ __forceinline__ void gather_row_t(const WRef& w, int64_t row, float* 
           make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
   }
 }
-__device__ __noinline__ void gather_row(const WRef& w, int64_t row, float* out, int tid) {
+__device__ __noinline__ void mega_gather_row(const WRef& w, int64_t row, float* out, int tid, int nthreads) {
   switch (w.enc) {
-    case E_Q4_0: gather_row_t<E_Q4_0>(w, row, out, tid); break;
-    case E_Q4_1: gather_row_t<E_Q4_1>(w, row, out, tid); break;
-    case E_Q8_0: gather_row_t<E_Q8_0>(w, row, out, tid); break;
-    case E_Q6_K: gather_row_t<E_Q6_K>(w, row, out, tid); break;
-    case E_MLX_U4: gather_row_t<E_MLX_U4>(w, row, out, tid); break;
-    case E_BF16: gather_row_t<E_BF16>(w, row, out, tid); break;
-    case E_F16: gather_row_t<E_F16>(w, row, out, tid); break;
-    default: gather_row_t<E_F32>(w, row, out, tid); break;
+    case E_Q4_0: gather_row_t<E_Q4_0>(w, row, out, tid, nthreads); break;
+    case E_Q4_1: gather_row_t<E_Q4_1>(w, row, out, tid, nthreads); break;
+    case E_Q8_0: gather_row_t<E_Q8_0>(w, row, out, tid, nthreads); break;
+    case E_Q6_K: gather_row_t<E_Q6_K>(w, row, out, tid, nthreads); break;
+    case E_MLX_U4: gather_row_t<E_MLX_U4>(w, row, out, tid, nthreads); break;
+    case E_BF16: gather_row_t<E_BF16>(w, row, out, tid, nthreads); break;
+    case E_F16: gather_row_t<E_F16>(w, row, out, tid, nthreads); break;
+    default: gather_row_t<E_F32>(w, row, out, tid, nthreads); break;
   }
 }
 
-__device__ __forceinline__ RowPtr chunk_row(const WRef& w, const uint8_t* slot, const Chunk& c,
-                                            int comp, int j) {
-  RowPtr rp;
-  rp.data = slot + c.doff[comp] + (int64_t)j * w.row_bytes();
-  rp.aux = w.aux;
-  rp.group = w.group;
-  if (w.enc == E_MLX_U4) {
-    const int ab = aux_row_bytes(w);
-    rp.sc = slot + c.doff[comp + 1] + j * ab;
-    rp.bi = slot + c.doff[comp + 2] + j * ab;
-  } else {
-    rp.sc = rp.bi = nullptr;
+constexpr int MK_CW = 16;               // consumer warps
+constexpr int MK_CT = MK_CW * 32;       // consumer threads
+constexpr int MK_THREADS = MK_CT + 32;  // + one producer warp
+constexpr int MK_SLOT = 18432;          // bytes per ring slot (one 16-row tile x K-slice)
+constexpr int MK_MISC_FLOATS = 6144;    // per-CTA scratch (attention state, reductions, partials)
+constexpr int MK_PART_OFF = 5120;       // misc floats [5120, 6144): 2 x [16 warps][32] partial sums
+constexpr long long MK_MBAR_SPINS = 1LL << 22;
+constexpr long long MK_GRID_SPINS = 1LL << 22;
+
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(MK_CT) : "memory"); }
+
+struct Smem {
+  float* xs;      // activation vector, f32
+  __half* xf;     // same, hi/lo f16 fragments
+  float* sx32;    // per-32 sums of the scaled activation
+  float* sx16;    // per-16 sums
+  float* misc;
+  uint8_t* ring;
+  uint64_t* full;
+  uint64_t* empty;
+  uint64_t* part_full;   // [2] partial-sum buffers: 16 warps arrived
+  uint64_t* part_empty;  // [2] finalising warp done reading
+  uint64_t* prog_bar;    // program copy landed
+  const MegaChunk* prog; // this CTA's chunk program (shared memory copy, or global)
+  const uint16_t* counts;
+  volatile int* abort;
+  int nslot;
+};
+
+// ---- producer: one bulk copy per tile row (lanes 0..15), MLX aux rows by lanes 16..31 --------
+__device__ __forceinline__ void produce_chunk(const MegaChunk* c, const Smem& sm, uint32_t pi, int lane) {
+  const int slot = pi % sm.nslot;
+  if (pi >= (uint32_t)sm.nslot) {
+    int ok = 1;
+    if (lane == 0) {
+      ok = mbar_wait_bounded(sm.empty + slot, ((pi / sm.nslot) - 1u) & 1u, MK_MBAR_SPINS, sm.abort) ? 1 : 0;
+      if (!ok && !*sm.abort) *sm.abort = 4;
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) return;
   }
-  return rp;
+  uint8_t* base = sm.ring + (size_t)slot * MK_SLOT;
+  const int i = lane & 15;
+  const int n = c->n;
+  const uint8_t* g0 = nullptr;
+  const uint8_t* g1 = nullptr;
+  uint8_t* d0 = nullptr;
+  uint8_t* d1 = nullptr;
+  uint32_t n0 = 0, n1 = 0;
+  if (i < n) {
+    if (lane < 16) {
+      const uint8_t* s = c->src + (size_t)i * c->rb;
+      const uint32_t off = (uint32_t)(reinterpret_cast<uintptr_t>(s) & 15);
+      g0 = s - off;
+      n0 = (off + c->seg + 15u) & ~15u;
+      d0 = base + i * c->pitch;
+    } else if (c->aseg) {
+      const uint8_t* s = c->sc + (size_t)i * c->arb;
+      uint32_t off = (uint32_t)(reinterpret_cast<uintptr_t>(s) & 15);
+      g0 = s - off;
+      n0 = (off + c->aseg + 15u) & ~15u;
+      d0 = base + 16 * c->pitch + i * c->apitch;
+      s = c->bi + (size_t)i * c->arb;
+      off = (uint32_t)(reinterpret_cast<uintptr_t>(s) & 15);
+      g1 = s - off;
+      n1 = (off + c->aseg + 15u) & ~15u;
+      d1 = base + 16 * c->pitch + (16 + i) * c->apitch;
+    }
+  }
+  uint32_t total = n0 + n1;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+  if (lane == 0) mbar_expect_tx(sm.full + slot, total);
+  __syncwarp();
+  if (n0) bulk_g2s(d0, g0, n0, sm.full + slot);
+  if (n1) bulk_g2s(d1, g1, n1, sm.full + slot);
 }
 
-// Sum over the consumer threads; every thread gets the total. `red` holds >= 8 floats.
+// ---- consumer helpers ---------------------------------------------------------------------------
 __device__ __forceinline__ float consumer_sum(float v, float* red, int lane, int warp) {
   v = warp_sum(v);
   consumer_sync();
@@ -266,48 +146,157 @@ __device__ __forceinline__ float consumer_sum(float v, float* red, int lane, int
   for (int i = 0; i < MK_CW; i++) t += red[i];
   return t;
 }
-
-// xs[i] = (x[i] * inv) * w[i]  with inv = 1/sqrt(mean(x^2) + eps); x is read from L2.
-__device__ __forceinline__ void stage_norm(const float* x, const void* w, int w_type, int n,
-                                           float eps, const Smem& sm, int tid, int lane, int warp) {
-  float ss = 0.f;
-  for (int i = tid; i < n; i += MK_CT) {
-    const float v = __ldcg(x + i);
-    sm.xs[i] = v;
-    ss = fmaf(v, v, ss);
-  }
-  ss = consumer_sum(ss, sm.misc + MK_MISC_FLOATS - 32, lane, warp);
-  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
-  for (int i = tid; i < n; i += MK_CT)
-    sm.xs[i] = __fmul_rn(__fmul_rn(sm.xs[i], inv),
-                         aux_load(reinterpret_cast<const uint8_t*>(w), w_type, i));
+__device__ __forceinline__ float consumer_max(float v, float* red, int lane, int warp) {
+  v = warp_max(v);
   consumer_sync();
+  if (lane == 0) red[warp] = v;
+  consumer_sync();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < MK_CW; i++) t = fmaxf(t, red[i]);
+  return t;
 }
 
-__device__ __forceinline__ bool wait_full(const Smem& sm, uint32_t ci) {
-  uint64_t* bar = sm.full + (ci % sm.nslot);
-  const unsigned parity = (ci / sm.nslot) & 1u;
-  for (long long it = 0; it < MK_MBAR_SPINS; it++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*sm.abort) return false;
+// Stage the activation vector of a phase in one pass. Thread i owns fragment item i = (block kb,
+// lane quarter t) and loads exactly the 8 elements that item holds (the items partition the
+// vector; n <= 8 * MK_CT), so the sum of squares and the scale come from one combined block
+// reduction and the normalised values go straight from registers to hi/lo f16 fragments and
+// 16-/32-run sums. Optional RMSNorm: v = (x*inv)*w, inv = 1/sqrt(mean(x^2)+eps).
+// Returns 2^24 / scale. `src_smem`: the vector already sits in sm.xs; else it is read from L2.
+__device__ __forceinline__ float stage_phase(const float* x, bool src_smem, const void* nw, int nw_type,
+                                             int n, float eps, int layout, const Smem& sm, int tid,
+                                             int lane, int warp) {
+  if (eps < -1.f) return 1.f;
+  float* red = sm.misc + MK_PART_OFF - 64;
+  const int items = (n >> 5) * 4;
+  const int kb = tid >> 2, t = tid & 3;
+  const bool live = tid < items;
+  // load order: A = 4 elements, B = 4 elements
+  const int baseA = kb * 32 + (layout == XL_MLXW ? 8 * t : 4 * t);
+  const int baseB = layout == XL_MLXW ? baseA + 4 : kb * 32 + 16 + 4 * t;
+  float v[8], w[8];
+  float ss = 0.f, mx = 0.f;
+  if (live) {
+    const float4 a4 = src_smem ? *reinterpret_cast<const float4*>(sm.xs + baseA)
+                               : __ldcg(reinterpret_cast<const float4*>(x + baseA));
+    const float4 b4 = src_smem ? *reinterpret_cast<const float4*>(sm.xs + baseB)
+                               : __ldcg(reinterpret_cast<const float4*>(x + baseB));
+    v[0] = a4.x, v[1] = a4.y, v[2] = a4.z, v[3] = a4.w;
+    v[4] = b4.x, v[5] = b4.y, v[6] = b4.z, v[7] = b4.w;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      w[i] = nw ? aux_load(reinterpret_cast<const uint8_t*>(nw), nw_type, (i < 4 ? baseA : baseB - 4) + i) : 1.0f;
+      ss = fmaf(v[i], v[i], ss);
+      mx = fmaxf(mx, fabsf(v[i] * w[i]));
+    }
   }
-  *sm.abort = 3;
-  return false;
+  ss = warp_sum(ss);
+  mx = warp_max(mx);
+  consumer_sync();
+  if (lane == 0) {
+    red[warp] = ss;
+    red[32 + warp] = mx;
+  }
+  consumer_sync();
+  float tss = 0.f, tmx = 0.f;
+#pragma unroll
+  for (int i = 0; i < MK_CW; i++) {
+    tss += red[i];
+    tmx = fmaxf(tmx, red[32 + i]);
+  }
+  const float inv = nw ? 1.0f / sqrtf(tss / (float)n + eps) : 1.0f;
+  float s, is;
+  scale_for(tmx * inv * 1.0001f, &s, &is);
+  float run0 = 0.f, run1 = 0.f;  // this item's share of the block's two 16-element runs
+  if (live) {
+    float sv[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) sv[i] = (nw ? __fmul_rn(__fmul_rn(v[i], inv), w[i]) : v[i]) * s;
+    const float sa = (sv[0] + sv[1]) + (sv[2] + sv[3]), sb = (sv[4] + sv[5]) + (sv[6] + sv[7]);
+    float f[8];  // fragment order
+    if (layout == XL_NIBBLE) {
+      f[0] = sv[0], f[1] = sv[2], f[2] = sv[4] * 0.0625f, f[3] = sv[6] * 0.0625f;
+      f[4] = sv[1], f[5] = sv[3], f[6] = sv[5] * 0.0625f, f[7] = sv[7] * 0.0625f;
+      run0 = sa, run1 = sb;
+    } else if (layout == XL_MLXW) {
+      f[0] = sv[0], f[1] = sv[4], f[2] = sv[1] * 0.0625f, f[3] = sv[5] * 0.0625f;
+      f[4] = sv[2], f[5] = sv[6], f[6] = sv[3] * 0.0625f, f[7] = sv[7] * 0.0625f;
+      if (t < 2) run0 = sa + sb; else run1 = sa + sb;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; i++) f[i] = sv[i];
+      run0 = sa, run1 = sb;
+    }
+    __half hi[8], lo[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const __half h = __float2half_rn(f[i]);
+      hi[i] = h;
+      lo[i] = __float2half_rn(f[i] - __half2float(h));
+    }
+    uint4* dst = reinterpret_cast<uint4*>(sm.xf + ((size_t)(kb * 2) * 4 + t) * 8);
+    dst[0] = *reinterpret_cast<uint4*>(hi);
+    dst[4] = *reinterpret_cast<uint4*>(lo);
+  }
+  // the four quarters of a block are four consecutive lanes
+  run0 += __shfl_xor_sync(0xffffffffu, run0, 1);
+  run1 += __shfl_xor_sync(0xffffffffu, run1, 1);
+  run0 += __shfl_xor_sync(0xffffffffu, run0, 2);
+  run1 += __shfl_xor_sync(0xffffffffu, run1, 2);
+  if (live && t == 0) {
+    sm.sx16[2 * kb] = run0;
+    sm.sx16[2 * kb + 1] = run1;
+    sm.sx32[kb] = run0 + run1;
+  }
+  consumer_sync();
+  return GV_2P24 * is;
 }
-__device__ __forceinline__ void release_slot(const Smem& sm, uint32_t ci, int lane) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(sm.empty + (ci % sm.nslot));
+
+// One unit of a chunk for this warp. p0 / p1: the chunk's bytes in rows g, g+8; a0 / a1: MLX
+// scales of those rows (biases 16 * apitch further).
+__device__ __forceinline__ void run_unit(int enc, int aux, int group_shift, const uint8_t* p0,
+                                         const uint8_t* p1, const uint8_t* a0, const uint8_t* a1,
+                                         int apitch16, int u, int kb0, const Smem& sm, int lane,
+                                         TileAcc<true>& acc) {
+  const int t = lane & 3;
+  const int c = (lane >> 2) & 1;
+  const __half* xf0 = sm.xf + (size_t)c * 32 + t * 8;  // block kb adds kb * 64 halfs
+  if (enc == E_Q4_0) {
+    const int kb = kb0 + 2 * u;
+    blk_q4<E_Q4_0, 0, true>(p0 + u * 36, p1 + u * 36, xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc);
+    blk_q4<E_Q4_0, 2, true>(p0 + u * 36 + 18, p1 + u * 36 + 18, xf0 + (size_t)(kb + 1) * 64,
+                            sm.sx32[kb + 1], 0.f, t, acc);
+  } else if (enc == E_Q4_1) {
+    const int kb = kb0 + u;
+    blk_q4<E_Q4_1, 0, true>(p0 + u * 20, p1 + u * 20, xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc);
+  } else if (enc == E_Q8_0) {
+    const int kb = kb0 + 2 * u;
+    blk_q8_0<0, true>(p0 + u * 68, p1 + u * 68, xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc);
+    blk_q8_0<2, true>(p0 + u * 68 + 34, p1 + u * 68 + 34, xf0 + (size_t)(kb + 1) * 64, sm.sx32[kb + 1],
+                      0.f, t, acc);
+  } else if (enc == E_MLX_U4) {
+    const int kb = kb0 + u;
+    const int gi = u >> group_shift;
+    blk_mlx<true>(p0 + u * 16, p1 + u * 16, aux_load(a0, aux, gi), aux_load(a1, aux, gi),
+                  aux_load(a0 + apitch16, aux, gi), aux_load(a1 + apitch16, aux, gi),
+                  xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc);
+  } else {
+    // Q6_K quarter: superblock u / 4 of the chunk, half n, sub-block s
+    const int sb = u >> 2, n = (u >> 1) & 1, s = u & 1;
+    const int kb = kb0 + sb * 8;
+    const uint8_t* s0 = p0 + sb * 210;
+    const uint8_t* s1 = p1 + sb * 210;
+    if (sb & 1)
+      q6k_quarter<2, true>(s0, s1, n, s, xf0 + (size_t)kb * 64, 64, sm.sx16 + 2 * kb, sm.sx16 + 2 * kb, t, acc);
+    else
+      q6k_quarter<0, true>(s0, s1, n, s, xf0 + (size_t)kb * 64, 64, sm.sx16 + 2 * kb, sm.sx16 + 2 * kb, t, acc);
+  }
 }
 
 __device__ __forceinline__ float round_kv(float v, int kv_type) {
   if (kv_type == E_BF16) return __bfloat162float(__float2bfloat16_rn(v));
   if (kv_type == E_F16) return __half2float(__float2half_rn(v));
   return v;
-}
-__device__ __forceinline__ float load_kv(const uint8_t* base, int kv_type, int64_t idx) {
-  if (kv_type == E_F32) return reinterpret_cast<const float*>(base)[idx];
-  const uint32_t b = reinterpret_cast<const uint16_t*>(base)[idx];
-  return kv_type == E_F16 ? f16_bits_to_f32(b) : bf16_bits_to_f32(b);
 }
 __device__ __forceinline__ void store_kv(uint8_t* base, int kv_type, int64_t idx, float v) {
   if (kv_type == E_F32)
@@ -317,7 +306,14 @@ __device__ __forceinline__ void store_kv(uint8_t* base, int kv_type, int64_t idx
   else
     reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
 }
-
+__device__ __forceinline__ uint32_t load_kv_bits(const uint8_t* base, int kv_type, int64_t idx) {
+  if (kv_type == E_F32) return reinterpret_cast<const uint32_t*>(base)[idx];
+  return reinterpret_cast<const uint16_t*>(base)[idx];
+}
+__device__ __forceinline__ float kv_bits_to_f32(uint32_t b, int kv_type) {
+  if (kv_type == E_F32) return __uint_as_float(b);
+  return kv_type == E_F16 ? f16_bits_to_f32(b) : bf16_bits_to_f32(b);
+}
 __device__ __forceinline__ bool arg_better(float v, long long i, float bv, long long bi) {
   return v > bv || (v == bv && i < bi);
 }
@@ -328,7 +324,8 @@ __device__ __forceinline__ unsigned long long gtime() {
   return t;
 }
 // Phase timing seen by CTA 0 (optional): kind 0 embed, 1 qkv, 2 attention, 3 o_proj, 4 gate/up,
-// 5 down, 6 lm_head, 7 argmax, 8 whole kernel.
+// 5 down, 6 lm_head, 7 argmax, 8 whole kernel; 9 staging, 10 waiting for weights, 11 tile math,
+// 12 grid barrier.
 struct Prof {
   unsigned long long* out;
   unsigned long long last, start;
@@ -351,7 +348,6 @@ struct Prof {
   __device__ void end() {
     if (on) out[8] = gtime() - start;
   }
-  // fine-grained accumulators: 9 staging, 10 waiting for weights, 11 row math, 12 grid barrier
   __device__ unsigned long long tic() const { return on ? gtime() : 0ULL; }
   __device__ void toc(int kind, unsigned long long t0) {
     if (on) out[kind] += gtime() - t0;
@@ -362,42 +358,40 @@ struct GridBar {
   unsigned long long gen;
 };
 
+// Arrival: release-add on a monotonic counter; waiting: acquire-poll the same counter.
 __device__ __forceinline__ void grid_sync(const MegaArgs& a, GridBar& gb, int G, int tid,
                                           const Smem& sm) {
+  if (a.debug_skip & 16) {
+    consumer_sync();
+    return;
+  }
   consumer_sync();
   if (tid == 0) {
     gb.gen += 1;
     const unsigned long long target = gb.gen * (unsigned long long)G;
-    __threadfence();  // release this CTA's writes before announcing arrival
-    const unsigned long long prev = atomicAdd(a.bar, 1ULL);
-    if (prev + 1 < target && !*sm.abort) {
-      const volatile unsigned long long* cnt = a.bar;
+    asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(a.bar) : "memory");
+    if (!*sm.abort) {
+      unsigned long long seen = 0;
       long long it = 0;
-      while (*cnt < target && ++it < MK_GRID_SPINS) {
-      }
-      if (*cnt < target) *sm.abort = 2;
+      do {
+        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(a.bar) : "memory");
+      } while (seen < target && ++it < MK_GRID_SPINS);
+      if (seen < target) *sm.abort = 2;
     }
-    __threadfence();  // acquire the other CTAs' writes
   }
   consumer_sync();
 }
 
-// ---- attention for one (head, split) ---------------------------------------------------
-__device__ __forceinline__ uint32_t load_kv_bits(const uint8_t* base, int kv_type, int64_t idx) {
-  if (kv_type == E_F32) return reinterpret_cast<const uint32_t*>(base)[idx];
-  return reinterpret_cast<const uint16_t*>(base)[idx];
-}
-__device__ __forceinline__ float kv_bits_to_f32(uint32_t b, int kv_type) {
-  if (kv_type == E_F32) return __uint_as_float(b);
-  return kv_type == E_F16 ? f16_bits_to_f32(b) : bf16_bits_to_f32(b);
-}
-
-// DPL = head-dim slots per lane (4 covers d <= 128, 8 covers d <= 256).
+// ---- attention for one (head, split); DPL = head-dim slots per lane ------------------------------
+// Latency plan: one L2 round trip for q/k/v and the norm weights, one combined block reduction
+// for both RMS sums, then every warp fetches all of its keys (K and V rows, up to KB at a time)
+// before touching any of them, so a short context costs one more round trip, not one per key.
 template <int DPL>
 __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const MegaLayer* L, int cta,
                                                 int64_t pos, int64_t seq, int nsplit, const Smem& sm,
                                                 int tid, int lane, int warp) {
   if (cta >= a.nh * nsplit) return;
+  constexpr int KB = 4;  // keys in flight per warp
   const int h = cta / nsplit, sp = cta - h * nsplit;
   const int grp = a.nh / a.nkv, kvh = h / grp, gi = h - kvh * grp;
   const int d = a.d, half = d / 2;
@@ -406,42 +400,51 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
   float* vn = sm.misc + 512;     // [256]
   float* wm = sm.misc + 768;     // [16]
   float* wl = sm.misc + 784;     // [16]
-  float* red = sm.misc + 800;    // [32]
+  float* red = sm.misc + 800;    // [64]
   float* wacc = sm.misc + 1024;  // [16][256]
-  for (int i = tid; i < d; i += MK_CT) {
-    qs[i] = __ldcg(a.q + (int64_t)h * d + i);
-    kn[i] = __ldcg(a.k + (int64_t)kvh * d + i);
-    vn[i] = round_kv(__ldcg(a.v + (int64_t)kvh * d + i), a.kv_type);
-  }
-  consumer_sync();
-  float qinv = 1.f, kinv = 1.f;
-  if (a.has_norm) {
-    float sq = 0.f, sk = 0.f;
-    for (int i = tid; i < d; i += MK_CT) {
-      sq = fmaf(qs[i], qs[i], sq);
-      sk = fmaf(kn[i], kn[i], sk);
-    }
-    sq = consumer_sum(sq, red, lane, warp);
-    sk = consumer_sum(sk, red + 16, lane, warp);
-    qinv = 1.0f / sqrtf(sq / (float)d + a.eps);
-    kinv = 1.0f / sqrtf(sk / (float)d + a.eps);
-  }
-  uint8_t* kc = a.kcache + (uint64_t)l * a.layer_stride;
-  uint8_t* vc = a.vcache + (uint64_t)l * a.layer_stride;
-  const int64_t plane = ((seq * a.nkv + kvh) * a.cap) * d;  // element offset of this head's plane
-  const bool writer = (sp == 0 && gi == 0);
-  for (int i = tid; i < half; i += MK_CT) {
-    float q1 = qs[i], q2 = qs[i + half], k1 = kn[i], k2 = kn[i + half];
+  // thread i < d/2 owns the rotation pair (i, i + d/2) of q and of k
+  float q1 = 0.f, q2 = 0.f, k1 = 0.f, k2 = 0.f, wq1 = 1.f, wq2 = 1.f, wk1 = 1.f, wk2 = 1.f;
+  const bool pair = tid < half;
+  if (pair) {
+    q1 = __ldcg(a.q + (int64_t)h * d + tid);
+    q2 = __ldcg(a.q + (int64_t)h * d + tid + half);
+    k1 = __ldcg(a.k + (int64_t)kvh * d + tid);
+    k2 = __ldcg(a.k + (int64_t)kvh * d + tid + half);
     if (a.has_norm) {
       const uint8_t* qw = reinterpret_cast<const uint8_t*>(L->q_norm);
       const uint8_t* kw = reinterpret_cast<const uint8_t*>(L->k_norm);
-      q1 = __fmul_rn(__fmul_rn(q1, qinv), aux_load(qw, L->qk_norm_type, i));
-      q2 = __fmul_rn(__fmul_rn(q2, qinv), aux_load(qw, L->qk_norm_type, i + half));
-      k1 = __fmul_rn(__fmul_rn(k1, kinv), aux_load(kw, L->qk_norm_type, i));
-      k2 = __fmul_rn(__fmul_rn(k2, kinv), aux_load(kw, L->qk_norm_type, i + half));
+      wq1 = aux_load(qw, L->qk_norm_type, tid), wq2 = aux_load(qw, L->qk_norm_type, tid + half);
+      wk1 = aux_load(kw, L->qk_norm_type, tid), wk2 = aux_load(kw, L->qk_norm_type, tid + half);
+    }
+  }
+  for (int i = tid; i < d; i += MK_CT) vn[i] = round_kv(__ldcg(a.v + (int64_t)kvh * d + i), a.kv_type);
+  float qinv = 1.f, kinv = 1.f;
+  if (a.has_norm) {
+    float sq = warp_sum(fmaf(q1, q1, q2 * q2)), sk = warp_sum(fmaf(k1, k1, k2 * k2));
+    consumer_sync();
+    if (lane == 0) {
+      red[warp] = sq;
+      red[32 + warp] = sk;
+    }
+    consumer_sync();
+    float tq = 0.f, tk = 0.f;
+#pragma unroll
+    for (int i = 0; i < MK_CW; i++) {
+      tq += red[i];
+      tk += red[32 + i];
+    }
+    qinv = 1.0f / sqrtf(tq / (float)d + a.eps);
+    kinv = 1.0f / sqrtf(tk / (float)d + a.eps);
+  }
+  if (pair) {
+    if (a.has_norm) {
+      q1 = __fmul_rn(__fmul_rn(q1, qinv), wq1);
+      q2 = __fmul_rn(__fmul_rn(q2, qinv), wq2);
+      k1 = __fmul_rn(__fmul_rn(k1, kinv), wk1);
+      k2 = __fmul_rn(__fmul_rn(k2, kinv), wk2);
     }
     if (a.has_rope) {
-      const float angle = __fmul_rn((float)pos, a.ft.f[i]);
+      const float angle = __fmul_rn((float)pos, a.ft.f[tid]);
       float sv, cv;
       sincosf(angle, &sv, &cv);
       const float ql = __fsub_rn(__fmul_rn(q1, cv), __fmul_rn(q2, sv));
@@ -450,22 +453,44 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
       const float kh = __fadd_rn(__fmul_rn(k1, sv), __fmul_rn(k2, cv));
       q1 = ql, q2 = qh, k1 = kl, k2 = kh;
     }
-    qs[i] = q1;
-    qs[i + half] = q2;
-    kn[i] = round_kv(k1, a.kv_type);
-    kn[i + half] = round_kv(k2, a.kv_type);
+    qs[tid] = q1;
+    qs[tid + half] = q2;
+    kn[tid] = round_kv(k1, a.kv_type);
+    kn[tid + half] = round_kv(k2, a.kv_type);
   }
+  uint8_t* kc = a.kcache + (uint64_t)l * a.layer_stride;
+  uint8_t* vc = a.vcache + (uint64_t)l * a.layer_stride;
+  const int64_t plane = ((seq * a.nkv + kvh) * a.cap) * d;  // element offset of this head's plane
+  const int64_t n = pos + 1;
+  const int64_t per = (n + nsplit - 1) / nsplit;
+  const int64_t k_lo = (int64_t)sp * per;
+  const int64_t k_hi = (k_lo + per < n) ? k_lo + per : n;
+  // first batch of this warp's keys: issue the loads before the barrier that publishes q
+  uint32_t kbits[KB][DPL], vbits[KB][DPL];
+  auto fetch = [&](int64_t key0) {
+#pragma unroll
+    for (int b = 0; b < KB; b++) {
+      const int64_t key = key0 + (int64_t)b * MK_CW;
+#pragma unroll
+      for (int j = 0; j < DPL; j++) {
+        const int idx = lane + 32 * j;
+        if (key < k_hi && key != pos && idx < d) {
+          kbits[b][j] = load_kv_bits(kc, a.kv_type, plane + key * d + idx);
+          vbits[b][j] = load_kv_bits(vc, a.kv_type, plane + key * d + idx);
+        } else {
+          kbits[b][j] = vbits[b][j] = 0;
+        }
+      }
+    }
+  };
+  fetch(k_lo + warp);
   consumer_sync();
-  if (writer) {
+  if (sp == 0 && gi == 0) {
     for (int i = tid; i < d; i += MK_CT) {
       store_kv(kc, a.kv_type, plane + pos * d + i, kn[i]);
       store_kv(vc, a.kv_type, plane + pos * d + i, vn[i]);
     }
   }
-  const int64_t n = pos + 1;
-  const int64_t per = (n + nsplit - 1) / nsplit;
-  const int64_t k_lo = (int64_t)sp * per;
-  const int64_t k_hi = (k_lo + per < n) ? k_lo + per : n;
   const float scale = 1.0f / sqrtf((float)d);
   float qreg[DPL], acc[DPL];
 #pragma unroll
@@ -475,48 +500,37 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
     acc[j] = 0.f;
   }
   float m = -3.40282347e38f, lsum = 0.f;
-  // Keys round-robin over warps; the next key's K and V rows are fetched while the
-  // current one is reduced, so two rows per warp are in flight.
-  uint32_t kb[DPL], vb[DPL], kb2[DPL], vb2[DPL];
-  auto fetch = [&](int64_t key, uint32_t* kk, uint32_t* vv) {
+  for (int64_t key0 = k_lo + warp; key0 < k_hi; key0 += (int64_t)KB * MK_CW) {
+    if (key0 != k_lo + warp) fetch(key0);
+    float sc[KB];
 #pragma unroll
-    for (int j = 0; j < DPL; j++) {
-      const int idx = lane + 32 * j;
-      if (idx < d && key != pos) {
-        kk[j] = load_kv_bits(kc, a.kv_type, plane + key * d + idx);
-        vv[j] = load_kv_bits(vc, a.kv_type, plane + key * d + idx);
-      } else {
-        kk[j] = vv[j] = 0;
+    for (int b = 0; b < KB; b++) {
+      const int64_t key = key0 + (int64_t)b * MK_CW;
+      float dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < DPL; j++) {
+        const int idx = lane + 32 * j;
+        if (idx < d) dot = fmaf(qreg[j], key == pos ? kn[idx] : kv_bits_to_f32(kbits[b][j], a.kv_type), dot);
+      }
+      sc[b] = warp_sum(dot) * scale;
+    }
+#pragma unroll
+    for (int b = 0; b < KB; b++) {
+      const int64_t key = key0 + (int64_t)b * MK_CW;
+      if (key < k_hi) {
+        const float mn = fmaxf(m, sc[b]);
+        const float factor = expf(m - mn);
+        const float p = expf(sc[b] - mn);
+        lsum = lsum * factor + p;
+#pragma unroll
+        for (int j = 0; j < DPL; j++) {
+          const int idx = lane + 32 * j;
+          if (idx < d)
+            acc[j] = acc[j] * factor + p * (key == pos ? vn[idx] : kv_bits_to_f32(vbits[b][j], a.kv_type));
+        }
+        m = mn;
       }
     }
-  };
-  int64_t key = k_lo + warp;
-  if (key < k_hi) fetch(key, kb, vb);
-  for (; key < k_hi; key += MK_CW) {
-    const int64_t nxt = key + MK_CW;
-    if (nxt < k_hi) fetch(nxt, kb2, vb2);
-    const bool fresh = key == pos;
-    float dot = 0.f;
-#pragma unroll
-    for (int j = 0; j < DPL; j++) {
-      const int idx = lane + 32 * j;
-      if (idx < d) dot = fmaf(qreg[j], fresh ? kn[idx] : kv_bits_to_f32(kb[j], a.kv_type), dot);
-    }
-    dot = warp_sum(dot);
-    const float sc = dot * scale;
-    const float mn = fmaxf(m, sc);
-    const float factor = expf(m - mn);
-    const float p = expf(sc - mn);
-    lsum = lsum * factor + p;
-#pragma unroll
-    for (int j = 0; j < DPL; j++) {
-      const int idx = lane + 32 * j;
-      if (idx < d)
-        acc[j] = acc[j] * factor + p * (fresh ? vn[idx] : kv_bits_to_f32(vb[j], a.kv_type));
-    }
-    m = mn;
-#pragma unroll
-    for (int j = 0; j < DPL; j++) kb[j] = kb2[j], vb[j] = vb2[j];
   }
   if (lane == 0) {
     wm[warp] = m;
@@ -550,7 +564,7 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
   }
 }
 
-// ---- the kernel --------------------------------------------------------------------------
+// ---- the kernel ------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaArgs a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -560,10 +574,20 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
   Smem sm;
   sm.nslot = a.nslot;
   sm.xs = reinterpret_cast<float*>(smem_raw);
-  sm.misc = sm.xs + a.xs_floats;
+  sm.xf = reinterpret_cast<__half*>(sm.xs + a.xs_floats);
+  sm.sx32 = reinterpret_cast<float*>(sm.xf + (size_t)a.xs_floats * 2);
+  sm.sx16 = sm.sx32 + a.xs_floats / 32;
+  sm.misc = sm.sx16 + a.xs_floats / 16;
   sm.ring = reinterpret_cast<uint8_t*>(sm.misc + MK_MISC_FLOATS);
   sm.full = reinterpret_cast<uint64_t*>(sm.ring + (size_t)a.nslot * MK_SLOT);
   sm.empty = sm.full + a.nslot;
+  sm.part_full = sm.empty + a.nslot;
+  sm.part_empty = sm.part_full + 2;
+  sm.prog_bar = sm.part_empty + 2;
+  uint8_t* prog_area = reinterpret_cast<uint8_t*>(sm.prog_bar + 2);
+  const int nph = 4 * a.layers + 1;
+  sm.prog = a.prog + (size_t)cta * a.max_chunks;
+  sm.counts = a.counts + (size_t)cta * nph;
   sm.abort = &s_abort;
   if (tid == 0) {
     s_abort = 0;
@@ -571,219 +595,255 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
       mbar_init(sm.full + i, 1);
       mbar_init(sm.empty + i, MK_CW);
     }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int i = 0; i < 2; i++) {
+      mbar_init(sm.part_full + i, MK_CW);
+      mbar_init(sm.part_empty + i, 1);
+    }
+    mbar_init(sm.prog_bar, 1);
+    mbar_fence_init();
+    if (a.prog_in_smem) {
+      // one bulk copy brings this CTA's whole program next to the math
+      const unsigned bytes = (unsigned)a.max_chunks * (unsigned)sizeof(MegaChunk);
+      mbar_expect_tx(sm.prog_bar, bytes);
+      bulk_g2s(prog_area, sm.prog, bytes, sm.prog_bar);
+    }
   }
   __syncthreads();
+  if (a.prog_in_smem) {
+    uint16_t* cdst = reinterpret_cast<uint16_t*>(prog_area + (size_t)a.max_chunks * sizeof(MegaChunk));
+    for (int i = tid; i < nph; i += MK_THREADS) cdst[i] = sm.counts[i];
+    if (!mbar_wait_bounded(sm.prog_bar, 0, MK_MBAR_SPINS, sm.abort) && !*sm.abort) *sm.abort = 7;
+    __syncthreads();
+    sm.prog = reinterpret_cast<const MegaChunk*>(prog_area);
+    sm.counts = cdst;
+  }
 
   if (warp == MK_CW) {
-    // ------------------------------ producer: stream this CTA's weight slices ----------
-    if (lane != 0) return;
-    uint32_t pi = 0;
-    auto issue = [&](const Chunk& c) {
-      const int slot = pi % sm.nslot;
-      bool ok = true;
-      if (pi >= (uint32_t)sm.nslot) {
-        const unsigned parity = ((pi / sm.nslot) - 1u) & 1u;
-        ok = false;
-        for (long long it = 0; it < MK_MBAR_SPINS; it++) {
-          if (mbar_try_wait(sm.empty + slot, parity)) {
-            ok = true;
-            break;
-          }
-          if (*sm.abort) break;
-        }
-        if (!ok && !*sm.abort) *sm.abort = 4;
-      }
-      if (ok && !*sm.abort) {
-        uint32_t total = 0;
-        for (int i = 0; i < c.ncopy; i++) total += c.bytes[i];
-        mbar_expect_tx(sm.full + slot, total);
-        uint8_t* base = sm.ring + (size_t)slot * MK_SLOT;
-        for (int i = 0; i < c.ncopy; i++) bulk_g2s(base + c.soff[i], c.g[i], c.bytes[i], sm.full + slot);
-      }
-      pi++;
-    };
-    for (int l = 0; l < a.layers; l++) {
-      const MegaLayer* L = a.L + l;
-      enum_phase(a, L, PH_QKV, cta, G, issue);
-      enum_phase(a, L, PH_O, cta, G, issue);
-      enum_phase(a, L, PH_GATEUP, cta, G, issue);
-      enum_phase(a, L, PH_DOWN, cta, G, issue);
-    }
-    enum_phase(a, a.L, PH_HEAD, cta, G, issue);
+    // ------------------------------ producer: stream this CTA's weight tiles --------------
+    int total = 0;
+    for (int i = lane; i < nph; i += 32) total += sm.counts[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    if (!(a.debug_skip & 32))
+      for (int pi = 0; pi < total; pi++) produce_chunk(sm.prog + pi, sm, (uint32_t)pi, lane);
     return;
   }
 
-  // -------------------------------- consumers ---------------------------------------------
+  // -------------------------------- consumers -------------------------------------------------
   GridBar gb;
   gb.gen = 0;
   if (tid == 0) gb.gen = *reinterpret_cast<const volatile unsigned long long*>(a.bar) / (unsigned long long)G;
   const int64_t token = __ldcg(a.io + 0), pos = __ldcg(a.io + 1), seq = __ldcg(a.io + 2);
-  int nsplit = (int)((pos + 1) / 32);
+  int nsplit = (int)((pos + 1 + 63) / 64);
   if (nsplit > a.max_split) nsplit = a.max_split;
   if (nsplit < 1) nsplit = 1;
   const int64_t qd = (int64_t)a.nh * a.d;
+  const int g = lane >> 2;
   uint32_t ci = 0;
-
+  unsigned closes = 0;
+  float out_scale = 1.f;
+  float bv = -INFINITY;  // running argmax over the rows this thread finalises
+  long long bi = 0x7fffffffffffffffLL;
   Prof prof;
   prof.begin(a.prof, cta == 0 && tid == 0);
-  if (cta == 0) gather_row(a.embed, token, a.hidden, tid);
-  { const unsigned long long t_ = prof.tic(); grid_sync(a, gb, G, tid, sm); prof.toc(12, t_); }
+  TileAcc<true> acc, acc2;
+
+  // One phase's chunks, in program order.
+  const MegaChunk* prog = sm.prog;
+  const uint16_t* counts = sm.counts;
+  auto run_phase = [&](int phase_index) {
+    acc.clear();
+    acc2.clear();
+    const int cnt = counts[phase_index];
+    for (int k = 0; k < cnt; k++, ci++) {
+      const MegaChunk* c = prog + ci;
+      const int slot = ci % sm.nslot;
+      // the finalising lanes fetch the residual now so that it is there when the tile closes
+      float resid = 0.f;
+      if (warp == 0 && lane < 16 && lane < c->n && (c->flags & 1) && ((c->flags >> 2) & 3) == MEGA_EP_RESIDUAL)
+        resid = __ldcg(c->out + c->out_row + lane);
+      const unsigned long long tw = prof.tic();
+      bool ok = (a.debug_skip & 32) ? true : mbar_wait_bounded(sm.full + slot, (ci / sm.nslot) & 1u, MK_MBAR_SPINS, sm.abort);
+      if (!ok && !*sm.abort) *sm.abort = 3;
+      prof.toc(10, tw);
+      const unsigned long long tr = prof.tic();
+      const int n = c->n, nu = c->nu, flags = c->flags;
+      if (ok && !(a.debug_skip & 1)) {
+        const uint8_t* base = sm.ring + (size_t)slot * MK_SLOT;
+        const int i0 = g < n ? g : n - 1, i1 = g + 8 < n ? g + 8 : n - 1;  // clamp to valid rows
+        const uint32_t pitch = c->pitch, rb = c->rb;
+        const uint8_t* src = c->src;
+        const uint8_t* p0 = base + i0 * pitch + (reinterpret_cast<uintptr_t>(src + (size_t)i0 * rb) & 15);
+        const uint8_t* p1 = base + i1 * pitch + (reinterpret_cast<uintptr_t>(src + (size_t)i1 * rb) & 15);
+        const uint8_t* a0 = nullptr;
+        const uint8_t* a1 = nullptr;
+        const int apitch = c->apitch;
+        if (c->aseg) {
+          const uint8_t* ab = base + 16 * pitch;
+          a0 = ab + i0 * apitch + (reinterpret_cast<uintptr_t>(c->sc + (size_t)i0 * c->arb) & 15);
+          a1 = ab + i1 * apitch + (reinterpret_cast<uintptr_t>(c->sc + (size_t)i1 * c->arb) & 15);
+        }
+        const int enc = c->enc, aux = c->aux, gs = c->group_shift, kb0 = c->kb0;
+        TileAcc<true>& A = (flags & 2) ? acc2 : acc;
+        for (int u = warp; u < nu; u += MK_CW) run_unit(enc, aux, gs, p0, p1, a0, a1, 16 * apitch, u, kb0, sm, lane, A);
+      }
+      prof.toc(11, tr);
+      __syncwarp();
+      if (lane == 0 && !(a.debug_skip & 32)) mbar_arrive(sm.empty + slot);
+      if (!(flags & 1) || (a.debug_skip & 8)) continue;
+      // tile complete: per-warp partial sums -> warp 0 adds them in a fixed order -> epilogue.
+      // The other warps do not wait: they hand their sums over through an mbarrier and go on.
+      const int buf = closes & 1;
+      const unsigned use = closes >> 1;
+      if (use > 0) {
+        if (!mbar_wait_bounded(sm.part_empty + buf, (use - 1u) & 1u, MK_MBAR_SPINS, sm.abort) && !*sm.abort)
+          *sm.abort = 5;
+      }
+      float* pw = sm.misc + MK_PART_OFF + ((size_t)buf * MK_CW + warp) * 32;
+      if ((lane & 3) == 0) {
+        pw[g] = acc.v[0];
+        pw[g + 8] = acc.v[1];
+        pw[16 + g] = acc2.v[0];
+        pw[16 + g + 8] = acc2.v[1];
+      }
+      acc.clear();
+      acc2.clear();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.part_full + buf);
+      if (warp == 0) {
+        if (!mbar_wait_bounded(sm.part_full + buf, use & 1u, MK_MBAR_SPINS, sm.abort) && !*sm.abort)
+          *sm.abort = 6;
+        if (lane < 16 && lane < n) {
+          const float* pb = sm.misc + MK_PART_OFF + (size_t)buf * MK_CW * 32 + lane;
+          float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+          for (int wv = 0; wv < MK_CW; wv++) {
+            s0 += pb[wv * 32];
+            s1 += pb[wv * 32 + 16];
+          }
+          s0 *= out_scale;
+          s1 *= out_scale;
+          const int ep = (flags >> 2) & 3;
+          const int64_t row = (int64_t)c->out_row + lane;
+          float* out = c->out;
+          if (ep == MEGA_EP_STORE) {
+            out[row] = s0;
+          } else if (ep == MEGA_EP_RESIDUAL) {
+            out[row] = resid + s0;
+          } else if (ep == MEGA_EP_SWIGLU) {
+            out[row] = (s0 / (1.0f + expf(-s0))) * s1;
+          } else {
+            out[row] = s0;
+            if (s0 > -INFINITY && arg_better(s0, row, bv, bi)) bv = s0, bi = row;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.part_empty + buf);
+      }
+      closes++;
+    }
+  };
+
+  auto gsync = [&]() {
+    const unsigned long long t_ = prof.tic();
+    grid_sync(a, gb, G, tid, sm);
+    prof.toc(12, t_);
+  };
+
+  if (cta == 0) mega_gather_row(a.embed, token, a.hidden, tid, MK_CT);
+  gsync();
   prof.mark(0);
 
   for (int l = 0; l < a.layers; l++) {
     const MegaLayer* L = a.L + l;
-    // ---- norm + q/k/v rows
-    { const unsigned long long t_ = prof.tic(); stage_norm(a.hidden, L->attn_norm, L->norm_type, a.H, a.eps, sm, tid, lane, warp); prof.toc(9, t_); }
-    enum_phase(a, L, PH_QKV, cta, G, [&](const Chunk& c) {
-      const unsigned long long tw_ = prof.tic();
-      const bool ok = wait_full(sm, ci);
-      prof.toc(10, tw_);
-      const unsigned long long tr_ = prof.tic();
-      const uint8_t* slot = sm.ring + (size_t)(ci % sm.nslot) * MK_SLOT;
-      const WRef& w = c.tag == 0 ? L->q : (c.tag == 1 ? L->k : L->v);
-      float* out = c.tag == 0 ? a.q : (c.tag == 1 ? a.k : a.v);
-      if (ok)
-        for (int j = warp; j < c.n; j += MK_CW) {
-          const float v = dot_row(w.enc, chunk_row(w, slot, c, 0, j), w.cols, sm.xs, lane);
-          if (lane == 0) out[c.r0 + j] = v;
-        }
-      prof.toc(11, tr_);
-      release_slot(sm, ci, lane);
-      ci++;
-    });
-    { const unsigned long long t_ = prof.tic(); grid_sync(a, gb, G, tid, sm); prof.toc(12, t_); }
+    unsigned long long ts = prof.tic();
+    out_scale = stage_phase(a.hidden, false, L->attn_norm, L->norm_type, a.H, a.eps,
+                            xl_for_encoding(L->q.enc), sm, tid, lane, warp);
+    prof.toc(9, ts);
+    run_phase(4 * l + 0);
+    gsync();
     prof.mark(1);
-    // ---- qk-norm, RoPE, KV write, attention
-    if (!*sm.abort) {
+    if (!*sm.abort && !(a.debug_skip & 4)) {
       if (a.d <= 128)
         phase_attention<4>(a, l, L, cta, pos, seq, nsplit, sm, tid, lane, warp);
       else
         phase_attention<8>(a, l, L, cta, pos, seq, nsplit, sm, tid, lane, warp);
     }
-    { const unsigned long long t_ = prof.tic(); grid_sync(a, gb, G, tid, sm); prof.toc(12, t_); }
+    gsync();
     prof.mark(2);
-    // ---- o_proj + residual
-    if (nsplit == 1) {
-      for (int i = tid; i < qd / 4; i += MK_CT)
-        reinterpret_cast<float4*>(sm.xs)[i] = __ldcg(reinterpret_cast<const float4*>(a.ctx) + i);
-    } else {
+    ts = prof.tic();
+    if (nsplit > 1) {
       for (int e = tid; e < qd; e += MK_CT) {
         const int h = e / a.d, i = e - h * a.d;
         const float* p0 = a.attn_part + (int64_t)h * a.max_split * (a.d + 2);
+        float pm[16], pl[16], po[16];
+#pragma unroll
+        for (int s = 0; s < 16; s++)
+          if (s < nsplit) {
+            const float* ps = p0 + s * (a.d + 2);
+            pm[s] = __ldcg(ps + a.d);
+            pl[s] = __ldcg(ps + a.d + 1);
+            po[s] = __ldcg(ps + i);
+          }
         float gm = -3.40282347e38f;
-        for (int s = 0; s < nsplit; s++) gm = fmaxf(gm, __ldcg(p0 + s * (a.d + 2) + a.d));
+#pragma unroll
+        for (int s = 0; s < 16; s++)
+          if (s < nsplit) gm = fmaxf(gm, pm[s]);
         float o = 0.f, gl = 0.f;
-        for (int s = 0; s < nsplit; s++) {
-          const float* ps = p0 + s * (a.d + 2);
-          const float wgt = expf(__ldcg(ps + a.d) - gm);
-          o += __ldcg(ps + i) * wgt;
-          gl += __ldcg(ps + a.d + 1) * wgt;
-        }
+#pragma unroll
+        for (int s = 0; s < 16; s++)
+          if (s < nsplit) {
+            const float wgt = expf(pm[s] - gm);
+            o += po[s] * wgt;
+            gl += pl[s] * wgt;
+          }
         sm.xs[e] = o / gl;
       }
+      consumer_sync();
     }
-    consumer_sync();
-    enum_phase(a, L, PH_O, cta, G, [&](const Chunk& c) {
-      const unsigned long long tw_ = prof.tic();
-      const bool ok = wait_full(sm, ci);
-      prof.toc(10, tw_);
-      const unsigned long long tr_ = prof.tic();
-      const uint8_t* slot = sm.ring + (size_t)(ci % sm.nslot) * MK_SLOT;
-      if (ok)
-        for (int j = warp; j < c.n; j += MK_CW) {
-          const float v = dot_row(L->o.enc, chunk_row(L->o, slot, c, 0, j), L->o.cols, sm.xs, lane);
-          if (lane == 0) a.hidden[c.r0 + j] = __ldcg(a.hidden + c.r0 + j) + v;
-        }
-      prof.toc(11, tr_);
-      release_slot(sm, ci, lane);
-      ci++;
-    });
-    { const unsigned long long t_ = prof.tic(); grid_sync(a, gb, G, tid, sm); prof.toc(12, t_); }
+    out_scale = stage_phase(a.ctx, nsplit > 1, nullptr, 0, (int)qd, 0.f, xl_for_encoding(L->o.enc), sm,
+                            tid, lane, warp);
+    prof.toc(9, ts);
+    run_phase(4 * l + 1);
+    gsync();
     prof.mark(3);
-    // ---- norm + gate/up + SwiGLU
-    { const unsigned long long t_ = prof.tic(); stage_norm(a.hidden, L->ffn_norm, L->norm_type, a.H, a.eps, sm, tid, lane, warp); prof.toc(9, t_); }
-    enum_phase(a, L, PH_GATEUP, cta, G, [&](const Chunk& c) {
-      const unsigned long long tw_ = prof.tic();
-      const bool ok = wait_full(sm, ci);
-      prof.toc(10, tw_);
-      const unsigned long long tr_ = prof.tic();
-      const uint8_t* slot = sm.ring + (size_t)(ci % sm.nslot) * MK_SLOT;
-      const int up_comp = L->gate.enc == E_MLX_U4 ? 3 : 1;
-      if (ok)
-        for (int j = warp; j < c.n; j += MK_CW) {
-          const float g = dot_row(L->gate.enc, chunk_row(L->gate, slot, c, 0, j), L->gate.cols, sm.xs, lane);
-          const float u = dot_row(L->up.enc, chunk_row(L->up, slot, c, up_comp, j), L->up.cols, sm.xs, lane);
-          if (lane == 0) a.act[c.r0 + j] = (g / (1.0f + expf(-g))) * u;
-        }
-      prof.toc(11, tr_);
-      release_slot(sm, ci, lane);
-      ci++;
-    });
-    { const unsigned long long t_ = prof.tic(); grid_sync(a, gb, G, tid, sm); prof.toc(12, t_); }
+    ts = prof.tic();
+    out_scale = stage_phase(a.hidden, false, L->ffn_norm, L->norm_type, a.H, a.eps,
+                            xl_for_encoding(L->gate.enc), sm, tid, lane, warp);
+    prof.toc(9, ts);
+    run_phase(4 * l + 2);
+    gsync();
     prof.mark(4);
-    // ---- down + residual
-    for (int i = tid; i < a.I / 4; i += MK_CT)
-      reinterpret_cast<float4*>(sm.xs)[i] = __ldcg(reinterpret_cast<const float4*>(a.act) + i);
-    consumer_sync();
-    enum_phase(a, L, PH_DOWN, cta, G, [&](const Chunk& c) {
-      const unsigned long long tw_ = prof.tic();
-      const bool ok = wait_full(sm, ci);
-      prof.toc(10, tw_);
-      const unsigned long long tr_ = prof.tic();
-      const uint8_t* slot = sm.ring + (size_t)(ci % sm.nslot) * MK_SLOT;
-      if (ok)
-        for (int j = warp; j < c.n; j += MK_CW) {
-          const float v = dot_row(L->down.enc, chunk_row(L->down, slot, c, 0, j), L->down.cols, sm.xs, lane);
-          if (lane == 0) a.hidden[c.r0 + j] = __ldcg(a.hidden + c.r0 + j) + v;
-        }
-      prof.toc(11, tr_);
-      release_slot(sm, ci, lane);
-      ci++;
-    });
-    { const unsigned long long t_ = prof.tic(); grid_sync(a, gb, G, tid, sm); prof.toc(12, t_); }
+    ts = prof.tic();
+    out_scale = stage_phase(a.act, false, nullptr, 0, a.I, 0.f, xl_for_encoding(L->down.enc), sm, tid,
+                            lane, warp);
+    prof.toc(9, ts);
+    run_phase(4 * l + 3);
+    gsync();
     prof.mark(5);
   }
 
   // ---- final norm + lm_head + argmax partials (first strict maximum)
-  { const unsigned long long t_ = prof.tic(); stage_norm(a.hidden, a.out_norm, a.out_norm_type, a.H, a.eps, sm, tid, lane, warp); prof.toc(9, t_); }
-  float bv = -INFINITY;
-  long long bi = 0x7fffffffffffffffLL;
-  enum_phase(a, a.L, PH_HEAD, cta, G, [&](const Chunk& c) {
-    const unsigned long long tw_ = prof.tic();
-      const bool ok = wait_full(sm, ci);
-      prof.toc(10, tw_);
-      const unsigned long long tr_ = prof.tic();
-    const uint8_t* slot = sm.ring + (size_t)(ci % sm.nslot) * MK_SLOT;
-    if (ok)
-      for (int j = warp; j < c.n; j += MK_CW) {
-        const float v = dot_row(a.lm_head.enc, chunk_row(a.lm_head, slot, c, 0, j), a.lm_head.cols, sm.xs, lane);
-        const long long row = c.r0 + j;
-        if (lane == 0) a.logits[row] = v;
-        if (v > -INFINITY && arg_better(v, row, bv, bi)) bv = v, bi = row;
-      }
-    prof.toc(11, tr_);
-    release_slot(sm, ci, lane);
-    ci++;
-  });
   {
-    float* rv = sm.misc;
-    long long* ri = reinterpret_cast<long long*>(sm.misc + 64);
-    consumer_sync();
-    if (lane == 0) {
-      rv[warp] = bv;
-      ri[warp] = bi;
+    const unsigned long long ts = prof.tic();
+    out_scale = stage_phase(a.hidden, false, a.out_norm, a.out_norm_type, a.H, a.eps,
+                            xl_for_encoding(a.lm_head.enc), sm, tid, lane, warp);
+    prof.toc(9, ts);
+  }
+  run_phase(4 * a.layers);
+  if (warp == 0) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) {  // the 16 finalising threads are lanes 0..15 of warp 0
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (arg_better(ov, oi, bv, bi)) bv = ov, bi = oi;
     }
-    consumer_sync();
-    if (tid == 0) {
-      for (int w = 1; w < MK_CW; w++)
-        if (arg_better(rv[w], ri[w], bv, bi)) bv = rv[w], bi = ri[w];
+    if (lane == 0) {
       a.argmax_val[cta] = bv;
       a.argmax_idx[cta] = bi;
     }
   }
-  { const unsigned long long t_ = prof.tic(); grid_sync(a, gb, G, tid, sm); prof.toc(12, t_); }
+  gsync();
   prof.mark(6);
   if (cta == 0 && warp == 0) {
     float v = -INFINITY;
@@ -824,25 +884,179 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
 
 }  // namespace
 
-size_t mega_smem_bytes(int nslot, int xs_floats) {
-  return (size_t)xs_floats * 4 + (size_t)MK_MISC_FLOATS * 4 + (size_t)nslot * MK_SLOT +
-         (size_t)nslot * 16 + 128;
+size_t mega_smem_bytes(int nslot, int xs_floats, size_t prog_bytes) {
+  return (size_t)xs_floats * 4 * 2 + (size_t)(xs_floats / 32 + xs_floats / 16) * 4 +
+         (size_t)MK_MISC_FLOATS * 4 + (size_t)nslot * MK_SLOT + (size_t)nslot * 16 + 128 + prog_bytes;
 }
 
-int mega_plan(int H, int I, int qd, int d, int* nslot, int* xs_floats, size_t* smem) {
+// prog_bytes: bytes of one CTA's program (chunks + counts, 16-byte rounded) to keep in shared
+// memory; *prog_in_smem tells whether it fit beside a ring of at least 5 slots.
+int mega_plan(int H, int I, int qd, int d, size_t prog_bytes, int* nslot, int* xs_floats, size_t* smem,
+              int* prog_in_smem) {
   int xs = H > I ? H : I;
   if (qd > xs) xs = qd;
-  xs = (xs + 31) / 32 * 32;
-  if (d > 256) return 0;
+  xs = (xs + 255) / 256 * 256;
+  if (d > 256 || xs > 8 * MK_CT) return 0;  // staging: one 8-element item per consumer thread
   const size_t budget = 225 * 1024;
-  const size_t fixed = (size_t)xs * 4 + (size_t)MK_MISC_FLOATS * 4 + 512;
-  if (fixed + 3 * (size_t)MK_SLOT > budget) return 0;
+  size_t fixed = mega_smem_bytes(0, xs, 0) + 512;
+  if (fixed + 4 * (size_t)MK_SLOT > budget) return 0;
+  *prog_in_smem = 0;
+  if (prog_bytes && fixed + prog_bytes + 5 * (size_t)(MK_SLOT + 16) <= budget) {
+    *prog_in_smem = 1;
+    fixed += prog_bytes;
+  }
   int n = (int)((budget - fixed) / (MK_SLOT + 16));
   if (n > 12) n = 12;
   *nslot = n;
   *xs_floats = xs;
-  *smem = mega_smem_bytes(n, xs);
+  *smem = mega_smem_bytes(n, xs, *prog_in_smem ? prog_bytes : 0);
   return 1;
+}
+
+// ---- host: chunk programs ------------------------------------------------------------------------
+namespace {
+int host_bank_pitch(int bytes) {
+  int p = (bytes + 15) / 16 * 16;
+  while ((p / 4) % 8 != 4) p += 16;
+  return p;
+}
+struct HostPlan {
+  int ubytes, ukb, units_total, unit_q6;
+};
+HostPlan host_plan(const WRef& w) {
+  HostPlan p{0, 1, 0, 0};
+  const int K = (int)w.cols;
+  switch (w.enc) {
+    case E_Q4_0: p.ubytes = 36, p.ukb = 2, p.units_total = K / 64; break;
+    case E_Q4_1: p.ubytes = 20, p.ukb = 1, p.units_total = K / 32; break;
+    case E_Q8_0: p.ubytes = 68, p.ukb = 2, p.units_total = K / 64; break;
+    case E_MLX_U4: p.ubytes = 16, p.ukb = 1, p.units_total = K / 32; break;
+    default: p.ubytes = 0, p.ukb = 2, p.units_total = K / 64, p.unit_q6 = 1; break;  // quarters
+  }
+  return p;
+}
+int seg_bytes(const HostPlan& p, int nu) { return p.unit_q6 ? (nu / 4) * 210 : nu * p.ubytes; }
+
+// Appends the chunks of rows [lo, hi) of `w`: tiles of 16 rows, each cut into the fewest K-slices
+// whose rows fit one ring slot (slices are multiples of 16 units so the 16 consumer warps share
+// them evenly; Q6_K slices are whole groups of 4 superblocks, which keeps rows 8-byte aligned).
+void add_tensor_chunks(const WRef& w, int64_t lo, int64_t hi, float* out, int ep, bool second,
+                       bool closes, std::vector<MegaChunk>* v) {
+  const HostPlan p = host_plan(w);
+  const int ael = w.aux == E_F32 ? 4 : 2;
+  for (int64_t r = lo; r < hi; r += 16) {
+    const int n = (int)std::min<int64_t>(16, hi - r);
+    // largest slice (multiple of 16 units) whose rows fit one slot; only valid rows are copied
+    int su = p.units_total < 16 ? p.units_total : 16;
+    for (int cand = 16; cand <= p.units_total && cand <= 240; cand += 16) {
+      const int pitch = host_bank_pitch(seg_bytes(p, cand) + 20);
+      const int ap = w.enc == E_MLX_U4 ? ((cand * 32 / w.group) * ael + 31) / 16 * 16 : 0;
+      const size_t need = ap ? (size_t)16 * pitch + 32 * (size_t)ap : (size_t)n * pitch;
+      if (need <= (size_t)MK_SLOT && pitch < 65536) su = cand;
+    }
+    const int nsl = (p.units_total + su - 1) / su;
+    for (int sl = 0; sl < nsl; sl++) {
+      const int u0 = sl * su, nu = std::min(su, p.units_total - u0);
+      MegaChunk c{};
+      const int64_t boff = p.unit_q6 ? (int64_t)(u0 / 4) * 210 : (int64_t)u0 * p.ubytes;
+      c.src = w.data + r * w.row_bytes() + boff;
+      c.rb = (uint32_t)w.row_bytes();
+      c.seg = (uint16_t)seg_bytes(p, nu);
+      c.pitch = (uint16_t)host_bank_pitch(seg_bytes(p, su) + 20);
+      c.kb0 = (uint16_t)(u0 * p.ukb);
+      c.n = (uint8_t)n;
+      c.nu = (uint8_t)nu;
+      c.enc = (uint8_t)w.enc;
+      c.out = out;
+      c.out_row = (int32_t)r;
+      c.flags = (uint8_t)(((closes && sl == nsl - 1) ? 1 : 0) | (second ? 2 : 0) | (ep << 2));
+      if (w.enc == E_MLX_U4) {
+        const int64_t arow = (int64_t)(w.cols / w.group) * ael, ao = (int64_t)(u0 * 32 / w.group) * ael;
+        c.sc = w.scales + r * arow + ao;
+        c.bi = w.biases + r * arow + ao;
+        c.arb = (uint32_t)arow;
+        c.aseg = (uint16_t)((nu * 32 / w.group) * ael);
+        c.apitch = (uint16_t)(((su * 32 / w.group) * ael + 31) / 16 * 16);
+        c.aux = (uint8_t)w.aux;
+        c.group_shift = (uint8_t)(w.group == 32 ? 0 : (w.group == 64 ? 1 : 2));
+      }
+      v->push_back(c);
+    }
+  }
+}
+}  // namespace
+
+int mega_build_program(const MegaBuildLayer* layers, int nlayers, const WRef& lm_head, int nh, int nkv,
+                       int d, int H, int I, int V, float* q, float* k, float* v, float* hidden,
+                       float* act, float* logits, int grid, std::vector<MegaChunk>* chunks,
+                       std::vector<uint16_t>* counts, int* max_chunks) {
+  const int nph = 4 * nlayers + 1;
+  std::vector<std::vector<MegaChunk>> per(grid);
+  counts->assign((size_t)grid * nph, 0);
+  const int64_t qd = (int64_t)nh * d, kvd = (int64_t)nkv * d;
+  for (int cta = 0; cta < grid; cta++) {
+    std::vector<MegaChunk>& pc = per[cta];
+    auto close_phase = [&](int ph, size_t before) {
+      (*counts)[(size_t)cta * nph + ph] = (uint16_t)(pc.size() - before);
+    };
+    for (int l = 0; l < nlayers; l++) {
+      const MegaBuildLayer& L = layers[l];
+      size_t b0 = pc.size();
+      {  // q, k, v share one balanced split of their concatenated rows
+        const int64_t R = qd + 2 * kvd, a0 = R * cta / grid, a1 = R * (cta + 1) / grid;
+        const int64_t offs[3] = {0, qd, qd + kvd}, lens[3] = {qd, kvd, kvd};
+        const WRef* ws[3] = {&L.q, &L.k, &L.v};
+        float* outs[3] = {q, k, v};
+        for (int t = 0; t < 3; t++) {
+          const int64_t lo = std::max(a0, offs[t]) - offs[t], hi = std::min(a1, offs[t] + lens[t]) - offs[t];
+          if (hi > lo) add_tensor_chunks(*ws[t], lo, hi, outs[t], MEGA_EP_STORE, false, true, &pc);
+        }
+      }
+      close_phase(4 * l + 0, b0);
+      b0 = pc.size();
+      add_tensor_chunks(L.o, (int64_t)H * cta / grid, (int64_t)H * (cta + 1) / grid, hidden, MEGA_EP_RESIDUAL,
+                        false, true, &pc);
+      close_phase(4 * l + 1, b0);
+      b0 = pc.size();
+      {  // per tile: gate slices, then up slices into the second accumulator; the pair closes after up
+        const int64_t lo = (int64_t)I * cta / grid, hi = (int64_t)I * (cta + 1) / grid;
+        for (int64_t r = lo; r < hi; r += 16) {
+          const int64_t e = std::min(r + 16, hi);
+          add_tensor_chunks(L.gate, r, e, act, MEGA_EP_SWIGLU, false, false, &pc);
+          add_tensor_chunks(L.up, r, e, act, MEGA_EP_SWIGLU, true, true, &pc);
+        }
+      }
+      close_phase(4 * l + 2, b0);
+      b0 = pc.size();
+      add_tensor_chunks(L.down, (int64_t)H * cta / grid, (int64_t)H * (cta + 1) / grid, hidden,
+                        MEGA_EP_RESIDUAL, false, true, &pc);
+      close_phase(4 * l + 3, b0);
+    }
+    const size_t b0 = pc.size();
+    add_tensor_chunks(lm_head, (int64_t)V * cta / grid, (int64_t)V * (cta + 1) / grid, logits, MEGA_EP_LOGITS,
+                      false, true, &pc);
+    close_phase(4 * nlayers, b0);
+  }
+  size_t mc = 1;
+  for (auto& pc : per) mc = std::max(mc, pc.size());
+  DYN_CHECK(mc < 60000, "decode program too long (%zu chunks per CTA)", mc);
+  *max_chunks = (int)mc;
+  chunks->assign((size_t)grid * mc, MegaChunk{});
+  for (int cta = 0; cta < grid; cta++)
+    std::copy(per[cta].begin(), per[cta].end(), chunks->begin() + (size_t)cta * mc);
+  return 0;
+}
+
+// Whether the persistent kernel's tile steps can read this tensor (encoding and row alignment).
+bool mega_supports_weight(const WRef& w) {
+  switch (w.enc) {
+    case E_Q4_0:
+    case E_Q8_0: return w.cols % 256 == 0;
+    case E_Q4_1: return w.cols % 128 == 0;
+    case E_Q6_K: return w.cols % 1024 == 0;
+    case E_MLX_U4: return w.cols % 256 == 0 && (w.group == 32 || w.group == 64 || w.group == 128);
+    default: return false;
+  }
 }
 
 int mega_grid_size(int device, size_t smem, int* grid) {

@@ -379,6 +379,37 @@ __device__ __forceinline__ void sblk_q6_k(const uint8_t* p0, const uint8_t* p1, 
   }
 }
 
+// One quarter of a Q6_K superblock: half n (128 elements), 16-element sub-block s of each of
+// its four 32-element slices (h, p). Loads the qh word once and each ql word once.
+// xfp: the lane's fragments of the superblock's first 32-block (xstride halfs per block);
+// sxa/sxb: 16-run sums of that first block.
+template <int PH, bool HILO>
+__device__ __forceinline__ void q6k_quarter(const uint8_t* p0, const uint8_t* p1, int n, int s,
+                                            const __half* xfp, int xstride, const float* sxa,
+                                            const float* sxb, int t, TileAcc<HILO>& acc) {
+  const int j0 = 16 * s + 4 * t;
+  const float d0 = ldh_f32(p0 + 208), d1 = ldh_f32(p1 + 208);
+  const uint32_t qh0 = ld32_ph<PH>(p0 + 128 + n * 32 + j0), qh1 = ld32_ph<PH>(p1 + 128 + n * 32 + j0);
+#pragma unroll
+  for (int p = 0; p < 2; p++) {
+    const uint32_t ql0 = ld32_ph<PH>(p0 + n * 64 + p * 32 + j0), ql1 = ld32_ph<PH>(p1 + n * 64 + p * 32 + j0);
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int e32 = n * 4 + h * 2 + p;
+      const uint4 b = *reinterpret_cast<const uint4*>(xfp + (size_t)e32 * xstride);
+      const uint32_t v0 = ((ql0 >> (4 * h)) & 0x0F0F0F0Fu) | (((qh0 >> (2 * (h * 2 + p))) & 0x03030303u) << 4);
+      const uint32_t v1 = ((ql1 >> (4 * h)) & 0x0F0F0F0Fu) | (((qh1 >> (2 * (h * 2 + p))) & 0x03030303u) << 4);
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      mma_f16_16816(c, __byte_perm(v0, 0, 0x4140), __byte_perm(v1, 0, 0x4140), __byte_perm(v0, 0, 0x4342),
+                    __byte_perm(v1, 0, 0x4342), s ? b.z : b.x, s ? b.w : b.y);
+      const int sci = 192 + n * 8 + h * 4 + p * 2 + s;
+      const float f0 = d0 * (float)*reinterpret_cast<const int8_t*>(p0 + sci);
+      const float f1 = d1 * (float)*reinterpret_cast<const int8_t*>(p1 + sci);
+      unit_apply<HILO>(acc, c, f0, f1, 32.0f * GV_2M24, sxa[2 * e32 + s], HILO ? 0.f : sxb[2 * e32 + s]);
+    }
+  }
+}
+
 __host__ __device__ inline bool gemv_mma_supports(int enc) {
   return enc == E_Q4_0 || enc == E_Q4_1 || enc == E_Q8_0 || enc == E_Q6_K || enc == E_MLX_U4;
 }

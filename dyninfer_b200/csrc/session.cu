@@ -85,6 +85,10 @@ struct dyninfer_cuda_session_t {
   float* amax_val = nullptr;
   long long* amax_idx = nullptr;
   unsigned long long* prof_dev = nullptr;
+  MegaChunk* prog_dev = nullptr;
+  uint16_t* counts_dev = nullptr;
+  int mega_max_chunks = 0;
+  int mega_prog_smem = 0;
   // graphs
   cudaGraphExec_t decode_graph = nullptr;  // H2D token/pos + forward + D2H token
   cudaGraphExec_t loop_graph = nullptr;    // forward + device-side advance
@@ -355,6 +359,10 @@ int ensure_hist(Session* s, size_t steps) {
   return 0;
 }
 
+int xl_for_encoding_host(int enc) {
+  return (enc == E_Q4_0 || enc == E_Q4_1) ? 0 : (enc == E_MLX_U4 ? 1 : 2);
+}
+
 void fill_mega_args(Session* s, MegaArgs* a, int advance) {
   const ModelCfg& c = s->cfg;
   a->layers = c.layers, a->H = c.hidden, a->I = c.inter, a->V = c.vocab;
@@ -377,7 +385,19 @@ void fill_mega_args(Session* s, MegaArgs* a, int advance) {
   a->error = reinterpret_cast<int*>(s->io_dev + 4);
   a->attn_part = s->attn_part, a->max_split = s->mega_max_split;
   a->argmax_val = s->amax_val, a->argmax_idx = s->amax_idx;
-  a->prof = s->prof_dev;
+  // phase timing reads the global timer thousands of times per launch on CTA 0 and slows the
+  // whole grid down; it is off unless DYNINFER_CUDA_PROFILE=1
+  {
+    const char* pe = getenv("DYNINFER_CUDA_PROFILE");
+    a->prof = (pe && pe[0] == '1') ? s->prof_dev : nullptr;
+  }
+  a->prog = s->prog_dev, a->counts = s->counts_dev, a->max_chunks = s->mega_max_chunks;
+  a->prog_in_smem = s->mega_prog_smem;
+  {
+    const char* dbg = getenv("DYNINFER_CUDA_DEBUG_SKIP");
+    a->debug_skip = dbg ? atoi(dbg) : 0;
+    if (a->debug_skip & 2) a->eps = -2.f;
+  }
   a->nslot = s->mega_nslot, a->xs_floats = s->mega_xs;
   a->ft = s->freq;
 }
@@ -642,8 +662,8 @@ int dyninfer_cuda_session_create_with_file_params(
   s->decode_weight_bytes = dwb;
 
   if (cfg.persistent &&
-      mega_plan(cfg.hidden, cfg.inter, (int)qd, cfg.head_dim, &s->mega_nslot, &s->mega_xs,
-                &s->mega_smem)) {
+      mega_plan(cfg.hidden, cfg.inter, (int)qd, cfg.head_dim, 0, &s->mega_nslot, &s->mega_xs,
+                &s->mega_smem, &s->mega_prog_smem)) {
     if (mega_grid_size(device, s->mega_smem, &s->mega_grid)) return fail();
     std::vector<MegaLayer> ml(cfg.layers);
     for (int l = 0; l < cfg.layers; l++) {
@@ -653,8 +673,17 @@ int dyninfer_cuda_session_create_with_file_params(
       ml[l].attn_norm = L.attn_norm.ptr, ml[l].ffn_norm = L.ffn_norm.ptr;
       ml[l].q_norm = L.q_norm.ptr, ml[l].k_norm = L.k_norm.ptr;
       ml[l].norm_type = L.attn_norm.type, ml[l].qk_norm_type = L.q_norm.type;
+      // the persistent kernel needs every linear readable by its tile steps, q/k/v sharing one
+      // activation layout, and gate/up sharing an encoding; other models use the graph path
+      const WRef* ws[7] = {&L.q, &L.k, &L.v, &L.o, &L.gate, &L.up, &L.down};
+      for (const WRef* wp : ws)
+        if (!mega_supports_weight(*wp)) s->mega_grid = 0;
       if (L.attn_norm.type != L.ffn_norm.type || L.gate.enc != L.up.enc) s->mega_grid = 0;
+      if (xl_for_encoding_host(L.q.enc) != xl_for_encoding_host(L.k.enc) ||
+          xl_for_encoding_host(L.q.enc) != xl_for_encoding_host(L.v.enc))
+        s->mega_grid = 0;
     }
+    if (!mega_supports_weight(s->lm_head)) s->mega_grid = 0;
     s->mega_max_split = std::max(1, std::min(16, s->mega_grid / std::max(1, cfg.heads)));
     if (s->mega_grid > 0) {
       const size_t part_bytes = (size_t)cfg.heads * s->mega_max_split * (cfg.head_dim + 2) * 4;
@@ -693,7 +722,8 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
   void* dev[] = {s->arena, s->kcache, s->vcache, s->hidden, s->xn, s->q, s->k, s->v, s->ctx, s->act,
                  s->logits, s->tokens_dev, s->row_pos_dev, s->row_seq_dev, s->out_token_dev,
                  s->hist_dev, s->hist_count_dev, s->argmax_scratch, s->mega_layers, s->io_dev,
-                 s->bar_dev, s->attn_part, s->amax_val, s->amax_idx, s->prof_dev};
+                 s->bar_dev, s->attn_part, s->amax_val, s->amax_idx, s->prof_dev, s->prog_dev,
+                 s->counts_dev};
   for (void* p : dev)
     if (p) cudaFree(p);
   if (s->logits_host) cudaFreeHost(s->logits_host);
@@ -748,6 +778,34 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
   }
   s->kv_configured = true;
   destroy_graphs(s);
+  if (s->mega && !s->prog_dev) {
+    std::vector<MegaBuildLayer> bl(c.layers);
+    for (int l = 0; l < c.layers; l++) {
+      const LayerW& L = s->layers[l];
+      bl[l].q = L.q, bl[l].k = L.k, bl[l].v = L.v, bl[l].o = L.o;
+      bl[l].gate = L.gate, bl[l].up = L.up, bl[l].down = L.down;
+    }
+    std::vector<MegaChunk> chunks;
+    std::vector<uint16_t> counts;
+    if (mega_build_program(bl.data(), c.layers, s->lm_head, c.heads, c.kv_heads, c.head_dim, c.hidden,
+                           c.inter, c.vocab, s->q, s->k, s->v, s->hidden, s->act, s->logits,
+                           s->mega_grid, &chunks, &counts, &s->mega_max_chunks))
+      return 1;
+    if (dev_alloc(s, (void**)&s->prog_dev, chunks.size() * sizeof(MegaChunk)) ||
+        dev_alloc(s, (void**)&s->counts_dev, counts.size() * sizeof(uint16_t)))
+      return 1;
+    DYN_CUDA(cudaMemcpy(s->prog_dev, chunks.data(), chunks.size() * sizeof(MegaChunk),
+                        cudaMemcpyHostToDevice));
+    DYN_CUDA(cudaMemcpy(s->counts_dev, counts.data(), counts.size() * sizeof(uint16_t),
+                        cudaMemcpyHostToDevice));
+    // final shared-memory plan: keep the program beside the ring when it fits
+    const size_t prog_bytes = ((size_t)s->mega_max_chunks * sizeof(MegaChunk) +
+                               (size_t)(4 * c.layers + 1) * 2 + 15) / 16 * 16;
+    DYN_CHECK(mega_plan(c.hidden, c.inter, c.heads * c.head_dim, c.head_dim, prog_bytes, &s->mega_nslot,
+                        &s->mega_xs, &s->mega_smem, &s->mega_prog_smem),
+              "persistent decode kernel: shared-memory plan failed");
+    if (mega_grid_size(s->device, s->mega_smem, &s->mega_grid)) return 1;
+  }
   return 0;
 }
 

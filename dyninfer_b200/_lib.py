@@ -57,6 +57,8 @@ PROTOTYPES = {
     "dyninfer_cuda_attention": (C.c_int, [_P, _P, _P, C.c_int, _I64, _I64, _I64, _I64, _I64, _I64, _P, _P]),
     "dyninfer_cuda_argmax_scratch_bytes": (C.c_size_t, [_I64]),
     "dyninfer_cuda_argmax": (C.c_int, [_P, _I64, _P, _P, _P]),
+    "dyninfer_cuda_argmax_static_max_n": (_I64, []),
+    "dyninfer_cuda_argmax_static": (C.c_int, [_P, _I64, _P, _P]),
     "dyninfer_cuda_session_create_with_file_params": (
         C.c_int, [C.c_char_p, C.c_char_p, C.POINTER(ParameterFile), C.c_size_t,
                   C.POINTER(FileParam), C.c_size_t, C.POINTER(_P)]),

@@ -120,6 +120,20 @@ size_t dyninfer_cuda_argmax_scratch_bytes(int64_t n);
 int dyninfer_cuda_argmax(const float* v_dev, int64_t n, int64_t* out_index_dev, void* scratch_dev,
                          void* stream);
 
+/* Argmax that allocates nothing. No counterpart in the reference: it exists for hosts that must
+ * not touch the device allocator on this call -- a serving loop that reserved all device memory
+ * up front (so an allocation could fail or stall behind other work), or a caller between
+ * operations that cannot tolerate the implicit synchronisation an allocation may bring. Same
+ * result as dyninfer_cuda_argmax, without a scratch argument: the per-block partial results go
+ * to a fixed 16 KiB array inside the library. n must not exceed
+ * dyninfer_cuda_argmax_static_max_n() (4,194,304 elements); larger n fails with a message.
+ * The first call on each device looks up the array's address (set-up work: make it before
+ * starting a stream capture). All calls on a device share the array; each call rewrites the
+ * slots it reads, so no clearing is needed between calls, but calls in flight at the same time
+ * race on it. */
+int64_t dyninfer_cuda_argmax_static_max_n(void);
+int dyninfer_cuda_argmax_static(const float* v_dev, int64_t n, int64_t* out_index_dev, void* stream);
+
 /* ---- session (paged-KV ABI) ----------------------------------------------- */
 
 typedef struct dyninfer_cuda_session_t dyninfer_cuda_session_t;

@@ -7,14 +7,17 @@ One step = one decode step (one generated token) of the seeded synthetic
 checkpoint (all linears Q4_0, tied Q6_K embedding / lm_head, GGUF v3), after a
 16-token prompt. Prints ONE JSON line on rank 0.
 
-  value     decode tok/s with everything resident in HBM: K replays of the captured
-            decode graph with the argmax fed back on the device, timed with CUDA
+  value     decode tok/s with everything resident in HBM: K launches of the persistent
+            decode kernel with the argmax fed back on the device, timed with CUDA
             events on the session stream (max over ranks).
   e2e       the same K steps through the public session call `decode_argmax`
             (C ABI `dyninfer_cuda_session_invoke_paged_chunk`): host token in from
             pinned memory, argmax token out, every step.
-  roofline  the lm_head product (151936 x 1024 Q6_K, the largest single launch),
-            timed alone with CUDA events, L2 flushed between launches.
+  roofline  the persistent decode kernel (the only kernel in the timed region): the
+            weight bytes one token reads / its average launch time, against the
+            measured HBM copy bandwidth. `roofline_lm_head_gemv` adds the largest
+            single product (151936 x 1024 Q6_K) as a stand-alone fused dequant-GEMV
+            launch, timed alone with CUDA events, L2 flushed between launches.
   cpu_baseline  the CPU restatement of the reference's direct path (oracle/) on the
             host cores, on a bounded sample of the same workload.
 
@@ -100,6 +103,11 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
                 "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_mega_kernel launch on this workload
+# (ncu capture summarised in profiles/decode_mega_kernel_qwen3_0_6b_q4_0.md)
+MEGA_DRAM_TRAFFIC = 384_432_768 + 12_080_000
 
 
 def checkpoint_path():
@@ -197,6 +205,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "f16", "f32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="prompt + W + K device-loop decode steps and nothing else (small case for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     rank = int(os.environ.get("RANK", "0"))
@@ -238,6 +248,11 @@ def main():
 
     # ---- device-resident arm
     toks_w, _ = session.decode_loop(first, W)
+    if args.decode_only:
+        _, ms = session.decode_loop(int(toks_w[-1]), K)
+        print(json.dumps({"decode_only": True, "steps": K, "ms_per_step": ms / K}), flush=True)
+        session.close()
+        return
     barrier()
     launches0 = session.launch_count()
     with ClockSampler(local_rank) as clocks:
@@ -278,10 +293,18 @@ def main():
                     "d2h_bytes_per_step": 8},
             "gpu_launches": int(gpu_launches),
             "clocks": clocks.summary(),
-            "roofline": {"bound": "hbm", "kernel": f"linear_rows_kernel<{lm_enc}> lm_head 151936x1024, M=1",
-                         "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "peak_source": peak_kind,
-                         "bytes_per_launch": lm_bytes, "ms_per_launch": lm_ms, "traffic": None},
+            # dominant kernel: the persistent decode kernel, one launch per token (all of the
+            # timed region). Algorithmic bytes per launch = the weight bytes one token reads.
+            "roofline": {"bound": "hbm", "kernel": "decode_mega_kernel (one launch per token)",
+                         "achieved": weight_bytes / (ms / K * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": weight_bytes / (ms / K * 1e-3) / 1e9 / hbm_peak, "peak_source": peak_kind,
+                         "bytes_per_launch": weight_bytes, "ms_per_launch": ms / K,
+                         "traffic": MEGA_DRAM_TRAFFIC},
+            # the largest single product of the step as its own launch (fused dequant-GEMV, M=1)
+            "roofline_lm_head_gemv": {"bound": "hbm", "kernel": f"gemv_tile_kernel<{lm_enc}> 151936x1024, M=1",
+                                      "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                                      "frac": achieved / hbm_peak, "bytes_per_launch": lm_bytes,
+                                      "ms_per_launch": lm_ms},
         }
         if not args.no_cpu_baseline:
             steps = 24

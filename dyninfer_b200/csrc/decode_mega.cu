@@ -43,7 +43,7 @@ __device__ __forceinline__ void gather_row_t(const WRef& w, int64_t row, float* 
           make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
   }
 }
-__device__ __noinline__ void mega_gather_row(const WRef& w, int64_t row, float* out, int tid, int nthreads) {
+__device__ __noinline__ void mega_gather_row(const WRef w, int64_t row, float* out, int tid, int nthreads) {
   switch (w.enc) {
     case E_Q4_0: gather_row_t<E_Q4_0>(w, row, out, tid, nthreads); break;
     case E_Q4_1: gather_row_t<E_Q4_1>(w, row, out, tid, nthreads); break;

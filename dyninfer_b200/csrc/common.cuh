@@ -142,6 +142,9 @@ int launch_gather(const WRef& w, const int64_t* tokens, int64_t count, float* ou
 int launch_linear(const WRef& w, const void* x, int x_type, int64_t m, float* y,
                   const float* residual, cudaStream_t s);
 // Tensor-core GEMV for few activation rows (gemv_mma.cu); *handled tells whether it ran.
+size_t gemv_cs_workspace_bytes(const WRef& w, int M);
+int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, const float* residual,
+                   uint8_t* ws, cudaStream_t s, bool* handled);
 size_t gemv_mma_workspace_bytes(const WRef& w, int x_type, int M);
 int launch_gemv_mma(const WRef& w, const void* x, int x_type, int M, float* y, const float* residual,
                     void* workspace, cudaStream_t s, bool* handled);

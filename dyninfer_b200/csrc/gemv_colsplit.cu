@@ -1,0 +1,359 @@
+// Fused dequant-GEMV for ONE activation row, "column-split" tensor-core scheme.
+//
+// mma.sync.m16n8k16 has 8 output columns but a matrix-vector product needs one (two with the
+// hi/lo f16 split of an f32 activation). This kernel uses the other columns to keep FOUR
+// quantisation blocks apart inside one instruction: lane quarter t (lane & 3) feeds the A operand
+// with the nibbles of block t of its two rows, and the B operand holds block t's activations only
+// in columns 2t (hi) and 2t+1 (lo), zeros elsewhere. The accumulator fragment of lane (g, t) is
+// then exactly (row g | row g+8) x (block t hi, lo): every lane applies one block scale per row
+// per 8 mma steps instead of one per block per step, and reads its 16 quant bytes + scale as one
+// contiguous run. Instruction cost drops to ~1.3 per weight, which is what it takes for the
+// product to be bound by HBM instead of by instruction issue.
+//
+// Q4_0 (18-byte blocks, crates/dyninfer-kernel-registry/src/gguf_codegen.rs:268-330 for the
+// decode rule w = (q - 8) * d): a unit is 8 blocks = 144 bytes per row = 36 words; lane t reads
+// words 9t .. 9t+8 of its rows, which hold blocks 2t (scale in the low half of word 0, quants
+// straddling words 0..4) and 2t+1 (scale in the high half of word 4, quants = words 5..8).
+// Even blocks form one mma group, odd blocks the next, so the alignment case is uniform per
+// group.
+//
+// Data movement: every warp owns a ring of CS_NST stages in shared memory; a stage is 16 rows x
+// 288 bytes (two units, K-span 512), one 1-D bulk copy (cp.async.bulk) per row completing on the
+// stage's mbarrier, rows 304 bytes apart so the 32 lanes of a fragment load hit 32 banks. A stage
+// is read into registers in one go and its slot refilled before the math starts. A warp walks a
+// contiguous range of (tile, K-slice) items and keeps the ring running across item boundaries.
+// All waits are bounded; a wait that runs out sets the error word in the workspace and the warp
+// leaves (its rows are then not written).
+#include <algorithm>
+
+#include "gemv_core.cuh"
+#include "ring.cuh"
+
+namespace dyn {
+
+namespace {
+
+constexpr int CS_WARPS = 16;
+constexpr int CS_NST = 2;            // stages per warp
+constexpr int CS_PAIRS = 1;          // unit pairs (512 elements, 288 bytes per row) per stage
+constexpr int CS_ROWB = 288 * CS_PAIRS;   // bytes of one row in a stage
+constexpr int CS_PITCH = CS_ROWB + 16;    // row pitch: 76 or 148 words = 12 or 20 (mod 32), conflict-free
+constexpr int CS_STAGE = 16 * CS_PITCH;
+constexpr int CS_KSTAGE = 512 * CS_PAIRS; // K elements per stage
+constexpr long long CS_SPINS = 1LL << 22;
+constexpr int CS_MAX_SMEM = 226 * 1024;  // dynamic shared memory the kernel may ask for (static: 128 bytes)
+constexpr int CS_RING_BYTES = CS_WARPS * CS_NST * CS_STAGE + CS_WARPS * CS_NST * 8;  // rings + barriers
+
+// ---- activation staging (every CTA, into its own shared memory) ---------------------------------
+// xq: per (unit U of 256 elements, parity e, word i, quarter t, hi/lo) one uint4 holding the B
+// registers of mma steps 2i (x, y) and 2i+1 (z, w) of block 8U + 2t + e:
+//   step 2i+o: b0 = (x[4i+o], x[4i+o+2]), b1 = (x[16+4i+o], x[16+4i+o+2]) / 16,
+// scaled so the row's largest magnitude sits in [2^12, 2^13); index ((U*2+e)*4+i)*8 + 2t + hl, so
+// the eight lanes that feed one step read 128 contiguous bytes.
+// sx8[b] = 8 * sum(block b of the scaled row) (the Q4_0 zero point), in accumulator units.
+// Returns 2^24 / scale (what turns accumulator units back into the product).
+__device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf16, int K, uint2* xq,
+                                            float* sx8, float* red) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  auto ld = [&](int i) -> float {
+    return x_bf16 ? bf16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t*>(x) + i))
+                  : __ldg(reinterpret_cast<const float*>(x) + i);
+  };
+  float mx = 0.f;
+  for (int i = tid; i < K; i += CS_WARPS * 32) mx = fmaxf(mx, fabsf(ld(i)));
+  mx = warp_max(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = 0.f;
+#pragma unroll
+  for (int i = 0; i < CS_WARPS; i++) mx = fmaxf(mx, red[i]);
+  float s, is;
+  scale_for(mx, &s, &is);
+  for (int j = tid; j < (K >> 2); j += CS_WARPS * 32) {  // item j: block j / 8, mma step j % 8
+    const int b = j >> 3, st = j & 7, i = st >> 1, o = st & 1;
+    const int U = b >> 3, r = b & 7, t = r >> 1, e = r & 1;
+    const float e0 = ld(b * 32 + 4 * i + o) * s, e1 = ld(b * 32 + 4 * i + o + 2) * s;
+    const float g0 = ld(b * 32 + 16 + 4 * i + o) * s, g1 = ld(b * 32 + 16 + 4 * i + o + 2) * s;
+    float sum = (e0 + e1) + (g0 + g1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    if (st == 0) sx8[b] = 8.0f * GV_2M24 * sum;
+    const float f0 = g0 * 0.0625f, f1 = g1 * 0.0625f;
+    const __half h0 = __float2half_rn(e0), h1 = __float2half_rn(e1);
+    const __half h2 = __float2half_rn(f0), h3 = __float2half_rn(f1);
+    const __half2 hi0 = __halves2half2(h0, h1), hi1 = __halves2half2(h2, h3);
+    const __half2 lo0 = __halves2half2(__float2half_rn(e0 - __half2float(h0)), __float2half_rn(e1 - __half2float(h1)));
+    const __half2 lo1 = __halves2half2(__float2half_rn(f0 - __half2float(h2)), __float2half_rn(f1 - __half2float(h3)));
+    uint2* dst = xq + ((size_t)(((U * 2 + e) * 4 + i) * 8 + 2 * t) * 2 + o);  // uint2 units; hl adds 2
+    dst[0] = make_uint2(*reinterpret_cast<const uint32_t*>(&hi0), *reinterpret_cast<const uint32_t*>(&hi1));
+    dst[2] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo0), *reinterpret_cast<const uint32_t*>(&lo1));
+  }
+  return GV_2P24 * is;
+}
+
+// ---- tiles -------------------------------------------------------------------------------------
+struct CsArgs {
+  const uint8_t* data;   // Q4_0 rows
+  int64_t N;
+  int64_t rb;            // bytes per row
+  int K;
+  int S;                 // K-slices per tile
+  int nst;               // stages per item (K / S / 512)
+  int ntiles;
+  const void* x;         // the activation row
+  int x_bf16;
+  float* misc;           // [0] = 2^24 / scale, for the K-slice reduction
+  float* y;
+  const float* residual;
+  float* partial;        // [S][N] when S > 1
+  int* error;
+};
+
+__global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_0_kernel(const CsArgs a) {
+  extern __shared__ __align__(128) uint8_t cs_smem[];
+  __shared__ int s_abort;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  uint8_t* ring = cs_smem + (size_t)warp * CS_NST * CS_STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(cs_smem + (size_t)CS_WARPS * CS_NST * CS_STAGE) + warp * CS_NST;
+  uint4* xq = reinterpret_cast<uint4*>(cs_smem + CS_RING_BYTES);
+  float* sx8 = reinterpret_cast<float*>(xq + (size_t)(a.K >> 8) * 64);
+  float* red = sx8 + (a.K >> 5);
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    if (blockIdx.x == 0) *a.error = 0;  // a wait that runs out (seconds later) sets it
+  }
+  if (lane == 0) {
+    for (int i = 0; i < CS_NST; i++) mbar_init(bars + i, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const int64_t nitems = (int64_t)a.ntiles * a.S;
+  const int64_t gw = (int64_t)blockIdx.x * CS_WARPS + warp;
+  const int64_t nwarps = (int64_t)gridDim.x * CS_WARPS;
+  const int64_t item_lo = nitems * gw / nwarps, item_hi = nitems * (gw + 1) / nwarps;  // balanced split
+  const int nst = a.nst;
+  const int total = item_lo < item_hi ? (int)(item_hi - item_lo) * nst : 0;
+
+  // copy role: lanes 0..15 fetch row `lane` of the tile. The copy cursor (tile, slice, stage,
+  // slot) runs CS_NST stages ahead of the math and advances without divisions.
+  const int S = a.S;
+  const int tile_lo = (int)(item_lo / S), sl_lo = (int)(item_lo - (int64_t)tile_lo * S);
+  int c_left = total, c_tile = tile_lo, c_sl = sl_lo, c_st = 0, c_slot = 0;
+  const int64_t last_row = a.N - 1;
+  auto issue = [&]() {
+    if (c_left <= 0) return;
+    c_left--;
+    if (lane == 0) mbar_expect_tx(bars + c_slot, 16 * CS_ROWB);
+    __syncwarp();
+    if (lane < 16) {
+      int64_t row = (int64_t)c_tile * 16 + lane;
+      if (row > last_row) row = last_row;
+      const uint8_t* src = a.data + row * a.rb + (int64_t)(c_sl * nst + c_st) * CS_ROWB;
+      bulk_g2s(ring + c_slot * CS_STAGE + lane * CS_PITCH, src, CS_ROWB, bars + c_slot);
+    }
+    if (++c_slot == CS_NST) c_slot = 0;
+    if (++c_st == nst) {
+      c_st = 0;
+      if (++c_sl == S) c_sl = 0, c_tile++;
+    }
+  };
+#pragma unroll
+  for (int q = 0; q < CS_NST; q++) issue();
+
+  // while the first stages are in flight: arrange the activation row in shared memory
+  const float out_scale = cs_stage_x(a.x, a.x_bf16, a.K, reinterpret_cast<uint2*>(xq), sx8, red);
+  if (blockIdx.x == 0 && threadIdx.x == 0) a.misc[0] = out_scale;
+  __syncthreads();
+  if (total == 0) return;
+  // only the lanes with g >> 1 == t feed non-zero B columns (hi for even g, lo for odd g)
+  const bool active = (g >> 1) == t;
+  float acc0 = 0.f, acc1 = 0.f;
+  int tile = tile_lo, sl = sl_lo, slot = 0;
+  unsigned parity = 0;
+  for (int64_t item = item_lo; item < item_hi; item++) {
+    for (int st = 0; st < nst; st++) {
+      if (!mbar_wait_bounded_sleepy(bars + slot, parity, CS_SPINS, &s_abort, 2000u)) {
+        if (!s_abort) {
+          s_abort = 1;
+          atomicExch(a.error, 1);
+        }
+        return;  // warp-uniform: every lane polls the same barrier
+      }
+      const uint8_t* base = ring + slot * CS_STAGE;
+      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(base + g * CS_PITCH) + 9 * t;
+      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(base + (g + 8) * CS_PITCH) + 9 * t;
+#pragma unroll
+      for (int pr = 0; pr < CS_PAIRS; pr++) {
+      const int U0 = ((sl * nst + st) * CS_PAIRS + pr) * 2;  // first 256-element unit of this pair
+      // the pair goes to registers first; after the last pair the slot can be refilled before the math
+      uint32_t w0[2][9], w1[2][9];
+#pragma unroll
+      for (int u = 0; u < 2; u++)
+#pragma unroll
+        for (int i = 0; i < 9; i++) {
+          w0[u][i] = r0[pr * 72 + u * 36 + i];
+          w1[u][i] = r1[pr * 72 + u * 36 + i];
+        }
+      if (pr == CS_PAIRS - 1) {
+        __syncwarp();
+        issue();
+        if (++slot == CS_NST) slot = 0, parity ^= 1u;
+      }
+      // four independent groups (unit u, parity e), their mma steps interleaved so that
+      // consecutive tensor instructions never depend on each other
+      const uint4* bp = xq + (size_t)U0 * 64 + g;   // group gi, word i: + gi * 32 + i * 8
+      const float* sxp = sx8 + U0 * 8 + 2 * t;
+      float c[4][4];
+#pragma unroll
+      for (int gi = 0; gi < 4; gi++) c[gi][0] = c[gi][1] = c[gi][2] = c[gi][3] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        uint32_t q0[4], q1[4];
+        uint4 bf[4];
+#pragma unroll
+        for (int gi = 0; gi < 4; gi++) {
+          const int u = gi >> 1;
+          if (gi & 1) {  // odd block: words 5..8
+            q0[gi] = w0[u][5 + i];
+            q1[gi] = w1[u][5 + i];
+          } else {       // even block: quants start 2 bytes into word 0
+            q0[gi] = __funnelshift_r(w0[u][i], w0[u][i + 1], 16);
+            q1[gi] = __funnelshift_r(w1[u][i], w1[u][i + 1], 16);
+          }
+          bf[gi] = active ? bp[gi * 32 + i * 8] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int gi = 0; gi < 4; gi++)
+          mma_f16_16816(c[gi], q0[gi] & 0x000F000Fu, q1[gi] & 0x000F000Fu, q0[gi] & 0x00F000F0u,
+                        q1[gi] & 0x00F000F0u, bf[gi].x, bf[gi].y);
+#pragma unroll
+        for (int gi = 0; gi < 4; gi++) {
+          const uint32_t s0 = q0[gi] >> 8, s1 = q1[gi] >> 8;
+          mma_f16_16816(c[gi], s0 & 0x000F000Fu, s1 & 0x000F000Fu, s0 & 0x00F000F0u, s1 & 0x00F000F0u,
+                        bf[gi].z, bf[gi].w);
+        }
+      }
+#pragma unroll
+      for (int gi = 0; gi < 4; gi++) {
+        const int u = gi >> 1;
+        const float sx = sxp[u * 8 + (gi & 1)];
+        const __half2 h0 = *reinterpret_cast<const __half2*>(&w0[u][(gi & 1) ? 4 : 0]);
+        const __half2 h1 = *reinterpret_cast<const __half2*>(&w1[u][(gi & 1) ? 4 : 0]);
+        const float d0 = (gi & 1) ? __high2float(h0) : __low2float(h0);
+        const float d1 = (gi & 1) ? __high2float(h1) : __low2float(h1);
+        acc0 = fmaf(d0, (c[gi][0] + c[gi][1]) - sx, acc0);
+        acc1 = fmaf(d1, (c[gi][2] + c[gi][3]) - sx, acc1);
+      }
+      }
+    }
+    // the four quarters of a row hold disjoint blocks: add them in a fixed order
+    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+    if (t == 0) {
+      const int64_t row0 = (int64_t)tile * 16 + g, row1 = row0 + 8;
+      if (a.S == 1) {
+        if (row0 < a.N) a.y[row0] = acc0 * out_scale + (a.residual ? a.residual[row0] : 0.f);
+        if (row1 < a.N) a.y[row1] = acc1 * out_scale + (a.residual ? a.residual[row1] : 0.f);
+      } else {
+        if (row0 < a.N) a.partial[(int64_t)sl * a.N + row0] = acc0;
+        if (row1 < a.N) a.partial[(int64_t)sl * a.N + row1] = acc1;
+      }
+    }
+    acc0 = acc1 = 0.f;
+    if (++sl == S) sl = 0, tile++;
+  }
+}
+
+// partial sums over the K-slices, fixed order
+__global__ void __launch_bounds__(256)
+cs_reduce_kernel(const float* __restrict__ partial, int S, int64_t N, const float* __restrict__ misc,
+                 float* y, const float* residual) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= N) return;
+  float v = 0.f;
+  for (int j = 0; j < S; j++) v += partial[(int64_t)j * N + i];
+  v *= misc[0];
+  if (residual) v += residual[i];
+  y[i] = v;
+}
+
+struct CsPlan {
+  int S, nst, ntiles, grid;
+  size_t smem, off_err, off_part, bytes;
+};
+
+size_t cs_smem_bytes(int K) { return (size_t)CS_RING_BYTES + (size_t)(K >> 8) * 1024 + (size_t)(K >> 5) * 4 + 128; }
+
+bool cs_shape_ok(const WRef& w, int M) {
+  return M == 1 && w.enc == E_Q4_0 && w.rows >= 1 && w.cols >= CS_KSTAGE && w.cols % CS_KSTAGE == 0 &&
+         cs_smem_bytes((int)w.cols) <= (size_t)CS_MAX_SMEM && (reinterpret_cast<uintptr_t>(w.data) & 15) == 0;
+}
+
+void cs_plan(const WRef& w, CsPlan* p) {
+  const int K = (int)w.cols, stages = K / CS_KSTAGE;
+  p->ntiles = (int)((w.rows + 15) / 16);
+  const int64_t warps = 148 * CS_WARPS;
+  // split K while there are fewer than ~8 items per warp and slices keep >= 1 stage
+  int S = 1;
+  for (int cand = 1; cand <= stages; cand++) {
+    if (stages % cand) continue;
+    S = cand;
+    if ((int64_t)p->ntiles * cand >= 8 * warps) break;
+  }
+  p->S = S;
+  p->nst = stages / S;
+  const int64_t items = (int64_t)p->ntiles * S;
+  p->grid = (int)std::min<int64_t>(148, (items + CS_WARPS - 1) / CS_WARPS);
+  p->smem = cs_smem_bytes(K);
+  p->off_err = 0;       // [0] error word, [64] 2^24 / scale
+  p->off_part = 256;
+  p->bytes = 256 + (S > 1 ? (size_t)S * w.rows * 4 : 0);
+}
+
+}  // namespace
+
+size_t gemv_cs_workspace_bytes(const WRef& w, int M) {
+  if (!cs_shape_ok(w, M)) return 0;
+  CsPlan p;
+  cs_plan(w, &p);
+  return p.bytes;
+}
+
+// Column-split GEMV for one activation row (f32 or bf16). *handled = false when the shape does
+// not qualify; the caller then uses another kernel. `ws` must hold gemv_cs_workspace_bytes.
+int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, const float* residual,
+                   uint8_t* ws, cudaStream_t s, bool* handled) {
+  *handled = false;
+  if (!cs_shape_ok(w, M)) return 0;
+  CsPlan p;
+  cs_plan(w, &p);
+  CsArgs a;
+  a.data = w.data, a.N = w.rows, a.rb = w.row_bytes(), a.K = (int)w.cols;
+  a.S = p.S, a.nst = p.nst, a.ntiles = p.ntiles;
+  a.x = x, a.x_bf16 = x_type == E_BF16 ? 1 : 0;
+  a.error = reinterpret_cast<int*>(ws + p.off_err);
+  a.misc = reinterpret_cast<float*>(ws + p.off_err + 64);
+  a.partial = reinterpret_cast<float*>(ws + p.off_part);
+  a.y = y, a.residual = residual;
+  static bool attr_done = false;
+  if (!attr_done) {
+    DYN_CUDA(cudaFuncSetAttribute(gemv_cs_q4_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CS_MAX_SMEM));
+    attr_done = true;
+  }
+  gemv_cs_q4_0_kernel<<<p.grid, CS_WARPS * 32, p.smem, s>>>(a);
+  count_launch(1);
+  if (p.S > 1) {
+    cs_reduce_kernel<<<(unsigned)((w.rows + 255) / 256), 256, 0, s>>>(a.partial, p.S, w.rows, a.misc, y, residual);
+    count_launch();
+  }
+  DYN_CUDA(cudaGetLastError());
+  *handled = true;
+  return 0;
+}
+
+}  // namespace dyn

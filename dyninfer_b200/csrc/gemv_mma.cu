@@ -391,6 +391,7 @@ bool shape_ok(const WRef& w, int x_type, int M) {
 
 // Scratch bytes the product needs (0 when the shape does not qualify for this kernel).
 size_t gemv_mma_workspace_bytes(const WRef& w, int x_type, int M) {
+  if (const size_t cs = gemv_cs_workspace_bytes(w, M)) return cs;
   if (!shape_ok(w, x_type, M)) return 0;
   Shape sh;
   plan_shape(w, M, x_type == E_BF16, &sh);
@@ -403,9 +404,13 @@ size_t gemv_mma_workspace_bytes(const WRef& w, int x_type, int M) {
 int launch_gemv_mma(const WRef& w, const void* x, int x_type, int M, float* y, const float* residual,
                     void* workspace, cudaStream_t s, bool* handled) {
   *handled = false;
-  if (!shape_ok(w, x_type, M)) return 0;
+  const size_t cs_bytes = gemv_cs_workspace_bytes(w, M);  // one row, Q4_0: column-split kernel
+  if (!cs_bytes && !shape_ok(w, x_type, M)) return 0;
   Shape sh;
-  plan_shape(w, M, x_type == E_BF16, &sh);
+  if (cs_bytes)
+    sh.bytes = cs_bytes;
+  else
+    plan_shape(w, M, x_type == E_BF16, &sh);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
   if (!ws) {
     // keep freed scratch cached in the device's default pool: without this every call pays
@@ -423,6 +428,11 @@ int launch_gemv_mma(const WRef& w, const void* x, int x_type, int M, float* y, c
     DYN_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&ws), sh.bytes, s));
   }
   int rc = 1;
+  if (cs_bytes) {
+    bool did = false;
+    rc = launch_gemv_cs(w, x, x_type, M, y, residual, ws, s, &did);
+    if (!rc && !did) rc = 1;
+  } else
   switch (w.enc) {
     case E_Q4_0: rc = run_gemv_enc<E_Q4_0>(w, x, x_type, M, y, residual, sh, ws, s); break;
     case E_Q4_1: rc = run_gemv_enc<E_Q4_1>(w, x, x_type, M, y, residual, sh, ws, s); break;

@@ -43,6 +43,24 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
   }
   return false;
 }
+// Same, but each poll may sleep up to `hint_ns` inside the instruction (it still returns as soon
+// as the phase completes), so that a waiting warp does not compete for issue slots.
+__device__ __forceinline__ bool mbar_wait_bounded_sleepy(uint64_t* bar, unsigned parity, long long spins,
+                                                         volatile int* abort, unsigned hint_ns) {
+  for (long long it = 0; it < spins; it++) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    if (ok) return true;
+    if (*abort) return false;
+  }
+  return false;
+}
 // 1-D bulk copy global -> this CTA's shared memory; completion is counted on `bar` in bytes.
 // Both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {

@@ -101,6 +101,26 @@ def test_linear_ragged_and_full_shapes(native_lib, oracle, enc, n, k):
     assert helpers.rel_err(got, oracle.linear(ow, x, fast=True)) < 1e-4
 
 
+@pytest.mark.parametrize("n,k", [(33, 512), (1000, 3072), (4096, 12288), (12288, 4096)])
+def test_linear_single_row_q4_0(native_lib, oracle, n, k):
+    """One activation row on Q4_0 (the decode shape): ragged last tile, split-K shapes, f32 and
+    bf16 activations, against the oracle's sequential and pairwise sums."""
+    from dyninfer_b200 import ops
+    dw, ow = make_pair(oracle, "gguf.q4_0", n, k, seed=n ^ k)
+    x = np.random.default_rng(k).normal(size=(1, k)).astype(np.float32)
+    want = oracle.linear(ow, x, fast=True)
+    got = ops.linear(dw, torch.from_numpy(x).cuda()).cpu().numpy()
+    assert helpers.rel_err(got, want) < 2e-5
+    xb = torch.from_numpy(x).to(torch.bfloat16)
+    got = ops.linear(dw, xb.cuda()).cpu().numpy()
+    assert helpers.rel_err(got, oracle.linear(ow, xb.float().numpy(), fast=True)) < 2e-5
+    x[0, ::7] = 0.0                                    # zeros and a huge dynamic range in one row
+    x[0, 5] = 3.0e4
+    x[0, 6] = 1.0e-6
+    got = ops.linear(dw, torch.from_numpy(x).cuda()).cpu().numpy()
+    assert helpers.rel_err(got, oracle.linear(ow, x, fast=True)) < 2e-5
+
+
 def test_linear_linearity_full_size_lm_head(native_lib, oracle):
     """Size-independent property at the lm_head's full size (151936 x 1024, Q6_K):
     W(a*x + y) == a*W(x) + W(y), and sampled rows against the oracle."""

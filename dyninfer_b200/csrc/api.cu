@@ -29,6 +29,22 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
   return 1;
 }
 
+// Scratch taken from the stream-ordered allocator is returned right after use; without a release
+// threshold the default pool trims to zero at every synchronisation and the next call pays a full
+// device allocation. Once per thread and device.
+int keep_scratch_pool_cached() {
+  static thread_local int tuned_device = -1;
+  int dev = 0;
+  DYN_CUDA(cudaGetDevice(&dev));
+  if (tuned_device == dev) return 0;
+  cudaMemPool_t pool;
+  DYN_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+  uint64_t keep = ~0ull;
+  DYN_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+  tuned_device = dev;
+  return 0;
+}
+
 void count_launch(int n) { *g_counter += (uint64_t)n; }
 uint64_t* launch_counter_slot() { return g_counter; }
 void set_launch_counter(uint64_t* p) { g_counter = p ? p : &g_default_counter; }

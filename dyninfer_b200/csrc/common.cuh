@@ -28,6 +28,8 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
     }                              \
   } while (0)
 
+int keep_scratch_pool_cached();  // raise the default memory pool's release threshold (idempotent)
+
 // Counts kernels launched by this library (per thread-attached counter).
 void count_launch(int n = 1);
 uint64_t* launch_counter_slot();  // where count_launch accumulates (thread-local pointer)
@@ -142,6 +144,8 @@ int launch_gather(const WRef& w, const int64_t* tokens, int64_t count, float* ou
 int launch_linear(const WRef& w, const void* x, int x_type, int64_t m, float* y,
                   const float* residual, cudaStream_t s);
 // Tensor-core GEMV for few activation rows (gemv_mma.cu); *handled tells whether it ran.
+int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float* y, const float* residual,
+                     cudaStream_t s, bool* handled);
 size_t gemv_cs_workspace_bytes(const WRef& w, int M);
 int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, const float* residual,
                    uint8_t* ws, cudaStream_t s, bool* handled);

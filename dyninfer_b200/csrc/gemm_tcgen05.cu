@@ -1,0 +1,461 @@
+// Dequant-in-shared-memory GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) for prefill
+// and every product with many activation rows: y[m, n] = sum_k x[m, k] * w[n, k], f32 accumulate.
+//
+// One CTA computes a 128 (weight rows) x BN (activation rows, <= 256) tile of y^T:
+//   * warps 0..7 dequantise: for every 64-wide K chunk they decode the raw checkpoint blocks of
+//     the tile's 128 rows with the exact decoders of codec.cuh (lanes along K, so a row's bytes
+//     are read contiguously), round to f16 and store them as the A operand in the canonical
+//     K-major 128-byte-swizzled layout (8-row groups of 1024 bytes, 16-byte chunk c of row r at
+//     position c ^ (r & 7));
+//   * one thread of warp 8 fetches the matching activation chunk (f16, prepared once per call) as the
+//     B operand with a 2-D TMA tile copy (cp.async.bulk.tensor, hardware 128-byte swizzle);
+//   * one thread of warp 9 issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16, four per
+//     chunk) with the accumulator in tensor memory, and releases each stage with tcgen05.commit;
+//   * warps 0..3 read the accumulator back with tcgen05.ld (lane = weight row) and write y with
+//     coalesced stores.
+// Stages hand over through mbarriers; every wait is bounded and reports through an error word, and
+// the tensor memory is always released before the CTA exits.
+//
+// Precision: weights enter as f16(exact dequantised value) (relative rounding 2^-12), activations
+// as f16 (bf16 inputs of ordinary magnitude convert exactly), products accumulate in f32.
+#include <cuda.h>
+
+#include <algorithm>
+
+#include "codec.cuh"
+#include "ring.cuh"
+
+namespace dyn {
+
+namespace {
+
+constexpr int TG_BM = 128;          // weight rows per CTA (MMA M)
+constexpr int TG_BK = 64;           // K elements per stage: 128 bytes of f16 per row
+constexpr int TG_A_WARPS = 8, TG_B_WARPS = 1;
+constexpr int TG_THREADS = (TG_A_WARPS + TG_B_WARPS + 1) * 32;
+constexpr int TG_STAGES = 3;
+constexpr int TG_A_BYTES = TG_BM * 128;
+constexpr long long TG_SPINS = 1LL << 24;
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// K-major, 128-byte swizzle: start >> 4, LBO = 1 (unused for swizzled K-major), SBO = 1024 bytes
+// between 8-row groups, descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3fff) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// kind::f16: D = f32, A = B = f16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// ---- activations -> f16 [Mpad, K] (rows >= M are zero) ------------------------------------------
+// Every row is scaled by a power of two that puts its largest magnitude in [2^12, 2^13), so the
+// conversion can neither overflow nor push ordinary entries into the f16 subnormals; inv_s[m]
+// undoes the scale in the epilogue (exact). One block per row.
+__global__ void __launch_bounds__(256)
+tg_prepare_x_kernel(const void* __restrict__ x, int x_bf16, int64_t M, int64_t K, __half* xh, float* inv_s) {
+  __shared__ float red[8];
+  const int64_t m = blockIdx.x;
+  const int tid = threadIdx.x;
+  __half* dst = xh + m * K;
+  if (m >= M) {
+    for (int64_t i = tid * 8; i < K; i += 256 * 8) *reinterpret_cast<uint4*>(dst + i) = make_uint4(0, 0, 0, 0);
+    if (tid == 0) inv_s[m] = 0.f;
+    return;
+  }
+  auto ld = [&](int64_t i) -> float {
+    return x_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(x)[m * K + i])
+                  : reinterpret_cast<const float*>(x)[m * K + i];
+  };
+  float mx = 0.f;
+  for (int64_t i = tid; i < K; i += 256) mx = fmaxf(mx, fabsf(ld(i)));
+  mx = warp_max(mx);
+  if ((tid & 31) == 0) red[tid >> 5] = mx;
+  __syncthreads();
+  mx = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) mx = fmaxf(mx, red[i]);
+  int e = 0;
+  if (mx > 0.f && mx < 3.0e38f) frexpf(mx, &e);
+  const float sc = ldexpf(1.0f, 13 - e);
+  if (tid == 0) inv_s[m] = ldexpf(1.0f, e - 13);
+  for (int64_t i = tid * 2; i < K; i += 512) {
+    const __half2 h = __floats2half2_rn(ld(i) * sc, ld(i + 1) * sc);
+    *reinterpret_cast<__half2*>(dst + i) = h;
+  }
+}
+
+struct TgArgs {
+  WRef w;
+  const __half* xh;  // [Mpad, K]
+  const float* inv_s; // [Mpad]
+  int64_t M;
+  int bn;            // activation rows per CTA (multiple of 16, <= 256)
+  int tmem_cols;     // power of two >= bn, >= 32
+  float* y;          // [M, N]
+  const float* residual;
+  int* error;
+};
+
+// Items of one row in a K chunk: every item is one decoder part; its groups that fall inside the
+// chunk are stored.
+template <int ENC>
+struct ChunkItems {
+  using C = Codec<ENC>;
+  static constexpr int IPR = C::BLOCK <= TG_BK ? (TG_BK / C::BLOCK) * C::PARTS : 8;  // Q6_K: 8 parts per quarter
+  __device__ static __forceinline__ void locate(int64_t k0, int it, int64_t* blk, int* part) {
+    if (C::BLOCK <= TG_BK) {
+      *blk = k0 / C::BLOCK + it / C::PARTS;
+      *part = it % C::PARTS;
+    } else {
+      *blk = k0 / C::BLOCK;
+      *part = (int)((k0 % C::BLOCK) / 128) * 8 + it;
+    }
+  }
+};
+
+template <int ENC>
+__global__ void __launch_bounds__(TG_THREADS, 1)
+dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
+  extern __shared__ __align__(1024) uint8_t tg_smem[];
+  __shared__ uint64_t full_bar[TG_STAGES], empty_bar[TG_STAGES], accum_bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort;
+  using C = Codec<ENC>;
+  using CI = ChunkItems<ENC>;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int bn = a.bn;
+  const int64_t N = a.w.rows, K = a.w.cols;
+  const int64_t n0 = (int64_t)blockIdx.x * TG_BM, m0 = (int64_t)blockIdx.y * bn;
+  const int nk = (int)(K / TG_BK);
+  const uint32_t stage_bytes = TG_A_BYTES + (uint32_t)bn * 128;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tg_smem) + 1023) & ~uintptr_t(1023));
+
+  if (tid == 0) {
+    s_abort = 0;
+    for (int i = 0; i < TG_STAGES; i++) {
+      mbar_init(full_bar + i, TG_A_WARPS + TG_B_WARPS);
+      mbar_init(empty_bar + i, 1);
+    }
+    mbar_init(&accum_bar, 1);
+    mbar_fence_init();
+  }
+  if (warp == TG_A_WARPS + TG_B_WARPS) {  // the MMA warp owns the tensor memory allocation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                 "r"((uint32_t)a.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = tmem_base_s;
+
+  if (warp < TG_A_WARPS) {
+    // ---------------- A producers: dequantise 128 rows x 64 k per stage --------------------------
+    if constexpr (ENC == E_Q4_0) {
+      // Fast path. Lane = (row sub-index, block of the chunk, quarter t): 4 quant bytes + the block
+      // scale -> 8 weights. The raw bytes of the next chunk are fetched before the current one is
+      // converted, so the global-memory latency is paid once, not once per chunk.
+      // (q - 8) * d in f16: nibble | 0x6400 = 1024 + q (low) or 1024 + 16 q (high, used in place);
+      // subtracting 1032, or multiplying by 1/16 and subtracting 72, is exact; the product with d
+      // rounds once, exactly like rounding the f32 value.
+      const int blk2 = (lane >> 2) & 1, t = lane & 3, rsub = lane >> 3;
+      const int64_t rb = a.w.row_bytes();
+      const uint8_t* rowp[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        int64_t row = n0 + warp * 4 + rsub + 32 * j;
+        if (row > N - 1) row = N - 1;
+        rowp[j] = a.w.data + row * rb + blk2 * 18;
+      }
+      uint32_t q_cur[4], q_nxt[4], d_cur[4], d_nxt[4];
+      auto fetch = [&](int kc, uint32_t (&q)[4], uint32_t (&d)[4]) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const uint8_t* p = rowp[j] + (int64_t)kc * 36;
+          d[j] = ld_u16(p);
+          q[j] = ld_u16(p + 2 + 4 * t) | (ld_u16(p + 4 + 4 * t) << 16);
+        }
+      };
+      fetch(0, q_cur, d_cur);
+      const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f), c72 = __floats2half2_rn(72.f, 72.f);
+      const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
+      for (int kc = 0; kc < nk; kc++) {
+        const int slot = kc % TG_STAGES;
+        if (kc + 1 < nk) fetch(kc + 1, q_nxt, d_nxt);
+        if (kc >= TG_STAGES &&
+            !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / TG_STAGES - 1) & 1u, TG_SPINS, &s_abort)) {
+          if (!s_abort) s_abort = 1;
+          break;
+        }
+        uint8_t* abase = smem + (size_t)slot * stage_bytes;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const int r = warp * 4 + rsub + 32 * j;
+          const uint32_t w = q_cur[j];
+          const __half dh = __ushort_as_half((unsigned short)d_cur[j]);
+          const __half2 d2 = __halves2half2(dh, dh);
+          uint32_t l02 = (w & 0x000F000Fu) | 0x64006400u, l13 = ((w >> 8) & 0x000F000Fu) | 0x64006400u;
+          uint32_t h02 = (w & 0x00F000F0u) | 0x64006400u, h13 = ((w >> 8) & 0x00F000F0u) | 0x64006400u;
+          __half2 v;
+          v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l02), c1032), d2);
+          l02 = *reinterpret_cast<uint32_t*>(&v);
+          v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l13), c1032), d2);
+          l13 = *reinterpret_cast<uint32_t*>(&v);
+          v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h02), c16th), c72), d2);
+          h02 = *reinterpret_cast<uint32_t*>(&v);
+          v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h13), c16th), c72), d2);
+          h13 = *reinterpret_cast<uint32_t*>(&v);
+          // elements 4t..4t+3 (low nibbles) and 16+4t..16+4t+3 (high nibbles) of block blk2
+          const uint2 lo = make_uint2(__byte_perm(l02, l13, 0x5410), __byte_perm(l02, l13, 0x7632));
+          const uint2 hi = make_uint2(__byte_perm(h02, h13, 0x5410), __byte_perm(h02, h13, 0x7632));
+          const int klo = blk2 * 32 + 4 * t, khi = klo + 16;
+          uint8_t* rowbase = abase + r * 128;
+          *reinterpret_cast<uint2*>(rowbase + (((klo >> 3) ^ (r & 7)) << 4) + (klo & 7) * 2) = lo;
+          *reinterpret_cast<uint2*>(rowbase + (((khi >> 3) ^ (r & 7)) << 4) + (khi & 7) * 2) = hi;
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar + slot);
+#pragma unroll
+        for (int j = 0; j < 4; j++) q_cur[j] = q_nxt[j], d_cur[j] = d_nxt[j];
+      }
+    } else {
+    constexpr int RPP = 32 / CI::IPR;  // rows per warp pass
+    const int it = lane % CI::IPR, rsub = lane / CI::IPR;
+    for (int kc = 0; kc < nk; kc++) {
+      const int slot = kc % TG_STAGES;
+      if (kc >= TG_STAGES &&
+          !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / TG_STAGES - 1) & 1u, TG_SPINS, &s_abort)) {
+        if (!s_abort) s_abort = 1;
+        break;
+      }
+      uint8_t* abase = smem + (size_t)slot * stage_bytes;
+      const int64_t k0 = (int64_t)kc * TG_BK;
+      int64_t blk;
+      int part;
+      CI::locate(k0, it, &blk, &part);
+      for (int r = warp * RPP + rsub; r < TG_BM; r += TG_A_WARPS * RPP) {
+        int64_t row = n0 + r;
+        if (row > N - 1) row = N - 1;
+        const RowPtr rp = row_ptr(a.w, row);
+        float wv[4 * C::G];
+        C::decode(rp, blk, part, wv);
+#pragma unroll
+        for (int g = 0; g < C::G; g++) {
+          const int koff = (int)(blk * C::BLOCK + C::xoff(part, g) - k0);
+          if (koff >= 0 && koff < TG_BK) {
+            const __half2 h0 = __floats2half2_rn(wv[4 * g], wv[4 * g + 1]);
+            const __half2 h1 = __floats2half2_rn(wv[4 * g + 2], wv[4 * g + 3]);
+            const int c = koff >> 3;
+            uint8_t* dst = abase + r * 128 + ((c ^ (r & 7)) << 4) + (koff & 7) * 2;
+            *reinterpret_cast<uint2*>(dst) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+          }
+        }
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_bar + slot);
+    }
+    }
+  } else if (warp < TG_A_WARPS + TG_B_WARPS) {
+    // ---------------- B producer: one TMA tile (bn rows x 64 k, swizzled by the hardware) per stage -----
+    if (lane == 0) {
+      for (int kc = 0; kc < nk; kc++) {
+        const int slot = kc % TG_STAGES;
+        if (kc >= TG_STAGES &&
+            !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / TG_STAGES - 1) & 1u, TG_SPINS, &s_abort)) {
+          if (!s_abort) s_abort = 1;
+          break;
+        }
+        mbar_expect_tx(full_bar + slot, (unsigned)bn * 128u);
+        tma_load_2d(smem + (size_t)slot * stage_bytes + TG_A_BYTES, &xmap, kc * TG_BK, (int)m0, full_bar + slot);
+      }
+    }
+  } else {
+    // ---------------- MMA issue: one thread ---------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(bn);
+      bool ok = true;
+      for (int kc = 0; kc < nk && ok; kc++) {
+        const int slot = kc % TG_STAGES;
+        ok = mbar_wait_bounded(full_bar + slot, (unsigned)(kc / TG_STAGES) & 1u, TG_SPINS, &s_abort);
+        if (!ok) {
+          if (!s_abort) s_abort = 2;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t aaddr = smem_u32(smem + (size_t)slot * stage_bytes);
+        const uint32_t baddr = aaddr + TG_A_BYTES;
+#pragma unroll
+        for (int k4 = 0; k4 < TG_BK / 16; k4++)
+          umma_f16(tmem_d, umma_desc(aaddr + k4 * 32), umma_desc(baddr + k4 * 32), idesc, (kc | k4) ? 1u : 0u);
+        umma_commit(empty_bar + slot);  // frees the stage once these MMAs have read it
+      }
+      umma_commit(&accum_bar);  // accumulator complete (also reached after a failed wait)
+    }
+  }
+
+  // ---------------- epilogue: warps 0..3, TMEM lane = weight row ------------------------------------
+  if (warp < 4) {
+    const bool ok = mbar_wait_bounded(&accum_bar, 0, TG_SPINS, &s_abort);
+    if (!ok && !s_abort) s_abort = 3;
+    tc_fence_after();
+    if (ok && !s_abort) {
+      const int64_t n = n0 + warp * 32 + lane;
+      for (int j0 = 0; j0 < bn; j0 += 8) {
+        uint32_t v[8];
+        const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)j0;
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                     : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const int64_t m = m0 + j0 + j;
+          if (m < a.M && n < N) {
+            float o = __uint_as_float(v[j]) * __ldg(a.inv_s + m);
+            if (a.residual) o += a.residual[m * N + n];
+            a.y[m * N + n] = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == TG_A_WARPS + TG_B_WARPS) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)a.tmem_cols)
+                 : "memory");
+  }
+  if (tid == 0 && s_abort) atomicExch(a.error, s_abort);
+}
+
+bool tg_shape_ok(const WRef& w, int64_t M) {
+  switch (w.enc) {
+    case E_Q4_0:
+    case E_Q4_1:
+    case E_Q8_0:
+    case E_MLX_U4: break;
+    case E_Q6_K: break;
+    default: return false;
+  }
+  if (w.enc == E_MLX_U4 && (w.group < 8 || w.cols % w.group)) return false;
+  return M >= 1 && w.rows >= 1 && w.cols >= TG_BK && w.cols % (w.enc == E_Q6_K ? 256 : TG_BK) == 0;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 2-D map over the f16 activations [rows, K]: boxes of 64 k x bn rows, 128-byte swizzle.
+int tg_make_xmap(__half* xh, int64_t rows, int64_t K, int bn, CUtensorMap* map) {
+  static EncodeTiledFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    DYN_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    DYN_CHECK(fn != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available");
+    encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)TG_BK, (cuuint32_t)bn};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  DYN_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
+template <int ENC>
+int tg_launch(const TgArgs& a, const CUtensorMap& xmap, dim3 grid, size_t smem, cudaStream_t s) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    DYN_CUDA(cudaFuncSetAttribute(dqgemm_tc_kernel<ENC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_done = true;
+  }
+  dqgemm_tc_kernel<ENC><<<grid, TG_THREADS, smem, s>>>(a, xmap);
+  return 0;
+}
+
+}  // namespace
+
+// Tensor-core dequant GEMM. *handled = false when the encoding or shape does not qualify.
+int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float* y, const float* residual,
+                     cudaStream_t s, bool* handled) {
+  *handled = false;
+  if (!tg_shape_ok(w, M)) return 0;
+  const int64_t K = w.cols;
+  // activation rows per CTA: as many as fit one accumulator (256), rounded up to the MMA granule
+  const int64_t mtiles = (M + 255) / 256;
+  int bn = (int)((M + mtiles - 1) / mtiles);
+  bn = (bn + 15) / 16 * 16;
+  const int64_t Mpad = mtiles * bn;
+  int cols = 32;
+  while (cols < bn) cols *= 2;
+  if (keep_scratch_pool_cached()) return 1;
+  uint8_t* ws = nullptr;
+  const size_t xh_bytes = ((size_t)Mpad * K * 2 + 255) / 256 * 256;
+  const size_t inv_bytes = ((size_t)Mpad * 4 + 255) / 256 * 256;
+  DYN_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&ws), xh_bytes + inv_bytes + 256, s));
+  __half* xh = reinterpret_cast<__half*>(ws);
+  float* inv_s = reinterpret_cast<float*>(ws + xh_bytes);
+  int* err = reinterpret_cast<int*>(ws + xh_bytes + inv_bytes);
+  DYN_CUDA(cudaMemsetAsync(err, 0, 4, s));
+  tg_prepare_x_kernel<<<(unsigned)Mpad, 256, 0, s>>>(x, x_type == E_BF16 ? 1 : 0, M, K, xh, inv_s);
+  TgArgs a;
+  a.w = w, a.xh = xh, a.inv_s = inv_s, a.M = M, a.bn = bn, a.tmem_cols = cols, a.y = y, a.residual = residual, a.error = err;
+  CUtensorMap xmap;
+  if (tg_make_xmap(xh, Mpad, K, bn, &xmap)) {
+    cudaFreeAsync(ws, s);
+    return 1;
+  }
+  const dim3 grid((unsigned)((w.rows + TG_BM - 1) / TG_BM), (unsigned)mtiles);
+  const size_t smem = (size_t)TG_STAGES * (TG_A_BYTES + (size_t)bn * 128) + 1024;
+  int rc = 1;
+  switch (w.enc) {
+    case E_Q4_0: rc = tg_launch<E_Q4_0>(a, xmap, grid, smem, s); break;
+    case E_Q4_1: rc = tg_launch<E_Q4_1>(a, xmap, grid, smem, s); break;
+    case E_Q8_0: rc = tg_launch<E_Q8_0>(a, xmap, grid, smem, s); break;
+    case E_Q6_K: rc = tg_launch<E_Q6_K>(a, xmap, grid, smem, s); break;
+    case E_MLX_U4: rc = tg_launch<E_MLX_U4>(a, xmap, grid, smem, s); break;
+    default: break;
+  }
+  count_launch(2);
+  cudaError_t e = cudaGetLastError();
+  cudaError_t e2 = cudaFreeAsync(ws, s);
+  if (rc) return rc;
+  if (e != cudaSuccess) return cuda_fail(e, "dqgemm_tc launch", __FILE__, __LINE__);
+  if (e2 != cudaSuccess) return cuda_fail(e2, "cudaFreeAsync", __FILE__, __LINE__);
+  *handled = true;
+  return 0;
+}
+
+}  // namespace dyn

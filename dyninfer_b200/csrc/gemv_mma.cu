@@ -413,18 +413,7 @@ int launch_gemv_mma(const WRef& w, const void* x, int x_type, int M, float* y, c
     plan_shape(w, M, x_type == E_BF16, &sh);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
   if (!ws) {
-    // keep freed scratch cached in the device's default pool: without this every call pays
-    // a full allocation (the pool otherwise trims to zero at each synchronisation)
-    static thread_local int tuned_device = -1;
-    int dev = 0;
-    DYN_CUDA(cudaGetDevice(&dev));
-    if (tuned_device != dev) {
-      cudaMemPool_t pool;
-      DYN_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
-      uint64_t keep = ~0ull;
-      DYN_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
-      tuned_device = dev;
-    }
+    if (keep_scratch_pool_cached()) return 1;
     DYN_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&ws), sh.bytes, s));
   }
   int rc = 1;

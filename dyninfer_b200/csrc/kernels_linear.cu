@@ -123,6 +123,11 @@ int launch_linear(const WRef& w, const void* x, int x_type, int64_t m, float* y,
   DYN_CHECK(x_type == E_F32 || x_type == E_BF16, "linear: x_type must be f32 or bf16, got %d",
             x_type);
   DYN_CHECK(m >= 1, "linear: m must be >= 1");
+  if (m > 16) {  // many rows: dequant-in-shared-memory tensor-core GEMM
+    bool handled = false;
+    if (launch_dqgemm_tc(w, x, x_type, m, y, residual, s, &handled)) return 1;
+    if (handled) return 0;
+  }
   {
     // few rows: tensor-core GEMV, 4 (f32) or 8 (bf16) activation rows per pass over the weights
     const int64_t step = x_type == E_BF16 ? 8 : 4;

@@ -375,7 +375,8 @@ __device__ __forceinline__ void grid_sync(const MegaArgs& a, GridBar& gb, int G,
       long long it = 0;
       do {
         asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(a.bar) : "memory");
-      } while (seen < target && ++it < MK_GRID_SPINS);
+        if (seen >= target) break;
+      } while (++it < MK_GRID_SPINS);
       if (seen < target) *sm.abort = 2;
     }
   }

@@ -2,14 +2,14 @@
 // and every product with many activation rows: y[m, n] = sum_k x[m, k] * w[n, k], f32 accumulate.
 //
 // One CTA computes a 128 (weight rows) x BN (activation rows, <= 256) tile of y^T:
-//   * warps 0..7 dequantise: for every 64-wide K chunk they decode the raw checkpoint blocks of
+//   * warps 0..15 dequantise (four groups of four, one pipeline stage each): for every 64-wide K chunk they decode the raw checkpoint blocks of
 //     the tile's 128 rows with the exact decoders of codec.cuh (lanes along K, so a row's bytes
 //     are read contiguously), round to f16 and store them as the A operand in the canonical
 //     K-major 128-byte-swizzled layout (8-row groups of 1024 bytes, 16-byte chunk c of row r at
 //     position c ^ (r & 7));
-//   * one thread of warp 8 fetches the matching activation chunk (f16, prepared once per call) as the
+//   * one thread of warp 16 fetches the matching activation chunk (f16, prepared once per call) as the
 //     B operand with a 2-D TMA tile copy (cp.async.bulk.tensor, hardware 128-byte swizzle);
-//   * one thread of warp 9 issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16, four per
+//   * one thread of warp 17 issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16, four per
 //     chunk) with the accumulator in tensor memory, and releases each stage with tcgen05.commit;
 //   * warps 0..3 read the accumulator back with tcgen05.ld (lane = weight row) and write y with
 //     coalesced stores.
@@ -31,9 +31,11 @@ namespace {
 
 constexpr int TG_BM = 128;          // weight rows per CTA (MMA M)
 constexpr int TG_BK = 64;           // K elements per stage: 128 bytes of f16 per row
-constexpr int TG_A_WARPS = 8, TG_B_WARPS = 1;
+constexpr int TG_GROUPS = 4;         // producer groups; group g fills stage g with chunks g, g + 4, ...
+constexpr int TG_GWARPS = 4;         // warps per group
+constexpr int TG_A_WARPS = TG_GROUPS * TG_GWARPS, TG_B_WARPS = 1;
 constexpr int TG_THREADS = (TG_A_WARPS + TG_B_WARPS + 1) * 32;
-constexpr int TG_STAGES = 3;
+constexpr int TG_STAGES = TG_GROUPS;
 constexpr int TG_A_BYTES = TG_BM * 128;
 constexpr long long TG_SPINS = 1LL << 24;
 
@@ -157,7 +159,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
   if (tid == 0) {
     s_abort = 0;
     for (int i = 0; i < TG_STAGES; i++) {
-      mbar_init(full_bar + i, TG_A_WARPS + TG_B_WARPS);
+      mbar_init(full_bar + i, TG_GWARPS + TG_B_WARPS);
       mbar_init(empty_bar + i, 1);
     }
     mbar_init(&accum_bar, 1);
@@ -176,112 +178,120 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
 
   if (warp < TG_A_WARPS) {
     // ---------------- A producers: dequantise 128 rows x 64 k per stage --------------------------
+    // Four groups of four warps; group g produces chunks g, g + 4, ... into stage g, so the fixed
+    // costs of a hand-over (proxy fence, barrier round trip) of up to four chunks overlap.
+    const int grp = warp / TG_GWARPS, wg = warp % TG_GWARPS;
+    uint8_t* abase = smem + (size_t)grp * stage_bytes;
     if constexpr (ENC == E_Q4_0) {
       // Fast path. Lane = (row sub-index, block of the chunk, quarter t): 4 quant bytes + the block
-      // scale -> 8 weights. The raw bytes of the next chunk are fetched before the current one is
-      // converted, so the global-memory latency is paid once, not once per chunk.
+      // scale -> 8 weights. The raw bytes of the group's next chunk are fetched before the current
+      // one is converted and stay in flight while the group waits for its stage to drain.
       // (q - 8) * d in f16: nibble | 0x6400 = 1024 + q (low) or 1024 + 16 q (high, used in place);
       // subtracting 1032, or multiplying by 1/16 and subtracting 72, is exact; the product with d
       // rounds once, exactly like rounding the f32 value.
+      constexpr int NJ = TG_BM / (TG_GWARPS * 4);  // rows per lane and chunk
       const int blk2 = (lane >> 2) & 1, t = lane & 3, rsub = lane >> 3;
       const int64_t rb = a.w.row_bytes();
-      const uint8_t* rowp[4];
+      const uint8_t* rowp[NJ];
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        int64_t row = n0 + warp * 4 + rsub + 32 * j;
+      for (int j = 0; j < NJ; j++) {
+        int64_t row = n0 + wg * 4 + rsub + 16 * j;
         if (row > N - 1) row = N - 1;
         rowp[j] = a.w.data + row * rb + blk2 * 18;
       }
-      uint32_t q_cur[4], q_nxt[4], d_cur[4], d_nxt[4];
-      auto fetch = [&](int kc, uint32_t (&q)[4], uint32_t (&d)[4]) {
+      uint32_t qa[2][NJ], qb[2][NJ], d[2][NJ];  // quant halves stay apart until use: no early dependent op
+      auto fetch = [&](int kc, uint32_t (&qlo)[NJ], uint32_t (&qhi)[NJ], uint32_t (&dd)[NJ]) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
+        for (int j = 0; j < NJ; j++) {
           const uint8_t* p = rowp[j] + (int64_t)kc * 36;
-          d[j] = ld_u16(p);
-          q[j] = ld_u16(p + 2 + 4 * t) | (ld_u16(p + 4 + 4 * t) << 16);
+          dd[j] = t == 0 ? ld_u16(p) : 0u;  // one scale load per block; the other quarters get it by shuffle
+          qlo[j] = ld_u16(p + 2 + 4 * t);
+          qhi[j] = ld_u16(p + 4 + 4 * t);
         }
       };
-      fetch(0, q_cur, d_cur);
+      if (grp < nk) fetch(grp, qa[0], qb[0], d[0]);
       const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f), c72 = __floats2half2_rn(72.f, 72.f);
       const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
-      for (int kc = 0; kc < nk; kc++) {
-        const int slot = kc % TG_STAGES;
-        if (kc + 1 < nk) fetch(kc + 1, q_nxt, d_nxt);
-        if (kc >= TG_STAGES &&
-            !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / TG_STAGES - 1) & 1u, TG_SPINS, &s_abort)) {
+      bool live = true;
+      int use = 0;  // how many times this group has filled its stage
+      for (int kc0 = grp; kc0 < nk && live; kc0 += 2 * TG_GROUPS) {
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          const int kc = kc0 + u * TG_GROUPS;
+          if (kc >= nk) break;
+          if (kc + TG_GROUPS < nk) fetch(kc + TG_GROUPS, qa[u ^ 1], qb[u ^ 1], d[u ^ 1]);
+          if (use > 0 && !mbar_wait_bounded(empty_bar + grp, (unsigned)(use - 1) & 1u, TG_SPINS, &s_abort)) {
+            if (!s_abort) s_abort = 1;
+            live = false;
+            break;
+          }
+#pragma unroll
+          for (int j = 0; j < NJ; j++) {
+            const int r = wg * 4 + rsub + 16 * j;
+            const uint32_t w = qa[u][j] | (qb[u][j] << 16);
+            const __half dh = __ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, d[u][j], lane & ~3));
+            const __half2 d2 = __halves2half2(dh, dh);
+            uint32_t l02 = (w & 0x000F000Fu) | 0x64006400u, l13 = ((w >> 8) & 0x000F000Fu) | 0x64006400u;
+            uint32_t h02 = (w & 0x00F000F0u) | 0x64006400u, h13 = ((w >> 8) & 0x00F000F0u) | 0x64006400u;
+            __half2 v;
+            v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l02), c1032), d2);
+            l02 = *reinterpret_cast<uint32_t*>(&v);
+            v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l13), c1032), d2);
+            l13 = *reinterpret_cast<uint32_t*>(&v);
+            v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h02), c16th), c72), d2);
+            h02 = *reinterpret_cast<uint32_t*>(&v);
+            v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h13), c16th), c72), d2);
+            h13 = *reinterpret_cast<uint32_t*>(&v);
+            // elements 4t..4t+3 (low nibbles) and 16+4t..16+4t+3 (high nibbles) of block blk2
+            const uint2 lo = make_uint2(__byte_perm(l02, l13, 0x5410), __byte_perm(l02, l13, 0x7632));
+            const uint2 hi = make_uint2(__byte_perm(h02, h13, 0x5410), __byte_perm(h02, h13, 0x7632));
+            const int klo = blk2 * 32 + 4 * t, khi = klo + 16;
+            uint8_t* rowbase = abase + r * 128;
+            *reinterpret_cast<uint2*>(rowbase + (((klo >> 3) ^ (r & 7)) << 4) + (klo & 7) * 2) = lo;
+            *reinterpret_cast<uint2*>(rowbase + (((khi >> 3) ^ (r & 7)) << 4) + (khi & 7) * 2) = hi;
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full_bar + grp);
+          use++;
+        }
+      }
+    } else {
+      constexpr int RPP = 32 / CI::IPR;  // rows per warp pass
+      const int it = lane % CI::IPR, rsub = lane / CI::IPR;
+      int use = 0;
+      for (int kc = grp; kc < nk; kc += TG_GROUPS, use++) {
+        if (use > 0 && !mbar_wait_bounded(empty_bar + grp, (unsigned)(use - 1) & 1u, TG_SPINS, &s_abort)) {
           if (!s_abort) s_abort = 1;
           break;
         }
-        uint8_t* abase = smem + (size_t)slot * stage_bytes;
+        const int64_t k0 = (int64_t)kc * TG_BK;
+        int64_t blk;
+        int part;
+        CI::locate(k0, it, &blk, &part);
+        for (int r = wg * RPP + rsub; r < TG_BM; r += TG_GWARPS * RPP) {
+          int64_t row = n0 + r;
+          if (row > N - 1) row = N - 1;
+          const RowPtr rp = row_ptr(a.w, row);
+          float wv[4 * C::G];
+          C::decode(rp, blk, part, wv);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-          const int r = warp * 4 + rsub + 32 * j;
-          const uint32_t w = q_cur[j];
-          const __half dh = __ushort_as_half((unsigned short)d_cur[j]);
-          const __half2 d2 = __halves2half2(dh, dh);
-          uint32_t l02 = (w & 0x000F000Fu) | 0x64006400u, l13 = ((w >> 8) & 0x000F000Fu) | 0x64006400u;
-          uint32_t h02 = (w & 0x00F000F0u) | 0x64006400u, h13 = ((w >> 8) & 0x00F000F0u) | 0x64006400u;
-          __half2 v;
-          v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l02), c1032), d2);
-          l02 = *reinterpret_cast<uint32_t*>(&v);
-          v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l13), c1032), d2);
-          l13 = *reinterpret_cast<uint32_t*>(&v);
-          v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h02), c16th), c72), d2);
-          h02 = *reinterpret_cast<uint32_t*>(&v);
-          v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h13), c16th), c72), d2);
-          h13 = *reinterpret_cast<uint32_t*>(&v);
-          // elements 4t..4t+3 (low nibbles) and 16+4t..16+4t+3 (high nibbles) of block blk2
-          const uint2 lo = make_uint2(__byte_perm(l02, l13, 0x5410), __byte_perm(l02, l13, 0x7632));
-          const uint2 hi = make_uint2(__byte_perm(h02, h13, 0x5410), __byte_perm(h02, h13, 0x7632));
-          const int klo = blk2 * 32 + 4 * t, khi = klo + 16;
-          uint8_t* rowbase = abase + r * 128;
-          *reinterpret_cast<uint2*>(rowbase + (((klo >> 3) ^ (r & 7)) << 4) + (klo & 7) * 2) = lo;
-          *reinterpret_cast<uint2*>(rowbase + (((khi >> 3) ^ (r & 7)) << 4) + (khi & 7) * 2) = hi;
+          for (int g = 0; g < C::G; g++) {
+            const int koff = (int)(blk * C::BLOCK + C::xoff(part, g) - k0);
+            if (koff >= 0 && koff < TG_BK) {
+              const __half2 h0 = __floats2half2_rn(wv[4 * g], wv[4 * g + 1]);
+              const __half2 h1 = __floats2half2_rn(wv[4 * g + 2], wv[4 * g + 3]);
+              const int c = koff >> 3;
+              uint8_t* dst = abase + r * 128 + ((c ^ (r & 7)) << 4) + (koff & 7) * 2;
+              *reinterpret_cast<uint2*>(dst) =
+                  make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+            }
+          }
         }
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(full_bar + slot);
-#pragma unroll
-        for (int j = 0; j < 4; j++) q_cur[j] = q_nxt[j], d_cur[j] = d_nxt[j];
+        if (lane == 0) mbar_arrive(full_bar + grp);
       }
-    } else {
-    constexpr int RPP = 32 / CI::IPR;  // rows per warp pass
-    const int it = lane % CI::IPR, rsub = lane / CI::IPR;
-    for (int kc = 0; kc < nk; kc++) {
-      const int slot = kc % TG_STAGES;
-      if (kc >= TG_STAGES &&
-          !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / TG_STAGES - 1) & 1u, TG_SPINS, &s_abort)) {
-        if (!s_abort) s_abort = 1;
-        break;
-      }
-      uint8_t* abase = smem + (size_t)slot * stage_bytes;
-      const int64_t k0 = (int64_t)kc * TG_BK;
-      int64_t blk;
-      int part;
-      CI::locate(k0, it, &blk, &part);
-      for (int r = warp * RPP + rsub; r < TG_BM; r += TG_A_WARPS * RPP) {
-        int64_t row = n0 + r;
-        if (row > N - 1) row = N - 1;
-        const RowPtr rp = row_ptr(a.w, row);
-        float wv[4 * C::G];
-        C::decode(rp, blk, part, wv);
-#pragma unroll
-        for (int g = 0; g < C::G; g++) {
-          const int koff = (int)(blk * C::BLOCK + C::xoff(part, g) - k0);
-          if (koff >= 0 && koff < TG_BK) {
-            const __half2 h0 = __floats2half2_rn(wv[4 * g], wv[4 * g + 1]);
-            const __half2 h1 = __floats2half2_rn(wv[4 * g + 2], wv[4 * g + 3]);
-            const int c = koff >> 3;
-            uint8_t* dst = abase + r * 128 + ((c ^ (r & 7)) << 4) + (koff & 7) * 2;
-            *reinterpret_cast<uint2*>(dst) =
-                make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
-          }
-        }
-      }
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(full_bar + slot);
-    }
     }
   } else if (warp < TG_A_WARPS + TG_B_WARPS) {
     // ---------------- B producer: one TMA tile (bn rows x 64 k, swizzled by the hardware) per stage -----

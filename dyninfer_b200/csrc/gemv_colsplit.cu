@@ -318,6 +318,7 @@ void cs_plan(const WRef& w, CsPlan* p) {
 }  // namespace
 
 size_t gemv_cs_workspace_bytes(const WRef& w, int M) {
+  if (w.enc == E_Q6_K) return gemv_cs_q6k_workspace_bytes(w, M);
   if (!cs_shape_ok(w, M)) return 0;
   CsPlan p;
   cs_plan(w, &p);
@@ -329,6 +330,12 @@ size_t gemv_cs_workspace_bytes(const WRef& w, int M) {
 int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, const float* residual,
                    uint8_t* ws, cudaStream_t s, bool* handled) {
   *handled = false;
+  if (w.enc == E_Q6_K) {
+    if (!gemv_cs_q6k_shape_ok(w, M)) return 0;
+    if (launch_gemv_cs_q6k(w, x, x_type, y, residual, ws, s)) return 1;
+    *handled = true;
+    return 0;
+  }
   if (!cs_shape_ok(w, M)) return 0;
   CsPlan p;
   cs_plan(w, &p);

@@ -17,7 +17,8 @@ checkpoint (all linears Q4_0, tied Q6_K embedding / lm_head, GGUF v3), after a
             weight bytes one token reads / its average launch time, against the
             measured HBM copy bandwidth. `roofline_lm_head_gemv` adds the largest
             single product (151936 x 1024 Q6_K) as a stand-alone fused dequant-GEMV
-            launch, timed alone with CUDA events, L2 flushed between launches.
+            launch, timed alone with CUDA events over back-to-back launches (its 127.6 MB
+            of weights exceed L2).
   cpu_baseline  the CPU restatement of the reference's direct path (oracle/) on the
             host cores, on a bounded sample of the same workload.
 
@@ -170,9 +171,10 @@ def run_reference_arm(args, rank):
 
 # ------------------------------------------------------------------------- GPU arm
 
-def time_lm_head(path, iters=20):
-    """Average device time of the lm_head launch alone (CUDA events on the launching stream,
-    a 512 MB write between launches evicts L2)."""
+def time_lm_head(path, batches=5, reps=8):
+    """Average device time of the stand-alone lm_head product (CUDA events on the launching stream
+    around `reps` back-to-back launches, median over `batches`). The 127.6 MB of weights exceed L2,
+    so consecutive launches cannot reuse cached weights."""
     import torch
     from dyninfer_b200 import checkpoint as ck, ops
     cat = ck.open_catalog(path)
@@ -182,19 +184,19 @@ def time_lm_head(path, iters=20):
     w = ops.DeviceWeight(p.encoding, p.shape[0], p.shape[1], raw)
     x = torch.randn(1, p.shape[1], device="cuda")
     y = torch.empty(1, p.shape[0], device="cuda")
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
     for _ in range(3):
         ops.linear(w, x, out=y)
     times = []
-    for _ in range(iters):
-        flush.fill_(1)
+    for _ in range(batches):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
         e0.record()
-        ops.linear(w, x, out=y)
+        for _ in range(reps):
+            ops.linear(w, x, out=y)
         e1.record()
         torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1))
-    return statistics.mean(times), c.length, p.encoding
+        times.append(e0.elapsed_time(e1) / reps)
+    return statistics.median(times), c.length, p.encoding
 
 
 def main():
@@ -218,20 +220,18 @@ def main():
         return
 
     import torch
-    import torch.distributed as dist
+    from dyninfer_b200 import replicas
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the cuda target has no CPU fallback")
     torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    replicas.init("nccl", torch.device("cuda", local_rank))
 
     from dyninfer_b200 import build
     from dyninfer_b200.runtime import ModelLoader, SessionConfig
     build.build()
     if rank == 0:
         ensure_checkpoint()
-    if world > 1:
-        dist.barrier()
+    replicas.barrier()
     path = checkpoint_path()
     model = ModelLoader().load(path, target=f"cuda:{local_rank}", max_kv=2048, kv_dtype=args.kv_dtype)
     prompt = prompt_ids()
@@ -242,8 +242,7 @@ def main():
     first = session.prefill_argmax(prompt)
 
     def barrier():
-        if world > 1:
-            dist.barrier()
+        replicas.barrier()
         torch.cuda.synchronize()
 
     # ---- device-resident arm
@@ -269,10 +268,8 @@ def main():
             nxt = session.decode_argmax(nxt)
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_s = float(t[0]), float(t[1]) / 1e3
+    ms, e2e_ms = replicas.max_over_ranks([ms, e2e_s * 1e3], device="cuda")   # slowest rank decides
+    e2e_s = e2e_ms / 1e3
     weight_bytes = session.decode_weight_bytes()
 
     if rank == 0:
@@ -280,7 +277,7 @@ def main():
         lm_ms, lm_bytes, lm_enc = time_lm_head(path)
         achieved = lm_bytes / (lm_ms * 1e-3) / 1e9
         out = {
-            "metric": "decode_tokens_per_s", "value": world * K / (ms * 1e-3), "unit": "tok/s",
+            "metric": "decode_tokens_per_s", "value": replicas.whole_job_rate(K, ms, world), "unit": "tok/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
@@ -301,7 +298,7 @@ def main():
                          "bytes_per_launch": weight_bytes, "ms_per_launch": ms / K,
                          "traffic": MEGA_DRAM_TRAFFIC},
             # the largest single product of the step as its own launch (fused dequant-GEMV, M=1)
-            "roofline_lm_head_gemv": {"bound": "hbm", "kernel": f"gemv_tile_kernel<{lm_enc}> 151936x1024, M=1",
+            "roofline_lm_head_gemv": {"bound": "hbm", "kernel": f"gemv_cs_q6k_kernel ({lm_enc}) 151936x1024, M=1",
                                       "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                                       "frac": achieved / hbm_peak, "bytes_per_launch": lm_bytes,
                                       "ms_per_launch": lm_ms},
@@ -315,9 +312,7 @@ def main():
                           "CPU restatement of the reference's direct path"}
         print(json.dumps(out), flush=True)
     session.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    replicas.shutdown()
 
 
 if __name__ == "__main__":

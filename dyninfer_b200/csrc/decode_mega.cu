@@ -325,7 +325,8 @@ __device__ __forceinline__ unsigned long long gtime() {
 }
 // Phase timing seen by CTA 0 (optional): kind 0 embed, 1 qkv, 2 attention, 3 o_proj, 4 gate/up,
 // 5 down, 6 lm_head, 7 argmax, 8 whole kernel; 9 staging, 10 waiting for weights, 11 tile math,
-// 12 grid barrier.
+// 12 grid barrier; attention of CTA 0: 13 q/k/v load + norm + RoPE + first key fetch, 14 scores and
+// softmax, 15 merge and write.
 struct Prof {
   unsigned long long* out;
   unsigned long long last, start;
@@ -390,8 +391,9 @@ __device__ __forceinline__ void grid_sync(const MegaArgs& a, GridBar& gb, int G,
 template <int DPL>
 __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const MegaLayer* L, int cta,
                                                 int64_t pos, int64_t seq, int nsplit, const Smem& sm,
-                                                int tid, int lane, int warp) {
+                                                int tid, int lane, int warp, Prof& prof) {
   if (cta >= a.nh * nsplit) return;
+  unsigned long long tp = prof.tic();
   constexpr int KB = 4;  // keys in flight per warp
   const int h = cta / nsplit, sp = cta - h * nsplit;
   const int grp = a.nh / a.nkv, kvh = h / grp, gi = h - kvh * grp;
@@ -486,6 +488,8 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
   };
   fetch(k_lo + warp);
   consumer_sync();
+  prof.toc(13, tp);
+  tp = prof.tic();
   if (sp == 0 && gi == 0) {
     for (int i = tid; i < d; i += MK_CT) {
       store_kv(kc, a.kv_type, plane + pos * d + i, kn[i]);
@@ -533,6 +537,8 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
       }
     }
   }
+  prof.toc(14, tp);
+  tp = prof.tic();
   if (lane == 0) {
     wm[warp] = m;
     wl[warp] = lsum;
@@ -563,6 +569,7 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
     part[d] = gm;
     part[d + 1] = gl;
   }
+  prof.toc(15, tp);
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------
@@ -766,9 +773,9 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
     prof.mark(1);
     if (!*sm.abort && !(a.debug_skip & 4)) {
       if (a.d <= 128)
-        phase_attention<4>(a, l, L, cta, pos, seq, nsplit, sm, tid, lane, warp);
+        phase_attention<4>(a, l, L, cta, pos, seq, nsplit, sm, tid, lane, warp, prof);
       else
-        phase_attention<8>(a, l, L, cta, pos, seq, nsplit, sm, tid, lane, warp);
+        phase_attention<8>(a, l, L, cta, pos, seq, nsplit, sm, tid, lane, warp, prof);
     }
     gsync();
     prof.mark(2);

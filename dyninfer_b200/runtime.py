@@ -265,7 +265,8 @@ class CudaSession:
         out = (C.c_double * 16)()
         check(lib().dyninfer_cuda_session_decode_phase_profile(self._h, out, 16))
         names = ("embed", "qkv", "attention", "o_proj", "gate_up", "down", "lm_head", "argmax", "total",
-                 "t_stage", "t_wait_weights", "t_rows", "t_grid_barrier")
+                 "t_stage", "t_wait_weights", "t_rows", "t_grid_barrier", "t_attn_prepare", "t_attn_scores",
+                 "t_attn_merge")
         return dict(zip(names, [float(v) for v in out]))
 
     def weight_bytes(self) -> int:

@@ -69,6 +69,12 @@ PROTOTYPES = {
     "dyninfer_cuda_session_invoke_paged_chunk": (
         C.c_int, [_P, C.POINTER(_I64), C.c_size_t, _I64, _I64, C.POINTER(C.POINTER(C.c_float)),
                   C.POINTER(C.c_size_t), C.POINTER(_I64), C.c_int]),
+    "dyninfer_cuda_session_invoke_paged_chunk_slot": (
+        C.c_int, [_P, C.POINTER(_I64), C.c_size_t, _I64, _I64, _I64, C.POINTER(C.POINTER(C.c_float)),
+                  C.POINTER(C.c_size_t), C.POINTER(_I64), C.c_int]),
+    "dyninfer_cuda_session_decode_batch": (
+        C.c_int, [_P, C.POINTER(_I64), C.POINTER(_I64), C.POINTER(_I64), C.c_size_t, C.POINTER(_I64),
+                  C.POINTER(C.POINTER(C.c_float)), C.c_int]),
     "dyninfer_cuda_session_reset_paged_kv": (C.c_int, [_P]),
     "dyninfer_cuda_session_kv_page_count": (C.c_size_t, [_P]),
     "dyninfer_cuda_session_kv_allocated_bytes": (C.c_size_t, [_P]),

@@ -146,6 +146,10 @@ int launch_linear(const WRef& w, const void* x, int x_type, int64_t m, float* y,
 // Tensor-core GEMV for few activation rows (gemv_mma.cu); *handled tells whether it ran.
 int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float* y, const float* residual,
                      cudaStream_t s, bool* handled);
+bool gemv_cs_q8_0_shape_ok(const WRef& w, int M);
+size_t gemv_cs_q8_0_workspace_bytes(const WRef& w, int M);
+int launch_gemv_cs_q8_0(const WRef& w, const void* x, int x_type, float* y, const float* residual, uint8_t* ws,
+                        cudaStream_t s);
 bool gemv_cs_q6k_shape_ok(const WRef& w, int M);
 size_t gemv_cs_q6k_workspace_bytes(const WRef& w, int M);
 int launch_gemv_cs_q6k(const WRef& w, const void* x, int x_type, float* y, const float* residual, uint8_t* ws,
@@ -199,5 +203,6 @@ int launch_attention(const AttnArgs& a, cudaStream_t s);
 
 size_t argmax_scratch_bytes(int64_t n);
 int launch_argmax(const float* v, int64_t n, int64_t* out, void* scratch, cudaStream_t s);
+int launch_argmax_rows(const float* v, int64_t rows, int64_t n, int64_t* out, cudaStream_t s);
 
 }  // namespace dyn

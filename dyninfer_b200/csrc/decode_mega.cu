@@ -60,7 +60,8 @@ constexpr int MK_CW = 16;               // consumer warps
 constexpr int MK_CT = MK_CW * 32;       // consumer threads
 constexpr int MK_THREADS = MK_CT + 32;  // + one producer warp
 constexpr int MK_SLOT = 18432;          // bytes per ring slot (one 16-row tile x K-slice)
-constexpr int MK_MISC_FLOATS = 6144;    // per-CTA scratch (attention state, reductions, partials)
+constexpr int MK_MISC_FLOATS = 6400;    // per-CTA scratch (attention state, reductions, partials, RoPE table)
+constexpr int MK_ROPE_OFF = 6144;       // misc floats [6144, 6400): cos[128], sin[128] of this token's position
 constexpr int MK_PART_OFF = 5120;       // misc floats [5120, 6144): 2 x [16 warps][32] partial sums
 constexpr long long MK_MBAR_SPINS = 1LL << 22;
 constexpr long long MK_GRID_SPINS = 1LL << 22;
@@ -166,7 +167,6 @@ __device__ __forceinline__ float consumer_max(float v, float* red, int lane, int
 __device__ __forceinline__ float stage_phase(const float* x, bool src_smem, const void* nw, int nw_type,
                                              int n, float eps, int layout, const Smem& sm, int tid,
                                              int lane, int warp) {
-  if (eps < -1.f) return 1.f;
   float* red = sm.misc + MK_PART_OFF - 64;
   const int items = (n >> 5) * 4;
   const int kb = tid >> 2, t = tid & 3;
@@ -335,7 +335,7 @@ struct Prof {
     out = p;
     on = active && p != nullptr;
     if (on) {
-      for (int i = 0; i < 16; i++) out[i] = 0;
+      for (int i = 0; i < 24; i++) out[i] = 0;
       last = start = gtime();
     }
   }
@@ -362,10 +362,6 @@ struct GridBar {
 // Arrival: release-add on a monotonic counter; waiting: acquire-poll the same counter.
 __device__ __forceinline__ void grid_sync(const MegaArgs& a, GridBar& gb, int G, int tid,
                                           const Smem& sm) {
-  if (a.debug_skip & 16) {
-    consumer_sync();
-    return;
-  }
   consumer_sync();
   if (tid == 0) {
     gb.gen += 1;
@@ -422,8 +418,11 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
   }
   for (int i = tid; i < d; i += MK_CT) vn[i] = round_kv(__ldcg(a.v + (int64_t)kvh * d + i), a.kv_type);
   float qinv = 1.f, kinv = 1.f;
+  unsigned long long tq_ = prof.tic();
   if (a.has_norm) {
     float sq = warp_sum(fmaf(q1, q1, q2 * q2)), sk = warp_sum(fmaf(k1, k1, k2 * k2));
+    prof.toc(16, tp);  // q/k/v and norm weights arrived
+    tq_ = prof.tic();
     consumer_sync();
     if (lane == 0) {
       red[warp] = sq;
@@ -438,6 +437,8 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
     }
     qinv = 1.0f / sqrtf(tq / (float)d + a.eps);
     kinv = 1.0f / sqrtf(tk / (float)d + a.eps);
+    prof.toc(17, tq_);  // block reduction of the two RMS sums
+    tq_ = prof.tic();
   }
   if (pair) {
     if (a.has_norm) {
@@ -447,9 +448,7 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
       k2 = __fmul_rn(__fmul_rn(k2, kinv), wk2);
     }
     if (a.has_rope) {
-      const float angle = __fmul_rn((float)pos, a.ft.f[tid]);
-      float sv, cv;
-      sincosf(angle, &sv, &cv);
+      const float cv = sm.misc[MK_ROPE_OFF + tid], sv = sm.misc[MK_ROPE_OFF + 128 + tid];  // once per token
       const float ql = __fsub_rn(__fmul_rn(q1, cv), __fmul_rn(q2, sv));
       const float qh = __fadd_rn(__fmul_rn(q1, sv), __fmul_rn(q2, cv));
       const float kl = __fsub_rn(__fmul_rn(k1, cv), __fmul_rn(k2, sv));
@@ -468,25 +467,54 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
   const int64_t per = (n + nsplit - 1) / nsplit;
   const int64_t k_lo = (int64_t)sp * per;
   const int64_t k_hi = (k_lo + per < n) ? k_lo + per : n;
-  // first batch of this warp's keys: issue the loads before the barrier that publishes q
-  uint32_t kbits[KB][DPL], vbits[KB][DPL];
+  // A lane owns DPL consecutive head dims (one 8- or 16-byte piece of every cached row), so a
+  // warp reads a key or value row with one coalesced vector load. First batch of this warp's
+  // keys: the loads are issued before the barrier that publishes q.
+  constexpr int WPL = DPL;  // raw words per lane and row (f32 cache); 2-byte caches use DPL / 2
+  const bool wide = a.kv_type == E_F32;
+  const int e0 = lane * DPL;  // first head dim of this lane
+  const bool lane_live = e0 < d;
+  uint32_t kraw[KB][WPL], vraw[KB][WPL];
   auto fetch = [&](int64_t key0) {
 #pragma unroll
     for (int b = 0; b < KB; b++) {
       const int64_t key = key0 + (int64_t)b * MK_CW;
 #pragma unroll
-      for (int j = 0; j < DPL; j++) {
-        const int idx = lane + 32 * j;
-        if (key < k_hi && key != pos && idx < d) {
-          kbits[b][j] = load_kv_bits(kc, a.kv_type, plane + key * d + idx);
-          vbits[b][j] = load_kv_bits(vc, a.kv_type, plane + key * d + idx);
+      for (int w = 0; w < WPL; w++) kraw[b][w] = vraw[b][w] = 0;
+      if (key < k_hi && key != pos && lane_live) {
+        const int64_t el = plane + key * d + e0;
+        if (wide) {
+          const uint4* kp = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(kc) + el);
+          const uint4* vp = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(vc) + el);
+#pragma unroll
+          for (int w4 = 0; w4 < WPL / 4; w4++) {
+            const uint4 kk = kp[w4], vv = vp[w4];
+            kraw[b][4 * w4] = kk.x, kraw[b][4 * w4 + 1] = kk.y, kraw[b][4 * w4 + 2] = kk.z, kraw[b][4 * w4 + 3] = kk.w;
+            vraw[b][4 * w4] = vv.x, vraw[b][4 * w4 + 1] = vv.y, vraw[b][4 * w4 + 2] = vv.z, vraw[b][4 * w4 + 3] = vv.w;
+          }
         } else {
-          kbits[b][j] = vbits[b][j] = 0;
+          const uint2* kp = reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(kc) + el);
+          const uint2* vp = reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(vc) + el);
+#pragma unroll
+          for (int w2 = 0; w2 < WPL / 4; w2++) {
+            const uint2 kk = kp[w2], vv = vp[w2];
+            kraw[b][2 * w2] = kk.x, kraw[b][2 * w2 + 1] = kk.y;
+            vraw[b][2 * w2] = vv.x, vraw[b][2 * w2 + 1] = vv.y;
+          }
         }
       }
     }
   };
+  // element j of a raw row piece as f32
+  auto elem = [&](const uint32_t (&raw)[WPL], int j) -> float {
+    if (wide) return __uint_as_float(raw[j]);
+    const uint32_t bits = (raw[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+    return a.kv_type == E_F16 ? f16_bits_to_f32(bits) : bf16_bits_to_f32(bits);
+  };
+  prof.toc(18, tq_);  // norm, RoPE, shared-memory hand-off, cache addresses
+  tq_ = prof.tic();
   fetch(k_lo + warp);
+  prof.toc(19, tq_);  // issuing the first key / value loads
   consumer_sync();
   prof.toc(13, tp);
   tp = prof.tic();
@@ -500,8 +528,7 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
   float qreg[DPL], acc[DPL];
 #pragma unroll
   for (int j = 0; j < DPL; j++) {
-    const int idx = lane + 32 * j;
-    qreg[j] = idx < d ? qs[idx] : 0.f;
+    qreg[j] = lane_live ? qs[e0 + j] : 0.f;
     acc[j] = 0.f;
   }
   float m = -3.40282347e38f, lsum = 0.f;
@@ -512,10 +539,9 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
     for (int b = 0; b < KB; b++) {
       const int64_t key = key0 + (int64_t)b * MK_CW;
       float dot = 0.f;
+      if (lane_live) {
 #pragma unroll
-      for (int j = 0; j < DPL; j++) {
-        const int idx = lane + 32 * j;
-        if (idx < d) dot = fmaf(qreg[j], key == pos ? kn[idx] : kv_bits_to_f32(kbits[b][j], a.kv_type), dot);
+        for (int j = 0; j < DPL; j++) dot = fmaf(qreg[j], key == pos ? kn[e0 + j] : elem(kraw[b], j), dot);
       }
       sc[b] = warp_sum(dot) * scale;
     }
@@ -527,11 +553,10 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
         const float factor = expf(m - mn);
         const float p = expf(sc[b] - mn);
         lsum = lsum * factor + p;
+        if (lane_live) {
 #pragma unroll
-        for (int j = 0; j < DPL; j++) {
-          const int idx = lane + 32 * j;
-          if (idx < d)
-            acc[j] = acc[j] * factor + p * (key == pos ? vn[idx] : kv_bits_to_f32(vbits[b][j], a.kv_type));
+          for (int j = 0; j < DPL; j++)
+            acc[j] = acc[j] * factor + p * (key == pos ? vn[e0 + j] : elem(vraw[b], j));
         }
         m = mn;
       }
@@ -543,23 +568,26 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
     wm[warp] = m;
     wl[warp] = lsum;
   }
+  if (lane_live) {
 #pragma unroll
-  for (int j = 0; j < DPL; j++) {
-    const int idx = lane + 32 * j;
-    if (idx < d) wacc[warp * 256 + idx] = acc[j];
+    for (int j = 0; j < DPL; j++) wacc[warp * 256 + e0 + j] = acc[j];
   }
   consumer_sync();
   float gm = wm[0];
 #pragma unroll
   for (int w = 1; w < MK_CW; w++) gm = fmaxf(gm, wm[w]);
+  // each warp's weight exp(m_w - gm) once, by one lane per warp, instead of per output element
+  float* wwt = red;  // [16], free since the RMS reduction
+  if (tid < MK_CW) wwt[tid] = expf(wm[tid] - gm);
+  consumer_sync();
   float gl = 0.f;
 #pragma unroll
-  for (int w = 0; w < MK_CW; w++) gl += wl[w] * expf(wm[w] - gm);
+  for (int w = 0; w < MK_CW; w++) gl += wl[w] * wwt[w];
   float* part = a.attn_part + ((int64_t)h * a.max_split + sp) * (d + 2);
   for (int idx = tid; idx < d; idx += MK_CT) {
     float o = 0.f;
 #pragma unroll
-    for (int w = 0; w < MK_CW; w++) o += wacc[w * 256 + idx] * expf(wm[w] - gm);
+    for (int w = 0; w < MK_CW; w++) o += wacc[w * 256 + idx] * wwt[w];
     if (nsplit == 1)
       a.ctx[(int64_t)h * d + idx] = o / gl;
     else
@@ -632,8 +660,7 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
     for (int i = lane; i < nph; i += 32) total += sm.counts[i];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-    if (!(a.debug_skip & 32))
-      for (int pi = 0; pi < total; pi++) produce_chunk(sm.prog + pi, sm, (uint32_t)pi, lane);
+    for (int pi = 0; pi < total; pi++) produce_chunk(sm.prog + pi, sm, (uint32_t)pi, lane);
     return;
   }
 
@@ -671,12 +698,12 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
       if (warp == 0 && lane < 16 && lane < c->n && (c->flags & 1) && ((c->flags >> 2) & 3) == MEGA_EP_RESIDUAL)
         resid = __ldcg(c->out + c->out_row + lane);
       const unsigned long long tw = prof.tic();
-      bool ok = (a.debug_skip & 32) ? true : mbar_wait_bounded(sm.full + slot, (ci / sm.nslot) & 1u, MK_MBAR_SPINS, sm.abort);
+      const bool ok = mbar_wait_bounded(sm.full + slot, (ci / sm.nslot) & 1u, MK_MBAR_SPINS, sm.abort);
       if (!ok && !*sm.abort) *sm.abort = 3;
       prof.toc(10, tw);
       const unsigned long long tr = prof.tic();
       const int n = c->n, nu = c->nu, flags = c->flags;
-      if (ok && !(a.debug_skip & 1)) {
+      if (ok) {
         const uint8_t* base = sm.ring + (size_t)slot * MK_SLOT;
         const int i0 = g < n ? g : n - 1, i1 = g + 8 < n ? g + 8 : n - 1;  // clamp to valid rows
         const uint32_t pitch = c->pitch, rb = c->rb;
@@ -697,8 +724,8 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
       }
       prof.toc(11, tr);
       __syncwarp();
-      if (lane == 0 && !(a.debug_skip & 32)) mbar_arrive(sm.empty + slot);
-      if (!(flags & 1) || (a.debug_skip & 8)) continue;
+      if (lane == 0) mbar_arrive(sm.empty + slot);
+      if (!(flags & 1)) continue;
       // tile complete: per-warp partial sums -> warp 0 adds them in a fixed order -> epilogue.
       // The other warps do not wait: they hand their sums over through an mbarrier and go on.
       const int buf = closes & 1;
@@ -758,6 +785,13 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
     prof.toc(12, t_);
   };
 
+  if (a.has_rope && tid < a.d / 2) {
+    // the rotation of this token's position, shared by all layers (kernels.rs:1047-1064)
+    float sv, cv;
+    sincosf(__fmul_rn((float)pos, a.ft.f[tid]), &sv, &cv);
+    sm.misc[MK_ROPE_OFF + tid] = cv;
+    sm.misc[MK_ROPE_OFF + 128 + tid] = sv;
+  }
   if (cta == 0) mega_gather_row(a.embed, token, a.hidden, tid, MK_CT);
   gsync();
   prof.mark(0);
@@ -771,7 +805,7 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
     run_phase(4 * l + 0);
     gsync();
     prof.mark(1);
-    if (!*sm.abort && !(a.debug_skip & 4)) {
+    if (!*sm.abort) {
       if (a.d <= 128)
         phase_attention<4>(a, l, L, cta, pos, seq, nsplit, sm, tid, lane, warp, prof);
       else

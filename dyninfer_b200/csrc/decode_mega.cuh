@@ -71,7 +71,6 @@ struct MegaArgs {
   const uint16_t* counts;    // [grid][4 * layers + 1] chunks per phase
   int max_chunks;
   int prog_in_smem;          // the CTA copies its program into shared memory at start
-  int debug_skip;           // timing experiments only: bit0 tile math, bit1 staging, bit2 attention
   int nslot;                // ring slots in shared memory
   int xs_floats;            // activation vector capacity in shared memory
   FreqTable ft;

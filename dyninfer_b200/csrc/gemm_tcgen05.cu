@@ -16,7 +16,8 @@
 // Stages hand over through mbarriers; every wait is bounded and reports through an error word, and
 // the tensor memory is always released before the CTA exits.
 //
-// Precision: weights enter as f16(exact dequantised value) (relative rounding 2^-12), activations
+// Precision: weights enter as f16(exact dequantised value) (relative rounding 2^-12; plain f32 / bf16
+// weights are rounded the same way and must lie inside the f16 range), activations
 // as f16 (bf16 inputs of ordinary magnitude convert exactly), products accumulate in f32.
 #include <cuda.h>
 
@@ -371,8 +372,11 @@ bool tg_shape_ok(const WRef& w, int64_t M) {
     case E_Q4_0:
     case E_Q4_1:
     case E_Q8_0:
-    case E_MLX_U4: break;
-    case E_Q6_K: break;
+    case E_MLX_U4:
+    case E_Q6_K:
+    case E_F32:
+    case E_F16:
+    case E_BF16: break;
     default: return false;
   }
   if (w.enc == E_MLX_U4 && (w.group < 8 || w.cols % w.group)) return false;
@@ -456,6 +460,9 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
     case E_Q8_0: rc = tg_launch<E_Q8_0>(a, xmap, grid, smem, s); break;
     case E_Q6_K: rc = tg_launch<E_Q6_K>(a, xmap, grid, smem, s); break;
     case E_MLX_U4: rc = tg_launch<E_MLX_U4>(a, xmap, grid, smem, s); break;
+    case E_F32: rc = tg_launch<E_F32>(a, xmap, grid, smem, s); break;
+    case E_F16: rc = tg_launch<E_F16>(a, xmap, grid, smem, s); break;
+    case E_BF16: rc = tg_launch<E_BF16>(a, xmap, grid, smem, s); break;
     default: break;
   }
   count_launch(2);

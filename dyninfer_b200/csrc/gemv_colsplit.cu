@@ -35,14 +35,23 @@ namespace {
 
 constexpr int CS_WARPS = 16;
 constexpr int CS_NST = 2;            // stages per warp
-constexpr int CS_PAIRS = 1;          // unit pairs (512 elements, 288 bytes per row) per stage
-constexpr int CS_ROWB = 288 * CS_PAIRS;   // bytes of one row in a stage
-constexpr int CS_PITCH = CS_ROWB + 16;    // row pitch: 76 or 148 words = 12 or 20 (mod 32), conflict-free
-constexpr int CS_STAGE = 16 * CS_PITCH;
+constexpr int CS_PAIRS = 1;          // unit pairs (512 elements) per stage
 constexpr int CS_KSTAGE = 512 * CS_PAIRS; // K elements per stage
+// Per encoding: words a lane reads per unit and row (two blocks incl. their scales), bytes of one
+// row in a stage, and the row pitch in shared memory (bytes of a stage row + 16).
+//   Q4_0: 18-byte blocks, 9 words, 288-byte rows, pitch 304 (76 words = 12 mod 32: conflict-free)
+//   Q4_1: 20-byte blocks (f16 d, f16 m, 16 quant bytes), 10 words, 320-byte rows, pitch 336
+template <int ENC>
+struct CsGeo {
+  static constexpr int LW = ENC == E_Q4_0 ? 9 : 10;          // words per lane, unit and row
+  static constexpr int UW = 4 * LW;                          // words per unit and row
+  static constexpr int ROWB = UW * 4 * 2 * CS_PAIRS;         // bytes of one row in a stage
+  static constexpr int PITCH = ROWB + 16;
+  static constexpr int STAGE = 16 * PITCH;
+  static constexpr int RING_BYTES = CS_WARPS * CS_NST * STAGE + CS_WARPS * CS_NST * 8;  // rings + barriers
+};
 constexpr long long CS_SPINS = 1LL << 22;
 constexpr int CS_MAX_SMEM = 226 * 1024;  // dynamic shared memory the kernel may ask for (static: 128 bytes)
-constexpr int CS_RING_BYTES = CS_WARPS * CS_NST * CS_STAGE + CS_WARPS * CS_NST * 8;  // rings + barriers
 
 // ---- activation staging (every CTA, into its own shared memory) ---------------------------------
 // xq: per (unit U of 256 elements, parity e, word i, quarter t, hi/lo) one uint4 holding the B
@@ -50,10 +59,11 @@ constexpr int CS_RING_BYTES = CS_WARPS * CS_NST * CS_STAGE + CS_WARPS * CS_NST *
 //   step 2i+o: b0 = (x[4i+o], x[4i+o+2]), b1 = (x[16+4i+o], x[16+4i+o+2]) / 16,
 // scaled so the row's largest magnitude sits in [2^12, 2^13); index ((U*2+e)*4+i)*8 + 2t + hl, so
 // the eight lanes that feed one step read 128 contiguous bytes.
-// sx8[b] = 8 * sum(block b of the scaled row) (the Q4_0 zero point), in accumulator units.
+// sx8[b] = sum_factor * sum(block b of the scaled row) in accumulator units (8 = the Q4_0 zero point;
+// 1 for Q4_1, whose minimum multiplies the plain sum).
 // Returns 2^24 / scale (what turns accumulator units back into the product).
 __device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf16, int K, uint2* xq,
-                                            float* sx8, float* red) {
+                                            float* sx8, float* red, float sum_factor) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   auto ld = [&](int i) -> float {
     return x_bf16 ? bf16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t*>(x) + i))
@@ -78,7 +88,7 @@ __device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-    if (st == 0) sx8[b] = 8.0f * GV_2M24 * sum;
+    if (st == 0) sx8[b] = sum_factor * GV_2M24 * sum;
     const float f0 = g0 * 0.0625f, f1 = g1 * 0.0625f;
     const __half h0 = __float2half_rn(e0), h1 = __float2half_rn(e1);
     const __half h2 = __float2half_rn(f0), h3 = __float2half_rn(f1);
@@ -110,14 +120,17 @@ struct CsArgs {
   int* error;
 };
 
-__global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_0_kernel(const CsArgs a) {
+template <int ENC>
+__global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsArgs a) {
+  using G = CsGeo<ENC>;
+  constexpr int LW = G::LW;
   extern __shared__ __align__(128) uint8_t cs_smem[];
   __shared__ int s_abort;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  uint8_t* ring = cs_smem + (size_t)warp * CS_NST * CS_STAGE;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(cs_smem + (size_t)CS_WARPS * CS_NST * CS_STAGE) + warp * CS_NST;
-  uint4* xq = reinterpret_cast<uint4*>(cs_smem + CS_RING_BYTES);
+  uint8_t* ring = cs_smem + (size_t)warp * CS_NST * G::STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(cs_smem + (size_t)CS_WARPS * CS_NST * G::STAGE) + warp * CS_NST;
+  uint4* xq = reinterpret_cast<uint4*>(cs_smem + G::RING_BYTES);
   float* sx8 = reinterpret_cast<float*>(xq + (size_t)(a.K >> 8) * 64);
   float* red = sx8 + (a.K >> 5);
   if (threadIdx.x == 0) {
@@ -146,13 +159,13 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_0_kernel(const Cs
   auto issue = [&]() {
     if (c_left <= 0) return;
     c_left--;
-    if (lane == 0) mbar_expect_tx(bars + c_slot, 16 * CS_ROWB);
+    if (lane == 0) mbar_expect_tx(bars + c_slot, 16 * G::ROWB);
     __syncwarp();
     if (lane < 16) {
       int64_t row = (int64_t)c_tile * 16 + lane;
       if (row > last_row) row = last_row;
-      const uint8_t* src = a.data + row * a.rb + (int64_t)(c_sl * nst + c_st) * CS_ROWB;
-      bulk_g2s(ring + c_slot * CS_STAGE + lane * CS_PITCH, src, CS_ROWB, bars + c_slot);
+      const uint8_t* src = a.data + row * a.rb + (int64_t)(c_sl * nst + c_st) * G::ROWB;
+      bulk_g2s(ring + c_slot * G::STAGE + lane * G::PITCH, src, G::ROWB, bars + c_slot);
     }
     if (++c_slot == CS_NST) c_slot = 0;
     if (++c_st == nst) {
@@ -164,7 +177,8 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_0_kernel(const Cs
   for (int q = 0; q < CS_NST; q++) issue();
 
   // while the first stages are in flight: arrange the activation row in shared memory
-  const float out_scale = cs_stage_x(a.x, a.x_bf16, a.K, reinterpret_cast<uint2*>(xq), sx8, red);
+  const float out_scale =
+      cs_stage_x(a.x, a.x_bf16, a.K, reinterpret_cast<uint2*>(xq), sx8, red, ENC == E_Q4_0 ? 8.0f : 1.0f);
   if (blockIdx.x == 0 && threadIdx.x == 0) a.misc[0] = out_scale;
   __syncthreads();
   if (total == 0) return;
@@ -182,20 +196,20 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_0_kernel(const Cs
         }
         return;  // warp-uniform: every lane polls the same barrier
       }
-      const uint8_t* base = ring + slot * CS_STAGE;
-      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(base + g * CS_PITCH) + 9 * t;
-      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(base + (g + 8) * CS_PITCH) + 9 * t;
+      const uint8_t* base = ring + slot * G::STAGE;
+      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(base + g * G::PITCH) + LW * t;
+      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(base + (g + 8) * G::PITCH) + LW * t;
 #pragma unroll
       for (int pr = 0; pr < CS_PAIRS; pr++) {
       const int U0 = ((sl * nst + st) * CS_PAIRS + pr) * 2;  // first 256-element unit of this pair
       // the pair goes to registers first; after the last pair the slot can be refilled before the math
-      uint32_t w0[2][9], w1[2][9];
+      uint32_t w0[2][LW], w1[2][LW];
 #pragma unroll
       for (int u = 0; u < 2; u++)
 #pragma unroll
-        for (int i = 0; i < 9; i++) {
-          w0[u][i] = r0[pr * 72 + u * 36 + i];
-          w1[u][i] = r1[pr * 72 + u * 36 + i];
+        for (int i = 0; i < LW; i++) {
+          w0[u][i] = r0[pr * 2 * G::UW + u * G::UW + i];
+          w1[u][i] = r1[pr * 2 * G::UW + u * G::UW + i];
         }
       if (pr == CS_PAIRS - 1) {
         __syncwarp();
@@ -216,10 +230,13 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_0_kernel(const Cs
 #pragma unroll
         for (int gi = 0; gi < 4; gi++) {
           const int u = gi >> 1;
-          if (gi & 1) {  // odd block: words 5..8
+          if (ENC == E_Q4_1) {  // both blocks word aligned: (d, m) then four quant words
+            q0[gi] = w0[u][5 * (gi & 1) + 1 + i];
+            q1[gi] = w1[u][5 * (gi & 1) + 1 + i];
+          } else if (gi & 1) {  // Q4_0 odd block: words 5..8
             q0[gi] = w0[u][5 + i];
             q1[gi] = w1[u][5 + i];
-          } else {       // even block: quants start 2 bytes into word 0
+          } else {       // Q4_0 even block: quants start 2 bytes into word 0
             q0[gi] = __funnelshift_r(w0[u][i], w0[u][i + 1], 16);
             q1[gi] = __funnelshift_r(w1[u][i], w1[u][i + 1], 16);
           }
@@ -240,12 +257,19 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_0_kernel(const Cs
       for (int gi = 0; gi < 4; gi++) {
         const int u = gi >> 1;
         const float sx = sxp[u * 8 + (gi & 1)];
-        const __half2 h0 = *reinterpret_cast<const __half2*>(&w0[u][(gi & 1) ? 4 : 0]);
-        const __half2 h1 = *reinterpret_cast<const __half2*>(&w1[u][(gi & 1) ? 4 : 0]);
-        const float d0 = (gi & 1) ? __high2float(h0) : __low2float(h0);
-        const float d1 = (gi & 1) ? __high2float(h1) : __low2float(h1);
-        acc0 = fmaf(d0, (c[gi][0] + c[gi][1]) - sx, acc0);
-        acc1 = fmaf(d1, (c[gi][2] + c[gi][3]) - sx, acc1);
+        if (ENC == E_Q4_1) {  // w = q * d + m: scale the tile sums, add the minimum times the plain sum
+          const __half2 h0 = *reinterpret_cast<const __half2*>(&w0[u][5 * (gi & 1)]);
+          const __half2 h1 = *reinterpret_cast<const __half2*>(&w1[u][5 * (gi & 1)]);
+          acc0 = fmaf(__low2float(h0), c[gi][0] + c[gi][1], fmaf(__high2float(h0), sx, acc0));
+          acc1 = fmaf(__low2float(h1), c[gi][2] + c[gi][3], fmaf(__high2float(h1), sx, acc1));
+        } else {
+          const __half2 h0 = *reinterpret_cast<const __half2*>(&w0[u][(gi & 1) ? 4 : 0]);
+          const __half2 h1 = *reinterpret_cast<const __half2*>(&w1[u][(gi & 1) ? 4 : 0]);
+          const float d0 = (gi & 1) ? __high2float(h0) : __low2float(h0);
+          const float d1 = (gi & 1) ? __high2float(h1) : __low2float(h1);
+          acc0 = fmaf(d0, (c[gi][0] + c[gi][1]) - sx, acc0);
+          acc1 = fmaf(d1, (c[gi][2] + c[gi][3]) - sx, acc1);
+        }
       }
       }
     }
@@ -287,11 +311,15 @@ struct CsPlan {
   size_t smem, off_err, off_part, bytes;
 };
 
-size_t cs_smem_bytes(int K) { return (size_t)CS_RING_BYTES + (size_t)(K >> 8) * 1024 + (size_t)(K >> 5) * 4 + 128; }
+size_t cs_smem_bytes(int enc, int K) {
+  const size_t ring = enc == E_Q4_0 ? CsGeo<E_Q4_0>::RING_BYTES : CsGeo<E_Q4_1>::RING_BYTES;
+  return ring + (size_t)(K >> 8) * 1024 + (size_t)(K >> 5) * 4 + 128;
+}
 
 bool cs_shape_ok(const WRef& w, int M) {
-  return M == 1 && w.enc == E_Q4_0 && w.rows >= 1 && w.cols >= CS_KSTAGE && w.cols % CS_KSTAGE == 0 &&
-         cs_smem_bytes((int)w.cols) <= (size_t)CS_MAX_SMEM && (reinterpret_cast<uintptr_t>(w.data) & 15) == 0;
+  return M == 1 && (w.enc == E_Q4_0 || w.enc == E_Q4_1) && w.rows >= 1 && w.cols >= CS_KSTAGE &&
+         w.cols % CS_KSTAGE == 0 && cs_smem_bytes(w.enc, (int)w.cols) <= (size_t)CS_MAX_SMEM &&
+         (reinterpret_cast<uintptr_t>(w.data) & 15) == 0;
 }
 
 void cs_plan(const WRef& w, CsPlan* p) {
@@ -309,7 +337,7 @@ void cs_plan(const WRef& w, CsPlan* p) {
   p->nst = stages / S;
   const int64_t items = (int64_t)p->ntiles * S;
   p->grid = (int)std::min<int64_t>(148, (items + CS_WARPS - 1) / CS_WARPS);
-  p->smem = cs_smem_bytes(K);
+  p->smem = cs_smem_bytes(w.enc, K);
   p->off_err = 0;       // [0] error word, [64] 2^24 / scale
   p->off_part = 256;
   p->bytes = 256 + (S > 1 ? (size_t)S * w.rows * 4 : 0);
@@ -319,6 +347,7 @@ void cs_plan(const WRef& w, CsPlan* p) {
 
 size_t gemv_cs_workspace_bytes(const WRef& w, int M) {
   if (w.enc == E_Q6_K) return gemv_cs_q6k_workspace_bytes(w, M);
+  if (w.enc == E_Q8_0) return gemv_cs_q8_0_workspace_bytes(w, M);
   if (!cs_shape_ok(w, M)) return 0;
   CsPlan p;
   cs_plan(w, &p);
@@ -336,6 +365,12 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
     *handled = true;
     return 0;
   }
+  if (w.enc == E_Q8_0) {
+    if (!gemv_cs_q8_0_shape_ok(w, M)) return 0;
+    if (launch_gemv_cs_q8_0(w, x, x_type, y, residual, ws, s)) return 1;
+    *handled = true;
+    return 0;
+  }
   if (!cs_shape_ok(w, M)) return 0;
   CsPlan p;
   cs_plan(w, &p);
@@ -349,10 +384,14 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
   a.y = y, a.residual = residual;
   static bool attr_done = false;
   if (!attr_done) {
-    DYN_CUDA(cudaFuncSetAttribute(gemv_cs_q4_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CS_MAX_SMEM));
+    DYN_CUDA(cudaFuncSetAttribute(gemv_cs_q4_kernel<E_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, CS_MAX_SMEM));
+    DYN_CUDA(cudaFuncSetAttribute(gemv_cs_q4_kernel<E_Q4_1>, cudaFuncAttributeMaxDynamicSharedMemorySize, CS_MAX_SMEM));
     attr_done = true;
   }
-  gemv_cs_q4_0_kernel<<<p.grid, CS_WARPS * 32, p.smem, s>>>(a);
+  if (w.enc == E_Q4_0)
+    gemv_cs_q4_kernel<E_Q4_0><<<p.grid, CS_WARPS * 32, p.smem, s>>>(a);
+  else
+    gemv_cs_q4_kernel<E_Q4_1><<<p.grid, CS_WARPS * 32, p.smem, s>>>(a);
   count_launch(1);
   if (p.S > 1) {
     cs_reduce_kernel<<<(unsigned)((w.rows + 255) / 256), 256, 0, s>>>(a.partial, p.S, w.rows, a.misc, y, residual);

@@ -357,6 +357,47 @@ argmax_final_kernel(const ArgPair* part, int count, int64_t* out) {
   if (threadIdx.x == 0) out[0] = si[0] == 0x7fffffffffffffffLL ? 0 : si[0];
 }
 
+// One block per row of v [rows, n]: first strict maximum of every row (batched decode).
+__global__ void __launch_bounds__(1024)
+argmax_rows_kernel(const float* __restrict__ v, int64_t n, int64_t* out) {
+  __shared__ float sv[32];
+  __shared__ long long si[32];
+  const float* row = v + (int64_t)blockIdx.x * n;
+  float bv = -INFINITY;
+  long long bi = 0x7fffffffffffffffLL;
+  for (int64_t i = threadIdx.x; i < n; i += 1024) {
+    const float x = row[i];
+    if (x > -INFINITY && arg_better(x, i, bv, bi)) bv = x, bi = i;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (arg_better(ov, oi, bv, bi)) bv = ov, bi = oi;
+  }
+  if (lane == 0) sv[warp] = bv, si[warp] = bi;
+  __syncthreads();
+  if (warp == 0) {
+    bv = sv[lane], bi = si[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (arg_better(ov, oi, bv, bi)) bv = ov, bi = oi;
+    }
+    if (lane == 0) out[blockIdx.x] = bi == 0x7fffffffffffffffLL ? 0 : bi;
+  }
+}
+
+int launch_argmax_rows(const float* v, int64_t rows, int64_t n, int64_t* out, cudaStream_t s) {
+  DYN_CHECK(rows >= 1 && n >= 1, "argmax_rows: rows and n must be >= 1");
+  argmax_rows_kernel<<<(unsigned)rows, 1024, 0, s>>>(v, n, out);
+  count_launch();
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
 size_t argmax_scratch_bytes(int64_t) { return sizeof(ArgPair) * ARGMAX_BLOCKS; }
 
 int launch_argmax(const float* v, int64_t n, int64_t* out, void* scratch, cudaStream_t s) {

@@ -71,6 +71,9 @@ struct dyninfer_cuda_session_t {
           *out_token_dev = nullptr, *hist_dev = nullptr, *hist_count_dev = nullptr;
   size_t hist_cap = 0;
   void* argmax_scratch = nullptr;
+  float* batch_logits = nullptr;      // [batch, vocab], allocated by the first batched step
+  int64_t* batch_tokens_dev = nullptr; // [batch]
+  float* batch_logits_host = nullptr;  // pinned, allocated when logits are first requested
   // pinned host staging
   float* logits_host = nullptr;
   int64_t* stage_host = nullptr;  // [0]=token [1]=pos [2]=seq [3]=out token, then chunk arrays
@@ -247,7 +250,7 @@ __global__ void advance_kernel(int64_t* tokens, int64_t* row_pos, const int64_t*
 
 // Enqueue the whole decoder for `rows` rows whose tokens / positions / slots are
 // already in device memory; logits and argmax come from row `logits_row`.
-int enqueue_forward(Session* s, int64_t rows, int64_t logits_row) {
+int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows = false) {
   const ModelCfg& c = s->cfg;
   cudaStream_t st = s->stream;
   const int64_t H = c.hidden, qd = (int64_t)c.heads * c.head_dim,
@@ -293,6 +296,13 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row) {
       if (launch_silu_mul(s->act, up_tmp, rows * c.inter, s->act, st)) return 1;
     }
     if (launch_linear(L.down, s->act, E_F32, rows, s->hidden, s->hidden, st)) return 1;
+  }
+  if (all_rows) {
+    // batched decode: every row is the last token of its own sequence
+    if (launch_rms_norm(s->hidden, s->out_norm.ptr, s->out_norm.type, rows, H, c.eps, s->xn, st)) return 1;
+    if (launch_linear(s->lm_head, s->xn, E_F32, rows, s->batch_logits, nullptr, st)) return 1;
+    if (launch_argmax_rows(s->batch_logits, rows, c.vocab, s->batch_tokens_dev, st)) return 1;
+    return 0;
   }
   // final norm of the one row that feeds the lm_head (dense_decoder.rs:1573-1615)
   if (launch_rms_norm(s->hidden + logits_row * H, s->out_norm.ptr, s->out_norm.type, 1, H, c.eps,
@@ -393,11 +403,6 @@ void fill_mega_args(Session* s, MegaArgs* a, int advance) {
   }
   a->prog = s->prog_dev, a->counts = s->counts_dev, a->max_chunks = s->mega_max_chunks;
   a->prog_in_smem = s->mega_prog_smem;
-  {
-    const char* dbg = getenv("DYNINFER_CUDA_DEBUG_SKIP");
-    a->debug_skip = dbg ? atoi(dbg) : 0;
-    if (a->debug_skip & 2) a->eps = -2.f;
-  }
   a->nslot = s->mega_nslot, a->xs_floats = s->mega_xs;
   a->ft = s->freq;
 }
@@ -692,7 +697,7 @@ int dyninfer_cuda_session_create_with_file_params(
           dev_alloc(s, (void**)&s->attn_part, part_bytes) ||
           dev_alloc(s, (void**)&s->amax_val, (size_t)s->mega_grid * 4) ||
           dev_alloc(s, (void**)&s->amax_idx, (size_t)s->mega_grid * 8) ||
-          dev_alloc(s, (void**)&s->prof_dev, 128))
+          dev_alloc(s, (void**)&s->prof_dev, 192))
         return fail();
       if (cudaMemcpy(s->mega_layers, ml.data(), ml.size() * sizeof(MegaLayer),
                      cudaMemcpyHostToDevice) != cudaSuccess ||
@@ -723,10 +728,11 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
                  s->logits, s->tokens_dev, s->row_pos_dev, s->row_seq_dev, s->out_token_dev,
                  s->hist_dev, s->hist_count_dev, s->argmax_scratch, s->mega_layers, s->io_dev,
                  s->bar_dev, s->attn_part, s->amax_val, s->amax_idx, s->prof_dev, s->prog_dev,
-                 s->counts_dev};
+                 s->counts_dev, s->batch_logits, s->batch_tokens_dev};
   for (void* p : dev)
     if (p) cudaFree(p);
   if (s->logits_host) cudaFreeHost(s->logits_host);
+  if (s->batch_logits_host) cudaFreeHost(s->batch_logits_host);
   if (s->stage_host) cudaFreeHost(s->stage_host);
   if (s->ev0) cudaEventDestroy(s->ev0);
   if (s->ev1) cudaEventDestroy(s->ev1);
@@ -881,11 +887,11 @@ int dyninfer_cuda_session_decode_phase_profile(dyninfer_cuda_session_t* s, doubl
                                                size_t count) {
   DYN_CHECK(s != nullptr && out_us != nullptr, "session or out_us is NULL");
   DYN_CHECK(s->mega && s->prof_dev, "the persistent decode kernel is not in use");
-  unsigned long long ns[16] = {0};
+  unsigned long long ns[24] = {0};
   DYN_CUDA(cudaSetDevice(s->device));
   DYN_CUDA(cudaStreamSynchronize(s->stream));
   DYN_CUDA(cudaMemcpy(ns, s->prof_dev, sizeof ns, cudaMemcpyDeviceToHost));
-  for (size_t i = 0; i < count && i < 16; i++) out_us[i] = (double)ns[i] * 1e-3;
+  for (size_t i = 0; i < count && i < 24; i++) out_us[i] = (double)ns[i] * 1e-3;
   return 0;
 }
 
@@ -897,7 +903,17 @@ int dyninfer_cuda_session_invoke_paged_chunk(dyninfer_cuda_session_t* s, const i
                                              size_t token_count, int64_t last, int64_t start_pos,
                                              float** out_logits, size_t* out_count,
                                              int64_t* out_token, int want_logits) {
+  return dyninfer_cuda_session_invoke_paged_chunk_slot(s, tokens, token_count, last, start_pos, 0, out_logits,
+                                                      out_count, out_token, want_logits);
+}
+
+int dyninfer_cuda_session_invoke_paged_chunk_slot(dyninfer_cuda_session_t* s, const int64_t* tokens,
+                                                  size_t token_count, int64_t last, int64_t start_pos,
+                                                  int64_t slot, float** out_logits, size_t* out_count,
+                                                  int64_t* out_token, int want_logits) {
   DYN_CHECK(s != nullptr, "session is NULL");
+  DYN_CHECK(slot >= 0 && slot < s->cfg.batch, "slot %lld outside [0, %d) (the descriptor's \"batch\")",
+            (long long)slot, s->cfg.batch);
   DYN_CHECK(s->kv_configured && s->pages > 0, "paged KV is not configured or has no pages");
   DYN_CHECK(tokens != nullptr, "tokens is NULL");
   // wrapper.c:1230-1235
@@ -919,7 +935,7 @@ int dyninfer_cuda_session_invoke_paged_chunk(dyninfer_cuda_session_t* s, const i
   if (rows == 1 && s->mega) {
     s->stage_host[0] = tokens[0];
     s->stage_host[1] = start_pos;
-    s->stage_host[2] = 0;
+    s->stage_host[2] = slot;
     MegaArgs ma;
     fill_mega_args(s, &ma, 0);
     DYN_CUDA(cudaMemcpyAsync(s->io_dev, s->stage_host, 24, cudaMemcpyHostToDevice, s->stream));
@@ -929,7 +945,7 @@ int dyninfer_cuda_session_invoke_paged_chunk(dyninfer_cuda_session_t* s, const i
     if (!s->decode_graph && capture(s, false, &s->decode_graph, &s->graph_nodes)) return 1;
     s->stage_host[0] = tokens[0];
     s->stage_host[1] = start_pos;
-    s->stage_host[2] = 0;
+    s->stage_host[2] = slot;
     DYN_CUDA(cudaGraphLaunch(s->decode_graph, s->stream));
     s->launches += s->graph_nodes;
   } else {
@@ -937,7 +953,7 @@ int dyninfer_cuda_session_invoke_paged_chunk(dyninfer_cuda_session_t* s, const i
     for (int64_t i = 0; i < rows; i++) {
       st[i] = tokens[i];
       st[rows + i] = start_pos + i;
-      st[2 * rows + i] = 0;
+      st[2 * rows + i] = slot;
     }
     DYN_CUDA(cudaMemcpyAsync(s->tokens_dev, st, rows * 8, cudaMemcpyHostToDevice, s->stream));
     DYN_CUDA(cudaMemcpyAsync(s->row_pos_dev, st + rows, rows * 8, cudaMemcpyHostToDevice, s->stream));
@@ -960,6 +976,60 @@ int dyninfer_cuda_session_invoke_paged_chunk(dyninfer_cuda_session_t* s, const i
     if (out_logits) *out_logits = nullptr;
     if (out_count) *out_count = 0;
   }
+  return 0;
+}
+
+// One decode step for `count` independent sequences: row i feeds tokens[i] at positions[i] into the
+// KV slot slots[i]; out_tokens[i] is the greedy next token of that sequence.
+int dyninfer_cuda_session_decode_batch(dyninfer_cuda_session_t* s, const int64_t* tokens,
+                                       const int64_t* positions, const int64_t* slots, size_t count,
+                                       int64_t* out_tokens, float** out_logits, int want_logits) {
+  DYN_CHECK(s != nullptr, "session is NULL");
+  DYN_CHECK(s->kv_configured && s->pages > 0, "paged KV is not configured or has no pages");
+  DYN_CHECK(tokens && positions && slots && out_tokens, "tokens, positions, slots or out_tokens is NULL");
+  DYN_CHECK(count >= 1 && (int64_t)count <= s->max_rows && (int)count <= s->cfg.batch,
+            "count %zu must be in [1, %d] (the descriptor's \"batch\")", count, s->cfg.batch);
+  DYN_CHECK(!want_logits || out_logits, "want_logits needs out_logits");
+  const int64_t rows = (int64_t)count;
+  const int64_t cap = (int64_t)(s->pages * s->page_size);
+  std::vector<char> used((size_t)s->cfg.batch, 0);
+  for (int64_t i = 0; i < rows; i++) {
+    DYN_CHECK(tokens[i] >= 0 && tokens[i] < s->cfg.vocab, "token id %lld at %lld outside [0, %d)",
+              (long long)tokens[i], (long long)i, s->cfg.vocab);
+    DYN_CHECK(positions[i] >= 0 && positions[i] < cap, "position %lld at %lld exceeds the KV capacity %lld",
+              (long long)positions[i], (long long)i, (long long)cap);
+    DYN_CHECK(slots[i] >= 0 && slots[i] < s->cfg.batch && !used[(size_t)slots[i]],
+              "slot %lld at %lld is out of range or used twice in one step", (long long)slots[i], (long long)i);
+    used[(size_t)slots[i]] = 1;
+  }
+  CounterScope scope(s);
+  DYN_CUDA(cudaSetDevice(s->device));
+  if (!s->batch_logits) {
+    if (dev_alloc(s, (void**)&s->batch_logits, (size_t)s->cfg.batch * s->cfg.vocab * 4) ||
+        dev_alloc(s, (void**)&s->batch_tokens_dev, (size_t)s->cfg.batch * 8))
+      return 1;
+  }
+  int64_t* st = s->stage_host + 8;
+  for (int64_t i = 0; i < rows; i++) {
+    st[i] = tokens[i];
+    st[rows + i] = positions[i];
+    st[2 * rows + i] = slots[i];
+  }
+  DYN_CUDA(cudaMemcpyAsync(s->tokens_dev, st, rows * 8, cudaMemcpyHostToDevice, s->stream));
+  DYN_CUDA(cudaMemcpyAsync(s->row_pos_dev, st + rows, rows * 8, cudaMemcpyHostToDevice, s->stream));
+  DYN_CUDA(cudaMemcpyAsync(s->row_seq_dev, st + 2 * rows, rows * 8, cudaMemcpyHostToDevice, s->stream));
+  if (enqueue_forward(s, rows, 0, true)) return 1;
+  DYN_CUDA(cudaMemcpyAsync(st, s->batch_tokens_dev, rows * 8, cudaMemcpyDeviceToHost, s->stream));
+  if (want_logits) {
+    if (!s->batch_logits_host &&
+        host_alloc(s, (void**)&s->batch_logits_host, (size_t)s->cfg.batch * s->cfg.vocab * 4))
+      return 1;
+    DYN_CUDA(cudaMemcpyAsync(s->batch_logits_host, s->batch_logits, (size_t)rows * s->cfg.vocab * 4,
+                             cudaMemcpyDeviceToHost, s->stream));
+  }
+  DYN_CUDA(cudaStreamSynchronize(s->stream));
+  for (int64_t i = 0; i < rows; i++) out_tokens[i] = st[i];
+  if (out_logits) *out_logits = want_logits ? s->batch_logits_host : nullptr;  // borrowed until the next call
   return 0;
 }
 

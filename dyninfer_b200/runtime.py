@@ -99,7 +99,8 @@ class CudaSession:
         self.kv_dtype = model.kv_dtype
         self.kv_elem = 4 if self.kv_dtype == "f32" else 2
         self.max_kv = int(model.max_kv)
-        desc = ck.model_descriptor(model.catalog, kv_dtype=self.kv_dtype, decode_kernel=model.decode_kernel)
+        desc = ck.model_descriptor(model.catalog, kv_dtype=self.kv_dtype, decode_kernel=model.decode_kernel,
+                                   batch=max(1, int(config.batch_size)))
         files = (_lib.ParameterFile * len(model.plan.file_paths))(
             *[_lib.ParameterFile(p.encode()) for p in model.plan.file_paths])
         self._keys = [p.external_key.encode() for p in model.plan.parameters]
@@ -116,7 +117,9 @@ class CudaSession:
     # -- lifetime
     def close(self):
         if getattr(self, "_h", None) and self._h.value:
-            lib().dyninfer_cuda_session_destroy(self._h)
+            native = _lib._lib          # already loaded; at interpreter shutdown modules may be half torn down
+            if native is not None:
+                native.dyninfer_cuda_session_destroy(self._h)
             self._h = C.c_void_p()
 
     __del__ = close
@@ -262,11 +265,11 @@ class CudaSession:
 
     def decode_phase_profile(self) -> dict:
         """Microseconds per phase kind in the last persistent-kernel launch (CTA 0's view)."""
-        out = (C.c_double * 16)()
-        check(lib().dyninfer_cuda_session_decode_phase_profile(self._h, out, 16))
+        out = (C.c_double * 24)()
+        check(lib().dyninfer_cuda_session_decode_phase_profile(self._h, out, 24))
         names = ("embed", "qkv", "attention", "o_proj", "gate_up", "down", "lm_head", "argmax", "total",
                  "t_stage", "t_wait_weights", "t_rows", "t_grid_barrier", "t_attn_prepare", "t_attn_scores",
-                 "t_attn_merge")
+                 "t_attn_merge", "t_attn_load", "t_attn_norm_reduce", "t_attn_rope", "t_attn_fetch_issue")
         return dict(zip(names, [float(v) for v in out]))
 
     def weight_bytes(self) -> int:
@@ -299,6 +302,83 @@ class LoadedModel:
 
     def create_session(self, config: SessionConfig | None = None) -> CudaSession:
         return CudaSession(self, config or SessionConfig())
+
+    def create_batched_session(self, config: SessionConfig) -> "BatchedCudaSession":
+        return BatchedCudaSession(self, config)
+
+
+class BatchedCudaSession(CudaSession):
+    """`config.batch_size` independent sequences sharing one weight upload and one KV pool (one
+    slot each). Extension of the cuda target: the reference session is batch 1. Prefill runs per
+    slot through the chunk call; `step` decodes every active slot in one pass over the weights."""
+
+    def __init__(self, model: "LoadedModel", config: SessionConfig):
+        if config.batch_size < 1:
+            raise DynInferError("batch_size must be >= 1")
+        super().__init__(model, config)
+        self.slots = int(config.batch_size)
+        self.positions = [0] * self.slots
+
+    def _require_batch_1(self):      # the single-sequence calls keep working on slot 0 only
+        return None
+
+    def prefill_slot(self, slot: int, tokens, want_logits: bool = False):
+        """Greedy first token (and optionally logits) of `tokens` placed in KV slot `slot` from position 0."""
+        tokens = [int(t) for t in tokens]
+        if not 0 <= slot < self.slots:
+            raise DynInferError(f"slot {slot} outside [0, {self.slots})")
+        if not tokens or len(tokens) > self._max_seq():
+            raise DynInferError(f"prefill length {len(tokens)} outside [1, {self._max_seq()}]")
+        self._ensure_pages()
+        cs = self.model.chunk_size
+        logits, token = None, -1
+        for ci in range(0, len(tokens), cs):
+            window, last = self._window(tokens[ci:ci + cs])
+            final = ci + cs >= len(tokens)
+            ptr, count, tok = C.POINTER(C.c_float)(), C.c_size_t(0), C.c_int64(-1)
+            check(lib().dyninfer_cuda_session_invoke_paged_chunk_slot(
+                self._h, window.ctypes.data_as(C.POINTER(C.c_int64)), window.size, int(last), ci, int(slot),
+                C.byref(ptr), C.byref(count), C.byref(tok), 1 if (want_logits and final) else 0))
+            token = int(tok.value)
+            if want_logits and final:
+                logits = np.ctypeslib.as_array(ptr, shape=(count.value,)).copy()
+        self.positions[slot] = len(tokens)
+        return (logits, token) if want_logits else token
+
+    def step(self, tokens: dict, want_logits: bool = False):
+        """One decode step: `tokens` maps slot -> token to feed. Returns slot -> next token
+        (and slot -> logits when asked)."""
+        slots = sorted(int(s) for s in tokens)
+        if not slots:
+            return ({}, {}) if want_logits else {}
+        for s in slots:
+            if not 0 <= s < self.slots:
+                raise DynInferError(f"slot {s} outside [0, {self.slots})")
+            if self.positions[s] >= self._max_seq():
+                raise DynInferError(f"slot {s}: decode position {self.positions[s]} exceeds session/KV limit {self._max_seq()}")
+        self._ensure_pages()
+        n = len(slots)
+        tok = np.array([int(tokens[s]) for s in slots], dtype=np.int64)
+        pos = np.array([self.positions[s] for s in slots], dtype=np.int64)
+        sl = np.array(slots, dtype=np.int64)
+        out = np.empty(n, dtype=np.int64)
+        ptr = C.POINTER(C.c_float)()
+        i64p = C.POINTER(C.c_int64)
+        check(lib().dyninfer_cuda_session_decode_batch(
+            self._h, tok.ctypes.data_as(i64p), pos.ctypes.data_as(i64p), sl.ctypes.data_as(i64p), n,
+            out.ctypes.data_as(i64p), C.byref(ptr), 1 if want_logits else 0))
+        for s in slots:
+            self.positions[s] += 1
+        nxt = {s: int(out[i]) for i, s in enumerate(slots)}
+        if not want_logits:
+            return nxt
+        vocab = self.metadata["vocabulary_size"]
+        lg = np.ctypeslib.as_array(ptr, shape=(n, vocab)).copy()
+        return nxt, {s: lg[i] for i, s in enumerate(slots)}
+
+    def reset(self):
+        super().reset()
+        self.positions = [0] * self.slots
 
 
 class ModelLoader:

@@ -208,6 +208,26 @@ typedef struct dyninfer_cuda_allocator_statistics_t {
 int dyninfer_cuda_session_allocator_statistics(const dyninfer_cuda_session_t* session,
                                                dyninfer_cuda_allocator_statistics_t* out_stats);
 
+/* ---- batching (extension: the reference session is batch 1) ----------------- */
+
+/* invoke_paged_chunk for KV slot `slot` of a session whose descriptor sets "batch" > 1: the same
+ * rules as dyninfer_cuda_session_invoke_paged_chunk (which is slot 0). Sequences in different
+ * slots are independent; each has its own positions. */
+int dyninfer_cuda_session_invoke_paged_chunk_slot(dyninfer_cuda_session_t* session,
+                                                  const int64_t* tokens, size_t token_count,
+                                                  int64_t last, int64_t start_pos, int64_t slot,
+                                                  float** out_logits, size_t* out_count,
+                                                  int64_t* out_token, int want_logits);
+
+/* One decode step for `count` sequences at once (count <= "batch"): row i feeds tokens[i] at
+ * positions[i] into slot slots[i] (all slots distinct) and out_tokens[i] receives the first strict
+ * maximum of its logits. With want_logits != 0, *out_logits points at [count, vocab] floats of
+ * session-owned pinned memory, borrowed until the next call. The linears run once for all rows
+ * (one pass over the weights), attention runs per sequence. */
+int dyninfer_cuda_session_decode_batch(dyninfer_cuda_session_t* session, const int64_t* tokens,
+                                       const int64_t* positions, const int64_t* slots, size_t count,
+                                       int64_t* out_tokens, float** out_logits, int want_logits);
+
 /* ---- session extensions (no reference precedent) --------------------------- */
 
 /* Total bytes of uploaded parameters (the reference's schema total_bytes used by

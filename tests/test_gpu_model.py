@@ -217,3 +217,42 @@ def test_persistent_kernel_long_context_split_kv(native_lib, oracle, tmp_path, k
             assert np.abs(outs[kernel][i] - want[i]).max() <= 1e-2
             assert helpers.cosine(outs[kernel][i], want[i]) >= 0.9999
         assert np.abs(outs["persistent"][i] - outs["graph"][i]).max() <= 1e-3
+
+
+@pytest.mark.parametrize("flavor,batch", [("gguf_q4_0", 3), ("mlx_u4", 5), ("gguf_mixed", 20)])
+def test_batched_decode_matches_per_sequence_oracle(native_lib, oracle, tmp_path, flavor, batch):
+    """`batch` sequences with different prompts and lengths share one session: every step decodes
+    all of them in one pass (20 rows go through the tensor-core GEMM where the shapes allow).
+    Each sequence must track its own single-sequence oracle run: logits max-abs <= 1e-2,
+    cosine >= 0.9999 (teacher-forced), and slots must not disturb each other."""
+    if flavor == "mlx_u4":
+        path = synth.write_qwen3_mlx(str(tmp_path / "mlx"), synth.TINY, seed=3)
+    else:
+        encs = {"attn_v": "gguf.q4_1", "ffn_down": "gguf.q8_0"} if flavor == "gguf_mixed" else None
+        path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), synth.TINY, seed=3, encodings=encs)
+    model = ModelLoader().load(path, max_kv=256, kv_dtype="f32", chunk_size=16)
+    cat = ck.open_catalog(path)
+    rng = np.random.default_rng(batch)
+    prompts = [rng.integers(0, synth.TINY["vocab"], size=int(rng.integers(1, 40))).tolist() for _ in range(batch)]
+    steps = 6
+    want = [oracle_run(oracle, cat, p, steps, kv_cap=256) for p in prompts]
+    with model.create_batched_session(SessionConfig(max_sequence_length=256, batch_size=batch)) as s:
+        feed = {}
+        for b, p in enumerate(prompts):
+            lg, tok = s.prefill_slot(b, p, want_logits=True)
+            assert np.abs(lg - want[b][0][0]).max() <= 1e-2 and helpers.cosine(lg, want[b][0][0]) >= 0.9999
+            feed[b] = want[b][1][0]
+        for i in range(steps):
+            nxt, logits = s.step(feed, want_logits=True)
+            for b in range(batch):
+                ref = want[b][0][i + 1]
+                assert np.abs(logits[b] - ref).max() <= 1e-2 and helpers.cosine(logits[b], ref) >= 0.9999
+                if nxt[b] != want[b][1][i + 1]:
+                    assert want[b][2][i + 1] < 1e-3            # only a near-tie may differ
+            feed = {b: want[b][1][i + 1] for b in range(batch)}
+        # a subset of the slots may step on its own; the others keep their state
+        sub = {0: want[0][1][steps], batch - 1: want[batch - 1][1][steps]}
+        assert set(s.step(sub)) == {0, batch - 1}
+        assert s.positions[0] == len(prompts[0]) + steps + 1 and s.positions[1] == len(prompts[1]) + steps
+        with pytest.raises(DynInferError):
+            s.step({batch: 1})

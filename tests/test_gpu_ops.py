@@ -102,12 +102,13 @@ def test_linear_ragged_and_full_shapes(native_lib, oracle, enc, n, k):
     assert helpers.rel_err(got, oracle.linear(ow, x, fast=True)) < 1e-4
 
 
+@pytest.mark.parametrize("enc", ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k"])
 @pytest.mark.parametrize("n,k", [(33, 512), (1000, 3072), (4096, 12288), (12288, 4096)])
-def test_linear_single_row_q4_0(native_lib, oracle, n, k):
-    """One activation row on Q4_0 (the decode shape): ragged last tile, split-K shapes, f32 and
-    bf16 activations, against the oracle's sequential and pairwise sums."""
+def test_linear_single_row_column_split(native_lib, oracle, enc, n, k):
+    """One activation row (the decode shape) on the column-split tensor-core kernels: ragged last
+    tile, split-K shapes, f32 and bf16 activations, against the oracle's pairwise sums."""
     from dyninfer_b200 import ops
-    dw, ow = make_pair(oracle, "gguf.q4_0", n, k, seed=n ^ k)
+    dw, ow = make_pair(oracle, enc, n, k, seed=n ^ k)
     x = np.random.default_rng(k).normal(size=(1, k)).astype(np.float32)
     want = oracle.linear(ow, x, fast=True)
     got = ops.linear(dw, torch.from_numpy(x).cuda()).cpu().numpy()

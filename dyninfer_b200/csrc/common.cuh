@@ -198,8 +198,12 @@ struct AttnArgs {
   float* ctx;  // [rows, nh*d]
   int64_t rows, nh, nkv, d, cap;
   int kv_type;
+  // >= 0: the rows are consecutive positions uniform_base + row of sequence uniform_seq even though
+  // row_pos / row_seq are given (prefill chunks); lets the tensor-core prefill kernel take them
+  int64_t uniform_base = -1, uniform_seq = 0;
 };
 int launch_attention(const AttnArgs& a, cudaStream_t s);
+int launch_attention_prefill(const AttnArgs& a, int64_t base_pos, int64_t seq, cudaStream_t s, bool* handled);
 
 size_t argmax_scratch_bytes(int64_t n);
 int launch_argmax(const float* v, int64_t n, int64_t* out, void* scratch, cudaStream_t s);

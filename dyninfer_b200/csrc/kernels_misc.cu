@@ -282,6 +282,13 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
   DYN_CHECK(a.d <= 256, "head_dim %lld unsupported (<= 256)", (long long)a.d);
   DYN_CHECK(a.nkv > 0 && a.nh % a.nkv == 0, "heads %lld not a multiple of kv heads %lld",
             (long long)a.nh, (long long)a.nkv);
+  if (!a.row_pos || a.uniform_base >= 0) {  // one sequence, consecutive positions: tensor-core kernel
+    bool handled = false;
+    if (launch_attention_prefill(a, a.row_pos ? a.uniform_base : a.base_pos, a.row_pos ? a.uniform_seq : 0, s,
+                                 &handled))
+      return 1;
+    if (handled) return 0;
+  }
   dim3 grid((unsigned)a.nh, (unsigned)a.rows);
   if (a.kv_type == E_F32)
     attention_kernel<E_F32><<<grid, ATT_WARPS * 32, 0, s>>>(a);

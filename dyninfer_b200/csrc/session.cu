@@ -66,7 +66,7 @@ struct dyninfer_cuda_session_t {
   // scratch
   int64_t max_rows = 0;
   float *hidden = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ctx = nullptr,
-        *act = nullptr, *logits = nullptr;
+        *act = nullptr, *up = nullptr, *logits = nullptr;
   int64_t *tokens_dev = nullptr, *row_pos_dev = nullptr, *row_seq_dev = nullptr,
           *out_token_dev = nullptr, *hist_dev = nullptr, *hist_count_dev = nullptr;
   size_t hist_cap = 0;
@@ -250,7 +250,8 @@ __global__ void advance_kernel(int64_t* tokens, int64_t* row_pos, const int64_t*
 
 // Enqueue the whole decoder for `rows` rows whose tokens / positions / slots are
 // already in device memory; logits and argmax come from row `logits_row`.
-int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows = false) {
+int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows = false,
+                    int64_t chunk_start = -1, int64_t chunk_slot = 0) {
   const ModelCfg& c = s->cfg;
   cudaStream_t st = s->stream;
   const int64_t H = c.hidden, qd = (int64_t)c.heads * c.head_dim,
@@ -281,19 +282,18 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
     aa.ctx = s->ctx;
     aa.rows = rows, aa.nh = c.heads, aa.nkv = c.kv_heads, aa.d = c.head_dim, aa.cap = cap;
     aa.kv_type = s->kv_type;
+    aa.uniform_base = chunk_start, aa.uniform_seq = chunk_slot;  // a prefill chunk: consecutive positions
     if (launch_attention(aa, st)) return 1;
     if (launch_linear(L.o, s->ctx, E_F32, rows, s->hidden, s->hidden, st)) return 1;
     if (launch_rms_norm(s->hidden, L.ffn_norm.ptr, L.ffn_norm.type, rows, H, c.eps, s->xn, st))
       return 1;
-    if (L.gate.enc == L.up.enc) {
+    if (L.gate.enc == L.up.enc && rows <= 16) {
       if (launch_linear_swiglu(L.gate, L.up, s->xn, rows, s->act, st)) return 1;
     } else {
-      // mixed encodings: two products, then the activation (q and ctx are free here)
+      // many rows (tensor-core GEMM) or mixed encodings: two products, then the activation
       if (launch_linear(L.gate, s->xn, E_F32, rows, s->act, nullptr, st)) return 1;
-      float* up_tmp = s->ctx;  // ctx holds rows*qd floats; only used when inter <= qd
-      DYN_CHECK((int64_t)c.inter <= qd, "gate/up with different encodings need inter <= heads*head_dim");
-      if (launch_linear(L.up, s->xn, E_F32, rows, up_tmp, nullptr, st)) return 1;
-      if (launch_silu_mul(s->act, up_tmp, rows * c.inter, s->act, st)) return 1;
+      if (launch_linear(L.up, s->xn, E_F32, rows, s->up, nullptr, st)) return 1;
+      if (launch_silu_mul(s->act, s->up, rows * c.inter, s->act, st)) return 1;
     }
     if (launch_linear(L.down, s->act, E_F32, rows, s->hidden, s->hidden, st)) return 1;
   }
@@ -724,7 +724,7 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
   cudaSetDevice(s->device);
   if (s->stream) cudaStreamSynchronize(s->stream);
   destroy_graphs(s);
-  void* dev[] = {s->arena, s->kcache, s->vcache, s->hidden, s->xn, s->q, s->k, s->v, s->ctx, s->act,
+  void* dev[] = {s->arena, s->kcache, s->vcache, s->hidden, s->xn, s->q, s->k, s->v, s->ctx, s->act, s->up,
                  s->logits, s->tokens_dev, s->row_pos_dev, s->row_seq_dev, s->out_token_dev,
                  s->hist_dev, s->hist_count_dev, s->argmax_scratch, s->mega_layers, s->io_dev,
                  s->bar_dev, s->attn_part, s->amax_val, s->amax_idx, s->prof_dev, s->prog_dev,
@@ -772,6 +772,7 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
         dev_alloc(s, (void**)&s->v, (size_t)rows * kvd * 4) ||
         dev_alloc(s, (void**)&s->ctx, (size_t)rows * qd * 4) ||
         dev_alloc(s, (void**)&s->act, (size_t)rows * c.inter * 4) ||
+        dev_alloc(s, (void**)&s->up, (size_t)rows * c.inter * 4) ||
         dev_alloc(s, (void**)&s->tokens_dev, (size_t)rows * 8) ||
         dev_alloc(s, (void**)&s->row_pos_dev, (size_t)rows * 8) ||
         dev_alloc(s, (void**)&s->row_seq_dev, (size_t)rows * 8) ||
@@ -959,7 +960,7 @@ int dyninfer_cuda_session_invoke_paged_chunk_slot(dyninfer_cuda_session_t* s, co
     DYN_CUDA(cudaMemcpyAsync(s->row_pos_dev, st + rows, rows * 8, cudaMemcpyHostToDevice, s->stream));
     DYN_CUDA(cudaMemcpyAsync(s->row_seq_dev, st + 2 * rows, rows * 8, cudaMemcpyHostToDevice,
                              s->stream));
-    if (enqueue_forward(s, rows, last)) return 1;
+    if (enqueue_forward(s, rows, last, false, start_pos, slot)) return 1;
     DYN_CUDA(cudaMemcpyAsync(s->stage_host + 3, s->out_token_dev, 8, cudaMemcpyDeviceToHost,
                              s->stream));
   }

@@ -256,3 +256,24 @@ def test_batched_decode_matches_per_sequence_oracle(native_lib, oracle, tmp_path
         assert s.positions[0] == len(prompts[0]) + steps + 1 and s.positions[1] == len(prompts[1]) + steps
         with pytest.raises(DynInferError):
             s.step({batch: 1})
+
+
+@pytest.mark.parametrize("kv", ["bf16", "f16"])
+def test_long_prompt_prefill_tensor_core_path(native_lib, oracle, tmp_path, kv):
+    """A 150-token prompt in chunks of 64 on a head-dim-128 model: the linears run on the tcgen05
+    GEMM and attention on the tensor-core prefill kernel. The logits after the prompt and over the
+    following greedy steps must match the oracle (logits max-abs <= 1e-2, cosine >= 0.9999)."""
+    cfg = dict(layers=2, hidden=256, heads=2, kv_heads=1, head_dim=128, intermediate=512, vocab=512, eps=1e-6,
+               theta=1e6)
+    path = synth.write_qwen3_gguf(str(tmp_path / "d128.gguf"), cfg, seed=21)
+    model = ModelLoader().load(path, max_kv=512, kv_dtype=kv, chunk_size=64)
+    cat = ck.open_catalog(path)
+    prompt = np.random.default_rng(9).integers(0, cfg["vocab"], size=150).tolist()
+    steps = 4
+    want_logits, want_toks, margins = oracle_run(oracle, cat, prompt, steps, kv_round=2 if kv == "bf16" else 1)
+    with model.create_session(SessionConfig(max_sequence_length=512)) as s:
+        lg = s.prefill(prompt).values
+        assert np.abs(lg - want_logits[0]).max() <= 1e-2 and helpers.cosine(lg, want_logits[0]) >= 0.9999
+        for i in range(steps):
+            lg = s.decode(want_toks[i]).values
+            assert np.abs(lg - want_logits[i + 1]).max() <= 1e-2 and helpers.cosine(lg, want_logits[i + 1]) >= 0.9999

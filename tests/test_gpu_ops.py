@@ -201,6 +201,31 @@ def test_attention_vs_oracle(native_lib, oracle, dtype, s, start, d, nh, nkv):
     assert np.abs(got - want).max() < 2e-5
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("s,start,nh,nkv", [(100, 37, 4, 2), (64, 0, 2, 2), (130, 500, 4, 1)])
+def test_attention_prefill_tensor_core(native_lib, oracle, dtype, s, start, nh, nkv):
+    """32 or more consecutive rows of one sequence on a 2-byte cache take the tensor-core
+    flash-attention kernel (head dim 128): ragged row blocks, GQA, a start position in the middle
+    of a key block. Q and P enter as hi+lo pairs, so the result stays within 1e-3 relative of the
+    f32 oracle (typically 1e-4)."""
+    from dyninfer_b200 import ops
+    d, cap = 128, 768
+    rng = np.random.default_rng(s + start)
+    q = rng.normal(size=(s, nh, d)).astype(np.float32)
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float16
+    kc = torch.from_numpy(rng.normal(size=(nkv, cap, d)).astype(np.float32)).to(tdt)
+    vc = torch.from_numpy(rng.normal(size=(nkv, cap, d)).astype(np.float32)).to(tdt)
+    kc[:, start + s:] = float("nan")                 # never-written rows must not leak into the result
+    vc[:, start + s:] = float("nan")
+    got = ops.attention(torch.from_numpy(q).cuda(), kc.cuda(), vc.cuda(), start).cpu().numpy()
+    kf, vf = kc.float().numpy(), vc.float().numpy()
+    kf[:, start + s:] = 0.0
+    vf[:, start + s:] = 0.0
+    want = oracle.attention(q, kf, vf, start, s)
+    assert np.isfinite(got).all()
+    assert helpers.rel_err(got, want) < 1e-3
+
+
 def test_argmax_first_maximum(native_lib, oracle):
     from dyninfer_b200 import ops
     rng = np.random.default_rng(3)

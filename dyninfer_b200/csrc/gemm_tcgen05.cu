@@ -428,7 +428,13 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
   if (!tg_shape_ok(w, M)) return 0;
   const int64_t K = w.cols;
   // activation rows per CTA: as many as fit one accumulator (256), rounded up to the MMA granule
-  const int64_t mtiles = (M + 255) / 256;
+  // ... unless that leaves most SMs idle (few weight-row tiles): then narrower activation tiles, down
+  // to 32 rows, so that more CTAs share the work (each re-dequantises its weight tile, which is
+  // cheap next to idle SMs)
+  const int64_t ntiles = (w.rows + TG_BM - 1) / TG_BM;
+  int64_t cap_rows = 256;
+  while (cap_rows > 32 && ntiles * ((M + cap_rows / 2 - 1) / (cap_rows / 2)) <= 148) cap_rows /= 2;  // stay within one wave
+  const int64_t mtiles = (M + cap_rows - 1) / cap_rows;
   int bn = (int)((M + mtiles - 1) / mtiles);
   bn = (bn + 15) / 16 * 16;
   const int64_t Mpad = mtiles * bn;

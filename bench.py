@@ -199,6 +199,29 @@ def time_lm_head(path, batches=5, reps=8):
     return statistics.median(times), c.length, p.encoding
 
 
+def time_prefill(model, n=2048, reps=3):
+    """Prefill tok/s of an `n`-token random prompt through the public session call (host clock
+    around `prefill_argmax`, which ends with the argmax token back on the host)."""
+    import torch
+    from dyninfer_b200 import synth
+    from dyninfer_b200.runtime import SessionConfig
+    ids = np.random.default_rng(SEED + 1).integers(0, synth.QWEN3_0_6B["vocab"], size=n).tolist()
+    old_max = model.max_kv
+    model.max_kv = max(model.max_kv, n + 8)
+    times = []
+    with model.create_session(SessionConfig(max_sequence_length=n + 8)) as s:
+        s.prefill_argmax(ids)                      # first use: allocations, tensor maps
+        for _ in range(reps):
+            s.reset()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            s.prefill_argmax(ids)
+            torch.cuda.synchronize()
+            times.append(time.perf_counter() - t0)
+    model.max_kv = old_max
+    return n / statistics.median(times)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -303,6 +326,8 @@ def main():
                                       "frac": achieved / hbm_peak, "bytes_per_launch": lm_bytes,
                                       "ms_per_launch": lm_ms},
         }
+        out["prefill"] = {"tokens": 2048, "chunk": model.chunk_size, "tokens_per_s": time_prefill(model),
+                          "note": "tcgen05 dequant GEMM + tensor-core flash attention, bf16 KV"}
         if not args.no_cpu_baseline:
             steps = 24
             tps, cores, dt = cpu_decode_rate(path, steps)

@@ -257,6 +257,78 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
           use++;
         }
       }
+    } else if constexpr (ENC == E_MLX_U4) {
+      // Fast path for MLX affine U4 (word j of a row = elements 8j .. 8j+7, nibble k = bits [4k, 4k+4);
+      // w = q * scale + bias per group, mlx_affine.rs:284-290,590-600). Lane = (row sub-index, word j of
+      // the chunk's 8 words): one aligned word + the group's scale and bias -> 8 consecutive f16
+      // weights = one 16-byte store. nibble | 0x6400 = 1024 + q; subtracting 1024 is exact and the
+      // f16 fused multiply-add q * s + b rounds once.
+      constexpr int NJ = TG_BM / (TG_GWARPS * 4);
+      const int j = lane & 7, rsub = lane >> 3;
+      const int ael = a.w.aux == E_F32 ? 4 : 2;
+      const int64_t gpr = K / a.w.group;  // groups per row
+      const uint32_t* wordp[NJ];
+      const uint8_t *scp[NJ], *bip[NJ];
+#pragma unroll
+      for (int jj = 0; jj < NJ; jj++) {
+        int64_t row = n0 + wg * 4 + rsub + 16 * jj;
+        if (row > N - 1) row = N - 1;
+        wordp[jj] = reinterpret_cast<const uint32_t*>(a.w.data) + row * (K / 8) + j;
+        scp[jj] = a.w.scales + row * gpr * ael;
+        bip[jj] = a.w.biases + row * gpr * ael;
+      }
+      uint32_t qw[2][NJ];
+      float sc[2][NJ], bi[2][NJ];
+      auto fetch = [&](int kc, uint32_t (&q)[NJ], float (&s_)[NJ], float (&b_)[NJ]) {
+        const int64_t gi = ((int64_t)kc * TG_BK + 8 * j) / a.w.group;
+#pragma unroll
+        for (int jj = 0; jj < NJ; jj++) {
+          q[jj] = wordp[jj][(int64_t)kc * 8];
+          s_[jj] = aux_load(scp[jj], a.w.aux, gi);
+          b_[jj] = aux_load(bip[jj], a.w.aux, gi);
+        }
+      };
+      if (grp < nk) fetch(grp, qw[0], sc[0], bi[0]);
+      const __half2 c1024 = __floats2half2_rn(1024.f, 1024.f);
+      bool live = true;
+      int use = 0;
+      for (int kc0 = grp; kc0 < nk && live; kc0 += 2 * TG_GROUPS) {
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          const int kc = kc0 + u * TG_GROUPS;
+          if (kc >= nk) break;
+          if (kc + TG_GROUPS < nk) fetch(kc + TG_GROUPS, qw[u ^ 1], sc[u ^ 1], bi[u ^ 1]);
+          if (use > 0 && !mbar_wait_bounded(empty_bar + grp, (unsigned)(use - 1) & 1u, TG_SPINS, &s_abort)) {
+            if (!s_abort) s_abort = 1;
+            live = false;
+            break;
+          }
+#pragma unroll
+          for (int jj = 0; jj < NJ; jj++) {
+            const int r = wg * 4 + rsub + 16 * jj;
+            const uint32_t w = qw[u][jj];
+            const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;   // nibbles 0,2,4,6 / 1,3,5,7
+            const __half2 s2 = __float2half2_rn(sc[u][jj]), b2 = __float2half2_rn(bi[u][jj]);
+            uint32_t pr[4];
+            pr[0] = (__byte_perm(lo, hi, 0x0400) & 0x00FF00FFu) | 0x64006400u;      // (n0, n1)
+            pr[1] = (__byte_perm(lo, hi, 0x0501) & 0x00FF00FFu) | 0x64006400u;      // (n2, n3)
+            pr[2] = (__byte_perm(lo, hi, 0x0602) & 0x00FF00FFu) | 0x64006400u;      // (n4, n5)
+            pr[3] = (__byte_perm(lo, hi, 0x0703) & 0x00FF00FFu) | 0x64006400u;      // (n6, n7)
+            uint4 out;
+            uint32_t* o = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              const __half2 v = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&pr[e]), c1024), s2, b2);
+              o[e] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            *reinterpret_cast<uint4*>(abase + r * 128 + ((j ^ (r & 7)) << 4)) = out;
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full_bar + grp);
+          use++;
+        }
+      }
     } else {
       constexpr int RPP = 32 / CI::IPR;  // rows per warp pass
       const int it = lane % CI::IPR, rsub = lane / CI::IPR;

@@ -95,6 +95,7 @@ struct dyninfer_cuda_session_t {
   // graphs
   cudaGraphExec_t decode_graph = nullptr;  // H2D token/pos + forward + D2H token
   cudaGraphExec_t loop_graph = nullptr;    // forward + device-side advance
+  std::map<int64_t, std::pair<cudaGraphExec_t, uint64_t>> batch_graphs;  // rows -> batched step (graph, nodes)
   uint64_t graph_nodes = 0, loop_nodes = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   // statistics
@@ -234,6 +235,9 @@ void destroy_graphs(Session* s) {
   if (s->decode_graph) cudaGraphExecDestroy(s->decode_graph);
   if (s->loop_graph) cudaGraphExecDestroy(s->loop_graph);
   s->decode_graph = s->loop_graph = nullptr;
+  for (auto& kv : s->batch_graphs)
+    if (kv.second.first) cudaGraphExecDestroy(kv.second.first);
+  s->batch_graphs.clear();
 }
 
 // Device-side greedy feedback: the produced token becomes the next input, the
@@ -349,6 +353,29 @@ int capture(Session* s, bool loop, cudaGraphExec_t* out, uint64_t* nodes) {
   DYN_CUDA(e);
   *nodes = s->launches - before;
   s->launches = before;  // capture enqueues nothing; replays are counted per launch
+  cudaError_t ie = cudaGraphInstantiate(out, g, 0);
+  cudaGraphDestroy(g);
+  DYN_CUDA(ie);
+  return 0;
+}
+
+// Batched step for `rows` sequences as a graph: tokens / positions / slots are read from the device
+// buffers the caller fills before every replay.
+int capture_batch(Session* s, int64_t rows, cudaGraphExec_t* out, uint64_t* nodes) {
+  cudaGraph_t g = nullptr;
+  const uint64_t before = s->launches;
+  DYN_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+  const int rc = enqueue_forward(s, rows, 0, true);
+  cudaError_t e = cudaStreamEndCapture(s->stream, &g);
+  if (rc) {
+    if (g) cudaGraphDestroy(g);
+    std::string keep = dyninfer_cuda_last_error();
+    set_error("graph capture of the batched step failed: %s", keep.c_str());
+    return 1;
+  }
+  DYN_CUDA(e);
+  *nodes = s->launches - before;
+  s->launches = before;
   cudaError_t ie = cudaGraphInstantiate(out, g, 0);
   cudaGraphDestroy(g);
   DYN_CUDA(ie);
@@ -1003,6 +1030,11 @@ int dyninfer_cuda_session_decode_batch(dyninfer_cuda_session_t* s, const int64_t
               "slot %lld at %lld is out of range or used twice in one step", (long long)slots[i], (long long)i);
     used[(size_t)slots[i]] = 1;
   }
+  if (rows == 1 && !want_logits) {  // a single sequence: the single-token fast path serves any slot
+    if (out_logits) *out_logits = nullptr;
+    return dyninfer_cuda_session_invoke_paged_chunk_slot(s, tokens, 1, 0, positions[0], slots[0], nullptr, nullptr,
+                                                         out_tokens, 0);
+  }
   CounterScope scope(s);
   DYN_CUDA(cudaSetDevice(s->device));
   if (!s->batch_logits) {
@@ -1019,7 +1051,15 @@ int dyninfer_cuda_session_decode_batch(dyninfer_cuda_session_t* s, const int64_t
   DYN_CUDA(cudaMemcpyAsync(s->tokens_dev, st, rows * 8, cudaMemcpyHostToDevice, s->stream));
   DYN_CUDA(cudaMemcpyAsync(s->row_pos_dev, st + rows, rows * 8, cudaMemcpyHostToDevice, s->stream));
   DYN_CUDA(cudaMemcpyAsync(s->row_seq_dev, st + 2 * rows, rows * 8, cudaMemcpyHostToDevice, s->stream));
-  if (enqueue_forward(s, rows, 0, true)) return 1;
+  auto it = s->batch_graphs.find(rows);
+  if (it == s->batch_graphs.end()) {
+    cudaGraphExec_t exec = nullptr;
+    uint64_t nodes = 0;
+    if (capture_batch(s, rows, &exec, &nodes)) return 1;
+    it = s->batch_graphs.emplace(rows, std::make_pair(exec, nodes)).first;
+  }
+  DYN_CUDA(cudaGraphLaunch(it->second.first, s->stream));
+  s->launches += it->second.second;
   DYN_CUDA(cudaMemcpyAsync(st, s->batch_tokens_dev, rows * 8, cudaMemcpyDeviceToHost, s->stream));
   if (want_logits) {
     if (!s->batch_logits_host &&

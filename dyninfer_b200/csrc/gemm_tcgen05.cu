@@ -36,7 +36,7 @@ constexpr int TG_GROUPS = 4;         // producer groups; group g fills stage g w
 constexpr int TG_GWARPS = 4;         // warps per group
 constexpr int TG_A_WARPS = TG_GROUPS * TG_GWARPS, TG_B_WARPS = 1;
 constexpr int TG_THREADS = (TG_A_WARPS + TG_B_WARPS + 1) * 32;
-constexpr int TG_STAGES = TG_GROUPS;
+constexpr int TG_MAX_SLOTS = 2 * TG_GROUPS;  // a group owns one pipeline slot, or two when they fit
 constexpr int TG_A_BYTES = TG_BM * 128;
 constexpr long long TG_SPINS = 1LL << 24;
 
@@ -118,6 +118,7 @@ struct TgArgs {
   int64_t M;
   int bn;            // activation rows per CTA (multiple of 16, <= 256)
   int tmem_cols;     // power of two >= bn, >= 32
+  int nslot;         // pipeline slots: 4, or 8 when the stages are small enough
   float* y;          // [M, N]
   const float* residual;
   int* error;
@@ -144,7 +145,8 @@ template <int ENC>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) uint8_t tg_smem[];
-  __shared__ uint64_t full_bar[TG_STAGES], empty_bar[TG_STAGES], accum_bar;
+  __shared__ uint64_t full_bar[TG_MAX_SLOTS], empty_bar[TG_MAX_SLOTS], accum_bar;
+  const int nslot = a.nslot;  // TG_GROUPS or 2 * TG_GROUPS; chunk kc uses slot kc % nslot and belongs to group kc % TG_GROUPS
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
   using C = Codec<ENC>;
@@ -159,7 +161,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
 
   if (tid == 0) {
     s_abort = 0;
-    for (int i = 0; i < TG_STAGES; i++) {
+    for (int i = 0; i < TG_MAX_SLOTS; i++) {
       mbar_init(full_bar + i, TG_GWARPS + TG_B_WARPS);
       mbar_init(empty_bar + i, 1);
     }
@@ -182,7 +184,6 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
     // Four groups of four warps; group g produces chunks g, g + 4, ... into stage g, so the fixed
     // costs of a hand-over (proxy fence, barrier round trip) of up to four chunks overlap.
     const int grp = warp / TG_GWARPS, wg = warp % TG_GWARPS;
-    uint8_t* abase = smem + (size_t)grp * stage_bytes;
     if constexpr (ENC == E_Q4_0) {
       // Fast path. Lane = (row sub-index, block of the chunk, quarter t): 4 quant bytes + the block
       // scale -> 8 weights. The raw bytes of the group's next chunk are fetched before the current
@@ -191,37 +192,46 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
       // subtracting 1032, or multiplying by 1/16 and subtracting 72, is exact; the product with d
       // rounds once, exactly like rounding the f32 value.
       constexpr int NJ = TG_BM / (TG_GWARPS * 4);  // rows per lane and chunk
-      const int blk2 = (lane >> 2) & 1, t = lane & 3, rsub = lane >> 3;
-      const int64_t rb = a.w.row_bytes();
-      const uint8_t* rowp[NJ];
+      const int blk2 = (lane >> 2) & 1, t = lane & 3, rsub = lane >> 3, l8 = lane & 7;
+      // A row's chunk is 36 bytes = 9 aligned words (rows are multiples of 36 bytes). The 8 lanes of
+      // a row fetch words 0..7 (lane 0 of the row also word 8) with 32-bit loads and pass them on by
+      // shuffle: a third of the load instructions and far fewer cache transactions than 2-byte loads.
+      const int64_t rw = a.w.row_bytes() / 4;
+      const uint32_t* roww[NJ];
 #pragma unroll
       for (int j = 0; j < NJ; j++) {
         int64_t row = n0 + wg * 4 + rsub + 16 * j;
         if (row > N - 1) row = N - 1;
-        rowp[j] = a.w.data + row * rb + blk2 * 18;
+        roww[j] = reinterpret_cast<const uint32_t*>(a.w.data) + row * rw;
       }
-      uint32_t qa[2][NJ], qb[2][NJ], d[2][NJ];  // quant halves stay apart until use: no early dependent op
-      auto fetch = [&](int kc, uint32_t (&qlo)[NJ], uint32_t (&qhi)[NJ], uint32_t (&dd)[NJ]) {
+      uint32_t qa[2][NJ], qb[2][NJ];  // word l8 of the chunk; word 8 (lane 0 of each row only)
+      auto fetch = [&](int kc, uint32_t (&wa)[NJ], uint32_t (&wb)[NJ]) {
 #pragma unroll
         for (int j = 0; j < NJ; j++) {
-          const uint8_t* p = rowp[j] + (int64_t)kc * 36;
-          dd[j] = t == 0 ? ld_u16(p) : 0u;  // one scale load per block; the other quarters get it by shuffle
-          qlo[j] = ld_u16(p + 2 + 4 * t);
-          qhi[j] = ld_u16(p + 4 + 4 * t);
+          const uint32_t* p = roww[j] + (int64_t)kc * 9;
+          wa[j] = p[l8];
+          wb[j] = l8 == 0 ? p[8] : 0u;
         }
       };
-      if (grp < nk) fetch(grp, qa[0], qb[0], d[0]);
+      // where this lane's 4 quant bytes and scale live among the 9 words:
+      //   block 0: scale = low half of word 0, quants = bytes 2+4t.. = words t, t+1 shifted by 16 bits
+      //   block 1: scale = high half of word 4, quants = word 5+t (word 8 for t = 3)
+      const int base8 = lane & ~7;
+      const int src_x = base8 + (blk2 ? ((5 + t) & 7) : t), src_y = base8 + ((t + 1) & 7);
+      const int src_d = base8 + (blk2 ? 4 : 0);
+      if (grp < nk) fetch(grp, qa[0], qb[0]);
       const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f), c72 = __floats2half2_rn(72.f, 72.f);
       const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
       bool live = true;
-      int use = 0;  // how many times this group has filled its stage
       for (int kc0 = grp; kc0 < nk && live; kc0 += 2 * TG_GROUPS) {
 #pragma unroll
         for (int u = 0; u < 2; u++) {
           const int kc = kc0 + u * TG_GROUPS;
           if (kc >= nk) break;
-          if (kc + TG_GROUPS < nk) fetch(kc + TG_GROUPS, qa[u ^ 1], qb[u ^ 1], d[u ^ 1]);
-          if (use > 0 && !mbar_wait_bounded(empty_bar + grp, (unsigned)(use - 1) & 1u, TG_SPINS, &s_abort)) {
+          if (kc + TG_GROUPS < nk) fetch(kc + TG_GROUPS, qa[u ^ 1], qb[u ^ 1]);
+          const int slot = kc % nslot;
+          uint8_t* abase = smem + (size_t)slot * stage_bytes;
+          if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / nslot - 1) & 1u, TG_SPINS, &s_abort)) {
             if (!s_abort) s_abort = 1;
             live = false;
             break;
@@ -229,8 +239,12 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
 #pragma unroll
           for (int j = 0; j < NJ; j++) {
             const int r = wg * 4 + rsub + 16 * j;
-            const uint32_t w = qa[u][j] | (qb[u][j] << 16);
-            const __half dh = __ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, d[u][j], lane & ~3));
+            const uint32_t x = __shfl_sync(0xffffffffu, qa[u][j], src_x);
+            const uint32_t x8 = __shfl_sync(0xffffffffu, qb[u][j], base8);
+            const uint32_t y = __shfl_sync(0xffffffffu, qa[u][j], src_y);
+            const uint32_t dw = __shfl_sync(0xffffffffu, qa[u][j], src_d);
+            const uint32_t w = blk2 ? (t == 3 ? x8 : x) : __funnelshift_r(x, y, 16);
+            const __half dh = __ushort_as_half((unsigned short)(blk2 ? dw >> 16 : dw & 0xffffu));
             const __half2 d2 = __halves2half2(dh, dh);
             uint32_t l02 = (w & 0x000F000Fu) | 0x64006400u, l13 = ((w >> 8) & 0x000F000Fu) | 0x64006400u;
             uint32_t h02 = (w & 0x00F000F0u) | 0x64006400u, h13 = ((w >> 8) & 0x00F000F0u) | 0x64006400u;
@@ -253,8 +267,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
           }
           fence_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(full_bar + grp);
-          use++;
+          if (lane == 0) mbar_arrive(full_bar + slot);
         }
       }
     } else if constexpr (ENC == E_MLX_U4) {
@@ -278,27 +291,27 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
         bip[jj] = a.w.biases + row * gpr * ael;
       }
       uint32_t qw[2][NJ];
-      float sc[2][NJ], bi[2][NJ];
-      auto fetch = [&](int kc, uint32_t (&q)[NJ], float (&s_)[NJ], float (&b_)[NJ]) {
+      float ax[2][NJ];  // even lanes hold the group's scale, odd lanes its bias (lane pairs share a group)
+      auto fetch = [&](int kc, uint32_t (&q)[NJ], float (&x_)[NJ]) {
         const int64_t gi = ((int64_t)kc * TG_BK + 8 * j) / a.w.group;
 #pragma unroll
         for (int jj = 0; jj < NJ; jj++) {
           q[jj] = wordp[jj][(int64_t)kc * 8];
-          s_[jj] = aux_load(scp[jj], a.w.aux, gi);
-          b_[jj] = aux_load(bip[jj], a.w.aux, gi);
+          x_[jj] = aux_load((j & 1) ? bip[jj] : scp[jj], a.w.aux, gi);
         }
       };
-      if (grp < nk) fetch(grp, qw[0], sc[0], bi[0]);
+      if (grp < nk) fetch(grp, qw[0], ax[0]);
       const __half2 c1024 = __floats2half2_rn(1024.f, 1024.f);
       bool live = true;
-      int use = 0;
       for (int kc0 = grp; kc0 < nk && live; kc0 += 2 * TG_GROUPS) {
 #pragma unroll
         for (int u = 0; u < 2; u++) {
           const int kc = kc0 + u * TG_GROUPS;
           if (kc >= nk) break;
-          if (kc + TG_GROUPS < nk) fetch(kc + TG_GROUPS, qw[u ^ 1], sc[u ^ 1], bi[u ^ 1]);
-          if (use > 0 && !mbar_wait_bounded(empty_bar + grp, (unsigned)(use - 1) & 1u, TG_SPINS, &s_abort)) {
+          if (kc + TG_GROUPS < nk) fetch(kc + TG_GROUPS, qw[u ^ 1], ax[u ^ 1]);
+          const int slot = kc % nslot;
+          uint8_t* abase = smem + (size_t)slot * stage_bytes;
+          if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / nslot - 1) & 1u, TG_SPINS, &s_abort)) {
             if (!s_abort) s_abort = 1;
             live = false;
             break;
@@ -308,7 +321,8 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
             const int r = wg * 4 + rsub + 16 * jj;
             const uint32_t w = qw[u][jj];
             const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;   // nibbles 0,2,4,6 / 1,3,5,7
-            const __half2 s2 = __float2half2_rn(sc[u][jj]), b2 = __float2half2_rn(bi[u][jj]);
+            const __half2 s2 = __float2half2_rn(__shfl_sync(0xffffffffu, ax[u][jj], lane & ~1));
+            const __half2 b2 = __float2half2_rn(__shfl_sync(0xffffffffu, ax[u][jj], lane | 1));
             uint32_t pr[4];
             pr[0] = (__byte_perm(lo, hi, 0x0400) & 0x00FF00FFu) | 0x64006400u;      // (n0, n1)
             pr[1] = (__byte_perm(lo, hi, 0x0501) & 0x00FF00FFu) | 0x64006400u;      // (n2, n3)
@@ -325,16 +339,16 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
           }
           fence_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(full_bar + grp);
-          use++;
+          if (lane == 0) mbar_arrive(full_bar + slot);
         }
       }
     } else {
       constexpr int RPP = 32 / CI::IPR;  // rows per warp pass
       const int it = lane % CI::IPR, rsub = lane / CI::IPR;
-      int use = 0;
-      for (int kc = grp; kc < nk; kc += TG_GROUPS, use++) {
-        if (use > 0 && !mbar_wait_bounded(empty_bar + grp, (unsigned)(use - 1) & 1u, TG_SPINS, &s_abort)) {
+      for (int kc = grp; kc < nk; kc += TG_GROUPS) {
+        const int slot = kc % nslot;
+        uint8_t* abase = smem + (size_t)slot * stage_bytes;
+        if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / nslot - 1) & 1u, TG_SPINS, &s_abort)) {
           if (!s_abort) s_abort = 1;
           break;
         }
@@ -363,16 +377,16 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
         }
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(full_bar + grp);
+        if (lane == 0) mbar_arrive(full_bar + slot);
       }
     }
   } else if (warp < TG_A_WARPS + TG_B_WARPS) {
     // ---------------- B producer: one TMA tile (bn rows x 64 k, swizzled by the hardware) per stage -----
     if (lane == 0) {
       for (int kc = 0; kc < nk; kc++) {
-        const int slot = kc % TG_STAGES;
-        if (kc >= TG_STAGES &&
-            !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / TG_STAGES - 1) & 1u, TG_SPINS, &s_abort)) {
+        const int slot = kc % nslot;
+        if (kc >= nslot &&
+            !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / nslot - 1) & 1u, TG_SPINS, &s_abort)) {
           if (!s_abort) s_abort = 1;
           break;
         }
@@ -386,8 +400,8 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
       const uint32_t idesc = umma_idesc(bn);
       bool ok = true;
       for (int kc = 0; kc < nk && ok; kc++) {
-        const int slot = kc % TG_STAGES;
-        ok = mbar_wait_bounded(full_bar + slot, (unsigned)(kc / TG_STAGES) & 1u, TG_SPINS, &s_abort);
+        const int slot = kc % nslot;
+        ok = mbar_wait_bounded(full_bar + slot, (unsigned)(kc / nslot) & 1u, TG_SPINS, &s_abort);
         if (!ok) {
           if (!s_abort) s_abort = 2;
           break;
@@ -530,7 +544,10 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
     return 1;
   }
   const dim3 grid((unsigned)((w.rows + TG_BM - 1) / TG_BM), (unsigned)mtiles);
-  const size_t smem = (size_t)TG_STAGES * (TG_A_BYTES + (size_t)bn * 128) + 1024;
+  const size_t stage_b = TG_A_BYTES + (size_t)bn * 128;
+  const int nslot = 2 * TG_GROUPS * stage_b + 1024 <= 200 * 1024 ? 2 * TG_GROUPS : TG_GROUPS;
+  a.nslot = nslot;
+  const size_t smem = (size_t)nslot * stage_b + 1024;
   int rc = 1;
   switch (w.enc) {
     case E_Q4_0: rc = tg_launch<E_Q4_0>(a, xmap, grid, smem, s); break;

@@ -108,7 +108,7 @@ class ClockSampler:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_mega_kernel launch on this workload
 # (ncu capture summarised in profiles/decode_mega_kernel_qwen3_0_6b_q4_0.md)
-MEGA_DRAM_TRAFFIC = 384_432_768 + 12_080_000
+MEGA_DRAM_TRAFFIC = 384_337_664 + 10_346_240
 
 
 def checkpoint_path():

@@ -134,15 +134,16 @@ def prompt_ids():
 
 # ------------------------------------------------------------------ CPU restatement
 
-def cpu_decode_rate(path, steps, prompt_tokens=4):
+def cpu_decode_rate(path, steps, prompt_tokens=4, warm=1):
     """Decode tok/s of the CPU restatement (all host threads) on a bounded sample."""
     from oracle import oracle as orc
     from dyninfer_b200 import checkpoint as ck
     orc.build()
     cat = ck.open_catalog(path)
-    m = orc.Model(cat.config, orc.weights_from_catalog(cat), kv_cap=prompt_tokens + steps + 2, fast=True)
+    m = orc.Model(cat.config, orc.weights_from_catalog(cat), kv_cap=prompt_tokens + steps + warm + 2, fast=True)
     _, tok = m.forward(prompt_ids()[:prompt_tokens])
-    _, tok = m.forward([tok])                      # one untimed step
+    for _ in range(max(1, warm)):                  # untimed steps
+        _, tok = m.forward([tok])
     t0 = time.perf_counter()
     for _ in range(steps):
         _, tok = m.forward([tok])
@@ -155,13 +156,14 @@ def run_reference_arm(args, rank):
         return
     path = ensure_checkpoint()
     steps = max(1, min(args.steps, 48))
-    tps, cores, dt = cpu_decode_rate(path, steps)
+    warm = max(1, min(args.warmup, 3))
+    tps, cores, dt = cpu_decode_rate(path, steps, warm=warm)
     sample = (f"{steps} greedy decode steps of the full 28-layer model after a 4-token prompt, "
               f"CPU restatement of the reference's direct path (the reference's own IREE llvm-cpu "
               f"build cannot run here), {cores} OpenMP threads")
     print(json.dumps({
         "impl": "reference", "metric": "decode_tokens_per_s", "value": tps, "unit": "tok/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": 1e3 * dt / steps,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": 1e3 * dt / steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": WORKLOAD},
         "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},

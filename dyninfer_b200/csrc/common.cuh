@@ -203,6 +203,8 @@ struct AttnArgs {
   int64_t uniform_base = -1, uniform_seq = 0;
 };
 int launch_attention(const AttnArgs& a, cudaStream_t s);
+size_t attention_split_scratch_bytes(int64_t rows, int64_t nh, int64_t d, int nsplit);
+int launch_attention_split(const AttnArgs& a, float* part, int nsplit, cudaStream_t s, bool* handled);
 int launch_attention_prefill(const AttnArgs& a, int64_t base_pos, int64_t seq, cudaStream_t s, bool* handled);
 
 size_t argmax_scratch_bytes(int64_t n);

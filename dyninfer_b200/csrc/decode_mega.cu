@@ -137,27 +137,6 @@ __device__ __forceinline__ void produce_chunk(const MegaChunk* c, const Smem& sm
 }
 
 // ---- consumer helpers ---------------------------------------------------------------------------
-__device__ __forceinline__ float consumer_sum(float v, float* red, int lane, int warp) {
-  v = warp_sum(v);
-  consumer_sync();
-  if (lane == 0) red[warp] = v;
-  consumer_sync();
-  float t = 0.f;
-#pragma unroll
-  for (int i = 0; i < MK_CW; i++) t += red[i];
-  return t;
-}
-__device__ __forceinline__ float consumer_max(float v, float* red, int lane, int warp) {
-  v = warp_max(v);
-  consumer_sync();
-  if (lane == 0) red[warp] = v;
-  consumer_sync();
-  float t = 0.f;
-#pragma unroll
-  for (int i = 0; i < MK_CW; i++) t = fmaxf(t, red[i]);
-  return t;
-}
-
 // Stage the activation vector of a phase in one pass. Thread i owns fragment item i = (block kb,
 // lane quarter t) and loads exactly the 8 elements that item holds (the items partition the
 // vector; n <= 8 * MK_CT), so the sum of squares and the scale come from one combined block
@@ -305,14 +284,6 @@ __device__ __forceinline__ void store_kv(uint8_t* base, int kv_type, int64_t idx
     reinterpret_cast<__half*>(base)[idx] = __float2half_rn(v);
   else
     reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
-}
-__device__ __forceinline__ uint32_t load_kv_bits(const uint8_t* base, int kv_type, int64_t idx) {
-  if (kv_type == E_F32) return reinterpret_cast<const uint32_t*>(base)[idx];
-  return reinterpret_cast<const uint16_t*>(base)[idx];
-}
-__device__ __forceinline__ float kv_bits_to_f32(uint32_t b, int kv_type) {
-  if (kv_type == E_F32) return __uint_as_float(b);
-  return kv_type == E_F16 ? f16_bits_to_f32(b) : bf16_bits_to_f32(b);
 }
 __device__ __forceinline__ bool arg_better(float v, long long i, float bv, long long bi) {
   return v > bv || (v == bv && i < bi);

@@ -37,14 +37,6 @@ __device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// 32-bit load from memory that is only 2-byte aligned: two aligned words and a funnel shift.
-// May touch up to 4 bytes past the requested word (callers keep that inside their buffer).
-__device__ __forceinline__ uint32_t lds_u32_a2(const uint8_t* p) {
-  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-  const uint32_t* q = reinterpret_cast<const uint32_t*>(a & ~uintptr_t(3));
-  return __funnelshift_r(q[0], q[1], (uint32_t)(a & 3) * 8);
-}
-
 // ---- activation staging ---------------------------------------------------------------
 // Fragment layouts (per 32-element block kb, column c, lane quarter t = lane & 3), 8 halfs:
 //   NIBBLE (Q4_0, Q4_1): x[4t] x[4t+2] x[16+4t]/16 x[16+4t+2]/16 x[4t+1] x[4t+3]
@@ -109,13 +101,6 @@ __device__ __forceinline__ void stage_item(const float* src, int layout, __half*
   }
 }
 
-// B fragments of block kb for this lane: 4 registers (two mma steps).
-template <int NCOL>
-__device__ __forceinline__ uint4 load_bfrag(const __half* xf, int kb, int lane) {
-  const int c = (lane >> 2) & (NCOL - 1), t = lane & 3;
-  return *reinterpret_cast<const uint4*>(xf + ((size_t)(kb * NCOL + c) * 4 + t) * 8);
-}
-
 // ---- accumulators ------------------------------------------------------------------------
 // A lane (g = lane >> 2, t = lane & 3) owns weight rows g and g + 8 of the tile.
 //   HILO : activation row t (columns 2t = hi, 2t+1 = lo): v[0] = row g, v[1] = row g + 8
@@ -128,128 +113,6 @@ struct TileAcc {
     for (int i = 0; i < (HILO ? 2 : 4); i++) v[i] = 0.f;
   }
 };
-
-// acc += sc_r * (C_r * 2^24) + ad_r * sx   for the lane's rows r in {g, g+8}.
-// sxa / sxb: activation-sum of this block for the lane's activation row(s).
-template <bool HILO>
-__device__ __forceinline__ void tile_apply(TileAcc<HILO>& a, const float (&c)[4], float sc0, float sc1,
-                                           float ad0, float ad1, float sxa, float sxb) {
-  if (HILO) {
-    a.v[0] = fmaf(sc0, (c[0] + c[1]) * GV_2P24, fmaf(ad0, sxa, a.v[0]));
-    a.v[1] = fmaf(sc1, (c[2] + c[3]) * GV_2P24, fmaf(ad1, sxa, a.v[1]));
-  } else {
-    a.v[0] = fmaf(sc0, c[0] * GV_2P24, fmaf(ad0, sxa, a.v[0]));
-    a.v[1] = fmaf(sc0, c[1] * GV_2P24, fmaf(ad0, sxb, a.v[1]));
-    a.v[2] = fmaf(sc1, c[2] * GV_2P24, fmaf(ad1, sxa, a.v[2]));
-    a.v[3] = fmaf(sc1, c[3] * GV_2P24, fmaf(ad1, sxb, a.v[3]));
-  }
-}
-
-// Access to one tile row's bytes of the current K-chunk. `base + off0` is the chunk's first
-// byte; every offset is reduced modulo MASK + 1, so the same code reads a linear buffer
-// (MASK = 0xffffffff) or a power-of-two byte ring that a copy engine refills (MASK = size - 1).
-template <uint32_t MASK>
-struct RowLd {
-  const uint8_t* base;
-  uint32_t off0;
-  const uint8_t* sc;  // MLX: this row's scales / biases for the chunk's first group (linear)
-  const uint8_t* bi;
-  __device__ __forceinline__ uint32_t u32(int off) const {  // 32-bit value at any 2-byte aligned offset
-    const uint32_t a = off0 + (uint32_t)off, a4 = a & ~3u;
-    const uint32_t lo = *reinterpret_cast<const uint32_t*>(base + (a4 & MASK));
-    const uint32_t hi = *reinterpret_cast<const uint32_t*>(base + ((a4 + 4u) & MASK));
-    return __funnelshift_r(lo, hi, (a & 3u) * 8u);
-  }
-  __device__ __forceinline__ uint32_t a32(int off) const {  // 4-byte aligned offset
-    return *reinterpret_cast<const uint32_t*>(base + ((off0 + (uint32_t)off) & MASK));
-  }
-  __device__ __forceinline__ uint32_t u16(int off) const {
-    return *reinterpret_cast<const uint16_t*>(base + ((off0 + (uint32_t)off) & MASK));
-  }
-  __device__ __forceinline__ int s8(int off) const {
-    return *reinterpret_cast<const int8_t*>(base + ((off0 + (uint32_t)off) & MASK));
-  }
-};
-
-// One 32-element block of a 16-row tile, any encoding. kl: index inside the chunk the loaders
-// address; kb: index inside the whole row (selects activation fragments and sums).
-// sxa / sxb point at the 16-run sums of the lane's activation row(s).
-template <int ENC, int NCOL, bool HILO, typename LD>
-__device__ __forceinline__ void tile_block(const LD& r0, const LD& r1, int kl, int kb,
-                                           const __half* xf, const float* sxa, const float* sxb,
-                                           int aux, int group, int lane, TileAcc<HILO>& acc) {
-  const int t = lane & 3;
-  const uint4 b = load_bfrag<NCOL>(xf, kb, lane);
-  if constexpr (ENC == E_Q4_0 || ENC == E_Q4_1) {
-    // byte l of the 16 quant bytes: low nibble = element l, high nibble = element l + 16
-    constexpr int BB = ENC == E_Q4_0 ? 18 : 20, QO = ENC == E_Q4_0 ? 2 : 4;
-    const int o = kl * BB;
-    const uint32_t w0 = ENC == E_Q4_0 ? r0.u32(o + QO + 4 * t) : r0.a32(o + QO + 4 * t);
-    const uint32_t w1 = ENC == E_Q4_0 ? r1.u32(o + QO + 4 * t) : r1.a32(o + QO + 4 * t);
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
-    mma_f16_16816(c, w0 & 0x000F000Fu, w1 & 0x000F000Fu, w0 & 0x00F000F0u, w1 & 0x00F000F0u, b.x, b.y);
-    const uint32_t s0 = w0 >> 8, s1 = w1 >> 8;
-    mma_f16_16816(c, s0 & 0x000F000Fu, s1 & 0x000F000Fu, s0 & 0x00F000F0u, s1 & 0x00F000F0u, b.z, b.w);
-    const float d0 = f16_bits_to_f32(r0.u16(o)), d1 = f16_bits_to_f32(r1.u16(o));
-    const float xa = sxa[2 * kb] + sxa[2 * kb + 1], xb = HILO ? 0.f : sxb[2 * kb] + sxb[2 * kb + 1];
-    if constexpr (ENC == E_Q4_0) {
-      tile_apply<HILO>(acc, c, d0, d1, -8.0f * d0, -8.0f * d1, xa, xb);  // d*(q-8)
-    } else {
-      const float m0 = f16_bits_to_f32(r0.u16(o + 2)), m1 = f16_bits_to_f32(r1.u16(o + 2));
-      tile_apply<HILO>(acc, c, d0, d1, m0, m1, xa, xb);  // d*q + m
-    }
-  } else if constexpr (ENC == E_Q8_0) {
-    // signed byte q = u - 128 with u = byte ^ 0x80
-    const int o = kl * 34;
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int hlf = 0; hlf < 2; hlf++) {
-      const uint32_t w0 = r0.u32(o + 2 + 16 * hlf + 4 * t) ^ 0x80808080u;
-      const uint32_t w1 = r1.u32(o + 2 + 16 * hlf + 4 * t) ^ 0x80808080u;
-      mma_f16_16816(c, __byte_perm(w0, 0, 0x4140), __byte_perm(w1, 0, 0x4140),
-                    __byte_perm(w0, 0, 0x4342), __byte_perm(w1, 0, 0x4342), hlf ? b.z : b.x,
-                    hlf ? b.w : b.y);
-    }
-    const float d0 = f16_bits_to_f32(r0.u16(o)), d1 = f16_bits_to_f32(r1.u16(o));
-    const float xa = sxa[2 * kb] + sxa[2 * kb + 1], xb = HILO ? 0.f : sxb[2 * kb] + sxb[2 * kb + 1];
-    tile_apply<HILO>(acc, c, d0, d1, -128.0f * d0, -128.0f * d1, xa, xb);
-  } else if constexpr (ENC == E_MLX_U4) {
-    // word j of a row: nibble i = element 8j + i; one scale/bias per `group` elements
-    const uint32_t w0 = r0.a32(kl * 16 + 4 * t), w1 = r1.a32(kl * 16 + 4 * t);
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
-    mma_f16_16816(c, w0 & 0x000F000Fu, w1 & 0x000F000Fu, w0 & 0x00F000F0u, w1 & 0x00F000F0u, b.x, b.y);
-    const uint32_t h0 = w0 >> 8, h1 = w1 >> 8;
-    mma_f16_16816(c, h0 & 0x000F000Fu, h1 & 0x000F000Fu, h0 & 0x00F000F0u, h1 & 0x00F000F0u, b.z, b.w);
-    const int gi = (kl * 32) / group;
-    const float xa = sxa[2 * kb] + sxa[2 * kb + 1], xb = HILO ? 0.f : sxb[2 * kb] + sxb[2 * kb + 1];
-    tile_apply<HILO>(acc, c, aux_load(r0.sc, aux, gi), aux_load(r1.sc, aux, gi),
-                     aux_load(r0.bi, aux, gi), aux_load(r1.bi, aux, gi), xa, xb);
-  } else if constexpr (ENC == E_Q6_K) {
-    // 32-block kl of the chunk = slice (n, h, p) of superblock kl / 8 (chunks start on
-    // superblock boundaries); its two 16-element halves carry separate int8 scales.
-    const int e32 = kl & 7, n = e32 >> 2, h = (e32 >> 1) & 1, p = e32 & 1;
-    const int o = (kl >> 3) * 210;
-    const float d0 = f16_bits_to_f32(r0.u16(o + 208)), d1 = f16_bits_to_f32(r1.u16(o + 208));
-    const int sci = o + 192 + n * 8 + h * 4 + p * 2;
-#pragma unroll
-    for (int s = 0; s < 2; s++) {
-      const int j0 = 16 * s + 4 * t;
-      const uint32_t l0 = r0.u32(o + n * 64 + p * 32 + j0) >> (4 * h);
-      const uint32_t l1 = r1.u32(o + n * 64 + p * 32 + j0) >> (4 * h);
-      const uint32_t q0 = r0.u32(o + 128 + n * 32 + j0) >> (2 * (h * 2 + p));
-      const uint32_t q1 = r1.u32(o + 128 + n * 32 + j0) >> (2 * (h * 2 + p));
-      const uint32_t v0 = (l0 & 0x0F0F0F0Fu) | ((q0 & 0x03030303u) << 4);  // 4 values 0..63
-      const uint32_t v1 = (l1 & 0x0F0F0F0Fu) | ((q1 & 0x03030303u) << 4);
-      float cs[4] = {0.f, 0.f, 0.f, 0.f};
-      mma_f16_16816(cs, __byte_perm(v0, 0, 0x4140), __byte_perm(v1, 0, 0x4140),
-                    __byte_perm(v0, 0, 0x4342), __byte_perm(v1, 0, 0x4342), s ? b.z : b.x,
-                    s ? b.w : b.y);
-      const float f0 = d0 * (float)r0.s8(sci + s), f1 = d1 * (float)r1.s8(sci + s);
-      tile_apply<HILO>(acc, cs, f0, f1, -32.0f * f0, -32.0f * f1, sxa[2 * kb + s],
-                       HILO ? 0.f : sxb[2 * kb + s]);
-    }
-  }
-}
 
 // ---- fast unit steps (static addressing) --------------------------------------------------
 // A "unit" is the smallest run of blocks whose 4-byte phase is known at compile time: block

@@ -277,6 +277,152 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_kernel(AttnArgs a) {
   }
 }
 
+// ---- decode attention with split keys (long contexts, batched decode) ------------------------
+// Grid (head, row, split): every CTA walks one slice of the row's keys; a lane owns DPL consecutive
+// head dims, so a warp reads a cached key or value row with one coalesced vector load, and four
+// keys per warp are in flight before any is used. Each CTA leaves (unnormalised output, max, sum)
+// for its slice; attention_merge_kernel combines the slices in a fixed order.
+template <int KV, int DPL>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attention_split_kernel(AttnArgs a, float* __restrict__ part, int nsplit) {
+  using T = typename KvT<KV>::T;
+  constexpr int KB = 4;
+  __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS];
+  __shared__ float s_acc[ATT_WARPS][32 * DPL];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t h = blockIdx.x, r = blockIdx.y, sp = blockIdx.z, d = a.d;
+  const int64_t kvh = h / (a.nh / a.nkv);
+  const int64_t pos = a.row_pos ? a.row_pos[r] : a.base_pos + r;
+  const int64_t seq = a.row_seq ? a.row_seq[r] : 0;
+  const int64_t n = pos + 1, per = (n + nsplit - 1) / nsplit;
+  const int64_t k_lo = sp * per, k_hi = k_lo + per < n ? k_lo + per : n;
+  const float scale = 1.0f / sqrtf((float)d);
+  const int e0 = lane * DPL;
+  const bool live = e0 < d;
+  const T* kb = reinterpret_cast<const T*>(a.kcache) + (seq * a.nkv + kvh) * a.cap * d + e0;
+  const T* vb = reinterpret_cast<const T*>(a.vcache) + (seq * a.nkv + kvh) * a.cap * d + e0;
+  float qreg[DPL], acc[DPL];
+#pragma unroll
+  for (int j = 0; j < DPL; j++) {
+    qreg[j] = live ? a.q[(r * a.nh + h) * d + e0 + j] : 0.f;
+    acc[j] = 0.f;
+  }
+  struct __align__(sizeof(T) * DPL) Row {  // one vector load per lane and cached row
+    T v[DPL];
+  };
+  float m = -3.40282347e38f, l = 0.f;
+  for (int64_t key0 = k_lo + warp; key0 < k_hi; key0 += (int64_t)KB * ATT_WARPS) {
+    Row kr[KB], vr[KB];
+#pragma unroll
+    for (int b = 0; b < KB; b++) {
+      const int64_t key = key0 + (int64_t)b * ATT_WARPS;
+      if (key < k_hi && live) {
+        kr[b] = *reinterpret_cast<const Row*>(kb + key * d);
+        vr[b] = *reinterpret_cast<const Row*>(vb + key * d);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < KB; b++) {
+      const int64_t key = key0 + (int64_t)b * ATT_WARPS;
+      if (key >= k_hi) break;  // warp-uniform
+      float dot = 0.f;
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < DPL; j++) dot = fmaf(qreg[j], KvT<KV>::dec(kr[b].v[j]), dot);
+      }
+      const float sc = warp_sum(dot) * scale;
+      const float mn = fmaxf(m, sc);
+      const float factor = expf(m - mn), p = expf(sc - mn);
+      l = l * factor + p;
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < DPL; j++) acc[j] = acc[j] * factor + p * KvT<KV>::dec(vr[b].v[j]);
+      }
+      m = mn;
+    }
+  }
+  if (lane == 0) s_m[warp] = m, s_l[warp] = l;
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < DPL; j++) s_acc[warp][e0 + j] = acc[j];
+  }
+  __syncthreads();
+  float gm = s_m[0];
+#pragma unroll
+  for (int w = 1; w < ATT_WARPS; w++) gm = fmaxf(gm, s_m[w]);
+  float wgt[ATT_WARPS], gl = 0.f;
+#pragma unroll
+  for (int w = 0; w < ATT_WARPS; w++) {
+    wgt[w] = expf(s_m[w] - gm);
+    gl += s_l[w] * wgt[w];
+  }
+  float* out = part + (((r * a.nh + h) * nsplit) + sp) * (d + 2);
+  for (int64_t idx = threadIdx.x; idx < d; idx += blockDim.x) {
+    float o = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; w++) o += s_acc[w][idx] * wgt[w];
+    out[idx] = o;
+  }
+  if (threadIdx.x == 0) out[d] = gm, out[d + 1] = gl;
+}
+
+__global__ void __launch_bounds__(256)
+attention_merge_kernel(const float* __restrict__ part, int nsplit, float* ctx, int64_t nh, int64_t d) {
+  const int64_t h = blockIdx.x, r = blockIdx.y;
+  const float* p0 = part + ((r * nh + h) * nsplit) * (d + 2);
+  float gm = -3.40282347e38f;
+  for (int s = 0; s < nsplit; s++) gm = fmaxf(gm, p0[s * (d + 2) + d]);
+  for (int64_t idx = threadIdx.x; idx < d; idx += blockDim.x) {
+    float o = 0.f, gl = 0.f;
+    for (int s = 0; s < nsplit; s++) {
+      const float* ps = p0 + s * (d + 2);
+      const float w = expf(ps[d] - gm);  // an empty slice has sum 0 and contributes nothing
+      o += ps[idx] * w;
+      gl += ps[d + 1] * w;
+    }
+    ctx[r * nh * d + h * d + idx] = o / gl;
+  }
+}
+
+template <int KV>
+static int run_attention_split(const AttnArgs& a, float* part, int nsplit, cudaStream_t s) {
+  const dim3 grid((unsigned)a.nh, (unsigned)a.rows, (unsigned)nsplit);
+  if (a.d == 64)
+    attention_split_kernel<KV, 2><<<grid, ATT_WARPS * 32, 0, s>>>(a, part, nsplit);
+  else if (a.d == 128)
+    attention_split_kernel<KV, 4><<<grid, ATT_WARPS * 32, 0, s>>>(a, part, nsplit);
+  else
+    attention_split_kernel<KV, 8><<<grid, ATT_WARPS * 32, 0, s>>>(a, part, nsplit);
+  attention_merge_kernel<<<dim3((unsigned)a.nh, (unsigned)a.rows), 256, 0, s>>>(part, nsplit, a.ctx, a.nh, a.d);
+  count_launch(2);
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
+size_t attention_split_scratch_bytes(int64_t rows, int64_t nh, int64_t d, int nsplit) {
+  return (size_t)rows * nh * nsplit * (d + 2) * sizeof(float);
+}
+
+// Split-key decode attention into caller scratch (attention_split_scratch_bytes). Head dims 64,
+// 128 and 256 only; *handled = false otherwise.
+int launch_attention_split(const AttnArgs& a, float* part, int nsplit, cudaStream_t s, bool* handled) {
+  *handled = false;
+  if (a.rows == 0 || (a.d != 64 && a.d != 128 && a.d != 256) || nsplit < 1) return 0;
+  DYN_CHECK(a.nkv > 0 && a.nh % a.nkv == 0, "heads %lld not a multiple of kv heads %lld", (long long)a.nh,
+            (long long)a.nkv);
+  int rc;
+  if (a.kv_type == E_F32)
+    rc = run_attention_split<E_F32>(a, part, nsplit, s);
+  else if (a.kv_type == E_F16)
+    rc = run_attention_split<E_F16>(a, part, nsplit, s);
+  else if (a.kv_type == E_BF16)
+    rc = run_attention_split<E_BF16>(a, part, nsplit, s);
+  else
+    return 0;
+  if (!rc) *handled = true;
+  return rc;
+}
+
 int launch_attention(const AttnArgs& a, cudaStream_t s) {
   if (a.rows == 0) return 0;
   DYN_CHECK(a.d <= 256, "head_dim %lld unsupported (<= 256)", (long long)a.d);
@@ -287,6 +433,24 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
     if (launch_attention_prefill(a, a.row_pos ? a.uniform_base : a.base_pos, a.row_pos ? a.uniform_seq : 0, s,
                                  &handled))
       return 1;
+    if (handled) return 0;
+  }
+  if (a.d == 64 || a.d == 128 || a.d == 256) {
+    // decode / batched decode: slice every row's keys over enough CTAs to fill the GPU. The slice
+    // count depends only on shapes and capacity, so a captured graph stays valid as positions grow.
+    int nsplit = (int)(592 / (a.rows * a.nh));
+    const int by_cap = (int)(a.cap / 128);
+    if (nsplit > by_cap) nsplit = by_cap;
+    if (nsplit > 32) nsplit = 32;
+    if (nsplit < 1) nsplit = 1;
+    if (keep_scratch_pool_cached()) return 1;
+    float* part = nullptr;
+    DYN_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&part), attention_split_scratch_bytes(a.rows, a.nh, a.d, nsplit), s));
+    bool handled = false;
+    const int rc = launch_attention_split(a, part, nsplit, s, &handled);
+    const cudaError_t fe = cudaFreeAsync(part, s);
+    if (rc) return rc;
+    if (fe != cudaSuccess) return cuda_fail(fe, "cudaFreeAsync", __FILE__, __LINE__);
     if (handled) return 0;
   }
   dim3 grid((unsigned)a.nh, (unsigned)a.rows);

@@ -113,6 +113,10 @@ class CudaSession:
         check(lib().dyninfer_cuda_session_configure_paged_kv(
             self._h, cfg["layers"], PAGE_SIZE, cfg["kv_heads"], cfg["head_dim"], self.kv_elem,
             model.chunk_size, cfg["vocab"]))
+        self._pages_ready = False
+        self._tok1 = (C.c_int64 * 1)()
+        self._out1 = C.c_int64(-1)
+        self._invoke_fn = lib().dyninfer_cuda_session_invoke_paged_chunk
 
     # -- lifetime
     def close(self):
@@ -141,6 +145,7 @@ class CudaSession:
     def _ensure_pages(self):
         pages = max(1, -(-self._max_seq() // PAGE_SIZE))
         check(lib().dyninfer_cuda_session_ensure_kv_pages(self._h, pages))
+        self._pages_ready = True
 
     def _window(self, tokens):
         w = self.model.chunk_size
@@ -191,8 +196,15 @@ class CudaSession:
         self._require_batch_1()
         if self.position_ >= self._max_seq():
             raise DynInferError(f"decode position {self.position_} exceeds session/KV limit {self._max_seq()}")
-        self._ensure_pages()
-        lg, nxt = self._invoke(np.array([int(token)], dtype=np.int64), 0, self.position_, want_logits)
+        if not self._pages_ready:
+            self._ensure_pages()
+        if want_logits:
+            lg, nxt = self._invoke(np.array([int(token)], dtype=np.int64), 0, self.position_, True)
+        else:
+            # the per-token hot call: reuse the argument objects instead of building arrays every step
+            self._tok1[0] = int(token)
+            check(self._invoke_fn(self._h, self._tok1, 1, 0, self.position_, None, None, C.byref(self._out1), 0))
+            lg, nxt = None, int(self._out1.value)
         self.history.append(int(token))
         self.position_ += 1
         return lg, nxt

@@ -291,7 +291,10 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
     if (launch_linear(L.o, s->ctx, E_F32, rows, s->hidden, s->hidden, st)) return 1;
     if (launch_rms_norm(s->hidden, L.ffn_norm.ptr, L.ffn_norm.type, rows, H, c.eps, s->xn, st))
       return 1;
-    if (L.gate.enc == L.up.enc && rows <= 16) {
+    // one row: the column-split GEMVs run at ~3x the fused scalar kernel's bandwidth, which more than
+    // pays for the separate activation launch
+    const bool fast_gemv = rows == 1 && gemv_cs_workspace_bytes(L.gate, 1) && gemv_cs_workspace_bytes(L.up, 1);
+    if (L.gate.enc == L.up.enc && rows <= 16 && !fast_gemv) {
       if (launch_linear_swiglu(L.gate, L.up, s->xn, rows, s->act, st)) return 1;
     } else {
       // many rows (tensor-core GEMM) or mixed encodings: two products, then the activation

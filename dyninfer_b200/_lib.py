@@ -75,6 +75,12 @@ PROTOTYPES = {
     "dyninfer_cuda_session_decode_batch": (
         C.c_int, [_P, C.POINTER(_I64), C.POINTER(_I64), C.POINTER(_I64), C.c_size_t, C.POINTER(_I64),
                   C.POINTER(C.POINTER(C.c_float)), C.c_int]),
+    "dyninfer_cuda_tp_unique_id_bytes": (C.c_size_t, []),
+    "dyninfer_cuda_tp_unique_id": (C.c_int, [C.c_char_p, C.c_size_t]),
+    "dyninfer_cuda_session_tp_init": (C.c_int, [_P, C.c_char_p, C.c_size_t]),
+    "dyninfer_cuda_tp_peer_handle_bytes": (C.c_size_t, []),
+    "dyninfer_cuda_session_tp_peer_handle": (C.c_int, [_P, C.c_char_p, C.c_size_t]),
+    "dyninfer_cuda_session_tp_peer_attach": (C.c_int, [_P, C.c_char_p, C.c_size_t]),
     "dyninfer_cuda_session_reset_paged_kv": (C.c_int, [_P]),
     "dyninfer_cuda_session_kv_page_count": (C.c_size_t, [_P]),
     "dyninfer_cuda_session_kv_allocated_bytes": (C.c_size_t, [_P]),

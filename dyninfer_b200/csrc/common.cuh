@@ -210,5 +210,36 @@ int launch_attention_prefill(const AttnArgs& a, int64_t base_pos, int64_t seq, c
 size_t argmax_scratch_bytes(int64_t n);
 int launch_argmax(const float* v, int64_t n, int64_t* out, void* scratch, cudaStream_t s);
 int launch_argmax_rows(const float* v, int64_t rows, int64_t n, int64_t* out, cudaStream_t s);
+// The same over logits held as `shards` slices [shards][rows][n_local]: index w * n_local + j.
+int launch_argmax_rows_sharded(const float* v, int64_t rows, int64_t n_local, int shards, int64_t* out,
+                               cudaStream_t s);
+
+// ---- tensor-parallel exchange over peer memory (tp_peer.cu) ----
+constexpr int TP_MAX_WORLD = 8;
+constexpr int TP_PEER_BLOCKS = 128;
+struct TpPeer {
+  int rank = 0, world = 1;
+  int64_t max_rows = 0;
+  uint8_t* base[TP_MAX_WORLD] = {};  // every rank's region as mapped in this process (own: the allocation)
+  size_t region_bytes = 0, flags_off = 0;
+  unsigned* epochs = nullptr;        // [TP_PEER_BLOCKS] exchanges entered per block, own
+  int* error_host = nullptr;         // pinned, mapped: which wait ran out (0 = none)
+  int* error_dev = nullptr;
+  bool attached = false;
+};
+size_t tp_peer_region_bytes(int64_t max_rows, int hidden);
+size_t tp_peer_flags_offset(int64_t max_rows, int hidden);
+// hidden[rows, H] += sum over ranks of slot `slot` of their regions; xn = RMSNorm(hidden) * norm_w
+// when xn is given. Every rank launches it with the same arguments in the same order.
+int launch_tp_exchange(const TpPeer& p, int slot, int64_t rows, int H, float* hidden, float* xn,
+                       const void* norm_w, int norm_type, float eps, cudaStream_t st);
+
+// ---- tensor-parallel exchange (tp_comm.cu; NCCL looked up at run time) ----
+size_t tp_unique_id_bytes();
+int tp_unique_id(uint8_t* out);
+int tp_comm_init(void** comm, const uint8_t* id_bytes, int rank, int world);
+void tp_comm_destroy(void* comm);
+int tp_all_reduce_sum(void* comm, const float* send, float* recv, size_t count, cudaStream_t st);
+int tp_all_gather(void* comm, const float* send, float* recv, size_t count_per_rank, cudaStream_t st);
 
 }  // namespace dyn

@@ -530,15 +530,18 @@ argmax_final_kernel(const ArgPair* part, int count, int64_t* out) {
 
 // One block per row of v [rows, n]: first strict maximum of every row (batched decode).
 __global__ void __launch_bounds__(1024)
-argmax_rows_kernel(const float* __restrict__ v, int64_t n, int64_t* out) {
+argmax_rows_kernel(const float* __restrict__ v, int64_t n, int shards, int64_t* out) {
   __shared__ float sv[32];
   __shared__ long long si[32];
-  const float* row = v + (int64_t)blockIdx.x * n;
   float bv = -INFINITY;
   long long bi = 0x7fffffffffffffffLL;
-  for (int64_t i = threadIdx.x; i < n; i += 1024) {
-    const float x = row[i];
-    if (x > -INFINITY && arg_better(x, i, bv, bi)) bv = x, bi = i;
+  // slice w of this row sits at [w][row][n]; its elements are indices w * n + j
+  for (int w = 0; w < shards; w++) {
+    const float* row = v + ((int64_t)w * gridDim.x + blockIdx.x) * n;
+    for (int64_t i = threadIdx.x; i < n; i += 1024) {
+      const float x = row[i];
+      if (x > -INFINITY && arg_better(x, (int64_t)w * n + i, bv, bi)) bv = x, bi = (int64_t)w * n + i;
+    }
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -563,7 +566,16 @@ argmax_rows_kernel(const float* __restrict__ v, int64_t n, int64_t* out) {
 
 int launch_argmax_rows(const float* v, int64_t rows, int64_t n, int64_t* out, cudaStream_t s) {
   DYN_CHECK(rows >= 1 && n >= 1, "argmax_rows: rows and n must be >= 1");
-  argmax_rows_kernel<<<(unsigned)rows, 1024, 0, s>>>(v, n, out);
+  argmax_rows_kernel<<<(unsigned)rows, 1024, 0, s>>>(v, n, 1, out);
+  count_launch();
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int launch_argmax_rows_sharded(const float* v, int64_t rows, int64_t n_local, int shards, int64_t* out,
+                               cudaStream_t s) {
+  DYN_CHECK(rows >= 1 && n_local >= 1 && shards >= 1, "argmax_rows: rows, n and shards must be >= 1");
+  argmax_rows_kernel<<<(unsigned)rows, 1024, 0, s>>>(v, n_local, shards, out);
   count_launch();
   DYN_CUDA(cudaGetLastError());
   return 0;

@@ -1,6 +1,7 @@
 // Session: owns the uploaded parameters (verbatim byte ranges), the paged KV pool,
 // the activation scratch and the captured decode graph. Shape and conventions follow
 // the reference's native session, third_party/iree_runtime_c_api/wrapper.c:914-1303.
+#include <dlfcn.h>
 #include <errno.h>
 #include <fcntl.h>
 #include <string.h>
@@ -8,6 +9,7 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <array>
 #include <map>
 #include <string>
 #include <vector>
@@ -37,6 +39,9 @@ struct ModelCfg {
   int batch = 1;
   int kv2_type = E_BF16;  // element type used when the KV cache is configured with 2 bytes
   bool persistent = true;  // single-token steps run as the persistent decode kernel
+  // tensor parallelism: heads / kv_heads / inter above are this rank's share; the lm_head holds
+  // lm_rows = vocab / tp_world consecutive rows starting at tp_rank * lm_rows
+  int tp_rank = 0, tp_world = 1, lm_rows = 0;
 };
 
 }  // namespace dyn
@@ -98,6 +103,13 @@ struct dyninfer_cuda_session_t {
   std::map<int64_t, std::pair<cudaGraphExec_t, uint64_t>> batch_graphs;  // rows -> batched step (graph, nodes)
   uint64_t graph_nodes = 0, loop_nodes = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  // tensor parallelism (tp_world > 1): communicator, partial-sum scratch, per-rank logits
+  void* tp_comm = nullptr;
+  float* tp_part = nullptr;    // [max_rows, hidden] partial o_proj / down products of ranks > 0
+  float* tp_logits = nullptr;  // [max(1, batch), lm_rows] this rank's slice of the logits
+  float* tp_gather = nullptr;  // [tp_world, batch, lm_rows] gathered slices of a batched step
+  bool tp_warm = false;        // the collectives have run once outside a capture
+  TpPeer peer;                 // peer-memory exchange (used instead of the all-reduce once attached)
   // statistics
   dyninfer_cuda_allocator_statistics_t stats{};
   uint64_t launches = 0;
@@ -143,12 +155,16 @@ struct Upload {  // one byte range placed in the arena
   uint64_t arena_off = 0, length = 0;
   size_t file = 0;
   uint64_t file_off = 0;
+  // strided source (a tensor-parallel slice of every row): `rows` segments of `seg` bytes,
+  // `stride` bytes apart in the file, packed back to back in the arena; rows == 0: contiguous
+  uint64_t rows = 0, seg = 0, stride = 0;
 };
 
 struct ParamDesc {
   int enc = -1, aux = E_BF16, group = 0;
   std::vector<int64_t> shape;
   std::map<std::string, Upload> comps;  // component name -> upload
+  std::map<std::string, std::array<uint64_t, 3>> strided;  // component -> rows, seg bytes, row stride
 };
 
 int read_range(int fd, uint64_t off, uint64_t len, uint8_t* dst_dev, uint8_t* staging,
@@ -166,6 +182,29 @@ int read_range(int fd, uint64_t off, uint64_t len, uint8_t* dst_dev, uint8_t* st
     }
     DYN_CUDA(cudaMemcpy(dst_dev + done, staging, n, cudaMemcpyHostToDevice));
     done += n;
+  }
+  return 0;
+}
+
+// A strided range (one span of every row): whole groups of rows are read in one piece and a
+// 2-D copy packs their spans into the arena; the bytes themselves are uploaded unchanged.
+int read_strided(int fd, const Upload& u, uint8_t* dst_dev, uint8_t* staging, size_t staging_bytes,
+                 const char* path) {
+  DYN_CHECK(u.stride <= staging_bytes, "row stride %llu of a strided range exceeds the staging buffer",
+            (unsigned long long)u.stride);
+  const uint64_t per = std::max<uint64_t>(1, staging_bytes / u.stride);
+  for (uint64_t r0 = 0; r0 < u.rows; r0 += per) {
+    const uint64_t n = std::min<uint64_t>(per, u.rows - r0);
+    const uint64_t bytes = (n - 1) * u.stride + u.seg, off = u.file_off + r0 * u.stride;
+    size_t got = 0;
+    while (got < bytes) {
+      ssize_t r = pread(fd, staging + got, bytes - got, (off_t)(off + got));
+      if (r < 0 && errno == EINTR) continue;
+      DYN_CHECK(r > 0, "short read of %s at offset %llu (%s)", path, (unsigned long long)(off + got),
+                r == 0 ? "end of file" : strerror(errno));
+      got += (size_t)r;
+    }
+    DYN_CUDA(cudaMemcpy2D(dst_dev + r0 * u.seg, u.seg, staging, u.stride, u.seg, n, cudaMemcpyHostToDevice));
   }
   return 0;
 }
@@ -252,20 +291,51 @@ __global__ void advance_kernel(int64_t* tokens, int64_t* row_pos, const int64_t*
   hist_count[0] = c + 1;
 }
 
+// A row-parallel product (o_proj, down) under tensor parallelism: every rank multiplies its span
+// of the reduction dimension and the sum over ranks plus the residual lands in `hidden` on every
+// rank (the same bits everywhere, so the ranks stay in step). With peer memory attached the
+// partial rows go to this rank's exchange slot and one kernel sums all ranks' slots and applies
+// the following RMSNorm (`norm` -> xn; *fused tells the caller). Otherwise rank 0 adds the
+// residual and an all-reduce sums.
+int tp_row_parallel(Session* s, const WRef& w, const float* x, int64_t rows, int slot, const NormW* norm,
+                    bool* fused, cudaStream_t st) {
+  *fused = false;
+  const ModelCfg& c = s->cfg;
+  if (s->peer.attached) {
+    float* part = reinterpret_cast<float*>(s->peer.base[c.tp_rank]) + (size_t)slot * s->peer.max_rows * c.hidden;
+    if (launch_linear(w, x, E_F32, rows, part, nullptr, st)) return 1;
+    *fused = norm != nullptr;
+    return launch_tp_exchange(s->peer, slot, rows, c.hidden, s->hidden, norm ? s->xn : nullptr,
+                              norm ? norm->ptr : nullptr, norm ? norm->type : E_F32, c.eps, st);
+  }
+  DYN_CHECK(s->tp_comm != nullptr,
+            "tensor-parallel session: dyninfer_cuda_session_tp_init has not been called");
+  const size_t n = (size_t)rows * c.hidden;
+  if (c.tp_rank == 0) {
+    if (launch_linear(w, x, E_F32, rows, s->hidden, s->hidden, st)) return 1;
+    return tp_all_reduce_sum(s->tp_comm, s->hidden, s->hidden, n, st);
+  }
+  if (launch_linear(w, x, E_F32, rows, s->tp_part, nullptr, st)) return 1;
+  return tp_all_reduce_sum(s->tp_comm, s->tp_part, s->hidden, n, st);
+}
+
 // Enqueue the whole decoder for `rows` rows whose tokens / positions / slots are
 // already in device memory; logits and argmax come from row `logits_row`.
 int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows = false,
                     int64_t chunk_start = -1, int64_t chunk_slot = 0) {
   const ModelCfg& c = s->cfg;
   cudaStream_t st = s->stream;
+  const bool tp = c.tp_world > 1;
   const int64_t H = c.hidden, qd = (int64_t)c.heads * c.head_dim,
                 kvd = (int64_t)c.kv_heads * c.head_dim;
   const int64_t cap = (int64_t)(s->pages * s->page_size);
   const size_t layer_stride = (size_t)c.batch * c.kv_heads * cap * c.head_dim * s->kv_elem;
   if (launch_gather(s->embed, s->tokens_dev, rows, s->hidden, st)) return 1;
+  bool normed = false;  // xn already holds this layer's attn_norm rows (fused into the last exchange)
   for (int l = 0; l < c.layers; l++) {
     const LayerW& L = s->layers[l];
-    if (launch_rms_norm(s->hidden, L.attn_norm.ptr, L.attn_norm.type, rows, H, c.eps, s->xn, st))
+    if (!normed &&
+        launch_rms_norm(s->hidden, L.attn_norm.ptr, L.attn_norm.type, rows, H, c.eps, s->xn, st))
       return 1;
     if (launch_linear(L.q, s->xn, E_F32, rows, s->q, nullptr, st)) return 1;
     if (launch_linear(L.k, s->xn, E_F32, rows, s->k, nullptr, st)) return 1;
@@ -288,8 +358,12 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
     aa.kv_type = s->kv_type;
     aa.uniform_base = chunk_start, aa.uniform_seq = chunk_slot;  // a prefill chunk: consecutive positions
     if (launch_attention(aa, st)) return 1;
-    if (launch_linear(L.o, s->ctx, E_F32, rows, s->hidden, s->hidden, st)) return 1;
-    if (launch_rms_norm(s->hidden, L.ffn_norm.ptr, L.ffn_norm.type, rows, H, c.eps, s->xn, st))
+    bool ffn_normed = false;
+    if (tp ? tp_row_parallel(s, L.o, s->ctx, rows, 0, &L.ffn_norm, &ffn_normed, st)
+           : launch_linear(L.o, s->ctx, E_F32, rows, s->hidden, s->hidden, st))
+      return 1;
+    if (!ffn_normed &&
+        launch_rms_norm(s->hidden, L.ffn_norm.ptr, L.ffn_norm.type, rows, H, c.eps, s->xn, st))
       return 1;
     // one row: the column-split GEMVs run at ~3x the fused scalar kernel's bandwidth, which more than
     // pays for the separate activation launch
@@ -302,11 +376,22 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
       if (launch_linear(L.up, s->xn, E_F32, rows, s->up, nullptr, st)) return 1;
       if (launch_silu_mul(s->act, s->up, rows * c.inter, s->act, st)) return 1;
     }
-    if (launch_linear(L.down, s->act, E_F32, rows, s->hidden, s->hidden, st)) return 1;
+    normed = false;
+    if (tp ? tp_row_parallel(s, L.down, s->act, rows, 1,
+                             l + 1 < c.layers ? &s->layers[l + 1].attn_norm : nullptr, &normed, st)
+           : launch_linear(L.down, s->act, E_F32, rows, s->hidden, s->hidden, st))
+      return 1;
   }
   if (all_rows) {
     // batched decode: every row is the last token of its own sequence
     if (launch_rms_norm(s->hidden, s->out_norm.ptr, s->out_norm.type, rows, H, c.eps, s->xn, st)) return 1;
+    if (tp) {
+      // every rank scores its rows of the vocabulary; the slices are gathered as
+      // [rank][row][lm_rows] and the first strict maximum is taken over all of them
+      if (launch_linear(s->lm_head, s->xn, E_F32, rows, s->tp_logits, nullptr, st)) return 1;
+      if (tp_all_gather(s->tp_comm, s->tp_logits, s->tp_gather, (size_t)rows * c.lm_rows, st)) return 1;
+      return launch_argmax_rows_sharded(s->tp_gather, rows, c.lm_rows, c.tp_world, s->batch_tokens_dev, st);
+    }
     if (launch_linear(s->lm_head, s->xn, E_F32, rows, s->batch_logits, nullptr, st)) return 1;
     if (launch_argmax_rows(s->batch_logits, rows, c.vocab, s->batch_tokens_dev, st)) return 1;
     return 0;
@@ -315,15 +400,39 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
   if (launch_rms_norm(s->hidden + logits_row * H, s->out_norm.ptr, s->out_norm.type, 1, H, c.eps,
                       s->xn, st))
     return 1;
-  if (launch_linear(s->lm_head, s->xn, E_F32, 1, s->logits, nullptr, st)) return 1;
+  if (tp) {
+    // one row: the gathered slices are the logits in vocabulary order
+    if (launch_linear(s->lm_head, s->xn, E_F32, 1, s->tp_logits, nullptr, st)) return 1;
+    if (tp_all_gather(s->tp_comm, s->tp_logits, s->logits, (size_t)c.lm_rows, st)) return 1;
+  } else if (launch_linear(s->lm_head, s->xn, E_F32, 1, s->logits, nullptr, st)) {
+    return 1;
+  }
   if (launch_argmax(s->logits, c.vocab, s->out_token_dev, s->argmax_scratch, st)) return 1;
   (void)kvd;
+  return 0;
+}
+
+// The exchange steps of a `rows`-row forward, run once on scratch data outside any capture, so
+// that the communicator sets up whatever these sizes need before they are recorded into a graph.
+int tp_warm_collectives(Session* s, int64_t rows, bool all_rows) {
+  const ModelCfg& c = s->cfg;
+  if (c.tp_world <= 1) return 0;
+  DYN_CHECK(s->tp_comm != nullptr,
+            "tensor-parallel session: dyninfer_cuda_session_tp_init has not been called");
+  const size_t n = (size_t)rows * c.hidden;
+  DYN_CUDA(cudaMemsetAsync(s->tp_part, 0, n * 4, s->stream));
+  if (tp_all_reduce_sum(s->tp_comm, s->tp_part, s->tp_part, n, s->stream)) return 1;
+  if (all_rows ? tp_all_gather(s->tp_comm, s->tp_logits, s->tp_gather, (size_t)rows * c.lm_rows, s->stream)
+               : tp_all_gather(s->tp_comm, s->tp_logits, s->logits, (size_t)c.lm_rows, s->stream))
+    return 1;
+  DYN_CUDA(cudaStreamSynchronize(s->stream));
   return 0;
 }
 
 int capture(Session* s, bool loop, cudaGraphExec_t* out, uint64_t* nodes) {
   cudaGraph_t g = nullptr;
   uint64_t before = s->launches;
+  if (tp_warm_collectives(s, 1, false)) return 1;
   DYN_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
   int rc = 0;
   if (!loop) {
@@ -367,6 +476,7 @@ int capture(Session* s, bool loop, cudaGraphExec_t* out, uint64_t* nodes) {
 int capture_batch(Session* s, int64_t rows, cudaGraphExec_t* out, uint64_t* nodes) {
   cudaGraph_t g = nullptr;
   const uint64_t before = s->launches;
+  if (tp_warm_collectives(s, rows, true)) return 1;
   DYN_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
   const int rc = enqueue_forward(s, rows, 0, true);
   cudaError_t e = cudaStreamEndCapture(s->stream, &g);
@@ -448,6 +558,16 @@ int mega_check_error(Session* s, int64_t word) {
   return 1;
 }
 
+// After the stream has drained: did a wait of the peer exchange run out during this call?
+int tp_check_error(Session* s) {
+  if (!s->peer.attached || !*s->peer.error_host) return 0;
+  const int which = *s->peer.error_host - 1;
+  *s->peer.error_host = 0;
+  set_error("tensor-parallel exchange: rank %d did not arrive within the wait limit (rank %d gave up); "
+            "the step's results are invalid", which, s->cfg.tp_rank);
+  return 1;
+}
+
 struct CounterScope {  // routes count_launch() to this session for the duration of a call
   explicit CounterScope(Session* s) { set_launch_counter(&s->launches); }
   ~CounterScope() { set_launch_counter(nullptr); }
@@ -513,11 +633,20 @@ int dyninfer_cuda_session_create_with_file_params(
               dk.c_str());
     cfg.persistent = dk == "persistent";
   }
+  cfg.tp_world = (int)desc.number("tp_world", 1);
+  cfg.tp_rank = (int)desc.number("tp_rank", 0);
+  DYN_CHECK(cfg.tp_world >= 1 && cfg.tp_rank >= 0 && cfg.tp_rank < cfg.tp_world,
+            "tensor-parallel rank %d outside [0, %d)", cfg.tp_rank, cfg.tp_world);
+  if (cfg.tp_world > 1) cfg.persistent = false;  // the single-GPU persistent kernel has no exchange step
   DYN_CHECK(cfg.layers > 0 && cfg.hidden > 0 && cfg.inter > 0 && cfg.heads > 0 &&
                 cfg.kv_heads > 0 && cfg.head_dim > 0 && cfg.vocab > 0 && cfg.batch > 0,
             "model descriptor lacks geometry (layers/hidden/intermediate/heads/kv_heads/head_dim/vocab)");
   DYN_CHECK(cfg.heads % cfg.kv_heads == 0, "heads %d is not a multiple of kv_heads %d", cfg.heads,
             cfg.kv_heads);
+  cfg.lm_rows = (int)desc.number("lm_head_rows", cfg.vocab);
+  DYN_CHECK(cfg.lm_rows > 0 && (int64_t)cfg.lm_rows * cfg.tp_world == cfg.vocab,
+            "lm_head_rows %d x tp_world %d does not equal the vocabulary %d", cfg.lm_rows, cfg.tp_world,
+            cfg.vocab);
   DYN_CHECK(cfg.head_dim % 2 == 0 && cfg.head_dim <= 256, "head_dim %d unsupported", cfg.head_dim);
   DYN_CHECK(cfg.hidden % 4 == 0 && cfg.inter % 4 == 0, "hidden and intermediate must be multiples of 4");
 
@@ -538,6 +667,16 @@ int dyninfer_cuda_session_create_with_file_params(
     const Json* sh = kv.second.get("shape");
     DYN_CHECK(sh && sh->kind == Json::Arr, "parameter `%s` lacks a shape", kv.first.c_str());
     for (auto& d : sh->arr) p.shape.push_back((int64_t)d.num);
+    if (const Json* st = kv.second.get("strided")) {
+      DYN_CHECK(st->kind == Json::Obj, "parameter `%s`: `strided` must be an object", kv.first.c_str());
+      for (auto& sc : st->obj) {
+        DYN_CHECK(sc.second.kind == Json::Arr && sc.second.arr.size() == 3,
+                  "parameter `%s`: strided component `%s` needs [rows, segment bytes, row stride]",
+                  kv.first.c_str(), sc.first.c_str());
+        p.strided[sc.first] = {(uint64_t)sc.second.arr[0].num, (uint64_t)sc.second.arr[1].num,
+                               (uint64_t)sc.second.arr[2].num};
+      }
+    }
     pd.emplace(kv.first, std::move(p));
   }
 
@@ -579,6 +718,31 @@ int dyninfer_cuda_session_create_with_file_params(
       set_error("parameter `%s`: source_file_index %zu out of range", key.c_str(),
                 fp.source_file_index);
       rc = 1;
+    } else if (it->second.strided.count(comp)) {
+      // length = bytes uploaded = rows * segment; the file span runs to the last row's segment
+      const auto& sd = it->second.strided[comp];
+      const uint64_t span = sd[0] ? (sd[0] - 1) * sd[2] + sd[1] : 0;
+      if (sd[0] == 0 || sd[1] == 0 || sd[2] < sd[1] || sd[0] * sd[1] != fp.length ||
+          fp.offset + span < fp.offset || fp.offset + span > fsize[fp.source_file_index]) {
+        set_error("parameter `%s`: strided range (%llu rows of %llu bytes every %llu, %llu bytes in all) "
+                  "is inconsistent or exceeds file size %llu", key.c_str(), (unsigned long long)sd[0],
+                  (unsigned long long)sd[1], (unsigned long long)sd[2], (unsigned long long)fp.length,
+                  (unsigned long long)fsize[fp.source_file_index]);
+        rc = 1;
+      } else if (it->second.comps.count(comp)) {
+        set_error("duplicate parameter key `%s`", key.c_str());
+        rc = 1;
+      } else {
+        Upload u;
+        u.arena_off = arena_bytes;
+        u.length = fp.length;
+        u.file = fp.source_file_index;
+        u.file_off = fp.offset;
+        u.rows = sd[0], u.seg = sd[1], u.stride = sd[2];
+        it->second.comps.emplace(comp, u);
+        arena_bytes += (fp.length + 64 + 255) / 256 * 256;
+        weight_bytes += fp.length;
+      }
     } else if (fp.length == 0 || fp.offset + fp.length < fp.offset ||
                fp.offset + fp.length > fsize[fp.source_file_index]) {
       set_error("parameter `%s`: byte range [%llu, +%llu) exceeds file size %llu", key.c_str(),
@@ -646,8 +810,10 @@ int dyninfer_cuda_session_create_with_file_params(
     for (auto& p : pd)
       for (auto& c : p.second.comps) {
         const Upload& u = c.second;
-        if (read_range(fds[u.file], u.file_off, u.length, s->arena + u.arena_off, staging,
-                       staging_bytes, files[u.file].path)) {
+        if (u.rows ? read_strided(fds[u.file], u, s->arena + u.arena_off, staging, staging_bytes,
+                                  files[u.file].path)
+                   : read_range(fds[u.file], u.file_off, u.length, s->arena + u.arena_off, staging,
+                                staging_bytes, files[u.file].path)) {
           cudaFreeHost(staging);
           return fail();
         }
@@ -664,7 +830,10 @@ int dyninfer_cuda_session_create_with_file_params(
                 kvd = (int64_t)cfg.kv_heads * cfg.head_dim, I = cfg.inter;
   if (bind_linear(pd, s->arena, "token_embd.weight", cfg.vocab, H, &s->embed)) return fail();
   if (pd.count("output.weight")) {
-    if (bind_linear(pd, s->arena, "output.weight", cfg.vocab, H, &s->lm_head)) return fail();
+    if (bind_linear(pd, s->arena, "output.weight", cfg.lm_rows, H, &s->lm_head)) return fail();
+  } else if (cfg.tp_world > 1) {
+    set_error("a tensor-parallel session needs `output.weight` (this rank's rows of the lm_head)");
+    return fail();
   } else {
     s->lm_head = s->embed;  // tied: same bytes (crates/dyninfer-architecture/src/naming.rs:70-96)
   }
@@ -739,6 +908,14 @@ int dyninfer_cuda_session_create_with_file_params(
       s->mega = true;
     }
   }
+  if (cfg.tp_world > 1) {
+    const size_t n = (size_t)std::max(1, cfg.batch) * cfg.lm_rows * 4;
+    if (dev_alloc(s, (void**)&s->tp_logits, n)) return fail();
+    if (cudaMemset(s->tp_logits, 0, n) != cudaSuccess) {
+      set_error("cudaMemset of the logits slice failed");
+      return fail();
+    }
+  }
   if (host_alloc(s, (void**)&s->logits_host, (size_t)cfg.vocab * 4)) return fail();
   if (dev_alloc(s, (void**)&s->logits, (size_t)cfg.vocab * 4) ||
       dev_alloc(s, (void**)&s->out_token_dev, 64) ||
@@ -758,7 +935,8 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
                  s->logits, s->tokens_dev, s->row_pos_dev, s->row_seq_dev, s->out_token_dev,
                  s->hist_dev, s->hist_count_dev, s->argmax_scratch, s->mega_layers, s->io_dev,
                  s->bar_dev, s->attn_part, s->amax_val, s->amax_idx, s->prof_dev, s->prog_dev,
-                 s->counts_dev, s->batch_logits, s->batch_tokens_dev};
+                 s->counts_dev, s->batch_logits, s->batch_tokens_dev, s->tp_part, s->tp_logits,
+                 s->tp_gather};
   for (void* p : dev)
     if (p) cudaFree(p);
   if (s->logits_host) cudaFreeHost(s->logits_host);
@@ -766,6 +944,12 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
   if (s->stage_host) cudaFreeHost(s->stage_host);
   if (s->ev0) cudaEventDestroy(s->ev0);
   if (s->ev1) cudaEventDestroy(s->ev1);
+  for (int r = 0; r < s->peer.world; r++)
+    if (r != s->peer.rank && s->peer.base[r]) cudaIpcCloseMemHandle(s->peer.base[r]);
+  if (s->peer.base[s->peer.rank]) cudaFree(s->peer.base[s->peer.rank]);
+  if (s->peer.epochs) cudaFree(s->peer.epochs);
+  if (s->peer.error_host) cudaFreeHost(s->peer.error_host);
+  if (s->tp_comm) tp_comm_destroy(s->tp_comm);
   if (s->stream) cudaStreamDestroy(s->stream);
   delete s;
 }
@@ -803,6 +987,7 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
         dev_alloc(s, (void**)&s->ctx, (size_t)rows * qd * 4) ||
         dev_alloc(s, (void**)&s->act, (size_t)rows * c.inter * 4) ||
         dev_alloc(s, (void**)&s->up, (size_t)rows * c.inter * 4) ||
+        (c.tp_world > 1 && dev_alloc(s, (void**)&s->tp_part, (size_t)rows * c.hidden * 4)) ||
         dev_alloc(s, (void**)&s->tokens_dev, (size_t)rows * 8) ||
         dev_alloc(s, (void**)&s->row_pos_dev, (size_t)rows * 8) ||
         dev_alloc(s, (void**)&s->row_seq_dev, (size_t)rows * 8) ||
@@ -998,6 +1183,7 @@ int dyninfer_cuda_session_invoke_paged_chunk_slot(dyninfer_cuda_session_t* s, co
     DYN_CUDA(cudaMemcpyAsync(s->logits_host, s->logits, (size_t)s->cfg.vocab * 4,
                              cudaMemcpyDeviceToHost, s->stream));
   DYN_CUDA(cudaStreamSynchronize(s->stream));
+  if (tp_check_error(s)) return 1;
   if (rows == 1 && s->mega && mega_check_error(s, s->stage_host[4])) return 1;
   if (out_token) *out_token = s->stage_host[3];
   if (want_logits) {
@@ -1042,7 +1228,9 @@ int dyninfer_cuda_session_decode_batch(dyninfer_cuda_session_t* s, const int64_t
   DYN_CUDA(cudaSetDevice(s->device));
   if (!s->batch_logits) {
     if (dev_alloc(s, (void**)&s->batch_logits, (size_t)s->cfg.batch * s->cfg.vocab * 4) ||
-        dev_alloc(s, (void**)&s->batch_tokens_dev, (size_t)s->cfg.batch * 8))
+        dev_alloc(s, (void**)&s->batch_tokens_dev, (size_t)s->cfg.batch * 8) ||
+        (s->cfg.tp_world > 1 &&
+         dev_alloc(s, (void**)&s->tp_gather, (size_t)s->cfg.batch * s->cfg.vocab * 4)))
       return 1;
   }
   int64_t* st = s->stage_host + 8;
@@ -1068,12 +1256,90 @@ int dyninfer_cuda_session_decode_batch(dyninfer_cuda_session_t* s, const int64_t
     if (!s->batch_logits_host &&
         host_alloc(s, (void**)&s->batch_logits_host, (size_t)s->cfg.batch * s->cfg.vocab * 4))
       return 1;
+    // gathered slices [rank][row][lm_rows] -> rows of the whole vocabulary
+    for (int w = 0; s->cfg.tp_world > 1 && w < s->cfg.tp_world; w++)
+      DYN_CUDA(cudaMemcpy2DAsync(s->batch_logits + (size_t)w * s->cfg.lm_rows, (size_t)s->cfg.vocab * 4,
+                                 s->tp_gather + (size_t)w * rows * s->cfg.lm_rows,
+                                 (size_t)s->cfg.lm_rows * 4, (size_t)s->cfg.lm_rows * 4, (size_t)rows,
+                                 cudaMemcpyDeviceToDevice, s->stream));
     DYN_CUDA(cudaMemcpyAsync(s->batch_logits_host, s->batch_logits, (size_t)rows * s->cfg.vocab * 4,
                              cudaMemcpyDeviceToHost, s->stream));
   }
   DYN_CUDA(cudaStreamSynchronize(s->stream));
+  if (tp_check_error(s)) return 1;
   for (int64_t i = 0; i < rows; i++) out_tokens[i] = st[i];
   if (out_logits) *out_logits = want_logits ? s->batch_logits_host : nullptr;  // borrowed until the next call
+  return 0;
+}
+
+size_t dyninfer_cuda_tp_unique_id_bytes(void) { return tp_unique_id_bytes(); }
+
+int dyninfer_cuda_tp_unique_id(uint8_t* out_id, size_t byte_count) {
+  DYN_CHECK(out_id != nullptr && byte_count == tp_unique_id_bytes(),
+            "out_id is NULL or byte_count is not dyninfer_cuda_tp_unique_id_bytes()");
+  return tp_unique_id(out_id);
+}
+
+int dyninfer_cuda_session_tp_init(dyninfer_cuda_session_t* s, const uint8_t* id, size_t byte_count) {
+  DYN_CHECK(s != nullptr, "session is NULL");
+  DYN_CHECK(s->cfg.tp_world > 1, "the session's descriptor does not set tp_world > 1");
+  DYN_CHECK(id != nullptr && byte_count == tp_unique_id_bytes(),
+            "id is NULL or byte_count is not dyninfer_cuda_tp_unique_id_bytes()");
+  DYN_CHECK(s->tp_comm == nullptr, "the session already has a communicator");
+  DYN_CUDA(cudaSetDevice(s->device));
+  return tp_comm_init(&s->tp_comm, id, s->cfg.tp_rank, s->cfg.tp_world);
+}
+
+size_t dyninfer_cuda_tp_peer_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
+
+int dyninfer_cuda_session_tp_peer_handle(dyninfer_cuda_session_t* s, uint8_t* out_handle, size_t byte_count) {
+  DYN_CHECK(s != nullptr, "session is NULL");
+  DYN_CHECK(s->cfg.tp_world > 1 && s->cfg.tp_world <= TP_MAX_WORLD,
+            "peer exchange needs 2..%d tensor-parallel ranks", TP_MAX_WORLD);
+  DYN_CHECK(s->kv_configured, "configure the paged KV first: the exchange region is sized by its chunk");
+  DYN_CHECK(out_handle != nullptr && byte_count == sizeof(cudaIpcMemHandle_t),
+            "out_handle is NULL or byte_count is not dyninfer_cuda_tp_peer_handle_bytes()");
+  DYN_CHECK(s->cfg.hidden % 4 == 0, "peer exchange needs hidden to be a multiple of 4");
+  DYN_CUDA(cudaSetDevice(s->device));
+  TpPeer& p = s->peer;
+  if (!p.base[s->cfg.tp_rank]) {
+    p.rank = s->cfg.tp_rank, p.world = s->cfg.tp_world, p.max_rows = s->max_rows;
+    p.region_bytes = tp_peer_region_bytes(s->max_rows, s->cfg.hidden);
+    p.flags_off = tp_peer_flags_offset(s->max_rows, s->cfg.hidden);
+    void* region = nullptr;
+    if (dev_alloc(s, &region, p.region_bytes) || dev_alloc(s, (void**)&p.epochs, TP_PEER_BLOCKS * 4)) return 1;
+    p.base[p.rank] = reinterpret_cast<uint8_t*>(region);
+    DYN_CUDA(cudaMemset(region, 0, p.region_bytes));
+    DYN_CUDA(cudaMemset(p.epochs, 0, TP_PEER_BLOCKS * 4));
+    DYN_CUDA(cudaHostAlloc((void**)&p.error_host, 64, cudaHostAllocMapped));
+    *p.error_host = 0;
+    DYN_CUDA(cudaHostGetDevicePointer((void**)&p.error_dev, p.error_host, 0));
+    DYN_CUDA(cudaDeviceSynchronize());
+  }
+  cudaIpcMemHandle_t h;
+  DYN_CUDA(cudaIpcGetMemHandle(&h, p.base[p.rank]));
+  memcpy(out_handle, &h, sizeof h);
+  return 0;
+}
+
+int dyninfer_cuda_session_tp_peer_attach(dyninfer_cuda_session_t* s, const uint8_t* handles, size_t byte_count) {
+  DYN_CHECK(s != nullptr, "session is NULL");
+  TpPeer& p = s->peer;
+  DYN_CHECK(p.base[s->cfg.tp_rank] != nullptr && !p.attached,
+            "call dyninfer_cuda_session_tp_peer_handle first (and attach once)");
+  DYN_CHECK(handles != nullptr && byte_count == (size_t)p.world * sizeof(cudaIpcMemHandle_t),
+            "handles must hold one handle per rank, in rank order");
+  DYN_CUDA(cudaSetDevice(s->device));
+  for (int r = 0; r < p.world; r++) {
+    if (r == p.rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handles + (size_t)r * sizeof h, sizeof h);
+    void* ptr = nullptr;
+    DYN_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    p.base[r] = reinterpret_cast<uint8_t*>(ptr);
+  }
+  p.attached = true;
+  destroy_graphs(s);
   return 0;
 }
 
@@ -1126,6 +1392,7 @@ int dyninfer_cuda_session_decode_loop(dyninfer_cuda_session_t* s, int64_t first_
   DYN_CUDA(cudaEventRecord(s->ev1, s->stream));
   s->launches += s->loop_nodes * steps;
   DYN_CUDA(cudaStreamSynchronize(s->stream));
+  if (tp_check_error(s)) return 1;
   if (out_device_ms) DYN_CUDA(cudaEventElapsedTime(out_device_ms, s->ev0, s->ev1));
   if (out_tokens)
     DYN_CUDA(cudaMemcpy(out_tokens, s->hist_dev, steps * 8, cudaMemcpyDeviceToHost));

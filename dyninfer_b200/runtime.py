@@ -99,20 +99,50 @@ class CudaSession:
         self.kv_dtype = model.kv_dtype
         self.kv_elem = 4 if self.kv_dtype == "f32" else 2
         self.max_kv = int(model.max_kv)
-        desc = ck.model_descriptor(model.catalog, kv_dtype=self.kv_dtype, decode_kernel=model.decode_kernel,
-                                   batch=max(1, int(config.batch_size)))
         files = (_lib.ParameterFile * len(model.plan.file_paths))(
             *[_lib.ParameterFile(p.encode()) for p in model.plan.file_paths])
-        self._keys = [p.external_key.encode() for p in model.plan.parameters]
+        kv_heads = cfg["kv_heads"]
+        if model.tp:
+            # one rank of a tensor-parallel group: this rank's slices and share of the geometry
+            from . import tp as _tp
+            rank, world = model.tp
+            desc, ranges = _tp.session_inputs(model.catalog, rank, world, kv_dtype=self.kv_dtype,
+                                              batch=max(1, int(config.batch_size)))
+            kv_heads = desc["kv_heads"]
+        else:
+            desc = ck.model_descriptor(model.catalog, kv_dtype=self.kv_dtype, decode_kernel=model.decode_kernel,
+                                       batch=max(1, int(config.batch_size)))
+            ranges = [(p.external_key, p.source_file_index, p.offset, p.length) for p in model.plan.parameters]
+        self._keys = [r[0].encode() for r in ranges]
         params = (_lib.FileParam * len(self._keys))(
-            *[_lib.FileParam(k, p.source_file_index, p.offset, p.length)
-              for k, p in zip(self._keys, model.plan.parameters)])
+            *[_lib.FileParam(k, r[1], r[2], r[3]) for k, r in zip(self._keys, ranges)])
         check(lib().dyninfer_cuda_session_create_with_file_params(
             model.device_uri.encode(), json.dumps(desc).encode(), files, len(files), params,
             len(self._keys), C.byref(self._h)))
+        if model.tp:
+            from . import tp as _tp
+            n = lib().dyninfer_cuda_tp_unique_id_bytes()
+
+            def make_id():
+                buf = C.create_string_buffer(n)
+                check(lib().dyninfer_cuda_tp_unique_id(buf, n))
+                return buf.raw
+            uid = _tp.exchange_unique_id(make_id)
+            check(lib().dyninfer_cuda_session_tp_init(self._h, uid, len(uid)))
         check(lib().dyninfer_cuda_session_configure_paged_kv(
-            self._h, cfg["layers"], PAGE_SIZE, cfg["kv_heads"], cfg["head_dim"], self.kv_elem,
+            self._h, cfg["layers"], PAGE_SIZE, kv_heads, cfg["head_dim"], self.kv_elem,
             model.chunk_size, cfg["vocab"]))
+        if model.tp and model.tp_exchange == "peer":
+            # partial products are summed by this library's own kernel over peer memory
+            import torch.distributed as dist
+            n = lib().dyninfer_cuda_tp_peer_handle_bytes()
+            buf = C.create_string_buffer(n)
+            check(lib().dyninfer_cuda_session_tp_peer_handle(self._h, buf, n))
+            handles = [None] * model.tp[1]
+            dist.all_gather_object(handles, buf.raw)
+            blob = b"".join(handles)
+            check(lib().dyninfer_cuda_session_tp_peer_attach(self._h, blob, len(blob)))
+            dist.barrier()
         self._pages_ready = False
         self._tok1 = (C.c_int64 * 1)()
         self._out1 = C.c_int64(-1)
@@ -299,8 +329,16 @@ class LoadedModel:
 
     def __init__(self, catalog: ck.Catalog, plan: ck.ProviderPlan, target: reg.TargetProfile,
                  device_uri: str, coverage: reg.CoverageReport, max_kv: int, kv_dtype: str,
-                 chunk_size: int, decode_kernel: str = "persistent"):
+                 chunk_size: int, decode_kernel: str = "persistent", tp: tuple | None = None,
+                 tp_exchange: str = "peer"):
         self.catalog, self.plan, self.target, self.device_uri = catalog, plan, target, device_uri
+        # (rank, world) of a tensor-parallel group: one process per GPU, every process loads the
+        # same checkpoint and uploads its own slices; torch.distributed must be initialised
+        self.tp = tp if tp and tp[1] > 1 else None
+        # "peer": o_proj / down partial sums through the fused peer-memory kernel; "nccl": all-reduce
+        if tp_exchange not in ("peer", "nccl"):
+            raise DynInferError(f"tp_exchange `{tp_exchange}` unknown (peer | nccl)")
+        self.tp_exchange = tp_exchange
         self.coverage, self.max_kv, self.kv_dtype, self.chunk_size = coverage, max_kv, kv_dtype, chunk_size
         # "persistent": one cooperative kernel per decoded token; "graph": a captured graph of
         # per-operator kernels (the path multi-row chunks always take)
@@ -418,12 +456,14 @@ class ModelLoader:
         return reg.dry_run_coverage(catalog.config, params, target, self.registry)
 
     def load(self, path: str, target: str = "cuda", max_kv: int = 2048, kv_dtype: str = "f32",
-             chunk_size: int = CHUNK_SIZE, decode_kernel: str = "persistent") -> LoadedModel:
+             chunk_size: int = CHUNK_SIZE, decode_kernel: str = "persistent",
+             tp: tuple | None = None, tp_exchange: str = "peer") -> LoadedModel:
         profile, uri = self.resolve_target(target)
         catalog = self.bind(path)
         coverage = self.kernel_coverage(catalog, profile).require_complete()
         plan = ck.build_runtime_provider_plan(catalog)
-        return LoadedModel(catalog, plan, profile, uri, coverage, max_kv, kv_dtype, chunk_size, decode_kernel)
+        return LoadedModel(catalog, plan, profile, uri, coverage, max_kv, kv_dtype, chunk_size, decode_kernel, tp,
+                           tp_exchange)
 
 
 # ----------------------------------------------------------------------- generation

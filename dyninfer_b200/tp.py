@@ -143,3 +143,44 @@ def read_shard(files: list, sp: ShardedParameter) -> dict:
                 buf += f.read(r.seg_bytes)
         out[r.component] = bytes(buf)
     return out
+
+
+def session_inputs(cat: Catalog, rank: int, world: int, **overrides):
+    """What rank `rank` hands to the session constructor: the model descriptor with this rank's
+    share of the geometry (heads, kv_heads and intermediate divided by `world`, `lm_head_rows`
+    = vocab / world, per-parameter local shapes, strided spans for the row-parallel products) and
+    the byte ranges as `(key, source_file_index, offset, byte_count)`, sorted by key."""
+    from .checkpoint import PARAMETER_SCOPE, model_descriptor
+    shards = plan(cat, rank, world)
+    cfg = cat.config
+    if int(cfg["intermediate"]) % world or int(cfg["vocab"]) % world:
+        raise CheckpointError(f"tensor-parallel degree {world} must divide intermediate and vocab")
+    desc = model_descriptor(cat, **overrides)
+    desc.update(tp_rank=rank, tp_world=world, heads=int(cfg["heads"]) // world,
+                kv_heads=int(cfg.get("kv_heads", cfg["heads"])) // world,
+                head_dim=int(cfg.get("head_dim", int(cfg["hidden"]) // int(cfg["heads"]))),
+                intermediate=int(cfg["intermediate"]) // world, lm_head_rows=int(cfg["vocab"]) // world,
+                decode_kernel="graph")
+    params, ranges = {}, []
+    for name, sp in shards.items():
+        src = cat.parameters.get(name) or cat.parameters["token_embd.weight"]    # tied lm_head alias
+        entry = {"encoding": sp.encoding, "shape": list(sp.shape), "group": src.group,
+                 "aux": (src.components[1].type_name if len(src.components) > 1 else "")}
+        strided = {r.component: [r.rows, r.seg_bytes, r.row_stride] for r in sp.ranges if r.rows > 1}
+        if strided:
+            entry["strided"] = strided
+        params[name] = entry
+        for r in sp.ranges:
+            ranges.append((f"{PARAMETER_SCOPE}::{name}::{r.component}", r.source_file_index, r.offset, r.nbytes))
+    desc["params"] = params
+    ranges.sort(key=lambda t: t[0])
+    return desc, ranges
+
+
+def exchange_unique_id(make_id):
+    """Rank 0 calls `make_id()` (bytes); every rank of the default torch.distributed group returns
+    the same bytes. The host-side hand-off the native communicator needs before its first step."""
+    import torch.distributed as dist
+    box = [make_id() if dist.get_rank() == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    return box[0]

@@ -228,6 +228,41 @@ int dyninfer_cuda_session_decode_batch(dyninfer_cuda_session_t* session, const i
                                        const int64_t* positions, const int64_t* slots, size_t count,
                                        int64_t* out_tokens, float** out_logits, int want_logits);
 
+/* ---- tensor parallelism (extension: one process per GPU, one session per rank) ------------- */
+
+/* A session whose descriptor sets "tp_world" W > 1 and "tp_rank" r is one rank of a tensor-parallel
+ * group. Its descriptor carries this rank's share of the geometry ("heads", "kv_heads",
+ * "intermediate" divided by W; "lm_head_rows" = vocab / W) and its byte ranges are this rank's
+ * slices, uploaded unchanged: consecutive rows of attn_q/k/v, ffn_gate/up and `output.weight`
+ * (rows [r * vocab / W, ...) of the lm_head), and, for attn_output / ffn_down, one span of the
+ * blocks of every row. Such a span is a strided range: the parameter's descriptor entry names it
+ * under "strided": {"<component>": [rows, segment_bytes, row_stride_bytes]}, the file param's
+ * `offset` is the first segment and `length` = rows * segment_bytes. Norm vectors and the embedding
+ * table are replicated. Each step sums the ranks' partial o_proj and down products (all-reduce,
+ * 2 per layer) and gathers the ranks' logits slices; KV cache and attention stay local to the
+ * rank's heads. Every rank must make the same calls in the same order.
+ *
+ * One rank obtains an id (dyninfer_cuda_tp_unique_id), the host program hands the same bytes to
+ * all ranks (any channel), and every rank calls dyninfer_cuda_session_tp_init before its first
+ * invoke. NCCL is looked up at run time; without it these calls fail with a message. */
+size_t dyninfer_cuda_tp_unique_id_bytes(void);
+int dyninfer_cuda_tp_unique_id(uint8_t* out_id, size_t byte_count);
+int dyninfer_cuda_session_tp_init(dyninfer_cuda_session_t* session, const uint8_t* id, size_t byte_count);
+
+/* Optional: sum the partial products over peer memory (NVLink / NVSwitch loads) instead of the
+ * all-reduce. After configure_paged_kv every rank calls _tp_peer_handle (allocates its exchange
+ * region and returns an inter-process handle to it), the host program collects the handles of all
+ * ranks in rank order and gives the concatenation to _tp_peer_attach on every rank. From then on
+ * each o_proj / down product writes this rank's partial rows into its region and ONE kernel per
+ * product signals the peers, waits for them (bounded; a rank that does not arrive makes the call
+ * fail with a message), adds all ranks' rows in rank order to the residual and applies the RMSNorm
+ * that feeds the next product. The logits slices are still gathered through the communicator. */
+size_t dyninfer_cuda_tp_peer_handle_bytes(void);
+int dyninfer_cuda_session_tp_peer_handle(dyninfer_cuda_session_t* session, uint8_t* out_handle,
+                                         size_t byte_count);
+int dyninfer_cuda_session_tp_peer_attach(dyninfer_cuda_session_t* session, const uint8_t* handles,
+                                         size_t byte_count);
+
 /* ---- session extensions (no reference precedent) --------------------------- */
 
 /* Total bytes of uploaded parameters (the reference's schema total_bytes used by

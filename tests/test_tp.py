@@ -119,3 +119,67 @@ def test_plan_ranges_and_rejections(tmp_path):
         tp.plan(cat, 2, 2)
     with pytest.raises(ck.CheckpointError):                                 # K/8 = 64 is not a Q6_K block multiple
         tp.shard_parameter(cat.parameters["token_embd.weight"], 0, 8, "row")
+
+
+def test_session_inputs_describe_the_rank(tmp_path):
+    """The descriptor of a rank carries its share of the geometry; the uploaded bytes of all ranks add
+    up to every sharded tensor once (replicated ones once per rank)."""
+    from dyninfer_b200 import checkpoint as ck, tp
+    path = str(tmp_path / "tp.gguf")
+    _write_model(path)
+    cat = ck.open_catalog(path)
+    d0, r0 = tp.session_inputs(cat, 0, 2, kv_dtype="f32")
+    d1, r1 = tp.session_inputs(cat, 1, 2, kv_dtype="f32")
+    for d, rank in ((d0, 0), (d1, 1)):
+        assert (d["tp_rank"], d["tp_world"]) == (rank, 2) and d["decode_kernel"] == "graph"
+        assert d["heads"] == CFG["heads"] // 2 and d["kv_heads"] == CFG["kv_heads"] // 2
+        assert d["intermediate"] == CFG["intermediate"] // 2 and d["lm_head_rows"] == CFG["vocab"] // 2
+        assert d["head_dim"] == CFG["head_dim"] and d["hidden"] == CFG["hidden"] and d["vocab"] == CFG["vocab"]
+        assert d["params"]["blk.0.attn_output.weight"]["strided"]["data"][0] == CFG["hidden"]
+        assert "strided" not in d["params"]["blk.0.attn_q.weight"]
+    by_key0, by_key1 = {r[0]: r for r in r0}, {r[0]: r for r in r1}
+    assert by_key0.keys() == by_key1.keys() and "weights::output.weight::data" in by_key0
+    for name, p in cat.parameters.items():
+        key = f"weights::{name}::data"
+        total = by_key0[key][3] + by_key1[key][3]
+        want = p.components[0].length * (2 if tp.plan(cat, 0, 2)[name].kind == "replicated" else 1)
+        assert total == want, name
+
+
+def test_strided_range_is_validated_before_any_device_work(tmp_path):
+    """A strided span that is inconsistent with its byte count or leaves the file is refused by the
+    session constructor (no GPU is needed to get that far)."""
+    import ctypes as C
+    import json
+    from dyninfer_b200 import _lib, checkpoint as ck, tp
+    path = str(tmp_path / "tp.gguf")
+    _write_model(path)
+    cat = ck.open_catalog(path)
+    desc, ranges = tp.session_inputs(cat, 1, 2, kv_dtype="f32")
+    lib = _lib.lib()
+    lib.dyninfer_cuda_last_error.restype = C.c_char_p
+
+    def create(desc, ranges):
+        files = (_lib.ParameterFile * 1)(_lib.ParameterFile(path.encode()))
+        keys = [r[0].encode() for r in ranges]
+        params = (_lib.FileParam * len(keys))(*[_lib.FileParam(k, r[1], r[2], r[3]) for k, r in zip(keys, ranges)])
+        h = C.c_void_p()
+        rc = lib.dyninfer_cuda_session_create_with_file_params(b"cuda:0", json.dumps(desc).encode(), files, 1,
+                                                               params, len(keys), C.byref(h))
+        msg = lib.dyninfer_cuda_last_error().decode() if rc else ""
+        if not rc:
+            lib.dyninfer_cuda_session_destroy(h)
+        return rc, msg
+
+    bad = json.loads(json.dumps(desc))
+    bad["params"]["blk.0.ffn_down.weight"]["strided"]["data"][0] += 1        # rows x segment != byte count
+    rc, msg = create(bad, ranges)
+    assert rc != 0 and "strided range" in msg and "ffn_down" in msg
+    far = json.loads(json.dumps(desc))
+    far["params"]["blk.0.ffn_down.weight"]["strided"]["data"][2] = 1 << 40    # last row far beyond the file
+    rc, msg = create(far, ranges)
+    assert rc != 0 and "exceeds file size" in msg
+    wrong = json.loads(json.dumps(desc))
+    wrong["lm_head_rows"] = CFG["vocab"]                                      # not vocab / tp_world
+    rc, msg = create(wrong, ranges)
+    assert rc != 0 and "lm_head_rows" in msg

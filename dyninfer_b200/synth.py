@@ -177,10 +177,13 @@ def linear_shapes(cfg: dict) -> dict:
 
 def write_qwen3_gguf(path: str, cfg: dict, seed: int = 0, encodings: dict | None = None,
                      embd: str = "gguf.q6_k", output: str | None = None,
-                     default: str = "gguf.q4_0") -> str:
+                     default: str = "gguf.q4_0", repeat_layers: bool = False) -> str:
     """Seeded Qwen3-shaped GGUF. `encodings` overrides the encoding per linear slot
     (e.g. {"attn_v": "gguf.q4_1", "ffn_down": "gguf.q8_0"}); `output`=None ties the
-    lm_head to token_embd (no output.weight tensor)."""
+    lm_head to token_embd (no output.weight tensor). `repeat_layers` writes layer 0's bytes
+    for every layer (each layer still has its own tensors and file ranges): the file is as large
+    and is read exactly like one with distinct layers, but is generated in a fraction of the time,
+    for throughput runs of the largest shapes."""
     enc = dict.fromkeys(linear_shapes(cfg), default)
     enc.update(encodings or {})
     a = "qwen3"
@@ -206,7 +209,10 @@ def write_qwen3_gguf(path: str, cfg: dict, seed: int = 0, encodings: dict | None
     t["output_norm.weight"] = ((cfg["hidden"],), 0, ones_h)
     for l in range(cfg["layers"]):
         for slot, (n, k) in linear_shapes(cfg).items():
-            add(f"blk.{l}.{slot}.weight", enc[slot], n, k)
+            if repeat_layers and l > 0:
+                t[f"blk.{l}.{slot}.weight"] = t[f"blk.0.{slot}.weight"]
+            else:
+                add(f"blk.{l}.{slot}.weight", enc[slot], n, k)
         t[f"blk.{l}.attn_norm.weight"] = ((cfg["hidden"],), 0, ones_h)
         t[f"blk.{l}.ffn_norm.weight"] = ((cfg["hidden"],), 0, ones_h)
         t[f"blk.{l}.attn_q_norm.weight"] = ((cfg["head_dim"],), 0, ones_d)

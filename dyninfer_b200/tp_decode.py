@@ -42,7 +42,8 @@ def _checkpoint(model: str, layers: int | None):
     if model == "8b-mixed":
         kw = dict(encodings={"attn_v": "gguf.q4_1", "ffn_down": "gguf.q8_0"}, embd="gguf.q6_k", output="gguf.q6_k")
     elif model == "32b-q4_0":
-        kw = dict(embd="gguf.q6_k", output="gguf.q6_k")
+        # every layer carries layer 0's bytes: 18 GB of distinct random blocks take minutes to draw
+        kw = dict(embd="gguf.q6_k", output="gguf.q6_k", repeat_layers=True)
     return path, cfg, kw
 
 

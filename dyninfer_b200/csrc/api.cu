@@ -7,6 +7,9 @@
 
 #include <string>
 
+#include <stdlib.h>
+
+
 #include "common.cuh"
 
 namespace dyn {
@@ -43,6 +46,19 @@ int keep_scratch_pool_cached() {
   DYN_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
   tuned_device = dev;
   return 0;
+}
+
+static thread_local void* g_scratch = nullptr;
+static thread_local size_t g_scratch_bytes = 0;
+void set_thread_scratch(void* ptr, size_t bytes) { g_scratch = ptr, g_scratch_bytes = ptr ? bytes : 0; }
+void* thread_scratch(size_t bytes) { return bytes <= g_scratch_bytes ? g_scratch : nullptr; }
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("DYNINFER_CUDA_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 void count_launch(int n) { *g_counter += (uint64_t)n; }

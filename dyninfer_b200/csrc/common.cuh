@@ -29,6 +29,31 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
   } while (0)
 
 int keep_scratch_pool_cached();  // raise the default memory pool's release threshold (idempotent)
+// A caller-owned scratch region for the products launched by this thread (a session sets its own
+// for the duration of a call): products whose scratch fits use it instead of the stream-ordered
+// allocator, so consecutive kernels of a captured graph are not separated by allocation nodes.
+void set_thread_scratch(void* ptr, size_t bytes);
+void* thread_scratch(size_t bytes);  // the region when it holds `bytes`, else nullptr
+
+// Programmatic dependent launch (sm_90+). A kernel launched with launch_pdl may start while the
+// kernel before it in the stream is still running; it must not touch anything that kernel (or an
+// earlier one) produces, nor write global memory, before pdl_wait(). pdl_trigger() lets the next
+// kernel of the stream start early; kernels that never call it release it when they exit.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+bool pdl_enabled();  // DYNINFER_CUDA_PDL=0 turns the attribute off (plain launches)
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 // Counts kernels launched by this library (per thread-attached counter).
 void count_launch(int n = 1);

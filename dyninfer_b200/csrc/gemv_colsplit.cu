@@ -133,10 +133,8 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
   uint4* xq = reinterpret_cast<uint4*>(cs_smem + G::RING_BYTES);
   float* sx8 = reinterpret_cast<float*>(xq + (size_t)(a.K >> 8) * 64);
   float* red = sx8 + (a.K >> 5);
-  if (threadIdx.x == 0) {
-    s_abort = 0;
-    if (blockIdx.x == 0) *a.error = 0;  // a wait that runs out (seconds later) sets it
-  }
+  pdl_trigger();  // the next kernel of the stream may start its own weight fetch
+  if (threadIdx.x == 0) s_abort = 0;
   if (lane == 0) {
     for (int i = 0; i < CS_NST; i++) mbar_init(bars + i, 1);
     mbar_fence_init();
@@ -176,6 +174,10 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
 #pragma unroll
   for (int q = 0; q < CS_NST; q++) issue();
 
+  // The weights do not depend on the kernels before this one: the first stages are already in
+  // flight. Everything else (the activation row, the scratch words) does.
+  pdl_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) *a.error = 0;  // a wait that runs out (seconds later) sets it
   // while the first stages are in flight: arrange the activation row in shared memory
   const float out_scale =
       cs_stage_x(a.x, a.x_bf16, a.K, reinterpret_cast<uint2*>(xq), sx8, red, ENC == E_Q4_0 ? 8.0f : 1.0f);
@@ -297,6 +299,8 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
 __global__ void __launch_bounds__(256)
 cs_reduce_kernel(const float* __restrict__ partial, int S, int64_t N, const float* __restrict__ misc,
                  float* y, const float* residual) {
+  pdl_trigger();
+  pdl_wait();  // the partial sums come from the kernel before this one
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= N) return;
   float v = 0.f;
@@ -389,12 +393,13 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
     attr_done = true;
   }
   if (w.enc == E_Q4_0)
-    gemv_cs_q4_kernel<E_Q4_0><<<p.grid, CS_WARPS * 32, p.smem, s>>>(a);
+    DYN_CUDA(launch_pdl(gemv_cs_q4_kernel<E_Q4_0>, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a));
   else
-    gemv_cs_q4_kernel<E_Q4_1><<<p.grid, CS_WARPS * 32, p.smem, s>>>(a);
+    DYN_CUDA(launch_pdl(gemv_cs_q4_kernel<E_Q4_1>, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a));
   count_launch(1);
   if (p.S > 1) {
-    cs_reduce_kernel<<<(unsigned)((w.rows + 255) / 256), 256, 0, s>>>(a.partial, p.S, w.rows, a.misc, y, residual);
+    DYN_CUDA(launch_pdl(cs_reduce_kernel, dim3((unsigned)((w.rows + 255) / 256)), dim3(256), 0, s,
+                        (const float*)a.partial, p.S, (int64_t)w.rows, (const float*)a.misc, y, residual));
     count_launch();
   }
   DYN_CUDA(cudaGetLastError());

@@ -170,10 +170,8 @@ __global__ void __launch_bounds__(Q6_WARPS * 32, 1) gemv_cs_q6k_kernel(const Q6A
   __half* xlo = xhi + a.K + 8;  // 16 bytes apart from a multiple of 128: hi and lo lanes hit different banks
   float* sx = reinterpret_cast<float*>(xlo + a.K + 8);
   float* red = sx + (a.K >> 4);
-  if (threadIdx.x == 0) {
-    s_abort = 0;
-    if (blockIdx.x == 0) *a.error = 0;
-  }
+  pdl_trigger();  // the next kernel of the stream may start its own weight fetch
+  if (threadIdx.x == 0) s_abort = 0;
   if (lane == 0) {
     for (int i = 0; i < Q6_NST; i++) mbar_init(bars + i, 1);
     mbar_fence_init();
@@ -211,6 +209,10 @@ __global__ void __launch_bounds__(Q6_WARPS * 32, 1) gemv_cs_q6k_kernel(const Q6A
 #pragma unroll
   for (int q = 0; q < Q6_NST; q++) issue();
 
+  // the weights do not depend on the kernels before this one (their first stages are in flight);
+  // the activation row and the scratch words do
+  pdl_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) *a.error = 0;
   const float out_scale = q6_stage_x(a.x, a.x_bf16, a.K, xhi, xlo, sx, red);
   if (blockIdx.x == 0 && threadIdx.x == 0) a.misc[0] = out_scale;
   __syncthreads();
@@ -266,6 +268,8 @@ __global__ void __launch_bounds__(Q6_WARPS * 32, 1) gemv_cs_q6k_kernel(const Q6A
 __global__ void __launch_bounds__(256)
 q6_reduce_kernel(const float* __restrict__ partial, int S, int64_t N, const float* __restrict__ misc, float* y,
                  const float* residual) {
+  pdl_trigger();
+  pdl_wait();  // the partial sums come from the kernel before this one
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= N) return;
   float v = 0.f;
@@ -335,10 +339,11 @@ int launch_gemv_cs_q6k(const WRef& w, const void* x, int x_type, float* y, const
     DYN_CUDA(cudaFuncSetAttribute(gemv_cs_q6k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q6_MAX_SMEM));
     attr_done = true;
   }
-  gemv_cs_q6k_kernel<<<p.grid, Q6_WARPS * 32, p.smem, s>>>(a);
+  DYN_CUDA(launch_pdl(gemv_cs_q6k_kernel, dim3(p.grid), dim3(Q6_WARPS * 32), p.smem, s, a));
   count_launch(1);
   if (p.S > 1) {
-    q6_reduce_kernel<<<(unsigned)((w.rows + 255) / 256), 256, 0, s>>>(a.partial, p.S, w.rows, a.misc, y, residual);
+    DYN_CUDA(launch_pdl(q6_reduce_kernel, dim3((unsigned)((w.rows + 255) / 256)), dim3(256), 0, s, (const float*)a.partial,
+                        p.S, (int64_t)w.rows, (const float*)a.misc, y, residual));
     count_launch();
   }
   DYN_CUDA(cudaGetLastError());

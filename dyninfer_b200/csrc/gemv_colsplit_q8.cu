@@ -93,10 +93,8 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 1) gemv_cs_q8_0_kernel(const Q8
   __half* xlo = xhi + a.K + 8;  // 16 bytes off a multiple of 128: hi and lo lanes hit different banks
   float* sx = reinterpret_cast<float*>(xlo + a.K + 8);
   float* red = sx + (a.K >> 5);
-  if (threadIdx.x == 0) {
-    s_abort = 0;
-    if (blockIdx.x == 0) *a.error = 0;
-  }
+  pdl_trigger();  // the next kernel of the stream may start its own weight fetch
+  if (threadIdx.x == 0) s_abort = 0;
   if (lane == 0) {
     for (int i = 0; i < Q8_NST; i++) mbar_init(bars + i, 1);
     mbar_fence_init();
@@ -133,6 +131,10 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 1) gemv_cs_q8_0_kernel(const Q8
 #pragma unroll
   for (int q = 0; q < Q8_NST; q++) issue();
 
+  // the weights do not depend on the kernels before this one (their first stages are in flight);
+  // the activation row and the scratch words do
+  pdl_wait();
+  if (blockIdx.x == 0 && threadIdx.x == 0) *a.error = 0;
   const float out_scale = q8_stage_x(a.x, a.x_bf16, a.K, xhi, xlo, sx, red);
   if (blockIdx.x == 0 && threadIdx.x == 0) a.misc[0] = out_scale;
   __syncthreads();
@@ -232,6 +234,8 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 1) gemv_cs_q8_0_kernel(const Q8
 __global__ void __launch_bounds__(256)
 q8_reduce_kernel(const float* __restrict__ partial, int S, int64_t N, const float* __restrict__ misc, float* y,
                  const float* residual) {
+  pdl_trigger();
+  pdl_wait();  // the partial sums come from the kernel before this one
   const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= N) return;
   float v = 0.f;
@@ -299,10 +303,11 @@ int launch_gemv_cs_q8_0(const WRef& w, const void* x, int x_type, float* y, cons
     DYN_CUDA(cudaFuncSetAttribute(gemv_cs_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q8_MAX_SMEM));
     attr_done = true;
   }
-  gemv_cs_q8_0_kernel<<<p.grid, Q8_WARPS * 32, p.smem, s>>>(a);
+  DYN_CUDA(launch_pdl(gemv_cs_q8_0_kernel, dim3(p.grid), dim3(Q8_WARPS * 32), p.smem, s, a));
   count_launch(1);
   if (p.S > 1) {
-    q8_reduce_kernel<<<(unsigned)((w.rows + 255) / 256), 256, 0, s>>>(a.partial, p.S, w.rows, a.misc, y, residual);
+    DYN_CUDA(launch_pdl(q8_reduce_kernel, dim3((unsigned)((w.rows + 255) / 256)), dim3(256), 0, s, (const float*)a.partial,
+                        p.S, (int64_t)w.rows, (const float*)a.misc, y, residual));
     count_launch();
   }
   DYN_CUDA(cudaGetLastError());

@@ -412,6 +412,7 @@ int launch_gemv_mma(const WRef& w, const void* x, int x_type, int M, float* y, c
   else
     plan_shape(w, M, x_type == E_BF16, &sh);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  if (!ws) ws = reinterpret_cast<uint8_t*>(workspace = thread_scratch(sh.bytes));  // the caller's region
   if (!ws) {
     if (keep_scratch_pool_cached()) return 1;
     DYN_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&ws), sh.bytes, s));

@@ -123,7 +123,12 @@ int launch_linear(const WRef& w, const void* x, int x_type, int64_t m, float* y,
   DYN_CHECK(x_type == E_F32 || x_type == E_BF16, "linear: x_type must be f32 or bf16, got %d",
             x_type);
   DYN_CHECK(m >= 1, "linear: m must be >= 1");
-  if (m > 16) {  // many rows: dequant-in-shared-memory tensor-core GEMM
+  // more rows than one pass of the tensor-core GEMV takes (4 with f32 activations, 8 with bf16):
+  // dequant-in-shared-memory tensor-core GEMM, one pass over the weights for all rows
+  // (below 17 rows only for the encodings whose GEMM producer is cheap enough to beat repeated GEMV
+  // passes: the GEMM's dequantisation cost does not shrink with the row count)
+  const bool cheap_producer = w.enc == E_Q4_0 || w.enc == E_MLX_U4;
+  if (m > 16 || (cheap_producer && m > (x_type == E_BF16 ? 8 : 4))) {
     bool handled = false;
     if (launch_dqgemm_tc(w, x, x_type, m, y, residual, s, &handled)) return 1;
     if (handled) return 0;

@@ -34,13 +34,42 @@ __device__ __forceinline__ float block_sum(float v, float* smem) {
 }
 
 // y = (x * inv) * w with inv = 1 / sqrt(sum(x^2)/H + eps)  (kernels.rs:817-829)
+// PER > 0: the row fits PER elements per thread; they are loaded once, all loads in flight
+// together, and stay in registers for the second pass (the loop form waits for one load after the
+// other because x and y may alias). Element-to-thread assignment and summation order are the same
+// in both forms.
+template <int PER>
 __global__ void __launch_bounds__(256)
 rms_norm_kernel(const float* x, const void* __restrict__ w, int w_type, int64_t width, float eps,
                 float* y) {
   __shared__ float red[32];
+  pdl_trigger();  // a product launched next may begin fetching its weights
   const float* xr = x + (int64_t)blockIdx.x * width;
   float* yr = y + (int64_t)blockIdx.x * width;
   float ss = 0.f;
+  if (PER > 0) {
+    float v[PER > 0 ? PER : 1], wv[PER > 0 ? PER : 1];
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+      const int64_t i = threadIdx.x + (int64_t)k * blockDim.x;
+      v[k] = i < width ? xr[i] : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+      const int64_t i = threadIdx.x + (int64_t)k * blockDim.x;
+      wv[k] = i < width ? aux_load(reinterpret_cast<const uint8_t*>(w), w_type, i) : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < PER; k++) ss = fmaf(v[k], v[k], ss);  // absent elements add +0
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+      const int64_t i = threadIdx.x + (int64_t)k * blockDim.x;
+      if (i < width) yr[i] = __fmul_rn(__fmul_rn(v[k], inv), wv[k]);
+    }
+    return;
+  }
   for (int64_t i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
   ss = block_sum(ss, red);
   const float ms = ss / (float)width;
@@ -55,7 +84,15 @@ int launch_rms_norm(const float* x, const void* w, int w_type, int64_t rows, int
                     float eps, float* y, cudaStream_t s) {
   if (rows == 0) return 0;
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 32);
-  rms_norm_kernel<<<(unsigned)rows, threads, 0, s>>>(x, w, w_type, width, eps, y);
+  if (width <= 8 * threads) {
+    rms_norm_kernel<8><<<(unsigned)rows, threads, 0, s>>>(x, w, w_type, width, eps, y);
+  } else if (width <= 16 * threads) {
+    rms_norm_kernel<16><<<(unsigned)rows, threads, 0, s>>>(x, w, w_type, width, eps, y);
+  } else if (width <= 32 * threads) {
+    rms_norm_kernel<32><<<(unsigned)rows, threads, 0, s>>>(x, w, w_type, width, eps, y);
+  } else {
+    rms_norm_kernel<0><<<(unsigned)rows, threads, 0, s>>>(x, w, w_type, width, eps, y);
+  }
   count_launch();
   DYN_CUDA(cudaGetLastError());
   return 0;
@@ -95,6 +132,7 @@ int launch_rope(float* x, int64_t s_rows, int64_t heads, int64_t d, int64_t star
 
 __global__ void silu_mul_kernel(const float* __restrict__ g, const float* __restrict__ u, int64_t n,
                                 float* __restrict__ y) {
+  pdl_trigger();  // a product launched next may begin fetching its weights
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
        i += (int64_t)gridDim.x * blockDim.x) {
     const float gv = g[i];
@@ -190,13 +228,13 @@ int launch_qkv_prepare(const QkvPrepArgs& a, const FreqTable& ft, cudaStream_t s
   DYN_CHECK(a.d % 2 == 0 && a.d <= 256, "head_dim %lld unsupported (even, <= 256)", (long long)a.d);
   dim3 grid((unsigned)a.rows, (unsigned)(a.nh + 2 * a.nkv));
   const int threads = a.d >= 128 ? 64 : 32;
-  if (a.kv_type == E_F32)
+  if (a.kv_type == E_F32) {
     qkv_prepare_kernel<E_F32><<<grid, threads, 0, s>>>(a, ft);
-  else if (a.kv_type == E_F16)
+  } else if (a.kv_type == E_F16) {
     qkv_prepare_kernel<E_F16><<<grid, threads, 0, s>>>(a, ft);
-  else if (a.kv_type == E_BF16)
+  } else if (a.kv_type == E_BF16) {
     qkv_prepare_kernel<E_BF16><<<grid, threads, 0, s>>>(a, ft);
-  else
+  } else
     DYN_CHECK(false, "kv_type %d unsupported", a.kv_type);
   count_launch();
   DYN_CUDA(cudaGetLastError());
@@ -368,6 +406,7 @@ attention_split_kernel(AttnArgs a, float* __restrict__ part, int nsplit) {
 
 __global__ void __launch_bounds__(256)
 attention_merge_kernel(const float* __restrict__ part, int nsplit, float* ctx, int64_t nh, int64_t d) {
+  pdl_trigger();  // a product launched next may begin fetching its weights
   const int64_t h = blockIdx.x, r = blockIdx.y;
   const float* p0 = part + ((r * nh + h) * nsplit) * (d + 2);
   float gm = -3.40282347e38f;
@@ -387,12 +426,13 @@ attention_merge_kernel(const float* __restrict__ part, int nsplit, float* ctx, i
 template <int KV>
 static int run_attention_split(const AttnArgs& a, float* part, int nsplit, cudaStream_t s) {
   const dim3 grid((unsigned)a.nh, (unsigned)a.rows, (unsigned)nsplit);
-  if (a.d == 64)
+  if (a.d == 64) {
     attention_split_kernel<KV, 2><<<grid, ATT_WARPS * 32, 0, s>>>(a, part, nsplit);
-  else if (a.d == 128)
+  } else if (a.d == 128) {
     attention_split_kernel<KV, 4><<<grid, ATT_WARPS * 32, 0, s>>>(a, part, nsplit);
-  else
+  } else {
     attention_split_kernel<KV, 8><<<grid, ATT_WARPS * 32, 0, s>>>(a, part, nsplit);
+  }
   attention_merge_kernel<<<dim3((unsigned)a.nh, (unsigned)a.rows), 256, 0, s>>>(part, nsplit, a.ctx, a.nh, a.d);
   count_launch(2);
   DYN_CUDA(cudaGetLastError());

@@ -110,6 +110,10 @@ struct dyninfer_cuda_session_t {
   float* tp_gather = nullptr;  // [tp_world, batch, lm_rows] gathered slices of a batched step
   bool tp_warm = false;        // the collectives have run once outside a capture
   TpPeer peer;                 // peer-memory exchange (used instead of the all-reduce once attached)
+  // scratch of the single-row products (K-slice partial sums), owned here so that a captured step
+  // has no allocation nodes between its kernels
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
   // statistics
   dyninfer_cuda_allocator_statistics_t stats{};
   uint64_t launches = 0;
@@ -367,8 +371,10 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
       return 1;
     // one row: the column-split GEMVs run at ~3x the fused scalar kernel's bandwidth, which more than
     // pays for the separate activation launch
-    const bool fast_gemv = rows == 1 && gemv_cs_workspace_bytes(L.gate, 1) && gemv_cs_workspace_bytes(L.up, 1);
-    if (L.gate.enc == L.up.enc && rows <= 16 && !fast_gemv) {
+    const bool fast_gemv = (rows == 1 && gemv_cs_workspace_bytes(L.gate, 1) && gemv_cs_workspace_bytes(L.up, 1)) ||
+                           (rows <= 4 && gemv_mma_workspace_bytes(L.gate, E_F32, (int)rows) &&
+                            gemv_mma_workspace_bytes(L.up, E_F32, (int)rows));
+    if (L.gate.enc == L.up.enc && rows <= 4 && !fast_gemv) {
       if (launch_linear_swiglu(L.gate, L.up, s->xn, rows, s->act, st)) return 1;
     } else {
       // many rows (tensor-core GEMM) or mixed encodings: two products, then the activation
@@ -568,9 +574,15 @@ int tp_check_error(Session* s) {
   return 1;
 }
 
-struct CounterScope {  // routes count_launch() to this session for the duration of a call
-  explicit CounterScope(Session* s) { set_launch_counter(&s->launches); }
-  ~CounterScope() { set_launch_counter(nullptr); }
+struct CounterScope {  // routes count_launch() and product scratch to this session for one call
+  explicit CounterScope(Session* s) {
+    set_launch_counter(&s->launches);
+    set_thread_scratch(s->scratch, s->scratch_bytes);
+  }
+  ~CounterScope() {
+    set_launch_counter(nullptr);
+    set_thread_scratch(nullptr, 0);
+  }
 };
 
 }  // namespace
@@ -864,6 +876,22 @@ int dyninfer_cuda_session_create_with_file_params(
            L.ffn_norm.bytes + L.q_norm.bytes + L.k_norm.bytes;
   }
   s->decode_weight_bytes = dwb;
+  {
+    size_t need = 0;
+    auto grow = [&](const WRef& w) {
+      for (int m = 1; m <= 8; m++) need = std::max(need, gemv_mma_workspace_bytes(w, E_F32, m));
+    };
+    grow(s->lm_head);
+    for (const LayerW& L : s->layers) {
+      const WRef* ws[7] = {&L.q, &L.k, &L.v, &L.o, &L.gate, &L.up, &L.down};
+      for (const WRef* wp : ws) grow(*wp);
+    }
+    if (need) {
+      if (dev_alloc(s, &s->scratch, need)) return fail();
+      s->scratch_bytes = need;
+      set_thread_scratch(s->scratch, s->scratch_bytes);  // `scope` was entered before the region existed
+    }
+  }
 
   if (cfg.persistent &&
       mega_plan(cfg.hidden, cfg.inter, (int)qd, cfg.head_dim, 0, &s->mega_nslot, &s->mega_xs,
@@ -936,7 +964,7 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
                  s->hist_dev, s->hist_count_dev, s->argmax_scratch, s->mega_layers, s->io_dev,
                  s->bar_dev, s->attn_part, s->amax_val, s->amax_idx, s->prof_dev, s->prog_dev,
                  s->counts_dev, s->batch_logits, s->batch_tokens_dev, s->tp_part, s->tp_logits,
-                 s->tp_gather};
+                 s->tp_gather, s->scratch};
   for (void* p : dev)
     if (p) cudaFree(p);
   if (s->logits_host) cudaFreeHost(s->logits_host);

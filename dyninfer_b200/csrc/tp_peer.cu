@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1) tp_exchange_kernel(const PeerAr
   __shared__ float red[32];
   __shared__ float s_inv;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_trigger();  // a product launched next may begin fetching its weights
   const unsigned e = a.epochs[blockIdx.x] + 1;
   // arrival: this rank's partial rows were written by the kernel before this one
   if (tid < a.world) {

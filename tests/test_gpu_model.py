@@ -129,7 +129,8 @@ def test_chunked_prefill_padding_and_limits(native_lib, oracle, tmp_path):
     model = ModelLoader().load(path, max_kv=300, chunk_size=8)       # 21 tokens = chunks 8 + 8 + 5 (right padded)
     with model.create_session(SessionConfig(max_sequence_length=300)) as s:
         lg = s.prefill(prompt).values
-        assert np.abs(lg - want[0]).max() <= 1e-3
+        # 8-row chunks of Q4_0 products run on the f16 tensor-core GEMM: the logits tolerance applies
+        assert np.abs(lg - want[0]).max() <= 1e-2 and helpers.cosine(lg, want[0]) >= 0.9999
         m = s.kv_cache_metrics()
         assert m.page_count == 2 and m.paged and m.chunk_size == 8 and m.filled_tokens == 21
         assert m.allocated_bytes == 2 * 2 * 2 * 512 * 64 * 4        # K+V x layers x kv heads x cap x d x 4
@@ -277,3 +278,30 @@ def test_long_prompt_prefill_tensor_core_path(native_lib, oracle, tmp_path, kv):
         for i in range(steps):
             lg = s.decode(want_toks[i]).values
             assert np.abs(lg - want_logits[i + 1]).max() <= 1e-2 and helpers.cosine(lg, want_logits[i + 1]) >= 0.9999
+
+
+def test_logit_drift_traces_cuda_vs_oracle(native_lib, oracle, tmp_path):
+    """The drift harness end to end: the cuda target and the oracle write logit traces of the same
+    forced trajectory (prompt of 12 ids, 10 forced decode inputs) and the per-row metric set stays
+    inside the logits tolerance (max-abs 1e-2, cosine 0.9999)."""
+    from dyninfer_b200 import drift
+    path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), synth.TINY, seed=23,
+                                  encodings={"attn_v": "gguf.q4_1", "ffn_down": "gguf.q8_0"})
+    cat = ck.open_catalog(path)
+    rng = np.random.default_rng(9)
+    prompt = rng.integers(0, synth.TINY["vocab"], size=12).tolist()
+    want_logits, want_toks, _ = oracle_run(oracle, cat, prompt, 10)
+    forced = want_toks[:10]                       # the oracle's own greedy trajectory
+    sha = drift.sha256_of(path)
+    with drift.TraceWriter(str(tmp_path / "ref"), "oracle-cpu", sha, synth.TINY["vocab"], prompt, forced) as w:
+        for row in want_logits:
+            w.write_row(row)
+        ref_dir = w.finish()
+    model = ModelLoader().load(path, max_kv=256, kv_dtype="f32", chunk_size=16)
+    with model.create_session(SessionConfig(max_sequence_length=256)) as s:
+        dyn_dir = drift.record(s, str(tmp_path / "dyn"), "dyninfer-cuda-sm_100a", sha, prompt, forced)
+    rep = drift.compare_traces(ref_dir, dyn_dir, top_k=5)
+    sm = rep["summary"]
+    assert sm["row_count"] == 11 and sm["max_absolute_error"] <= 1e-2 and sm["min_cosine_similarity"] >= 0.9999
+    assert sm["max_softmax_kl"] < 1e-4 and sm["min_top_k_overlap_fraction"] >= 0.8
+    assert rep["reference_engine"] == "oracle-cpu" and rep["dyninfer_engine"] == "dyninfer-cuda-sm_100a"

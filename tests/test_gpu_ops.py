@@ -87,7 +87,7 @@ def test_linear_vs_oracle(native_lib, oracle, enc, m):
     got_bf16 = ops.linear(dw, xb.cuda()).cpu().numpy()
     got_f32 = ops.linear(dw, xb.float().cuda()).cpu().numpy()
     assert helpers.rel_err(got_bf16, want) < 1e-3 and helpers.rel_err(got_f32, want) < 1e-3
-    if m <= 16:                                            # exact weights, f32 sums: only the order differs
+    if m <= 4:                                             # exact weights, f32 sums: only the order differs
         assert helpers.rel_err(got_f32, want) < 2e-5      # (more rows use the f16 tensor-core GEMM)
 
 

@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <array>
 #include <map>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -30,6 +31,10 @@ struct NormW {
 struct LayerW {
   NormW attn_norm, ffn_norm, q_norm, k_norm;
   WRef q, k, v, o, gate, up, down;
+  // rows of consecutive matrices seen as one (data == nullptr: not laid back to back)
+  WRef qkv;     // [q; k] or [q; k; v]
+  int qkv_parts = 0;
+  WRef gate_up; // [gate; up]
 };
 
 struct ModelCfg {
@@ -72,6 +77,7 @@ struct dyninfer_cuda_session_t {
   int64_t max_rows = 0;
   float *hidden = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ctx = nullptr,
         *act = nullptr, *up = nullptr, *logits = nullptr;
+  float *qkv1 = nullptr, *gu1 = nullptr;  // one row of [q | k | v] and of [gate | up] for the fused products
   int64_t *tokens_dev = nullptr, *row_pos_dev = nullptr, *row_seq_dev = nullptr,
           *out_token_dev = nullptr, *hist_dev = nullptr, *hist_count_dev = nullptr;
   size_t hist_cap = 0;
@@ -341,11 +347,19 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
     if (!normed &&
         launch_rms_norm(s->hidden, L.attn_norm.ptr, L.attn_norm.type, rows, H, c.eps, s->xn, st))
       return 1;
-    if (launch_linear(L.q, s->xn, E_F32, rows, s->q, nullptr, st)) return 1;
-    if (launch_linear(L.k, s->xn, E_F32, rows, s->k, nullptr, st)) return 1;
-    if (launch_linear(L.v, s->xn, E_F32, rows, s->v, nullptr, st)) return 1;
+    // one row: matrices laid back to back in the arena are one product into [q | k | v]
+    float *qp = s->q, *kp = s->k, *vp = s->v;
+    if (rows == 1 && L.qkv_parts >= 2) {
+      qp = s->qkv1, kp = qp + qd, vp = kp + kvd;
+      if (launch_linear(L.qkv, s->xn, E_F32, 1, qp, nullptr, st)) return 1;
+      if (L.qkv_parts == 2 && launch_linear(L.v, s->xn, E_F32, 1, vp, nullptr, st)) return 1;
+    } else {
+      if (launch_linear(L.q, s->xn, E_F32, rows, qp, nullptr, st)) return 1;
+      if (launch_linear(L.k, s->xn, E_F32, rows, kp, nullptr, st)) return 1;
+      if (launch_linear(L.v, s->xn, E_F32, rows, vp, nullptr, st)) return 1;
+    }
     QkvPrepArgs pa{};
-    pa.q = s->q, pa.k = s->k, pa.v = s->v;
+    pa.q = qp, pa.k = kp, pa.v = vp;
     pa.kcache = s->kcache + (size_t)l * layer_stride;
     pa.vcache = s->vcache + (size_t)l * layer_stride;
     pa.q_norm_w = L.q_norm.ptr, pa.k_norm_w = L.k_norm.ptr, pa.norm_w_type = L.q_norm.type;
@@ -355,7 +369,7 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
     pa.eps = c.eps;
     if (launch_qkv_prepare(pa, s->freq, st)) return 1;
     AttnArgs aa{};
-    aa.q = s->q, aa.kcache = pa.kcache, aa.vcache = pa.vcache;
+    aa.q = qp, aa.kcache = pa.kcache, aa.vcache = pa.vcache;
     aa.row_pos = s->row_pos_dev, aa.row_seq = s->row_seq_dev, aa.base_pos = 0;
     aa.ctx = s->ctx;
     aa.rows = rows, aa.nh = c.heads, aa.nkv = c.kv_heads, aa.d = c.head_dim, aa.cap = cap;
@@ -374,7 +388,11 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
     const bool fast_gemv = (rows == 1 && gemv_cs_workspace_bytes(L.gate, 1) && gemv_cs_workspace_bytes(L.up, 1)) ||
                            (rows <= 4 && gemv_mma_workspace_bytes(L.gate, E_F32, (int)rows) &&
                             gemv_mma_workspace_bytes(L.up, E_F32, (int)rows));
-    if (L.gate.enc == L.up.enc && rows <= 4 && !fast_gemv) {
+    if (rows == 1 && L.gate_up.data && gemv_cs_workspace_bytes(L.gate_up, 1)) {
+      // [gate; up] as one product, then the activation
+      if (launch_linear(L.gate_up, s->xn, E_F32, 1, s->gu1, nullptr, st)) return 1;
+      if (launch_silu_mul(s->gu1, s->gu1 + c.inter, c.inter, s->act, st)) return 1;
+    } else if (L.gate.enc == L.up.enc && rows <= 4 && !fast_gemv) {
       if (launch_linear_swiglu(L.gate, L.up, s->xn, rows, s->act, st)) return 1;
     } else {
       // many rows (tensor-core GEMM) or mixed encodings: two products, then the activation
@@ -779,6 +797,50 @@ int dyninfer_cuda_session_create_with_file_params(
     close_all();
     return 1;
   }
+  // Placement in the arena. The q, k, v matrices of a layer (and gate, up) that share encoding and
+  // width are laid back to back: their rows then form ONE matrix [q; k; v] whose single-row
+  // product is one launch instead of three (every range is still uploaded unchanged).
+  {
+    uint64_t cursor = 0;
+    std::set<const Upload*> placed;
+    auto plain_data = [&](const std::string& name) -> Upload* {
+      auto it = pd.find(name);
+      if (it == pd.end() || it->second.enc == E_MLX_U4 || it->second.shape.size() != 2) return nullptr;
+      if (it->second.comps.size() != 1 || !it->second.comps.count("data")) return nullptr;
+      return &it->second.comps["data"];
+    };
+    auto same_kind = [&](const std::string& a, const std::string& b) {
+      const ParamDesc &pa = pd[a], &pb = pd[b];
+      return pa.enc == pb.enc && pa.shape[1] == pb.shape[1];
+    };
+    auto place_run = [&](const std::vector<std::string>& names) {
+      // the longest prefix of `names` that can be fused, at least two matrices
+      std::vector<Upload*> run;
+      for (const std::string& n : names) {
+        Upload* u = plain_data(n);
+        if (!u || u->length % 16 || (!run.empty() && !same_kind(names[0], n))) break;
+        run.push_back(u);
+      }
+      if (run.size() < 2) return;
+      for (size_t i = 0; i < run.size(); i++) {
+        run[i]->arena_off = cursor;
+        cursor += i + 1 < run.size() ? run[i]->length : (run[i]->length + 64 + 255) / 256 * 256;
+        placed.insert(run[i]);
+      }
+    };
+    for (int l = 0; l < cfg.layers; l++) {
+      const std::string b = "blk." + std::to_string(l) + ".";
+      place_run({b + "attn_q.weight", b + "attn_k.weight", b + "attn_v.weight"});
+      place_run({b + "ffn_gate.weight", b + "ffn_up.weight"});
+    }
+    for (auto& p : pd)
+      for (auto& c : p.second.comps) {
+        if (placed.count(&c.second)) continue;
+        c.second.arena_off = cursor;
+        cursor += (c.second.length + 64 + 255) / 256 * 256;  // 64 B of readable slack per range
+      }
+    arena_bytes = cursor;
+  }
 
   {
     int n = 0;
@@ -867,6 +929,22 @@ int dyninfer_cuda_session_create_with_file_params(
         bind_linear(pd, s->arena, p + "ffn_up.weight", I, H, &L.up) ||
         bind_linear(pd, s->arena, p + "ffn_down.weight", H, I, &L.down))
       return fail();
+    {
+      auto follows = [](const WRef& a, const WRef& b) {
+        return a.enc == b.enc && a.enc != E_MLX_U4 && a.cols == b.cols &&
+               reinterpret_cast<const uint8_t*>(b.data) == reinterpret_cast<const uint8_t*>(a.data) + a.total_bytes();
+      };
+      if (follows(L.q, L.k)) {
+        L.qkv = L.q;
+        L.qkv.rows = L.q.rows + L.k.rows;
+        L.qkv_parts = 2;
+        if (follows(L.k, L.v)) L.qkv.rows += L.v.rows, L.qkv_parts = 3;
+      }
+      if (follows(L.gate, L.up)) {
+        L.gate_up = L.gate;
+        L.gate_up.rows = L.gate.rows + L.up.rows;
+      }
+    }
     if (cfg.qk_norm && L.q_norm.type != L.k_norm.type) {
       set_error("q_norm and k_norm weights of layer %d differ in type", l);
       return fail();
@@ -964,7 +1042,7 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
                  s->hist_dev, s->hist_count_dev, s->argmax_scratch, s->mega_layers, s->io_dev,
                  s->bar_dev, s->attn_part, s->amax_val, s->amax_idx, s->prof_dev, s->prog_dev,
                  s->counts_dev, s->batch_logits, s->batch_tokens_dev, s->tp_part, s->tp_logits,
-                 s->tp_gather, s->scratch};
+                 s->tp_gather, s->scratch, s->qkv1, s->gu1};
   for (void* p : dev)
     if (p) cudaFree(p);
   if (s->logits_host) cudaFreeHost(s->logits_host);
@@ -1015,6 +1093,8 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
         dev_alloc(s, (void**)&s->ctx, (size_t)rows * qd * 4) ||
         dev_alloc(s, (void**)&s->act, (size_t)rows * c.inter * 4) ||
         dev_alloc(s, (void**)&s->up, (size_t)rows * c.inter * 4) ||
+        dev_alloc(s, (void**)&s->qkv1, (size_t)(qd + 2 * kvd) * 4) ||
+        dev_alloc(s, (void**)&s->gu1, (size_t)2 * c.inter * 4) ||
         (c.tp_world > 1 && dev_alloc(s, (void**)&s->tp_part, (size_t)rows * c.hidden * 4)) ||
         dev_alloc(s, (void**)&s->tokens_dev, (size_t)rows * 8) ||
         dev_alloc(s, (void**)&s->row_pos_dev, (size_t)rows * 8) ||

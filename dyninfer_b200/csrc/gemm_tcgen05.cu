@@ -122,6 +122,10 @@ struct TgArgs {
   float* y;          // [M, N]
   const float* residual;
   int* error;
+  // K split over gridDim.z CTAs per tile (few weight-row tiles would leave most SMs idle): CTA z takes
+  // chunks [z * nk_split, ...) and writes its scaled sums to partial[z][M][N]; a second pass adds them
+  int nk_split;      // chunks per split (all of them when gridDim.z == 1)
+  float* partial;
 };
 
 // Items of one row in a K chunk: every item is one decoder part; its groups that fall inside the
@@ -155,7 +159,8 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
   const int bn = a.bn;
   const int64_t N = a.w.rows, K = a.w.cols;
   const int64_t n0 = (int64_t)blockIdx.x * TG_BM, m0 = (int64_t)blockIdx.y * bn;
-  const int nk = (int)(K / TG_BK);
+  const int kbase = (int)blockIdx.z * a.nk_split;  // first chunk of this CTA's share of K
+  const int nk = min(a.nk_split, (int)(K / TG_BK) - kbase);
   const uint32_t stage_bytes = TG_A_BYTES + (uint32_t)bn * 128;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tg_smem) + 1023) & ~uintptr_t(1023));
 
@@ -208,7 +213,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
       auto fetch = [&](int kc, uint32_t (&wa)[NJ], uint32_t (&wb)[NJ]) {
 #pragma unroll
         for (int j = 0; j < NJ; j++) {
-          const uint32_t* p = roww[j] + (int64_t)kc * 9;
+          const uint32_t* p = roww[j] + (int64_t)(kbase + kc) * 9;
           wa[j] = p[l8];
           wb[j] = l8 == 0 ? p[8] : 0u;
         }
@@ -293,10 +298,10 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
       uint32_t qw[2][NJ];
       float ax[2][NJ];  // even lanes hold the group's scale, odd lanes its bias (lane pairs share a group)
       auto fetch = [&](int kc, uint32_t (&q)[NJ], float (&x_)[NJ]) {
-        const int64_t gi = ((int64_t)kc * TG_BK + 8 * j) / a.w.group;
+        const int64_t gi = ((int64_t)(kbase + kc) * TG_BK + 8 * j) / a.w.group;
 #pragma unroll
         for (int jj = 0; jj < NJ; jj++) {
-          q[jj] = wordp[jj][(int64_t)kc * 8];
+          q[jj] = wordp[jj][(int64_t)(kbase + kc) * 8];
           x_[jj] = aux_load((j & 1) ? bip[jj] : scp[jj], a.w.aux, gi);
         }
       };
@@ -352,7 +357,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
           if (!s_abort) s_abort = 1;
           break;
         }
-        const int64_t k0 = (int64_t)kc * TG_BK;
+        const int64_t k0 = (int64_t)(kbase + kc) * TG_BK;
         int64_t blk;
         int part;
         CI::locate(k0, it, &blk, &part);
@@ -391,7 +396,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
           break;
         }
         mbar_expect_tx(full_bar + slot, (unsigned)bn * 128u);
-        tma_load_2d(smem + (size_t)slot * stage_bytes + TG_A_BYTES, &xmap, kc * TG_BK, (int)m0, full_bar + slot);
+        tma_load_2d(smem + (size_t)slot * stage_bytes + TG_A_BYTES, &xmap, (kbase + kc) * TG_BK, (int)m0, full_bar + slot);
       }
     }
   } else {
@@ -437,8 +442,12 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
           const int64_t m = m0 + j0 + j;
           if (m < a.M && n < N) {
             float o = __uint_as_float(v[j]) * __ldg(a.inv_s + m);
-            if (a.residual) o += a.residual[m * N + n];
-            a.y[m * N + n] = o;
+            if (gridDim.z > 1) {
+              a.partial[((int64_t)blockIdx.z * a.M + m) * N + n] = o;
+            } else {
+              if (a.residual) o += a.residual[m * N + n];
+              a.y[m * N + n] = o;
+            }
           }
         }
       }
@@ -494,6 +503,17 @@ int tg_make_xmap(__half* xh, int64_t rows, int64_t K, int bn, CUtensorMap* map) 
   return 0;
 }
 
+// y = sum over the K splits (fixed order) + residual
+__global__ void __launch_bounds__(256)
+tg_split_reduce_kernel(const float* __restrict__ partial, int splits, int64_t count, float* y, const float* residual) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= count) return;
+  float v = 0.f;
+  for (int z = 0; z < splits; z++) v += partial[(int64_t)z * count + i];
+  if (residual) v += residual[i];
+  y[i] = v;
+}
+
 template <int ENC>
 int tg_launch(const TgArgs& a, const CUtensorMap& xmap, dim3 grid, size_t smem, cudaStream_t s) {
   static bool attr_done = false;
@@ -543,7 +563,17 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
     cudaFreeAsync(ws, s);
     return 1;
   }
-  const dim3 grid((unsigned)((w.rows + TG_BM - 1) / TG_BM), (unsigned)mtiles);
+  // few tiles: split K as well, at least 4 chunks (256 elements) per CTA, at most 8 ways
+  const int nk_all = (int)(K / TG_BK);
+  int splits = 1;
+  while (splits < 8 && ntiles * mtiles * (splits * 2) <= 148 && nk_all / (splits * 2) >= 4) splits *= 2;
+  const int nk_split = (nk_all + splits - 1) / splits;
+  splits = (nk_all + nk_split - 1) / nk_split;
+  float* partial = nullptr;
+  if (splits > 1)
+    DYN_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&partial), (size_t)splits * M * w.rows * 4, s));
+  a.nk_split = nk_split, a.partial = partial;
+  const dim3 grid((unsigned)((w.rows + TG_BM - 1) / TG_BM), (unsigned)mtiles, (unsigned)splits);
   const size_t stage_b = TG_A_BYTES + (size_t)bn * 128;
   const int nslot = 2 * TG_GROUPS * stage_b + 1024 <= 200 * 1024 ? 2 * TG_GROUPS : TG_GROUPS;
   a.nslot = nslot;
@@ -561,6 +591,14 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
     default: break;
   }
   count_launch(2);
+  if (splits > 1) {
+    if (!rc) {
+      const int64_t count = M * w.rows;
+      tg_split_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, s>>>(partial, splits, count, y, residual);
+      count_launch();
+    }
+    cudaFreeAsync(partial, s);
+  }
   cudaError_t e = cudaGetLastError();
   cudaError_t e2 = cudaFreeAsync(ws, s);
   if (rc) return rc;

@@ -69,7 +69,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -106,8 +106,9 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode_mega_kernel launch on this workload
-# (ncu capture summarised in profiles/decode_mega_kernel_qwen3_0_6b_q4_0.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_mega_kernel launch on this workload,
+# recorded from an ncu capture of this kernel (a profiler cannot run inside the timed region); the
+# bench line labels it as recorded, not measured in this run
 MEGA_DRAM_TRAFFIC = 384_337_664 + 10_346_240
 
 
@@ -134,21 +135,63 @@ def prompt_ids():
 
 # ------------------------------------------------------------------ CPU restatement
 
-def cpu_decode_rate(path, steps, prompt_tokens=4, warm=1):
-    """Decode tok/s of the CPU restatement (all host threads) on a bounded sample."""
+def use_all_host_threads():
+    """The CPU restatement runs on every core this process may use, whatever OMP_NUM_THREADS the
+    launcher exported (torch.distributed.run sets it to 1). Must run before the library loads."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(max(1, n))
+    return n
+
+
+def cpu_decode(path, steps, warm=1, kv_round=2):
+    """The CPU restatement (all host threads) on the bench workload: the same 16-token prompt, then
+    greedy steps. Returns (decode tok/s over `steps` timed steps, threads, seconds, tokens, margins):
+    tokens[0] follows the prompt, tokens[1 + i] follows decode step i (warm-up steps included);
+    margins[i] is the top-2 logit gap behind tokens[i]."""
+    cores = use_all_host_threads()
     from oracle import oracle as orc
     from dyninfer_b200 import checkpoint as ck
     orc.build()
+    orc.set_num_threads(cores)                     # the OpenMP runtime may have loaded before the env change
     cat = ck.open_catalog(path)
-    m = orc.Model(cat.config, orc.weights_from_catalog(cat), kv_cap=prompt_tokens + steps + warm + 2, fast=True)
-    _, tok = m.forward(prompt_ids()[:prompt_tokens])
+    m = orc.Model(cat.config, orc.weights_from_catalog(cat), kv_cap=PROMPT_LEN + steps + warm + 2,
+                  kv_round=kv_round, fast=True)
+
+    def margin(lg):
+        top2 = np.partition(lg, -2)[-2:]
+        return float(top2[1] - top2[0])
+
+    lg, tok = m.forward(prompt_ids())
+    toks, margins = [tok], [margin(lg)]
     for _ in range(max(1, warm)):                  # untimed steps
-        _, tok = m.forward([tok])
+        lg, tok = m.forward([tok])
+        toks.append(tok)
+        margins.append(margin(lg))
     t0 = time.perf_counter()
     for _ in range(steps):
-        _, tok = m.forward([tok])
+        lg, tok = m.forward([tok])
+        toks.append(tok)
+        margins.append(margin(lg))
     dt = time.perf_counter() - t0
-    return steps / dt, orc.num_threads(), dt
+    return steps / dt, orc.num_threads(), dt, toks, margins
+
+
+def parity_against(cpu_toks, cpu_margins, gpu_toks, tie=1e-3):
+    """Greedy tokens of the device loop against the CPU restatement's: identical except where the
+    restatement's own top-2 margin is a near-tie (< 1e-3), after which the paths legitimately part."""
+    n = min(len(cpu_toks), len(gpu_toks))
+    prefix = 0
+    while prefix < n and int(cpu_toks[prefix]) == int(gpu_toks[prefix]):
+        prefix += 1
+    out = {"tokens_compared": n, "common_prefix": prefix, "equal": prefix == n, "near_ties": 0,
+           "reference": "CPU restatement, bf16-rounded KV like the device cache"}
+    if prefix < n:
+        out["margin_at_divergence"] = cpu_margins[prefix]
+        out["near_ties"] = int(cpu_margins[prefix] < tie)
+        out["ok"] = bool(cpu_margins[prefix] < tie)
+    else:
+        out["ok"] = True
+    return out
 
 
 def run_reference_arm(args, rank):
@@ -157,8 +200,8 @@ def run_reference_arm(args, rank):
     path = ensure_checkpoint()
     steps = max(1, min(args.steps, 48))
     warm = max(1, min(args.warmup, 3))
-    tps, cores, dt = cpu_decode_rate(path, steps, warm=warm)
-    sample = (f"{steps} greedy decode steps of the full 28-layer model after a 4-token prompt, "
+    tps, cores, dt, _, _ = cpu_decode(path, steps, warm=warm)
+    sample = (f"{steps} greedy decode steps of the full 28-layer model after the {PROMPT_LEN}-token prompt, "
               f"CPU restatement of the reference's direct path (the reference's own IREE llvm-cpu "
               f"build cannot run here), {cores} OpenMP threads")
     print(json.dumps({
@@ -321,7 +364,7 @@ def main():
                          "achieved": weight_bytes / (ms / K * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
                          "frac": weight_bytes / (ms / K * 1e-3) / 1e9 / hbm_peak, "peak_source": peak_kind,
                          "bytes_per_launch": weight_bytes, "ms_per_launch": ms / K,
-                         "traffic": MEGA_DRAM_TRAFFIC},
+                         "traffic": MEGA_DRAM_TRAFFIC, "traffic_source": "recorded ncu capture of this kernel"},
             # the largest single product of the step as its own launch (fused dequant-GEMV, M=1)
             "roofline_lm_head_gemv": {"bound": "hbm", "kernel": f"gemv_cs_q6k_kernel ({lm_enc}) 151936x1024, M=1",
                                       "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
@@ -331,12 +374,15 @@ def main():
         out["prefill"] = {"tokens": 2048, "chunk": model.chunk_size, "tokens_per_s": time_prefill(model),
                           "note": "tcgen05 dequant GEMM + tensor-core flash attention, bf16 KV"}
         if not args.no_cpu_baseline:
-            steps = 24
-            tps, cores, dt = cpu_decode_rate(path, steps)
+            steps, warm = 28, 4
+            tps, cores, dt, cpu_toks, cpu_margins = cpu_decode(path, steps, warm=warm,
+                                                               kv_round={"bf16": 2, "f16": 1, "f32": 0}[args.kv_dtype])
             out["cpu_baseline"] = {
                 "value": tps, "unit": "tok/s", "cores": cores, "kind": "port",
-                "sample": f"{steps} decode steps of the same model after a 4-token prompt ({dt:.1f} s), "
-                          "CPU restatement of the reference's direct path"}
+                "sample": f"{steps} decode steps of the same model after the same {PROMPT_LEN}-token prompt "
+                          f"({dt:.1f} s), CPU restatement of the reference's direct path"}
+            # the same run checks the timed loop: its first tokens against the restatement's
+            out["parity"] = parity_against(cpu_toks, cpu_margins, [first] + [int(t) for t in toks_w] + [int(t) for t in toks])
         print(json.dumps(out), flush=True)
     session.close()
     replicas.shutdown()

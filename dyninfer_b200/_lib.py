@@ -47,6 +47,7 @@ PROTOTYPES = {
     "dyninfer_cuda_abi_version": (C.c_int, []),
     "dyninfer_cuda_last_error": (C.c_char_p, []),
     "dyninfer_cuda_device_count": (C.c_int, [C.POINTER(C.c_int)]),
+    "dyninfer_cuda_check_device_error": (C.c_int, []),
     "dyninfer_cuda_row_bytes": (C.c_uint64, [C.c_int, _I64]),
     "dyninfer_cuda_dequant": (C.c_int, [C.POINTER(Weight), _P, _P]),
     "dyninfer_cuda_embedding_gather": (C.c_int, [C.POINTER(Weight), _P, _I64, _P, _P]),
@@ -81,6 +82,7 @@ PROTOTYPES = {
     "dyninfer_cuda_tp_peer_handle_bytes": (C.c_size_t, []),
     "dyninfer_cuda_session_tp_peer_handle": (C.c_int, [_P, C.c_char_p, C.c_size_t]),
     "dyninfer_cuda_session_tp_peer_attach": (C.c_int, [_P, C.c_char_p, C.c_size_t]),
+    "dyninfer_cuda_tp_exchange_wait_probe": (C.c_int, [C.c_int, _I64, _I64]),
     "dyninfer_cuda_session_reset_paged_kv": (C.c_int, [_P]),
     "dyninfer_cuda_session_kv_page_count": (C.c_size_t, [_P]),
     "dyninfer_cuda_session_kv_allocated_bytes": (C.c_size_t, [_P]),
@@ -90,6 +92,7 @@ PROTOTYPES = {
     "dyninfer_cuda_session_decode_loop": (C.c_int, [_P, _I64, _I64, C.c_size_t, C.POINTER(_I64),
                                                     C.POINTER(C.c_float)]),
     "dyninfer_cuda_session_launch_count": (C.c_uint64, [_P]),
+    "dyninfer_cuda_session_uses_persistent_kernel": (C.c_int, [_P]),
     "dyninfer_cuda_session_decode_phase_profile": (C.c_int, [_P, C.POINTER(C.c_double), C.c_size_t]),
 }
 

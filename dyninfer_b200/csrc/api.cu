@@ -5,10 +5,11 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <map>
+#include <mutex>
 #include <string>
 
 #include <stdlib.h>
-
 
 #include "common.cuh"
 
@@ -59,6 +60,86 @@ bool pdl_enabled() {
     return !(e && e[0] == '0');
   }();
   return on;
+}
+
+// ---- per-device facts: SM count, opted-in shared memory per kernel, sticky error word ----------
+namespace {
+constexpr int MAX_DEVICES = 64;
+struct DeviceSlot {
+  int sms = 0;
+  int* err_host = nullptr;  // pinned, mapped: written by kernels whose bounded wait gave up
+  int* err_dev = nullptr;
+  std::map<const void*, int> smem_attr;  // kernel -> largest dynamic shared memory opted into
+};
+std::mutex g_dev_mu;
+DeviceSlot g_dev[MAX_DEVICES];
+DeviceSlot* current_slot() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+  return g_dev + dev;
+}
+}  // namespace
+
+int sm_count() {
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  DeviceSlot* d = current_slot();
+  if (!d) return 0;
+  if (!d->sms) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      return 0;
+    d->sms = n;
+  }
+  return d->sms;
+}
+
+int ensure_dynamic_smem(const void* kernel, int bytes) {
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  DeviceSlot* d = current_slot();
+  DYN_CHECK(d != nullptr, "no current CUDA device");
+  auto it = d->smem_attr.find(kernel);
+  if (it != d->smem_attr.end() && it->second >= bytes) return 0;
+  DYN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  d->smem_attr[kernel] = bytes;
+  return 0;
+}
+
+int* device_error_word() {
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  DeviceSlot* d = current_slot();
+  if (!d) {
+    set_error("no current CUDA device");
+    return nullptr;
+  }
+  if (!d->err_dev) {
+    int* h = nullptr;
+    int* p = nullptr;
+    cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&h), 64, cudaHostAllocMapped | cudaHostAllocPortable);
+    if (e == cudaSuccess) e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&p), h, 0);
+    if (e != cudaSuccess) {
+      cuda_fail(e, "allocating the device error word", __FILE__, __LINE__);
+      return nullptr;
+    }
+    *h = 0;
+    d->err_host = h, d->err_dev = p;
+  }
+  return d->err_dev;
+}
+
+int check_device_error(const char* what) {
+  int code = 0;
+  {
+    std::lock_guard<std::mutex> lk(g_dev_mu);
+    DeviceSlot* d = current_slot();
+    if (!d || !d->err_host) return 0;
+    code = *reinterpret_cast<volatile int*>(d->err_host);
+    if (code) *reinterpret_cast<volatile int*>(d->err_host) = 0;
+  }
+  if (!code) return 0;
+  set_error("%s: a bounded wait inside a kernel expired (code %d: 1 single-row product weight ring, "
+            "2 tensor-core GEMM pipeline); the results of the call are invalid", what, code);
+  return 1;
 }
 
 void count_launch(int n) { *g_counter += (uint64_t)n; }
@@ -223,6 +304,11 @@ int dyninfer_cuda_argmax(const float* v_dev, int64_t n, int64_t* out_index_dev, 
   DYN_CHECK(aligned(scratch_dev, 16), "argmax: scratch must be 16-byte aligned");
   if (require_device()) return 1;
   return launch_argmax(v_dev, n, out_index_dev, scratch_dev, (cudaStream_t)stream);
+}
+
+int dyninfer_cuda_check_device_error(void) {
+  if (require_device()) return 1;
+  return check_device_error("device error word");
 }
 
 void dyninfer_cuda_free(void*) {}

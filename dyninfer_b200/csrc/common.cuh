@@ -55,6 +55,27 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Facts about the current device, cached per device ordinal (a process may hold sessions on
+// several devices).
+int sm_count();  // multiprocessors of the current device; 0 when the query fails
+// Opts `kernel` into `bytes` of dynamic shared memory on the current device (once per device
+// and kernel; the attribute belongs to the device's context).
+int ensure_dynamic_smem(const void* kernel, int bytes);
+// The current device's sticky error word: pinned host memory mapped into the device. A kernel
+// whose bounded wait gives up stores a non-zero code there and never clears it; the host reads
+// and clears it with check_device_error() after the stream has drained. nullptr on failure
+// (message set). The first call on a device allocates; sessions and the operator entry points
+// make it before any launch or stream capture.
+int* device_error_word();
+int check_device_error(const char* what);  // 1 (message set, word cleared) when a wait expired
+enum { DEV_ERR_GEMV_RING = 1, DEV_ERR_GEMM_PIPE = 2 };
+__device__ __forceinline__ void report_wait_expired(int* word, int code) {
+  if (word) {
+    *reinterpret_cast<volatile int*>(word) = code;
+    __threadfence_system();
+  }
+}
+
 // Counts kernels launched by this library (per thread-attached counter).
 void count_launch(int n = 1);
 uint64_t* launch_counter_slot();  // where count_launch accumulates (thread-local pointer)
@@ -251,6 +272,7 @@ struct TpPeer {
   int* error_host = nullptr;         // pinned, mapped: which wait ran out (0 = none)
   int* error_dev = nullptr;
   bool attached = false;
+  long long spin_limit = 0;          // polls before a wait gives up (0: the default, about ten seconds)
 };
 size_t tp_peer_region_bytes(int64_t max_rows, int hidden);
 size_t tp_peer_flags_offset(int64_t max_rows, int hidden);

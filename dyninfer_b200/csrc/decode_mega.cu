@@ -1,21 +1,37 @@
 // Persistent single-token decode kernel: one launch per generated token.
 //
-// One CTA per SM, launched cooperatively so that all CTAs are co-resident. Each CTA owns a
-// fixed, balanced slice of the rows of every weight matrix, cut into tiles of 16 rows (x
-// K-slices). A producer warp streams the tiles — the verbatim checkpoint bytes, one 1-D bulk
-// async copy per row segment (cp.async.bulk + mbarrier transaction counts) — from HBM into a
-// shared-memory ring, running as far ahead of the math as the ring allows: weight traffic never
-// waits for the activation dependency chain. Rows land PITCH bytes apart with PITCH/4 = 4
-// (mod 8), so the tensor-core fragment loads are bank-conflict free. Sixteen consumer warps
-// split each tile's K range, run the tile steps of gemv_core.cuh against the activation vector
-// staged in shared memory in fragment order, and reduce their partial sums in a fixed order.
-// CTAs meet at a grid barrier between dependent phases:
+// One CTA per SM, launched cooperatively so that all CTAs are co-resident. Each CTA owns a fixed,
+// balanced slice of the rows of every weight matrix, cut into tiles of 16 rows (x K-slices). A
+// producer warp streams the tiles -- the verbatim checkpoint bytes, one 1-D bulk async copy per
+// row segment (cp.async.bulk + mbarrier transaction counts) -- from HBM into a shared-memory
+// ring, running as far ahead of the math as the ring allows: weight traffic never waits for the
+// activation dependency chain. Rows land PITCH bytes apart with PITCH/4 = 4 (mod 8), so the
+// tensor-core fragment loads are bank-conflict free. Sixteen consumer warps split each tile's K
+// range and run the tile steps of gemv_core.cuh against the activation vector staged in shared
+// memory in fragment order.
 //
-//   embed | per layer: norm+QKV | qk-norm+RoPE+KV-write+attention | o_proj+res |
-//   norm+gate/up+SwiGLU | down+res | final: norm+lm_head+argmax partials | argmax
+// The step is a chain of dependent phases, and what bounds it is the hand-off between them, not
+// bandwidth. Three rules keep a hand-off near one L2 round trip:
 //
-// Every wait (mbarrier, grid barrier) is bounded: when it gives up it raises the error word,
-// the remaining phases are skipped in lockstep and the kernel ends.
+//   * Vectors travel between CTAs as (value, epoch) pairs of 8 bytes. A producer stores a pair
+//     with one store; a consumer polls the pairs themselves until they carry the epoch of this
+//     token and layer. Arrival and data are the same round trip: there is no grid barrier and no
+//     second load after a flag. Every vector has its own buffer; a buffer is rewritten a full
+//     layer later, by which time every reader has passed (each CTA needs all of a phase's outputs
+//     before it can produce the next phase's).
+//   * A phase's tiles keep their sums in registers ("round": at most MEGA_TA tiles); the sixteen
+//     K-slice partials of a round meet in shared memory once, behind one block barrier, and the
+//     first warps finish them (scale, residual / SwiGLU / logits) and store the pairs.
+//   * Nothing but the activation vector is fetched on the critical path: norm weights and the
+//     cached keys and values of earlier positions are requested before the poll begins; the
+//     residual rows a CTA owns stay in its shared memory for the whole token.
+//
+//   per layer: norm+QKV | qk-norm+RoPE+KV-write+attention | o_proj+res | norm+gate/up+SwiGLU |
+//   down+res ; then: norm+lm_head+argmax partials | argmax
+//
+// Every wait (mbarrier, pair poll) is bounded: when it gives up it raises the error word, the
+// CTA stops waiting for the rest of the launch (it still stores its pairs, so no other CTA is
+// held up by it) and the kernel ends; the host fails the call.
 #include <algorithm>
 
 #include "codec.cuh"
@@ -26,6 +42,89 @@
 namespace dyn {
 
 namespace {
+
+constexpr int MK_CW = 16;               // consumer warps
+constexpr int MK_CT = MK_CW * 32;       // consumer threads
+constexpr int MK_THREADS = MK_CT + 32;  // + one producer warp
+constexpr int MK_SLOT = 18432;          // bytes per ring slot (one 16-row tile x K-slice)
+constexpr int MK_PART = MEGA_TA * MK_CW * 16;  // floats of one partial-sum buffer
+// per-CTA scratch, in floats
+constexpr int MK_OFF_PART = 0;                       // 2 x MK_PART
+constexpr int MK_OFF_QS = 2 * MK_PART;               // [128] q of this CTA's head
+constexpr int MK_OFF_KN = MK_OFF_QS + 128;           // [128] new key (as cached)
+constexpr int MK_OFF_VN = MK_OFF_KN + 128;           // [128] new value (as cached)
+constexpr int MK_OFF_WM = MK_OFF_VN + 128;           // [16] per-warp running max
+constexpr int MK_OFF_WL = MK_OFF_WM + 16;            // [16] per-warp running sum
+constexpr int MK_OFF_RED = MK_OFF_WL + 16;           // [64] block reductions
+constexpr int MK_OFF_WACC = MK_OFF_RED + 64;         // [16][128] per-warp weighted values
+constexpr int MK_OFF_ROPE = MK_OFF_WACC + 16 * 128;  // cos[64], sin[64] of this token's position
+constexpr int MK_OFF_RES = MK_OFF_ROPE + 128;        // [64] residual rows this CTA owns
+constexpr int MK_OFF_AMAX = MK_OFF_RES + 64;         // [2 x 128] argmax candidates
+constexpr int MK_MISC_FLOATS = MK_OFF_AMAX + 256;
+constexpr int MK_MAX_OWNED = 64;  // hidden rows per CTA
+constexpr long long MK_MBAR_SPINS = 1LL << 22;
+constexpr long long MK_LL_SPINS = 1LL << 21;  // x ~0.5 us per poll round
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(MK_CT) : "memory"); }
+
+// ---- (value, epoch) pairs ----------------------------------------------------------------------
+__device__ __forceinline__ void ll_store(float* buf, int64_t idx, float v, unsigned ep) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(buf + 2 * idx), "r"(__float_as_uint(v)), "r"(ep)
+               : "memory");
+}
+// The 16-byte line that holds pairs idx and idx + 1 (idx even).
+__device__ __forceinline__ uint4 ll_load(const float* buf, int64_t idx) {
+  uint4 r;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(buf + 2 * idx)
+               : "memory");
+  return r;
+}
+// Polls NL lines until all carry `ep`. v[2i], v[2i+1] = the two values of line i. Gives up when the
+// CTA has already given up elsewhere or after MK_LL_SPINS rounds (then *abort = 8).
+template <int NL>
+__device__ __forceinline__ void ll_poll(const float* buf, const int64_t (&idx)[NL], unsigned ep, float (&v)[2 * NL],
+                                        volatile int* abort) {
+  uint4 r[NL];
+  long long it = 0;
+  for (;;) {
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < NL; i++) r[i] = ll_load(buf, idx[i]);
+#pragma unroll
+    for (int i = 0; i < NL; i++) ok = ok && r[i].y == ep && r[i].w == ep;
+    if (ok) break;
+    if (*abort) break;
+    if (++it >= MK_LL_SPINS) {
+      *abort = 8;
+      break;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NL; i++) {
+    v[2 * i] = __uint_as_float(r[i].x);
+    v[2 * i + 1] = __uint_as_float(r[i].z);
+  }
+}
+
+struct Smem {
+  float* xs;      // activation vector, f32
+  __half* xf;     // same, hi/lo f16 fragments
+  float* sx32;    // per-32 sums of the scaled activation
+  float* sx16;    // per-16 sums
+  float* misc;
+  uint8_t* ring;
+  uint64_t* full;
+  uint64_t* empty;
+  uint64_t* prog_bar;  // program copy landed
+  const MegaChunk* chunks;
+  const MegaTile* tiles;
+  const MegaRound* rounds;
+  const uint16_t* phase_rounds;
+  volatile int* abort;
+  int nslot;
+};
 
 // Embedding row through the exact scalar decoders (one row per token: not performance relevant).
 template <int ENC>
@@ -55,37 +154,6 @@ __device__ __noinline__ void mega_gather_row(const WRef w, int64_t row, float* o
     default: gather_row_t<E_F32>(w, row, out, tid, nthreads); break;
   }
 }
-
-constexpr int MK_CW = 16;               // consumer warps
-constexpr int MK_CT = MK_CW * 32;       // consumer threads
-constexpr int MK_THREADS = MK_CT + 32;  // + one producer warp
-constexpr int MK_SLOT = 18432;          // bytes per ring slot (one 16-row tile x K-slice)
-constexpr int MK_MISC_FLOATS = 6400;    // per-CTA scratch (attention state, reductions, partials, RoPE table)
-constexpr int MK_ROPE_OFF = 6144;       // misc floats [6144, 6400): cos[128], sin[128] of this token's position
-constexpr int MK_PART_OFF = 5120;       // misc floats [5120, 6144): 2 x [16 warps][32] partial sums
-constexpr long long MK_MBAR_SPINS = 1LL << 22;
-constexpr long long MK_GRID_SPINS = 1LL << 22;
-
-
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(MK_CT) : "memory"); }
-
-struct Smem {
-  float* xs;      // activation vector, f32
-  __half* xf;     // same, hi/lo f16 fragments
-  float* sx32;    // per-32 sums of the scaled activation
-  float* sx16;    // per-16 sums
-  float* misc;
-  uint8_t* ring;
-  uint64_t* full;
-  uint64_t* empty;
-  uint64_t* part_full;   // [2] partial-sum buffers: 16 warps arrived
-  uint64_t* part_empty;  // [2] finalising warp done reading
-  uint64_t* prog_bar;    // program copy landed
-  const MegaChunk* prog; // this CTA's chunk program (shared memory copy, or global)
-  const uint16_t* counts;
-  volatile int* abort;
-  int nslot;
-};
 
 // ---- producer: one bulk copy per tile row (lanes 0..15), MLX aux rows by lanes 16..31 --------
 __device__ __forceinline__ void produce_chunk(const MegaChunk* c, const Smem& sm, uint32_t pi, int lane) {
@@ -136,42 +204,80 @@ __device__ __forceinline__ void produce_chunk(const MegaChunk* c, const Smem& sm
   if (n1) bulk_g2s(d1, g1, n1, sm.full + slot);
 }
 
-// ---- consumer helpers ---------------------------------------------------------------------------
-// Stage the activation vector of a phase in one pass. Thread i owns fragment item i = (block kb,
-// lane quarter t) and loads exactly the 8 elements that item holds (the items partition the
-// vector; n <= 8 * MK_CT), so the sum of squares and the scale come from one combined block
-// reduction and the normalised values go straight from registers to hi/lo f16 fragments and
-// 16-/32-run sums. Optional RMSNorm: v = (x*inv)*w, inv = 1/sqrt(mean(x^2)+eps).
-// Returns 2^24 / scale. `src_smem`: the vector already sits in sm.xs; else it is read from L2.
-__device__ __forceinline__ float stage_phase(const float* x, bool src_smem, const void* nw, int nw_type,
-                                             int n, float eps, int layout, const Smem& sm, int tid,
-                                             int lane, int warp) {
-  float* red = sm.misc + MK_PART_OFF - 64;
-  const int items = (n >> 5) * 4;
-  const int kb = tid >> 2, t = tid & 3;
-  const bool live = tid < items;
-  // load order: A = 4 elements, B = 4 elements
-  const int baseA = kb * 32 + (layout == XL_MLXW ? 8 * t : 4 * t);
-  const int baseB = layout == XL_MLXW ? baseA + 4 : kb * 32 + 16 + 4 * t;
-  float v[8], w[8];
+// ---- staging the activation vector of a phase ---------------------------------------------------
+// Item i = (block kb = i / 4, lane quarter t = i % 4) holds 8 elements of the vector: A = 4
+// elements at baseA, B = 4 elements at baseB (the items partition the vector). Pass 1 brings each
+// item's elements in (polled pairs, the split-KV partials, or already in xs), stores them to xs
+// and accumulates the sum of squares and the largest magnitude; one block reduction gives the
+// RMSNorm factor and the power-of-two scale; pass 2 writes the hi/lo f16 fragments and the
+// 16-/32-run sums. Returns 2^24 / scale.
+enum { SRC_XS = 0, SRC_LL = 1, SRC_PARTIALS = 2 };
+
+struct StageSrc {
+  int kind;
+  const float* ll;  // SRC_LL: the pair buffer; SRC_PARTIALS: a.ll_part
+  unsigned ep;
+  int nsplit, max_split, d;  // SRC_PARTIALS
+};
+
+__device__ __forceinline__ float stage_phase(const StageSrc& src, const void* nw, int nw_type, int n, float eps,
+                                             int layout, const Smem& sm, int tid, int lane, int warp) {
+  float* red = sm.misc + MK_OFF_RED;
+  const int items = n >> 3;
   float ss = 0.f, mx = 0.f;
-  if (live) {
-    const float4 a4 = src_smem ? *reinterpret_cast<const float4*>(sm.xs + baseA)
-                               : __ldcg(reinterpret_cast<const float4*>(x + baseA));
-    const float4 b4 = src_smem ? *reinterpret_cast<const float4*>(sm.xs + baseB)
-                               : __ldcg(reinterpret_cast<const float4*>(x + baseB));
-    v[0] = a4.x, v[1] = a4.y, v[2] = a4.z, v[3] = a4.w;
-    v[4] = b4.x, v[5] = b4.y, v[6] = b4.z, v[7] = b4.w;
+  for (int i = tid; i < items; i += MK_CT) {  // items is a multiple of 4; a lane quad is one 32-block
+    const int kb = i >> 2, t = i & 3;
+    const int baseA = kb * 32 + (layout == XL_MLXW ? 8 * t : 4 * t);
+    const int baseB = layout == XL_MLXW ? baseA + 4 : kb * 32 + 16 + 4 * t;
+    // norm weights first: their loads are in flight while the pairs are polled
+    float w[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-      w[i] = nw ? aux_load(reinterpret_cast<const uint8_t*>(nw), nw_type, (i < 4 ? baseA : baseB - 4) + i) : 1.0f;
-      ss = fmaf(v[i], v[i], ss);
-      mx = fmaxf(mx, fabsf(v[i] * w[i]));
+    for (int j = 0; j < 8; j++)
+      w[j] = nw ? aux_load(reinterpret_cast<const uint8_t*>(nw), nw_type, (j < 4 ? baseA : baseB - 4) + j) : 1.0f;
+    float v[8];
+    if (src.kind == SRC_LL) {
+      const int64_t idx[4] = {baseA, baseA + 2, baseB, baseB + 2};
+      ll_poll<4>(src.ll, idx, src.ep, v, sm.abort);
+    } else if (src.kind == SRC_PARTIALS) {
+      // merge the split-KV partial outputs of this item's head in split order (online softmax merge)
+      const int head = baseA / src.d, ia = baseA - head * src.d, ib = baseB - head * src.d;
+      float M = -3.40282347e38f, Lsum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; j++) v[j] = 0.f;
+      for (int s = 0; s < src.nsplit; s++) {
+        const int64_t pb = ((int64_t)head * src.max_split + s) * (src.d + 2);
+        const int64_t idx[5] = {pb + ia, pb + ia + 2, pb + ib, pb + ib + 2, pb + src.d};
+        float p[10];
+        ll_poll<5>(src.ll, idx, src.ep, p, sm.abort);
+        const float ms = p[8], ls = p[9];
+        const float mn = fmaxf(M, ms);
+        const float f = expf(M - mn), wgt = expf(ms - mn);
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = v[j] * f + p[j] * wgt;
+        Lsum = Lsum * f + ls * wgt;
+        M = mn;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; j++) v[j] = v[j] / Lsum;
+    } else {
+      const float4 a4 = *reinterpret_cast<const float4*>(sm.xs + baseA);
+      const float4 b4 = *reinterpret_cast<const float4*>(sm.xs + baseB);
+      v[0] = a4.x, v[1] = a4.y, v[2] = a4.z, v[3] = a4.w;
+      v[4] = b4.x, v[5] = b4.y, v[6] = b4.z, v[7] = b4.w;
+    }
+    if (src.kind != SRC_XS) {
+      *reinterpret_cast<float4*>(sm.xs + baseA) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(sm.xs + baseB) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      ss = fmaf(v[j], v[j], ss);
+      mx = fmaxf(mx, fabsf(v[j] * w[j]));
     }
   }
   ss = warp_sum(ss);
   mx = warp_max(mx);
-  consumer_sync();
+  consumer_sync();  // red is free (earlier readers are past their last use)
   if (lane == 0) {
     red[warp] = ss;
     red[32 + warp] = mx;
@@ -186,46 +292,59 @@ __device__ __forceinline__ float stage_phase(const float* x, bool src_smem, cons
   const float inv = nw ? 1.0f / sqrtf(tss / (float)n + eps) : 1.0f;
   float s, is;
   scale_for(tmx * inv * 1.0001f, &s, &is);
-  float run0 = 0.f, run1 = 0.f;  // this item's share of the block's two 16-element runs
-  if (live) {
-    float sv[8];
+  for (int iw = warp * 32; iw < items; iw += MK_CT) {  // whole warps enter, for the shuffles below
+    const int i = iw + lane;
+    const bool live = i < items;
+    const int kb = i >> 2, t = i & 3;
+    const int baseA = kb * 32 + (layout == XL_MLXW ? 8 * t : 4 * t);
+    const int baseB = layout == XL_MLXW ? baseA + 4 : kb * 32 + 16 + 4 * t;
+    float run0 = 0.f, run1 = 0.f;  // this item's share of the block's two 16-element runs
+    if (live) {
+      const float4 a4 = *reinterpret_cast<const float4*>(sm.xs + baseA);  // written by this thread
+      const float4 b4 = *reinterpret_cast<const float4*>(sm.xs + baseB);
+      const float v[8] = {a4.x, a4.y, a4.z, a4.w, b4.x, b4.y, b4.z, b4.w};
+      float sv[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) sv[i] = (nw ? __fmul_rn(__fmul_rn(v[i], inv), w[i]) : v[i]) * s;
-    const float sa = (sv[0] + sv[1]) + (sv[2] + sv[3]), sb = (sv[4] + sv[5]) + (sv[6] + sv[7]);
-    float f[8];  // fragment order
-    if (layout == XL_NIBBLE) {
-      f[0] = sv[0], f[1] = sv[2], f[2] = sv[4] * 0.0625f, f[3] = sv[6] * 0.0625f;
-      f[4] = sv[1], f[5] = sv[3], f[6] = sv[5] * 0.0625f, f[7] = sv[7] * 0.0625f;
-      run0 = sa, run1 = sb;
-    } else if (layout == XL_MLXW) {
-      f[0] = sv[0], f[1] = sv[4], f[2] = sv[1] * 0.0625f, f[3] = sv[5] * 0.0625f;
-      f[4] = sv[2], f[5] = sv[6], f[6] = sv[3] * 0.0625f, f[7] = sv[7] * 0.0625f;
-      if (t < 2) run0 = sa + sb; else run1 = sa + sb;
-    } else {
+      for (int j = 0; j < 8; j++) {
+        const float wj = nw ? aux_load(reinterpret_cast<const uint8_t*>(nw), nw_type, (j < 4 ? baseA : baseB - 4) + j) : 1.0f;
+        sv[j] = (nw ? __fmul_rn(__fmul_rn(v[j], inv), wj) : v[j]) * s;
+      }
+      const float sa = (sv[0] + sv[1]) + (sv[2] + sv[3]), sb = (sv[4] + sv[5]) + (sv[6] + sv[7]);
+      float f[8];  // fragment order
+      if (layout == XL_NIBBLE) {
+        f[0] = sv[0], f[1] = sv[2], f[2] = sv[4] * 0.0625f, f[3] = sv[6] * 0.0625f;
+        f[4] = sv[1], f[5] = sv[3], f[6] = sv[5] * 0.0625f, f[7] = sv[7] * 0.0625f;
+        run0 = sa, run1 = sb;
+      } else if (layout == XL_MLXW) {
+        f[0] = sv[0], f[1] = sv[4], f[2] = sv[1] * 0.0625f, f[3] = sv[5] * 0.0625f;
+        f[4] = sv[2], f[5] = sv[6], f[6] = sv[3] * 0.0625f, f[7] = sv[7] * 0.0625f;
+        if (t < 2) run0 = sa + sb; else run1 = sa + sb;
+      } else {
 #pragma unroll
-      for (int i = 0; i < 8; i++) f[i] = sv[i];
-      run0 = sa, run1 = sb;
+        for (int j = 0; j < 8; j++) f[j] = sv[j];
+        run0 = sa, run1 = sb;
+      }
+      __half hi[8], lo[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const __half h = __float2half_rn(f[j]);
+        hi[j] = h;
+        lo[j] = __float2half_rn(f[j] - __half2float(h));
+      }
+      uint4* dst = reinterpret_cast<uint4*>(sm.xf + ((size_t)(kb * 2) * 4 + t) * 8);
+      dst[0] = *reinterpret_cast<uint4*>(hi);
+      dst[4] = *reinterpret_cast<uint4*>(lo);
     }
-    __half hi[8], lo[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-      const __half h = __float2half_rn(f[i]);
-      hi[i] = h;
-      lo[i] = __float2half_rn(f[i] - __half2float(h));
+    // the four quarters of a block are four consecutive lanes
+    run0 += __shfl_xor_sync(0xffffffffu, run0, 1);
+    run1 += __shfl_xor_sync(0xffffffffu, run1, 1);
+    run0 += __shfl_xor_sync(0xffffffffu, run0, 2);
+    run1 += __shfl_xor_sync(0xffffffffu, run1, 2);
+    if (live && t == 0) {
+      sm.sx16[2 * kb] = run0;
+      sm.sx16[2 * kb + 1] = run1;
+      sm.sx32[kb] = run0 + run1;
     }
-    uint4* dst = reinterpret_cast<uint4*>(sm.xf + ((size_t)(kb * 2) * 4 + t) * 8);
-    dst[0] = *reinterpret_cast<uint4*>(hi);
-    dst[4] = *reinterpret_cast<uint4*>(lo);
-  }
-  // the four quarters of a block are four consecutive lanes
-  run0 += __shfl_xor_sync(0xffffffffu, run0, 1);
-  run1 += __shfl_xor_sync(0xffffffffu, run1, 1);
-  run0 += __shfl_xor_sync(0xffffffffu, run0, 2);
-  run1 += __shfl_xor_sync(0xffffffffu, run1, 2);
-  if (live && t == 0) {
-    sm.sx16[2 * kb] = run0;
-    sm.sx16[2 * kb + 1] = run1;
-    sm.sx32[kb] = run0 + run1;
   }
   consumer_sync();
   return GV_2P24 * is;
@@ -294,10 +413,10 @@ __device__ __forceinline__ unsigned long long gtime() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Phase timing seen by CTA 0 (optional): kind 0 embed, 1 qkv, 2 attention, 3 o_proj, 4 gate/up,
-// 5 down, 6 lm_head, 7 argmax, 8 whole kernel; 9 staging, 10 waiting for weights, 11 tile math,
-// 12 grid barrier; attention of CTA 0: 13 q/k/v load + norm + RoPE + first key fetch, 14 scores and
-// softmax, 15 merge and write.
+// Timing seen by CTA 0, thread 0 (optional). By phase: 0 embed, 1 qkv, 2 attention, 3 o_proj,
+// 4 gate/up, 5 down, 6 lm_head, 7 argmax, 8 whole kernel. Across phases: 9 staging (poll +
+// conversion), 10 waiting for weights, 11 tile math, 12 round reduction + epilogue; attention of
+// CTA 0: 13 until q/k/v are in place, 14 scores and softmax, 15 merge and write.
 struct Prof {
   unsigned long long* out;
   unsigned long long last, start;
@@ -326,111 +445,27 @@ struct Prof {
   }
 };
 
-struct GridBar {
-  unsigned long long gen;
-};
-
-// Arrival: release-add on a monotonic counter; waiting: acquire-poll the same counter.
-__device__ __forceinline__ void grid_sync(const MegaArgs& a, GridBar& gb, int G, int tid,
-                                          const Smem& sm) {
-  consumer_sync();
-  if (tid == 0) {
-    gb.gen += 1;
-    const unsigned long long target = gb.gen * (unsigned long long)G;
-    asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(a.bar) : "memory");
-    if (!*sm.abort) {
-      unsigned long long seen = 0;
-      long long it = 0;
-      do {
-        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(a.bar) : "memory");
-        if (seen >= target) break;
-      } while (++it < MK_GRID_SPINS);
-      if (seen < target) *sm.abort = 2;
-    }
-  }
-  consumer_sync();
-}
-
-// ---- attention for one (head, split); DPL = head-dim slots per lane ------------------------------
-// Latency plan: one L2 round trip for q/k/v and the norm weights, one combined block reduction
-// for both RMS sums, then every warp fetches all of its keys (K and V rows, up to KB at a time)
-// before touching any of them, so a short context costs one more round trip, not one per key.
-template <int DPL>
+// ---- attention for one (head, split); head dim 64 or 128, a lane owns 4 head dims ----------------
+// Latency plan: the cached keys and values of earlier positions and the norm weights are requested
+// first; then warps 0 / 1 / 2 poll this token's q / k / v of the head (one or two lines per lane),
+// normalise and rotate them inside the warp (no block reduction) and leave them in shared memory.
 __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const MegaLayer* L, int cta,
-                                                int64_t pos, int64_t seq, int nsplit, const Smem& sm,
-                                                int tid, int lane, int warp, Prof& prof) {
+                                                int64_t pos, int64_t seq, int nsplit, unsigned ep,
+                                                const Smem& sm, int tid, int lane, int warp, Prof& prof) {
   if (cta >= a.nh * nsplit) return;
   unsigned long long tp = prof.tic();
-  constexpr int KB = 4;  // keys in flight per warp
+  constexpr int KB = 4;   // keys in flight per warp
+  constexpr int DPL = 4;  // head dims per lane
   const int h = cta / nsplit, sp = cta - h * nsplit;
   const int grp = a.nh / a.nkv, kvh = h / grp, gi = h - kvh * grp;
   const int d = a.d, half = d / 2;
-  float* qs = sm.misc;           // [256]
-  float* kn = sm.misc + 256;     // [256]
-  float* vn = sm.misc + 512;     // [256]
-  float* wm = sm.misc + 768;     // [16]
-  float* wl = sm.misc + 784;     // [16]
-  float* red = sm.misc + 800;    // [64]
-  float* wacc = sm.misc + 1024;  // [16][256]
-  // thread i < d/2 owns the rotation pair (i, i + d/2) of q and of k
-  float q1 = 0.f, q2 = 0.f, k1 = 0.f, k2 = 0.f, wq1 = 1.f, wq2 = 1.f, wk1 = 1.f, wk2 = 1.f;
-  const bool pair = tid < half;
-  if (pair) {
-    q1 = __ldcg(a.q + (int64_t)h * d + tid);
-    q2 = __ldcg(a.q + (int64_t)h * d + tid + half);
-    k1 = __ldcg(a.k + (int64_t)kvh * d + tid);
-    k2 = __ldcg(a.k + (int64_t)kvh * d + tid + half);
-    if (a.has_norm) {
-      const uint8_t* qw = reinterpret_cast<const uint8_t*>(L->q_norm);
-      const uint8_t* kw = reinterpret_cast<const uint8_t*>(L->k_norm);
-      wq1 = aux_load(qw, L->qk_norm_type, tid), wq2 = aux_load(qw, L->qk_norm_type, tid + half);
-      wk1 = aux_load(kw, L->qk_norm_type, tid), wk2 = aux_load(kw, L->qk_norm_type, tid + half);
-    }
-  }
-  for (int i = tid; i < d; i += MK_CT) vn[i] = round_kv(__ldcg(a.v + (int64_t)kvh * d + i), a.kv_type);
-  float qinv = 1.f, kinv = 1.f;
-  unsigned long long tq_ = prof.tic();
-  if (a.has_norm) {
-    float sq = warp_sum(fmaf(q1, q1, q2 * q2)), sk = warp_sum(fmaf(k1, k1, k2 * k2));
-    prof.toc(16, tp);  // q/k/v and norm weights arrived
-    tq_ = prof.tic();
-    consumer_sync();
-    if (lane == 0) {
-      red[warp] = sq;
-      red[32 + warp] = sk;
-    }
-    consumer_sync();
-    float tq = 0.f, tk = 0.f;
-#pragma unroll
-    for (int i = 0; i < MK_CW; i++) {
-      tq += red[i];
-      tk += red[32 + i];
-    }
-    qinv = 1.0f / sqrtf(tq / (float)d + a.eps);
-    kinv = 1.0f / sqrtf(tk / (float)d + a.eps);
-    prof.toc(17, tq_);  // block reduction of the two RMS sums
-    tq_ = prof.tic();
-  }
-  if (pair) {
-    if (a.has_norm) {
-      q1 = __fmul_rn(__fmul_rn(q1, qinv), wq1);
-      q2 = __fmul_rn(__fmul_rn(q2, qinv), wq2);
-      k1 = __fmul_rn(__fmul_rn(k1, kinv), wk1);
-      k2 = __fmul_rn(__fmul_rn(k2, kinv), wk2);
-    }
-    if (a.has_rope) {
-      const float cv = sm.misc[MK_ROPE_OFF + tid], sv = sm.misc[MK_ROPE_OFF + 128 + tid];  // once per token
-      const float ql = __fsub_rn(__fmul_rn(q1, cv), __fmul_rn(q2, sv));
-      const float qh = __fadd_rn(__fmul_rn(q1, sv), __fmul_rn(q2, cv));
-      const float kl = __fsub_rn(__fmul_rn(k1, cv), __fmul_rn(k2, sv));
-      const float kh = __fadd_rn(__fmul_rn(k1, sv), __fmul_rn(k2, cv));
-      q1 = ql, q2 = qh, k1 = kl, k2 = kh;
-    }
-    qs[tid] = q1;
-    qs[tid + half] = q2;
-    kn[tid] = round_kv(k1, a.kv_type);
-    kn[tid + half] = round_kv(k2, a.kv_type);
-  }
+  float* qs = sm.misc + MK_OFF_QS;
+  float* kn = sm.misc + MK_OFF_KN;
+  float* vn = sm.misc + MK_OFF_VN;
+  float* wm = sm.misc + MK_OFF_WM;
+  float* wl = sm.misc + MK_OFF_WL;
+  float* wwt = sm.misc + MK_OFF_RED;
+  float* wacc = sm.misc + MK_OFF_WACC;
   uint8_t* kc = a.kcache + (uint64_t)l * a.layer_stride;
   uint8_t* vc = a.vcache + (uint64_t)l * a.layer_stride;
   const int64_t plane = ((seq * a.nkv + kvh) * a.cap) * d;  // element offset of this head's plane
@@ -439,53 +474,86 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
   const int64_t k_lo = (int64_t)sp * per;
   const int64_t k_hi = (k_lo + per < n) ? k_lo + per : n;
   // A lane owns DPL consecutive head dims (one 8- or 16-byte piece of every cached row), so a
-  // warp reads a key or value row with one coalesced vector load. First batch of this warp's
-  // keys: the loads are issued before the barrier that publishes q.
-  constexpr int WPL = DPL;  // raw words per lane and row (f32 cache); 2-byte caches use DPL / 2
+  // warp reads a key or value row with one coalesced vector load.
   const bool wide = a.kv_type == E_F32;
   const int e0 = lane * DPL;  // first head dim of this lane
   const bool lane_live = e0 < d;
-  uint32_t kraw[KB][WPL], vraw[KB][WPL];
+  uint32_t kraw[KB][DPL], vraw[KB][DPL];
   auto fetch = [&](int64_t key0) {
 #pragma unroll
     for (int b = 0; b < KB; b++) {
       const int64_t key = key0 + (int64_t)b * MK_CW;
 #pragma unroll
-      for (int w = 0; w < WPL; w++) kraw[b][w] = vraw[b][w] = 0;
+      for (int w = 0; w < DPL; w++) kraw[b][w] = vraw[b][w] = 0;
       if (key < k_hi && key != pos && lane_live) {
         const int64_t el = plane + key * d + e0;
         if (wide) {
-          const uint4* kp = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(kc) + el);
-          const uint4* vp = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(vc) + el);
-#pragma unroll
-          for (int w4 = 0; w4 < WPL / 4; w4++) {
-            const uint4 kk = kp[w4], vv = vp[w4];
-            kraw[b][4 * w4] = kk.x, kraw[b][4 * w4 + 1] = kk.y, kraw[b][4 * w4 + 2] = kk.z, kraw[b][4 * w4 + 3] = kk.w;
-            vraw[b][4 * w4] = vv.x, vraw[b][4 * w4 + 1] = vv.y, vraw[b][4 * w4 + 2] = vv.z, vraw[b][4 * w4 + 3] = vv.w;
-          }
+          const uint4 kk = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(kc) + el));
+          const uint4 vv = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(vc) + el));
+          kraw[b][0] = kk.x, kraw[b][1] = kk.y, kraw[b][2] = kk.z, kraw[b][3] = kk.w;
+          vraw[b][0] = vv.x, vraw[b][1] = vv.y, vraw[b][2] = vv.z, vraw[b][3] = vv.w;
         } else {
-          const uint2* kp = reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(kc) + el);
-          const uint2* vp = reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(vc) + el);
-#pragma unroll
-          for (int w2 = 0; w2 < WPL / 4; w2++) {
-            const uint2 kk = kp[w2], vv = vp[w2];
-            kraw[b][2 * w2] = kk.x, kraw[b][2 * w2 + 1] = kk.y;
-            vraw[b][2 * w2] = vv.x, vraw[b][2 * w2 + 1] = vv.y;
-          }
+          const uint2 kk = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(kc) + el));
+          const uint2 vv = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(vc) + el));
+          kraw[b][0] = kk.x, kraw[b][1] = kk.y;
+          vraw[b][0] = vv.x, vraw[b][1] = vv.y;
         }
       }
     }
   };
   // element j of a raw row piece as f32
-  auto elem = [&](const uint32_t (&raw)[WPL], int j) -> float {
+  auto elem = [&](const uint32_t (&raw)[DPL], int j) -> float {
     if (wide) return __uint_as_float(raw[j]);
     const uint32_t bits = (raw[j >> 1] >> (16 * (j & 1))) & 0xffffu;
     return a.kv_type == E_F16 ? f16_bits_to_f32(bits) : bf16_bits_to_f32(bits);
   };
-  prof.toc(18, tq_);  // norm, RoPE, shared-memory hand-off, cache addresses
-  tq_ = prof.tic();
-  fetch(k_lo + warp);
-  prof.toc(19, tq_);  // issuing the first key / value loads
+  fetch(k_lo + warp);  // in flight while q / k / v of this token arrive
+
+  if (warp < 3) {
+    // lane j < d/4 holds elements i = 2j, 2j+1 and their rotation partners i + d/2
+    const int64_t qd = (int64_t)a.nh * d, kvd = (int64_t)a.nkv * d;
+    const int64_t base = warp == 0 ? (int64_t)h * d : (warp == 1 ? qd + (int64_t)kvh * d : qd + kvd + (int64_t)kvh * d);
+    const bool act = lane < d / 4;
+    const int i0 = 2 * lane;
+    float w1a = 1.f, w1b = 1.f, w2a = 1.f, w2b = 1.f;
+    if (act && a.has_norm && warp < 2) {
+      const uint8_t* nw = reinterpret_cast<const uint8_t*>(warp == 0 ? L->q_norm : L->k_norm);
+      w1a = aux_load(nw, L->qk_norm_type, i0), w1b = aux_load(nw, L->qk_norm_type, i0 + 1);
+      w2a = aux_load(nw, L->qk_norm_type, i0 + half), w2b = aux_load(nw, L->qk_norm_type, i0 + half + 1);
+    }
+    float x[4] = {0.f, 0.f, 0.f, 0.f};  // x1a x1b x2a x2b
+    if (act) {
+      const int64_t idx[2] = {base + i0, base + i0 + half};
+      ll_poll<2>(a.ll_qkv, idx, ep, x, sm.abort);
+    }
+    if (warp < 2) {
+      if (a.has_norm) {
+        const float ssq = warp_sum(fmaf(x[0], x[0], x[1] * x[1]) + fmaf(x[2], x[2], x[3] * x[3]));
+        const float inv = 1.0f / sqrtf(ssq / (float)d + a.eps);
+        x[0] = __fmul_rn(__fmul_rn(x[0], inv), w1a);
+        x[1] = __fmul_rn(__fmul_rn(x[1], inv), w1b);
+        x[2] = __fmul_rn(__fmul_rn(x[2], inv), w2a);
+        x[3] = __fmul_rn(__fmul_rn(x[3], inv), w2b);
+      }
+      if (a.has_rope && act) {
+        const float* cs = sm.misc + MK_OFF_ROPE;
+        const float ca = cs[i0], cb = cs[i0 + 1], sa = cs[64 + i0], sb = cs[64 + i0 + 1];
+        const float la = __fsub_rn(__fmul_rn(x[0], ca), __fmul_rn(x[2], sa));
+        const float ha = __fadd_rn(__fmul_rn(x[0], sa), __fmul_rn(x[2], ca));
+        const float lb = __fsub_rn(__fmul_rn(x[1], cb), __fmul_rn(x[3], sb));
+        const float hb = __fadd_rn(__fmul_rn(x[1], sb), __fmul_rn(x[3], cb));
+        x[0] = la, x[1] = lb, x[2] = ha, x[3] = hb;
+      }
+    }
+    if (act) {
+      float* dst = warp == 0 ? qs : (warp == 1 ? kn : vn);
+      const bool rnd = warp != 0;
+      dst[i0] = rnd ? round_kv(x[0], a.kv_type) : x[0];
+      dst[i0 + 1] = rnd ? round_kv(x[1], a.kv_type) : x[1];
+      dst[i0 + half] = rnd ? round_kv(x[2], a.kv_type) : x[2];
+      dst[i0 + half + 1] = rnd ? round_kv(x[3], a.kv_type) : x[3];
+    }
+  }
   consumer_sync();
   prof.toc(13, tp);
   tp = prof.tic();
@@ -541,32 +609,31 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
   }
   if (lane_live) {
 #pragma unroll
-    for (int j = 0; j < DPL; j++) wacc[warp * 256 + e0 + j] = acc[j];
+    for (int j = 0; j < DPL; j++) wacc[warp * 128 + e0 + j] = acc[j];
   }
   consumer_sync();
   float gm = wm[0];
 #pragma unroll
   for (int w = 1; w < MK_CW; w++) gm = fmaxf(gm, wm[w]);
   // each warp's weight exp(m_w - gm) once, by one lane per warp, instead of per output element
-  float* wwt = red;  // [16], free since the RMS reduction
   if (tid < MK_CW) wwt[tid] = expf(wm[tid] - gm);
   consumer_sync();
   float gl = 0.f;
 #pragma unroll
   for (int w = 0; w < MK_CW; w++) gl += wl[w] * wwt[w];
-  float* part = a.attn_part + ((int64_t)h * a.max_split + sp) * (d + 2);
+  const int64_t pbase = ((int64_t)h * a.max_split + sp) * (d + 2);
   for (int idx = tid; idx < d; idx += MK_CT) {
     float o = 0.f;
 #pragma unroll
-    for (int w = 0; w < MK_CW; w++) o += wacc[w * 256 + idx] * wwt[w];
+    for (int w = 0; w < MK_CW; w++) o += wacc[w * 128 + idx] * wwt[w];
     if (nsplit == 1)
-      a.ctx[(int64_t)h * d + idx] = o / gl;
+      ll_store(a.ll_ctx, (int64_t)h * d + idx, o / gl, ep);
     else
-      part[idx] = o;
+      ll_store(a.ll_part, pbase + idx, o, ep);
   }
   if (nsplit > 1 && tid == 0) {
-    part[d] = gm;
-    part[d + 1] = gl;
+    ll_store(a.ll_part, pbase + d, gm, ep);
+    ll_store(a.ll_part, pbase + d + 1, gl, ep);
   }
   prof.toc(15, tp);
 }
@@ -588,13 +655,8 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
   sm.ring = reinterpret_cast<uint8_t*>(sm.misc + MK_MISC_FLOATS);
   sm.full = reinterpret_cast<uint64_t*>(sm.ring + (size_t)a.nslot * MK_SLOT);
   sm.empty = sm.full + a.nslot;
-  sm.part_full = sm.empty + a.nslot;
-  sm.part_empty = sm.part_full + 2;
-  sm.prog_bar = sm.part_empty + 2;
+  sm.prog_bar = sm.empty + a.nslot;
   uint8_t* prog_area = reinterpret_cast<uint8_t*>(sm.prog_bar + 2);
-  const int nph = 4 * a.layers + 1;
-  sm.prog = a.prog + (size_t)cta * a.max_chunks;
-  sm.counts = a.counts + (size_t)cta * nph;
   sm.abort = &s_abort;
   if (tid == 0) {
     s_abort = 0;
@@ -602,269 +664,239 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
       mbar_init(sm.full + i, 1);
       mbar_init(sm.empty + i, MK_CW);
     }
-    for (int i = 0; i < 2; i++) {
-      mbar_init(sm.part_full + i, MK_CW);
-      mbar_init(sm.part_empty + i, 1);
-    }
     mbar_init(sm.prog_bar, 1);
     mbar_fence_init();
-    if (a.prog_in_smem) {
-      // one bulk copy brings this CTA's whole program next to the math
-      const unsigned bytes = (unsigned)a.max_chunks * (unsigned)sizeof(MegaChunk);
-      mbar_expect_tx(sm.prog_bar, bytes);
-      bulk_g2s(prog_area, sm.prog, bytes, sm.prog_bar);
-    }
+    // one bulk copy brings this CTA's whole program next to the math
+    mbar_expect_tx(sm.prog_bar, (unsigned)a.lay.bytes);
+    bulk_g2s(prog_area, a.prog + (size_t)cta * a.lay.bytes, (unsigned)a.lay.bytes, sm.prog_bar);
   }
   __syncthreads();
-  if (a.prog_in_smem) {
-    uint16_t* cdst = reinterpret_cast<uint16_t*>(prog_area + (size_t)a.max_chunks * sizeof(MegaChunk));
-    for (int i = tid; i < nph; i += MK_THREADS) cdst[i] = sm.counts[i];
-    if (!mbar_wait_bounded(sm.prog_bar, 0, MK_MBAR_SPINS, sm.abort) && !*sm.abort) *sm.abort = 7;
-    __syncthreads();
-    sm.prog = reinterpret_cast<const MegaChunk*>(prog_area);
-    sm.counts = cdst;
-  }
+  if (!mbar_wait_bounded(sm.prog_bar, 0, MK_MBAR_SPINS, sm.abort) && !*sm.abort) *sm.abort = 7;
+  const MegaProgHeader* hdr = reinterpret_cast<const MegaProgHeader*>(prog_area);
+  sm.chunks = reinterpret_cast<const MegaChunk*>(prog_area + sizeof(MegaProgHeader));
+  sm.tiles = reinterpret_cast<const MegaTile*>(prog_area + a.lay.off_tiles);
+  sm.rounds = reinterpret_cast<const MegaRound*>(prog_area + a.lay.off_rounds);
+  sm.phase_rounds = reinterpret_cast<const uint16_t*>(prog_area + a.lay.off_phase);
 
   if (warp == MK_CW) {
     // ------------------------------ producer: stream this CTA's weight tiles --------------
-    int total = 0;
-    for (int i = lane; i < nph; i += 32) total += sm.counts[i];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-    for (int pi = 0; pi < total; pi++) produce_chunk(sm.prog + pi, sm, (uint32_t)pi, lane);
+    const int total = *sm.abort ? 0 : (int)hdr->nchunks;
+    for (int pi = 0; pi < total; pi++) produce_chunk(sm.chunks + pi, sm, (uint32_t)pi, lane);
     return;
   }
 
   // -------------------------------- consumers -------------------------------------------------
-  GridBar gb;
-  gb.gen = 0;
-  if (tid == 0) gb.gen = *reinterpret_cast<const volatile unsigned long long*>(a.bar) / (unsigned long long)G;
   const int64_t token = __ldcg(a.io + 0), pos = __ldcg(a.io + 1), seq = __ldcg(a.io + 2);
   int nsplit = (int)((pos + 1 + 63) / 64);
   if (nsplit > a.max_split) nsplit = a.max_split;
   if (nsplit < 1) nsplit = 1;
   const int64_t qd = (int64_t)a.nh * a.d;
   const int g = lane >> 2;
-  uint32_t ci = 0;
-  unsigned closes = 0;
-  float out_scale = 1.f;
-  float bv = -INFINITY;  // running argmax over the rows this thread finalises
+  const int hid_lo = (int)hdr->hid_lo;
+  float* res = sm.misc + MK_OFF_RES;
+  uint32_t ci = 0, ri = 0, ti = 0;
+  unsigned nround = 0;
+  float bv = -INFINITY;  // running argmax over the rows this thread finishes
   long long bi = 0x7fffffffffffffffLL;
   Prof prof;
   prof.begin(a.prof, cta == 0 && tid == 0);
-  TileAcc<true> acc, acc2;
 
-  // One phase's chunks, in program order.
-  const MegaChunk* prog = sm.prog;
-  const uint16_t* counts = sm.counts;
-  auto run_phase = [&](int phase_index) {
-    acc.clear();
-    acc2.clear();
-    const int cnt = counts[phase_index];
-    for (int k = 0; k < cnt; k++, ci++) {
-      const MegaChunk* c = prog + ci;
-      const int slot = ci % sm.nslot;
-      // the finalising lanes fetch the residual now so that it is there when the tile closes
-      float resid = 0.f;
-      if (warp == 0 && lane < 16 && lane < c->n && (c->flags & 1) && ((c->flags >> 2) & 3) == MEGA_EP_RESIDUAL)
-        resid = __ldcg(c->out + c->out_row + lane);
-      const unsigned long long tw = prof.tic();
-      const bool ok = mbar_wait_bounded(sm.full + slot, (ci / sm.nslot) & 1u, MK_MBAR_SPINS, sm.abort);
-      if (!ok && !*sm.abort) *sm.abort = 3;
-      prof.toc(10, tw);
-      const unsigned long long tr = prof.tic();
-      const int n = c->n, nu = c->nu, flags = c->flags;
-      if (ok) {
-        const uint8_t* base = sm.ring + (size_t)slot * MK_SLOT;
-        const int i0 = g < n ? g : n - 1, i1 = g + 8 < n ? g + 8 : n - 1;  // clamp to valid rows
-        const uint32_t pitch = c->pitch, rb = c->rb;
-        const uint8_t* src = c->src;
-        const uint8_t* p0 = base + i0 * pitch + (reinterpret_cast<uintptr_t>(src + (size_t)i0 * rb) & 15);
-        const uint8_t* p1 = base + i1 * pitch + (reinterpret_cast<uintptr_t>(src + (size_t)i1 * rb) & 15);
-        const uint8_t* a0 = nullptr;
-        const uint8_t* a1 = nullptr;
-        const int apitch = c->apitch;
-        if (c->aseg) {
-          const uint8_t* ab = base + 16 * pitch;
-          a0 = ab + i0 * apitch + (reinterpret_cast<uintptr_t>(c->sc + (size_t)i0 * c->arb) & 15);
-          a1 = ab + i1 * apitch + (reinterpret_cast<uintptr_t>(c->sc + (size_t)i1 * c->arb) & 15);
-        }
-        const int enc = c->enc, aux = c->aux, gs = c->group_shift, kb0 = c->kb0;
-        TileAcc<true>& A = (flags & 2) ? acc2 : acc;
-        for (int u = warp; u < nu; u += MK_CW) run_unit(enc, aux, gs, p0, p1, a0, a1, 16 * apitch, u, kb0, sm, lane, A);
-      }
-      prof.toc(11, tr);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sm.empty + slot);
-      if (!(flags & 1)) continue;
-      // tile complete: per-warp partial sums -> warp 0 adds them in a fixed order -> epilogue.
-      // The other warps do not wait: they hand their sums over through an mbarrier and go on.
-      const int buf = closes & 1;
-      const unsigned use = closes >> 1;
-      if (use > 0) {
-        if (!mbar_wait_bounded(sm.part_empty + buf, (use - 1u) & 1u, MK_MBAR_SPINS, sm.abort) && !*sm.abort)
-          *sm.abort = 5;
-      }
-      float* pw = sm.misc + MK_PART_OFF + ((size_t)buf * MK_CW + warp) * 32;
-      if ((lane & 3) == 0) {
-        pw[g] = acc.v[0];
-        pw[g + 8] = acc.v[1];
-        pw[16 + g] = acc2.v[0];
-        pw[16 + g + 8] = acc2.v[1];
-      }
-      acc.clear();
-      acc2.clear();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sm.part_full + buf);
-      if (warp == 0) {
-        if (!mbar_wait_bounded(sm.part_full + buf, use & 1u, MK_MBAR_SPINS, sm.abort) && !*sm.abort)
-          *sm.abort = 6;
-        if (lane < 16 && lane < n) {
-          const float* pb = sm.misc + MK_PART_OFF + (size_t)buf * MK_CW * 32 + lane;
-          float s0 = 0.f, s1 = 0.f;
+  // One phase's rounds, in program order.
+  auto run_phase = [&](int phase_index, unsigned ep, float out_scale) {
+    const int nr = sm.phase_rounds[phase_index];
+    for (int r = 0; r < nr; r++, ri++) {
+      const MegaRound R = sm.rounds[ri];
+      TileAcc<true> acc[MEGA_TA];
 #pragma unroll
-          for (int wv = 0; wv < MK_CW; wv++) {
-            s0 += pb[wv * 32];
-            s1 += pb[wv * 32 + 16];
+      for (int j = 0; j < MEGA_TA; j++) acc[j].clear();
+      for (int k = 0; k < (int)R.nchunks; k++, ci++) {
+        const MegaChunk* c = sm.chunks + ci;
+        const int slot = ci % sm.nslot;
+        const unsigned long long tw = prof.tic();
+        const bool ok = mbar_wait_bounded(sm.full + slot, (ci / sm.nslot) & 1u, MK_MBAR_SPINS, sm.abort);
+        if (!ok && !*sm.abort) *sm.abort = 3;
+        prof.toc(10, tw);
+        const unsigned long long tr = prof.tic();
+        if (ok) {
+          const int n = c->n, nu = c->nu;
+          const uint8_t* base = sm.ring + (size_t)slot * MK_SLOT;
+          const int i0 = g < n ? g : n - 1, i1 = g + 8 < n ? g + 8 : n - 1;  // clamp to valid rows
+          const uint32_t pitch = c->pitch, rb = c->rb;
+          const uint8_t* src = c->src;
+          const uint8_t* p0 = base + i0 * pitch + (reinterpret_cast<uintptr_t>(src + (size_t)i0 * rb) & 15);
+          const uint8_t* p1 = base + i1 * pitch + (reinterpret_cast<uintptr_t>(src + (size_t)i1 * rb) & 15);
+          const uint8_t* a0 = nullptr;
+          const uint8_t* a1 = nullptr;
+          const int apitch = c->apitch;
+          if (c->aseg) {
+            const uint8_t* ab = base + 16 * pitch;
+            a0 = ab + i0 * apitch + (reinterpret_cast<uintptr_t>(c->sc + (size_t)i0 * c->arb) & 15);
+            a1 = ab + i1 * apitch + (reinterpret_cast<uintptr_t>(c->sc + (size_t)i1 * c->arb) & 15);
           }
+          const int enc = c->enc, aux = c->aux, gs = c->group_shift, kb0 = c->kb0, which = c->acc;
+          TileAcc<true> t;
+          t.clear();
+          for (int u = warp; u < nu; u += MK_CW) run_unit(enc, aux, gs, p0, p1, a0, a1, 16 * apitch, u, kb0, sm, lane, t);
+#pragma unroll
+          for (int j = 0; j < MEGA_TA; j++)
+            if (which == j) {
+              acc[j].v[0] += t.v[0];
+              acc[j].v[1] += t.v[1];
+            }
+        }
+        prof.toc(11, tr);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.empty + slot);
+      }
+      // the sixteen K-slice partials of every tile of the round meet here, once
+      const unsigned long long tc = prof.tic();
+      float* pb = sm.misc + MK_OFF_PART + (nround & 1u) * MK_PART;
+      nround++;
+      if ((lane & 3) == 0) {
+#pragma unroll
+        for (int j = 0; j < MEGA_TA; j++)
+          if (j < (int)R.naccs) {
+            pb[(j * MK_CW + warp) * 16 + g] = acc[j].v[0];
+            pb[(j * MK_CW + warp) * 16 + g + 8] = acc[j].v[1];
+          }
+      }
+      consumer_sync();
+      const int nt = R.ntiles;
+      if (tid < nt * 16) {
+        const MegaTile T = sm.tiles[ti + (tid >> 4)];
+        const int row = tid & 15;
+        if (row < (int)T.n) {
+          const float* p1 = pb + (int)T.acc * MK_CW * 16 + row;
+          float s0 = 0.f;
+#pragma unroll
+          for (int wv = 0; wv < MK_CW; wv++) s0 += p1[wv * 16];
           s0 *= out_scale;
-          s1 *= out_scale;
-          const int ep = (flags >> 2) & 3;
-          const int64_t row = (int64_t)c->out_row + lane;
-          float* out = c->out;
-          if (ep == MEGA_EP_STORE) {
-            out[row] = s0;
-          } else if (ep == MEGA_EP_RESIDUAL) {
-            out[row] = resid + s0;
-          } else if (ep == MEGA_EP_SWIGLU) {
-            out[row] = (s0 / (1.0f + expf(-s0))) * s1;
+          const int64_t orow = (int64_t)T.out_row + row;
+          if (T.ep == MEGA_EP_QKV) {
+            ll_store(a.ll_qkv, orow, s0, ep);
+          } else if (T.ep == MEGA_EP_RESID_O || T.ep == MEGA_EP_RESID_DOWN) {
+            const float hnew = res[orow - hid_lo] + s0;
+            res[orow - hid_lo] = hnew;
+            ll_store(a.ll_hidden[T.ep == MEGA_EP_RESID_O ? 0 : 1], orow, hnew, ep);
+          } else if (T.ep == MEGA_EP_SWIGLU) {
+            const float* p2 = pb + (int)T.acc2 * MK_CW * 16 + row;
+            float s1 = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < MK_CW; wv++) s1 += p2[wv * 16];
+            s1 *= out_scale;
+            ll_store(a.ll_act, orow, (s0 / (1.0f + expf(-s0))) * s1, ep);
           } else {
-            out[row] = s0;
-            if (s0 > -INFINITY && arg_better(s0, row, bv, bi)) bv = s0, bi = row;
+            a.logits[orow] = s0;
+            if (s0 > -INFINITY && arg_better(s0, orow, bv, bi)) bv = s0, bi = orow;
           }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sm.part_empty + buf);
       }
-      closes++;
+      ti += nt;
+      prof.toc(12, tc);
     }
-  };
-
-  auto gsync = [&]() {
-    const unsigned long long t_ = prof.tic();
-    grid_sync(a, gb, G, tid, sm);
-    prof.toc(12, t_);
   };
 
   if (a.has_rope && tid < a.d / 2) {
     // the rotation of this token's position, shared by all layers (kernels.rs:1047-1064)
     float sv, cv;
     sincosf(__fmul_rn((float)pos, a.ft.f[tid]), &sv, &cv);
-    sm.misc[MK_ROPE_OFF + tid] = cv;
-    sm.misc[MK_ROPE_OFF + 128 + tid] = sv;
+    sm.misc[MK_OFF_ROPE + tid] = cv;
+    sm.misc[MK_OFF_ROPE + 64 + tid] = sv;
   }
-  if (cta == 0) mega_gather_row(a.embed, token, a.hidden, tid, MK_CT);
-  gsync();
+  // every CTA decodes the token's embedding row for itself: no hand-off before the first product
+  mega_gather_row(a.embed, token, sm.xs, tid, MK_CT);
+  consumer_sync();
+  {
+    const int hid_hi = (int)((int64_t)a.H * (cta + 1) / G);
+    for (int i = hid_lo + tid; i < hid_hi; i += MK_CT) res[i - hid_lo] = sm.xs[i];
+  }
   prof.mark(0);
 
+  StageSrc src;
+  src.nsplit = nsplit, src.max_split = a.max_split, src.d = a.d;
   for (int l = 0; l < a.layers; l++) {
     const MegaLayer* L = a.L + l;
+    const unsigned ep = a.epoch_base + 1u + (unsigned)l;
     unsigned long long ts = prof.tic();
-    out_scale = stage_phase(a.hidden, false, L->attn_norm, L->norm_type, a.H, a.eps,
-                            xl_for_encoding(L->q.enc), sm, tid, lane, warp);
+    src.kind = l == 0 ? SRC_XS : SRC_LL, src.ll = a.ll_hidden[1], src.ep = ep - 1u;
+    float out_scale = stage_phase(src, L->attn_norm, L->norm_type, a.H, a.eps, xl_for_encoding(L->q.enc), sm, tid,
+                                  lane, warp);
     prof.toc(9, ts);
-    run_phase(4 * l + 0);
-    gsync();
+    run_phase(4 * l + 0, ep, out_scale);
     prof.mark(1);
-    if (!*sm.abort) {
-      if (a.d <= 128)
-        phase_attention<4>(a, l, L, cta, pos, seq, nsplit, sm, tid, lane, warp, prof);
-      else
-        phase_attention<8>(a, l, L, cta, pos, seq, nsplit, sm, tid, lane, warp, prof);
-    }
-    gsync();
+    phase_attention(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
     prof.mark(2);
     ts = prof.tic();
-    if (nsplit > 1) {
-      for (int e = tid; e < qd; e += MK_CT) {
-        const int h = e / a.d, i = e - h * a.d;
-        const float* p0 = a.attn_part + (int64_t)h * a.max_split * (a.d + 2);
-        float pm[16], pl[16], po[16];
-#pragma unroll
-        for (int s = 0; s < 16; s++)
-          if (s < nsplit) {
-            const float* ps = p0 + s * (a.d + 2);
-            pm[s] = __ldcg(ps + a.d);
-            pl[s] = __ldcg(ps + a.d + 1);
-            po[s] = __ldcg(ps + i);
-          }
-        float gm = -3.40282347e38f;
-#pragma unroll
-        for (int s = 0; s < 16; s++)
-          if (s < nsplit) gm = fmaxf(gm, pm[s]);
-        float o = 0.f, gl = 0.f;
-#pragma unroll
-        for (int s = 0; s < 16; s++)
-          if (s < nsplit) {
-            const float wgt = expf(pm[s] - gm);
-            o += po[s] * wgt;
-            gl += pl[s] * wgt;
-          }
-        sm.xs[e] = o / gl;
-      }
-      consumer_sync();
-    }
-    out_scale = stage_phase(a.ctx, nsplit > 1, nullptr, 0, (int)qd, 0.f, xl_for_encoding(L->o.enc), sm,
-                            tid, lane, warp);
+    src.kind = nsplit > 1 ? SRC_PARTIALS : SRC_LL, src.ll = nsplit > 1 ? a.ll_part : a.ll_ctx, src.ep = ep;
+    out_scale = stage_phase(src, nullptr, 0, (int)qd, 0.f, xl_for_encoding(L->o.enc), sm, tid, lane, warp);
     prof.toc(9, ts);
-    run_phase(4 * l + 1);
-    gsync();
+    run_phase(4 * l + 1, ep, out_scale);
     prof.mark(3);
     ts = prof.tic();
-    out_scale = stage_phase(a.hidden, false, L->ffn_norm, L->norm_type, a.H, a.eps,
-                            xl_for_encoding(L->gate.enc), sm, tid, lane, warp);
+    src.kind = SRC_LL, src.ll = a.ll_hidden[0], src.ep = ep;
+    out_scale = stage_phase(src, L->ffn_norm, L->norm_type, a.H, a.eps, xl_for_encoding(L->gate.enc), sm, tid, lane,
+                            warp);
     prof.toc(9, ts);
-    run_phase(4 * l + 2);
-    gsync();
+    run_phase(4 * l + 2, ep, out_scale);
     prof.mark(4);
     ts = prof.tic();
-    out_scale = stage_phase(a.act, false, nullptr, 0, a.I, 0.f, xl_for_encoding(L->down.enc), sm, tid,
-                            lane, warp);
+    src.kind = SRC_LL, src.ll = a.ll_act, src.ep = ep;
+    out_scale = stage_phase(src, nullptr, 0, a.I, 0.f, xl_for_encoding(L->down.enc), sm, tid, lane, warp);
     prof.toc(9, ts);
-    run_phase(4 * l + 3);
-    gsync();
+    run_phase(4 * l + 3, ep, out_scale);
     prof.mark(5);
   }
 
-  // ---- final norm + lm_head + argmax partials (first strict maximum)
+  // ---- final norm + lm_head + argmax (first strict maximum)
+  const unsigned ep_last = a.epoch_base + (unsigned)a.layers;
   {
     const unsigned long long ts = prof.tic();
-    out_scale = stage_phase(a.hidden, false, a.out_norm, a.out_norm_type, a.H, a.eps,
-                            xl_for_encoding(a.lm_head.enc), sm, tid, lane, warp);
+    src.kind = a.layers > 0 ? SRC_LL : SRC_XS, src.ll = a.ll_hidden[1], src.ep = ep_last;
+    const float out_scale = stage_phase(src, a.out_norm, a.out_norm_type, a.H, a.eps, xl_for_encoding(a.lm_head.enc),
+                                        sm, tid, lane, warp);
     prof.toc(9, ts);
+    run_phase(4 * a.layers, ep_last + 1u, out_scale);
   }
-  run_phase(4 * a.layers);
-  if (warp == 0) {
+  {
+    // the (at most 128) finishing threads hold this CTA's candidates
+    float* cv = sm.misc + MK_OFF_AMAX;
+    if (tid < MEGA_TA * 16) {
+      cv[tid] = bv;
+      cv[128 + tid] = __int_as_float((int)(bi == 0x7fffffffffffffffLL ? 0x7fffffff : bi));
+    }
+    consumer_sync();
+    if (warp == 0) {
+      float v = -INFINITY;
+      long long i = 0x7fffffffffffffffLL;
+      for (int c = lane; c < MEGA_TA * 16; c += 32) {
+        const float ov = cv[c];
+        const int oi = __float_as_int(cv[128 + c]);
+        if (oi != 0x7fffffff && arg_better(ov, oi, v, i)) v = ov, i = oi;
+      }
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) {  // the 16 finalising threads are lanes 0..15 of warp 0
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (arg_better(ov, oi, bv, bi)) bv = ov, bi = oi;
-    }
-    if (lane == 0) {
-      a.argmax_val[cta] = bv;
-      a.argmax_idx[cta] = bi;
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const long long oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (arg_better(ov, oi, v, i)) v = ov, i = oi;
+      }
+      if (lane == 0) {
+        // one 16-byte line per CTA: (value, epoch), (row, epoch)
+        ll_store(a.ll_amax, 2 * (int64_t)cta, v, ep_last + 1u);
+        ll_store(a.ll_amax, 2 * (int64_t)cta + 1, __int_as_float((int)(i == 0x7fffffffffffffffLL ? 0x7fffffff : i)),
+                 ep_last + 1u);
+      }
     }
   }
-  gsync();
   prof.mark(6);
   if (cta == 0 && warp == 0) {
     float v = -INFINITY;
     long long i = 0x7fffffffffffffffLL;
     for (int c = lane; c < G; c += 32) {
-      const float cv = __ldcg(a.argmax_val + c);
-      const long long cidx = __ldcg(a.argmax_idx + c);
-      if (arg_better(cv, cidx, v, i)) v = cv, i = cidx;
+      const int64_t idx[1] = {2 * (int64_t)c};
+      float p[2];
+      ll_poll<1>(a.ll_amax, idx, ep_last + 1u, p, sm.abort);
+      const int oi = __float_as_int(p[1]);
+      if (oi != 0x7fffffff && arg_better(p[0], oi, v, i)) v = p[0], i = oi;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -902,27 +934,20 @@ size_t mega_smem_bytes(int nslot, int xs_floats, size_t prog_bytes) {
          (size_t)MK_MISC_FLOATS * 4 + (size_t)nslot * MK_SLOT + (size_t)nslot * 16 + 128 + prog_bytes;
 }
 
-// prog_bytes: bytes of one CTA's program (chunks + counts, 16-byte rounded) to keep in shared
-// memory; *prog_in_smem tells whether it fit beside a ring of at least 5 slots.
-int mega_plan(int H, int I, int qd, int d, size_t prog_bytes, int* nslot, int* xs_floats, size_t* smem,
-              int* prog_in_smem) {
+// prog_bytes: bytes of one CTA's program blob, which lives in shared memory beside the ring.
+int mega_plan(int H, int I, int qd, int d, size_t prog_bytes, int* nslot, int* xs_floats, size_t* smem) {
   int xs = H > I ? H : I;
   if (qd > xs) xs = qd;
   xs = (xs + 255) / 256 * 256;
-  if (d > 256 || xs > 8 * MK_CT) return 0;  // staging: one 8-element item per consumer thread
+  if ((d != 64 && d != 128) || H % 32 || I % 32 || qd % 32) return 0;
   const size_t budget = 225 * 1024;
-  size_t fixed = mega_smem_bytes(0, xs, 0) + 512;
-  if (fixed + 4 * (size_t)MK_SLOT > budget) return 0;
-  *prog_in_smem = 0;
-  if (prog_bytes && fixed + prog_bytes + 5 * (size_t)(MK_SLOT + 16) <= budget) {
-    *prog_in_smem = 1;
-    fixed += prog_bytes;
-  }
+  const size_t fixed = mega_smem_bytes(0, xs, prog_bytes) + 512;
+  if (fixed + 4 * (size_t)(MK_SLOT + 16) > budget) return 0;
   int n = (int)((budget - fixed) / (MK_SLOT + 16));
   if (n > 12) n = 12;
   *nslot = n;
   *xs_floats = xs;
-  *smem = mega_smem_bytes(n, xs, *prog_in_smem ? prog_bytes : 0);
+  *smem = mega_smem_bytes(n, xs, prog_bytes);
   return 1;
 }
 
@@ -950,113 +975,166 @@ HostPlan host_plan(const WRef& w) {
 }
 int seg_bytes(const HostPlan& p, int nu) { return p.unit_q6 ? (nu / 4) * 210 : nu * p.ubytes; }
 
-// Appends the chunks of rows [lo, hi) of `w`: tiles of 16 rows, each cut into the fewest K-slices
-// whose rows fit one ring slot (slices are multiples of 16 units so the 16 consumer warps share
-// them evenly; Q6_K slices are whole groups of 4 superblocks, which keeps rows 8-byte aligned).
-void add_tensor_chunks(const WRef& w, int64_t lo, int64_t hi, float* out, int ep, bool second,
-                       bool closes, std::vector<MegaChunk>* v) {
+// Appends the chunks of rows [r, r + n) (n <= 16) of `w`, summed into accumulator `acc`: the
+// fewest K-slices whose rows fit one ring slot (slices are multiples of 16 units so the 16
+// consumer warps share them evenly; Q6_K slices are whole groups of 4 superblocks, which keeps
+// rows 8-byte aligned).
+void add_tile_chunks(const WRef& w, int64_t r, int n, int acc, std::vector<MegaChunk>* v) {
   const HostPlan p = host_plan(w);
   const int ael = w.aux == E_F32 ? 4 : 2;
-  for (int64_t r = lo; r < hi; r += 16) {
-    const int n = (int)std::min<int64_t>(16, hi - r);
-    // largest slice (multiple of 16 units) whose rows fit one slot; only valid rows are copied
-    int su = p.units_total < 16 ? p.units_total : 16;
-    for (int cand = 16; cand <= p.units_total && cand <= 240; cand += 16) {
-      const int pitch = host_bank_pitch(seg_bytes(p, cand) + 20);
-      const int ap = w.enc == E_MLX_U4 ? ((cand * 32 / w.group) * ael + 31) / 16 * 16 : 0;
-      const size_t need = ap ? (size_t)16 * pitch + 32 * (size_t)ap : (size_t)n * pitch;
-      if (need <= (size_t)MK_SLOT && pitch < 65536) su = cand;
+  // largest slice (multiple of 16 units) whose rows fit one slot; only valid rows are copied
+  int su = p.units_total < 16 ? p.units_total : 16;
+  for (int cand = 16; cand <= p.units_total && cand <= 240; cand += 16) {
+    const int pitch = host_bank_pitch(seg_bytes(p, cand) + 20);
+    const int ap = w.enc == E_MLX_U4 ? ((cand * 32 / w.group) * ael + 31) / 16 * 16 : 0;
+    const size_t need = ap ? (size_t)16 * pitch + 32 * (size_t)ap : (size_t)n * pitch;
+    if (need <= (size_t)MK_SLOT && pitch < 65536) su = cand;
+  }
+  const int nsl = (p.units_total + su - 1) / su;
+  for (int sl = 0; sl < nsl; sl++) {
+    const int u0 = sl * su, nu = std::min(su, p.units_total - u0);
+    MegaChunk c{};
+    const int64_t boff = p.unit_q6 ? (int64_t)(u0 / 4) * 210 : (int64_t)u0 * p.ubytes;
+    c.src = w.data + r * w.row_bytes() + boff;
+    c.rb = (uint32_t)w.row_bytes();
+    c.seg = (uint16_t)seg_bytes(p, nu);
+    c.pitch = (uint16_t)host_bank_pitch(seg_bytes(p, su) + 20);
+    c.kb0 = (uint16_t)(u0 * p.ukb);
+    c.n = (uint8_t)n;
+    c.nu = (uint8_t)nu;
+    c.enc = (uint8_t)w.enc;
+    c.acc = (uint8_t)acc;
+    if (w.enc == E_MLX_U4) {
+      const int64_t arow = (int64_t)(w.cols / w.group) * ael, ao = (int64_t)(u0 * 32 / w.group) * ael;
+      c.sc = w.scales + r * arow + ao;
+      c.bi = w.biases + r * arow + ao;
+      c.arb = (uint32_t)arow;
+      c.aseg = (uint16_t)((nu * 32 / w.group) * ael);
+      c.apitch = (uint16_t)(((su * 32 / w.group) * ael + 31) / 16 * 16);
+      c.aux = (uint8_t)w.aux;
+      c.group_shift = (uint8_t)(w.group == 32 ? 0 : (w.group == 64 ? 1 : 2));
     }
-    const int nsl = (p.units_total + su - 1) / su;
-    for (int sl = 0; sl < nsl; sl++) {
-      const int u0 = sl * su, nu = std::min(su, p.units_total - u0);
-      MegaChunk c{};
-      const int64_t boff = p.unit_q6 ? (int64_t)(u0 / 4) * 210 : (int64_t)u0 * p.ubytes;
-      c.src = w.data + r * w.row_bytes() + boff;
-      c.rb = (uint32_t)w.row_bytes();
-      c.seg = (uint16_t)seg_bytes(p, nu);
-      c.pitch = (uint16_t)host_bank_pitch(seg_bytes(p, su) + 20);
-      c.kb0 = (uint16_t)(u0 * p.ukb);
-      c.n = (uint8_t)n;
-      c.nu = (uint8_t)nu;
-      c.enc = (uint8_t)w.enc;
-      c.out = out;
-      c.out_row = (int32_t)r;
-      c.flags = (uint8_t)(((closes && sl == nsl - 1) ? 1 : 0) | (second ? 2 : 0) | (ep << 2));
-      if (w.enc == E_MLX_U4) {
-        const int64_t arow = (int64_t)(w.cols / w.group) * ael, ao = (int64_t)(u0 * 32 / w.group) * ael;
-        c.sc = w.scales + r * arow + ao;
-        c.bi = w.biases + r * arow + ao;
-        c.arb = (uint32_t)arow;
-        c.aseg = (uint16_t)((nu * 32 / w.group) * ael);
-        c.apitch = (uint16_t)(((su * 32 / w.group) * ael + 31) / 16 * 16);
-        c.aux = (uint8_t)w.aux;
-        c.group_shift = (uint8_t)(w.group == 32 ? 0 : (w.group == 64 ? 1 : 2));
-      }
-      v->push_back(c);
-    }
+    v->push_back(c);
   }
 }
+
+struct CtaProgram {
+  std::vector<MegaChunk> chunks;
+  std::vector<MegaTile> tiles;
+  std::vector<MegaRound> rounds;
+  std::vector<uint16_t> phase_rounds;
+  // the round being filled
+  int accs = 0;
+  bool open = false;
+  void begin_phase() {
+    phase_rounds.push_back(0);
+    open = false;
+  }
+  void need(int naccs) {
+    if (!open || accs + naccs > MEGA_TA) {
+      rounds.push_back(MegaRound{0, 0, 0});
+      phase_rounds.back()++;
+      accs = 0;
+      open = true;
+    }
+  }
+  // rows [lo, hi) of w (and of w2 for SwiGLU pairs), output rows out_off + row
+  void add_rows(const WRef& w, const WRef* w2, int64_t lo, int64_t hi, int64_t out_off, int ep) {
+    for (int64_t r = lo; r < hi; r += 16) {
+      const int n = (int)std::min<int64_t>(16, hi - r);
+      need(w2 ? 2 : 1);
+      MegaTile t{};
+      t.out_row = (int32_t)(out_off + r), t.n = (uint8_t)n, t.ep = (uint8_t)ep;
+      t.acc = (uint8_t)accs, t.acc2 = (uint8_t)(w2 ? accs + 1 : 0);
+      const size_t before = chunks.size();
+      add_tile_chunks(w, r, n, accs, &chunks);
+      if (w2) add_tile_chunks(*w2, r, n, accs + 1, &chunks);
+      accs += w2 ? 2 : 1;
+      rounds.back().naccs = (uint8_t)accs;
+      tiles.push_back(t);
+      rounds.back().nchunks = (uint16_t)(rounds.back().nchunks + (chunks.size() - before));
+      rounds.back().ntiles++;
+    }
+  }
+};
 }  // namespace
 
 int mega_build_program(const MegaBuildLayer* layers, int nlayers, const WRef& lm_head, int nh, int nkv,
-                       int d, int H, int I, int V, float* q, float* k, float* v, float* hidden,
-                       float* act, float* logits, int grid, std::vector<MegaChunk>* chunks,
-                       std::vector<uint16_t>* counts, int* max_chunks) {
+                       int d, int H, int I, int V, int grid, std::vector<uint8_t>* blob, MegaProgLayout* lay) {
   const int nph = 4 * nlayers + 1;
-  std::vector<std::vector<MegaChunk>> per(grid);
-  counts->assign((size_t)grid * nph, 0);
+  std::vector<CtaProgram> per(grid);
   const int64_t qd = (int64_t)nh * d, kvd = (int64_t)nkv * d;
   for (int cta = 0; cta < grid; cta++) {
-    std::vector<MegaChunk>& pc = per[cta];
-    auto close_phase = [&](int ph, size_t before) {
-      (*counts)[(size_t)cta * nph + ph] = (uint16_t)(pc.size() - before);
-    };
+    CtaProgram& pc = per[cta];
+    const int64_t h0 = (int64_t)H * cta / grid, h1 = (int64_t)H * (cta + 1) / grid;
+    DYN_CHECK(h1 - h0 <= MK_MAX_OWNED, "persistent decode kernel: %lld hidden rows per CTA exceed %d",
+              (long long)(h1 - h0), MK_MAX_OWNED);
     for (int l = 0; l < nlayers; l++) {
       const MegaBuildLayer& L = layers[l];
-      size_t b0 = pc.size();
+      pc.begin_phase();
       {  // q, k, v share one balanced split of their concatenated rows
         const int64_t R = qd + 2 * kvd, a0 = R * cta / grid, a1 = R * (cta + 1) / grid;
         const int64_t offs[3] = {0, qd, qd + kvd}, lens[3] = {qd, kvd, kvd};
         const WRef* ws[3] = {&L.q, &L.k, &L.v};
-        float* outs[3] = {q, k, v};
         for (int t = 0; t < 3; t++) {
           const int64_t lo = std::max(a0, offs[t]) - offs[t], hi = std::min(a1, offs[t] + lens[t]) - offs[t];
-          if (hi > lo) add_tensor_chunks(*ws[t], lo, hi, outs[t], MEGA_EP_STORE, false, true, &pc);
+          if (hi > lo) pc.add_rows(*ws[t], nullptr, lo, hi, offs[t], MEGA_EP_QKV);
         }
       }
-      close_phase(4 * l + 0, b0);
-      b0 = pc.size();
-      add_tensor_chunks(L.o, (int64_t)H * cta / grid, (int64_t)H * (cta + 1) / grid, hidden, MEGA_EP_RESIDUAL,
-                        false, true, &pc);
-      close_phase(4 * l + 1, b0);
-      b0 = pc.size();
-      {  // per tile: gate slices, then up slices into the second accumulator; the pair closes after up
-        const int64_t lo = (int64_t)I * cta / grid, hi = (int64_t)I * (cta + 1) / grid;
-        for (int64_t r = lo; r < hi; r += 16) {
-          const int64_t e = std::min(r + 16, hi);
-          add_tensor_chunks(L.gate, r, e, act, MEGA_EP_SWIGLU, false, false, &pc);
-          add_tensor_chunks(L.up, r, e, act, MEGA_EP_SWIGLU, true, true, &pc);
-        }
-      }
-      close_phase(4 * l + 2, b0);
-      b0 = pc.size();
-      add_tensor_chunks(L.down, (int64_t)H * cta / grid, (int64_t)H * (cta + 1) / grid, hidden,
-                        MEGA_EP_RESIDUAL, false, true, &pc);
-      close_phase(4 * l + 3, b0);
+      pc.begin_phase();
+      pc.add_rows(L.o, nullptr, h0, h1, 0, MEGA_EP_RESID_O);
+      pc.begin_phase();
+      pc.add_rows(L.gate, &L.up, (int64_t)I * cta / grid, (int64_t)I * (cta + 1) / grid, 0, MEGA_EP_SWIGLU);
+      pc.begin_phase();
+      pc.add_rows(L.down, nullptr, h0, h1, 0, MEGA_EP_RESID_DOWN);
     }
-    const size_t b0 = pc.size();
-    add_tensor_chunks(lm_head, (int64_t)V * cta / grid, (int64_t)V * (cta + 1) / grid, logits, MEGA_EP_LOGITS,
-                      false, true, &pc);
-    close_phase(4 * nlayers, b0);
+    pc.begin_phase();
+    pc.add_rows(lm_head, nullptr, (int64_t)V * cta / grid, (int64_t)V * (cta + 1) / grid, 0, MEGA_EP_LOGITS);
   }
-  size_t mc = 1;
-  for (auto& pc : per) mc = std::max(mc, pc.size());
-  DYN_CHECK(mc < 60000, "decode program too long (%zu chunks per CTA)", mc);
-  *max_chunks = (int)mc;
-  chunks->assign((size_t)grid * mc, MegaChunk{});
-  for (int cta = 0; cta < grid; cta++)
-    std::copy(per[cta].begin(), per[cta].end(), chunks->begin() + (size_t)cta * mc);
+  // every output row of every phase is produced exactly once, by a tile of at most 16 rows
+  {
+    std::vector<int64_t> rows((size_t)nph, 0);
+    for (auto& pc : per) {
+      size_t ti = 0, ri = 0;
+      DYN_CHECK((int)pc.phase_rounds.size() == nph, "decode program: phase count mismatch");
+      for (int ph = 0; ph < nph; ph++)
+        for (int r = 0; r < pc.phase_rounds[ph]; r++, ri++) {
+          DYN_CHECK(pc.rounds[ri].naccs <= MEGA_TA && pc.rounds[ri].ntiles <= MEGA_TA, "decode program: round too wide");
+          for (int t = 0; t < pc.rounds[ri].ntiles; t++, ti++) {
+            DYN_CHECK(pc.tiles[ti].n >= 1 && pc.tiles[ti].n <= 16, "decode program: bad tile");
+            rows[ph] += pc.tiles[ti].n;
+          }
+        }
+    }
+    for (int l = 0; l < nlayers; l++)
+      DYN_CHECK(rows[4 * l] == qd + 2 * kvd && rows[4 * l + 1] == H && rows[4 * l + 2] == I && rows[4 * l + 3] == H,
+                "decode program: layer %d rows are not covered exactly once", l);
+    DYN_CHECK(rows[4 * nlayers] == V, "decode program: lm_head rows are not covered exactly once");
+  }
+  size_t mc = 1, mt = 1, mr = 1;
+  for (auto& pc : per) {
+    mc = std::max(mc, pc.chunks.size());
+    mt = std::max(mt, pc.tiles.size());
+    mr = std::max(mr, pc.rounds.size());
+  }
+  DYN_CHECK(mc < 60000 && mr < 60000, "decode program too long (%zu chunks per CTA)", mc);
+  lay->max_chunks = (int)mc, lay->max_tiles = (int)mt, lay->max_rounds = (int)mr, lay->nph = nph;
+  lay->off_tiles = sizeof(MegaProgHeader) + mc * sizeof(MegaChunk);
+  lay->off_rounds = lay->off_tiles + mt * sizeof(MegaTile);
+  lay->off_phase = lay->off_rounds + mr * sizeof(MegaRound);
+  lay->bytes = (lay->off_phase + (size_t)nph * 2 + 15) / 16 * 16;
+  blob->assign((size_t)grid * lay->bytes, 0);
+  for (int cta = 0; cta < grid; cta++) {
+    const CtaProgram& pc = per[cta];
+    uint8_t* b = blob->data() + (size_t)cta * lay->bytes;
+    MegaProgHeader h{(uint32_t)pc.chunks.size(), (uint32_t)pc.tiles.size(), (uint32_t)pc.rounds.size(),
+                     (uint32_t)((int64_t)H * cta / grid)};
+    memcpy(b, &h, sizeof h);
+    if (!pc.chunks.empty()) memcpy(b + sizeof h, pc.chunks.data(), pc.chunks.size() * sizeof(MegaChunk));
+    if (!pc.tiles.empty()) memcpy(b + lay->off_tiles, pc.tiles.data(), pc.tiles.size() * sizeof(MegaTile));
+    if (!pc.rounds.empty()) memcpy(b + lay->off_rounds, pc.rounds.data(), pc.rounds.size() * sizeof(MegaRound));
+    memcpy(b + lay->off_phase, pc.phase_rounds.data(), pc.phase_rounds.size() * 2);
+  }
   return 0;
 }
 
@@ -1073,8 +1151,7 @@ bool mega_supports_weight(const WRef& w) {
 }
 
 int mega_grid_size(int device, size_t smem, int* grid) {
-  DYN_CUDA(cudaFuncSetAttribute(decode_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)smem));
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(decode_mega_kernel), (int)smem)) return 1;
   int sms = 0, per_sm = 0, coop = 0;
   DYN_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
   DYN_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));

@@ -459,7 +459,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)a.tmem_cols)
                  : "memory");
   }
-  if (tid == 0 && s_abort) atomicExch(a.error, s_abort);
+  if (tid == 0 && s_abort) report_wait_expired(a.error, DEV_ERR_GEMM_PIPE);
 }
 
 bool tg_shape_ok(const WRef& w, int64_t M) {
@@ -516,14 +516,31 @@ tg_split_reduce_kernel(const float* __restrict__ partial, int splits, int64_t co
 
 template <int ENC>
 int tg_launch(const TgArgs& a, const CUtensorMap& xmap, dim3 grid, size_t smem, cudaStream_t s) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    DYN_CUDA(cudaFuncSetAttribute(dqgemm_tc_kernel<ENC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr_done = true;
-  }
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(dqgemm_tc_kernel<ENC>), 200 * 1024)) return 1;
   dqgemm_tc_kernel<ENC><<<grid, TG_THREADS, smem, s>>>(a, xmap);
   return 0;
 }
+
+// Scratch of one product: the caller's region when it is large enough (a session's own scratch:
+// no allocation nodes inside a captured step), else the stream-ordered allocator. Freed on every
+// path by the destructor.
+struct TgScratch {
+  uint8_t* ptr = nullptr;
+  bool pooled = false;
+  cudaStream_t s;
+  explicit TgScratch(cudaStream_t st) : s(st) {}
+  int take(size_t bytes) {
+    ptr = reinterpret_cast<uint8_t*>(thread_scratch(bytes));
+    if (ptr) return 0;
+    if (keep_scratch_pool_cached()) return 1;
+    DYN_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&ptr), bytes, s));
+    pooled = true;
+    return 0;
+  }
+  ~TgScratch() {
+    if (pooled && ptr) cudaFreeAsync(ptr, s);
+  }
+};
 
 }  // namespace
 
@@ -533,45 +550,41 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
   *handled = false;
   if (!tg_shape_ok(w, M)) return 0;
   const int64_t K = w.cols;
+  const int sms = std::max(1, sm_count());
   // activation rows per CTA: as many as fit one accumulator (256), rounded up to the MMA granule
   // ... unless that leaves most SMs idle (few weight-row tiles): then narrower activation tiles, down
   // to 32 rows, so that more CTAs share the work (each re-dequantises its weight tile, which is
   // cheap next to idle SMs)
   const int64_t ntiles = (w.rows + TG_BM - 1) / TG_BM;
   int64_t cap_rows = 256;
-  while (cap_rows > 32 && ntiles * ((M + cap_rows / 2 - 1) / (cap_rows / 2)) <= 148) cap_rows /= 2;  // stay within one wave
+  while (cap_rows > 32 && ntiles * ((M + cap_rows / 2 - 1) / (cap_rows / 2)) <= sms) cap_rows /= 2;  // stay within one wave
   const int64_t mtiles = (M + cap_rows - 1) / cap_rows;
   int bn = (int)((M + mtiles - 1) / mtiles);
   bn = (bn + 15) / 16 * 16;
   const int64_t Mpad = mtiles * bn;
   int cols = 32;
   while (cols < bn) cols *= 2;
-  if (keep_scratch_pool_cached()) return 1;
-  uint8_t* ws = nullptr;
+  // few tiles: split K as well, at least 4 chunks (256 elements) per CTA, at most 8 ways
+  const int nk_all = (int)(K / TG_BK);
+  int splits = 1;
+  while (splits < 8 && ntiles * mtiles * (splits * 2) <= sms && nk_all / (splits * 2) >= 4) splits *= 2;
+  const int nk_split = (nk_all + splits - 1) / splits;
+  splits = (nk_all + nk_split - 1) / nk_split;
   const size_t xh_bytes = ((size_t)Mpad * K * 2 + 255) / 256 * 256;
   const size_t inv_bytes = ((size_t)Mpad * 4 + 255) / 256 * 256;
-  DYN_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&ws), xh_bytes + inv_bytes + 256, s));
-  __half* xh = reinterpret_cast<__half*>(ws);
-  float* inv_s = reinterpret_cast<float*>(ws + xh_bytes);
-  int* err = reinterpret_cast<int*>(ws + xh_bytes + inv_bytes);
-  DYN_CUDA(cudaMemsetAsync(err, 0, 4, s));
+  const size_t part_bytes = splits > 1 ? (size_t)splits * M * w.rows * 4 : 0;
+  TgScratch ws(s);
+  if (ws.take(xh_bytes + inv_bytes + part_bytes)) return 1;
+  __half* xh = reinterpret_cast<__half*>(ws.ptr);
+  float* inv_s = reinterpret_cast<float*>(ws.ptr + xh_bytes);
+  float* partial = splits > 1 ? reinterpret_cast<float*>(ws.ptr + xh_bytes + inv_bytes) : nullptr;
+  int* err = device_error_word();
+  if (!err) return 1;
   tg_prepare_x_kernel<<<(unsigned)Mpad, 256, 0, s>>>(x, x_type == E_BF16 ? 1 : 0, M, K, xh, inv_s);
   TgArgs a;
   a.w = w, a.xh = xh, a.inv_s = inv_s, a.M = M, a.bn = bn, a.tmem_cols = cols, a.y = y, a.residual = residual, a.error = err;
   CUtensorMap xmap;
-  if (tg_make_xmap(xh, Mpad, K, bn, &xmap)) {
-    cudaFreeAsync(ws, s);
-    return 1;
-  }
-  // few tiles: split K as well, at least 4 chunks (256 elements) per CTA, at most 8 ways
-  const int nk_all = (int)(K / TG_BK);
-  int splits = 1;
-  while (splits < 8 && ntiles * mtiles * (splits * 2) <= 148 && nk_all / (splits * 2) >= 4) splits *= 2;
-  const int nk_split = (nk_all + splits - 1) / splits;
-  splits = (nk_all + nk_split - 1) / nk_split;
-  float* partial = nullptr;
-  if (splits > 1)
-    DYN_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&partial), (size_t)splits * M * w.rows * 4, s));
+  if (tg_make_xmap(xh, Mpad, K, bn, &xmap)) return 1;
   a.nk_split = nk_split, a.partial = partial;
   const dim3 grid((unsigned)((w.rows + TG_BM - 1) / TG_BM), (unsigned)mtiles, (unsigned)splits);
   const size_t stage_b = TG_A_BYTES + (size_t)bn * 128;
@@ -590,20 +603,14 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
     case E_BF16: rc = tg_launch<E_BF16>(a, xmap, grid, smem, s); break;
     default: break;
   }
+  if (rc) return rc;
   count_launch(2);
   if (splits > 1) {
-    if (!rc) {
-      const int64_t count = M * w.rows;
-      tg_split_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, s>>>(partial, splits, count, y, residual);
-      count_launch();
-    }
-    cudaFreeAsync(partial, s);
+    const int64_t count = M * w.rows;
+    tg_split_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, s>>>(partial, splits, count, y, residual);
+    count_launch();
   }
-  cudaError_t e = cudaGetLastError();
-  cudaError_t e2 = cudaFreeAsync(ws, s);
-  if (rc) return rc;
-  if (e != cudaSuccess) return cuda_fail(e, "dqgemm_tc launch", __FILE__, __LINE__);
-  if (e2 != cudaSuccess) return cuda_fail(e2, "cudaFreeAsync", __FILE__, __LINE__);
+  DYN_CUDA(cudaGetLastError());
   *handled = true;
   return 0;
 }

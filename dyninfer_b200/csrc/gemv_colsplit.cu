@@ -177,7 +177,6 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
   // The weights do not depend on the kernels before this one: the first stages are already in
   // flight. Everything else (the activation row, the scratch words) does.
   pdl_wait();
-  if (blockIdx.x == 0 && threadIdx.x == 0) *a.error = 0;  // a wait that runs out (seconds later) sets it
   // while the first stages are in flight: arrange the activation row in shared memory
   const float out_scale =
       cs_stage_x(a.x, a.x_bf16, a.K, reinterpret_cast<uint2*>(xq), sx8, red, ENC == E_Q4_0 ? 8.0f : 1.0f);
@@ -194,7 +193,7 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
       if (!mbar_wait_bounded_sleepy(bars + slot, parity, CS_SPINS, &s_abort, 2000u)) {
         if (!s_abort) {
           s_abort = 1;
-          atomicExch(a.error, 1);
+          report_wait_expired(a.error, DEV_ERR_GEMV_RING);
         }
         return;  // warp-uniform: every lane polls the same barrier
       }
@@ -329,7 +328,8 @@ bool cs_shape_ok(const WRef& w, int M) {
 void cs_plan(const WRef& w, CsPlan* p) {
   const int K = (int)w.cols, stages = K / CS_KSTAGE;
   p->ntiles = (int)((w.rows + 15) / 16);
-  const int64_t warps = 148 * CS_WARPS;
+  const int sms = std::max(1, sm_count());
+  const int64_t warps = (int64_t)sms * CS_WARPS;
   // split K while there are fewer than ~8 items per warp and slices keep >= 1 stage
   int S = 1;
   for (int cand = 1; cand <= stages; cand++) {
@@ -340,9 +340,9 @@ void cs_plan(const WRef& w, CsPlan* p) {
   p->S = S;
   p->nst = stages / S;
   const int64_t items = (int64_t)p->ntiles * S;
-  p->grid = (int)std::min<int64_t>(148, (items + CS_WARPS - 1) / CS_WARPS);
+  p->grid = (int)std::min<int64_t>(sms, (items + CS_WARPS - 1) / CS_WARPS);
   p->smem = cs_smem_bytes(w.enc, K);
-  p->off_err = 0;       // [0] error word, [64] 2^24 / scale
+  p->off_err = 0;       // [64] 2^24 / scale
   p->off_part = 256;
   p->bytes = 256 + (S > 1 ? (size_t)S * w.rows * 4 : 0);
 }
@@ -382,16 +382,15 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
   a.data = w.data, a.N = w.rows, a.rb = w.row_bytes(), a.K = (int)w.cols;
   a.S = p.S, a.nst = p.nst, a.ntiles = p.ntiles;
   a.x = x, a.x_bf16 = x_type == E_BF16 ? 1 : 0;
-  a.error = reinterpret_cast<int*>(ws + p.off_err);
+  a.error = device_error_word();
+  if (!a.error) return 1;
   a.misc = reinterpret_cast<float*>(ws + p.off_err + 64);
   a.partial = reinterpret_cast<float*>(ws + p.off_part);
   a.y = y, a.residual = residual;
-  static bool attr_done = false;
-  if (!attr_done) {
-    DYN_CUDA(cudaFuncSetAttribute(gemv_cs_q4_kernel<E_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, CS_MAX_SMEM));
-    DYN_CUDA(cudaFuncSetAttribute(gemv_cs_q4_kernel<E_Q4_1>, cudaFuncAttributeMaxDynamicSharedMemorySize, CS_MAX_SMEM));
-    attr_done = true;
-  }
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(w.enc == E_Q4_0 ? gemv_cs_q4_kernel<E_Q4_0>
+                                                                       : gemv_cs_q4_kernel<E_Q4_1>),
+                          CS_MAX_SMEM))
+    return 1;
   if (w.enc == E_Q4_0)
     DYN_CUDA(launch_pdl(gemv_cs_q4_kernel<E_Q4_0>, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a));
   else

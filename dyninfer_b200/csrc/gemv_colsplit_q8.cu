@@ -134,7 +134,6 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 1) gemv_cs_q8_0_kernel(const Q8
   // the weights do not depend on the kernels before this one (their first stages are in flight);
   // the activation row and the scratch words do
   pdl_wait();
-  if (blockIdx.x == 0 && threadIdx.x == 0) *a.error = 0;
   const float out_scale = q8_stage_x(a.x, a.x_bf16, a.K, xhi, xlo, sx, red);
   if (blockIdx.x == 0 && threadIdx.x == 0) a.misc[0] = out_scale;
   __syncthreads();
@@ -149,7 +148,7 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 1) gemv_cs_q8_0_kernel(const Q8
       if (!mbar_wait_bounded_sleepy(bars + slot, parity, Q8_SPINS, &s_abort, 2000u)) {
         if (!s_abort) {
           s_abort = 1;
-          atomicExch(a.error, 1);
+          report_wait_expired(a.error, DEV_ERR_GEMV_RING);
         }
         return;
       }
@@ -257,7 +256,8 @@ struct Q8Plan {
 void q8_plan(const WRef& w, Q8Plan* p) {
   const int K = (int)w.cols, stages = K / Q8_KSTAGE;
   p->ntiles = (int)((w.rows + 15) / 16);
-  const int64_t warps = 148 * Q8_WARPS;
+  const int sms = std::max(1, sm_count());
+  const int64_t warps = (int64_t)sms * Q8_WARPS;
   int S = 1;
   for (int cand = 1; cand <= stages; cand++) {
     if (stages % cand) continue;
@@ -267,7 +267,7 @@ void q8_plan(const WRef& w, Q8Plan* p) {
   p->S = S;
   p->nst = stages / S;
   const int64_t items = (int64_t)p->ntiles * S;
-  p->grid = (int)std::min<int64_t>(148, (items + Q8_WARPS - 1) / Q8_WARPS);
+  p->grid = (int)std::min<int64_t>(sms, (items + Q8_WARPS - 1) / Q8_WARPS);
   p->smem = q8_smem_bytes(K);
   p->bytes = 256 + (S > 1 ? (size_t)S * w.rows * 4 : 0);
 }
@@ -294,15 +294,12 @@ int launch_gemv_cs_q8_0(const WRef& w, const void* x, int x_type, float* y, cons
   a.data = w.data, a.N = w.rows, a.rb = w.row_bytes(), a.K = (int)w.cols;
   a.S = p.S, a.nst = p.nst, a.ntiles = p.ntiles;
   a.x = x, a.x_bf16 = x_type == E_BF16 ? 1 : 0;
-  a.error = reinterpret_cast<int*>(ws);
+  a.error = device_error_word();
+  if (!a.error) return 1;
   a.misc = reinterpret_cast<float*>(ws + 64);
   a.partial = reinterpret_cast<float*>(ws + 256);
   a.y = y, a.residual = residual;
-  static bool attr_done = false;
-  if (!attr_done) {
-    DYN_CUDA(cudaFuncSetAttribute(gemv_cs_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q8_MAX_SMEM));
-    attr_done = true;
-  }
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(gemv_cs_q8_0_kernel), Q8_MAX_SMEM)) return 1;
   DYN_CUDA(launch_pdl(gemv_cs_q8_0_kernel, dim3(p.grid), dim3(Q8_WARPS * 32), p.smem, s, a));
   count_launch(1);
   if (p.S > 1) {

@@ -314,7 +314,8 @@ void plan_shape(const WRef& w, int M, bool bf16, Shape* sh) {
   if (w.enc == E_Q6_K) unit = 32;
   if (w.enc == E_MLX_U4) unit = w.group / 32;
   int S = 1;
-  while (S < 16 && (int64_t)sh->ntiles * S < 148 * 16 && kb_total / (S * 2) >= 8 * unit) S *= 2;
+  const int sms = std::max(1, sm_count());
+  while (S < 16 && (int64_t)sh->ntiles * S < (int64_t)sms * 16 && kb_total / (S * 2) >= 8 * unit) S *= 2;
   int per = (kb_total + S - 1) / S;
   per = (per + unit - 1) / unit * unit;
   sh->kb_per = per;
@@ -350,12 +351,7 @@ int run_gemv(const WRef& w, const void* x, int x_bf16, int M, float* y, const fl
   XView xv{xf, sx16, sx32, inv_s};
   const int64_t units = (int64_t)sh.ntiles * sh.S;
   constexpr int tile_smem = GT_WARPS * 16 * UG<ENC>::PITCH;
-  static bool attr_done = false;
-  if (!attr_done) {
-    DYN_CUDA(cudaFuncSetAttribute(gemv_tile_kernel<ENC, NCOL, HILO>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, tile_smem));
-    attr_done = true;
-  }
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(gemv_tile_kernel<ENC, NCOL, HILO>), tile_smem)) return 1;
   gemv_tile_kernel<ENC, NCOL, HILO><<<(unsigned)((units + GT_WARPS - 1) / GT_WARPS), GT_WARPS * 32, tile_smem, s>>>(
       w, xv, M, y, residual, partial, sh.S, sh.kb_per, sh.ntiles);
   count_launch(2);

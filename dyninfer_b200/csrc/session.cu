@@ -94,15 +94,12 @@ struct dyninfer_cuda_session_t {
   size_t mega_smem = 0;
   MegaLayer* mega_layers = nullptr;
   int64_t* io_dev = nullptr;  // [0] token [1] position [2] slot [3] produced token [4] error word
-  unsigned long long* bar_dev = nullptr;
-  float* attn_part = nullptr;
-  float* amax_val = nullptr;
-  long long* amax_idx = nullptr;
   unsigned long long* prof_dev = nullptr;
-  MegaChunk* prog_dev = nullptr;
-  uint16_t* counts_dev = nullptr;
-  int mega_max_chunks = 0;
-  int mega_prog_smem = 0;
+  uint8_t* prog_dev = nullptr;  // [grid] program blobs
+  MegaProgLayout mega_lay;
+  float* ll_dev = nullptr;  // hand-off vectors of (value, epoch) pairs, one allocation
+  size_t ll_off[7] = {};    // float offsets: hidden0, hidden1, qkv, ctx, part, act, amax
+  unsigned mega_epoch = 0;  // epochs used so far (each launch takes layers + 2)
   // graphs
   cudaGraphExec_t decode_graph = nullptr;  // H2D token/pos + forward + D2H token
   cudaGraphExec_t loop_graph = nullptr;    // forward + device-side advance
@@ -546,8 +543,15 @@ void fill_mega_args(Session* s, MegaArgs* a, int advance) {
   a->L = s->mega_layers;
   a->embed = s->embed, a->lm_head = s->lm_head;
   a->out_norm = s->out_norm.ptr, a->out_norm_type = s->out_norm.type;
-  a->hidden = s->hidden, a->q = s->q, a->k = s->k, a->v = s->v, a->ctx = s->ctx, a->act = s->act;
   a->logits = s->logits;
+  a->ll_hidden[0] = s->ll_dev + s->ll_off[0], a->ll_hidden[1] = s->ll_dev + s->ll_off[1];
+  a->ll_qkv = s->ll_dev + s->ll_off[2], a->ll_ctx = s->ll_dev + s->ll_off[3];
+  a->ll_part = s->ll_dev + s->ll_off[4], a->ll_act = s->ll_dev + s->ll_off[5];
+  a->ll_amax = s->ll_dev + s->ll_off[6];
+  // every launch gets epochs of its own; the buffers start zeroed, so epoch 0 is never used
+  if (s->mega_epoch > 0xffffffffu - 2u * (unsigned)(c.layers + 2)) s->mega_epoch = 0;
+  a->epoch_base = s->mega_epoch;
+  s->mega_epoch += (unsigned)c.layers + 2u;
   a->kcache = s->kcache, a->vcache = s->vcache;
   a->cap = (int64_t)(s->pages * s->page_size);
   a->layer_stride = (uint64_t)c.batch * c.kv_heads * (uint64_t)a->cap * c.head_dim * s->kv_elem;
@@ -555,30 +559,27 @@ void fill_mega_args(Session* s, MegaArgs* a, int advance) {
   a->io = s->io_dev;
   a->hist = s->hist_dev, a->hist_count = s->hist_count_dev, a->hist_cap = (int64_t)s->hist_cap;
   a->advance = advance;
-  a->bar = s->bar_dev;
   a->error = reinterpret_cast<int*>(s->io_dev + 4);
-  a->attn_part = s->attn_part, a->max_split = s->mega_max_split;
-  a->argmax_val = s->amax_val, a->argmax_idx = s->amax_idx;
+  a->max_split = s->mega_max_split;
   // phase timing reads the global timer thousands of times per launch on CTA 0 and slows the
   // whole grid down; it is off unless DYNINFER_CUDA_PROFILE=1
   {
     const char* pe = getenv("DYNINFER_CUDA_PROFILE");
     a->prof = (pe && pe[0] == '1') ? s->prof_dev : nullptr;
   }
-  a->prog = s->prog_dev, a->counts = s->counts_dev, a->max_chunks = s->mega_max_chunks;
-  a->prog_in_smem = s->mega_prog_smem;
+  a->prog = s->prog_dev, a->lay = s->mega_lay;
   a->nslot = s->mega_nslot, a->xs_floats = s->mega_xs;
   a->ft = s->freq;
 }
 
-// A bounded wait inside the kernel gave up: report it and put the barrier words back to zero.
+// A bounded wait inside the kernel gave up: report it and clear the word.
 int mega_check_error(Session* s, int64_t word) {
   if ((int)word == 0) return 0;
-  cudaMemsetAsync(s->bar_dev, 0, 64, s->stream);
   cudaMemsetAsync(s->io_dev + 4, 0, 8, s->stream);
   cudaStreamSynchronize(s->stream);
-  set_error("persistent decode kernel: a bounded wait expired (code %d: 2 grid barrier, 3 weight "
-            "ring full-wait, 4 ring empty-wait)", (int)word);
+  set_error("persistent decode kernel: a bounded wait expired (code %d: 3 weight ring full-wait, "
+            "4 ring empty-wait, 7 program copy, 8 hand-off vector never arrived); the step's results "
+            "are invalid", (int)word);
   return 1;
 }
 
@@ -751,8 +752,12 @@ int dyninfer_cuda_session_create_with_file_params(
     } else if (it->second.strided.count(comp)) {
       // length = bytes uploaded = rows * segment; the file span runs to the last row's segment
       const auto& sd = it->second.strided[comp];
-      const uint64_t span = sd[0] ? (sd[0] - 1) * sd[2] + sd[1] : 0;
-      if (sd[0] == 0 || sd[1] == 0 || sd[2] < sd[1] || sd[0] * sd[1] != fp.length ||
+      // products checked for wrap-around before they are compared with the file size
+      uint64_t span = 0, bytes = 0;
+      const bool wraps = sd[0] == 0 || __builtin_mul_overflow(sd[0] - 1, sd[2], &span) ||
+                         __builtin_add_overflow(span, sd[1], &span) ||
+                         __builtin_mul_overflow(sd[0], sd[1], &bytes);
+      if (wraps || sd[1] == 0 || sd[2] < sd[1] || bytes != fp.length ||
           fp.offset + span < fp.offset || fp.offset + span > fsize[fp.source_file_index]) {
         set_error("parameter `%s`: strided range (%llu rows of %llu bytes every %llu, %llu bytes in all) "
                   "is inconsistent or exceeds file size %llu", key.c_str(), (unsigned long long)sd[0],
@@ -870,6 +875,7 @@ int dyninfer_cuda_session_create_with_file_params(
   }
   cudaEventCreate(&s->ev0);
   cudaEventCreate(&s->ev1);
+  if (!device_error_word()) return fail();  // allocated before any launch or stream capture
   fill_freq_table(&s->freq, cfg.head_dim, cfg.theta);
   if (dev_alloc(s, (void**)&s->arena, arena_bytes)) return fail();
   s->arena_bytes = arena_bytes;
@@ -971,10 +977,13 @@ int dyninfer_cuda_session_create_with_file_params(
     }
   }
 
-  if (cfg.persistent &&
-      mega_plan(cfg.hidden, cfg.inter, (int)qd, cfg.head_dim, 0, &s->mega_nslot, &s->mega_xs,
-                &s->mega_smem, &s->mega_prog_smem)) {
-    if (mega_grid_size(device, s->mega_smem, &s->mega_grid)) return fail();
+  if (cfg.persistent) {
+    // candidates: every linear readable by the tile steps, q/k/v sharing one activation layout,
+    // gate/up sharing an encoding, head dim 64 or 128; the shared-memory plan (ring + program) is
+    // made when the KV geometry is configured. Other models use the operator path.
+    int nslot = 0, xs = 0;
+    size_t smem = 0;
+    bool ok = mega_plan(cfg.hidden, cfg.inter, (int)qd, cfg.head_dim, 0, &nslot, &xs, &smem) != 0;
     std::vector<MegaLayer> ml(cfg.layers);
     for (int l = 0; l < cfg.layers; l++) {
       const LayerW& L = s->layers[l];
@@ -983,31 +992,24 @@ int dyninfer_cuda_session_create_with_file_params(
       ml[l].attn_norm = L.attn_norm.ptr, ml[l].ffn_norm = L.ffn_norm.ptr;
       ml[l].q_norm = L.q_norm.ptr, ml[l].k_norm = L.k_norm.ptr;
       ml[l].norm_type = L.attn_norm.type, ml[l].qk_norm_type = L.q_norm.type;
-      // the persistent kernel needs every linear readable by its tile steps, q/k/v sharing one
-      // activation layout, and gate/up sharing an encoding; other models use the graph path
       const WRef* ws[7] = {&L.q, &L.k, &L.v, &L.o, &L.gate, &L.up, &L.down};
       for (const WRef* wp : ws)
-        if (!mega_supports_weight(*wp)) s->mega_grid = 0;
-      if (L.attn_norm.type != L.ffn_norm.type || L.gate.enc != L.up.enc) s->mega_grid = 0;
+        if (!mega_supports_weight(*wp)) ok = false;
+      if (L.attn_norm.type != L.ffn_norm.type || L.gate.enc != L.up.enc) ok = false;
       if (xl_for_encoding_host(L.q.enc) != xl_for_encoding_host(L.k.enc) ||
           xl_for_encoding_host(L.q.enc) != xl_for_encoding_host(L.v.enc))
-        s->mega_grid = 0;
+        ok = false;
     }
-    if (!mega_supports_weight(s->lm_head)) s->mega_grid = 0;
-    s->mega_max_split = std::max(1, std::min(16, s->mega_grid / std::max(1, cfg.heads)));
-    if (s->mega_grid > 0) {
-      const size_t part_bytes = (size_t)cfg.heads * s->mega_max_split * (cfg.head_dim + 2) * 4;
+    if (!mega_supports_weight(s->lm_head) || cfg.heads % cfg.kv_heads != 0) ok = false;
+    if (ok) {
+      if (mega_grid_size(device, smem, &s->mega_grid)) return fail();
+      s->mega_max_split = std::max(1, std::min(16, s->mega_grid / std::max(1, cfg.heads)));
       if (dev_alloc(s, (void**)&s->mega_layers, ml.size() * sizeof(MegaLayer)) ||
-          dev_alloc(s, (void**)&s->io_dev, 64) || dev_alloc(s, (void**)&s->bar_dev, 64) ||
-          dev_alloc(s, (void**)&s->attn_part, part_bytes) ||
-          dev_alloc(s, (void**)&s->amax_val, (size_t)s->mega_grid * 4) ||
-          dev_alloc(s, (void**)&s->amax_idx, (size_t)s->mega_grid * 8) ||
-          dev_alloc(s, (void**)&s->prof_dev, 192))
+          dev_alloc(s, (void**)&s->io_dev, 64) || dev_alloc(s, (void**)&s->prof_dev, 192))
         return fail();
       if (cudaMemcpy(s->mega_layers, ml.data(), ml.size() * sizeof(MegaLayer),
                      cudaMemcpyHostToDevice) != cudaSuccess ||
-          cudaMemset(s->io_dev, 0, 64) != cudaSuccess ||
-          cudaMemset(s->bar_dev, 0, 64) != cudaSuccess) {
+          cudaMemset(s->io_dev, 0, 64) != cudaSuccess) {
         set_error("initialising the persistent decode kernel state failed");
         return fail();
       }
@@ -1040,8 +1042,7 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
   void* dev[] = {s->arena, s->kcache, s->vcache, s->hidden, s->xn, s->q, s->k, s->v, s->ctx, s->act, s->up,
                  s->logits, s->tokens_dev, s->row_pos_dev, s->row_seq_dev, s->out_token_dev,
                  s->hist_dev, s->hist_count_dev, s->argmax_scratch, s->mega_layers, s->io_dev,
-                 s->bar_dev, s->attn_part, s->amax_val, s->amax_idx, s->prof_dev, s->prog_dev,
-                 s->counts_dev, s->batch_logits, s->batch_tokens_dev, s->tp_part, s->tp_logits,
+                 s->prof_dev, s->prog_dev, s->ll_dev, s->batch_logits, s->batch_tokens_dev, s->tp_part, s->tp_logits,
                  s->tp_gather, s->scratch, s->qkv1, s->gu1};
   for (void* p : dev)
     if (p) cudaFree(p);
@@ -1072,6 +1073,10 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
             "paged KV geometry (layers %zu, kv heads %zu, head_dim %zu, vocab %zu) does not match the model",
             layer_count, kv_head_count, head_dim, vocab_size);
   DYN_CHECK(page_size > 0 && chunk_size > 0, "page_size and chunk_size must be positive");
+  // wrapper.c:921: one of the two must divide the other
+  DYN_CHECK(page_size % chunk_size == 0 || chunk_size % page_size == 0,
+            "invalid paged KV configuration: page_size %zu and chunk_size %zu do not divide one another",
+            page_size, chunk_size);
   DYN_CHECK(kv_element_byte_count == 4 || kv_element_byte_count == 2,
             "kv_element_byte_count %zu unsupported (4 = f32, 2 = bf16/f16)", kv_element_byte_count);
   CounterScope scope(s);
@@ -1115,26 +1120,33 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
       bl[l].q = L.q, bl[l].k = L.k, bl[l].v = L.v, bl[l].o = L.o;
       bl[l].gate = L.gate, bl[l].up = L.up, bl[l].down = L.down;
     }
-    std::vector<MegaChunk> chunks;
-    std::vector<uint16_t> counts;
+    std::vector<uint8_t> blob;
     if (mega_build_program(bl.data(), c.layers, s->lm_head, c.heads, c.kv_heads, c.head_dim, c.hidden,
-                           c.inter, c.vocab, s->q, s->k, s->v, s->hidden, s->act, s->logits,
-                           s->mega_grid, &chunks, &counts, &s->mega_max_chunks))
+                           c.inter, c.vocab, s->mega_grid, &blob, &s->mega_lay))
       return 1;
-    if (dev_alloc(s, (void**)&s->prog_dev, chunks.size() * sizeof(MegaChunk)) ||
-        dev_alloc(s, (void**)&s->counts_dev, counts.size() * sizeof(uint16_t)))
-      return 1;
-    DYN_CUDA(cudaMemcpy(s->prog_dev, chunks.data(), chunks.size() * sizeof(MegaChunk),
-                        cudaMemcpyHostToDevice));
-    DYN_CUDA(cudaMemcpy(s->counts_dev, counts.data(), counts.size() * sizeof(uint16_t),
-                        cudaMemcpyHostToDevice));
-    // final shared-memory plan: keep the program beside the ring when it fits
-    const size_t prog_bytes = ((size_t)s->mega_max_chunks * sizeof(MegaChunk) +
-                               (size_t)(4 * c.layers + 1) * 2 + 15) / 16 * 16;
-    DYN_CHECK(mega_plan(c.hidden, c.inter, c.heads * c.head_dim, c.head_dim, prog_bytes, &s->mega_nslot,
-                        &s->mega_xs, &s->mega_smem, &s->mega_prog_smem),
-              "persistent decode kernel: shared-memory plan failed");
-    if (mega_grid_size(s->device, s->mega_smem, &s->mega_grid)) return 1;
+    // the program lives in shared memory beside the ring; a model whose program does not fit
+    // decodes on the operator path
+    if (!mega_plan(c.hidden, c.inter, c.heads * c.head_dim, c.head_dim, s->mega_lay.bytes, &s->mega_nslot,
+                   &s->mega_xs, &s->mega_smem)) {
+      s->mega = false;
+    } else {
+      if (mega_grid_size(s->device, s->mega_smem, &s->mega_grid)) return 1;
+      if (dev_alloc(s, (void**)&s->prog_dev, blob.size())) return 1;
+      DYN_CUDA(cudaMemcpy(s->prog_dev, blob.data(), blob.size(), cudaMemcpyHostToDevice));
+      // hand-off vectors: (value, epoch) pairs = 2 floats per element, each vector 256-byte aligned
+      const size_t qd = (size_t)c.heads * c.head_dim, kvd = (size_t)c.kv_heads * c.head_dim;
+      const size_t elems[7] = {(size_t)c.hidden, (size_t)c.hidden, qd + 2 * kvd, qd,
+                               (size_t)c.heads * s->mega_max_split * (c.head_dim + 2), (size_t)c.inter,
+                               2 * (size_t)s->mega_grid};
+      size_t off = 0;
+      for (int i = 0; i < 7; i++) {
+        s->ll_off[i] = off;
+        off += (2 * elems[i] + 63) / 64 * 64;
+      }
+      if (dev_alloc(s, (void**)&s->ll_dev, off * 4)) return 1;
+      DYN_CUDA(cudaMemset(s->ll_dev, 0, off * 4));
+      s->mega_epoch = 0;
+    }
   }
   return 0;
 }
@@ -1219,6 +1231,10 @@ int dyninfer_cuda_session_decode_phase_profile(dyninfer_cuda_session_t* s, doubl
   return 0;
 }
 
+int dyninfer_cuda_session_uses_persistent_kernel(const dyninfer_cuda_session_t* s) {
+  return s && s->mega && s->prog_dev ? 1 : 0;
+}
+
 uint64_t dyninfer_cuda_session_launch_count(const dyninfer_cuda_session_t* s) {
   return s ? s->launches : 0;
 }
@@ -1292,6 +1308,7 @@ int dyninfer_cuda_session_invoke_paged_chunk_slot(dyninfer_cuda_session_t* s, co
                              cudaMemcpyDeviceToHost, s->stream));
   DYN_CUDA(cudaStreamSynchronize(s->stream));
   if (tp_check_error(s)) return 1;
+  if (check_device_error("session step")) return 1;
   if (rows == 1 && s->mega && mega_check_error(s, s->stage_host[4])) return 1;
   if (out_token) *out_token = s->stage_host[3];
   if (want_logits) {
@@ -1375,6 +1392,7 @@ int dyninfer_cuda_session_decode_batch(dyninfer_cuda_session_t* s, const int64_t
   }
   DYN_CUDA(cudaStreamSynchronize(s->stream));
   if (tp_check_error(s)) return 1;
+  if (check_device_error("session step")) return 1;
   for (int64_t i = 0; i < rows; i++) out_tokens[i] = st[i];
   if (out_logits) *out_logits = want_logits ? s->batch_logits_host : nullptr;  // borrowed until the next call
   return 0;
@@ -1501,6 +1519,7 @@ int dyninfer_cuda_session_decode_loop(dyninfer_cuda_session_t* s, int64_t first_
   s->launches += s->loop_nodes * steps;
   DYN_CUDA(cudaStreamSynchronize(s->stream));
   if (tp_check_error(s)) return 1;
+  if (check_device_error("session step")) return 1;
   if (out_device_ms) DYN_CUDA(cudaEventElapsedTime(out_device_ms, s->ev0, s->ev1));
   if (out_tokens)
     DYN_CUDA(cudaMemcpy(out_tokens, s->hist_dev, steps * 8, cudaMemcpyDeviceToHost));

@@ -43,6 +43,7 @@ struct PeerArgs {
   int norm_type;
   float eps;
   int rank, world, rows, H;
+  long long spins;                  // polls before a wait gives up
 };
 
 __global__ void __launch_bounds__(TP_THREADS, 1) tp_exchange_kernel(const PeerArgs a) {
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1) tp_exchange_kernel(const PeerAr
     const unsigned* mine = a.flags[a.rank] + (size_t)blockIdx.x * TP_MAX_WORLD + tid;
     long long it = 0;
     unsigned seen = 0;
-    for (; it < TP_SPINS; it++) {
+    for (; it < a.spins; it++) {
       seen = ld_acquire_sys(mine);
       if ((int)(seen - e) >= 0) break;
       __nanosleep(200);
@@ -131,6 +132,7 @@ int launch_tp_exchange(const TpPeer& p, int slot, int64_t rows, int H, float* hi
   a.epochs = p.epochs, a.error = p.error_dev;
   a.hidden = hidden, a.xn = xn, a.norm_w = norm_w, a.norm_type = norm_type, a.eps = eps;
   a.rank = p.rank, a.world = p.world, a.rows = (int)rows, a.H = H;
+  a.spins = p.spin_limit > 0 ? p.spin_limit : TP_SPINS;
   const int grid = (int)std::min<int64_t>(rows, TP_PEER_BLOCKS);
   tp_exchange_kernel<<<grid, TP_THREADS, 0, st>>>(a);
   count_launch();
@@ -139,3 +141,66 @@ int launch_tp_exchange(const TpPeer& p, int slot, int64_t rows, int H, float* hi
 }
 
 }  // namespace dyn
+
+// Exercises the bounded wait of the exchange on ONE device, with no peer involved: a two-rank
+// exchange whose "peer" region is a second local allocation whose arrival flag nobody raises.
+// The kernel must give up after `spin_limit` polls, record which rank was missing and finish;
+// the call then fails with the same message a session reports. The device stays usable.
+extern "C" int dyninfer_cuda_tp_exchange_wait_probe(int hidden, int64_t rows, int64_t spin_limit) {
+  using namespace dyn;
+  DYN_CHECK(hidden >= 4 && hidden % 4 == 0 && rows >= 1 && rows <= 64 && spin_limit >= 1 && spin_limit <= 10000000,
+            "wait probe: hidden %d, rows %lld or spin_limit %lld out of range", hidden, (long long)rows,
+            (long long)spin_limit);
+  TpPeer p;
+  p.rank = 0, p.world = 2, p.max_rows = rows, p.spin_limit = spin_limit;
+  p.region_bytes = tp_peer_region_bytes(rows, hidden);
+  p.flags_off = tp_peer_flags_offset(rows, hidden);
+  float *hid = nullptr, *xn = nullptr, *ones = nullptr;
+  cudaStream_t st = nullptr;
+  int rc = 1;
+  auto cleanup = [&]() {
+    for (int r = 0; r < 2; r++)
+      if (p.base[r]) cudaFree(p.base[r]);
+    if (p.epochs) cudaFree(p.epochs);
+    if (p.error_host) cudaFreeHost(p.error_host);
+    if (hid) cudaFree(hid);
+    if (xn) cudaFree(xn);
+    if (ones) cudaFree(ones);
+    if (st) cudaStreamDestroy(st);
+  };
+  do {
+    bool ok = true;
+    for (int r = 0; r < 2 && ok; r++)
+      ok = cudaMalloc(reinterpret_cast<void**>(&p.base[r]), p.region_bytes) == cudaSuccess &&
+           cudaMemset(p.base[r], 0, p.region_bytes) == cudaSuccess;
+    const size_t vb = (size_t)rows * hidden * 4;
+    ok = ok && cudaMalloc(reinterpret_cast<void**>(&p.epochs), TP_PEER_BLOCKS * 4) == cudaSuccess &&
+         cudaMemset(p.epochs, 0, TP_PEER_BLOCKS * 4) == cudaSuccess &&
+         cudaHostAlloc(reinterpret_cast<void**>(&p.error_host), 64, cudaHostAllocMapped) == cudaSuccess &&
+         cudaHostGetDevicePointer(reinterpret_cast<void**>(&p.error_dev), p.error_host, 0) == cudaSuccess &&
+         cudaMalloc(reinterpret_cast<void**>(&hid), vb) == cudaSuccess && cudaMemset(hid, 0, vb) == cudaSuccess &&
+         cudaMalloc(reinterpret_cast<void**>(&xn), vb) == cudaSuccess &&
+         cudaMalloc(reinterpret_cast<void**>(&ones), (size_t)hidden * 4) == cudaSuccess &&
+         cudaMemset(ones, 0, (size_t)hidden * 4) == cudaSuccess &&
+         cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess;
+    if (!ok) {
+      cuda_fail(cudaGetLastError(), "wait probe set-up", __FILE__, __LINE__);
+      break;
+    }
+    *p.error_host = 0;
+    if (launch_tp_exchange(p, 0, rows, hidden, hid, xn, ones, E_F32, 1e-6f, st)) break;
+    const cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+      cuda_fail(e, "wait probe kernel", __FILE__, __LINE__);
+      break;
+    }
+    if (*p.error_host) {
+      set_error("tensor-parallel exchange: rank %d did not arrive within the wait limit (rank %d gave up); "
+                "the step's results are invalid", *p.error_host - 1, p.rank);
+      break;
+    }
+    rc = 0;  // the wait did not expire: nothing to report
+  } while (false);
+  cleanup();
+  return rc;
+}

@@ -127,3 +127,9 @@ def argmax(v: torch.Tensor) -> int:
                           device=v.device)
     check(lib().dyninfer_cuda_argmax(_p(v), v.numel(), _p(out), _p(scratch), _stream()))
     return int(out.item())
+
+
+def check_device_error():
+    """Call after synchronising: raises when a kernel's bounded wait (weight ring, GEMM pipeline)
+    expired since the last check, in which case the results produced since then are invalid."""
+    check(lib().dyninfer_cuda_check_device_error())

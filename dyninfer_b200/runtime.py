@@ -310,9 +310,14 @@ class CudaSession:
         out = (C.c_double * 24)()
         check(lib().dyninfer_cuda_session_decode_phase_profile(self._h, out, 24))
         names = ("embed", "qkv", "attention", "o_proj", "gate_up", "down", "lm_head", "argmax", "total",
-                 "t_stage", "t_wait_weights", "t_rows", "t_grid_barrier", "t_attn_prepare", "t_attn_scores",
-                 "t_attn_merge", "t_attn_load", "t_attn_norm_reduce", "t_attn_rope", "t_attn_fetch_issue")
+                 "t_stage", "t_wait_weights", "t_rows", "t_round_reduce", "t_attn_prepare", "t_attn_scores",
+                 "t_attn_merge")
         return dict(zip(names, [float(v) for v in out]))
+
+    def uses_persistent_kernel(self) -> bool:
+        """Whether single-row steps run as the one-launch-per-token persistent kernel (decided when
+        the KV geometry is configured; False: a captured graph of per-operator kernels)."""
+        return bool(lib().dyninfer_cuda_session_uses_persistent_kernel(self._h))
 
     def weight_bytes(self) -> int:
         return int(lib().dyninfer_cuda_session_weight_bytes(self._h))

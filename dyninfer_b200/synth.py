@@ -166,6 +166,12 @@ QWEN3_32B = dict(layers=64, hidden=5120, heads=64, kv_heads=8, head_dim=128, int
                  vocab=151936, eps=1e-6, theta=1e6)
 TINY = dict(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, intermediate=512,
             vocab=512, eps=1e-6, theta=1e6)
+# The smallest shapes the persistent decode kernel takes (a Q6_K table needs 1024-wide rows):
+# two layers, head dim 128 / 64, a vocabulary that leaves some CTAs without lm_head rows.
+SMALL_D128 = dict(layers=2, hidden=1024, heads=4, kv_heads=2, head_dim=128, intermediate=1536,
+                  vocab=2048, eps=1e-6, theta=1e6)
+SMALL_D64 = dict(layers=3, hidden=1024, heads=8, kv_heads=2, head_dim=64, intermediate=1024,
+                 vocab=1000, eps=1e-6, theta=1e6)
 
 
 def linear_shapes(cfg: dict) -> dict:

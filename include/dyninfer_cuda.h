@@ -75,6 +75,14 @@ int dyninfer_cuda_device_count(int* out_count);
 /* Bytes per row of an encoded [*, cols] tensor; 0 if cols is not a whole number of blocks. */
 uint64_t dyninfer_cuda_row_bytes(int encoding, int64_t cols);
 
+/* The operator entry points below are asynchronous on the caller's stream, so a kernel whose
+ * bounded wait (weight ring, GEMM pipeline) gives up cannot fail the call that launched it: it
+ * leaves a code in a per-device error word instead. Call this after synchronising the stream:
+ * non-zero (message via last_error, word cleared) means results since the last check are
+ * invalid. Session calls check it themselves before they return. Error convention as
+ * wrapper.h:38; the reference has no asynchronous operator surface, hence no counterpart. */
+int dyninfer_cuda_check_device_error(void);
+
 /* ---- single operators (device pointers) ----------------------------------- */
 
 /* Bit-exact dequantisation to f32 [rows, cols]
@@ -262,6 +270,13 @@ int dyninfer_cuda_session_tp_peer_handle(dyninfer_cuda_session_t* session, uint8
                                          size_t byte_count);
 int dyninfer_cuda_session_tp_peer_attach(dyninfer_cuda_session_t* session, const uint8_t* handles,
                                          size_t byte_count);
+/* Diagnostic for the bounded wait of that kernel, on ONE device and without a peer: runs a
+ * two-rank exchange ([rows, hidden], rows <= 64) whose second region is a local allocation
+ * whose arrival flag is never raised, with the wait limited to `spin_limit` polls (~0.25 us each,
+ * <= 10,000,000). The expected outcome is a non-zero return with the session's "did not
+ * arrive" message and a device that still answers; 0 means the wait did not expire. No
+ * counterpart in the reference (it has no multi-device path). */
+int dyninfer_cuda_tp_exchange_wait_probe(int hidden, int64_t rows, int64_t spin_limit);
 
 /* ---- session extensions (no reference precedent) --------------------------- */
 
@@ -278,6 +293,11 @@ uint64_t dyninfer_cuda_session_decode_weight_bytes(const dyninfer_cuda_session_t
 int dyninfer_cuda_session_decode_loop(dyninfer_cuda_session_t* session, int64_t first_token,
                                       int64_t start_pos, size_t steps, int64_t* out_tokens,
                                       float* out_device_ms);
+
+/* 1 when single-row steps of this session run as the persistent decode kernel (one launch per
+ * token), 0 when they run as a captured graph of per-operator kernels. Decided by
+ * configure_paged_kv (encodings, head dim and whether the per-CTA program fits shared memory). */
+int dyninfer_cuda_session_uses_persistent_kernel(const dyninfer_cuda_session_t* session);
 
 /* Time CTA 0 of the persistent decode kernel spent per phase kind during its most recent
  * launch, microseconds (device global timer): [0] embedding, [1] norm+QKV, [2] attention,

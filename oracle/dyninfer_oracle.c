@@ -585,6 +585,16 @@ ORC_API int64_t orc_model_forward(orc_model* m, const int64_t* tokens, int64_t n
   return tok;
 }
 
+/* Sets the number of OpenMP threads of later calls (a launcher may have exported OMP_NUM_THREADS=1
+ * for its workers; the timed CPU baseline states and uses the cores it was given). */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

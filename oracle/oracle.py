@@ -76,6 +76,7 @@ def lib():
         L.orc_model_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                         C.c_void_p, C.c_void_p]
         L.orc_num_threads.restype = C.c_int
+        L.orc_set_num_threads.argtypes = [C.c_int]
         L.orc_f16_to_f32.restype = C.c_float
         L.orc_f16_to_f32.argtypes = [C.c_uint16]
         _lib = L
@@ -231,6 +232,12 @@ class Model:
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def set_num_threads(n: int) -> int:
+    """Use `n` OpenMP threads from now on, whatever OMP_NUM_THREADS said when the runtime loaded."""
+    lib().orc_set_num_threads(int(n))
+    return num_threads()
 
 
 def weights_from_catalog(cat) -> dict:

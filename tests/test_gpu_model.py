@@ -86,18 +86,22 @@ def test_gqa_rope_qknorm_prefill_vs_decode(native_lib, oracle, tmp_path):
 def test_tiny_qwen3_logits_and_greedy(native_lib, oracle, tmp_path, flavor, kv, kernel):
     """Seeded Qwen3-shaped model (2 layers): prompt of 16 ids, 32 greedy steps.
     logits max-abs <= 1e-2, cosine >= 0.9999, identical greedy tokens except near-ties."""
+    # the persistent kernel needs 1024-wide Q6_K rows: its cases run on the smallest shapes it takes
+    cfg = synth.TINY if kernel == "graph" or flavor == "mlx_u4" else (synth.SMALL_D64 if kv == "f32" else synth.SMALL_D128)
     if flavor == "mlx_u4":
-        path = synth.write_qwen3_mlx(str(tmp_path / "mlx"), synth.TINY, seed=11)
+        path = synth.write_qwen3_mlx(str(tmp_path / "mlx"), cfg, seed=11)
     else:
         encs = {"attn_v": "gguf.q4_1", "ffn_down": "gguf.q8_0"} if flavor == "gguf_mixed" else None
-        path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), synth.TINY, seed=11, encodings=encs,
+        path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), cfg, seed=11, encodings=encs,
                                       output="gguf.q6_k" if flavor == "gguf_mixed" else None)
     model = ModelLoader().load(path, max_kv=512, kv_dtype=kv, chunk_size=16, decode_kernel=kernel)
     cat = ck.open_catalog(path)
-    prompt = np.random.default_rng(5).integers(0, synth.TINY["vocab"], size=16).tolist()
+    prompt = np.random.default_rng(5).integers(0, cfg["vocab"], size=16).tolist()
     steps = 32
     want_logits, want_toks, margins = oracle_run(oracle, cat, prompt, steps, kv_round=2 if kv == "bf16" else 0)
     with model.create_session(SessionConfig(max_sequence_length=512)) as s:
+        # the path under test is the one that runs (bf16 embeddings keep MLX models on the operator path)
+        assert s.uses_persistent_kernel() == (kernel == "persistent" and flavor != "mlx_u4")
         lg = s.prefill(prompt).values
         assert np.abs(lg - want_logits[0]).max() <= 1e-2 and helpers.cosine(lg, want_logits[0]) >= 0.9999
         toks = [int(np.argmax(lg))]
@@ -200,7 +204,8 @@ def test_generate_and_perf_report(native_lib, tmp_path):
 def test_persistent_kernel_long_context_split_kv(native_lib, oracle, tmp_path, kv):
     """Context past 256 keys makes the persistent kernel split each head's keys over several
     CTAs; its logits must track both the oracle and the per-operator graph path."""
-    path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), synth.TINY, seed=21)
+    cfg = synth.SMALL_D64 if kv == "f16" else synth.SMALL_D128
+    path = synth.write_qwen3_gguf(str(tmp_path / "q.gguf"), cfg, seed=21)
     cat = ck.open_catalog(path)
     prompt = np.random.default_rng(2).integers(0, 512, size=600).tolist()
     rnd = {"f32": 0, "f16": 1, "bf16": 2}[kv]
@@ -209,6 +214,7 @@ def test_persistent_kernel_long_context_split_kv(native_lib, oracle, tmp_path, k
     for kernel in ("persistent", "graph"):
         model = ModelLoader().load(path, max_kv=1024, kv_dtype=kv, chunk_size=128, decode_kernel=kernel)
         with model.create_session(SessionConfig(max_sequence_length=1024)) as s:
+            assert s.uses_persistent_kernel() == (kernel == "persistent")
             lg = [s.prefill(prompt).values]
             for i in range(3):
                 lg.append(s.decode(toks[i]).values)

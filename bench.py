@@ -267,6 +267,75 @@ def time_prefill(model, n=2048, reps=3):
     return n / statistics.median(times)
 
 
+# ------------------------------------------------------------- tensor-parallel section
+
+TP_MODEL, TP_LAYERS, TP_FULL_LAYERS = "32b-q4_0", 8, 64
+
+
+def tp_section(rank, world, local_rank, no_check=False):
+    """The configuration that shards: Qwen3-32B shape (hidden 5120, 64/8 heads of 128, intermediate
+    25600, Q4_0 linears, Q6_K embeddings and head), tensor parallel over the N ranks of this run with
+    one exchange after o_proj and one after down. The file holds TP_LAYERS of the 64 layers (every
+    layer carries layer 0's random bytes) so that writing and loading it stays within seconds; times
+    per step are therefore those of an 8-layer model of the full width. Batch 1 and batch 32,
+    4096-token random prompts, 256 greedy steps. At N > 1 rank 0 afterwards times the unsharded
+    model alone (the N = 1 point of the strong-scaling curve), and a short run's logits are compared
+    with the CPU restatement."""
+    import torch
+    from dyninfer_b200 import replicas, tp_decode
+    out = {"model": f"qwen3-32b-shape q4_0, q6_k embeddings and head, {TP_LAYERS} of {TP_FULL_LAYERS} layers written "
+                    "(each carries layer 0's bytes)", "n_gpus": world, "prompt": 4096, "steps": 256,
+           "scaling": "strong", "timing": "host clock around synchronised calls, maximum over ranks"}
+    runs = {}
+    for batch in (1, 32):
+        r = tp_decode.run(TP_MODEL, TP_LAYERS, prompt=4096, steps=256, warmup=3, batch=batch, chunk=512,
+                          kv_dtype="bf16", exchange="peer")
+        runs[batch] = r
+        out[f"batch{batch}"] = {k: r[k] for k in ("tokens_per_s", "ms_per_step", "prefill_tokens_per_s",
+                                                  "weight_bytes_per_step_per_rank", "weight_gbs_per_gpu",
+                                                  "weight_gbs_all_ranks", "exchange")}
+    # short run for the parity check: prompt of 8 ids, the logits of its last row and of one step
+    dump = os.path.join(os.path.dirname(checkpoint_path()), f"tp_logits_{os.getpid()}.npz") if rank == 0 else ""
+    tp_decode.run(TP_MODEL, TP_LAYERS, prompt=8, steps=2, warmup=1, batch=1, chunk=512, kv_dtype="bf16",
+                  exchange="peer", dump_logits=dump)
+    replicas.barrier()
+    if rank != 0:
+        replicas.barrier()          # rank 0 is timing the unsharded model
+        return None
+    if world > 1:
+        # the N = 1 point, measured in this run on rank 0's GPU while the other ranks wait
+        for batch in (1, 32):
+            r1 = tp_decode.run(TP_MODEL, TP_LAYERS, prompt=4096, steps=256, warmup=3, batch=batch, chunk=512,
+                               kv_dtype="bf16", solo=True)
+            out[f"batch{batch}"]["n1_ms_per_step"] = r1["ms_per_step"]
+            out[f"batch{batch}"]["strong_scaling_efficiency"] = round(
+                r1["ms_per_step"] / (world * runs[batch]["ms_per_step"]), 3)
+        replicas.barrier()
+    if not no_check:
+        use_all_host_threads()
+        from oracle import oracle as orc
+        from dyninfer_b200 import checkpoint as ck
+        orc.build()
+        orc.set_num_threads(len(os.sched_getaffinity(0)))
+        d = np.load(dump)
+        cat = ck.open_catalog(str(d["checkpoint"]))
+        m = orc.Model(cat.config, orc.weights_from_catalog(cat), kv_cap=32, kv_round=2, fast=True)
+        lg0, tok0 = m.forward(d["prompt"].tolist())
+        par = {"reference": "CPU restatement on the same file and prompt, bf16-rounded KV",
+               "prefill_logits_max_abs_diff": float(np.abs(d["prefill_logits"] - lg0).max()),
+               "first_token_equal": bool(int(d["first_token"]) == int(tok0))}
+        if par["first_token_equal"]:
+            lg1, _ = m.forward([tok0])
+            par["step_logits_max_abs_diff"] = float(np.abs(d["step_logits"] - lg1).max())
+        par["ok"] = bool(par["prefill_logits_max_abs_diff"] <= 1e-2 and par.get("step_logits_max_abs_diff", 0.0) <= 1e-2)
+        out["parity"] = par
+    try:
+        os.remove(dump)
+    except OSError:
+        pass
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -275,6 +344,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "f16", "f32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel section (32B shape)")
     ap.add_argument("--decode-only", action="store_true",
                     help="prompt + W + K device-loop decode steps and nothing else (small case for profiler captures)")
     args = ap.parse_args()
@@ -282,6 +352,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    # in-switch reduction off in every library used: a rank that dies while bound to an NVLink
+    # multicast object can fault its peers
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 
     if args.impl == "reference":
         run_reference_arm(args, rank)
@@ -339,6 +412,9 @@ def main():
     ms, e2e_ms = replicas.max_over_ranks([ms, e2e_s * 1e3], device="cuda")   # slowest rank decides
     e2e_s = e2e_ms / 1e3
     weight_bytes = session.decode_weight_bytes()
+    session.close()
+    session = None
+    tp = None if args.no_tp else tp_section(rank, world, local_rank, no_check=args.no_cpu_baseline)
 
     if rank == 0:
         hbm_peak, peak_kind = peaks()
@@ -383,8 +459,9 @@ def main():
                           f"({dt:.1f} s), CPU restatement of the reference's direct path"}
             # the same run checks the timed loop: its first tokens against the restatement's
             out["parity"] = parity_against(cpu_toks, cpu_margins, [first] + [int(t) for t in toks_w] + [int(t) for t in toks])
+        if tp is not None:
+            out["tp"] = tp
         print(json.dumps(out), flush=True)
-    session.close()
     replicas.shutdown()
 
 

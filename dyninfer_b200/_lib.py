@@ -9,10 +9,11 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libdyninfer_cuda.so")
+# DYNINFER_CUDA_LIB names another build of the library (e.g. one compiled with different kernel options)
+LIB_PATH = os.environ.get("DYNINFER_CUDA_LIB") or os.path.join(HERE, "libdyninfer_cuda.so")
 
 ENC = {"plain.f32": 0, "plain.f16": 1, "plain.bf16": 2, "gguf.q4_0": 3, "gguf.q4_1": 4,
-       "gguf.q8_0": 5, "gguf.q6_k": 6, "mlx.affine.u4": 7}
+       "gguf.q8_0": 5, "gguf.q6_k": 6, "mlx.affine.u4": 7, "gguf.q4_k": 8, "gguf.q5_k": 9}
 ENC_NAME = {v: k for k, v in ENC.items()}
 
 
@@ -93,6 +94,7 @@ PROTOTYPES = {
                                                     C.POINTER(C.c_float)]),
     "dyninfer_cuda_session_launch_count": (C.c_uint64, [_P]),
     "dyninfer_cuda_session_uses_persistent_kernel": (C.c_int, [_P]),
+    "dyninfer_cuda_session_decode_trace": (C.c_int, [_P, C.POINTER(C.c_uint64), C.c_size_t, C.POINTER(C.c_size_t)]),
     "dyninfer_cuda_session_decode_phase_profile": (C.c_int, [_P, C.POINTER(C.c_double), C.c_size_t]),
 }
 

@@ -150,7 +150,7 @@ static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 
 int wref_from_api(const dyninfer_cuda_weight_t* w, WRef* out) {
   DYN_CHECK(w != nullptr, "weight descriptor is NULL");
-  DYN_CHECK(w->encoding >= E_F32 && w->encoding <= E_MLX_U4, "unknown encoding %d", w->encoding);
+  DYN_CHECK(w->encoding >= E_F32 && w->encoding <= E_LAST, "unknown encoding %d", w->encoding);
   DYN_CHECK(w->rows >= 0 && w->cols > 0, "weight shape [%lld, %lld] is invalid",
             (long long)w->rows, (long long)w->cols);
   int unit = enc_block_elems(w->encoding);
@@ -211,7 +211,7 @@ int dyninfer_cuda_device_count(int* out_count) {
 }
 
 uint64_t dyninfer_cuda_row_bytes(int encoding, int64_t cols) {
-  if (encoding < E_F32 || encoding > E_MLX_U4 || cols <= 0) return 0;
+  if (encoding < E_F32 || encoding > E_LAST || cols <= 0) return 0;
   return (uint64_t)enc_row_bytes(encoding, cols);
 }
 

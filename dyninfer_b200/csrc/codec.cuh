@@ -43,7 +43,7 @@ struct Codec;
 // w = f32(q - 8) * f32(d). gguf_codegen.rs:412-472.
 template <>
 struct Codec<E_Q4_0> {
-  static constexpr int BLOCK = 32, BYTES = 18, PARTS = 4, G = 2;
+  static constexpr int BLOCK = 32, BYTES = 18, PARTS = 4, G = 2, CHUNK_DIV = 1;
   __device__ static __forceinline__ int xoff(int part, int g) { return g * 16 + 4 * part; }
   __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int part, float* w) {
     const uint8_t* b = r.data + blk * BYTES;
@@ -61,7 +61,7 @@ struct Codec<E_Q4_0> {
 // Q4_1: f16 d @0, f16 m @2, 16 bytes @4; w = f32(q)*d + m. gguf_codegen.rs:373-375,425-465.
 template <>
 struct Codec<E_Q4_1> {
-  static constexpr int BLOCK = 32, BYTES = 20, PARTS = 4, G = 2;
+  static constexpr int BLOCK = 32, BYTES = 20, PARTS = 4, G = 2, CHUNK_DIV = 1;
   __device__ static __forceinline__ int xoff(int part, int g) { return g * 16 + 4 * part; }
   __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int part, float* w) {
     const uint8_t* b = r.data + blk * BYTES;
@@ -80,7 +80,7 @@ struct Codec<E_Q4_1> {
 // Q8_0: f16 d @0, 32 int8 @2; w = f32(q) * d. gguf_codegen.rs:382-410.
 template <>
 struct Codec<E_Q8_0> {
-  static constexpr int BLOCK = 32, BYTES = 34, PARTS = 8, G = 1;
+  static constexpr int BLOCK = 32, BYTES = 34, PARTS = 8, G = 1, CHUNK_DIV = 1;
   __device__ static __forceinline__ int xoff(int part, int) { return 4 * part; }
   __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int part, float* w) {
     const uint8_t* b = r.data + blk * BYTES;
@@ -100,7 +100,9 @@ struct Codec<E_Q8_0> {
 // gguf_codegen.rs:474-526. A part is (n, 4 consecutive j); group g = (h, p).
 template <>
 struct Codec<E_Q6_K> {
-  static constexpr int BLOCK = 256, BYTES = 210, PARTS = 16, G = 4;
+  // CHUNK_DIV: the 8 parts that cover a 64-element K chunk starting koff elements into the block are
+  // parts (koff / CHUNK_DIV) * 8 .. + 7 (a Q6_K part spans a 128-element half)
+  static constexpr int BLOCK = 256, BYTES = 210, PARTS = 16, G = 4, CHUNK_DIV = 128;
   __device__ static __forceinline__ int xoff(int part, int g) {
     return (part >> 3) * 128 + (g >> 1) * 64 + (g & 1) * 32 + 4 * (part & 7);
   }
@@ -127,11 +129,66 @@ struct Codec<E_Q6_K> {
   }
 };
 
+// Q4_K / Q5_K (the K-quants real Q4_K_M / UD-Q4_K_XL files mix in; schema-only in the reference,
+// crates/dyninfer-checkpoint-gguf/src/types.rs:21-22,137-201, so the arithmetic follows GGML's
+// published dequantisation as the `gguf` Python package evaluates it in f32):
+//   f16 d @0, f16 dmin @2, 12 bytes of 6-bit scales / mins @4 for 8 sub-blocks of 32,
+//   Q4_K: 128 nibble bytes @16; Q5_K: 32 high-bit bytes @16, 128 nibble bytes @48.
+//   element 64*jj + 32*h + l (jj < 4, h < 2, l < 32): sub-block j = 2*jj + h, nibble h of byte
+//   32*jj + l (Q5_K: plus 16 * bit j of high byte l);
+//   sc_j, m_j: j < 4: s[j] & 63, s[j+4] & 63; j >= 4: (s[j+4] & 15) | ((s[j-4] >> 6) << 4),
+//   (s[j+4] >> 4) | ((s[j] >> 6) << 4);  w = (f32(d) * sc_j) * q - (f32(dmin) * m_j), each
+//   product and the difference rounded on its own.
+// A part is (jj, 4 consecutive l); group g = h.
+__device__ __forceinline__ void kquant_scale_min(const uint8_t* s, int j, float* sc, float* mn) {
+  uint32_t a, b;
+  if (j < 4) {
+    a = s[j] & 63u;
+    b = s[j + 4] & 63u;
+  } else {
+    a = (s[j + 4] & 15u) | ((uint32_t)(s[j - 4] >> 6) << 4);
+    b = (uint32_t)(s[j + 4] >> 4) | ((uint32_t)(s[j] >> 6) << 4);
+  }
+  *sc = (float)a;
+  *mn = (float)b;
+}
+template <int ENC>
+struct KQuant45 {
+  static constexpr bool Q5 = ENC == E_Q5_K;
+  static constexpr int BLOCK = 256, BYTES = Q5 ? 176 : 144, PARTS = 32, G = 2, CHUNK_DIV = 64;
+  __device__ static __forceinline__ int xoff(int part, int g) { return (part >> 3) * 64 + g * 32 + 4 * (part & 7); }
+  __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int part, float* w) {
+    const uint8_t* b = r.data + blk * BYTES;  // 144 and 176 are multiples of 16: blocks stay word aligned
+    const int jj = part >> 3, l4 = part & 7;
+    const float d = f16_bits_to_f32(ld_u16(b)), dmin = f16_bits_to_f32(ld_u16(b + 2));
+    const uint32_t ql = *reinterpret_cast<const uint32_t*>(b + (Q5 ? 48 : 16) + 32 * jj + 4 * l4);
+    uint32_t qh = 0;
+    if (Q5) qh = *reinterpret_cast<const uint32_t*>(b + 16 + 4 * l4);
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int j = 2 * jj + h;
+      float sc, mn;
+      kquant_scale_min(b + 4, j, &sc, &mn);
+      const float ds = __fmul_rn(d, sc), dm = __fmul_rn(dmin, mn);
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        uint32_t q = (ql >> (8 * i + 4 * h)) & 15u;
+        if (Q5) q |= ((qh >> (8 * i + j)) & 1u) << 4;
+        w[4 * h + i] = __fsub_rn(__fmul_rn(ds, (float)q), dm);
+      }
+    }
+  }
+};
+template <>
+struct Codec<E_Q4_K> : KQuant45<E_Q4_K> {};
+template <>
+struct Codec<E_Q5_K> : KQuant45<E_Q5_K> {};
+
 // MLX affine U4: ui32[N, K/8], lane k of a word = bits [4k, 4k+4); per group:
 // w = f32(q)*scale + bias. mlx_affine.rs:284-290,590-600. One word is one "block".
 template <>
 struct Codec<E_MLX_U4> {
-  static constexpr int BLOCK = 8, BYTES = 4, PARTS = 1, G = 2;
+  static constexpr int BLOCK = 8, BYTES = 4, PARTS = 1, G = 2, CHUNK_DIV = 1;
   __device__ static __forceinline__ int xoff(int, int g) { return 4 * g; }
   __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int, float* w) {
     const uint32_t q = reinterpret_cast<const uint32_t*>(r.data)[blk];
@@ -148,7 +205,7 @@ struct Codec<E_MLX_U4> {
 // crates/dyninfer-compiler/src/lowering/kernels.rs:1157-1173). Block = 4 elements.
 template <>
 struct Codec<E_F32> {
-  static constexpr int BLOCK = 4, BYTES = 16, PARTS = 1, G = 1;
+  static constexpr int BLOCK = 4, BYTES = 16, PARTS = 1, G = 1, CHUNK_DIV = 1;
   __device__ static __forceinline__ int xoff(int, int) { return 0; }
   __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int, float* w) {
     const float4 v = reinterpret_cast<const float4*>(r.data)[blk];
@@ -157,7 +214,7 @@ struct Codec<E_F32> {
 };
 template <>
 struct Codec<E_F16> {
-  static constexpr int BLOCK = 4, BYTES = 8, PARTS = 1, G = 1;
+  static constexpr int BLOCK = 4, BYTES = 8, PARTS = 1, G = 1, CHUNK_DIV = 1;
   __device__ static __forceinline__ int xoff(int, int) { return 0; }
   __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int, float* w) {
     const uint2 v = reinterpret_cast<const uint2*>(r.data)[blk];
@@ -167,7 +224,7 @@ struct Codec<E_F16> {
 };
 template <>
 struct Codec<E_BF16> {
-  static constexpr int BLOCK = 4, BYTES = 8, PARTS = 1, G = 1;
+  static constexpr int BLOCK = 4, BYTES = 8, PARTS = 1, G = 1, CHUNK_DIV = 1;
   __device__ static __forceinline__ int xoff(int, int) { return 0; }
   __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int, float* w) {
     const uint2 v = reinterpret_cast<const uint2*>(r.data)[blk];
@@ -187,6 +244,8 @@ struct Codec<E_BF16> {
     case E_Q8_0: { constexpr int ENC = E_Q8_0; __VA_ARGS__; } break;     \
     case E_Q6_K: { constexpr int ENC = E_Q6_K; __VA_ARGS__; } break;     \
     case E_MLX_U4: { constexpr int ENC = E_MLX_U4; __VA_ARGS__; } break; \
+    case E_Q4_K: { constexpr int ENC = E_Q4_K; __VA_ARGS__; } break;     \
+    case E_Q5_K: { constexpr int ENC = E_Q5_K; __VA_ARGS__; } break;     \
     default:                                            \
       dyn::set_error("unknown encoding %d", (int)(enc)); \
       return 1;                                         \

@@ -90,6 +90,9 @@ enum : int {
   E_Q8_0 = DYNINFER_ENC_Q8_0,
   E_Q6_K = DYNINFER_ENC_Q6_K,
   E_MLX_U4 = DYNINFER_ENC_MLX_U4,
+  E_Q4_K = DYNINFER_ENC_Q4_K,
+  E_Q5_K = DYNINFER_ENC_Q5_K,
+  E_LAST = DYNINFER_ENC_Q5_K,
 };
 
 __host__ __device__ inline int enc_block_elems(int enc) {
@@ -99,6 +102,8 @@ __host__ __device__ inline int enc_block_elems(int enc) {
     case E_Q8_0:
       return 32;
     case E_Q6_K:
+    case E_Q4_K:
+    case E_Q5_K:
       return 256;
     case E_MLX_U4:
       return 8;
@@ -121,6 +126,10 @@ __host__ __device__ inline int enc_block_bytes(int enc) {
       return 34;
     case E_Q6_K:
       return 210;
+    case E_Q4_K:
+      return 144;
+    case E_Q5_K:
+      return 176;
     case E_MLX_U4:
       return 4;
     default:
@@ -203,6 +212,8 @@ int launch_gemv_cs_q6k(const WRef& w, const void* x, int x_type, float* y, const
 size_t gemv_cs_workspace_bytes(const WRef& w, int M);
 int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, const float* residual,
                    uint8_t* ws, cudaStream_t s, bool* handled);
+int launch_gemv_plain(const WRef& w, const void* x, int x_type, int M, float* y, const float* residual,
+                      cudaStream_t s, bool* handled);
 size_t gemv_mma_workspace_bytes(const WRef& w, int x_type, int M);
 int launch_gemv_mma(const WRef& w, const void* x, int x_type, int M, float* y, const float* residual,
                     void* workspace, cudaStream_t s, bool* handled);

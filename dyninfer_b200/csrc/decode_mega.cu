@@ -43,9 +43,33 @@ namespace dyn {
 
 namespace {
 
-constexpr int MK_CW = 16;               // consumer warps
-constexpr int MK_CT = MK_CW * 32;       // consumer threads
-constexpr int MK_THREADS = MK_CT + 32;  // + one producer warp
+#ifndef MK_OPT_CW
+#define MK_OPT_CW 8
+#endif
+constexpr int MK_CW = MK_OPT_CW;   // consumer warps (a power of two)
+constexpr int MK_CT = MK_CW * 32;  // consumer threads
+// Sixteen warps (four per scheduler partition) leave 128 registers per thread; a seventeenth warp
+// for the weight copies would cut that to 96 and the kernel would spill. So the warps take turns
+// as producer: after chunk c, warp c % 16 issues the copies of the chunk nslot - 1 ahead, into
+// the slot chunk c - 1 has just left (a few dozen instructions: byte counts and alignments come
+// precomputed from the host). MK_PRODUCER_WARP = true restores the separate warp.
+#ifndef MK_OPT_PRODUCER_WARP
+#define MK_OPT_PRODUCER_WARP 1
+#endif
+#ifndef MK_OPT_POLL2
+#define MK_OPT_POLL2 0
+#endif
+#ifndef MK_OPT_LOCAL
+#define MK_OPT_LOCAL 1
+#endif
+#ifndef MK_OPT_KSLICE2
+#define MK_OPT_KSLICE2 0
+#endif
+#ifndef MK_OPT_PAIRS
+#define MK_OPT_PAIRS 0
+#endif
+constexpr bool MK_PRODUCER_WARP = MK_OPT_PRODUCER_WARP != 0;
+constexpr int MK_THREADS = MK_CT + (MK_PRODUCER_WARP ? 32 : 0);
 constexpr int MK_SLOT = 18432;          // bytes per ring slot (one 16-row tile x K-slice)
 constexpr int MK_PART = MEGA_TA * MK_CW * 16;  // floats of one partial-sum buffer
 // per-CTA scratch, in floats
@@ -55,7 +79,7 @@ constexpr int MK_OFF_KN = MK_OFF_QS + 128;           // [128] new key (as cached
 constexpr int MK_OFF_VN = MK_OFF_KN + 128;           // [128] new value (as cached)
 constexpr int MK_OFF_WM = MK_OFF_VN + 128;           // [16] per-warp running max
 constexpr int MK_OFF_WL = MK_OFF_WM + 16;            // [16] per-warp running sum
-constexpr int MK_OFF_RED = MK_OFF_WL + 16;           // [64] block reductions
+constexpr int MK_OFF_RED = MK_OFF_WL + 16;           // [64] block reductions; [32, 64): per-warp sums of squares of two phases
 constexpr int MK_OFF_WACC = MK_OFF_RED + 64;         // [16][128] per-warp weighted values
 constexpr int MK_OFF_ROPE = MK_OFF_WACC + 16 * 128;  // cos[64], sin[64] of this token's position
 constexpr int MK_OFF_RES = MK_OFF_ROPE + 128;        // [64] residual rows this CTA owns
@@ -108,11 +132,65 @@ __device__ __forceinline__ void ll_poll(const float* buf, const int64_t (&idx)[N
   }
 }
 
+// The same with two samples of every line in flight, half a round trip apart: a poll that waits
+// for one load at a time looks at the data once per L2 round trip (0.5 - 1 us across the two dies),
+// so a pair arriving just after a sample waits most of a round trip to be seen; a second, staggered
+// sample halves that wait.
+template <int NL>
+__device__ __forceinline__ void ll_poll2(const float* buf, const int64_t (&idx)[NL], unsigned ep, float (&v)[2 * NL],
+                                         volatile int* abort) {
+  uint4 ra[NL], rb[NL];
+#pragma unroll
+  for (int i = 0; i < NL; i++) ra[i] = ll_load(buf, idx[i]);
+  __nanosleep(300);
+#pragma unroll
+  for (int i = 0; i < NL; i++) rb[i] = ll_load(buf, idx[i]);
+  long long it = 0;
+  bool from_b = false;
+  for (;;) {
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < NL; i++) ok = ok && ra[i].y == ep && ra[i].w == ep;
+    if (ok) break;
+#pragma unroll
+    for (int i = 0; i < NL; i++) ra[i] = ll_load(buf, idx[i]);
+    ok = true;
+#pragma unroll
+    for (int i = 0; i < NL; i++) ok = ok && rb[i].y == ep && rb[i].w == ep;
+    if (ok) {
+      from_b = true;
+      break;
+    }
+#pragma unroll
+    for (int i = 0; i < NL; i++) rb[i] = ll_load(buf, idx[i]);
+    if (*abort) break;
+    if (++it >= MK_LL_SPINS) {
+      *abort = 8;
+      break;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NL; i++) {
+    v[2 * i] = __uint_as_float(from_b ? rb[i].x : ra[i].x);
+    v[2 * i + 1] = __uint_as_float(from_b ? rb[i].z : ra[i].z);
+  }
+}
+
+// Ask L2 for a line that will be read later (norm vectors and cached keys / values of the NEXT
+// layer: the weight stream pushes everything a token wrote out of L2 before the next token reads it,
+// and a miss on the dependency chain costs a DRAM round trip).
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+__device__ __forceinline__ void prefetch_span(const void* p, size_t bytes, int tid, int nthreads) {
+  const uint8_t* b = reinterpret_cast<const uint8_t*>(p);
+  for (size_t off = (size_t)tid * 128; off < bytes; off += (size_t)nthreads * 128) prefetch_l2(b + off);
+}
+
 struct Smem {
   float* xs;      // activation vector, f32
   __half* xf;     // same, hi/lo f16 fragments
   float* sx32;    // per-32 sums of the scaled activation
   float* sx16;    // per-16 sums
+  float* isx;     // per 32-block: 2^24 / the power-of-two scale its activations were staged with
   float* misc;
   uint8_t* ring;
   uint64_t* full;
@@ -122,7 +200,9 @@ struct Smem {
   const MegaTile* tiles;
   const MegaRound* rounds;
   const uint16_t* phase_rounds;
+  const MegaLayerHot* hot;
   volatile int* abort;
+  uint32_t nchunks;  // chunks of one token's program
   int nslot;
 };
 
@@ -156,256 +236,42 @@ __device__ __noinline__ void mega_gather_row(const WRef w, int64_t row, float* o
 }
 
 // ---- producer: one bulk copy per tile row (lanes 0..15), MLX aux rows by lanes 16..31 --------
-__device__ __forceinline__ void produce_chunk(const MegaChunk* c, const Smem& sm, uint32_t pi, int lane) {
-  const int slot = pi % sm.nslot;
-  if (pi >= (uint32_t)sm.nslot) {
+// slot / lap: ring position of the chunk and how many times the ring has gone round before it.
+__device__ __forceinline__ void produce_chunk(const MegaChunk* c, const Smem& sm, int slot, uint32_t lap, int lane) {
+  if (lap > 0) {
     int ok = 1;
     if (lane == 0) {
-      ok = mbar_wait_bounded(sm.empty + slot, ((pi / sm.nslot) - 1u) & 1u, MK_MBAR_SPINS, sm.abort) ? 1 : 0;
+      ok = mbar_wait_bounded(sm.empty + slot, (lap - 1u) & 1u, MK_MBAR_SPINS, sm.abort) ? 1 : 0;
       if (!ok && !*sm.abort) *sm.abort = 4;
     }
     ok = __shfl_sync(0xffffffffu, ok, 0);
     if (!ok) return;
   }
   uint8_t* base = sm.ring + (size_t)slot * MK_SLOT;
-  const int i = lane & 15;
-  const int n = c->n;
-  const uint8_t* g0 = nullptr;
-  const uint8_t* g1 = nullptr;
-  uint8_t* d0 = nullptr;
-  uint8_t* d1 = nullptr;
-  uint32_t n0 = 0, n1 = 0;
-  if (i < n) {
-    if (lane < 16) {
-      const uint8_t* s = c->src + (size_t)i * c->rb;
-      const uint32_t off = (uint32_t)(reinterpret_cast<uintptr_t>(s) & 15);
-      g0 = s - off;
-      n0 = (off + c->seg + 15u) & ~15u;
-      d0 = base + i * c->pitch;
-    } else if (c->aseg) {
-      const uint8_t* s = c->sc + (size_t)i * c->arb;
-      uint32_t off = (uint32_t)(reinterpret_cast<uintptr_t>(s) & 15);
-      g0 = s - off;
-      n0 = (off + c->aseg + 15u) & ~15u;
-      d0 = base + 16 * c->pitch + i * c->apitch;
-      s = c->bi + (size_t)i * c->arb;
-      off = (uint32_t)(reinterpret_cast<uintptr_t>(s) & 15);
-      g1 = s - off;
-      n1 = (off + c->aseg + 15u) & ~15u;
-      d1 = base + 16 * c->pitch + (16 + i) * c->apitch;
+  if (c->contig) {
+    // the tile's rows follow each other in memory: one copy, rows rb bytes apart in the slot
+    if (lane == 0) {
+      mbar_expect_tx(sm.full + slot, c->contig);
+      bulk_g2s(base, c->src - c->al, c->contig, sm.full + slot);
     }
+    return;
   }
-  uint32_t total = n0 + n1;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-  if (lane == 0) mbar_expect_tx(sm.full + slot, total);
+  // the byte count of all copies is known on the host (tx): no reduction over the lanes
+  if (lane == 0) mbar_expect_tx(sm.full + slot, c->tx);
   __syncwarp();
-  if (n0) bulk_g2s(d0, g0, n0, sm.full + slot);
-  if (n1) bulk_g2s(d1, g1, n1, sm.full + slot);
-}
-
-// ---- staging the activation vector of a phase ---------------------------------------------------
-// Item i = (block kb = i / 4, lane quarter t = i % 4) holds 8 elements of the vector: A = 4
-// elements at baseA, B = 4 elements at baseB (the items partition the vector). Pass 1 brings each
-// item's elements in (polled pairs, the split-KV partials, or already in xs), stores them to xs
-// and accumulates the sum of squares and the largest magnitude; one block reduction gives the
-// RMSNorm factor and the power-of-two scale; pass 2 writes the hi/lo f16 fragments and the
-// 16-/32-run sums. Returns 2^24 / scale.
-enum { SRC_XS = 0, SRC_LL = 1, SRC_PARTIALS = 2 };
-
-struct StageSrc {
-  int kind;
-  const float* ll;  // SRC_LL: the pair buffer; SRC_PARTIALS: a.ll_part
-  unsigned ep;
-  int nsplit, max_split, d;  // SRC_PARTIALS
-};
-
-__device__ __forceinline__ float stage_phase(const StageSrc& src, const void* nw, int nw_type, int n, float eps,
-                                             int layout, const Smem& sm, int tid, int lane, int warp) {
-  float* red = sm.misc + MK_OFF_RED;
-  const int items = n >> 3;
-  float ss = 0.f, mx = 0.f;
-  for (int i = tid; i < items; i += MK_CT) {  // items is a multiple of 4; a lane quad is one 32-block
-    const int kb = i >> 2, t = i & 3;
-    const int baseA = kb * 32 + (layout == XL_MLXW ? 8 * t : 4 * t);
-    const int baseB = layout == XL_MLXW ? baseA + 4 : kb * 32 + 16 + 4 * t;
-    // norm weights first: their loads are in flight while the pairs are polled
-    float w[8];
-#pragma unroll
-    for (int j = 0; j < 8; j++)
-      w[j] = nw ? aux_load(reinterpret_cast<const uint8_t*>(nw), nw_type, (j < 4 ? baseA : baseB - 4) + j) : 1.0f;
-    float v[8];
-    if (src.kind == SRC_LL) {
-      const int64_t idx[4] = {baseA, baseA + 2, baseB, baseB + 2};
-      ll_poll<4>(src.ll, idx, src.ep, v, sm.abort);
-    } else if (src.kind == SRC_PARTIALS) {
-      // merge the split-KV partial outputs of this item's head in split order (online softmax merge)
-      const int head = baseA / src.d, ia = baseA - head * src.d, ib = baseB - head * src.d;
-      float M = -3.40282347e38f, Lsum = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; j++) v[j] = 0.f;
-      for (int s = 0; s < src.nsplit; s++) {
-        const int64_t pb = ((int64_t)head * src.max_split + s) * (src.d + 2);
-        const int64_t idx[5] = {pb + ia, pb + ia + 2, pb + ib, pb + ib + 2, pb + src.d};
-        float p[10];
-        ll_poll<5>(src.ll, idx, src.ep, p, sm.abort);
-        const float ms = p[8], ls = p[9];
-        const float mn = fmaxf(M, ms);
-        const float f = expf(M - mn), wgt = expf(ms - mn);
-#pragma unroll
-        for (int j = 0; j < 8; j++) v[j] = v[j] * f + p[j] * wgt;
-        Lsum = Lsum * f + ls * wgt;
-        M = mn;
-      }
-#pragma unroll
-      for (int j = 0; j < 8; j++) v[j] = v[j] / Lsum;
-    } else {
-      const float4 a4 = *reinterpret_cast<const float4*>(sm.xs + baseA);
-      const float4 b4 = *reinterpret_cast<const float4*>(sm.xs + baseB);
-      v[0] = a4.x, v[1] = a4.y, v[2] = a4.z, v[3] = a4.w;
-      v[4] = b4.x, v[5] = b4.y, v[6] = b4.z, v[7] = b4.w;
-    }
-    if (src.kind != SRC_XS) {
-      *reinterpret_cast<float4*>(sm.xs + baseA) = make_float4(v[0], v[1], v[2], v[3]);
-      *reinterpret_cast<float4*>(sm.xs + baseB) = make_float4(v[4], v[5], v[6], v[7]);
-    }
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-      ss = fmaf(v[j], v[j], ss);
-      mx = fmaxf(mx, fabsf(v[j] * w[j]));
-    }
+  const int i = lane & 15;
+  if (i >= (int)c->n) return;
+  if (lane < 16) {
+    const uint32_t off = ((uint32_t)c->al + (uint32_t)i * c->al_step) & 15u;
+    bulk_g2s(base + i * c->pitch, c->src + (size_t)i * c->rb - off, (off + c->seg + 15u) & ~15u, sm.full + slot);
+  } else if (c->aseg) {
+    // scales and biases share their alignment (both tensors start 256-byte aligned in the arena)
+    const uint32_t off = ((uint32_t)c->aal + (uint32_t)i * c->aal_step) & 15u;
+    const uint32_t nb = (off + c->aseg + 15u) & ~15u;
+    uint8_t* d = base + 16 * c->pitch + i * c->apitch;
+    bulk_g2s(d, c->sc + (size_t)i * c->arb - off, nb, sm.full + slot);
+    bulk_g2s(d + 16 * c->apitch, c->bi + (size_t)i * c->arb - off, nb, sm.full + slot);
   }
-  ss = warp_sum(ss);
-  mx = warp_max(mx);
-  consumer_sync();  // red is free (earlier readers are past their last use)
-  if (lane == 0) {
-    red[warp] = ss;
-    red[32 + warp] = mx;
-  }
-  consumer_sync();
-  float tss = 0.f, tmx = 0.f;
-#pragma unroll
-  for (int i = 0; i < MK_CW; i++) {
-    tss += red[i];
-    tmx = fmaxf(tmx, red[32 + i]);
-  }
-  const float inv = nw ? 1.0f / sqrtf(tss / (float)n + eps) : 1.0f;
-  float s, is;
-  scale_for(tmx * inv * 1.0001f, &s, &is);
-  for (int iw = warp * 32; iw < items; iw += MK_CT) {  // whole warps enter, for the shuffles below
-    const int i = iw + lane;
-    const bool live = i < items;
-    const int kb = i >> 2, t = i & 3;
-    const int baseA = kb * 32 + (layout == XL_MLXW ? 8 * t : 4 * t);
-    const int baseB = layout == XL_MLXW ? baseA + 4 : kb * 32 + 16 + 4 * t;
-    float run0 = 0.f, run1 = 0.f;  // this item's share of the block's two 16-element runs
-    if (live) {
-      const float4 a4 = *reinterpret_cast<const float4*>(sm.xs + baseA);  // written by this thread
-      const float4 b4 = *reinterpret_cast<const float4*>(sm.xs + baseB);
-      const float v[8] = {a4.x, a4.y, a4.z, a4.w, b4.x, b4.y, b4.z, b4.w};
-      float sv[8];
-#pragma unroll
-      for (int j = 0; j < 8; j++) {
-        const float wj = nw ? aux_load(reinterpret_cast<const uint8_t*>(nw), nw_type, (j < 4 ? baseA : baseB - 4) + j) : 1.0f;
-        sv[j] = (nw ? __fmul_rn(__fmul_rn(v[j], inv), wj) : v[j]) * s;
-      }
-      const float sa = (sv[0] + sv[1]) + (sv[2] + sv[3]), sb = (sv[4] + sv[5]) + (sv[6] + sv[7]);
-      float f[8];  // fragment order
-      if (layout == XL_NIBBLE) {
-        f[0] = sv[0], f[1] = sv[2], f[2] = sv[4] * 0.0625f, f[3] = sv[6] * 0.0625f;
-        f[4] = sv[1], f[5] = sv[3], f[6] = sv[5] * 0.0625f, f[7] = sv[7] * 0.0625f;
-        run0 = sa, run1 = sb;
-      } else if (layout == XL_MLXW) {
-        f[0] = sv[0], f[1] = sv[4], f[2] = sv[1] * 0.0625f, f[3] = sv[5] * 0.0625f;
-        f[4] = sv[2], f[5] = sv[6], f[6] = sv[3] * 0.0625f, f[7] = sv[7] * 0.0625f;
-        if (t < 2) run0 = sa + sb; else run1 = sa + sb;
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; j++) f[j] = sv[j];
-        run0 = sa, run1 = sb;
-      }
-      __half hi[8], lo[8];
-#pragma unroll
-      for (int j = 0; j < 8; j++) {
-        const __half h = __float2half_rn(f[j]);
-        hi[j] = h;
-        lo[j] = __float2half_rn(f[j] - __half2float(h));
-      }
-      uint4* dst = reinterpret_cast<uint4*>(sm.xf + ((size_t)(kb * 2) * 4 + t) * 8);
-      dst[0] = *reinterpret_cast<uint4*>(hi);
-      dst[4] = *reinterpret_cast<uint4*>(lo);
-    }
-    // the four quarters of a block are four consecutive lanes
-    run0 += __shfl_xor_sync(0xffffffffu, run0, 1);
-    run1 += __shfl_xor_sync(0xffffffffu, run1, 1);
-    run0 += __shfl_xor_sync(0xffffffffu, run0, 2);
-    run1 += __shfl_xor_sync(0xffffffffu, run1, 2);
-    if (live && t == 0) {
-      sm.sx16[2 * kb] = run0;
-      sm.sx16[2 * kb + 1] = run1;
-      sm.sx32[kb] = run0 + run1;
-    }
-  }
-  consumer_sync();
-  return GV_2P24 * is;
-}
-
-// One unit of a chunk for this warp. p0 / p1: the chunk's bytes in rows g, g+8; a0 / a1: MLX
-// scales of those rows (biases 16 * apitch further).
-__device__ __forceinline__ void run_unit(int enc, int aux, int group_shift, const uint8_t* p0,
-                                         const uint8_t* p1, const uint8_t* a0, const uint8_t* a1,
-                                         int apitch16, int u, int kb0, const Smem& sm, int lane,
-                                         TileAcc<true>& acc) {
-  const int t = lane & 3;
-  const int c = (lane >> 2) & 1;
-  const __half* xf0 = sm.xf + (size_t)c * 32 + t * 8;  // block kb adds kb * 64 halfs
-  if (enc == E_Q4_0) {
-    const int kb = kb0 + 2 * u;
-    blk_q4<E_Q4_0, 0, true>(p0 + u * 36, p1 + u * 36, xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc);
-    blk_q4<E_Q4_0, 2, true>(p0 + u * 36 + 18, p1 + u * 36 + 18, xf0 + (size_t)(kb + 1) * 64,
-                            sm.sx32[kb + 1], 0.f, t, acc);
-  } else if (enc == E_Q4_1) {
-    const int kb = kb0 + u;
-    blk_q4<E_Q4_1, 0, true>(p0 + u * 20, p1 + u * 20, xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc);
-  } else if (enc == E_Q8_0) {
-    const int kb = kb0 + 2 * u;
-    blk_q8_0<0, true>(p0 + u * 68, p1 + u * 68, xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc);
-    blk_q8_0<2, true>(p0 + u * 68 + 34, p1 + u * 68 + 34, xf0 + (size_t)(kb + 1) * 64, sm.sx32[kb + 1],
-                      0.f, t, acc);
-  } else if (enc == E_MLX_U4) {
-    const int kb = kb0 + u;
-    const int gi = u >> group_shift;
-    blk_mlx<true>(p0 + u * 16, p1 + u * 16, aux_load(a0, aux, gi), aux_load(a1, aux, gi),
-                  aux_load(a0 + apitch16, aux, gi), aux_load(a1 + apitch16, aux, gi),
-                  xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc);
-  } else {
-    // Q6_K quarter: superblock u / 4 of the chunk, half n, sub-block s
-    const int sb = u >> 2, n = (u >> 1) & 1, s = u & 1;
-    const int kb = kb0 + sb * 8;
-    const uint8_t* s0 = p0 + sb * 210;
-    const uint8_t* s1 = p1 + sb * 210;
-    if (sb & 1)
-      q6k_quarter<2, true>(s0, s1, n, s, xf0 + (size_t)kb * 64, 64, sm.sx16 + 2 * kb, sm.sx16 + 2 * kb, t, acc);
-    else
-      q6k_quarter<0, true>(s0, s1, n, s, xf0 + (size_t)kb * 64, 64, sm.sx16 + 2 * kb, sm.sx16 + 2 * kb, t, acc);
-  }
-}
-
-__device__ __forceinline__ float round_kv(float v, int kv_type) {
-  if (kv_type == E_BF16) return __bfloat162float(__float2bfloat16_rn(v));
-  if (kv_type == E_F16) return __half2float(__float2half_rn(v));
-  return v;
-}
-__device__ __forceinline__ void store_kv(uint8_t* base, int kv_type, int64_t idx, float v) {
-  if (kv_type == E_F32)
-    reinterpret_cast<float*>(base)[idx] = v;
-  else if (kv_type == E_F16)
-    reinterpret_cast<__half*>(base)[idx] = __float2half_rn(v);
-  else
-    reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
-}
-__device__ __forceinline__ bool arg_better(float v, long long i, float bv, long long bi) {
-  return v > bv || (v == bv && i < bi);
 }
 
 __device__ __forceinline__ unsigned long long gtime() {
@@ -416,11 +282,17 @@ __device__ __forceinline__ unsigned long long gtime() {
 // Timing seen by CTA 0, thread 0 (optional). By phase: 0 embed, 1 qkv, 2 attention, 3 o_proj,
 // 4 gate/up, 5 down, 6 lm_head, 7 argmax, 8 whole kernel. Across phases: 9 staging (poll +
 // conversion), 10 waiting for weights, 11 tile math, 12 round reduction + epilogue; attention of
-// CTA 0: 13 until q/k/v are in place, 14 scores and softmax, 15 merge and write.
+// CTA 0: 13 until q/k/v are in place, 14 scores and softmax, 15 merge and write; staging split: 16 until
+// the vector has arrived, 17 reduction + conversion.
 struct Prof {
   unsigned long long* out;
+  unsigned long long* trace;  // this CTA's [layers + 1][16] stamps (thread 0), or nullptr
+  int layer;
   unsigned long long last, start;
   bool on;
+  __device__ void stamp(int id) {
+    if (trace) trace[layer * 16 + id] = gtime();
+  }
   __device__ void begin(unsigned long long* p, bool active) {
     out = p;
     on = active && p != nullptr;
@@ -445,16 +317,345 @@ struct Prof {
   }
 };
 
+// ---- staging the activation vector of a phase ---------------------------------------------------
+// Item i = (block kb = i / 4, lane quarter t = i % 4) holds 8 elements of the vector: A = 4
+// elements at baseA, B = 4 elements at baseB (the items partition the vector). An item's elements
+// come from polled pairs, from the split-KV partials, or from xs (the embedding row).
+//
+// Two ways of staging:
+//   * per warp (stage_local): a warp stages exactly the 32-blocks its own K-slice of the phase's
+//     tiles reads, each block with a power-of-two scale of its own (the tile steps multiply the
+//     block's contribution by 2^24 / scale, isx[kb]), and goes straight on to its tile steps: no
+//     block barrier between the arrival of the vector and the math, and a warp whose slice has
+//     arrived does not wait for the others. RMSNorm is split: the weights are applied here, the
+//     factor 1/sqrt(mean(x^2)+eps) -- a scalar, the product is linear in it -- is applied to the
+//     finished sums; each warp leaves its sum of squares in `red` for the finishing threads.
+//   * whole block (stage_phase): one scale for the vector, RMSNorm applied here; for encodings whose
+//     units share 32-blocks between warps (Q6_K quarters) and for phases of mixed encodings.
+enum { SRC_XS = 0, SRC_LL = 1, SRC_PARTIALS = 2 };
+
+struct StageSrc {
+  int kind;
+  const float* ll;  // SRC_LL: the pair buffer; SRC_PARTIALS: a.ll_part
+  unsigned ep;
+  int nsplit, max_split, d;  // SRC_PARTIALS
+};
+
+__device__ __forceinline__ void item_bases(int layout, int kb, int t, int* baseA, int* baseB) {
+  *baseA = kb * 32 + (layout == XL_MLXW ? 8 * t : 4 * t);
+  *baseB = layout == XL_MLXW ? *baseA + 4 : kb * 32 + 16 + 4 * t;
+}
+
+// The 8 elements of one item.
+__device__ __forceinline__ void item_fetch(const StageSrc& src, int baseA, int baseB, const Smem& sm, float (&v)[8]) {
+  if (src.kind == SRC_LL) {
+    const int64_t idx[4] = {baseA, baseA + 2, baseB, baseB + 2};
+    if (MK_OPT_POLL2) ll_poll2<4>(src.ll, idx, src.ep, v, sm.abort); else ll_poll<4>(src.ll, idx, src.ep, v, sm.abort);
+  } else if (src.kind == SRC_PARTIALS) {
+    // merge the split-KV partial outputs of this item's head in split order (online softmax merge)
+    const int head = baseA / src.d, ia = baseA - head * src.d, ib = baseB - head * src.d;
+    float M = -3.40282347e38f, Lsum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) v[j] = 0.f;
+    for (int s = 0; s < src.nsplit; s++) {
+      const int64_t pb = ((int64_t)head * src.max_split + s) * (src.d + 4);
+      const int64_t idx[5] = {pb + ia, pb + ia + 2, pb + ib, pb + ib + 2, pb + src.d};
+      float p[10];
+      ll_poll<5>(src.ll, idx, src.ep, p, sm.abort);
+      const float ms = p[8], ls = p[9];
+      const float mn = fmaxf(M, ms);
+      const float f = expf(M - mn), wgt = expf(ms - mn);
+#pragma unroll
+      for (int j = 0; j < 8; j++) v[j] = v[j] * f + p[j] * wgt;
+      Lsum = Lsum * f + ls * wgt;
+      M = mn;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) v[j] = v[j] / Lsum;
+  } else {
+    const float4 a4 = *reinterpret_cast<const float4*>(sm.xs + baseA);
+    const float4 b4 = *reinterpret_cast<const float4*>(sm.xs + baseB);
+    v[0] = a4.x, v[1] = a4.y, v[2] = a4.z, v[3] = a4.w;
+    v[4] = b4.x, v[5] = b4.y, v[6] = b4.z, v[7] = b4.w;
+  }
+}
+
+// Writes one item's hi/lo f16 fragments from its 8 scaled values sv and returns its share of the
+// block's two 16-element runs.
+__device__ __forceinline__ void item_store(const float (&sv)[8], int layout, int kb, int t, const Smem& sm, float* run0,
+                                           float* run1) {
+  const float sa = (sv[0] + sv[1]) + (sv[2] + sv[3]), sb = (sv[4] + sv[5]) + (sv[6] + sv[7]);
+  float f[8];  // fragment order
+  if (layout == XL_NIBBLE) {
+    f[0] = sv[0], f[1] = sv[2], f[2] = sv[4] * 0.0625f, f[3] = sv[6] * 0.0625f;
+    f[4] = sv[1], f[5] = sv[3], f[6] = sv[5] * 0.0625f, f[7] = sv[7] * 0.0625f;
+    *run0 = sa, *run1 = sb;
+  } else if (layout == XL_MLXW) {
+    f[0] = sv[0], f[1] = sv[4], f[2] = sv[1] * 0.0625f, f[3] = sv[5] * 0.0625f;
+    f[4] = sv[2], f[5] = sv[6], f[6] = sv[3] * 0.0625f, f[7] = sv[7] * 0.0625f;
+    if (t < 2) *run0 = sa + sb, *run1 = 0.f; else *run0 = 0.f, *run1 = sa + sb;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; j++) f[j] = sv[j];
+    *run0 = sa, *run1 = sb;
+  }
+  __half hi[8], lo[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const __half h = __float2half_rn(f[j]);
+    hi[j] = h;
+    lo[j] = __float2half_rn(f[j] - __half2float(h));
+  }
+  uint4* dst = reinterpret_cast<uint4*>(sm.xf + ((size_t)(kb * 2) * 4 + t) * 8);
+  dst[0] = *reinterpret_cast<uint4*>(hi);
+  dst[4] = *reinterpret_cast<uint4*>(lo);
+}
+
+// Per-warp staging. ukb: 32-blocks per unit of the phase's encoding; the warp owns the units
+// U = warp, warp + 16, ... of the K range (n / 32 blocks), as its tile steps do. `ssq` receives the
+// warp's sum of squares of the raw vector elements it staged.
+__device__ __forceinline__ void stage_local(const StageSrc& src, const void* nw, int nw_type, int n, int ukb,
+                                            int layout, const Smem& sm, float* ssq, int lane, int warp) {
+  const int units = (n >> 5) / ukb;                      // units over the whole K range
+  const int mine = units > warp ? (units - warp + MK_CW - 1) / MK_CW : 0;  // units of this warp
+  const int ipu = 4 * ukb;                               // items per unit
+  float ss = 0.f;
+  for (int i0 = 0; i0 < mine * ipu; i0 += 32) {          // whole warps enter, for the shuffles below
+    const int i = i0 + lane;
+    const bool live = i < mine * ipu;
+    const int j = i / ipu, r = i - j * ipu;
+    const int kb = (warp + MK_CW * j) * ukb + (r >> 2), t = r & 3;
+    int baseA, baseB;
+    item_bases(layout, kb, t, &baseA, &baseB);
+    float run0 = 0.f, run1 = 0.f, mx = 0.f;
+    float v[8];
+    if (live) {
+      // norm weights first: their loads are in flight while the pairs are polled
+      float w[8];
+#pragma unroll
+      for (int q = 0; q < 8; q++)
+        w[q] = nw ? aux_load(reinterpret_cast<const uint8_t*>(nw), nw_type, (q < 4 ? baseA : baseB - 4) + q) : 1.0f;
+      item_fetch(src, baseA, baseB, sm, v);
+#pragma unroll
+      for (int q = 0; q < 8; q++) {
+        ss = fmaf(v[q], v[q], ss);
+        v[q] = __fmul_rn(v[q], w[q]);
+        mx = fmaxf(mx, fabsf(v[q]));
+      }
+    }
+    // the block's own scale: its four items are four consecutive lanes
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    float s, is;
+    scale_for(mx * 1.0001f, &s, &is);
+    if (live) {
+      float sv[8];
+#pragma unroll
+      for (int q = 0; q < 8; q++) sv[q] = v[q] * s;
+      item_store(sv, layout, kb, t, sm, &run0, &run1);
+    }
+    run0 += __shfl_xor_sync(0xffffffffu, run0, 1);
+    run1 += __shfl_xor_sync(0xffffffffu, run1, 1);
+    run0 += __shfl_xor_sync(0xffffffffu, run0, 2);
+    run1 += __shfl_xor_sync(0xffffffffu, run1, 2);
+    if (live && t == 0) {
+      sm.sx16[2 * kb] = run0;
+      sm.sx16[2 * kb + 1] = run1;
+      sm.sx32[kb] = run0 + run1;
+      sm.isx[kb] = GV_2P24 * is;
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) *ssq = ss;
+  __syncwarp();
+}
+
+// Whole-block staging: pass 1 brings each item's elements in, stores them to xs and accumulates
+// the sum of squares and the largest magnitude; one block reduction gives the RMSNorm factor and
+// the power-of-two scale; pass 2 writes the fragments and sums.
+__device__ __forceinline__ void stage_phase(const StageSrc& src, const void* nw, int nw_type, int n, float eps,
+                                            int layout, const Smem& sm, int tid, int lane, int warp) {
+  float* red = sm.misc + MK_OFF_RED;
+  const int items = n >> 3;
+  float ss = 0.f, mx = 0.f;
+  for (int i = tid; i < items; i += MK_CT) {
+    const int kb = i >> 2, t = i & 3;
+    int baseA, baseB;
+    item_bases(layout, kb, t, &baseA, &baseB);
+    float w[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+      w[j] = nw ? aux_load(reinterpret_cast<const uint8_t*>(nw), nw_type, (j < 4 ? baseA : baseB - 4) + j) : 1.0f;
+    float v[8];
+    item_fetch(src, baseA, baseB, sm, v);
+    if (src.kind != SRC_XS) {
+      *reinterpret_cast<float4*>(sm.xs + baseA) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(sm.xs + baseB) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      ss = fmaf(v[j], v[j], ss);
+      mx = fmaxf(mx, fabsf(v[j] * w[j]));
+    }
+  }
+  ss = warp_sum(ss);
+  mx = warp_max(mx);
+  consumer_sync();  // red is free (earlier readers are past their last use)
+  if (lane == 0) {
+    red[warp] = ss;
+    red[16 + warp] = mx;
+  }
+  consumer_sync();
+  float tss = 0.f, tmx = 0.f;
+#pragma unroll
+  for (int i = 0; i < MK_CW; i++) {
+    tss += red[i];
+    tmx = fmaxf(tmx, red[16 + i]);
+  }
+  const float inv = nw ? 1.0f / sqrtf(tss / (float)n + eps) : 1.0f;
+  float s, is;
+  scale_for(tmx * inv * 1.0001f, &s, &is);
+  for (int iw = warp * 32; iw < items; iw += MK_CT) {  // whole warps enter, for the shuffles below
+    const int i = iw + lane;
+    const bool live = i < items;
+    const int kb = i >> 2, t = i & 3;
+    int baseA, baseB;
+    item_bases(layout, kb, t, &baseA, &baseB);
+    float run0 = 0.f, run1 = 0.f;
+    if (live) {
+      const float4 a4 = *reinterpret_cast<const float4*>(sm.xs + baseA);  // written by this thread
+      const float4 b4 = *reinterpret_cast<const float4*>(sm.xs + baseB);
+      const float v[8] = {a4.x, a4.y, a4.z, a4.w, b4.x, b4.y, b4.z, b4.w};
+      float sv[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const float wj = nw ? aux_load(reinterpret_cast<const uint8_t*>(nw), nw_type, (j < 4 ? baseA : baseB - 4) + j) : 1.0f;
+        sv[j] = (nw ? __fmul_rn(__fmul_rn(v[j], inv), wj) : v[j]) * s;
+      }
+      item_store(sv, layout, kb, t, sm, &run0, &run1);
+    }
+    run0 += __shfl_xor_sync(0xffffffffu, run0, 1);
+    run1 += __shfl_xor_sync(0xffffffffu, run1, 1);
+    run0 += __shfl_xor_sync(0xffffffffu, run0, 2);
+    run1 += __shfl_xor_sync(0xffffffffu, run1, 2);
+    if (live && t == 0) {
+      sm.sx16[2 * kb] = run0;
+      sm.sx16[2 * kb + 1] = run1;
+      sm.sx32[kb] = run0 + run1;
+      sm.isx[kb] = GV_2P24 * is;
+    }
+  }
+  consumer_sync();
+}
+
+// One unit of a chunk for this warp. p0 / p1: the chunk's bytes in rows g, g+8; a0 / a1: MLX
+// scales of those rows (biases 16 * apitch further).
+template <int ENC>
+__device__ __forceinline__ void run_unit_t(int aux, int group_shift, const uint8_t* p0, const uint8_t* p1,
+                                           const uint8_t* a0, const uint8_t* a1, int apitch16, int u, int kb0,
+                                           const Smem& sm, int lane, TileAcc<true>& acc) {
+  const int t = lane & 3;
+  const int c = (lane >> 2) & 1;
+  const __half* xf0 = sm.xf + (size_t)c * 32 + t * 8;  // block kb adds kb * 64 halfs
+  if (ENC == E_Q4_0) {
+    const int kb = kb0 + 2 * u;
+    blk_q4<E_Q4_0, 0, true>(p0 + u * 36, p1 + u * 36, xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc, sm.isx[kb]);
+    blk_q4<E_Q4_0, 2, true>(p0 + u * 36 + 18, p1 + u * 36 + 18, xf0 + (size_t)(kb + 1) * 64,
+                            sm.sx32[kb + 1], 0.f, t, acc, sm.isx[kb + 1]);
+  } else if (ENC == E_Q4_1) {
+    const int kb = kb0 + u;
+    blk_q4<E_Q4_1, 0, true>(p0 + u * 20, p1 + u * 20, xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc, sm.isx[kb]);
+  } else if (ENC == E_Q8_0) {
+    const int kb = kb0 + 2 * u;
+    blk_q8_0<0, true>(p0 + u * 68, p1 + u * 68, xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc, sm.isx[kb]);
+    blk_q8_0<2, true>(p0 + u * 68 + 34, p1 + u * 68 + 34, xf0 + (size_t)(kb + 1) * 64, sm.sx32[kb + 1],
+                      0.f, t, acc, sm.isx[kb + 1]);
+  } else if (ENC == E_MLX_U4) {
+    const int kb = kb0 + u;
+    const int gi = u >> group_shift;
+    const float bs = sm.isx[kb];
+    blk_mlx<true>(p0 + u * 16, p1 + u * 16, aux_load(a0, aux, gi) * bs, aux_load(a1, aux, gi) * bs,
+                  aux_load(a0 + apitch16, aux, gi) * bs, aux_load(a1 + apitch16, aux, gi) * bs,
+                  xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc);
+  } else {
+    // Q6_K quarter: superblock u / 4 of the chunk, half n, sub-block s
+    const int sb = u >> 2, n = (u >> 1) & 1, s = u & 1;
+    const int kb = kb0 + sb * 8;
+    const uint8_t* s0 = p0 + sb * 210;
+    const uint8_t* s1 = p1 + sb * 210;
+    // the quarter spans four 32-blocks: Q6_K phases stage the whole vector with one scale
+    const float bs = sm.isx[kb];
+    if (sb & 1)
+      q6k_quarter<2, true>(s0, s1, n, s, xf0 + (size_t)kb * 64, 64, sm.sx16 + 2 * kb, sm.sx16 + 2 * kb, t, acc, bs);
+    else
+      q6k_quarter<0, true>(s0, s1, n, s, xf0 + (size_t)kb * 64, 64, sm.sx16 + 2 * kb, sm.sx16 + 2 * kb, t, acc, bs);
+  }
+}
+// ENC < 0: the chunk says which encoding it holds (phases whose tensors differ).
+template <int ENC>
+__device__ __forceinline__ void run_unit(int enc, int aux, int group_shift, const uint8_t* p0, const uint8_t* p1,
+                                         const uint8_t* a0, const uint8_t* a1, int apitch16, int u, int kb0,
+                                         const Smem& sm, int lane, TileAcc<true>& acc) {
+  if (ENC >= 0) {
+    run_unit_t<ENC < 0 ? E_Q4_0 : ENC>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc);
+    return;
+  }
+  switch (enc) {
+    case E_Q4_0: run_unit_t<E_Q4_0>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc); break;
+    case E_Q4_1: run_unit_t<E_Q4_1>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc); break;
+    case E_Q8_0: run_unit_t<E_Q8_0>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc); break;
+    case E_MLX_U4: run_unit_t<E_MLX_U4>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc); break;
+    default: run_unit_t<E_Q6_K>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc); break;
+  }
+}
+
+__device__ __forceinline__ float round_kv(float v, int kv_type) {
+  if (kv_type == E_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  if (kv_type == E_F16) return __half2float(__float2half_rn(v));
+  return v;
+}
+__device__ __forceinline__ void store_kv(uint8_t* base, int kv_type, int64_t idx, float v) {
+  if (kv_type == E_F32)
+    reinterpret_cast<float*>(base)[idx] = v;
+  else if (kv_type == E_F16)
+    reinterpret_cast<__half*>(base)[idx] = __float2half_rn(v);
+  else
+    reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ bool arg_better(float v, long long i, float bv, long long bi) {
+  return v > bv || (v == bv && i < bi);
+}
+
 // ---- attention for one (head, split); head dim 64 or 128, a lane owns 4 head dims ----------------
 // Latency plan: the cached keys and values of earlier positions and the norm weights are requested
 // first; then warps 0 / 1 / 2 poll this token's q / k / v of the head (one or two lines per lane),
 // normalise and rotate them inside the warp (no block reduction) and leave them in shared memory.
-__device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const MegaLayer* L, int cta,
+// The cached rows [k_lo, min(k_hi, pos)) of this CTA's (head, split) in layer l: one run per pool.
+__device__ __forceinline__ void prefetch_kv(const MegaArgs& a, int l, int cta, int64_t pos, int64_t seq, int nsplit,
+                                            int tid) {
+  if (cta >= a.nh * nsplit || l >= a.layers || (a.opts & 1)) return;
+  const int h = cta / nsplit, sp = cta - h * nsplit;
+  const int kvh = h / (a.nh / a.nkv);
+  const int64_t n = pos + 1, per = (n + nsplit - 1) / nsplit;
+  const int64_t k_lo = (int64_t)sp * per;
+  int64_t k_hi = (k_lo + per < n) ? k_lo + per : n;
+  if (k_hi > pos) k_hi = pos;
+  if (k_hi <= k_lo) return;
+  const size_t el = a.kv_type == E_F32 ? 4 : 2;
+  const size_t start = (size_t)(((seq * a.nkv + kvh) * a.cap + k_lo) * a.d) * el;
+  const size_t bytes = (size_t)(k_hi - k_lo) * a.d * el;
+  prefetch_span(a.kcache + (uint64_t)l * a.layer_stride + start, bytes, tid, MK_CT);
+  prefetch_span(a.vcache + (uint64_t)l * a.layer_stride + start, bytes, tid, MK_CT);
+}
+
+template <bool WIDE>  // f32 cache (16 bytes per lane and row) or a 2-byte type (8 bytes)
+__device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, const MegaLayerHot* L, int cta,
                                                 int64_t pos, int64_t seq, int nsplit, unsigned ep,
                                                 const Smem& sm, int tid, int lane, int warp, Prof& prof) {
   if (cta >= a.nh * nsplit) return;
   unsigned long long tp = prof.tic();
-  constexpr int KB = 4;   // keys in flight per warp
+  // keys in flight per warp: with a 2-byte cache one batch covers the 64 keys of a split
+  constexpr int KB = (WIDE ? 32 : 64) / MK_CW;
   constexpr int DPL = 4;  // head dims per lane
   const int h = cta / nsplit, sp = cta - h * nsplit;
   const int grp = a.nh / a.nkv, kvh = h / grp, gi = h - kvh * grp;
@@ -469,25 +670,26 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
   uint8_t* kc = a.kcache + (uint64_t)l * a.layer_stride;
   uint8_t* vc = a.vcache + (uint64_t)l * a.layer_stride;
   const int64_t plane = ((seq * a.nkv + kvh) * a.cap) * d;  // element offset of this head's plane
-  const int64_t n = pos + 1;
-  const int64_t per = (n + nsplit - 1) / nsplit;
-  const int64_t k_lo = (int64_t)sp * per;
-  const int64_t k_hi = (k_lo + per < n) ? k_lo + per : n;
+  const int pos32 = (int)pos;  // positions are below the cache capacity, which fits 31 bits
+  const int n = pos32 + 1;
+  const int per = (n + nsplit - 1) / nsplit;
+  const int k_lo = sp * per;
+  const int k_hi = (k_lo + per < n) ? k_lo + per : n;
   // A lane owns DPL consecutive head dims (one 8- or 16-byte piece of every cached row), so a
   // warp reads a key or value row with one coalesced vector load.
-  const bool wide = a.kv_type == E_F32;
+  constexpr int WPL = WIDE ? DPL : DPL / 2;  // raw words per lane and row
   const int e0 = lane * DPL;  // first head dim of this lane
   const bool lane_live = e0 < d;
-  uint32_t kraw[KB][DPL], vraw[KB][DPL];
-  auto fetch = [&](int64_t key0) {
+  uint32_t kraw[KB][WPL], vraw[KB][WPL];
+  auto fetch = [&](int key0) {
 #pragma unroll
     for (int b = 0; b < KB; b++) {
-      const int64_t key = key0 + (int64_t)b * MK_CW;
+      const int key = key0 + b * MK_CW;
 #pragma unroll
-      for (int w = 0; w < DPL; w++) kraw[b][w] = vraw[b][w] = 0;
-      if (key < k_hi && key != pos && lane_live) {
-        const int64_t el = plane + key * d + e0;
-        if (wide) {
+      for (int w = 0; w < WPL; w++) kraw[b][w] = vraw[b][w] = 0;
+      if (key < k_hi && key != pos32 && lane_live) {
+        const int64_t el = plane + (int64_t)key * d + e0;
+        if constexpr (WIDE) {
           const uint4 kk = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(kc) + el));
           const uint4 vv = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(vc) + el));
           kraw[b][0] = kk.x, kraw[b][1] = kk.y, kraw[b][2] = kk.z, kraw[b][3] = kk.w;
@@ -501,11 +703,18 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
       }
     }
   };
-  // element j of a raw row piece as f32
-  auto elem = [&](const uint32_t (&raw)[DPL], int j) -> float {
-    if (wide) return __uint_as_float(raw[j]);
-    const uint32_t bits = (raw[j >> 1] >> (16 * (j & 1))) & 0xffffu;
-    return a.kv_type == E_F16 ? f16_bits_to_f32(bits) : bf16_bits_to_f32(bits);
+  // a raw row piece as f32 (one branch per piece, not per element)
+  auto unpack = [&](const uint32_t (&raw)[WPL], float (&f)[DPL]) {
+    if constexpr (WIDE) {
+#pragma unroll
+      for (int j = 0; j < DPL; j++) f[j] = __uint_as_float(raw[j]);
+    } else if (a.kv_type == E_BF16) {
+      f[0] = __uint_as_float(raw[0] << 16), f[1] = __uint_as_float(raw[0] & 0xffff0000u);
+      f[2] = __uint_as_float(raw[1] << 16), f[3] = __uint_as_float(raw[1] & 0xffff0000u);
+    } else {
+      f[0] = f16_bits_to_f32(raw[0] & 0xffffu), f[1] = f16_bits_to_f32(raw[0] >> 16);
+      f[2] = f16_bits_to_f32(raw[1] & 0xffffu), f[3] = f16_bits_to_f32(raw[1] >> 16);
+    }
   };
   fetch(k_lo + warp);  // in flight while q / k / v of this token arrive
 
@@ -524,7 +733,7 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
     float x[4] = {0.f, 0.f, 0.f, 0.f};  // x1a x1b x2a x2b
     if (act) {
       const int64_t idx[2] = {base + i0, base + i0 + half};
-      ll_poll<2>(a.ll_qkv, idx, ep, x, sm.abort);
+      if (MK_OPT_POLL2) ll_poll2<2>(a.ll_qkv, idx, ep, x, sm.abort); else ll_poll<2>(a.ll_qkv, idx, ep, x, sm.abort);
     }
     if (warp < 2) {
       if (a.has_norm) {
@@ -555,6 +764,7 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
     }
   }
   consumer_sync();
+  prof.stamp(3);
   prof.toc(13, tp);
   tp = prof.tic();
   if (sp == 0 && gi == 0) {
@@ -571,37 +781,52 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
     acc[j] = 0.f;
   }
   float m = -3.40282347e38f, lsum = 0.f;
-  for (int64_t key0 = k_lo + warp; key0 < k_hi; key0 += (int64_t)KB * MK_CW) {
+  for (int key0 = k_lo + warp; key0 < k_hi; key0 += KB * MK_CW) {
     if (key0 != k_lo + warp) fetch(key0);
     float sc[KB];
 #pragma unroll
     for (int b = 0; b < KB; b++) {
-      const int64_t key = key0 + (int64_t)b * MK_CW;
-      float dot = 0.f;
-      if (lane_live) {
+      float kf[DPL];
+      unpack(kraw[b], kf);
+      if (key0 + b * MK_CW == pos32 && lane_live) {  // this token's own key (warp-uniform)
 #pragma unroll
-        for (int j = 0; j < DPL; j++) dot = fmaf(qreg[j], key == pos ? kn[e0 + j] : elem(kraw[b], j), dot);
+        for (int j = 0; j < DPL; j++) kf[j] = kn[e0 + j];
       }
+      float dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < DPL; j++) dot = fmaf(qreg[j], kf[j], dot);
       sc[b] = warp_sum(dot) * scale;
     }
+    // one rescale per batch: the batch maximum first, then independent exponentials
+    float mb = m;
+#pragma unroll
+    for (int b = 0; b < KB; b++)
+      if (key0 + b * MK_CW < k_hi) mb = fmaxf(mb, sc[b]);
+    const float factor = expf(m - mb);
+    float p[KB];
+#pragma unroll
+    for (int b = 0; b < KB; b++) p[b] = key0 + b * MK_CW < k_hi ? expf(sc[b] - mb) : 0.f;
+    float psum = 0.f;
+#pragma unroll
+    for (int b = 0; b < KB; b++) psum += p[b];
+    lsum = lsum * factor + psum;
+#pragma unroll
+    for (int j = 0; j < DPL; j++) acc[j] *= factor;
 #pragma unroll
     for (int b = 0; b < KB; b++) {
-      const int64_t key = key0 + (int64_t)b * MK_CW;
-      if (key < k_hi) {
-        const float mn = fmaxf(m, sc[b]);
-        const float factor = expf(m - mn);
-        const float p = expf(sc[b] - mn);
-        lsum = lsum * factor + p;
-        if (lane_live) {
+      float vf[DPL];
+      unpack(vraw[b], vf);
+      if (key0 + b * MK_CW == pos32 && lane_live) {
 #pragma unroll
-          for (int j = 0; j < DPL; j++)
-            acc[j] = acc[j] * factor + p * (key == pos ? vn[e0 + j] : elem(vraw[b], j));
-        }
-        m = mn;
+        for (int j = 0; j < DPL; j++) vf[j] = vn[e0 + j];
       }
+#pragma unroll
+      for (int j = 0; j < DPL; j++) acc[j] = fmaf(p[b], vf[j], acc[j]);
     }
+    m = mb;
   }
   prof.toc(14, tp);
+  prof.stamp(14);
   tp = prof.tic();
   if (lane == 0) {
     wm[warp] = m;
@@ -618,10 +843,11 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
   // each warp's weight exp(m_w - gm) once, by one lane per warp, instead of per output element
   if (tid < MK_CW) wwt[tid] = expf(wm[tid] - gm);
   consumer_sync();
+  prof.stamp(15);
   float gl = 0.f;
 #pragma unroll
   for (int w = 0; w < MK_CW; w++) gl += wl[w] * wwt[w];
-  const int64_t pbase = ((int64_t)h * a.max_split + sp) * (d + 2);
+  const int64_t pbase = ((int64_t)h * a.max_split + sp) * (d + 4);
   for (int idx = tid; idx < d; idx += MK_CT) {
     float o = 0.f;
 #pragma unroll
@@ -635,7 +861,236 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
     ll_store(a.ll_part, pbase + d, gm, ep);
     ll_store(a.ll_part, pbase + d + 1, gl, ep);
   }
+  prof.stamp(4);
   prof.toc(15, tp);
+  prefetch_kv(a, l + 1, cta, pos, seq, nsplit, tid);  // the next layer's rows: in L2 by the time they are read
+}
+
+__device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const MegaLayerHot* L, int cta,
+                                                int64_t pos, int64_t seq, int nsplit, unsigned ep,
+                                                const Smem& sm, int tid, int lane, int warp, Prof& prof) {
+  if (a.kv_type == E_F32)
+    phase_attention_t<true>(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
+  else
+    phase_attention_t<false>(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
+}
+
+// ---- one phase's rounds, in program order ---------------------------------------------------------
+struct Walk {
+  uint32_t ci, ri, ti;    // next chunk, round, tile of this CTA's program
+  uint32_t slot, parity;  // ring position of chunk ci
+  // the next chunk whose copies are to be issued: sequence number over the launch, index in the
+  // program, token of the launch, ring slot and lap
+  uint32_t fill_seq, fill_idx, fill_step, fill_slot, fill_lap;
+  unsigned nround;        // rounds so far (selects the partial-sum buffer)
+  unsigned nlocal;        // per-warp stagings so far (selects the sum-of-squares buffer)
+  float bv;               // running argmax over the rows this thread finishes
+  long long bi;
+};
+
+// Issues the copies of one more chunk (all warps keep the same counters; the warp whose turn it is
+// acts). The target slot was left by the chunk before the one just finished; its release by all
+// sixteen warps is waited for, bounded.
+__device__ __forceinline__ void refill(const MegaArgs& a, const Smem& sm, Walk& w, int lane, int warp) {
+  if (MK_PRODUCER_WARP || w.fill_step >= (uint32_t)a.steps) return;
+  if (warp == (int)(w.fill_seq & (MK_CW - 1))) produce_chunk(sm.chunks + w.fill_idx, sm, (int)w.fill_slot, w.fill_lap, lane);
+  w.fill_seq++;
+  if (++w.fill_idx == sm.nchunks) w.fill_idx = 0, w.fill_step++;
+  if (++w.fill_slot == (uint32_t)sm.nslot) w.fill_slot = 0, w.fill_lap++;
+}
+
+template <int ENC>
+__device__ __forceinline__ void run_phase_t(const MegaArgs& a, const Smem& sm, Walk& w, int nr, unsigned ep,
+                                            const float* ssq, int n_in, float* res, int hid_lo, int tid, int lane,
+                                            int warp, Prof& prof, int sid) {
+  const int g = lane >> 2;
+  for (int r = 0; r < nr; r++, w.ri++) {
+    const MegaRound R = sm.rounds[w.ri];
+    float* pb = sm.misc + MK_OFF_PART + (w.nround & 1u) * MK_PART;
+    w.nround++;
+    // chunks of one tile follow each other: a tile's sums stay in registers until the next tile begins
+    TileAcc<true> t;
+    t.clear();
+    int cur = -1;
+    auto flush = [&]() {
+      if (cur >= 0 && (lane & 3) == 0) {
+        pb[(cur * MK_CW + warp) * 16 + g] = t.v[0];
+        pb[(cur * MK_CW + warp) * 16 + g + 8] = t.v[1];
+      }
+    };
+    // Geometry of one chunk for this lane, from the 16 bytes a consumer reads.
+    struct Geo {
+      const uint8_t *p0, *p1, *a0, *a1;
+      int nu, enc, aux, gs, kb0, apitch16;
+    };
+    auto geometry = [&](const uint4& hot, int slot) {
+      Geo q;
+      const int pitch = (int)(hot.x & 0xffffu);
+      const int n = (int)(hot.y & 0xffu);
+      const int al = (int)(hot.z & 0xffu), al_step = (int)((hot.z >> 8) & 0xffu);
+      const int apitch = (int)(hot.w & 0xffffu);
+      q.kb0 = (int)(hot.x >> 16), q.nu = (int)((hot.y >> 8) & 0xffu), q.enc = (int)(hot.y >> 24);
+      q.aux = (int)((hot.z >> 16) & 0xffu), q.gs = (int)(hot.z >> 24), q.apitch16 = 16 * apitch;
+      const uint8_t* base = sm.ring + (size_t)slot * MK_SLOT;
+      const int i0 = g < n ? g : n - 1, i1 = g + 8 < n ? g + 8 : n - 1;  // clamp to valid rows
+      q.p0 = base + i0 * pitch + ((al + i0 * al_step) & 15);
+      q.p1 = base + i1 * pitch + ((al + i1 * al_step) & 15);
+      q.a0 = q.a1 = nullptr;
+      if (apitch) {
+        const int aal = (int)((hot.w >> 16) & 0xffu), aal_step = (int)(hot.w >> 24);
+        const uint8_t* ab = base + 16 * pitch;
+        q.a0 = ab + i0 * apitch + ((aal + i0 * aal_step) & 15);
+        q.a1 = ab + i1 * apitch + ((aal + i1 * aal_step) & 15);
+      }
+      return q;
+    };
+    auto release = [&](int slot) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.empty + slot);
+      if (++w.slot == (uint32_t)sm.nslot) w.slot = 0, w.parity ^= 1u;
+      refill(a, sm, w, lane, warp);
+    };
+    for (int k = 0; k < (int)R.nchunks;) {
+      const uint4 hot = *reinterpret_cast<const uint4*>(sm.chunks + w.ci);
+      const int which = (int)((hot.y >> 16) & 0xffu);
+      const int slot = (int)w.slot;
+      const unsigned long long tw = prof.tic();
+      bool ok = mbar_wait_bounded(sm.full + slot, w.parity, MK_MBAR_SPINS, sm.abort);
+      // Two tiles at a time where the next chunk belongs to another tile: their tile steps are
+      // independent, and issued side by side they hide each other's latencies.
+      uint4 hot2 = hot;
+      bool pair = false;
+      if (k + 1 < (int)R.nchunks) {
+        hot2 = *reinterpret_cast<const uint4*>(sm.chunks + w.ci + 1);
+        pair = MK_OPT_PAIRS && (int)((hot2.y >> 16) & 0xffu) != which && ((hot2.y >> 8) & 0xffu) == ((hot.y >> 8) & 0xffu);
+      }
+      int slot2 = slot + 1;
+      unsigned parity2 = w.parity;
+      if (slot2 == sm.nslot) slot2 = 0, parity2 ^= 1u;
+      if (pair) ok = mbar_wait_bounded(sm.full + slot2, parity2, MK_MBAR_SPINS, sm.abort) && ok;
+      if (!ok && !*sm.abort) *sm.abort = 3;
+      prof.toc(10, tw);
+      const unsigned long long tr = prof.tic();
+      if (which != cur) {
+        flush();
+        t.clear();
+        cur = which;
+      }
+      if (!pair) {
+        if (ok) {
+          const Geo q = geometry(hot, slot);
+          // two K-slices of the tile side by side (a second accumulator), for the same reason
+          TileAcc<true> t2;
+          t2.clear();
+          int u = warp;
+          for (; MK_OPT_KSLICE2 && u + MK_CW < q.nu; u += 2 * MK_CW) {
+            run_unit<ENC>(q.enc, q.aux, q.gs, q.p0, q.p1, q.a0, q.a1, q.apitch16, u, q.kb0, sm, lane, t);
+            run_unit<ENC>(q.enc, q.aux, q.gs, q.p0, q.p1, q.a0, q.a1, q.apitch16, u + MK_CW, q.kb0, sm, lane, t2);
+          }
+          for (; u < q.nu; u += MK_CW) run_unit<ENC>(q.enc, q.aux, q.gs, q.p0, q.p1, q.a0, q.a1, q.apitch16, u, q.kb0, sm, lane, t);
+          t.v[0] += t2.v[0];
+          t.v[1] += t2.v[1];
+        }
+        prof.toc(11, tr);
+        release(slot);
+        k += 1, w.ci += 1;
+      } else {
+        TileAcc<true> t2;
+        t2.clear();
+        if (ok) {
+          const Geo q = geometry(hot, slot), q2 = geometry(hot2, slot2);
+          for (int u = warp; u < q.nu; u += MK_CW) {
+            run_unit<ENC>(q.enc, q.aux, q.gs, q.p0, q.p1, q.a0, q.a1, q.apitch16, u, q.kb0, sm, lane, t);
+            run_unit<ENC>(q2.enc, q2.aux, q2.gs, q2.p0, q2.p1, q2.a0, q2.a1, q2.apitch16, u, q2.kb0, sm, lane, t2);
+          }
+        }
+        prof.toc(11, tr);
+        release(slot);
+        release(slot2);
+        flush();  // the first tile of the pair is complete unless more of its slices follow; the second goes on
+        t = t2;
+        cur = (int)((hot2.y >> 16) & 0xffu);
+        k += 2, w.ci += 2;
+      }
+    }
+    flush();
+    prof.stamp(sid + 1);
+    // the sixteen K-slice partials of every tile of the round meet here, once
+    const unsigned long long tc = prof.tic();
+    consumer_sync();
+    const int nt = R.ntiles;
+    if (tid < nt * 16) {
+      const MegaTile T = sm.tiles[w.ti + (tid >> 4)];
+      const int row = tid & 15;
+      if (row < (int)T.n) {
+        // per-warp staging leaves RMSNorm's scalar factor to be applied here
+        float out_scale = 1.0f;
+        if (ssq) {
+          float tss = 0.f;
+#pragma unroll
+          for (int wv = 0; wv < MK_CW; wv++) tss += ssq[wv];
+          out_scale = 1.0f / sqrtf(tss / (float)n_in + a.eps);
+        }
+        const float* p1 = pb + (int)T.acc * MK_CW * 16 + row;
+        float s0 = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < MK_CW; wv++) s0 += p1[wv * 16];
+        s0 *= out_scale;
+        const int64_t orow = (int64_t)T.out_row + row;
+        if (T.ep == MEGA_EP_QKV) {
+          ll_store(a.ll_qkv, orow, s0, ep);
+        } else if (T.ep == MEGA_EP_RESID_O || T.ep == MEGA_EP_RESID_DOWN) {
+          const float hnew = res[orow - hid_lo] + s0;
+          res[orow - hid_lo] = hnew;
+          ll_store(a.ll_hidden[T.ep == MEGA_EP_RESID_O ? 0 : 1], orow, hnew, ep);
+        } else if (T.ep == MEGA_EP_SWIGLU) {
+          const float* p2 = pb + (int)T.acc2 * MK_CW * 16 + row;
+          float s1 = 0.f;
+#pragma unroll
+          for (int wv = 0; wv < MK_CW; wv++) s1 += p2[wv * 16];
+          s1 *= out_scale;
+          ll_store(a.ll_act, orow, (s0 / (1.0f + expf(-s0))) * s1, ep);
+        } else {
+          a.logits[orow] = s0;
+          if (s0 > -INFINITY && arg_better(s0, orow, w.bv, w.bi)) w.bv = s0, w.bi = orow;
+        }
+      }
+    }
+    w.ti += nt;
+    prof.stamp(sid + 2);
+    prof.toc(12, tc);
+  }
+}
+
+// phase word: low byte = rounds, high byte = the phase's common encoding (0xff: per chunk)
+// Stages the phase's input vector (per warp where the encoding allows) and runs its rounds. A CTA
+// without rows in the phase neither waits for the vector nor stages it.
+__device__ __forceinline__ void run_phase(const MegaArgs& a, const Smem& sm, Walk& w, int phase_index, unsigned ep,
+                                          const StageSrc& src, const void* nw, int nw_type, int n_in, int layout_enc,
+                                          float* res, int hid_lo, int tid, int lane, int warp, Prof& prof) {
+  const unsigned word = sm.phase_rounds[phase_index];
+  const int nr = (int)(word & 0xffu), enc = (int)(word >> 8);
+  if (nr == 0) return;
+  const unsigned long long ts = prof.tic();
+  const float* ssq = nullptr;
+  if (MK_OPT_LOCAL && (enc == E_Q4_0 || enc == E_Q4_1 || enc == E_Q8_0 || enc == E_MLX_U4)) {
+    float* mine = sm.misc + MK_OFF_RED + 32 + (w.nlocal & 1u) * MK_CW;  // consecutive per-warp stages alternate
+    w.nlocal++;
+    stage_local(src, nw, nw_type, n_in, (enc == E_Q4_0 || enc == E_Q8_0) ? 2 : 1, xl_for_encoding(enc), sm, mine + warp,
+                lane, warp);
+    if (nw) ssq = mine;
+  } else {
+    stage_phase(src, nw, nw_type, n_in, a.eps, xl_for_encoding(layout_enc), sm, tid, lane, warp);
+  }
+  prof.toc(9, ts);
+  const int sid = (phase_index & 3) == 0 ? 0 : 2 + 3 * (phase_index & 3);  // 0, 5, 8, 11
+  prof.stamp(sid);
+  if (enc == E_Q4_0)
+    run_phase_t<E_Q4_0>(a, sm, w, nr, ep, ssq, n_in, res, hid_lo, tid, lane, warp, prof, sid);
+  else if (enc == E_Q6_K)
+    run_phase_t<E_Q6_K>(a, sm, w, nr, ep, ssq, n_in, res, hid_lo, tid, lane, warp, prof, sid);
+  else
+    run_phase_t<-1>(a, sm, w, nr, ep, ssq, n_in, res, hid_lo, tid, lane, warp, prof, sid);
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------
@@ -651,7 +1106,8 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
   sm.xf = reinterpret_cast<__half*>(sm.xs + a.xs_floats);
   sm.sx32 = reinterpret_cast<float*>(sm.xf + (size_t)a.xs_floats * 2);
   sm.sx16 = sm.sx32 + a.xs_floats / 32;
-  sm.misc = sm.sx16 + a.xs_floats / 16;
+  sm.isx = sm.sx16 + a.xs_floats / 16;
+  sm.misc = sm.isx + a.xs_floats / 32;
   sm.ring = reinterpret_cast<uint8_t*>(sm.misc + MK_MISC_FLOATS);
   sm.full = reinterpret_cast<uint64_t*>(sm.ring + (size_t)a.nslot * MK_SLOT);
   sm.empty = sm.full + a.nslot;
@@ -677,124 +1133,46 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
   sm.tiles = reinterpret_cast<const MegaTile*>(prog_area + a.lay.off_tiles);
   sm.rounds = reinterpret_cast<const MegaRound*>(prog_area + a.lay.off_rounds);
   sm.phase_rounds = reinterpret_cast<const uint16_t*>(prog_area + a.lay.off_phase);
+  sm.hot = reinterpret_cast<const MegaLayerHot*>(prog_area + a.lay.off_layers);
 
-  if (warp == MK_CW) {
+  sm.nchunks = hdr->nchunks;
+  if (MK_PRODUCER_WARP && warp == MK_CW) {
     // ------------------------------ producer: stream this CTA's weight tiles --------------
     const int total = *sm.abort ? 0 : (int)hdr->nchunks;
-    for (int pi = 0; pi < total; pi++) produce_chunk(sm.chunks + pi, sm, (uint32_t)pi, lane);
+    int slot = 0;
+    uint32_t lap = 0;
+    for (int step = 0; step < a.steps; step++)  // the same program for every token of the launch
+      for (int pi = 0; pi < total; pi++) {
+        produce_chunk(sm.chunks + pi, sm, slot, lap, lane);
+        if (++slot == sm.nslot) slot = 0, lap++;
+      }
     return;
   }
-
   // -------------------------------- consumers -------------------------------------------------
-  const int64_t token = __ldcg(a.io + 0), pos = __ldcg(a.io + 1), seq = __ldcg(a.io + 2);
+  int64_t token = __ldcg(a.io + 0), pos = __ldcg(a.io + 1);
+  const int64_t seq = __ldcg(a.io + 2);
+  const int64_t qd = (int64_t)a.nh * a.d;
+  const int hid_lo = (int)hdr->hid_lo;
+  float* res = sm.misc + MK_OFF_RES;
+  Walk wk;
+  wk.ci = wk.ri = wk.ti = 0, wk.slot = 0, wk.parity = 0, wk.nround = 0, wk.nlocal = 0;
+  wk.bv = -INFINITY, wk.bi = 0x7fffffffffffffffLL;
+  wk.fill_seq = wk.fill_idx = wk.fill_slot = wk.fill_lap = 0;
+  wk.fill_step = (sm.nchunks == 0 || *sm.abort) ? (uint32_t)a.steps : 0u;
+  for (int i = 0; i < sm.nslot - 1; i++) refill(a, sm, wk, lane, warp);  // the ring's first fill: warp i issues chunk i
+  Prof prof;
+  // One launch decodes a.steps tokens: every CTA learns each token from the argmax hand-off and goes
+  // on with the next position; the weight ring and its barriers simply keep running.
+  for (int step = 0; step < a.steps; step++) {
+  const unsigned epoch_base = a.epoch_base + (unsigned)step * (unsigned)(a.layers + 2);
   int nsplit = (int)((pos + 1 + 63) / 64);
   if (nsplit > a.max_split) nsplit = a.max_split;
   if (nsplit < 1) nsplit = 1;
-  const int64_t qd = (int64_t)a.nh * a.d;
-  const int g = lane >> 2;
-  const int hid_lo = (int)hdr->hid_lo;
-  float* res = sm.misc + MK_OFF_RES;
-  uint32_t ci = 0, ri = 0, ti = 0;
-  unsigned nround = 0;
-  float bv = -INFINITY;  // running argmax over the rows this thread finishes
-  long long bi = 0x7fffffffffffffffLL;
-  Prof prof;
+  wk.ci = wk.ri = wk.ti = 0;
+  wk.bv = -INFINITY, wk.bi = 0x7fffffffffffffffLL;
   prof.begin(a.prof, cta == 0 && tid == 0);
-
-  // One phase's rounds, in program order.
-  auto run_phase = [&](int phase_index, unsigned ep, float out_scale) {
-    const int nr = sm.phase_rounds[phase_index];
-    for (int r = 0; r < nr; r++, ri++) {
-      const MegaRound R = sm.rounds[ri];
-      TileAcc<true> acc[MEGA_TA];
-#pragma unroll
-      for (int j = 0; j < MEGA_TA; j++) acc[j].clear();
-      for (int k = 0; k < (int)R.nchunks; k++, ci++) {
-        const MegaChunk* c = sm.chunks + ci;
-        const int slot = ci % sm.nslot;
-        const unsigned long long tw = prof.tic();
-        const bool ok = mbar_wait_bounded(sm.full + slot, (ci / sm.nslot) & 1u, MK_MBAR_SPINS, sm.abort);
-        if (!ok && !*sm.abort) *sm.abort = 3;
-        prof.toc(10, tw);
-        const unsigned long long tr = prof.tic();
-        if (ok) {
-          const int n = c->n, nu = c->nu;
-          const uint8_t* base = sm.ring + (size_t)slot * MK_SLOT;
-          const int i0 = g < n ? g : n - 1, i1 = g + 8 < n ? g + 8 : n - 1;  // clamp to valid rows
-          const uint32_t pitch = c->pitch, rb = c->rb;
-          const uint8_t* src = c->src;
-          const uint8_t* p0 = base + i0 * pitch + (reinterpret_cast<uintptr_t>(src + (size_t)i0 * rb) & 15);
-          const uint8_t* p1 = base + i1 * pitch + (reinterpret_cast<uintptr_t>(src + (size_t)i1 * rb) & 15);
-          const uint8_t* a0 = nullptr;
-          const uint8_t* a1 = nullptr;
-          const int apitch = c->apitch;
-          if (c->aseg) {
-            const uint8_t* ab = base + 16 * pitch;
-            a0 = ab + i0 * apitch + (reinterpret_cast<uintptr_t>(c->sc + (size_t)i0 * c->arb) & 15);
-            a1 = ab + i1 * apitch + (reinterpret_cast<uintptr_t>(c->sc + (size_t)i1 * c->arb) & 15);
-          }
-          const int enc = c->enc, aux = c->aux, gs = c->group_shift, kb0 = c->kb0, which = c->acc;
-          TileAcc<true> t;
-          t.clear();
-          for (int u = warp; u < nu; u += MK_CW) run_unit(enc, aux, gs, p0, p1, a0, a1, 16 * apitch, u, kb0, sm, lane, t);
-#pragma unroll
-          for (int j = 0; j < MEGA_TA; j++)
-            if (which == j) {
-              acc[j].v[0] += t.v[0];
-              acc[j].v[1] += t.v[1];
-            }
-        }
-        prof.toc(11, tr);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sm.empty + slot);
-      }
-      // the sixteen K-slice partials of every tile of the round meet here, once
-      const unsigned long long tc = prof.tic();
-      float* pb = sm.misc + MK_OFF_PART + (nround & 1u) * MK_PART;
-      nround++;
-      if ((lane & 3) == 0) {
-#pragma unroll
-        for (int j = 0; j < MEGA_TA; j++)
-          if (j < (int)R.naccs) {
-            pb[(j * MK_CW + warp) * 16 + g] = acc[j].v[0];
-            pb[(j * MK_CW + warp) * 16 + g + 8] = acc[j].v[1];
-          }
-      }
-      consumer_sync();
-      const int nt = R.ntiles;
-      if (tid < nt * 16) {
-        const MegaTile T = sm.tiles[ti + (tid >> 4)];
-        const int row = tid & 15;
-        if (row < (int)T.n) {
-          const float* p1 = pb + (int)T.acc * MK_CW * 16 + row;
-          float s0 = 0.f;
-#pragma unroll
-          for (int wv = 0; wv < MK_CW; wv++) s0 += p1[wv * 16];
-          s0 *= out_scale;
-          const int64_t orow = (int64_t)T.out_row + row;
-          if (T.ep == MEGA_EP_QKV) {
-            ll_store(a.ll_qkv, orow, s0, ep);
-          } else if (T.ep == MEGA_EP_RESID_O || T.ep == MEGA_EP_RESID_DOWN) {
-            const float hnew = res[orow - hid_lo] + s0;
-            res[orow - hid_lo] = hnew;
-            ll_store(a.ll_hidden[T.ep == MEGA_EP_RESID_O ? 0 : 1], orow, hnew, ep);
-          } else if (T.ep == MEGA_EP_SWIGLU) {
-            const float* p2 = pb + (int)T.acc2 * MK_CW * 16 + row;
-            float s1 = 0.f;
-#pragma unroll
-            for (int wv = 0; wv < MK_CW; wv++) s1 += p2[wv * 16];
-            s1 *= out_scale;
-            ll_store(a.ll_act, orow, (s0 / (1.0f + expf(-s0))) * s1, ep);
-          } else {
-            a.logits[orow] = s0;
-            if (s0 > -INFINITY && arg_better(s0, orow, bv, bi)) bv = s0, bi = orow;
-          }
-        }
-      }
-      ti += nt;
-      prof.toc(12, tc);
-    }
-  };
+  prof.trace = (a.trace && tid == 0) ? a.trace + (size_t)cta * (a.layers + 1) * 16 : nullptr;
+  prof.layer = 0;
 
   if (a.has_rope && tid < a.d / 2) {
     // the rotation of this token's position, shared by all layers (kernels.rs:1047-1064)
@@ -803,11 +1181,12 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
     sm.misc[MK_OFF_ROPE + tid] = cv;
     sm.misc[MK_OFF_ROPE + 64 + tid] = sv;
   }
+  prefetch_kv(a, 0, cta, pos, seq, nsplit, tid);
   // every CTA decodes the token's embedding row for itself: no hand-off before the first product
   mega_gather_row(a.embed, token, sm.xs, tid, MK_CT);
   consumer_sync();
   {
-    const int hid_hi = (int)((int64_t)a.H * (cta + 1) / G);
+    const int hid_hi = (int)hdr->hid_hi;
     for (int i = hid_lo + tid; i < hid_hi; i += MK_CT) res[i - hid_lo] = sm.xs[i];
   }
   prof.mark(0);
@@ -815,54 +1194,50 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
   StageSrc src;
   src.nsplit = nsplit, src.max_split = a.max_split, src.d = a.d;
   for (int l = 0; l < a.layers; l++) {
-    const MegaLayer* L = a.L + l;
-    const unsigned ep = a.epoch_base + 1u + (unsigned)l;
-    unsigned long long ts = prof.tic();
+    const MegaLayerHot* L = sm.hot + l;
+    if (!(a.opts & 2)) {  // the next layer's norm vectors (the final one behind the last layer)
+      const size_t nel = L->norm_type == E_F32 ? 4 : 2, qel = L->qk_norm_type == E_F32 ? 4 : 2;
+      if (l + 1 < a.layers) {
+        prefetch_span(L[1].attn_norm, (size_t)a.H * nel, tid, MK_CT);
+        prefetch_span(L[1].ffn_norm, (size_t)a.H * nel, tid, MK_CT);
+        if (a.has_norm && cta < a.nh * nsplit && tid < 2)
+          prefetch_span(tid == 0 ? L[1].q_norm : L[1].k_norm, (size_t)a.d * qel, 0, 1);
+      } else {
+        prefetch_span(a.out_norm, (size_t)a.H * (a.out_norm_type == E_F32 ? 4 : 2), tid, MK_CT);
+      }
+    }
+    const unsigned ep = epoch_base + 1u + (unsigned)l;
+    prof.layer = l;
     src.kind = l == 0 ? SRC_XS : SRC_LL, src.ll = a.ll_hidden[1], src.ep = ep - 1u;
-    float out_scale = stage_phase(src, L->attn_norm, L->norm_type, a.H, a.eps, xl_for_encoding(L->q.enc), sm, tid,
-                                  lane, warp);
-    prof.toc(9, ts);
-    run_phase(4 * l + 0, ep, out_scale);
+    run_phase(a, sm, wk, 4 * l + 0, ep, src, L->attn_norm, L->norm_type, a.H, L->enc_q, res, hid_lo, tid, lane, warp,
+              prof);
     prof.mark(1);
     phase_attention(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
     prof.mark(2);
-    ts = prof.tic();
     src.kind = nsplit > 1 ? SRC_PARTIALS : SRC_LL, src.ll = nsplit > 1 ? a.ll_part : a.ll_ctx, src.ep = ep;
-    out_scale = stage_phase(src, nullptr, 0, (int)qd, 0.f, xl_for_encoding(L->o.enc), sm, tid, lane, warp);
-    prof.toc(9, ts);
-    run_phase(4 * l + 1, ep, out_scale);
+    run_phase(a, sm, wk, 4 * l + 1, ep, src, nullptr, 0, (int)qd, L->enc_o, res, hid_lo, tid, lane, warp, prof);
     prof.mark(3);
-    ts = prof.tic();
     src.kind = SRC_LL, src.ll = a.ll_hidden[0], src.ep = ep;
-    out_scale = stage_phase(src, L->ffn_norm, L->norm_type, a.H, a.eps, xl_for_encoding(L->gate.enc), sm, tid, lane,
-                            warp);
-    prof.toc(9, ts);
-    run_phase(4 * l + 2, ep, out_scale);
+    run_phase(a, sm, wk, 4 * l + 2, ep, src, L->ffn_norm, L->norm_type, a.H, L->enc_gate, res, hid_lo, tid, lane, warp,
+              prof);
     prof.mark(4);
-    ts = prof.tic();
     src.kind = SRC_LL, src.ll = a.ll_act, src.ep = ep;
-    out_scale = stage_phase(src, nullptr, 0, a.I, 0.f, xl_for_encoding(L->down.enc), sm, tid, lane, warp);
-    prof.toc(9, ts);
-    run_phase(4 * l + 3, ep, out_scale);
+    run_phase(a, sm, wk, 4 * l + 3, ep, src, nullptr, 0, a.I, L->enc_down, res, hid_lo, tid, lane, warp, prof);
     prof.mark(5);
   }
 
   // ---- final norm + lm_head + argmax (first strict maximum)
-  const unsigned ep_last = a.epoch_base + (unsigned)a.layers;
-  {
-    const unsigned long long ts = prof.tic();
-    src.kind = a.layers > 0 ? SRC_LL : SRC_XS, src.ll = a.ll_hidden[1], src.ep = ep_last;
-    const float out_scale = stage_phase(src, a.out_norm, a.out_norm_type, a.H, a.eps, xl_for_encoding(a.lm_head.enc),
-                                        sm, tid, lane, warp);
-    prof.toc(9, ts);
-    run_phase(4 * a.layers, ep_last + 1u, out_scale);
-  }
+  const unsigned ep_last = epoch_base + (unsigned)a.layers;
+  prof.layer = a.layers;
+  src.kind = a.layers > 0 ? SRC_LL : SRC_XS, src.ll = a.ll_hidden[1], src.ep = ep_last;
+  run_phase(a, sm, wk, 4 * a.layers, ep_last + 1u, src, a.out_norm, a.out_norm_type, a.H, a.lm_head.enc, res, hid_lo,
+            tid, lane, warp, prof);
   {
     // the (at most 128) finishing threads hold this CTA's candidates
     float* cv = sm.misc + MK_OFF_AMAX;
     if (tid < MEGA_TA * 16) {
-      cv[tid] = bv;
-      cv[128 + tid] = __int_as_float((int)(bi == 0x7fffffffffffffffLL ? 0x7fffffff : bi));
+      cv[tid] = wk.bv;
+      cv[128 + tid] = __int_as_float((int)(wk.bi == 0x7fffffffffffffffLL ? 0x7fffffff : wk.bi));
     }
     consumer_sync();
     if (warp == 0) {
@@ -880,19 +1255,24 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
         if (arg_better(ov, oi, v, i)) v = ov, i = oi;
       }
       if (lane == 0) {
-        // one 16-byte line per CTA: (value, epoch), (row, epoch)
-        ll_store(a.ll_amax, 2 * (int64_t)cta, v, ep_last + 1u);
-        ll_store(a.ll_amax, 2 * (int64_t)cta + 1, __int_as_float((int)(i == 0x7fffffffffffffffLL ? 0x7fffffff : i)),
+        // this CTA's cache rows of the token (stored by other threads, before block barriers this
+        // thread has passed) are ordered before the pair that lets the next token begin
+        __threadfence();
+        // one 32-byte sector per CTA: (value, epoch), (row, epoch), unused
+        ll_store(a.ll_amax, 4 * (int64_t)cta, v, ep_last + 1u);
+        ll_store(a.ll_amax, 4 * (int64_t)cta + 1, __int_as_float((int)(i == 0x7fffffffffffffffLL ? 0x7fffffff : i)),
                  ep_last + 1u);
       }
     }
   }
   prof.mark(6);
-  if (cta == 0 && warp == 0) {
+  // every CTA reads all candidates and arrives at the same token (first strict maximum)
+  int* next_tok = reinterpret_cast<int*>(sm.misc + MK_OFF_AMAX);
+  if (warp == 0) {
     float v = -INFINITY;
     long long i = 0x7fffffffffffffffLL;
     for (int c = lane; c < G; c += 32) {
-      const int64_t idx[1] = {2 * (int64_t)c};
+      const int64_t idx[1] = {4 * (int64_t)c};
       float p[2];
       ll_poll<1>(a.ll_amax, idx, ep_last + 1u, p, sm.abort);
       const int oi = __float_as_int(p[1]);
@@ -904,20 +1284,30 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
       const long long oi = __shfl_xor_sync(0xffffffffu, i, o);
       if (arg_better(ov, oi, v, i)) v = ov, i = oi;
     }
+    __threadfence();  // the cache rows other CTAs stored for this token are visible to what follows
     if (lane == 0) {
       const int64_t tok = i == 0x7fffffffffffffffLL ? 0 : (int64_t)i;
-      a.io[3] = tok;
-      if (a.advance) {
-        a.io[0] = tok;
-        a.io[1] = pos + 1;
-        const int64_t cnt = a.hist_count[0];
-        if (cnt < a.hist_cap) a.hist[cnt] = tok;
-        a.hist_count[0] = cnt + 1;
+      *next_tok = (int)tok;
+      if (cta == 0) {
+        a.io[3] = tok;
+        if (a.advance) {
+          a.io[0] = tok;
+          a.io[1] = pos + 1;
+          const int64_t cnt = a.hist_count[0];
+          if (cnt < a.hist_cap) a.hist[cnt] = tok;
+          a.hist_count[0] = cnt + 1;
+        }
       }
     }
   }
   prof.mark(7);
   prof.end();
+  consumer_sync();
+  token = *next_tok;
+  pos += 1;
+  if (*sm.abort) break;
+  consumer_sync();  // next_tok shares its words with the candidates of the next token
+  }  // tokens of the launch
   if (tid == 0 && *sm.abort) {
     atomicExch(a.error, *sm.abort);
     // let any bulk copy still in flight land before the CTA's shared memory is released
@@ -930,7 +1320,7 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
 }  // namespace
 
 size_t mega_smem_bytes(int nslot, int xs_floats, size_t prog_bytes) {
-  return (size_t)xs_floats * 4 * 2 + (size_t)(xs_floats / 32 + xs_floats / 16) * 4 +
+  return (size_t)xs_floats * 4 * 2 + (size_t)(xs_floats / 32 + xs_floats / 16 + xs_floats / 32) * 4 +
          (size_t)MK_MISC_FLOATS * 4 + (size_t)nslot * MK_SLOT + (size_t)nslot * 16 + 128 + prog_bytes;
 }
 
@@ -1004,6 +1394,17 @@ void add_tile_chunks(const WRef& w, int64_t r, int n, int acc, std::vector<MegaC
     c.nu = (uint8_t)nu;
     c.enc = (uint8_t)w.enc;
     c.acc = (uint8_t)acc;
+    c.al = (uint8_t)(reinterpret_cast<uintptr_t>(c.src) & 15);
+    c.al_step = (uint8_t)(c.rb & 15u);
+    // Q6_K rows over the full K are copied as one run: their natural pitch (840 bytes for K = 1024)
+    // spreads the eight row pairs over the banks almost as well as a padded pitch does, and one copy
+    // replaces sixteen
+    for (int i = 0; i < n; i++) c.tx += ((((uint32_t)c.al + (uint32_t)i * c.al_step) & 15u) + c.seg + 15u) & ~15u;
+    if (w.enc == E_Q6_K && nsl == 1 && (size_t)n * c.rb + 16 <= (size_t)MK_SLOT && c.rb % 4 == 0 && ((c.rb / 4) & 1) == 0) {
+      c.pitch = (uint16_t)c.rb;
+      c.al_step = 0;
+      c.contig = (uint32_t)((c.al + (size_t)n * c.rb + 15) / 16 * 16);
+    }
     if (w.enc == E_MLX_U4) {
       const int64_t arow = (int64_t)(w.cols / w.group) * ael, ao = (int64_t)(u0 * 32 / w.group) * ael;
       c.sc = w.scales + r * arow + ao;
@@ -1011,6 +1412,9 @@ void add_tile_chunks(const WRef& w, int64_t r, int n, int acc, std::vector<MegaC
       c.arb = (uint32_t)arow;
       c.aseg = (uint16_t)((nu * 32 / w.group) * ael);
       c.apitch = (uint16_t)(((su * 32 / w.group) * ael + 31) / 16 * 16);
+      c.aal = (uint8_t)(reinterpret_cast<uintptr_t>(c.sc) & 15);
+      c.aal_step = (uint8_t)(c.arb & 15u);
+      for (int i = 0; i < n; i++) c.tx += 2u * (((((uint32_t)c.aal + (uint32_t)i * c.aal_step) & 15u) + c.aseg + 15u) & ~15u);
       c.aux = (uint8_t)w.aux;
       c.group_shift = (uint8_t)(w.group == 32 ? 0 : (w.group == 64 ? 1 : 2));
     }
@@ -1059,21 +1463,29 @@ struct CtaProgram {
 };
 }  // namespace
 
-int mega_build_program(const MegaBuildLayer* layers, int nlayers, const WRef& lm_head, int nh, int nkv,
-                       int d, int H, int I, int V, int grid, std::vector<uint8_t>* blob, MegaProgLayout* lay) {
+// First row of CTA `cta` when `n` rows are dealt to `grid` CTAs in units of 4 rows. Four pairs are
+// one 32-byte sector of a hand-off vector: when two CTAs store into the same sector the hand-off
+// takes more than twice as long (2.46 us against 1.10 us for a 1024-element vector between 148
+// CTAs), so no sector has two writers. Needs n % 4 == 0.
+static int64_t split4(int64_t n, int cta, int grid) { return 4 * ((n / 4) * cta / grid); }
+
+int mega_build_program(const MegaBuildLayer* layers, const MegaLayer* full, int nlayers, const WRef& lm_head, int nh,
+                       int nkv, int d, int H, int I, int V, int grid, std::vector<uint8_t>* blob, MegaProgLayout* lay) {
+  DYN_CHECK(H % 4 == 0 && I % 4 == 0 && (nh * d) % 4 == 0 && (nkv * d) % 4 == 0,
+            "persistent decode kernel: widths must be multiples of 4");
   const int nph = 4 * nlayers + 1;
   std::vector<CtaProgram> per(grid);
   const int64_t qd = (int64_t)nh * d, kvd = (int64_t)nkv * d;
   for (int cta = 0; cta < grid; cta++) {
     CtaProgram& pc = per[cta];
-    const int64_t h0 = (int64_t)H * cta / grid, h1 = (int64_t)H * (cta + 1) / grid;
+    const int64_t h0 = split4(H, cta, grid), h1 = split4(H, cta + 1, grid);
     DYN_CHECK(h1 - h0 <= MK_MAX_OWNED, "persistent decode kernel: %lld hidden rows per CTA exceed %d",
               (long long)(h1 - h0), MK_MAX_OWNED);
     for (int l = 0; l < nlayers; l++) {
       const MegaBuildLayer& L = layers[l];
       pc.begin_phase();
       {  // q, k, v share one balanced split of their concatenated rows
-        const int64_t R = qd + 2 * kvd, a0 = R * cta / grid, a1 = R * (cta + 1) / grid;
+        const int64_t R = qd + 2 * kvd, a0 = split4(R, cta, grid), a1 = split4(R, cta + 1, grid);
         const int64_t offs[3] = {0, qd, qd + kvd}, lens[3] = {qd, kvd, kvd};
         const WRef* ws[3] = {&L.q, &L.k, &L.v};
         for (int t = 0; t < 3; t++) {
@@ -1084,7 +1496,7 @@ int mega_build_program(const MegaBuildLayer* layers, int nlayers, const WRef& lm
       pc.begin_phase();
       pc.add_rows(L.o, nullptr, h0, h1, 0, MEGA_EP_RESID_O);
       pc.begin_phase();
-      pc.add_rows(L.gate, &L.up, (int64_t)I * cta / grid, (int64_t)I * (cta + 1) / grid, 0, MEGA_EP_SWIGLU);
+      pc.add_rows(L.gate, &L.up, split4(I, cta, grid), split4(I, cta + 1, grid), 0, MEGA_EP_SWIGLU);
       pc.begin_phase();
       pc.add_rows(L.down, nullptr, h0, h1, 0, MEGA_EP_RESID_DOWN);
     }
@@ -1100,6 +1512,7 @@ int mega_build_program(const MegaBuildLayer* layers, int nlayers, const WRef& lm
       for (int ph = 0; ph < nph; ph++)
         for (int r = 0; r < pc.phase_rounds[ph]; r++, ri++) {
           DYN_CHECK(pc.rounds[ri].naccs <= MEGA_TA && pc.rounds[ri].ntiles <= MEGA_TA, "decode program: round too wide");
+          DYN_CHECK(pc.phase_rounds[ph] <= 255, "decode program: more than 255 rounds in a phase");
           for (int t = 0; t < pc.rounds[ri].ntiles; t++, ti++) {
             DYN_CHECK(pc.tiles[ti].n >= 1 && pc.tiles[ti].n <= 16, "decode program: bad tile");
             rows[ph] += pc.tiles[ti].n;
@@ -1122,18 +1535,39 @@ int mega_build_program(const MegaBuildLayer* layers, int nlayers, const WRef& lm
   lay->off_tiles = sizeof(MegaProgHeader) + mc * sizeof(MegaChunk);
   lay->off_rounds = lay->off_tiles + mt * sizeof(MegaTile);
   lay->off_phase = lay->off_rounds + mr * sizeof(MegaRound);
-  lay->bytes = (lay->off_phase + (size_t)nph * 2 + 15) / 16 * 16;
+  lay->off_layers = (lay->off_phase + (size_t)nph * 2 + 7) / 8 * 8;
+  lay->bytes = (lay->off_layers + (size_t)nlayers * sizeof(MegaLayerHot) + 15) / 16 * 16;
   blob->assign((size_t)grid * lay->bytes, 0);
+  std::vector<MegaLayerHot> hot(nlayers);
+  for (int l = 0; l < nlayers; l++) {
+    MegaLayerHot& t = hot[l];
+    memset(&t, 0, sizeof t);
+    t.attn_norm = full[l].attn_norm, t.ffn_norm = full[l].ffn_norm, t.q_norm = full[l].q_norm, t.k_norm = full[l].k_norm;
+    t.norm_type = (uint8_t)full[l].norm_type, t.qk_norm_type = (uint8_t)full[l].qk_norm_type;
+    t.enc_q = (uint8_t)full[l].q.enc, t.enc_o = (uint8_t)full[l].o.enc;
+    t.enc_gate = (uint8_t)full[l].gate.enc, t.enc_down = (uint8_t)full[l].down.enc;
+  }
   for (int cta = 0; cta < grid; cta++) {
     const CtaProgram& pc = per[cta];
     uint8_t* b = blob->data() + (size_t)cta * lay->bytes;
-    MegaProgHeader h{(uint32_t)pc.chunks.size(), (uint32_t)pc.tiles.size(), (uint32_t)pc.rounds.size(),
-                     (uint32_t)((int64_t)H * cta / grid)};
+    MegaProgHeader h{(uint32_t)pc.chunks.size(), (uint32_t)split4(H, cta + 1, grid), (uint32_t)pc.rounds.size(),
+                     (uint32_t)split4(H, cta, grid)};
     memcpy(b, &h, sizeof h);
     if (!pc.chunks.empty()) memcpy(b + sizeof h, pc.chunks.data(), pc.chunks.size() * sizeof(MegaChunk));
     if (!pc.tiles.empty()) memcpy(b + lay->off_tiles, pc.tiles.data(), pc.tiles.size() * sizeof(MegaTile));
     if (!pc.rounds.empty()) memcpy(b + lay->off_rounds, pc.rounds.data(), pc.rounds.size() * sizeof(MegaRound));
-    memcpy(b + lay->off_phase, pc.phase_rounds.data(), pc.phase_rounds.size() * 2);
+    // phase word: rounds in the low byte, the encoding every chunk of the phase shares in the high byte
+    std::vector<uint16_t> words(pc.phase_rounds.size());
+    size_t ci = 0, ri = 0;
+    for (size_t ph = 0; ph < pc.phase_rounds.size(); ph++) {
+      int enc = -1;
+      for (int r = 0; r < pc.phase_rounds[ph]; r++, ri++)
+        for (int k = 0; k < pc.rounds[ri].nchunks; k++, ci++)
+          enc = enc == -1 ? pc.chunks[ci].enc : (enc == pc.chunks[ci].enc ? enc : 0xff);
+      words[ph] = (uint16_t)(pc.phase_rounds[ph] | ((enc < 0 ? 0xff : enc) << 8));
+    }
+    memcpy(b + lay->off_phase, words.data(), words.size() * 2);
+    if (nlayers) memcpy(b + lay->off_layers, hot.data(), hot.size() * sizeof(MegaLayerHot));
   }
   return 0;
 }
@@ -1145,7 +1579,9 @@ bool mega_supports_weight(const WRef& w) {
     case E_Q8_0: return w.cols % 256 == 0;
     case E_Q4_1: return w.cols % 128 == 0;
     case E_Q6_K: return w.cols % 1024 == 0;
-    case E_MLX_U4: return w.cols % 256 == 0 && (w.group == 32 || w.group == 64 || w.group == 128);
+    case E_MLX_U4:  // scales and biases are copied with one alignment rule: they must agree modulo 16
+      return w.cols % 256 == 0 && (w.group == 32 || w.group == 64 || w.group == 128) &&
+             ((reinterpret_cast<uintptr_t>(w.scales) ^ reinterpret_cast<uintptr_t>(w.biases)) & 15) == 0;
     default: return false;
   }
 }

@@ -133,14 +133,14 @@ struct TgArgs {
 template <int ENC>
 struct ChunkItems {
   using C = Codec<ENC>;
-  static constexpr int IPR = C::BLOCK <= TG_BK ? (TG_BK / C::BLOCK) * C::PARTS : 8;  // Q6_K: 8 parts per quarter
+  static constexpr int IPR = C::BLOCK <= TG_BK ? (TG_BK / C::BLOCK) * C::PARTS : 8;  // 256-element blocks: 8 parts per chunk
   __device__ static __forceinline__ void locate(int64_t k0, int it, int64_t* blk, int* part) {
     if (C::BLOCK <= TG_BK) {
       *blk = k0 / C::BLOCK + it / C::PARTS;
       *part = it % C::PARTS;
     } else {
       *blk = k0 / C::BLOCK;
-      *part = (int)((k0 % C::BLOCK) / 128) * 8 + it;
+      *part = (int)((k0 % C::BLOCK) / C::CHUNK_DIV) * 8 + it;
     }
   }
 };
@@ -469,13 +469,15 @@ bool tg_shape_ok(const WRef& w, int64_t M) {
     case E_Q8_0:
     case E_MLX_U4:
     case E_Q6_K:
+    case E_Q4_K:
+    case E_Q5_K:
     case E_F32:
     case E_F16:
     case E_BF16: break;
     default: return false;
   }
   if (w.enc == E_MLX_U4 && (w.group < 8 || w.cols % w.group)) return false;
-  return M >= 1 && w.rows >= 1 && w.cols >= TG_BK && w.cols % (w.enc == E_Q6_K ? 256 : TG_BK) == 0;
+  return M >= 1 && w.rows >= 1 && w.cols >= TG_BK && w.cols % ((w.enc == E_Q6_K || w.enc == E_Q4_K || w.enc == E_Q5_K) ? 256 : TG_BK) == 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -597,6 +599,8 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
     case E_Q4_1: rc = tg_launch<E_Q4_1>(a, xmap, grid, smem, s); break;
     case E_Q8_0: rc = tg_launch<E_Q8_0>(a, xmap, grid, smem, s); break;
     case E_Q6_K: rc = tg_launch<E_Q6_K>(a, xmap, grid, smem, s); break;
+    case E_Q4_K: rc = tg_launch<E_Q4_K>(a, xmap, grid, smem, s); break;
+    case E_Q5_K: rc = tg_launch<E_Q5_K>(a, xmap, grid, smem, s); break;
     case E_MLX_U4: rc = tg_launch<E_MLX_U4>(a, xmap, grid, smem, s); break;
     case E_F32: rc = tg_launch<E_F32>(a, xmap, grid, smem, s); break;
     case E_F16: rc = tg_launch<E_F16>(a, xmap, grid, smem, s); break;

@@ -162,10 +162,12 @@ __device__ __forceinline__ void unit_apply_add(TileAcc<HILO>& a, const float (&c
 }
 
 // One Q4_0 / Q4_1 block. PH: phase (0 / 2) of the block base. xfp: this lane's fragment
-// pointer for the block; sxa/sxb: 32-block activation sums of the lane's row(s).
+// pointer for the block; sxa/sxb: 32-block activation sums of the lane's row(s). bs: an extra
+// factor on the block's contribution (callers that scale every activation block by its own power
+// of two pass 2^24 / that scale and keep their accumulators in true units).
 template <int ENC, int PH, bool HILO>
 __device__ __forceinline__ void blk_q4(const uint8_t* p0, const uint8_t* p1, const __half* xfp,
-                                       float sxa, float sxb, int t, TileAcc<HILO>& acc) {
+                                       float sxa, float sxb, int t, TileAcc<HILO>& acc, float bs = 1.0f) {
   constexpr int QO = ENC == E_Q4_0 ? 2 : 4;
   const uint32_t w0 = ld32_ph<(PH + QO) & 3>(p0 + QO + 4 * t);
   const uint32_t w1 = ld32_ph<(PH + QO) & 3>(p1 + QO + 4 * t);
@@ -174,16 +176,16 @@ __device__ __forceinline__ void blk_q4(const uint8_t* p0, const uint8_t* p1, con
   mma_f16_16816(c, w0 & 0x000F000Fu, w1 & 0x000F000Fu, w0 & 0x00F000F0u, w1 & 0x00F000F0u, b.x, b.y);
   const uint32_t s0 = w0 >> 8, s1 = w1 >> 8;
   mma_f16_16816(c, s0 & 0x000F000Fu, s1 & 0x000F000Fu, s0 & 0x00F000F0u, s1 & 0x00F000F0u, b.z, b.w);
-  const float d0 = ldh_f32(p0), d1 = ldh_f32(p1);
+  const float d0 = ldh_f32(p0) * bs, d1 = ldh_f32(p1) * bs;
   if (ENC == E_Q4_0)
     unit_apply<HILO>(acc, c, d0, d1, 8.0f * GV_2M24, sxa, sxb);
   else
-    unit_apply_add<HILO>(acc, c, d0, d1, ldh_f32(p0 + 2), ldh_f32(p1 + 2), sxa * GV_2M24, sxb * GV_2M24);
+    unit_apply_add<HILO>(acc, c, d0, d1, ldh_f32(p0 + 2) * bs, ldh_f32(p1 + 2) * bs, sxa * GV_2M24, sxb * GV_2M24);
 }
 
 template <int PH, bool HILO>
 __device__ __forceinline__ void blk_q8_0(const uint8_t* p0, const uint8_t* p1, const __half* xfp,
-                                         float sxa, float sxb, int t, TileAcc<HILO>& acc) {
+                                         float sxa, float sxb, int t, TileAcc<HILO>& acc, float bs = 1.0f) {
   const uint4 b = *reinterpret_cast<const uint4*>(xfp);
   float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -193,7 +195,7 @@ __device__ __forceinline__ void blk_q8_0(const uint8_t* p0, const uint8_t* p1, c
     mma_f16_16816(c, __byte_perm(w0, 0, 0x4140), __byte_perm(w1, 0, 0x4140), __byte_perm(w0, 0, 0x4342),
                   __byte_perm(w1, 0, 0x4342), hlf ? b.z : b.x, hlf ? b.w : b.y);
   }
-  unit_apply<HILO>(acc, c, ldh_f32(p0), ldh_f32(p1), 128.0f * GV_2M24, sxa, sxb);
+  unit_apply<HILO>(acc, c, ldh_f32(p0) * bs, ldh_f32(p1) * bs, 128.0f * GV_2M24, sxa, sxb);
 }
 
 template <bool HILO>
@@ -249,9 +251,9 @@ __device__ __forceinline__ void sblk_q6_k(const uint8_t* p0, const uint8_t* p1, 
 template <int PH, bool HILO>
 __device__ __forceinline__ void q6k_quarter(const uint8_t* p0, const uint8_t* p1, int n, int s,
                                             const __half* xfp, int xstride, const float* sxa,
-                                            const float* sxb, int t, TileAcc<HILO>& acc) {
+                                            const float* sxb, int t, TileAcc<HILO>& acc, float bs = 1.0f) {
   const int j0 = 16 * s + 4 * t;
-  const float d0 = ldh_f32(p0 + 208), d1 = ldh_f32(p1 + 208);
+  const float d0 = ldh_f32(p0 + 208) * bs, d1 = ldh_f32(p1 + 208) * bs;
   const uint32_t qh0 = ld32_ph<PH>(p0 + 128 + n * 32 + j0), qh1 = ld32_ph<PH>(p1 + 128 + n * 32 + j0);
 #pragma unroll
   for (int p = 0; p < 2; p++) {

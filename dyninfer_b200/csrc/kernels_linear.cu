@@ -133,6 +133,12 @@ int launch_linear(const WRef& w, const void* x, int x_type, int64_t m, float* y,
     if (launch_dqgemm_tc(w, x, x_type, m, y, residual, s, &handled)) return 1;
     if (handled) return 0;
   }
+  if (m <= 4 && (w.enc == E_BF16 || w.enc == E_F16)) {
+    // plain 2-byte weights (a tied bf16 embedding table as lm_head): streaming kernel
+    bool handled = false;
+    if (launch_gemv_plain(w, x, x_type, (int)m, y, residual, s, &handled)) return 1;
+    if (handled) return 0;
+  }
   {
     // few rows: tensor-core GEMV, 4 (f32) or 8 (bf16) activation rows per pass over the weights
     const int64_t step = x_type == E_BF16 ? 8 : 4;

@@ -95,6 +95,7 @@ struct dyninfer_cuda_session_t {
   MegaLayer* mega_layers = nullptr;
   int64_t* io_dev = nullptr;  // [0] token [1] position [2] slot [3] produced token [4] error word
   unsigned long long* prof_dev = nullptr;
+  unsigned long long* trace_dev = nullptr;  // [grid][layers + 1][16] event stamps (DYNINFER_CUDA_TRACE=1)
   uint8_t* prog_dev = nullptr;  // [grid] program blobs
   MegaProgLayout mega_lay;
   float* ll_dev = nullptr;  // hand-off vectors of (value, epoch) pairs, one allocation
@@ -154,6 +155,8 @@ int enc_from_name(const std::string& n) {
   if (n == "gguf.q4_1") return E_Q4_1;
   if (n == "gguf.q8_0") return E_Q8_0;
   if (n == "gguf.q6_k") return E_Q6_K;
+  if (n == "gguf.q4_k") return E_Q4_K;
+  if (n == "gguf.q5_k") return E_Q5_K;
   if (n == "mlx.affine.u4") return E_MLX_U4;
   return -1;
 }
@@ -534,7 +537,7 @@ int xl_for_encoding_host(int enc) {
   return (enc == E_Q4_0 || enc == E_Q4_1) ? 0 : (enc == E_MLX_U4 ? 1 : 2);
 }
 
-void fill_mega_args(Session* s, MegaArgs* a, int advance) {
+void fill_mega_args(Session* s, MegaArgs* a, int advance, int steps = 1) {
   const ModelCfg& c = s->cfg;
   a->layers = c.layers, a->H = c.hidden, a->I = c.inter, a->V = c.vocab;
   a->nh = c.heads, a->nkv = c.kv_heads, a->d = c.head_dim;
@@ -549,9 +552,15 @@ void fill_mega_args(Session* s, MegaArgs* a, int advance) {
   a->ll_part = s->ll_dev + s->ll_off[4], a->ll_act = s->ll_dev + s->ll_off[5];
   a->ll_amax = s->ll_dev + s->ll_off[6];
   // every launch gets epochs of its own; the buffers start zeroed, so epoch 0 is never used
-  if (s->mega_epoch > 0xffffffffu - 2u * (unsigned)(c.layers + 2)) s->mega_epoch = 0;
+  const unsigned span = (unsigned)steps * ((unsigned)c.layers + 2u);
+  if (s->mega_epoch > 0xffffffffu - 2u * span) s->mega_epoch = 0;
   a->epoch_base = s->mega_epoch;
-  s->mega_epoch += (unsigned)c.layers + 2u;
+  s->mega_epoch += span;
+  a->steps = steps;
+  {
+    const char* oe = getenv("DYNINFER_CUDA_MEGA_OPTS");
+    a->opts = oe ? atoi(oe) : 0;
+  }
   a->kcache = s->kcache, a->vcache = s->vcache;
   a->cap = (int64_t)(s->pages * s->page_size);
   a->layer_stride = (uint64_t)c.batch * c.kv_heads * (uint64_t)a->cap * c.head_dim * s->kv_elem;
@@ -566,6 +575,7 @@ void fill_mega_args(Session* s, MegaArgs* a, int advance) {
   {
     const char* pe = getenv("DYNINFER_CUDA_PROFILE");
     a->prof = (pe && pe[0] == '1') ? s->prof_dev : nullptr;
+    a->trace = s->trace_dev;
   }
   a->prog = s->prog_dev, a->lay = s->mega_lay;
   a->nslot = s->mega_nslot, a->xs_floats = s->mega_xs;
@@ -1042,7 +1052,7 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
   void* dev[] = {s->arena, s->kcache, s->vcache, s->hidden, s->xn, s->q, s->k, s->v, s->ctx, s->act, s->up,
                  s->logits, s->tokens_dev, s->row_pos_dev, s->row_seq_dev, s->out_token_dev,
                  s->hist_dev, s->hist_count_dev, s->argmax_scratch, s->mega_layers, s->io_dev,
-                 s->prof_dev, s->prog_dev, s->ll_dev, s->batch_logits, s->batch_tokens_dev, s->tp_part, s->tp_logits,
+                 s->prof_dev, s->trace_dev, s->prog_dev, s->ll_dev, s->batch_logits, s->batch_tokens_dev, s->tp_part, s->tp_logits,
                  s->tp_gather, s->scratch, s->qkv1, s->gu1};
   for (void* p : dev)
     if (p) cudaFree(p);
@@ -1115,13 +1125,19 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
   destroy_graphs(s);
   if (s->mega && !s->prog_dev) {
     std::vector<MegaBuildLayer> bl(c.layers);
+    std::vector<MegaLayer> ml(c.layers);
     for (int l = 0; l < c.layers; l++) {
       const LayerW& L = s->layers[l];
       bl[l].q = L.q, bl[l].k = L.k, bl[l].v = L.v, bl[l].o = L.o;
       bl[l].gate = L.gate, bl[l].up = L.up, bl[l].down = L.down;
+      ml[l].q = L.q, ml[l].k = L.k, ml[l].v = L.v, ml[l].o = L.o;
+      ml[l].gate = L.gate, ml[l].up = L.up, ml[l].down = L.down;
+      ml[l].attn_norm = L.attn_norm.ptr, ml[l].ffn_norm = L.ffn_norm.ptr;
+      ml[l].q_norm = L.q_norm.ptr, ml[l].k_norm = L.k_norm.ptr;
+      ml[l].norm_type = L.attn_norm.type, ml[l].qk_norm_type = L.q_norm.type;
     }
     std::vector<uint8_t> blob;
-    if (mega_build_program(bl.data(), c.layers, s->lm_head, c.heads, c.kv_heads, c.head_dim, c.hidden,
+    if (mega_build_program(bl.data(), ml.data(), c.layers, s->lm_head, c.heads, c.kv_heads, c.head_dim, c.hidden,
                            c.inter, c.vocab, s->mega_grid, &blob, &s->mega_lay))
       return 1;
     // the program lives in shared memory beside the ring; a model whose program does not fit
@@ -1136,8 +1152,8 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
       // hand-off vectors: (value, epoch) pairs = 2 floats per element, each vector 256-byte aligned
       const size_t qd = (size_t)c.heads * c.head_dim, kvd = (size_t)c.kv_heads * c.head_dim;
       const size_t elems[7] = {(size_t)c.hidden, (size_t)c.hidden, qd + 2 * kvd, qd,
-                               (size_t)c.heads * s->mega_max_split * (c.head_dim + 2), (size_t)c.inter,
-                               2 * (size_t)s->mega_grid};
+                               (size_t)c.heads * s->mega_max_split * (c.head_dim + 4), (size_t)c.inter,
+                               4 * (size_t)s->mega_grid};
       size_t off = 0;
       for (int i = 0; i < 7; i++) {
         s->ll_off[i] = off;
@@ -1146,6 +1162,12 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
       if (dev_alloc(s, (void**)&s->ll_dev, off * 4)) return 1;
       DYN_CUDA(cudaMemset(s->ll_dev, 0, off * 4));
       s->mega_epoch = 0;
+      const char* te = getenv("DYNINFER_CUDA_TRACE");
+      if (te && te[0] == '1') {
+        const size_t tb = (size_t)s->mega_grid * (c.layers + 1) * 16 * 8;
+        if (dev_alloc(s, (void**)&s->trace_dev, tb)) return 1;
+        DYN_CUDA(cudaMemset(s->trace_dev, 0, tb));
+      }
     }
   }
   return 0;
@@ -1233,6 +1255,17 @@ int dyninfer_cuda_session_decode_phase_profile(dyninfer_cuda_session_t* s, doubl
 
 int dyninfer_cuda_session_uses_persistent_kernel(const dyninfer_cuda_session_t* s) {
   return s && s->mega && s->prog_dev ? 1 : 0;
+}
+
+int dyninfer_cuda_session_decode_trace(dyninfer_cuda_session_t* s, uint64_t* out, size_t count, size_t* out_needed) {
+  DYN_CHECK(s != nullptr && out_needed != nullptr, "session or out_needed is NULL");
+  const size_t need = s->trace_dev ? (size_t)s->mega_grid * (s->cfg.layers + 1) * 16 : 0;
+  *out_needed = need;
+  if (!out || count < need || need == 0) return 0;
+  DYN_CUDA(cudaSetDevice(s->device));
+  DYN_CUDA(cudaStreamSynchronize(s->stream));
+  DYN_CUDA(cudaMemcpy(out, s->trace_dev, need * 8, cudaMemcpyDeviceToHost));
+  return 0;
 }
 
 uint64_t dyninfer_cuda_session_launch_count(const dyninfer_cuda_session_t* s) {
@@ -1489,13 +1522,17 @@ int dyninfer_cuda_session_decode_loop(dyninfer_cuda_session_t* s, int64_t first_
     s->stage_host[0] = first_token;
     s->stage_host[1] = start_pos;
     s->stage_host[2] = 0;
-    MegaArgs ma;
-    fill_mega_args(s, &ma, 1);
     DYN_CUDA(cudaMemcpyAsync(s->io_dev, s->stage_host, 24, cudaMemcpyHostToDevice, s->stream));
     DYN_CUDA(cudaMemsetAsync(s->hist_count_dev, 0, 8, s->stream));
     DYN_CUDA(cudaEventRecord(s->ev0, s->stream));
-    for (size_t i = 0; i < steps; i++)
+    // several tokens per launch: the launch gap and the kernel's prologue are paid once per group
+    size_t per = 16;
+    if (const char* e = getenv("DYNINFER_CUDA_TOKENS_PER_LAUNCH")) per = (size_t)std::max(1, std::min(256, atoi(e)));
+    for (size_t i = 0; i < steps; i += per) {
+      MegaArgs ma;
+      fill_mega_args(s, &ma, 1, (int)std::min(per, steps - i));
       if (launch_decode_mega(ma, s->mega_grid, s->mega_smem, s->stream)) return 1;
+    }
     DYN_CUDA(cudaEventRecord(s->ev1, s->stream));
     DYN_CUDA(cudaMemcpyAsync(s->stage_host + 3, s->io_dev + 3, 16, cudaMemcpyDeviceToHost, s->stream));
     DYN_CUDA(cudaStreamSynchronize(s->stream));

@@ -311,8 +311,21 @@ class CudaSession:
         check(lib().dyninfer_cuda_session_decode_phase_profile(self._h, out, 24))
         names = ("embed", "qkv", "attention", "o_proj", "gate_up", "down", "lm_head", "argmax", "total",
                  "t_stage", "t_wait_weights", "t_rows", "t_round_reduce", "t_attn_prepare", "t_attn_scores",
-                 "t_attn_merge")
+                 "t_attn_merge", "t_stage_arrive", "t_stage_convert")
         return dict(zip(names, [float(v) for v in out]))
+
+    def decode_trace(self):
+        """[CTAs, layers + 1, 16] global-timer stamps (ns) of the last persistent-kernel launch, or None
+        when the session was not created with DYNINFER_CUDA_TRACE=1."""
+        need = C.c_size_t(0)
+        check(lib().dyninfer_cuda_session_decode_trace(self._h, None, 0, C.byref(need)))
+        if not need.value:
+            return None
+        out = np.zeros(need.value, dtype=np.uint64)
+        check(lib().dyninfer_cuda_session_decode_trace(self._h, out.ctypes.data_as(C.POINTER(C.c_uint64)), need.value,
+                                                       C.byref(need)))
+        layers = self.model.catalog.config["layers"]
+        return out.reshape(-1, layers + 1, 16)
 
     def uses_persistent_kernel(self) -> bool:
         """Whether single-row steps run as the one-launch-per-token persistent kernel (decided when

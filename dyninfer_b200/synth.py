@@ -141,6 +141,18 @@ def random_weight(enc: str, rows: int, cols: int, seed: int, group: int = 64):
         d = (np.float32(0.02 / 680.0) * rng.uniform(0.5, 1.5, size=nb).astype(np.float32)).astype(np.float16)
         blk[:, 208:210] = d.view(np.uint8).reshape(-1, 2)
         return {"data": blk.reshape(-1)}
+    if enc in ("gguf.q4_k", "gguf.q5_k"):
+        # uniform nibble / high-bit / 6-bit scale and min bytes; f16 d, dmin sized for std ~= 0.02:
+        # w = d*sc*q - dmin*m with sc, m ~ U[0,63], q ~ U[0,15] (U[0,31] for Q5_K)
+        nb, bsz = rows * cols // 256, (144 if enc == "gguf.q4_k" else 176)
+        blk = np.empty((nb, bsz), dtype=np.uint8)
+        blk[:, 4:] = rng.integers(0, 256, size=(nb, bsz - 4), dtype=np.uint8)
+        qmax = 15.0 if enc == "gguf.q4_k" else 31.0
+        d = (np.float32(0.02 / (31.5 * qmax * 0.35)) * rng.uniform(0.5, 1.5, size=nb).astype(np.float32)).astype(np.float16)
+        dmin = (d.astype(np.float32) * np.float32(qmax / 2)).astype(np.float16)     # centres the values near zero
+        blk[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+        blk[:, 2:4] = dmin.view(np.uint8).reshape(-1, 2)
+        return {"data": blk.reshape(-1)}
     if enc == "mlx.affine.u4":
         packed = rng.integers(0, 2 ** 32, size=(rows, cols // 8), dtype=np.uint32)
         s = (np.float32(0.0043) * rng.uniform(0.5, 1.5, size=(rows, cols // group)).astype(np.float32))

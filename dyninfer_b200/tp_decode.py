@@ -47,83 +47,87 @@ def _checkpoint(model: str, layers: int | None):
     return path, cfg, kw
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--model", default="0.6b-q4_0", choices=["tiny", "0.6b-q4_0", "8b-mixed", "32b-q4_0"])
-    ap.add_argument("--layers", type=int, default=0)
-    ap.add_argument("--prompt", type=int, default=512)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--chunk", type=int, default=512)
-    ap.add_argument("--kv-dtype", default="bf16")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
-                    help="sum of the partial products: own peer-memory kernel, or NCCL all-reduce")
-    ap.add_argument("--check", action="store_true")
-    args = ap.parse_args()
+def run(model: str = "0.6b-q4_0", layers: int = 0, prompt: int = 512, steps: int = 64, warmup: int = 3,
+        batch: int = 1, chunk: int = 512, kv_dtype: str = "bf16", exchange: str = "peer", check: bool = False,
+        dump_logits: str = "", solo: bool = False) -> dict:
+    """One tensor-parallel run over the ranks of the default process group (any backend that can move
+    Python objects; the data path uses this library's own communicator). Every rank calls it with the
+    same arguments; the returned dict is complete on rank 0. `solo`: this process alone runs the
+    unsharded model on its own GPU, whatever the process group is (no collective is issued)."""
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("tensor-parallel decode needs CUDA devices: the cuda target has no CPU fallback")
     rank, local, world = replicas.world()
+    if solo:
+        rank, world = 0, 1
+    sync = (lambda: None) if solo else replicas.barrier
     torch.cuda.set_device(local)
-    replicas.init("gloo")
-    path, cfg, kw = _checkpoint(args.model, args.layers or None)
+    path, cfg, kw = _checkpoint(model, layers or None)
     if rank == 0 and not os.path.exists(path):
         tmp = path + f".tmp{os.getpid()}"
         synth.write_qwen3_gguf(tmp, cfg, seed=SEED, **kw)
         os.replace(tmp, path)
-    replicas.barrier()
-    max_seq = args.prompt + args.steps + args.warmup + 8
+    sync()
+    max_seq = prompt + steps + warmup + 8
     t_load = time.perf_counter()
-    model = ModelLoader().load(path, target=f"cuda:{local}", max_kv=max_seq, kv_dtype=args.kv_dtype,
-                               chunk_size=args.chunk, tp=(rank, world), tp_exchange=args.exchange)
+    tp = (rank, world) if world > 1 else None
+    loaded = ModelLoader().load(path, target=f"cuda:{local}", max_kv=max_seq, kv_dtype=kv_dtype,
+                                chunk_size=chunk, tp=tp, tp_exchange=exchange,
+                                decode_kernel="graph")
     rng = np.random.default_rng(SEED)
-    prompts = [rng.integers(0, cfg["vocab"], size=args.prompt).tolist() for _ in range(args.batch)]
+    prompts = [rng.integers(0, cfg["vocab"], size=prompt).tolist() for _ in range(batch)]
     result = {}
-    with model.create_batched_session(SessionConfig(max_sequence_length=max_seq, batch_size=args.batch)) as s:
+    with loaded.create_batched_session(SessionConfig(max_sequence_length=max_seq, batch_size=batch)) as s:
         torch.cuda.synchronize()
         load_s = time.perf_counter() - t_load
         s.prefill_slot(0, prompts[0])                      # untimed: first-use set-up
-        replicas.barrier()
+        sync()
         t0 = time.perf_counter()
-        feed = {slot: s.prefill_slot(slot, prompts[slot]) for slot in range(args.batch)}
+        feed = {slot: s.prefill_slot(slot, prompts[slot]) for slot in range(batch)}
         torch.cuda.synchronize()
         prefill_s = time.perf_counter() - t0
         first = dict(feed)
-        produced = [[] for _ in range(args.batch)]
-        for _ in range(args.warmup):
+        produced = [[] for _ in range(batch)]
+        for _ in range(warmup):
             feed = s.step(feed)
             for k, v in feed.items():
                 produced[k].append(v)
-        replicas.barrier()
+        sync()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        for _ in range(args.steps):
+        for _ in range(steps):
             feed = s.step(feed)
             for k, v in feed.items():
                 produced[k].append(v)
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         wbytes = s.decode_weight_bytes()
-        if args.check:   # logits of the prompt's last row and of one batched step, all ranks in step
+        if check or dump_logits:   # logits of the prompt's last row and of one batched step, all ranks in step
             tp_lg, tp_tok = s.prefill_slot(0, prompts[0], want_logits=True)
             _, tp_step_lg = s.step({0: tp_tok}, want_logits=True)
-    prefill_s, dt = replicas.max_over_ranks([prefill_s, dt])
+            if dump_logits and rank == 0:
+                np.savez(dump_logits, prompt=np.array(prompts[0], dtype=np.int64), prefill_logits=tp_lg,
+                         first_token=np.int64(tp_tok), step_logits=tp_step_lg[0], checkpoint=np.array(path))
+    dev = "cuda" if world > 1 else "cpu"
+    if not solo:
+        prefill_s, dt = replicas.max_over_ranks([prefill_s, dt], device=dev)
     result.update({
-        "workload": f"{args.model} ({cfg['layers']} layers), tensor parallel over {world} GPUs, prompt "
-                    f"{args.prompt}, batch {args.batch}, greedy decode",
-        "tp": world, "exchange": args.exchange, "batch": args.batch, "steps": args.steps,
-        "prefill_tokens_per_s": round(args.batch * args.prompt / prefill_s, 1),
-        "tokens_per_s": round(args.batch * args.steps / dt, 1), "ms_per_step": round(1e3 * dt / args.steps, 3),
+        "workload": f"{model} ({cfg['layers']} layers), tensor parallel over {world} GPUs, prompt "
+                    f"{prompt}, batch {batch}, greedy decode",
+        "tp": world, "exchange": exchange if world > 1 else "none", "batch": batch, "steps": steps,
+        "prefill_tokens_per_s": round(batch * prompt / prefill_s, 1),
+        "tokens_per_s": round(batch * steps / dt, 1), "ms_per_step": round(1e3 * dt / steps, 3),
         "weight_bytes_per_step_per_rank": int(wbytes),
-        "weight_gbs_all_ranks": round(world * wbytes * args.steps / dt / 1e9, 1),
+        "weight_gbs_per_gpu": round(wbytes * steps / dt / 1e9, 1),
+        "weight_gbs_all_ranks": round(world * wbytes * steps / dt / 1e9, 1),
         "load_s": round(load_s, 1),
         "timing": "host clock around synchronised C-ABI calls, maximum over ranks",
     })
-    if args.check:
+    if check:
         # every rank must have produced the same tokens; rank 0 compares with the unsharded model
         import torch.distributed as dist
-        mine = torch.tensor([first[k] for k in sorted(first)] + [t for p in produced for t in p], dtype=torch.int64)
+        mine = torch.tensor([first[k] for k in sorted(first)] + [t for p in produced for t in p], dtype=torch.int64,
+                            device=dev)
         theirs = [torch.zeros_like(mine) for _ in range(world)]
         if world > 1:
             dist.all_gather(theirs, mine)
@@ -131,14 +135,14 @@ def main() -> None:
             theirs = [mine]
         result["ranks_agree"] = bool(all(torch.equal(t, mine) for t in theirs))
         if rank == 0:
-            ref = ModelLoader().load(path, target=f"cuda:{local}", max_kv=max_seq, kv_dtype=args.kv_dtype,
-                                     chunk_size=args.chunk, decode_kernel="graph")
+            ref = ModelLoader().load(path, target=f"cuda:{local}", max_kv=max_seq, kv_dtype=kv_dtype,
+                                     chunk_size=chunk, decode_kernel="graph")
             with ref.create_batched_session(SessionConfig(max_sequence_length=max_seq,
-                                                          batch_size=args.batch)) as r:
-                rfeed = {slot: r.prefill_slot(slot, prompts[slot]) for slot in range(args.batch)}
+                                                          batch_size=batch)) as r:
+                rfeed = {slot: r.prefill_slot(slot, prompts[slot]) for slot in range(batch)}
                 rfirst = dict(rfeed)
-                rprod = [[] for _ in range(args.batch)]
-                for _ in range(args.warmup + args.steps):
+                rprod = [[] for _ in range(batch)]
+                for _ in range(warmup + steps):
                     rfeed = r.step(rfeed)
                     for k, v in rfeed.items():
                         rprod[k].append(v)
@@ -158,7 +162,29 @@ def main() -> None:
                                "prefill_logits_max_abs_diff": float(np.abs(tp_lg - ref_lg).max()),
                                "step_logits_max_abs_diff": float(np.abs(tp_step_lg[0] - ref_step_lg[0]).max()),
                                "logits_max_abs": float(np.abs(ref_lg).max())}
-    if rank == 0:
+    return result
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="0.6b-q4_0", choices=["tiny", "0.6b-q4_0", "8b-mixed", "32b-q4_0"])
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--chunk", type=int, default=512)
+    ap.add_argument("--kv-dtype", default="bf16")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="sum of the partial products: own peer-memory kernel, or NCCL all-reduce")
+    ap.add_argument("--check", action="store_true")
+    ap.add_argument("--dump-logits", default="",
+                    help="rank 0 writes the prompt, the logits of its last row and of one step to this .npz")
+    args = ap.parse_args()
+    replicas.init("gloo")
+    result = run(args.model, args.layers, args.prompt, args.steps, args.warmup, args.batch, args.chunk,
+                 args.kv_dtype, args.exchange, args.check, args.dump_logits)
+    if replicas.world()[0] == 0:
         print(json.dumps(result), flush=True)
     replicas.shutdown()
 

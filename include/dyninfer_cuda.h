@@ -45,7 +45,9 @@ enum {
   DYNINFER_ENC_Q4_1 = 4,   /* gguf.q4_1:  32 el / 20 B */
   DYNINFER_ENC_Q8_0 = 5,   /* gguf.q8_0:  32 el / 34 B */
   DYNINFER_ENC_Q6_K = 6,   /* gguf.q6_k: 256 el / 210 B */
-  DYNINFER_ENC_MLX_U4 = 7  /* mlx.affine.u4: u32 words + scales + biases */
+  DYNINFER_ENC_MLX_U4 = 7, /* mlx.affine.u4: u32 words + scales + biases */
+  DYNINFER_ENC_Q4_K = 8,   /* gguf.q4_k: 256 el / 144 B */
+  DYNINFER_ENC_Q5_K = 9    /* gguf.q5_k: 256 el / 176 B */
 };
 
 /* One [rows, cols] parameter as the verbatim checkpoint bytes, resident in
@@ -305,6 +307,15 @@ int dyninfer_cuda_session_uses_persistent_kernel(const dyninfer_cuda_session_t* 
  * includes the grid barrier that ends it. Fails when the session uses the graph path. */
 int dyninfer_cuda_session_decode_phase_profile(dyninfer_cuda_session_t* session, double* out_us,
                                                size_t count);
+
+/* Event trace of the most recent persistent-kernel launch, recorded when the session was
+ * configured with DYNINFER_CUDA_TRACE=1 in the environment: [CTAs][layers + 1][16] device
+ * global-timer stamps (ns) taken by thread 0 of every CTA. Per layer: 0 QKV input staged, 1 its
+ * tile steps done, 2 its outputs stored; 3 attention has q/k/v, 4 attention stored; 5-7 o_proj,
+ * 8-10 gate/up, 11-13 down likewise; row `layers`: 0-2 = lm_head. *out_needed receives the number
+ * of entries (0 when tracing is off); nothing is copied unless `count` covers it. */
+int dyninfer_cuda_session_decode_trace(dyninfer_cuda_session_t* session, uint64_t* out, size_t count,
+                                       size_t* out_needed);
 
 /* Number of kernels this library has launched on behalf of `session` since creation. */
 uint64_t dyninfer_cuda_session_launch_count(const dyninfer_cuda_session_t* session);

@@ -9,7 +9,7 @@
  * reference file:line it follows.
  *
  * Pin status:
- *   - dequantisation of Q4_0 / Q4_1 / Q8_0 / Q6_K: pinned, bit for bit,
+ *   - dequantisation of Q4_0 / Q4_1 / Q8_0 / Q6_K / Q4_K / Q5_K: pinned, bit for bit,
  *     against the third-party `gguf` Python package and against the
  *     reference's own fixture packers restated in tests/fixtures_ref.py
  *     (crates/dyninfer-checkpoint-gguf/src/q4.rs:16-128).
@@ -43,7 +43,9 @@ enum {
   ORC_Q4_1 = 4,
   ORC_Q8_0 = 5,
   ORC_Q6_K = 6,
-  ORC_MLX_U4 = 7
+  ORC_MLX_U4 = 7,
+  ORC_Q4_K = 8,
+  ORC_Q5_K = 9
 };
 
 typedef struct {
@@ -130,6 +132,8 @@ ORC_API int64_t orc_block_elems(int enc) {
     case ORC_Q8_0:
       return 32;
     case ORC_Q6_K:
+    case ORC_Q4_K:
+    case ORC_Q5_K:
       return 256;
     case ORC_MLX_U4:
       return 8;
@@ -152,6 +156,10 @@ ORC_API int64_t orc_block_bytes(int enc) {
       return 34;
     case ORC_Q6_K:
       return 210;
+    case ORC_Q4_K:
+      return 144;
+    case ORC_Q5_K:
+      return 176;
     case ORC_MLX_U4:
       return 4;
     default:
@@ -222,6 +230,45 @@ static void dq_q6_k(const uint8_t* blk, float* out) {
         }
 }
 
+/* Q4_K / Q5_K: schema-only in the reference
+ * (crates/dyninfer-checkpoint-gguf/src/types.rs:21-22,137-201), so this restates GGML's published
+ * dequantisation as the third-party `gguf` package (0.19) evaluates it, in f32:
+ * f16 d at 0, f16 dmin at 2, 12 bytes of 6-bit scales/mins at 4 (8 sub-blocks of 32); Q4_K: 128
+ * nibble bytes at 16; Q5_K: 32 high-bit bytes at 16 and 128 nibble bytes at 48. Element
+ * 64*jj + 32*h + l uses sub-block j = 2*jj + h, nibble h of byte 32*jj + l (Q5_K: + 16 * bit j of high
+ * byte l); w = (d * sc_j) * q - (dmin * m_j), each product and the difference rounded on its own.
+ * Pinned by tests/golden/dequant_golden.npz. */
+static void kq_scale_min(const uint8_t* s, int j, float* sc, float* mn) {
+  unsigned a, b;
+  if (j < 4) {
+    a = s[j] & 63u;
+    b = s[j + 4] & 63u;
+  } else {
+    a = (s[j + 4] & 15u) | ((unsigned)(s[j - 4] >> 6) << 4);
+    b = (unsigned)(s[j + 4] >> 4) | ((unsigned)(s[j] >> 6) << 4);
+  }
+  *sc = (float)a;
+  *mn = (float)b;
+}
+static void dq_q45_k(const uint8_t* blk, float* out, int five) {
+  const float d = f16_to_f32(rd16(blk)), dmin = f16_to_f32(rd16(blk + 2));
+  const uint8_t* qh = blk + 16;
+  const uint8_t* qs = blk + (five ? 48 : 16);
+  for (int j = 0; j < 8; j++) {
+    float sc, mn;
+    kq_scale_min(blk + 4, j, &sc, &mn);
+    const float ds = d * sc;
+    const float dm = dmin * mn;
+    const int jj = j >> 1, h = j & 1;
+    for (int l = 0; l < 32; l++) {
+      unsigned q = (qs[32 * jj + l] >> (4 * h)) & 15u;
+      if (five) q |= ((unsigned)(qh[l] >> j) & 1u) << 4;
+      const float scaled = ds * (float)q;
+      out[64 * jj + 32 * h + l] = scaled - dm;
+    }
+  }
+}
+
 ORC_API void orc_dequant_row(const orc_tensor* t, int64_t row, float* out) {
   const int64_t K = t->cols;
   switch (t->enc) {
@@ -249,6 +296,14 @@ ORC_API void orc_dequant_row(const orc_tensor* t, int64_t row, float* out) {
     case ORC_Q6_K: {
       const uint8_t* p = t->data + row * (K / 256) * 210;
       for (int64_t b = 0; b < K / 256; b++) dq_q6_k(p + b * 210, out + b * 256);
+    } break;
+    case ORC_Q4_K: {
+      const uint8_t* p = t->data + row * (K / 256) * 144;
+      for (int64_t b = 0; b < K / 256; b++) dq_q45_k(p + b * 144, out + b * 256, 0);
+    } break;
+    case ORC_Q5_K: {
+      const uint8_t* p = t->data + row * (K / 256) * 176;
+      for (int64_t b = 0; b < K / 256; b++) dq_q45_k(p + b * 176, out + b * 256, 1);
     } break;
     case ORC_MLX_U4: {
       /* packed ui32[N, K/8], lane k of a word is bits [4k, 4k+4); per group of

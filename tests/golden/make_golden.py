@@ -19,7 +19,8 @@ from gguf import quants  # noqa: E402
 from dyninfer_b200 import synth  # noqa: E402
 
 QT = {"gguf.q4_0": gguf.GGMLQuantizationType.Q4_0, "gguf.q4_1": gguf.GGMLQuantizationType.Q4_1,
-      "gguf.q8_0": gguf.GGMLQuantizationType.Q8_0, "gguf.q6_k": gguf.GGMLQuantizationType.Q6_K}
+      "gguf.q8_0": gguf.GGMLQuantizationType.Q8_0, "gguf.q6_k": gguf.GGMLQuantizationType.Q6_K,
+      "gguf.q4_k": gguf.GGMLQuantizationType.Q4_K, "gguf.q5_k": gguf.GGMLQuantizationType.Q5_K}
 
 
 def main():
@@ -28,14 +29,16 @@ def main():
         rows, cols = 6, 512
         raw = synth.random_weight(enc, rows, cols, 1234 + i)["data"]
         # edge blocks: zero scale, extreme nibbles, negative scale, f16 subnormal scale
-        bsz = {"gguf.q4_0": 18, "gguf.q4_1": 20, "gguf.q8_0": 34, "gguf.q6_k": 210}[enc]
+        bsz = {"gguf.q4_0": 18, "gguf.q4_1": 20, "gguf.q8_0": 34, "gguf.q6_k": 210, "gguf.q4_k": 144,
+               "gguf.q5_k": 176}[enc]
         blk = raw.reshape(-1, bsz).copy()
         doff = 208 if enc == "gguf.q6_k" else 0
         blk[0, doff:doff + 2] = 0
         blk[1, doff:doff + 2] = np.array([0x8400], np.uint16).view(np.uint8)   # -6.1e-5
         blk[2, doff:doff + 2] = np.array([0x0001], np.uint16).view(np.uint8)   # smallest subnormal
-        blk[3, (2 if doff == 0 else 0):(2 if doff == 0 else 0) + 16] = 0xFF
-        blk[4, (2 if doff == 0 else 0):(2 if doff == 0 else 0) + 16] = 0x00
+        qoff = {"gguf.q4_k": 4, "gguf.q5_k": 4}.get(enc, 2 if doff == 0 else 0)   # K-quants: the packed scales
+        blk[3, qoff:qoff + 16] = 0xFF
+        blk[4, qoff:qoff + 16] = 0x00
         raw = blk.reshape(-1)
         ref = quants.dequantize(raw.reshape(rows, -1), qt).astype(np.float32)
         out[enc + ":raw"] = raw

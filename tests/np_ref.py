@@ -44,6 +44,33 @@ def dequant(enc, raw, rows, cols, scales=None, biases=None, group=64):
                 s = np.repeat(sc[:, :, h, p, :], 16, axis=-1)
                 w[:, :, h, p, :] = (q.astype(np.float32) * s) * d[:, None, None]
         w = w.reshape(nb, 256)
+    elif enc in ("gguf.q4_k", "gguf.q5_k"):
+        # GGML's published K-quant layout (schema-only in the reference): d, dmin f16; 12 bytes of
+        # 6-bit scales / mins; Q5_K: 32 high-bit bytes; 128 nibble bytes
+        five = enc == "gguf.q5_k"
+        b = raw.reshape(-1, 176 if five else 144)
+        nb = b.shape[0]
+        d, dmin = _f16(b[:, 0:2]), _f16(b[:, 2:4])
+        s = b[:, 4:16].astype(np.uint32)
+        sc = np.empty((nb, 8), np.uint32)
+        mn = np.empty((nb, 8), np.uint32)
+        for j in range(8):
+            if j < 4:
+                sc[:, j], mn[:, j] = s[:, j] & 63, s[:, j + 4] & 63
+            else:
+                sc[:, j] = (s[:, j + 4] & 15) | ((s[:, j - 4] >> 6) << 4)
+                mn[:, j] = (s[:, j + 4] >> 4) | ((s[:, j] >> 6) << 4)
+        qs = b[:, 48:176] if five else b[:, 16:144]
+        qh = b[:, 16:48] if five else None
+        w = np.empty((nb, 8, 32), np.float32)
+        for j in range(8):
+            q = (qs[:, 32 * (j // 2):32 * (j // 2) + 32] >> (4 * (j % 2))) & 15
+            if five:
+                q = q | (((qh >> j) & 1) << 4)
+            ds = d * sc[:, j].astype(np.float32)
+            dm = dmin * mn[:, j].astype(np.float32)
+            w[:, j, :] = ds[:, None] * q.astype(np.float32) - dm[:, None]
+        w = w.reshape(nb, 256)
     elif enc == "mlx.affine.u4":
         words = raw.view(np.uint32).reshape(rows, cols // 8)
         q = np.stack([(words >> np.uint32(4 * k)) & np.uint32(15) for k in range(8)], axis=-1)

@@ -80,6 +80,25 @@ def test_gqa_rope_qknorm_prefill_vs_decode(native_lib, oracle, tmp_path):
             s.decode(1)
 
 
+def test_k_quant_tensors_in_a_mixed_model(native_lib, oracle, tmp_path):
+    """Q4_K and Q5_K linears (what Q4_K_M / UD-Q4_K_XL files mix with Q4_0 and Q6_K) through the
+    operator path: prompt in chunks (tensor-core GEMM), then single-row steps."""
+    path = synth.write_qwen3_gguf(str(tmp_path / "kq.gguf"), synth.TINY, seed=13,
+                                  encodings={"attn_q": "gguf.q4_k", "attn_output": "gguf.q5_k", "ffn_gate": "gguf.q4_k",
+                                             "ffn_up": "gguf.q4_k", "ffn_down": "gguf.q5_k"})
+    cat = ck.open_catalog(path)
+    prompt = np.random.default_rng(8).integers(0, synth.TINY["vocab"], size=40).tolist()
+    want_logits, want_toks, margins = oracle_run(oracle, cat, prompt, 6)
+    model = ModelLoader().load(path, max_kv=256, kv_dtype="f32", chunk_size=32)
+    with model.create_session(SessionConfig(max_sequence_length=256)) as s:
+        assert not s.uses_persistent_kernel()
+        lg = s.prefill(prompt).values
+        assert np.abs(lg - want_logits[0]).max() <= 1e-2 and helpers.cosine(lg, want_logits[0]) >= 0.9999
+        for i in range(6):
+            lg = s.decode(want_toks[i]).values
+            assert np.abs(lg - want_logits[i + 1]).max() <= 1e-2 and helpers.cosine(lg, want_logits[i + 1]) >= 0.9999
+
+
 @pytest.mark.parametrize("flavor", ["gguf_q4_0", "gguf_mixed", "mlx_u4"])
 @pytest.mark.parametrize("kv", ["f32", "bf16"])
 @pytest.mark.parametrize("kernel", ["persistent", "graph"])

@@ -10,7 +10,8 @@ from dyninfer_b200 import synth
 pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
-ENCS = ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "mlx.affine.u4", "plain.bf16", "plain.f16", "plain.f32"]
+GGUF_ENCS = ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "gguf.q4_k", "gguf.q5_k"]
+ENCS = GGUF_ENCS + ["mlx.affine.u4", "plain.bf16", "plain.f16", "plain.f32"]
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "dequant_golden.npz")
 
 
@@ -41,7 +42,7 @@ def test_dequant_bit_exact(native_lib, oracle, enc, shape):
 def test_dequant_golden_and_mlx_f32_aux(native_lib, oracle):
     from dyninfer_b200 import ops
     g = np.load(GOLD)
-    for enc in ENCS[:4]:
+    for enc in GGUF_ENCS:
         want = g[enc + ":f32"]
         dw = ops.DeviceWeight(enc, want.shape[0], want.shape[1], g[enc + ":raw"])
         assert helpers.bits_equal(ops.dequant(dw).cpu().numpy(), want), enc

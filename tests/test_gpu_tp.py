@@ -27,14 +27,16 @@ def _free_port():
                                                 ("8b-mixed", 2, ["--prompt", "96", "--chunk", "64", "--steps", "8",
                                                                  "--batch", "3"])])
 @pytest.mark.parametrize("exchange", ["nccl", "peer"])
-def test_two_gpu_tensor_parallel_matches_unsharded(tmp_path, model, layers, extra, exchange):
+def test_two_gpu_tensor_parallel_matches_unsharded(tmp_path, oracle, model, layers, extra, exchange):
+    import numpy as np
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, DYNINFER_BENCH_DIR=str(tmp_path), NCCL_NVLS_ENABLE="0")
+    dump = str(tmp_path / "rank0_logits.npz")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), "-m", "dyninfer_b200.tp_decode",
-           "--model", model, "--check", "--kv-dtype", "f32", "--exchange", exchange] + extra
+           "--model", model, "--check", "--kv-dtype", "f32", "--exchange", exchange, "--dump-logits", dump] + extra
     if layers:
         cmd += ["--layers", str(layers)]
     out = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
@@ -47,3 +49,16 @@ def test_two_gpu_tensor_parallel_matches_unsharded(tmp_path, model, layers, extr
     assert c["step_logits_max_abs_diff"] <= 1e-2 * max(1.0, c["logits_max_abs"]), c
     assert c["first_tokens_equal"], c
     assert min(c["common_prefix_per_sequence"]) >= 4, c
+    # rank 0's logits against the CPU oracle on the same checkpoint and prompt (not only against
+    # the unsharded CUDA session): max-abs <= 1e-2, cosine >= 0.9999
+    import helpers
+    from dyninfer_b200 import checkpoint as ck
+    from test_gpu_model import oracle_run
+    d = np.load(dump)
+    cat = ck.open_catalog(str(d["checkpoint"]))
+    want_logits, want_toks, _ = oracle_run(oracle, cat, d["prompt"].tolist(), 1, kv_cap=256)
+    assert np.abs(d["prefill_logits"] - want_logits[0]).max() <= 1e-2
+    assert helpers.cosine(d["prefill_logits"], want_logits[0]) >= 0.9999
+    if int(d["first_token"]) == want_toks[0]:
+        assert np.abs(d["step_logits"] - want_logits[1]).max() <= 1e-2
+        assert helpers.cosine(d["step_logits"], want_logits[1]) >= 0.9999

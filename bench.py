@@ -352,8 +352,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    # in-switch reduction off in every library used: a rank that dies while bound to an NVLink
-    # multicast object can fault its peers
+    # in-switch reduction off in every library used: a rank that dies while its memory is bound
+    # to the switch's shared mapping can fault its peers
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 
     if args.impl == "reference":

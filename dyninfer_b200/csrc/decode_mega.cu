@@ -84,7 +84,10 @@ constexpr int MK_OFF_WACC = MK_OFF_RED + 64;         // [16][128] per-warp weigh
 constexpr int MK_OFF_ROPE = MK_OFF_WACC + 16 * 128;  // cos[64], sin[64] of this token's position
 constexpr int MK_OFF_RES = MK_OFF_ROPE + 128;        // [64] residual rows this CTA owns
 constexpr int MK_OFF_AMAX = MK_OFF_RES + 64;         // [2 x 128] argmax candidates
-constexpr int MK_MISC_FLOATS = MK_OFF_AMAX + 256;
+constexpr int MK_OFF_KVK = MK_OFF_AMAX + 256;        // 16 KB: the first batch of cached keys of this CTA's (head, split)
+constexpr int MK_OFF_KVV = MK_OFF_KVK + 4096;        // 16 KB: and of cached values
+constexpr int MK_MISC_FLOATS = MK_OFF_KVV + 4096;
+constexpr int MK_KV_STAGE_BYTES = 16384;             // 64 rows of 128 two-byte elements, or 32 rows of f32
 constexpr int MK_MAX_OWNED = 64;  // hidden rows per CTA
 constexpr long long MK_MBAR_SPINS = 1LL << 22;
 constexpr long long MK_LL_SPINS = 1LL << 21;  // x ~0.5 us per poll round
@@ -284,16 +287,30 @@ __device__ __forceinline__ unsigned long long gtime() {
 // conversion), 10 waiting for weights, 11 tile math, 12 round reduction + epilogue; attention of
 // CTA 0: 13 until q/k/v are in place, 14 scores and softmax, 15 merge and write; staging split: 16 until
 // the vector has arrived, 17 reduction + conversion.
-struct Prof {
+// INSTR = false compiles every method to nothing: the kernel that serves requests carries no timer
+// code (the instrumented twin is launched when a profile or a trace was asked for).
+template <bool INSTR>
+struct ProfT {
   unsigned long long* out;
   unsigned long long* trace;  // this CTA's [layers + 1][16] stamps (thread 0), or nullptr
   int layer;
   unsigned long long last, start;
   bool on;
   __device__ void stamp(int id) {
+    if constexpr (!INSTR) return;
+#ifdef MK_DEBUG_ATT_STAMPS
+    if (id >= 9 && id <= 13) return;
+#endif
     if (trace) trace[layer * 16 + id] = gtime();
   }
+  __device__ void stamp_dbg(int id) {
+    if constexpr (!INSTR) return;
+#ifdef MK_DEBUG_ATT_STAMPS
+    if (trace) trace[layer * 16 + id] = gtime();
+#endif
+  }
   __device__ void begin(unsigned long long* p, bool active) {
+    if constexpr (!INSTR) return;
     out = p;
     on = active && p != nullptr;
     if (on) {
@@ -302,6 +319,7 @@ struct Prof {
     }
   }
   __device__ void mark(int kind) {
+    if constexpr (!INSTR) return;
     if (on) {
       const unsigned long long t = gtime();
       out[kind] += t - last;
@@ -309,10 +327,15 @@ struct Prof {
     }
   }
   __device__ void end() {
+    if constexpr (!INSTR) return;
     if (on) out[8] = gtime() - start;
   }
-  __device__ unsigned long long tic() const { return on ? gtime() : 0ULL; }
+  __device__ unsigned long long tic() const {
+    if constexpr (!INSTR) return 0ULL;
+    return on ? gtime() : 0ULL;
+  }
   __device__ void toc(int kind, unsigned long long t0) {
+    if constexpr (!INSTR) return;
     if (on) out[kind] += gtime() - t0;
   }
 };
@@ -630,43 +653,89 @@ __device__ __forceinline__ bool arg_better(float v, long long i, float bv, long 
 // Latency plan: the cached keys and values of earlier positions and the norm weights are requested
 // first; then warps 0 / 1 / 2 poll this token's q / k / v of the head (one or two lines per lane),
 // normalise and rotate them inside the warp (no block reduction) and leave them in shared memory.
-// The cached rows [k_lo, min(k_hi, pos)) of this CTA's (head, split) in layer l: one run per pool.
-__device__ __forceinline__ void prefetch_kv(const MegaArgs& a, int l, int cta, int64_t pos, int64_t seq, int nsplit,
-                                            int tid) {
-  if (cta >= a.nh * nsplit || l >= a.layers || (a.opts & 1)) return;
-  const int h = cta / nsplit, sp = cta - h * nsplit;
-  const int kvh = h / (a.nh / a.nkv);
-  const int64_t n = pos + 1, per = (n + nsplit - 1) / nsplit;
-  const int64_t k_lo = (int64_t)sp * per;
-  int64_t k_hi = (k_lo + per < n) ? k_lo + per : n;
-  if (k_hi > pos) k_hi = pos;
-  if (k_hi <= k_lo) return;
-  const size_t el = a.kv_type == E_F32 ? 4 : 2;
-  const size_t start = (size_t)(((seq * a.nkv + kvh) * a.cap + k_lo) * a.d) * el;
-  const size_t bytes = (size_t)(k_hi - k_lo) * a.d * el;
-  prefetch_span(a.kcache + (uint64_t)l * a.layer_stride + start, bytes, tid, MK_CT);
-  prefetch_span(a.vcache + (uint64_t)l * a.layer_stride + start, bytes, tid, MK_CT);
+// The cached rows [k_lo, min(k_hi, pos)) of this CTA's (head, split) in layer l are one run per pool.
+// Its first batch (64 rows of a 2-byte cache, 32 of an f32 cache) is copied into shared memory with
+// 16-byte asynchronous copies a layer ahead: a load issued when attention begins would queue behind
+// the weight copies that refill the ring at that moment (measured: ~1 us until the rows arrived).
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Byte offset of byte `b` of staged row `row`: 16-byte pieces of odd rows of a 2-byte cache are
+// exchanged in groups of four (piece ^ 4), which makes the score loop's 16-byte reads (two rows per
+// quarter warp, four threads per row) free of bank conflicts. Rows of an f32 cache need no exchange.
+__device__ __forceinline__ int kv_stage_off(int row, int b, int rowbytes, bool wide) {
+  const int piece = (b >> 4) ^ ((!wide && (row & 1)) ? 4 : 0);
+  return row * rowbytes + (piece << 4) + (b & 15);
 }
 
-template <bool WIDE>  // f32 cache (16 bytes per lane and row) or a 2-byte type (8 bytes)
+// Copies the cached rows [k_first, k_first + batch) ∩ [.., min(k_hi, pos)) of this CTA's (head, split)
+// in layer l into the staging buffers (asynchronous, one commit group).
+__device__ __forceinline__ void stage_kv(const MegaArgs& a, int l, int cta, int64_t pos, int64_t seq, int nsplit,
+                                         const Smem& sm, int tid, int batch_index = 0) {
+  if (cta >= a.nh * nsplit || l >= a.layers) return;
+  const int h = cta / nsplit, sp = cta - h * nsplit;
+  const int kvh = h / (a.nh / a.nkv);
+  const bool wide = a.kv_type == E_F32;
+  const int el = wide ? 4 : 2, rowbytes = a.d * el;
+  const int64_t n = pos + 1, per = (n + nsplit - 1) / nsplit;
+  const int64_t k_first = (int64_t)sp * per + (int64_t)batch_index * (wide ? 32 : 64);
+  int64_t k_hi = ((int64_t)sp * per + per < n) ? (int64_t)sp * per + per : n;
+  if (k_hi > pos) k_hi = pos;
+  if (k_hi <= k_first) return;
+  const size_t start = (size_t)(((seq * a.nkv + kvh) * a.cap + k_first) * a.d) * el;
+  int bytes = (int)((k_hi - k_first) * rowbytes);  // a multiple of 128
+  if (bytes > MK_KV_STAGE_BYTES) bytes = MK_KV_STAGE_BYTES;
+  const uint8_t* ksrc = a.kcache + (uint64_t)l * a.layer_stride + start;
+  const uint8_t* vsrc = a.vcache + (uint64_t)l * a.layer_stride + start;
+  uint8_t* kdst = reinterpret_cast<uint8_t*>(sm.misc + MK_OFF_KVK);
+  uint8_t* vdst = reinterpret_cast<uint8_t*>(sm.misc + MK_OFF_KVV);
+  const int rshift = 31 - __clz(rowbytes);  // rows are 128, 256 or 512 bytes
+  for (int off = tid * 16; off < bytes; off += MK_CT * 16) {
+    const int row = off >> rshift;
+    const int o = kv_stage_off(row, off - (row << rshift), rowbytes, wide);
+    cp_async16(kdst + o, ksrc + off);
+    cp_async16(vdst + o, vsrc + off);
+  }
+  cp_async_commit();
+}
+
+// Attention of one (head, split) over the keys [k_lo, k_hi), in batches of 64 (32 for an f32 cache)
+// staged in shared memory. The code is deliberately compact (rolled loops, no per-key unrolling): it
+// runs once per layer, and instructions that are not in the instruction cache cost more than the
+// arithmetic they encode.
+//   scores : thread (key = tid / TPK, part = tid % TPK) multiplies q with 16-byte pieces part,
+//            part + TPK, ... of its key's row; TPK lanes add up by shuffle
+//   softmax: batch maximum and sum through shared memory (two block barriers), running maximum and
+//            sum across batches
+//   values : thread (pair = tid % (d/2), group = tid / (d/2)) accumulates two head dims over the
+//            keys of its group; groups are added in a fixed order at the end
+template <int KVT, class Prof>
 __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, const MegaLayerHot* L, int cta,
                                                 int64_t pos, int64_t seq, int nsplit, unsigned ep,
                                                 const Smem& sm, int tid, int lane, int warp, Prof& prof) {
   if (cta >= a.nh * nsplit) return;
+  constexpr bool WIDE = KVT == E_F32;
+  constexpr int EL = WIDE ? 4 : 2;
+  constexpr int BK = WIDE ? 32 : 64;    // keys per batch
+  constexpr int TPK = MK_CT / BK;       // threads per key
+  constexpr int EPP = 16 / EL;          // elements per 16-byte piece
   unsigned long long tp = prof.tic();
-  // keys in flight per warp: with a 2-byte cache one batch covers the 64 keys of a split
-  constexpr int KB = (WIDE ? 32 : 64) / MK_CW;
-  constexpr int DPL = 4;  // head dims per lane
   const int h = cta / nsplit, sp = cta - h * nsplit;
   const int grp = a.nh / a.nkv, kvh = h / grp, gi = h - kvh * grp;
-  const int d = a.d, half = d / 2;
+  const int d = a.d, half = d / 2, rowbytes = d * EL;
   float* qs = sm.misc + MK_OFF_QS;
   float* kn = sm.misc + MK_OFF_KN;
   float* vn = sm.misc + MK_OFF_VN;
   float* wm = sm.misc + MK_OFF_WM;
   float* wl = sm.misc + MK_OFF_WL;
-  float* wwt = sm.misc + MK_OFF_RED;
+  float* ps = sm.misc + MK_OFF_RED;     // [64] the batch's softmax numerators
   float* wacc = sm.misc + MK_OFF_WACC;
+  uint8_t* kbuf = reinterpret_cast<uint8_t*>(sm.misc + MK_OFF_KVK);
+  uint8_t* vbuf = reinterpret_cast<uint8_t*>(sm.misc + MK_OFF_KVV);
   uint8_t* kc = a.kcache + (uint64_t)l * a.layer_stride;
   uint8_t* vc = a.vcache + (uint64_t)l * a.layer_stride;
   const int64_t plane = ((seq * a.nkv + kvh) * a.cap) * d;  // element offset of this head's plane
@@ -675,48 +744,18 @@ __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, cons
   const int per = (n + nsplit - 1) / nsplit;
   const int k_lo = sp * per;
   const int k_hi = (k_lo + per < n) ? k_lo + per : n;
-  // A lane owns DPL consecutive head dims (one 8- or 16-byte piece of every cached row), so a
-  // warp reads a key or value row with one coalesced vector load.
-  constexpr int WPL = WIDE ? DPL : DPL / 2;  // raw words per lane and row
-  const int e0 = lane * DPL;  // first head dim of this lane
-  const bool lane_live = e0 < d;
-  uint32_t kraw[KB][WPL], vraw[KB][WPL];
-  auto fetch = [&](int key0) {
-#pragma unroll
-    for (int b = 0; b < KB; b++) {
-      const int key = key0 + b * MK_CW;
-#pragma unroll
-      for (int w = 0; w < WPL; w++) kraw[b][w] = vraw[b][w] = 0;
-      if (key < k_hi && key != pos32 && lane_live) {
-        const int64_t el = plane + (int64_t)key * d + e0;
-        if constexpr (WIDE) {
-          const uint4 kk = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(kc) + el));
-          const uint4 vv = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(vc) + el));
-          kraw[b][0] = kk.x, kraw[b][1] = kk.y, kraw[b][2] = kk.z, kraw[b][3] = kk.w;
-          vraw[b][0] = vv.x, vraw[b][1] = vv.y, vraw[b][2] = vv.z, vraw[b][3] = vv.w;
-        } else {
-          const uint2 kk = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(kc) + el));
-          const uint2 vv = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(vc) + el));
-          kraw[b][0] = kk.x, kraw[b][1] = kk.y;
-          vraw[b][0] = vv.x, vraw[b][1] = vv.y;
-        }
-      }
-    }
+  // this token's own key / value row goes into the staged batch that holds position pos
+  auto put_own = [&](uint8_t* buf, int row, int e, float v) {
+    const int o = kv_stage_off(row, e * EL, rowbytes, WIDE);
+    if constexpr (WIDE)
+      *reinterpret_cast<float*>(buf + o) = v;
+    else if constexpr (KVT == E_BF16)
+      *reinterpret_cast<__nv_bfloat16*>(buf + o) = __float2bfloat16_rn(v);
+    else
+      *reinterpret_cast<__half*>(buf + o) = __float2half_rn(v);
   };
-  // a raw row piece as f32 (one branch per piece, not per element)
-  auto unpack = [&](const uint32_t (&raw)[WPL], float (&f)[DPL]) {
-    if constexpr (WIDE) {
-#pragma unroll
-      for (int j = 0; j < DPL; j++) f[j] = __uint_as_float(raw[j]);
-    } else if (a.kv_type == E_BF16) {
-      f[0] = __uint_as_float(raw[0] << 16), f[1] = __uint_as_float(raw[0] & 0xffff0000u);
-      f[2] = __uint_as_float(raw[1] << 16), f[3] = __uint_as_float(raw[1] & 0xffff0000u);
-    } else {
-      f[0] = f16_bits_to_f32(raw[0] & 0xffffu), f[1] = f16_bits_to_f32(raw[0] >> 16);
-      f[2] = f16_bits_to_f32(raw[1] & 0xffffu), f[3] = f16_bits_to_f32(raw[1] >> 16);
-    }
-  };
-  fetch(k_lo + warp);  // in flight while q / k / v of this token arrive
+  const bool own_here = pos32 >= k_lo && pos32 < k_hi;  // the last split
+  const int own_row0 = pos32 - k_lo;                      // its row if it falls into the first batch
 
   if (warp < 3) {
     // lane j < d/4 holds elements i = 2j, 2j+1 and their rotation partners i + d/2
@@ -756,123 +795,156 @@ __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, cons
     }
     if (act) {
       float* dst = warp == 0 ? qs : (warp == 1 ? kn : vn);
-      const bool rnd = warp != 0;
-      dst[i0] = rnd ? round_kv(x[0], a.kv_type) : x[0];
-      dst[i0 + 1] = rnd ? round_kv(x[1], a.kv_type) : x[1];
-      dst[i0 + half] = rnd ? round_kv(x[2], a.kv_type) : x[2];
-      dst[i0 + half + 1] = rnd ? round_kv(x[3], a.kv_type) : x[3];
+      const int e[4] = {i0, i0 + 1, i0 + half, i0 + half + 1};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        dst[e[j]] = warp == 0 ? x[j] : round_kv(x[j], KVT);
+        if (warp != 0 && own_here && own_row0 < BK) put_own(warp == 1 ? kbuf : vbuf, own_row0, e[j], x[j]);
+      }
     }
   }
+  cp_async_wait_all();  // this thread's share of the staged rows; the barrier covers the others'
   consumer_sync();
   prof.stamp(3);
   prof.toc(13, tp);
   tp = prof.tic();
   if (sp == 0 && gi == 0) {
     for (int i = tid; i < d; i += MK_CT) {
-      store_kv(kc, a.kv_type, plane + pos * d + i, kn[i]);
-      store_kv(vc, a.kv_type, plane + pos * d + i, vn[i]);
+      store_kv(kc, KVT, plane + pos * d + i, kn[i]);
+      store_kv(vc, KVT, plane + pos * d + i, vn[i]);
     }
   }
   const float scale = 1.0f / sqrtf((float)d);
-  float qreg[DPL], acc[DPL];
-#pragma unroll
-  for (int j = 0; j < DPL; j++) {
-    qreg[j] = lane_live ? qs[e0 + j] : 0.f;
-    acc[j] = 0.f;
-  }
-  float m = -3.40282347e38f, lsum = 0.f;
-  for (int key0 = k_lo + warp; key0 < k_hi; key0 += KB * MK_CW) {
-    if (key0 != k_lo + warp) fetch(key0);
-    float sc[KB];
-#pragma unroll
-    for (int b = 0; b < KB; b++) {
-      float kf[DPL];
-      unpack(kraw[b], kf);
-      if (key0 + b * MK_CW == pos32 && lane_live) {  // this token's own key (warp-uniform)
-#pragma unroll
-        for (int j = 0; j < DPL; j++) kf[j] = kn[e0 + j];
+  const int kl = tid / TPK, part = tid - kl * TPK;  // key within the batch, piece phase
+  const int npair = d >> 1, kg = tid / npair, dp = tid - kg * npair;  // value pass: dim pair, key group
+  const int kpg = BK / (MK_CT / npair);                                // keys per group
+  const int npiece = rowbytes >> 4;
+  float m_run = -3.40282347e38f, l_run = 0.f, acc0 = 0.f, acc1 = 0.f;
+  int bi = 0;
+  for (int k0 = k_lo; k0 < k_hi; k0 += BK, bi++) {
+    if (bi > 0) {  // long contexts: the later batches are brought in when their turn comes
+      consumer_sync();  // everyone is done with the previous batch
+      stage_kv(a, l, cta, pos, seq, nsplit, sm, tid, bi);
+      if (own_here && pos32 >= k0 && pos32 < k0 + BK && tid < d) {
+        put_own(kbuf, pos32 - k0, tid, kn[tid]);
+        put_own(vbuf, pos32 - k0, tid, vn[tid]);
       }
-      float dot = 0.f;
-#pragma unroll
-      for (int j = 0; j < DPL; j++) dot = fmaf(qreg[j], kf[j], dot);
-      sc[b] = warp_sum(dot) * scale;
+      cp_async_wait_all();
+      consumer_sync();
     }
-    // one rescale per batch: the batch maximum first, then independent exponentials
-    float mb = m;
+    const int nvalid = k_hi - k0 < BK ? k_hi - k0 : BK;
+    // ---- scores
+    float dot = 0.f;
+    if (kl < nvalid) {
+#pragma unroll 2
+      for (int pc = part; pc < npiece; pc += TPK) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(kbuf + kv_stage_off(kl, pc << 4, rowbytes, WIDE));
+        const float* q = qs + pc * EPP;
+        const float4 q0 = *reinterpret_cast<const float4*>(q);
+        if constexpr (WIDE) {
+          dot = fmaf(q0.x, __uint_as_float(raw.x), dot), dot = fmaf(q0.y, __uint_as_float(raw.y), dot);
+          dot = fmaf(q0.z, __uint_as_float(raw.z), dot), dot = fmaf(q0.w, __uint_as_float(raw.w), dot);
+        } else {
+          const float4 q1 = *reinterpret_cast<const float4*>(q + 4);
+          const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+          const float qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-    for (int b = 0; b < KB; b++)
-      if (key0 + b * MK_CW < k_hi) mb = fmaxf(mb, sc[b]);
-    const float factor = expf(m - mb);
-    float p[KB];
-#pragma unroll
-    for (int b = 0; b < KB; b++) p[b] = key0 + b * MK_CW < k_hi ? expf(sc[b] - mb) : 0.f;
-    float psum = 0.f;
-#pragma unroll
-    for (int b = 0; b < KB; b++) psum += p[b];
-    lsum = lsum * factor + psum;
-#pragma unroll
-    for (int j = 0; j < DPL; j++) acc[j] *= factor;
-#pragma unroll
-    for (int b = 0; b < KB; b++) {
-      float vf[DPL];
-      unpack(vraw[b], vf);
-      if (key0 + b * MK_CW == pos32 && lane_live) {
-#pragma unroll
-        for (int j = 0; j < DPL; j++) vf[j] = vn[e0 + j];
+          for (int j = 0; j < 4; j++) {
+            const float lo = KVT == E_BF16 ? __uint_as_float(r[j] << 16) : f16_bits_to_f32(r[j] & 0xffffu);
+            const float hi = KVT == E_BF16 ? __uint_as_float(r[j] & 0xffff0000u) : f16_bits_to_f32(r[j] >> 16);
+            dot = fmaf(qq[2 * j], lo, dot);
+            dot = fmaf(qq[2 * j + 1], hi, dot);
+          }
+        }
       }
-#pragma unroll
-      for (int j = 0; j < DPL; j++) acc[j] = fmaf(p[b], vf[j], acc[j]);
     }
-    m = mb;
+#pragma unroll
+    for (int o = 1; o < TPK; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float sc = kl < nvalid ? dot * scale : -INFINITY;
+    const float wmax = warp_max(sc);
+    if (lane == 0) wm[warp] = wmax;
+    consumer_sync();
+    float m_new = m_run;
+#pragma unroll
+    for (int w = 0; w < MK_CW; w++) m_new = fmaxf(m_new, wm[w]);
+    const float pr = expf(sc - m_new);  // a key past the range: exp(-inf) = 0
+    if (part == 0) ps[kl] = pr;
+    const float wsum = warp_sum(part == 0 ? pr : 0.f);
+    if (lane == 0) wl[warp] = wsum;
+    consumer_sync();
+    float l_batch = 0.f;
+#pragma unroll
+    for (int w = 0; w < MK_CW; w++) l_batch += wl[w];
+    const float factor = expf(m_run - m_new);
+    l_run = l_run * factor + l_batch;
+    acc0 *= factor, acc1 *= factor;
+    m_run = m_new;
+    // ---- values
+    const int kq_end = (kg + 1) * kpg < nvalid ? (kg + 1) * kpg : nvalid;
+#pragma unroll 4
+    for (int kq = kg * kpg; kq < kq_end; kq++) {
+      const float pk = ps[kq];
+      const uint8_t* vp = vbuf + kv_stage_off(kq, dp * 2 * EL, rowbytes, WIDE);
+      float v0, v1;
+      if constexpr (WIDE) {
+        const float2 vv = *reinterpret_cast<const float2*>(vp);
+        v0 = vv.x, v1 = vv.y;
+      } else {
+        const uint32_t r = *reinterpret_cast<const uint32_t*>(vp);
+        v0 = KVT == E_BF16 ? __uint_as_float(r << 16) : f16_bits_to_f32(r & 0xffffu);
+        v1 = KVT == E_BF16 ? __uint_as_float(r & 0xffff0000u) : f16_bits_to_f32(r >> 16);
+      }
+      acc0 = fmaf(pk, v0, acc0);
+      acc1 = fmaf(pk, v1, acc1);
+    }
   }
   prof.toc(14, tp);
   prof.stamp(14);
   tp = prof.tic();
-  if (lane == 0) {
-    wm[warp] = m;
-    wl[warp] = lsum;
-  }
-  if (lane_live) {
-#pragma unroll
-    for (int j = 0; j < DPL; j++) wacc[warp * 128 + e0 + j] = acc[j];
-  }
-  consumer_sync();
-  float gm = wm[0];
-#pragma unroll
-  for (int w = 1; w < MK_CW; w++) gm = fmaxf(gm, wm[w]);
-  // each warp's weight exp(m_w - gm) once, by one lane per warp, instead of per output element
-  if (tid < MK_CW) wwt[tid] = expf(wm[tid] - gm);
+  // the key groups' sums meet in shared memory and are added in group order
+  wacc[kg * 128 + 2 * dp] = acc0;
+  wacc[kg * 128 + 2 * dp + 1] = acc1;
   consumer_sync();
   prof.stamp(15);
-  float gl = 0.f;
-#pragma unroll
-  for (int w = 0; w < MK_CW; w++) gl += wl[w] * wwt[w];
+  const int ngroups = MK_CT / npair;
   const int64_t pbase = ((int64_t)h * a.max_split + sp) * (d + 4);
-  for (int idx = tid; idx < d; idx += MK_CT) {
+  if (tid < d) {
     float o = 0.f;
-#pragma unroll
-    for (int w = 0; w < MK_CW; w++) o += wacc[w * 128 + idx] * wwt[w];
+    for (int g = 0; g < ngroups; g++) o += wacc[g * 128 + tid];
     if (nsplit == 1)
-      ll_store(a.ll_ctx, (int64_t)h * d + idx, o / gl, ep);
+      ll_store(a.ll_ctx, (int64_t)h * d + tid, o / l_run, ep);
     else
-      ll_store(a.ll_part, pbase + idx, o, ep);
+      ll_store(a.ll_part, pbase + tid, o, ep);
   }
   if (nsplit > 1 && tid == 0) {
-    ll_store(a.ll_part, pbase + d, gm, ep);
-    ll_store(a.ll_part, pbase + d + 1, gl, ep);
+    ll_store(a.ll_part, pbase + d, m_run, ep);
+    ll_store(a.ll_part, pbase + d + 1, l_run, ep);
   }
   prof.stamp(4);
   prof.toc(15, tp);
-  prefetch_kv(a, l + 1, cta, pos, seq, nsplit, tid);  // the next layer's rows: in L2 by the time they are read
+  consumer_sync();  // wacc and the staging buffers are free again
+  stage_kv(a, l + 1, cta, pos, seq, nsplit, sm, tid);  // the next layer's first batch
 }
 
+template <class Prof>
 __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const MegaLayerHot* L, int cta,
                                                 int64_t pos, int64_t seq, int nsplit, unsigned ep,
                                                 const Smem& sm, int tid, int lane, int warp, Prof& prof) {
+#ifndef MK_SIZE_PROBE
   if (a.kv_type == E_F32)
-    phase_attention_t<true>(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
+    phase_attention_t<E_F32>(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
   else
-    phase_attention_t<false>(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
+#endif
+#if !defined(MK_SIZE_PROBE) || MK_SIZE_PROBE < 3
+  if (a.kv_type == E_BF16)
+#else
+  if (false)
+#endif
+    phase_attention_t<E_BF16>(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
+#ifndef MK_SIZE_PROBE
+  else
+    phase_attention_t<E_F16>(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
+#endif
 }
 
 // ---- one phase's rounds, in program order ---------------------------------------------------------
@@ -899,7 +971,7 @@ __device__ __forceinline__ void refill(const MegaArgs& a, const Smem& sm, Walk& 
   if (++w.fill_slot == (uint32_t)sm.nslot) w.fill_slot = 0, w.fill_lap++;
 }
 
-template <int ENC>
+template <int ENC, class Prof>
 __device__ __forceinline__ void run_phase_t(const MegaArgs& a, const Smem& sm, Walk& w, int nr, unsigned ep,
                                             const float* ssq, int n_in, float* res, int hid_lo, int tid, int lane,
                                             int warp, Prof& prof, int sid) {
@@ -1065,6 +1137,7 @@ __device__ __forceinline__ void run_phase_t(const MegaArgs& a, const Smem& sm, W
 // phase word: low byte = rounds, high byte = the phase's common encoding (0xff: per chunk)
 // Stages the phase's input vector (per warp where the encoding allows) and runs its rounds. A CTA
 // without rows in the phase neither waits for the vector nor stages it.
+template <class Prof>
 __device__ __forceinline__ void run_phase(const MegaArgs& a, const Smem& sm, Walk& w, int phase_index, unsigned ep,
                                           const StageSrc& src, const void* nw, int nw_type, int n_in, int layout_enc,
                                           float* res, int hid_lo, int tid, int lane, int warp, Prof& prof) {
@@ -1080,21 +1153,28 @@ __device__ __forceinline__ void run_phase(const MegaArgs& a, const Smem& sm, Wal
                 lane, warp);
     if (nw) ssq = mine;
   } else {
+#if !defined(MK_SIZE_PROBE) || MK_SIZE_PROBE < 4
     stage_phase(src, nw, nw_type, n_in, a.eps, xl_for_encoding(layout_enc), sm, tid, lane, warp);
+#endif
   }
   prof.toc(9, ts);
   const int sid = (phase_index & 3) == 0 ? 0 : 2 + 3 * (phase_index & 3);  // 0, 5, 8, 11
   prof.stamp(sid);
   if (enc == E_Q4_0)
     run_phase_t<E_Q4_0>(a, sm, w, nr, ep, ssq, n_in, res, hid_lo, tid, lane, warp, prof, sid);
+#if !defined(MK_SIZE_PROBE) || MK_SIZE_PROBE < 2
   else if (enc == E_Q6_K)
     run_phase_t<E_Q6_K>(a, sm, w, nr, ep, ssq, n_in, res, hid_lo, tid, lane, warp, prof, sid);
+#endif
+#ifndef MK_SIZE_PROBE
   else
     run_phase_t<-1>(a, sm, w, nr, ep, ssq, n_in, res, hid_lo, tid, lane, warp, prof, sid);
+#endif
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaArgs a) {
+template <bool INSTR>
+__device__ __forceinline__ void decode_mega_body(const MegaArgs& a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int cta = blockIdx.x, G = gridDim.x;
@@ -1160,7 +1240,7 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
   wk.fill_seq = wk.fill_idx = wk.fill_slot = wk.fill_lap = 0;
   wk.fill_step = (sm.nchunks == 0 || *sm.abort) ? (uint32_t)a.steps : 0u;
   for (int i = 0; i < sm.nslot - 1; i++) refill(a, sm, wk, lane, warp);  // the ring's first fill: warp i issues chunk i
-  Prof prof;
+  ProfT<INSTR> prof;
   // One launch decodes a.steps tokens: every CTA learns each token from the argmax hand-off and goes
   // on with the next position; the weight ring and its barriers simply keep running.
   for (int step = 0; step < a.steps; step++) {
@@ -1171,7 +1251,7 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
   wk.ci = wk.ri = wk.ti = 0;
   wk.bv = -INFINITY, wk.bi = 0x7fffffffffffffffLL;
   prof.begin(a.prof, cta == 0 && tid == 0);
-  prof.trace = (a.trace && tid == 0) ? a.trace + (size_t)cta * (a.layers + 1) * 16 : nullptr;
+  if constexpr (INSTR) prof.trace = (a.trace && tid == 0) ? a.trace + (size_t)cta * (a.layers + 1) * 16 : nullptr;
   prof.layer = 0;
 
   if (a.has_rope && tid < a.d / 2) {
@@ -1181,7 +1261,7 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
     sm.misc[MK_OFF_ROPE + tid] = cv;
     sm.misc[MK_OFF_ROPE + 64 + tid] = sv;
   }
-  prefetch_kv(a, 0, cta, pos, seq, nsplit, tid);
+  stage_kv(a, 0, cta, pos, seq, nsplit, sm, tid);
   // every CTA decodes the token's embedding row for itself: no hand-off before the first product
   mega_gather_row(a.embed, token, sm.xs, tid, MK_CT);
   consumer_sync();
@@ -1193,45 +1273,54 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
 
   StageSrc src;
   src.nsplit = nsplit, src.max_split = a.max_split, src.d = a.d;
-  for (int l = 0; l < a.layers; l++) {
-    const MegaLayerHot* L = sm.hot + l;
-    if (!(a.opts & 2)) {  // the next layer's norm vectors (the final one behind the last layer)
-      const size_t nel = L->norm_type == E_F32 ? 4 : 2, qel = L->qk_norm_type == E_F32 ? 4 : 2;
-      if (l + 1 < a.layers) {
-        prefetch_span(L[1].attn_norm, (size_t)a.H * nel, tid, MK_CT);
-        prefetch_span(L[1].ffn_norm, (size_t)a.H * nel, tid, MK_CT);
-        if (a.has_norm && cta < a.nh * nsplit && tid < 2)
-          prefetch_span(tid == 0 ? L[1].q_norm : L[1].k_norm, (size_t)a.d * qel, 0, 1);
-      } else {
-        prefetch_span(a.out_norm, (size_t)a.H * (a.out_norm_type == E_F32 ? 4 : 2), tid, MK_CT);
+  // One loop over the 4 * layers + 1 products (q/k/v, o, gate/up, down per layer, then the head) so
+  // that the product code exists once in the kernel: the five products of a layer run the same
+  // instructions, which then stay in the instruction cache from layer to layer.
+  const int nprod = 4 * a.layers;
+  const MegaLayerHot* L = sm.hot;
+  unsigned ep = epoch_base;
+  for (int ph = 0; ph <= nprod; ph++) {
+    const int l = ph >> 2, k = ph & 3;
+    const bool head = ph == nprod;
+    const void* nw = nullptr;
+    int nw_type = 0, n_in, lenc;
+    if (k == 0) {
+      // layer l begins (l == layers: the final norm and the head, which follow the same hand-off rule)
+      ep = epoch_base + 1u + (unsigned)l;
+      prof.layer = l;
+      if (!head) {
+        L = sm.hot + l;
+        if (!(a.opts & 2)) {  // the next layer's norm vectors (the final one behind the last layer)
+          const size_t nel = L->norm_type == E_F32 ? 4 : 2, qel = L->qk_norm_type == E_F32 ? 4 : 2;
+          if (l + 1 < a.layers) {
+            prefetch_span(L[1].attn_norm, (size_t)a.H * nel, tid, MK_CT);
+            prefetch_span(L[1].ffn_norm, (size_t)a.H * nel, tid, MK_CT);
+            if (a.has_norm && cta < a.nh * nsplit && tid < 2)
+              prefetch_span(tid == 0 ? L[1].q_norm : L[1].k_norm, (size_t)a.d * qel, 0, 1);
+          } else {
+            prefetch_span(a.out_norm, (size_t)a.H * (a.out_norm_type == E_F32 ? 4 : 2), tid, MK_CT);
+          }
+        }
       }
+      src.kind = l == 0 ? SRC_XS : SRC_LL, src.ll = a.ll_hidden[1], src.ep = ep - 1u;
+      nw = head ? a.out_norm : L->attn_norm, nw_type = head ? a.out_norm_type : L->norm_type;
+      n_in = a.H, lenc = head ? a.lm_head.enc : L->enc_q;
+    } else if (k == 1) {
+      phase_attention(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
+      prof.mark(2);
+      src.kind = nsplit > 1 ? SRC_PARTIALS : SRC_LL, src.ll = nsplit > 1 ? a.ll_part : a.ll_ctx, src.ep = ep;
+      n_in = (int)qd, lenc = L->enc_o;
+    } else if (k == 2) {
+      src.kind = SRC_LL, src.ll = a.ll_hidden[0], src.ep = ep;
+      nw = L->ffn_norm, nw_type = L->norm_type, n_in = a.H, lenc = L->enc_gate;
+    } else {
+      src.kind = SRC_LL, src.ll = a.ll_act, src.ep = ep;
+      n_in = a.I, lenc = L->enc_down;
     }
-    const unsigned ep = epoch_base + 1u + (unsigned)l;
-    prof.layer = l;
-    src.kind = l == 0 ? SRC_XS : SRC_LL, src.ll = a.ll_hidden[1], src.ep = ep - 1u;
-    run_phase(a, sm, wk, 4 * l + 0, ep, src, L->attn_norm, L->norm_type, a.H, L->enc_q, res, hid_lo, tid, lane, warp,
-              prof);
-    prof.mark(1);
-    phase_attention(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
-    prof.mark(2);
-    src.kind = nsplit > 1 ? SRC_PARTIALS : SRC_LL, src.ll = nsplit > 1 ? a.ll_part : a.ll_ctx, src.ep = ep;
-    run_phase(a, sm, wk, 4 * l + 1, ep, src, nullptr, 0, (int)qd, L->enc_o, res, hid_lo, tid, lane, warp, prof);
-    prof.mark(3);
-    src.kind = SRC_LL, src.ll = a.ll_hidden[0], src.ep = ep;
-    run_phase(a, sm, wk, 4 * l + 2, ep, src, L->ffn_norm, L->norm_type, a.H, L->enc_gate, res, hid_lo, tid, lane, warp,
-              prof);
-    prof.mark(4);
-    src.kind = SRC_LL, src.ll = a.ll_act, src.ep = ep;
-    run_phase(a, sm, wk, 4 * l + 3, ep, src, nullptr, 0, a.I, L->enc_down, res, hid_lo, tid, lane, warp, prof);
-    prof.mark(5);
+    run_phase(a, sm, wk, ph, ep, src, nw, nw_type, n_in, lenc, res, hid_lo, tid, lane, warp, prof);
+    prof.mark(head ? 6 : (k == 0 ? 1 : 2 + k));
   }
-
-  // ---- final norm + lm_head + argmax (first strict maximum)
   const unsigned ep_last = epoch_base + (unsigned)a.layers;
-  prof.layer = a.layers;
-  src.kind = a.layers > 0 ? SRC_LL : SRC_XS, src.ll = a.ll_hidden[1], src.ep = ep_last;
-  run_phase(a, sm, wk, 4 * a.layers, ep_last + 1u, src, a.out_norm, a.out_norm_type, a.H, a.lm_head.enc, res, hid_lo,
-            tid, lane, warp, prof);
   {
     // the (at most 128) finishing threads hold this CTA's candidates
     float* cv = sm.misc + MK_OFF_AMAX;
@@ -1315,6 +1404,12 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaAr
     while (clock64() - t0 < (1LL << 22)) {
     }
   }
+}
+
+__global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel(const MegaArgs a) { decode_mega_body<false>(a); }
+// the same kernel with the per-phase timers and the event trace compiled in
+__global__ void __launch_bounds__(MK_THREADS, 1) decode_mega_kernel_timed(const MegaArgs a) {
+  decode_mega_body<true>(a);
 }
 
 }  // namespace
@@ -1588,6 +1683,7 @@ bool mega_supports_weight(const WRef& w) {
 
 int mega_grid_size(int device, size_t smem, int* grid) {
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(decode_mega_kernel), (int)smem)) return 1;
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(decode_mega_kernel_timed), (int)smem)) return 1;
   int sms = 0, per_sm = 0, coop = 0;
   DYN_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
   DYN_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
@@ -1601,8 +1697,9 @@ int mega_grid_size(int device, size_t smem, int* grid) {
 
 int launch_decode_mega(const MegaArgs& a, int grid, size_t smem, cudaStream_t s) {
   void* args[] = {const_cast<MegaArgs*>(&a)};
-  DYN_CUDA(cudaLaunchCooperativeKernel((void*)decode_mega_kernel, dim3(grid), dim3(MK_THREADS), args,
-                                       smem, s));
+  const bool timed = a.prof != nullptr || a.trace != nullptr;
+  DYN_CUDA(cudaLaunchCooperativeKernel(timed ? (void*)decode_mega_kernel_timed : (void*)decode_mega_kernel, dim3(grid),
+                                       dim3(MK_THREADS), args, smem, s));
   count_launch();
   return 0;
 }

@@ -62,10 +62,13 @@ constexpr int CS_MAX_SMEM = 226 * 1024;  // dynamic shared memory the kernel may
 // sx8[b] = sum_factor * sum(block b of the scaled row) in accumulator units (8 = the Q4_0 zero point;
 // 1 for Q4_1, whose minimum multiplies the plain sum).
 // Returns 2^24 / scale (what turns accumulator units back into the product).
-__device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf16, int K, uint2* xq,
+// K may end half way through a stage (K % 512 == 256): the arrangement then covers Kpad = K + 256
+// elements, the last 256 of them zeros.
+__device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf16, int K, int Kpad, uint2* xq,
                                             float* sx8, float* red, float sum_factor) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   auto ld = [&](int i) -> float {
+    if (i >= K) return 0.f;
     return x_bf16 ? bf16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t*>(x) + i))
                   : __ldg(reinterpret_cast<const float*>(x) + i);
   };
@@ -79,7 +82,7 @@ __device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf
   for (int i = 0; i < CS_WARPS; i++) mx = fmaxf(mx, red[i]);
   float s, is;
   scale_for(mx, &s, &is);
-  for (int j = tid; j < (K >> 2); j += CS_WARPS * 32) {  // item j: block j / 8, mma step j % 8
+  for (int j = tid; j < (Kpad >> 2); j += CS_WARPS * 32) {  // item j: block j / 8, mma step j % 8
     const int b = j >> 3, st = j & 7, i = st >> 1, o = st & 1;
     const int U = b >> 3, r = b & 7, t = r >> 1, e = r & 1;
     const float e0 = ld(b * 32 + 4 * i + o) * s, e1 = ld(b * 32 + 4 * i + o + 2) * s;
@@ -109,7 +112,8 @@ struct CsArgs {
   int64_t rb;            // bytes per row
   int K;
   int S;                 // K-slices per tile
-  int nst;               // stages per item (K / S / 512)
+  int nst;               // stages per item (ceil(K / 512) / S)
+  int tail;              // 1 when the last stage of a row holds one unit (K % 512 == 256)
   int ntiles;
   const void* x;         // the activation row
   int x_bf16;
@@ -131,8 +135,9 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
   uint8_t* ring = cs_smem + (size_t)warp * CS_NST * G::STAGE;
   uint64_t* bars = reinterpret_cast<uint64_t*>(cs_smem + (size_t)CS_WARPS * CS_NST * G::STAGE) + warp * CS_NST;
   uint4* xq = reinterpret_cast<uint4*>(cs_smem + G::RING_BYTES);
-  float* sx8 = reinterpret_cast<float*>(xq + (size_t)(a.K >> 8) * 64);
-  float* red = sx8 + (a.K >> 5);
+  const int Kpad = a.K + (a.tail ? 256 : 0);
+  float* sx8 = reinterpret_cast<float*>(xq + (size_t)(Kpad >> 8) * 64);
+  float* red = sx8 + (Kpad >> 5);
   pdl_trigger();  // the next kernel of the stream may start its own weight fetch
   if (threadIdx.x == 0) s_abort = 0;
   if (lane == 0) {
@@ -157,13 +162,16 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
   auto issue = [&]() {
     if (c_left <= 0) return;
     c_left--;
-    if (lane == 0) mbar_expect_tx(bars + c_slot, 16 * G::ROWB);
+    // the last stage of a row with a tail holds one unit; the second unit's slot keeps older bytes,
+    // which meet zero activations and whose scales are not applied
+    const unsigned rowb = (a.tail && c_sl == S - 1 && c_st == nst - 1) ? G::ROWB / 2 : G::ROWB;
+    if (lane == 0) mbar_expect_tx(bars + c_slot, 16 * rowb);
     __syncwarp();
     if (lane < 16) {
       int64_t row = (int64_t)c_tile * 16 + lane;
       if (row > last_row) row = last_row;
       const uint8_t* src = a.data + row * a.rb + (int64_t)(c_sl * nst + c_st) * G::ROWB;
-      bulk_g2s(ring + c_slot * G::STAGE + lane * G::PITCH, src, G::ROWB, bars + c_slot);
+      bulk_g2s(ring + c_slot * G::STAGE + lane * G::PITCH, src, rowb, bars + c_slot);
     }
     if (++c_slot == CS_NST) c_slot = 0;
     if (++c_st == nst) {
@@ -179,7 +187,7 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
   pdl_wait();
   // while the first stages are in flight: arrange the activation row in shared memory
   const float out_scale =
-      cs_stage_x(a.x, a.x_bf16, a.K, reinterpret_cast<uint2*>(xq), sx8, red, ENC == E_Q4_0 ? 8.0f : 1.0f);
+      cs_stage_x(a.x, a.x_bf16, a.K, Kpad, reinterpret_cast<uint2*>(xq), sx8, red, ENC == E_Q4_0 ? 8.0f : 1.0f);
   if (blockIdx.x == 0 && threadIdx.x == 0) a.misc[0] = out_scale;
   __syncthreads();
   if (total == 0) return;
@@ -197,6 +205,7 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
         }
         return;  // warp-uniform: every lane polls the same barrier
       }
+      const bool half_stage = a.tail && sl == S - 1 && st == nst - 1;  // warp-uniform
       const uint8_t* base = ring + slot * G::STAGE;
       const uint32_t* r0 = reinterpret_cast<const uint32_t*>(base + g * G::PITCH) + LW * t;
       const uint32_t* r1 = reinterpret_cast<const uint32_t*>(base + (g + 8) * G::PITCH) + LW * t;
@@ -257,6 +266,7 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
 #pragma unroll
       for (int gi = 0; gi < 4; gi++) {
         const int u = gi >> 1;
+        if (u == 1 && half_stage) continue;  // no second unit: its scale bytes are not weights
         const float sx = sxp[u * 8 + (gi & 1)];
         if (ENC == E_Q4_1) {  // w = q * d + m: scale the tile sums, add the minimum times the plain sum
           const __half2 h0 = *reinterpret_cast<const __half2*>(&w0[u][5 * (gi & 1)]);
@@ -316,17 +326,18 @@ struct CsPlan {
 
 size_t cs_smem_bytes(int enc, int K) {
   const size_t ring = enc == E_Q4_0 ? CsGeo<E_Q4_0>::RING_BYTES : CsGeo<E_Q4_1>::RING_BYTES;
-  return ring + (size_t)(K >> 8) * 1024 + (size_t)(K >> 5) * 4 + 128;
+  const int Kpad = (K + CS_KSTAGE - 1) / CS_KSTAGE * CS_KSTAGE;
+  return ring + (size_t)(Kpad >> 8) * 1024 + (size_t)(Kpad >> 5) * 4 + 128;
 }
 
 bool cs_shape_ok(const WRef& w, int M) {
   return M == 1 && (w.enc == E_Q4_0 || w.enc == E_Q4_1) && w.rows >= 1 && w.cols >= CS_KSTAGE &&
-         w.cols % CS_KSTAGE == 0 && cs_smem_bytes(w.enc, (int)w.cols) <= (size_t)CS_MAX_SMEM &&
+         w.cols % (CS_KSTAGE / 2) == 0 && cs_smem_bytes(w.enc, (int)w.cols) <= (size_t)CS_MAX_SMEM &&
          (reinterpret_cast<uintptr_t>(w.data) & 15) == 0;
 }
 
 void cs_plan(const WRef& w, CsPlan* p) {
-  const int K = (int)w.cols, stages = K / CS_KSTAGE;
+  const int K = (int)w.cols, stages = (K + CS_KSTAGE - 1) / CS_KSTAGE;
   p->ntiles = (int)((w.rows + 15) / 16);
   const int sms = std::max(1, sm_count());
   const int64_t warps = (int64_t)sms * CS_WARPS;
@@ -380,7 +391,7 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
   cs_plan(w, &p);
   CsArgs a;
   a.data = w.data, a.N = w.rows, a.rb = w.row_bytes(), a.K = (int)w.cols;
-  a.S = p.S, a.nst = p.nst, a.ntiles = p.ntiles;
+  a.S = p.S, a.nst = p.nst, a.ntiles = p.ntiles, a.tail = (w.cols % CS_KSTAGE) ? 1 : 0;
   a.x = x, a.x_bf16 = x_type == E_BF16 ? 1 : 0;
   a.error = device_error_word();
   if (!a.error) return 1;

@@ -104,10 +104,11 @@ def test_linear_ragged_and_full_shapes(native_lib, oracle, enc, n, k):
 
 
 @pytest.mark.parametrize("enc", ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k"])
-@pytest.mark.parametrize("n,k", [(33, 512), (1000, 3072), (4096, 12288), (12288, 4096)])
+@pytest.mark.parametrize("n,k", [(33, 512), (1000, 3072), (4096, 12288), (12288, 4096), (40, 768), (5120, 6400)])
 def test_linear_single_row_column_split(native_lib, oracle, enc, n, k):
     """One activation row (the decode shape) on the column-split tensor-core kernels: ragged last
-    tile, split-K shapes, f32 and bf16 activations, against the oracle's pairwise sums."""
+    tile, split-K shapes, rows that end half way through a 512-element stage (the shard widths of
+    a down projection split four ways), f32 and bf16 activations, against the oracle's pairwise sums."""
     from dyninfer_b200 import ops
     dw, ow = make_pair(oracle, enc, n, k, seed=n ^ k)
     x = np.random.default_rng(k).normal(size=(1, k)).astype(np.float32)

@@ -285,7 +285,7 @@ def tp_section(rank, world, local_rank, no_check=False):
     from dyninfer_b200 import replicas, tp_decode
     out = {"model": f"qwen3-32b-shape q4_0, q6_k embeddings and head, {TP_LAYERS} of {TP_FULL_LAYERS} layers written "
                     "(each carries layer 0's bytes)", "n_gpus": world, "prompt": 4096, "steps": 256,
-           "scaling": "strong", "timing": "host clock around synchronised calls, maximum over ranks"}
+           "scaling": "strong", "timing": "CUDA events on each rank's session stream, maximum over ranks"}
     runs = {}
     for batch in (1, 32):
         r = tp_decode.run(TP_MODEL, TP_LAYERS, prompt=4096, steps=256, warmup=3, batch=batch, chunk=512,
@@ -295,7 +295,9 @@ def tp_section(rank, world, local_rank, no_check=False):
                                                   "weight_bytes_per_step_per_rank", "weight_gbs_per_gpu",
                                                   "weight_gbs_all_ranks", "exchange")}
     # short run for the parity check: prompt of 8 ids, the logits of its last row and of one step
-    dump = os.path.join(os.path.dirname(checkpoint_path()), f"tp_logits_{os.getpid()}.npz") if rank == 0 else ""
+    # every rank passes the same (non-empty) name: the extra calls that produce the logits are
+    # collective, only rank 0 writes the file
+    dump = os.path.join(os.path.dirname(checkpoint_path()), f"tp_logits_w{world}.npz")
     tp_decode.run(TP_MODEL, TP_LAYERS, prompt=8, steps=2, warmup=1, batch=1, chunk=512, kv_dtype="bf16",
                   exchange="peer", dump_logits=dump)
     replicas.barrier()
@@ -434,13 +436,17 @@ def main():
                     "d2h_bytes_per_step": 8},
             "gpu_launches": int(gpu_launches),
             "clocks": clocks.summary(),
-            # dominant kernel: the persistent decode kernel, one launch per token (all of the
-            # timed region). Algorithmic bytes per launch = the weight bytes one token reads.
-            "roofline": {"bound": "hbm", "kernel": "decode_mega_kernel (one launch per token)",
+            # dominant kernel: the persistent decode kernel, the only kernel of the timed region; one
+            # launch decodes K / gpu_launches tokens. Algorithmic bytes per launch = the weight bytes
+            # one token reads x the tokens of a launch; traffic likewise from a one-token capture.
+            "roofline": {"bound": "hbm", "kernel": "decode_mega_kernel",
+                         "tokens_per_launch": K / max(1, gpu_launches),
                          "achieved": weight_bytes / (ms / K * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
                          "frac": weight_bytes / (ms / K * 1e-3) / 1e9 / hbm_peak, "peak_source": peak_kind,
-                         "bytes_per_launch": weight_bytes, "ms_per_launch": ms / K,
-                         "traffic": MEGA_DRAM_TRAFFIC, "traffic_source": "recorded ncu capture of this kernel"},
+                         "bytes_per_launch": weight_bytes * K / max(1, gpu_launches),
+                         "ms_per_launch": ms / max(1, gpu_launches),
+                         "traffic": MEGA_DRAM_TRAFFIC * K / max(1, gpu_launches),
+                         "traffic_source": "ncu capture of a one-token launch of this kernel, times the tokens of a launch"},
             # the largest single product of the step as its own launch (fused dequant-GEMV, M=1)
             "roofline_lm_head_gemv": {"bound": "hbm", "kernel": f"gemv_cs_q6k_kernel ({lm_enc}) 151936x1024, M=1",
                                       "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",

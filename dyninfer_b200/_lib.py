@@ -95,6 +95,7 @@ PROTOTYPES = {
     "dyninfer_cuda_session_launch_count": (C.c_uint64, [_P]),
     "dyninfer_cuda_session_uses_persistent_kernel": (C.c_int, [_P]),
     "dyninfer_cuda_session_decode_trace": (C.c_int, [_P, C.POINTER(C.c_uint64), C.c_size_t, C.POINTER(C.c_size_t)]),
+    "dyninfer_cuda_session_timer": (C.c_int, [_P, C.c_int, C.POINTER(C.c_float)]),
     "dyninfer_cuda_session_decode_phase_profile": (C.c_int, [_P, C.POINTER(C.c_double), C.c_size_t]),
 }
 

@@ -1,4 +1,4 @@
-// Persistent single-token decode kernel: one launch per generated token.
+// Persistent decode kernel: one launch decodes one or several consecutive tokens of one sequence.
 //
 // One CTA per SM, launched cooperatively so that all CTAs are co-resident. Each CTA owns a fixed,
 // balanced slice of the rows of every weight matrix, cut into tiles of 16 rows (x K-slices). A
@@ -6,7 +6,7 @@
 // row segment (cp.async.bulk + mbarrier transaction counts) -- from HBM into a shared-memory
 // ring, running as far ahead of the math as the ring allows: weight traffic never waits for the
 // activation dependency chain. Rows land PITCH bytes apart with PITCH/4 = 4 (mod 8), so the
-// tensor-core fragment loads are bank-conflict free. Sixteen consumer warps split each tile's K
+// tensor-core fragment loads are bank-conflict free. Eight consumer warps split each tile's K
 // range and run the tile steps of gemv_core.cuh against the activation vector staged in shared
 // memory in fragment order.
 //
@@ -19,12 +19,18 @@
 //     second load after a flag. Every vector has its own buffer; a buffer is rewritten a full
 //     layer later, by which time every reader has passed (each CTA needs all of a phase's outputs
 //     before it can produce the next phase's).
-//   * A phase's tiles keep their sums in registers ("round": at most MEGA_TA tiles); the sixteen
+//   * A phase's tiles keep their sums in registers ("round": at most MEGA_TA tiles); the eight
 //     K-slice partials of a round meet in shared memory once, behind one block barrier, and the
 //     first warps finish them (scale, residual / SwiGLU / logits) and store the pairs.
-//   * Nothing but the activation vector is fetched on the critical path: norm weights and the
-//     cached keys and values of earlier positions are requested before the poll begins; the
-//     residual rows a CTA owns stay in its shared memory for the whole token.
+//   * Nothing but the activation vector is fetched on the critical path: norm weights are
+//     requested before the poll begins, the cached keys and values of earlier positions are
+//     copied into shared memory a layer ahead, and the residual rows a CTA owns stay in its
+//     shared memory for the whole token.
+//   * Code that runs once per layer is kept small: on this GPU a warp executes straight-line
+//     code at about one instruction per cycle while it fits 8 KB, one per 2.7 cycles up to 32 KB
+//     and one per 6 cycles beyond (measured), whatever the arithmetic. The 4 * layers + 1 products
+//     therefore share ONE copy of the product code (a loop), attention uses rolled loops, and
+//     the timers exist only in a twin kernel.
 //
 //   per layer: norm+QKV | qk-norm+RoPE+KV-write+attention | o_proj+res | norm+gate/up+SwiGLU |
 //   down+res ; then: norm+lm_head+argmax partials | argmax
@@ -48,28 +54,13 @@ namespace {
 #endif
 constexpr int MK_CW = MK_OPT_CW;   // consumer warps (a power of two)
 constexpr int MK_CT = MK_CW * 32;  // consumer threads
-// Sixteen warps (four per scheduler partition) leave 128 registers per thread; a seventeenth warp
-// for the weight copies would cut that to 96 and the kernel would spill. So the warps take turns
-// as producer: after chunk c, warp c % 16 issues the copies of the chunk nslot - 1 ahead, into
-// the slot chunk c - 1 has just left (a few dozen instructions: byte counts and alignments come
-// precomputed from the host). MK_PRODUCER_WARP = true restores the separate warp.
-#ifndef MK_OPT_PRODUCER_WARP
-#define MK_OPT_PRODUCER_WARP 1
-#endif
-#ifndef MK_OPT_POLL2
-#define MK_OPT_POLL2 0
-#endif
+// Eight consumer warps and one producer warp: nine warps leave 168 registers per thread (sixteen
+// consumers plus a producer would leave 96 and spill; measured alternatives -- 4 or 16 consumers,
+// consumers taking turns as producer -- were slower). MK_OPT_LOCAL = 0 forces whole-block staging.
 #ifndef MK_OPT_LOCAL
 #define MK_OPT_LOCAL 1
 #endif
-#ifndef MK_OPT_KSLICE2
-#define MK_OPT_KSLICE2 0
-#endif
-#ifndef MK_OPT_PAIRS
-#define MK_OPT_PAIRS 0
-#endif
-constexpr bool MK_PRODUCER_WARP = MK_OPT_PRODUCER_WARP != 0;
-constexpr int MK_THREADS = MK_CT + (MK_PRODUCER_WARP ? 32 : 0);
+constexpr int MK_THREADS = MK_CT + 32;
 constexpr int MK_SLOT = 18432;          // bytes per ring slot (one 16-row tile x K-slice)
 constexpr int MK_PART = MEGA_TA * MK_CW * 16;  // floats of one partial-sum buffer
 // per-CTA scratch, in floats
@@ -132,50 +123,6 @@ __device__ __forceinline__ void ll_poll(const float* buf, const int64_t (&idx)[N
   for (int i = 0; i < NL; i++) {
     v[2 * i] = __uint_as_float(r[i].x);
     v[2 * i + 1] = __uint_as_float(r[i].z);
-  }
-}
-
-// The same with two samples of every line in flight, half a round trip apart: a poll that waits
-// for one load at a time looks at the data once per L2 round trip (0.5 - 1 us across the two dies),
-// so a pair arriving just after a sample waits most of a round trip to be seen; a second, staggered
-// sample halves that wait.
-template <int NL>
-__device__ __forceinline__ void ll_poll2(const float* buf, const int64_t (&idx)[NL], unsigned ep, float (&v)[2 * NL],
-                                         volatile int* abort) {
-  uint4 ra[NL], rb[NL];
-#pragma unroll
-  for (int i = 0; i < NL; i++) ra[i] = ll_load(buf, idx[i]);
-  __nanosleep(300);
-#pragma unroll
-  for (int i = 0; i < NL; i++) rb[i] = ll_load(buf, idx[i]);
-  long long it = 0;
-  bool from_b = false;
-  for (;;) {
-    bool ok = true;
-#pragma unroll
-    for (int i = 0; i < NL; i++) ok = ok && ra[i].y == ep && ra[i].w == ep;
-    if (ok) break;
-#pragma unroll
-    for (int i = 0; i < NL; i++) ra[i] = ll_load(buf, idx[i]);
-    ok = true;
-#pragma unroll
-    for (int i = 0; i < NL; i++) ok = ok && rb[i].y == ep && rb[i].w == ep;
-    if (ok) {
-      from_b = true;
-      break;
-    }
-#pragma unroll
-    for (int i = 0; i < NL; i++) rb[i] = ll_load(buf, idx[i]);
-    if (*abort) break;
-    if (++it >= MK_LL_SPINS) {
-      *abort = 8;
-      break;
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < NL; i++) {
-    v[2 * i] = __uint_as_float(from_b ? rb[i].x : ra[i].x);
-    v[2 * i + 1] = __uint_as_float(from_b ? rb[i].z : ra[i].z);
   }
 }
 
@@ -266,7 +213,8 @@ __device__ __forceinline__ void produce_chunk(const MegaChunk* c, const Smem& sm
   if (i >= (int)c->n) return;
   if (lane < 16) {
     const uint32_t off = ((uint32_t)c->al + (uint32_t)i * c->al_step) & 15u;
-    bulk_g2s(base + i * c->pitch, c->src + (size_t)i * c->rb - off, (off + c->seg + 15u) & ~15u, sm.full + slot);
+    const uint8_t* row = c->src + (size_t)i * c->rb + (i >= 8 ? (int64_t)c->jump16 * 16 : 0);
+    bulk_g2s(base + i * c->pitch, row - off, (off + c->seg + 15u) & ~15u, sm.full + slot);
   } else if (c->aseg) {
     // scales and biases share their alignment (both tensors start 256-byte aligned in the arena)
     const uint32_t off = ((uint32_t)c->aal + (uint32_t)i * c->aal_step) & 15u;
@@ -373,7 +321,7 @@ __device__ __forceinline__ void item_bases(int layout, int kb, int t, int* baseA
 __device__ __forceinline__ void item_fetch(const StageSrc& src, int baseA, int baseB, const Smem& sm, float (&v)[8]) {
   if (src.kind == SRC_LL) {
     const int64_t idx[4] = {baseA, baseA + 2, baseB, baseB + 2};
-    if (MK_OPT_POLL2) ll_poll2<4>(src.ll, idx, src.ep, v, sm.abort); else ll_poll<4>(src.ll, idx, src.ep, v, sm.abort);
+    ll_poll<4>(src.ll, idx, src.ep, v, sm.abort);
   } else if (src.kind == SRC_PARTIALS) {
     // merge the split-KV partial outputs of this item's head in split order (online softmax merge)
     const int head = baseA / src.d, ia = baseA - head * src.d, ib = baseB - head * src.d;
@@ -772,7 +720,7 @@ __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, cons
     float x[4] = {0.f, 0.f, 0.f, 0.f};  // x1a x1b x2a x2b
     if (act) {
       const int64_t idx[2] = {base + i0, base + i0 + half};
-      if (MK_OPT_POLL2) ll_poll2<2>(a.ll_qkv, idx, ep, x, sm.abort); else ll_poll<2>(a.ll_qkv, idx, ep, x, sm.abort);
+      ll_poll<2>(a.ll_qkv, idx, ep, x, sm.abort);
     }
     if (warp < 2) {
       if (a.has_norm) {
@@ -951,25 +899,11 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
 struct Walk {
   uint32_t ci, ri, ti;    // next chunk, round, tile of this CTA's program
   uint32_t slot, parity;  // ring position of chunk ci
-  // the next chunk whose copies are to be issued: sequence number over the launch, index in the
-  // program, token of the launch, ring slot and lap
-  uint32_t fill_seq, fill_idx, fill_step, fill_slot, fill_lap;
   unsigned nround;        // rounds so far (selects the partial-sum buffer)
   unsigned nlocal;        // per-warp stagings so far (selects the sum-of-squares buffer)
   float bv;               // running argmax over the rows this thread finishes
   long long bi;
 };
-
-// Issues the copies of one more chunk (all warps keep the same counters; the warp whose turn it is
-// acts). The target slot was left by the chunk before the one just finished; its release by all
-// sixteen warps is waited for, bounded.
-__device__ __forceinline__ void refill(const MegaArgs& a, const Smem& sm, Walk& w, int lane, int warp) {
-  if (MK_PRODUCER_WARP || w.fill_step >= (uint32_t)a.steps) return;
-  if (warp == (int)(w.fill_seq & (MK_CW - 1))) produce_chunk(sm.chunks + w.fill_idx, sm, (int)w.fill_slot, w.fill_lap, lane);
-  w.fill_seq++;
-  if (++w.fill_idx == sm.nchunks) w.fill_idx = 0, w.fill_step++;
-  if (++w.fill_slot == (uint32_t)sm.nslot) w.fill_slot = 0, w.fill_lap++;
-}
 
 template <int ENC, class Prof>
 __device__ __forceinline__ void run_phase_t(const MegaArgs& a, const Smem& sm, Walk& w, int nr, unsigned ep,
@@ -1020,26 +954,13 @@ __device__ __forceinline__ void run_phase_t(const MegaArgs& a, const Smem& sm, W
       __syncwarp();
       if (lane == 0) mbar_arrive(sm.empty + slot);
       if (++w.slot == (uint32_t)sm.nslot) w.slot = 0, w.parity ^= 1u;
-      refill(a, sm, w, lane, warp);
     };
-    for (int k = 0; k < (int)R.nchunks;) {
+    for (int k = 0; k < (int)R.nchunks; k++, w.ci++) {
       const uint4 hot = *reinterpret_cast<const uint4*>(sm.chunks + w.ci);
       const int which = (int)((hot.y >> 16) & 0xffu);
       const int slot = (int)w.slot;
       const unsigned long long tw = prof.tic();
-      bool ok = mbar_wait_bounded(sm.full + slot, w.parity, MK_MBAR_SPINS, sm.abort);
-      // Two tiles at a time where the next chunk belongs to another tile: their tile steps are
-      // independent, and issued side by side they hide each other's latencies.
-      uint4 hot2 = hot;
-      bool pair = false;
-      if (k + 1 < (int)R.nchunks) {
-        hot2 = *reinterpret_cast<const uint4*>(sm.chunks + w.ci + 1);
-        pair = MK_OPT_PAIRS && (int)((hot2.y >> 16) & 0xffu) != which && ((hot2.y >> 8) & 0xffu) == ((hot.y >> 8) & 0xffu);
-      }
-      int slot2 = slot + 1;
-      unsigned parity2 = w.parity;
-      if (slot2 == sm.nslot) slot2 = 0, parity2 ^= 1u;
-      if (pair) ok = mbar_wait_bounded(sm.full + slot2, parity2, MK_MBAR_SPINS, sm.abort) && ok;
+      const bool ok = mbar_wait_bounded(sm.full + slot, w.parity, MK_MBAR_SPINS, sm.abort);
       if (!ok && !*sm.abort) *sm.abort = 3;
       prof.toc(10, tw);
       const unsigned long long tr = prof.tic();
@@ -1048,46 +969,17 @@ __device__ __forceinline__ void run_phase_t(const MegaArgs& a, const Smem& sm, W
         t.clear();
         cur = which;
       }
-      if (!pair) {
-        if (ok) {
-          const Geo q = geometry(hot, slot);
-          // two K-slices of the tile side by side (a second accumulator), for the same reason
-          TileAcc<true> t2;
-          t2.clear();
-          int u = warp;
-          for (; MK_OPT_KSLICE2 && u + MK_CW < q.nu; u += 2 * MK_CW) {
-            run_unit<ENC>(q.enc, q.aux, q.gs, q.p0, q.p1, q.a0, q.a1, q.apitch16, u, q.kb0, sm, lane, t);
-            run_unit<ENC>(q.enc, q.aux, q.gs, q.p0, q.p1, q.a0, q.a1, q.apitch16, u + MK_CW, q.kb0, sm, lane, t2);
-          }
-          for (; u < q.nu; u += MK_CW) run_unit<ENC>(q.enc, q.aux, q.gs, q.p0, q.p1, q.a0, q.a1, q.apitch16, u, q.kb0, sm, lane, t);
-          t.v[0] += t2.v[0];
-          t.v[1] += t2.v[1];
-        }
-        prof.toc(11, tr);
-        release(slot);
-        k += 1, w.ci += 1;
-      } else {
-        TileAcc<true> t2;
-        t2.clear();
-        if (ok) {
-          const Geo q = geometry(hot, slot), q2 = geometry(hot2, slot2);
-          for (int u = warp; u < q.nu; u += MK_CW) {
-            run_unit<ENC>(q.enc, q.aux, q.gs, q.p0, q.p1, q.a0, q.a1, q.apitch16, u, q.kb0, sm, lane, t);
-            run_unit<ENC>(q2.enc, q2.aux, q2.gs, q2.p0, q2.p1, q2.a0, q2.a1, q2.apitch16, u, q2.kb0, sm, lane, t2);
-          }
-        }
-        prof.toc(11, tr);
-        release(slot);
-        release(slot2);
-        flush();  // the first tile of the pair is complete unless more of its slices follow; the second goes on
-        t = t2;
-        cur = (int)((hot2.y >> 16) & 0xffu);
-        k += 2, w.ci += 2;
+      if (ok) {
+        const Geo q = geometry(hot, slot);
+        for (int u = warp; u < q.nu; u += MK_CW)
+          run_unit<ENC>(q.enc, q.aux, q.gs, q.p0, q.p1, q.a0, q.a1, q.apitch16, u, q.kb0, sm, lane, t);
       }
+      prof.toc(11, tr);
+      release(slot);
     }
     flush();
     prof.stamp(sid + 1);
-    // the sixteen K-slice partials of every tile of the round meet here, once
+    // the K-slice partials of every tile of the round meet here, once
     const unsigned long long tc = prof.tic();
     consumer_sync();
     const int nt = R.ntiles;
@@ -1120,6 +1012,12 @@ __device__ __forceinline__ void run_phase_t(const MegaArgs& a, const Smem& sm, W
           float s1 = 0.f;
 #pragma unroll
           for (int wv = 0; wv < MK_CW; wv++) s1 += p2[wv * 16];
+          s1 *= out_scale;
+          ll_store(a.ll_act, orow, (s0 / (1.0f + expf(-s0))) * s1, ep);
+        } else if (T.ep == MEGA_EP_SWIGLU_IL) {
+          float s1 = 0.f;  // the same row of `up`: tile row + 8 of the same accumulator
+#pragma unroll
+          for (int wv = 0; wv < MK_CW; wv++) s1 += p1[wv * 16 + 8];
           s1 *= out_scale;
           ll_store(a.ll_act, orow, (s0 / (1.0f + expf(-s0))) * s1, ep);
         } else {
@@ -1216,7 +1114,7 @@ __device__ __forceinline__ void decode_mega_body(const MegaArgs& a) {
   sm.hot = reinterpret_cast<const MegaLayerHot*>(prog_area + a.lay.off_layers);
 
   sm.nchunks = hdr->nchunks;
-  if (MK_PRODUCER_WARP && warp == MK_CW) {
+  if (warp == MK_CW) {
     // ------------------------------ producer: stream this CTA's weight tiles --------------
     const int total = *sm.abort ? 0 : (int)hdr->nchunks;
     int slot = 0;
@@ -1237,9 +1135,6 @@ __device__ __forceinline__ void decode_mega_body(const MegaArgs& a) {
   Walk wk;
   wk.ci = wk.ri = wk.ti = 0, wk.slot = 0, wk.parity = 0, wk.nround = 0, wk.nlocal = 0;
   wk.bv = -INFINITY, wk.bi = 0x7fffffffffffffffLL;
-  wk.fill_seq = wk.fill_idx = wk.fill_slot = wk.fill_lap = 0;
-  wk.fill_step = (sm.nchunks == 0 || *sm.abort) ? (uint32_t)a.steps : 0u;
-  for (int i = 0; i < sm.nslot - 1; i++) refill(a, sm, wk, lane, warp);  // the ring's first fill: warp i issues chunk i
   ProfT<INSTR> prof;
   // One launch decodes a.steps tokens: every CTA learns each token from the argmax hand-off and goes
   // on with the next position; the weight ring and its barriers simply keep running.
@@ -1464,7 +1359,7 @@ int seg_bytes(const HostPlan& p, int nu) { return p.unit_q6 ? (nu / 4) * 210 : n
 // fewest K-slices whose rows fit one ring slot (slices are multiples of 16 units so the 16
 // consumer warps share them evenly; Q6_K slices are whole groups of 4 superblocks, which keeps
 // rows 8-byte aligned).
-void add_tile_chunks(const WRef& w, int64_t r, int n, int acc, std::vector<MegaChunk>* v) {
+void add_tile_chunks(const WRef& w, int64_t r, int n, int acc, std::vector<MegaChunk>* v, int64_t jump = 0) {
   const HostPlan p = host_plan(w);
   const int ael = w.aux == E_F32 ? 4 : 2;
   // largest slice (multiple of 16 units) whose rows fit one slot; only valid rows are copied
@@ -1491,11 +1386,12 @@ void add_tile_chunks(const WRef& w, int64_t r, int n, int acc, std::vector<MegaC
     c.acc = (uint8_t)acc;
     c.al = (uint8_t)(reinterpret_cast<uintptr_t>(c.src) & 15);
     c.al_step = (uint8_t)(c.rb & 15u);
+    c.jump16 = (int32_t)(jump / 16);
     // Q6_K rows over the full K are copied as one run: their natural pitch (840 bytes for K = 1024)
     // spreads the eight row pairs over the banks almost as well as a padded pitch does, and one copy
     // replaces sixteen
     for (int i = 0; i < n; i++) c.tx += ((((uint32_t)c.al + (uint32_t)i * c.al_step) & 15u) + c.seg + 15u) & ~15u;
-    if (w.enc == E_Q6_K && nsl == 1 && (size_t)n * c.rb + 16 <= (size_t)MK_SLOT && c.rb % 4 == 0 && ((c.rb / 4) & 1) == 0) {
+    if (w.enc == E_Q6_K && jump == 0 && nsl == 1 && (size_t)n * c.rb + 16 <= (size_t)MK_SLOT && c.rb % 4 == 0 && ((c.rb / 4) & 1) == 0) {
       c.pitch = (uint16_t)c.rb;
       c.al_step = 0;
       c.contig = (uint32_t)((c.al + (size_t)n * c.rb + 15) / 16 * 16);
@@ -1537,6 +1433,24 @@ struct CtaProgram {
       open = true;
     }
   }
+  // gate and up rows [lo, hi), eight of each per tile (rows 0..7 gate, 8..15 up): three tiles where
+  // separate gate and up tiles would take four for 24 rows. (hi - lo) % 8 == 0.
+  void add_rows_interleaved(const WRef& gate, const WRef& up, int64_t lo, int64_t hi) {
+    const int64_t rb = (int64_t)gate.row_bytes();
+    const int64_t jump = (up.data - gate.data) - 8 * rb;
+    for (int64_t r = lo; r < hi; r += 8) {
+      need(1);
+      MegaTile t{};
+      t.out_row = (int32_t)r, t.n = 8, t.ep = (uint8_t)MEGA_EP_SWIGLU_IL, t.acc = (uint8_t)accs, t.acc2 = 0;
+      const size_t before = chunks.size();
+      add_tile_chunks(gate, r, 16, accs, &chunks, jump);
+      accs += 1;
+      rounds.back().naccs = (uint8_t)accs;
+      tiles.push_back(t);
+      rounds.back().nchunks = (uint16_t)(rounds.back().nchunks + (chunks.size() - before));
+      rounds.back().ntiles++;
+    }
+  }
   // rows [lo, hi) of w (and of w2 for SwiGLU pairs), output rows out_off + row
   void add_rows(const WRef& w, const WRef* w2, int64_t lo, int64_t hi, int64_t out_off, int ep) {
     for (int64_t r = lo; r < hi; r += 16) {
@@ -1563,6 +1477,13 @@ struct CtaProgram {
 // takes more than twice as long (2.46 us against 1.10 us for a 1024-element vector between 148
 // CTAs), so no sector has two writers. Needs n % 4 == 0.
 static int64_t split4(int64_t n, int cta, int grid) { return 4 * ((n / 4) * cta / grid); }
+static int64_t split8(int64_t n, int cta, int grid) { return 8 * ((n / 8) * cta / grid); }
+// gate and up can share tiles when they are the same kind of matrix and 16-byte congruent
+static bool can_interleave(const WRef& g, const WRef& u, int I) {
+  return (g.enc == E_Q4_0 || g.enc == E_Q4_1 || g.enc == E_Q8_0) && u.enc == g.enc && u.cols == g.cols && I % 8 == 0 &&
+         ((u.data - g.data) - 8 * (int64_t)g.row_bytes()) % 16 == 0 &&
+         std::llabs(((u.data - g.data) - 8 * (int64_t)g.row_bytes()) / 16) < (1LL << 31);
+}
 
 int mega_build_program(const MegaBuildLayer* layers, const MegaLayer* full, int nlayers, const WRef& lm_head, int nh,
                        int nkv, int d, int H, int I, int V, int grid, std::vector<uint8_t>* blob, MegaProgLayout* lay) {
@@ -1591,7 +1512,10 @@ int mega_build_program(const MegaBuildLayer* layers, const MegaLayer* full, int 
       pc.begin_phase();
       pc.add_rows(L.o, nullptr, h0, h1, 0, MEGA_EP_RESID_O);
       pc.begin_phase();
-      pc.add_rows(L.gate, &L.up, split4(I, cta, grid), split4(I, cta + 1, grid), 0, MEGA_EP_SWIGLU);
+      if (can_interleave(L.gate, L.up, I))
+        pc.add_rows_interleaved(L.gate, L.up, split8(I, cta, grid), split8(I, cta + 1, grid));
+      else
+        pc.add_rows(L.gate, &L.up, split4(I, cta, grid), split4(I, cta + 1, grid), 0, MEGA_EP_SWIGLU);
       pc.begin_phase();
       pc.add_rows(L.down, nullptr, h0, h1, 0, MEGA_EP_RESID_DOWN);
     }

@@ -36,12 +36,20 @@ struct MegaChunk {
   uint16_t seg, aseg;  // bytes per row in this chunk: data, MLX aux
   uint32_t contig;     // != 0: the rows are one run in memory, copied by a single bulk copy of this many bytes
   uint32_t tx;         // bytes all per-row copies of the chunk bring (the slot barrier's transaction count)
-  uint32_t pad_;
+  int32_t jump16;      // rows 8..15 come from a second matrix: their source is 16 * jump16 bytes further on
 };
 static_assert(sizeof(MegaChunk) == 64, "MegaChunk must stay 64 bytes");
 
 // What happens to a finished tile of output rows.
-enum { MEGA_EP_QKV = 0, MEGA_EP_RESID_O = 1, MEGA_EP_SWIGLU = 2, MEGA_EP_RESID_DOWN = 3, MEGA_EP_LOGITS = 4 };
+// SWIGLU_IL: tile rows 0..7 are gate rows, rows 8..15 the same rows of up (one accumulator).
+enum {
+  MEGA_EP_QKV = 0,
+  MEGA_EP_RESID_O = 1,
+  MEGA_EP_SWIGLU = 2,
+  MEGA_EP_RESID_DOWN = 3,
+  MEGA_EP_LOGITS = 4,
+  MEGA_EP_SWIGLU_IL = 5
+};
 struct MegaTile {
   int32_t out_row;  // index of tile row 0 in the phase's output vector
   uint8_t n;        // valid rows

@@ -18,16 +18,24 @@
 // group.
 //
 // Data movement: every warp owns a ring of CS_NST stages in shared memory; a stage is 16 rows x
-// 288 bytes (two units, K-span 512), one 1-D bulk copy (cp.async.bulk) per row completing on the
-// stage's mbarrier, rows 304 bytes apart so the 32 lanes of a fragment load hit 32 banks. A stage
-// is read into registers in one go and its slot refilled before the math starts. A warp walks a
-// contiguous range of (tile, K-slice) items and keeps the ring running across item boundaries.
+// 288 bytes (two units, K-span 512), brought by FOUR 2-D tensor copies (cp.async.bulk.tensor over a
+// map of the matrix as [rows][row bytes / 4] words) of 8 rows x one unit each, completing on the
+// stage's mbarrier. (One 1-D bulk copy per row, sixteen per stage, is what this kernel used before:
+// with 288-byte copies the copy engine's request rate, not HBM, set the pace -- the copies alone
+// ran at 69 % of the measured HBM peak.) A box lands densely, 144 bytes per row = 36 words, so the
+// eight rows of a fragment load start 4 banks apart and the four lane quarters 9 words apart: 32
+// lanes, 32 banks. Box bytes past the end of a row or of the matrix arrive as zeros, which is how a
+// row that ends half way through a stage (K % 512 == 256) and the ragged last tile are handled. A
+// stage is read into registers in one go and its slot refilled before the math starts. A warp
+// walks a contiguous range of (tile, K-slice) items and keeps the ring running across item
+// boundaries.
 // All waits are bounded; a wait that runs out sets the error word in the workspace and the warp
 // leaves (its rows are then not written).
 #include <algorithm>
 
 #include "gemv_core.cuh"
 #include "ring.cuh"
+#include "tensor_map.cuh"
 
 namespace dyn {
 
@@ -39,19 +47,21 @@ constexpr int CS_PAIRS = 1;          // unit pairs (512 elements) per stage
 constexpr int CS_KSTAGE = 512 * CS_PAIRS; // K elements per stage
 // Per encoding: words a lane reads per unit and row (two blocks incl. their scales), bytes of one
 // row in a stage, and the row pitch in shared memory (bytes of a stage row + 16).
-//   Q4_0: 18-byte blocks, 9 words, 288-byte rows, pitch 304 (76 words = 12 mod 32: conflict-free)
-//   Q4_1: 20-byte blocks (f16 d, f16 m, 16 quant bytes), 10 words, 320-byte rows, pitch 336
+//   Q4_0: 18-byte blocks, 9 words per lane, 144-byte unit rows (36 words: conflict-free)
+//   Q4_1: 20-byte blocks (f16 d, f16 m, 16 quant bytes), 10 words, 160-byte unit rows (two-way conflicts)
+// A stage holds, for each of its two units, a box of rows 0..7 and a box of rows 8..15.
 template <int ENC>
 struct CsGeo {
   static constexpr int LW = ENC == E_Q4_0 ? 9 : 10;          // words per lane, unit and row
   static constexpr int UW = 4 * LW;                          // words per unit and row
   static constexpr int ROWB = UW * 4 * 2 * CS_PAIRS;         // bytes of one row in a stage
-  static constexpr int PITCH = ROWB + 16;
-  static constexpr int STAGE = 16 * PITCH;
+  static constexpr int BOX = 8 * UW * 4;                     // bytes of one box (8 rows of one unit): 1152 / 1280
+  static constexpr int STAGE = 4 * CS_PAIRS * BOX;           // a multiple of 128
   static constexpr int RING_BYTES = CS_WARPS * CS_NST * STAGE + CS_WARPS * CS_NST * 8;  // rings + barriers
 };
 constexpr long long CS_SPINS = 1LL << 22;
 constexpr int CS_MAX_SMEM = 226 * 1024;  // dynamic shared memory the kernel may ask for (static: 128 bytes)
+
 
 // ---- activation staging (every CTA, into its own shared memory) ---------------------------------
 // xq: per (unit U of 256 elements, parity e, word i, quarter t, hi/lo) one uint4 holding the B
@@ -107,13 +117,11 @@ __device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf
 
 // ---- tiles -------------------------------------------------------------------------------------
 struct CsArgs {
-  const uint8_t* data;   // Q4_0 rows
   int64_t N;
-  int64_t rb;            // bytes per row
   int K;
   int S;                 // K-slices per tile
   int nst;               // stages per item (ceil(K / 512) / S)
-  int tail;              // 1 when the last stage of a row holds one unit (K % 512 == 256)
+  int tail;              // 1 when the last stage of a row holds one unit (K % 512 == 256): the rest reads as zeros
   int ntiles;
   const void* x;         // the activation row
   int x_bf16;
@@ -125,7 +133,8 @@ struct CsArgs {
 };
 
 template <int ENC>
-__global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsArgs a) {
+__global__ void __launch_bounds__(CS_WARPS * 32, 1)
+gemv_cs_q4_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap) {
   using G = CsGeo<ENC>;
   constexpr int LW = G::LW;
   extern __shared__ __align__(128) uint8_t cs_smem[];
@@ -153,25 +162,22 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
   const int nst = a.nst;
   const int total = item_lo < item_hi ? (int)(item_hi - item_lo) * nst : 0;
 
-  // copy role: lanes 0..15 fetch row `lane` of the tile. The copy cursor (tile, slice, stage,
-  // slot) runs CS_NST stages ahead of the math and advances without divisions.
+  // copy role: lanes 0..3 each fetch one box (unit lane >> 1, rows 8 * (lane & 1) ..) of the stage.
+  // The copy cursor (tile, slice, stage, slot) runs CS_NST stages ahead of the math and advances
+  // without divisions.
   const int S = a.S;
   const int tile_lo = (int)(item_lo / S), sl_lo = (int)(item_lo - (int64_t)tile_lo * S);
   int c_left = total, c_tile = tile_lo, c_sl = sl_lo, c_st = 0, c_slot = 0;
-  const int64_t last_row = a.N - 1;
   auto issue = [&]() {
     if (c_left <= 0) return;
     c_left--;
-    // the last stage of a row with a tail holds one unit; the second unit's slot keeps older bytes,
-    // which meet zero activations and whose scales are not applied
-    const unsigned rowb = (a.tail && c_sl == S - 1 && c_st == nst - 1) ? G::ROWB / 2 : G::ROWB;
-    if (lane == 0) mbar_expect_tx(bars + c_slot, 16 * rowb);
+    if (lane == 0) mbar_expect_tx(bars + c_slot, G::STAGE);  // boxes count in full, zeros included
     __syncwarp();
-    if (lane < 16) {
-      int64_t row = (int64_t)c_tile * 16 + lane;
-      if (row > last_row) row = last_row;
-      const uint8_t* src = a.data + row * a.rb + (int64_t)(c_sl * nst + c_st) * G::ROWB;
-      bulk_g2s(ring + c_slot * G::STAGE + lane * G::PITCH, src, rowb, bars + c_slot);
+    if (lane < 4) {
+      const int u = lane >> 1, hf = lane & 1;
+      const int x = ((c_sl * nst + c_st) * 2 + u) * G::UW;  // words into the row: a multiple of 4
+      const int y = c_tile * 16 + hf * 8;
+      tma_box_g2s(ring + c_slot * G::STAGE + lane * G::BOX, &wmap, x, y, bars + c_slot);
     }
     if (++c_slot == CS_NST) c_slot = 0;
     if (++c_st == nst) {
@@ -205,10 +211,10 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
         }
         return;  // warp-uniform: every lane polls the same barrier
       }
-      const bool half_stage = a.tail && sl == S - 1 && st == nst - 1;  // warp-uniform
+      // box (unit u, rows 8 hf ..) sits at (2 u + hf) * BOX; row g of a box at g * UW words
       const uint8_t* base = ring + slot * G::STAGE;
-      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(base + g * G::PITCH) + LW * t;
-      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(base + (g + 8) * G::PITCH) + LW * t;
+      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(base) + g * G::UW + LW * t;
+      const uint32_t* r1 = r0 + G::BOX / 4;
 #pragma unroll
       for (int pr = 0; pr < CS_PAIRS; pr++) {
       const int U0 = ((sl * nst + st) * CS_PAIRS + pr) * 2;  // first 256-element unit of this pair
@@ -218,8 +224,8 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
       for (int u = 0; u < 2; u++)
 #pragma unroll
         for (int i = 0; i < LW; i++) {
-          w0[u][i] = r0[pr * 2 * G::UW + u * G::UW + i];
-          w1[u][i] = r1[pr * 2 * G::UW + u * G::UW + i];
+          w0[u][i] = r0[(pr * 2 + u) * (G::BOX / 2) + i];
+          w1[u][i] = r1[(pr * 2 + u) * (G::BOX / 2) + i];
         }
       if (pr == CS_PAIRS - 1) {
         __syncwarp();
@@ -266,7 +272,6 @@ __global__ void __launch_bounds__(CS_WARPS * 32, 1) gemv_cs_q4_kernel(const CsAr
 #pragma unroll
       for (int gi = 0; gi < 4; gi++) {
         const int u = gi >> 1;
-        if (u == 1 && half_stage) continue;  // no second unit: its scale bytes are not weights
         const float sx = sxp[u * 8 + (gi & 1)];
         if (ENC == E_Q4_1) {  // w = q * d + m: scale the tile sums, add the minimum times the plain sum
           const __half2 h0 = *reinterpret_cast<const __half2*>(&w0[u][5 * (gi & 1)]);
@@ -390,7 +395,11 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
   CsPlan p;
   cs_plan(w, &p);
   CsArgs a;
-  a.data = w.data, a.N = w.rows, a.rb = w.row_bytes(), a.K = (int)w.cols;
+  a.N = w.rows, a.K = (int)w.cols;
+  // the matrix as [rows][row bytes / 4] words; boxes of 8 rows x one unit
+  CUtensorMap wmap;
+  if (make_row_box_map(w.data, w.row_bytes(), w.rows, w.enc == E_Q4_0 ? CsGeo<E_Q4_0>::UW : CsGeo<E_Q4_1>::UW, 8, &wmap))
+    return 1;
   a.S = p.S, a.nst = p.nst, a.ntiles = p.ntiles, a.tail = (w.cols % CS_KSTAGE) ? 1 : 0;
   a.x = x, a.x_bf16 = x_type == E_BF16 ? 1 : 0;
   a.error = device_error_word();
@@ -403,9 +412,9 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
                           CS_MAX_SMEM))
     return 1;
   if (w.enc == E_Q4_0)
-    DYN_CUDA(launch_pdl(gemv_cs_q4_kernel<E_Q4_0>, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a));
+    DYN_CUDA(launch_pdl(gemv_cs_q4_kernel<E_Q4_0>, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a, wmap));
   else
-    DYN_CUDA(launch_pdl(gemv_cs_q4_kernel<E_Q4_1>, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a));
+    DYN_CUDA(launch_pdl(gemv_cs_q4_kernel<E_Q4_1>, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a, wmap));
   count_launch(1);
   if (p.S > 1) {
     DYN_CUDA(launch_pdl(cs_reduce_kernel, dim3((unsigned)((w.rows + 255) / 256)), dim3(256), 0, s,

@@ -8,12 +8,15 @@
 // biased to unsigned (q + 128, exact zero point) and widened to f16 subnormals with byte permutes;
 // one quant word = one mma step. Activations stay in natural order as two f16 arrays (hi, lo) in
 // shared memory; every block's sum times 128 undoes the bias. Per warp a ring of two stages of
-// 16 rows x 272 bytes (pitch 304: conflict-free), one cp.async.bulk per row; a stage is read into
+// 16 rows x 272 bytes, brought by two 2-D tensor copies of 8 rows each (dense rows of 68 words: the
+// eight rows of a fragment load start 4 banks apart, the lane quarters 17 words apart, so the 32
+// lanes hit 32 banks; rows past the end of the matrix arrive as zeros); a stage is read into
 // registers and its slot refilled before the math. All waits are bounded.
 #include <algorithm>
 
 #include "gemv_core.cuh"
 #include "ring.cuh"
+#include "tensor_map.cuh"
 
 namespace dyn {
 
@@ -22,16 +25,15 @@ namespace {
 constexpr int Q8_WARPS = 16;
 constexpr int Q8_NST = 2;
 constexpr int Q8_ROWB = 272;     // one unit of 8 blocks
-constexpr int Q8_PITCH = 304;    // 76 words = 12 (mod 32)
-constexpr int Q8_STAGE = 16 * Q8_PITCH;
+constexpr int Q8_BOX = 8 * Q8_ROWB;   // one box: rows 0..7 or 8..15 of the unit (2176 bytes = 17 x 128)
+constexpr int Q8_STAGE = 2 * Q8_BOX;
 constexpr int Q8_KSTAGE = 256;
 constexpr long long Q8_SPINS = 1LL << 22;
 constexpr int Q8_MAX_SMEM = 226 * 1024;
 constexpr int Q8_RING_BYTES = Q8_WARPS * Q8_NST * Q8_STAGE + Q8_WARPS * Q8_NST * 8;
 
 struct Q8Args {
-  const uint8_t* data;
-  int64_t N, rb;
+  int64_t N;
   int K, S, nst, ntiles;
   const void* x;
   int x_bf16;
@@ -82,7 +84,8 @@ __device__ __forceinline__ float q8_stage_x(const void* __restrict__ x, int x_bf
   return GV_2P24 * is;
 }
 
-__global__ void __launch_bounds__(Q8_WARPS * 32, 1) gemv_cs_q8_0_kernel(const Q8Args a) {
+__global__ void __launch_bounds__(Q8_WARPS * 32, 1)
+gemv_cs_q8_0_kernel(const Q8Args a, const __grid_constant__ CUtensorMap wmap) {
   extern __shared__ __align__(128) uint8_t q8_smem[];
   __shared__ int s_abort;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -110,18 +113,14 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 1) gemv_cs_q8_0_kernel(const Q8
   const int S = a.S;
   const int tile_lo = (int)(item_lo / S), sl_lo = (int)(item_lo - (int64_t)tile_lo * S);
   int c_left = total, c_tile = tile_lo, c_sl = sl_lo, c_st = 0, c_slot = 0;
-  const int64_t last_row = a.N - 1;
   auto issue = [&]() {
     if (c_left <= 0) return;
     c_left--;
-    if (lane == 0) mbar_expect_tx(bars + c_slot, 16 * Q8_ROWB);
+    if (lane == 0) mbar_expect_tx(bars + c_slot, Q8_STAGE);
     __syncwarp();
-    if (lane < 16) {
-      int64_t row = (int64_t)c_tile * 16 + lane;
-      if (row > last_row) row = last_row;
-      const uint8_t* src = a.data + row * a.rb + (int64_t)(c_sl * nst + c_st) * Q8_ROWB;
-      bulk_g2s(ring + c_slot * Q8_STAGE + lane * Q8_PITCH, src, Q8_ROWB, bars + c_slot);
-    }
+    if (lane < 2)  // box `lane`: rows 8 * lane .. of the tile, words of unit (c_sl * nst + c_st)
+      tma_box_g2s(ring + c_slot * Q8_STAGE + lane * Q8_BOX, &wmap, (c_sl * nst + c_st) * (Q8_ROWB / 4),
+                  c_tile * 16 + lane * 8, bars + c_slot);
     if (++c_slot == Q8_NST) c_slot = 0;
     if (++c_st == nst) {
       c_st = 0;
@@ -153,8 +152,8 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 1) gemv_cs_q8_0_kernel(const Q8
         return;
       }
       const uint8_t* base = ring + slot * Q8_STAGE;
-      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(base + g * Q8_PITCH) + 17 * t;
-      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(base + (g + 8) * Q8_PITCH) + 17 * t;
+      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(base + g * Q8_ROWB) + 17 * t;
+      const uint32_t* r1 = r0 + Q8_BOX / 4;
       uint32_t w0[17], w1[17];
 #pragma unroll
       for (int i = 0; i < 17; i++) {
@@ -291,7 +290,9 @@ int launch_gemv_cs_q8_0(const WRef& w, const void* x, int x_type, float* y, cons
   Q8Plan p;
   q8_plan(w, &p);
   Q8Args a;
-  a.data = w.data, a.N = w.rows, a.rb = w.row_bytes(), a.K = (int)w.cols;
+  a.N = w.rows, a.K = (int)w.cols;
+  CUtensorMap wmap;
+  if (make_row_box_map(w.data, w.row_bytes(), w.rows, Q8_ROWB / 4, 8, &wmap)) return 1;
   a.S = p.S, a.nst = p.nst, a.ntiles = p.ntiles;
   a.x = x, a.x_bf16 = x_type == E_BF16 ? 1 : 0;
   a.error = device_error_word();
@@ -300,7 +301,7 @@ int launch_gemv_cs_q8_0(const WRef& w, const void* x, int x_type, float* y, cons
   a.partial = reinterpret_cast<float*>(ws + 256);
   a.y = y, a.residual = residual;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(gemv_cs_q8_0_kernel), Q8_MAX_SMEM)) return 1;
-  DYN_CUDA(launch_pdl(gemv_cs_q8_0_kernel, dim3(p.grid), dim3(Q8_WARPS * 32), p.smem, s, a));
+  DYN_CUDA(launch_pdl(gemv_cs_q8_0_kernel, dim3(p.grid), dim3(Q8_WARPS * 32), p.smem, s, a, wmap));
   count_launch(1);
   if (p.S > 1) {
     DYN_CUDA(launch_pdl(q8_reduce_kernel, dim3((unsigned)((w.rows + 255) / 256)), dim3(256), 0, s, (const float*)a.partial,

@@ -56,6 +56,7 @@ using namespace dyn;
 struct dyninfer_cuda_session_t {
   int device = 0;
   cudaStream_t stream = nullptr;
+  cudaEvent_t tm0 = nullptr, tm1 = nullptr;  // dyninfer_cuda_session_timer
   ModelCfg cfg;
   FreqTable freq;
   // parameters
@@ -1059,6 +1060,8 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
   if (s->logits_host) cudaFreeHost(s->logits_host);
   if (s->batch_logits_host) cudaFreeHost(s->batch_logits_host);
   if (s->stage_host) cudaFreeHost(s->stage_host);
+  if (s->tm0) cudaEventDestroy(s->tm0);
+  if (s->tm1) cudaEventDestroy(s->tm1);
   if (s->ev0) cudaEventDestroy(s->ev0);
   if (s->ev1) cudaEventDestroy(s->ev1);
   for (int r = 0; r < s->peer.world; r++)
@@ -1266,6 +1269,24 @@ int dyninfer_cuda_session_decode_trace(dyninfer_cuda_session_t* s, uint64_t* out
   DYN_CUDA(cudaStreamSynchronize(s->stream));
   DYN_CUDA(cudaMemcpy(out, s->trace_dev, need * 8, cudaMemcpyDeviceToHost));
   return 0;
+}
+
+int dyninfer_cuda_session_timer(dyninfer_cuda_session_t* s, int stop, float* out_ms) {
+  DYN_CHECK(s != nullptr, "session is NULL");
+  DYN_CUDA(cudaSetDevice(s->device));
+  if (!s->tm0) {
+    DYN_CUDA(cudaEventCreate(&s->tm0));
+    DYN_CUDA(cudaEventCreate(&s->tm1));
+  }
+  if (!stop) {
+    DYN_CUDA(cudaEventRecord(s->tm0, s->stream));
+    return 0;
+  }
+  DYN_CHECK(out_ms != nullptr, "out_ms is NULL");
+  DYN_CUDA(cudaEventRecord(s->tm1, s->stream));
+  DYN_CUDA(cudaEventSynchronize(s->tm1));
+  DYN_CUDA(cudaEventElapsedTime(out_ms, s->tm0, s->tm1));
+  return check_device_error("session timer");
 }
 
 uint64_t dyninfer_cuda_session_launch_count(const dyninfer_cuda_session_t* s) {

@@ -314,6 +314,16 @@ class CudaSession:
                  "t_attn_merge", "t_stage_arrive", "t_stage_convert")
         return dict(zip(names, [float(v) for v in out]))
 
+    def timer_start(self) -> None:
+        """Starts the device-side stopwatch of the session's stream (CUDA events)."""
+        check(lib().dyninfer_cuda_session_timer(self._h, 0, None))
+
+    def timer_stop(self) -> float:
+        """Milliseconds the session's stream spent since `timer_start` (waits for the work)."""
+        ms = C.c_float()
+        check(lib().dyninfer_cuda_session_timer(self._h, 1, C.byref(ms)))
+        return float(ms.value)
+
     def decode_trace(self):
         """[CTAs, layers + 1, 16] global-timer stamps (ns) of the last persistent-kernel launch, or None
         when the session was not created with DYNINFER_CUDA_TRACE=1."""

@@ -52,7 +52,8 @@ def run(model: str = "0.6b-q4_0", layers: int = 0, prompt: int = 512, steps: int
         dump_logits: str = "", solo: bool = False) -> dict:
     """One tensor-parallel run over the ranks of the default process group (any backend that can move
     Python objects; the data path uses this library's own communicator). Every rank calls it with the
-    same arguments; the returned dict is complete on rank 0. `solo`: this process alone runs the
+    same arguments (`check` and `dump_logits` add collective calls: a rank that leaves them out
+    leaves the others waiting in the exchange); the returned dict is complete on rank 0. `solo`: this process alone runs the
     unsharded model on its own GPU, whatever the process group is (no collective is issued)."""
     import torch
     if not torch.cuda.is_available():
@@ -82,10 +83,9 @@ def run(model: str = "0.6b-q4_0", layers: int = 0, prompt: int = 512, steps: int
         load_s = time.perf_counter() - t_load
         s.prefill_slot(0, prompts[0])                      # untimed: first-use set-up
         sync()
-        t0 = time.perf_counter()
+        s.timer_start()
         feed = {slot: s.prefill_slot(slot, prompts[slot]) for slot in range(batch)}
-        torch.cuda.synchronize()
-        prefill_s = time.perf_counter() - t0
+        prefill_s = s.timer_stop() / 1e3
         first = dict(feed)
         produced = [[] for _ in range(batch)]
         for _ in range(warmup):
@@ -94,13 +94,12 @@ def run(model: str = "0.6b-q4_0", layers: int = 0, prompt: int = 512, steps: int
                 produced[k].append(v)
         sync()
         torch.cuda.synchronize()
-        t0 = time.perf_counter()
+        s.timer_start()
         for _ in range(steps):
             feed = s.step(feed)
             for k, v in feed.items():
                 produced[k].append(v)
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
+        dt = s.timer_stop() / 1e3
         wbytes = s.decode_weight_bytes()
         if check or dump_logits:   # logits of the prompt's last row and of one batched step, all ranks in step
             tp_lg, tp_tok = s.prefill_slot(0, prompts[0], want_logits=True)
@@ -121,7 +120,7 @@ def run(model: str = "0.6b-q4_0", layers: int = 0, prompt: int = 512, steps: int
         "weight_gbs_per_gpu": round(wbytes * steps / dt / 1e9, 1),
         "weight_gbs_all_ranks": round(world * wbytes * steps / dt / 1e9, 1),
         "load_s": round(load_s, 1),
-        "timing": "host clock around synchronised C-ABI calls, maximum over ranks",
+        "timing": "CUDA events on each rank's session stream around the timed calls, maximum over ranks",
     })
     if check:
         # every rank must have produced the same tokens; rank 0 compares with the unsharded model

@@ -317,6 +317,12 @@ int dyninfer_cuda_session_decode_phase_profile(dyninfer_cuda_session_t* session,
 int dyninfer_cuda_session_decode_trace(dyninfer_cuda_session_t* session, uint64_t* out, size_t count,
                                        size_t* out_needed);
 
+/* Device-side stopwatch on the session's stream (CUDA events): stop = 0 records the start after
+ * the work queued so far; stop = 1 records the end, waits for it and writes the milliseconds the
+ * stream spent between the two to *out_ms. What the bench and the tensor-parallel runner time
+ * multi-call regions with (no reference counterpart: the reference times on the host). */
+int dyninfer_cuda_session_timer(dyninfer_cuda_session_t* session, int stop, float* out_ms);
+
 /* Number of kernels this library has launched on behalf of `session` since creation. */
 uint64_t dyninfer_cuda_session_launch_count(const dyninfer_cuda_session_t* session);
 

@@ -139,6 +139,14 @@ def use_all_host_threads():
     """The CPU restatement runs on every core this process may use, whatever OMP_NUM_THREADS the
     launcher exported (torch.distributed.run sets it to 1). Must run before the library loads."""
     n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    # a container's CPU quota can be smaller than its affinity mask; threads beyond the quota only
+    # spin against the throttle
+    try:
+        quota, period = open("/sys/fs/cgroup/cpu.max").read().split()[:2]
+        if quota != "max":
+            n = min(n, max(1, int(quota) // int(period)))
+    except (OSError, ValueError):
+        pass
     os.environ["OMP_NUM_THREADS"] = str(max(1, n))
     return n
 
@@ -314,11 +322,11 @@ def tp_section(rank, world, local_rank, no_check=False):
                 r1["ms_per_step"] / (world * runs[batch]["ms_per_step"]), 3)
         replicas.barrier()
     if not no_check:
-        use_all_host_threads()
+        cores = use_all_host_threads()
         from oracle import oracle as orc
         from dyninfer_b200 import checkpoint as ck
         orc.build()
-        orc.set_num_threads(len(os.sched_getaffinity(0)))
+        orc.set_num_threads(cores)
         d = np.load(dump)
         cat = ck.open_catalog(str(d["checkpoint"]))
         m = orc.Model(cat.config, orc.weights_from_catalog(cat), kv_cap=32, kv_round=2, fast=True)

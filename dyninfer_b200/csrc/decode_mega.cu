@@ -620,28 +620,45 @@ __device__ __forceinline__ int kv_stage_off(int row, int b, int rowbytes, bool w
   return row * rowbytes + (piece << 4) + (b & 15);
 }
 
-// Copies the cached rows [k_first, k_first + batch) ∩ [.., min(k_hi, pos)) of this CTA's (head, split)
-// in layer l into the staging buffers (asynchronous, one commit group).
-__device__ __forceinline__ void stage_kv(const MegaArgs& a, int l, int cta, int64_t pos, int64_t seq, int nsplit,
-                                         const Smem& sm, int tid, int batch_index = 0) {
-  if (cta >= a.nh * nsplit || l >= a.layers) return;
-  const int h = cta / nsplit, sp = cta - h * nsplit;
-  const int kvh = h / (a.nh / a.nkv);
+// Where this CTA's (head, split) sits for the token being decoded: worked out once per token (the
+// divisions are not cheap and this code is cold every time it runs), used by every layer.
+struct AttGeo {
+  int h;             // head; >= the number of heads when this CTA has no (head, split)
+  int sp, kvh, gi;
+  int k_lo, k_hi;    // keys [k_lo, k_hi) of positions 0 .. pos
+  size_t plane_bytes;  // byte offset of (sequence, kv head, position 0) inside a layer of the pool
+};
+__device__ __forceinline__ AttGeo att_geometry(const MegaArgs& a, int cta, int pos, int seq, int nsplit) {
+  AttGeo g;
+  g.h = cta / nsplit, g.sp = cta - g.h * nsplit;
+  const int grp = a.nh / a.nkv;
+  g.kvh = g.h / grp, g.gi = g.h - g.kvh * grp;
+  const int n = pos + 1, per = (n + nsplit - 1) / nsplit;
+  g.k_lo = g.sp * per;
+  g.k_hi = g.k_lo + per < n ? g.k_lo + per : n;
+  const int rshift = 31 - __clz(a.d * (a.kv_type == E_F32 ? 4 : 2));  // rows are 128, 256 or 512 bytes
+  g.plane_bytes = ((size_t)((int64_t)seq * a.nkv + g.kvh) * (size_t)a.cap) << rshift;
+  return g;
+}
+
+// Copies the cached rows [k_first, k_first + batch) of this CTA's (head, split) that exist already
+// (positions below pos) from layer l of the pool into the staging buffers: asynchronous, one
+// commit group.
+__device__ __forceinline__ void stage_kv(const MegaArgs& a, const AttGeo& g, int l, int pos, const Smem& sm, int tid,
+                                         int batch_index = 0) {
+  if (g.h >= a.nh || l >= a.layers) return;
   const bool wide = a.kv_type == E_F32;
-  const int el = wide ? 4 : 2, rowbytes = a.d * el;
-  const int64_t n = pos + 1, per = (n + nsplit - 1) / nsplit;
-  const int64_t k_first = (int64_t)sp * per + (int64_t)batch_index * (wide ? 32 : 64);
-  int64_t k_hi = ((int64_t)sp * per + per < n) ? (int64_t)sp * per + per : n;
-  if (k_hi > pos) k_hi = pos;
-  if (k_hi <= k_first) return;
-  const size_t start = (size_t)(((seq * a.nkv + kvh) * a.cap + k_first) * a.d) * el;
-  int bytes = (int)((k_hi - k_first) * rowbytes);  // a multiple of 128
+  const int rowbytes = a.d * (wide ? 4 : 2), rshift = 31 - __clz(rowbytes);
+  const int k_first = g.k_lo + batch_index * (wide ? 32 : 64);
+  const int k_end = g.k_hi < pos ? g.k_hi : pos;
+  if (k_end <= k_first) return;
+  int bytes = (k_end - k_first) << rshift;  // a multiple of 128
   if (bytes > MK_KV_STAGE_BYTES) bytes = MK_KV_STAGE_BYTES;
-  const uint8_t* ksrc = a.kcache + (uint64_t)l * a.layer_stride + start;
-  const uint8_t* vsrc = a.vcache + (uint64_t)l * a.layer_stride + start;
+  const size_t start = (size_t)l * a.layer_stride + g.plane_bytes + ((size_t)k_first << rshift);
+  const uint8_t* ksrc = a.kcache + start;
+  const uint8_t* vsrc = a.vcache + start;
   uint8_t* kdst = reinterpret_cast<uint8_t*>(sm.misc + MK_OFF_KVK);
   uint8_t* vdst = reinterpret_cast<uint8_t*>(sm.misc + MK_OFF_KVV);
-  const int rshift = 31 - __clz(rowbytes);  // rows are 128, 256 or 512 bytes
   for (int off = tid * 16; off < bytes; off += MK_CT * 16) {
     const int row = off >> rshift;
     const int o = kv_stage_off(row, off - (row << rshift), rowbytes, wide);
@@ -662,18 +679,17 @@ __device__ __forceinline__ void stage_kv(const MegaArgs& a, int l, int cta, int6
 //   values : thread (pair = tid % (d/2), group = tid / (d/2)) accumulates two head dims over the
 //            keys of its group; groups are added in a fixed order at the end
 template <int KVT, class Prof>
-__device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, const MegaLayerHot* L, int cta,
-                                                int64_t pos, int64_t seq, int nsplit, unsigned ep,
-                                                const Smem& sm, int tid, int lane, int warp, Prof& prof) {
-  if (cta >= a.nh * nsplit) return;
+__device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, const MegaLayerHot* L, const AttGeo& G,
+                                                int64_t pos, int nsplit, unsigned ep, const Smem& sm, int tid,
+                                                int lane, int warp, Prof& prof) {
+  if (G.h >= a.nh) return;
   constexpr bool WIDE = KVT == E_F32;
   constexpr int EL = WIDE ? 4 : 2;
   constexpr int BK = WIDE ? 32 : 64;    // keys per batch
   constexpr int TPK = MK_CT / BK;       // threads per key
   constexpr int EPP = 16 / EL;          // elements per 16-byte piece
   unsigned long long tp = prof.tic();
-  const int h = cta / nsplit, sp = cta - h * nsplit;
-  const int grp = a.nh / a.nkv, kvh = h / grp, gi = h - kvh * grp;
+  const int h = G.h, sp = G.sp, kvh = G.kvh, gi = G.gi;
   const int d = a.d, half = d / 2, rowbytes = d * EL;
   float* qs = sm.misc + MK_OFF_QS;
   float* kn = sm.misc + MK_OFF_KN;
@@ -686,12 +702,9 @@ __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, cons
   uint8_t* vbuf = reinterpret_cast<uint8_t*>(sm.misc + MK_OFF_KVV);
   uint8_t* kc = a.kcache + (uint64_t)l * a.layer_stride;
   uint8_t* vc = a.vcache + (uint64_t)l * a.layer_stride;
-  const int64_t plane = ((seq * a.nkv + kvh) * a.cap) * d;  // element offset of this head's plane
+  const int64_t plane = (int64_t)(G.plane_bytes / EL);  // element offset of this head's plane
   const int pos32 = (int)pos;  // positions are below the cache capacity, which fits 31 bits
-  const int n = pos32 + 1;
-  const int per = (n + nsplit - 1) / nsplit;
-  const int k_lo = sp * per;
-  const int k_hi = (k_lo + per < n) ? k_lo + per : n;
+  const int k_lo = G.k_lo, k_hi = G.k_hi;
   // this token's own key / value row goes into the staged batch that holds position pos
   auto put_own = [&](uint8_t* buf, int row, int e, float v) {
     const int o = kv_stage_off(row, e * EL, rowbytes, WIDE);
@@ -772,7 +785,7 @@ __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, cons
   for (int k0 = k_lo; k0 < k_hi; k0 += BK, bi++) {
     if (bi > 0) {  // long contexts: the later batches are brought in when their turn comes
       consumer_sync();  // everyone is done with the previous batch
-      stage_kv(a, l, cta, pos, seq, nsplit, sm, tid, bi);
+      stage_kv(a, G, l, pos32, sm, tid, bi);
       if (own_here && pos32 >= k0 && pos32 < k0 + BK && tid < d) {
         put_own(kbuf, pos32 - k0, tid, kn[tid]);
         put_own(vbuf, pos32 - k0, tid, vn[tid]);
@@ -809,6 +822,7 @@ __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, cons
 #pragma unroll
     for (int o = 1; o < TPK; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
     const float sc = kl < nvalid ? dot * scale : -INFINITY;
+    prof.stamp_dbg(9);
     const float wmax = warp_max(sc);
     if (lane == 0) wm[warp] = wmax;
     consumer_sync();
@@ -823,6 +837,7 @@ __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, cons
     float l_batch = 0.f;
 #pragma unroll
     for (int w = 0; w < MK_CW; w++) l_batch += wl[w];
+    prof.stamp_dbg(10);
     const float factor = expf(m_run - m_new);
     l_run = l_run * factor + l_batch;
     acc0 *= factor, acc1 *= factor;
@@ -846,6 +861,7 @@ __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, cons
       acc1 = fmaf(pk, v1, acc1);
     }
   }
+  prof.stamp_dbg(11);
   prof.toc(14, tp);
   prof.stamp(14);
   tp = prof.tic();
@@ -870,17 +886,17 @@ __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, cons
   }
   prof.stamp(4);
   prof.toc(15, tp);
-  consumer_sync();  // wacc and the staging buffers are free again
-  stage_kv(a, l + 1, cta, pos, seq, nsplit, sm, tid);  // the next layer's first batch
+  // the next layer's first batch: every warp is past its reads of the staging buffers (barrier above)
+  stage_kv(a, G, l + 1, pos32, sm, tid);
 }
 
 template <class Prof>
-__device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const MegaLayerHot* L, int cta,
-                                                int64_t pos, int64_t seq, int nsplit, unsigned ep,
-                                                const Smem& sm, int tid, int lane, int warp, Prof& prof) {
+__device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const MegaLayerHot* L, const AttGeo& G,
+                                                int64_t pos, int nsplit, unsigned ep, const Smem& sm, int tid,
+                                                int lane, int warp, Prof& prof) {
 #ifndef MK_SIZE_PROBE
   if (a.kv_type == E_F32)
-    phase_attention_t<E_F32>(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
+    phase_attention_t<E_F32>(a, l, L, G, pos, nsplit, ep, sm, tid, lane, warp, prof);
   else
 #endif
 #if !defined(MK_SIZE_PROBE) || MK_SIZE_PROBE < 3
@@ -888,10 +904,10 @@ __device__ __forceinline__ void phase_attention(const MegaArgs& a, int l, const 
 #else
   if (false)
 #endif
-    phase_attention_t<E_BF16>(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
+    phase_attention_t<E_BF16>(a, l, L, G, pos, nsplit, ep, sm, tid, lane, warp, prof);
 #ifndef MK_SIZE_PROBE
   else
-    phase_attention_t<E_F16>(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
+    phase_attention_t<E_F16>(a, l, L, G, pos, nsplit, ep, sm, tid, lane, warp, prof);
 #endif
 }
 
@@ -971,7 +987,8 @@ __device__ __forceinline__ void run_phase_t(const MegaArgs& a, const Smem& sm, W
       }
       if (ok) {
         const Geo q = geometry(hot, slot);
-        for (int u = warp; u < q.nu; u += MK_CW)
+        int u = warp;
+        for (; u < q.nu; u += MK_CW)
           run_unit<ENC>(q.enc, q.aux, q.gs, q.p0, q.p1, q.a0, q.a1, q.apitch16, u, q.kb0, sm, lane, t);
       }
       prof.toc(11, tr);
@@ -1156,7 +1173,8 @@ __device__ __forceinline__ void decode_mega_body(const MegaArgs& a) {
     sm.misc[MK_OFF_ROPE + tid] = cv;
     sm.misc[MK_OFF_ROPE + 64 + tid] = sv;
   }
-  stage_kv(a, 0, cta, pos, seq, nsplit, sm, tid);
+  const AttGeo AG = att_geometry(a, cta, (int)pos, (int)seq, nsplit);
+  stage_kv(a, AG, 0, (int)pos, sm, tid);
   // every CTA decodes the token's embedding row for itself: no hand-off before the first product
   mega_gather_row(a.embed, token, sm.xs, tid, MK_CT);
   consumer_sync();
@@ -1201,7 +1219,7 @@ __device__ __forceinline__ void decode_mega_body(const MegaArgs& a) {
       nw = head ? a.out_norm : L->attn_norm, nw_type = head ? a.out_norm_type : L->norm_type;
       n_in = a.H, lenc = head ? a.lm_head.enc : L->enc_q;
     } else if (k == 1) {
-      phase_attention(a, l, L, cta, pos, seq, nsplit, ep, sm, tid, lane, warp, prof);
+      phase_attention(a, l, L, AG, pos, nsplit, ep, sm, tid, lane, warp, prof);
       prof.mark(2);
       src.kind = nsplit > 1 ? SRC_PARTIALS : SRC_LL, src.ll = nsplit > 1 ? a.ll_part : a.ll_ctx, src.ep = ep;
       n_in = (int)qd, lenc = L->enc_o;

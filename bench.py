@@ -109,7 +109,7 @@ class ClockSampler:
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_mega_kernel launch on this workload,
 # recorded from an ncu capture of this kernel (a profiler cannot run inside the timed region); the
 # bench line labels it as recorded, not measured in this run
-MEGA_DRAM_TRAFFIC = 384_337_664 + 10_346_240
+MEGA_DRAM_TRAFFIC = 381_600_640 + 4_658_560
 
 
 def checkpoint_path():

@@ -72,9 +72,12 @@ constexpr int CS_MAX_SMEM = 226 * 1024;  // dynamic shared memory the kernel may
 // sx8[b] = sum_factor * sum(block b of the scaled row) in accumulator units (8 = the Q4_0 zero point;
 // 1 for Q4_1, whose minimum multiplies the plain sum).
 // Returns 2^24 / scale (what turns accumulator units back into the product).
-// K may end half way through a stage (K % 512 == 256): the arrangement then covers Kpad = K + 256
-// elements, the last 256 of them zeros.
-__device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf16, int K, int Kpad, uint2* xq,
+// K may end half way through a stage (K % 512 == 256): elements past K read as zeros.
+// Only the span [k0, k0 + kspan) of the row is arranged (the K-slices this CTA's items touch: items
+// are numbered slice-major, so a CTA works inside one or two slices and the arrangement costs
+// 1/S of the row instead of all of it); the scale comes from the whole row, so that every CTA
+// uses the same one. xq and sx8 are indexed from the start of the span.
+__device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf16, int K, int k0, int kspan, uint2* xq,
                                             float* sx8, float* red, float sum_factor) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   auto ld = [&](int i) -> float {
@@ -92,11 +95,12 @@ __device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf
   for (int i = 0; i < CS_WARPS; i++) mx = fmaxf(mx, red[i]);
   float s, is;
   scale_for(mx, &s, &is);
-  for (int j = tid; j < (Kpad >> 2); j += CS_WARPS * 32) {  // item j: block j / 8, mma step j % 8
+  for (int j = tid; j < (kspan >> 2); j += CS_WARPS * 32) {  // item j: block j / 8 of the span, mma step j % 8
     const int b = j >> 3, st = j & 7, i = st >> 1, o = st & 1;
     const int U = b >> 3, r = b & 7, t = r >> 1, e = r & 1;
-    const float e0 = ld(b * 32 + 4 * i + o) * s, e1 = ld(b * 32 + 4 * i + o + 2) * s;
-    const float g0 = ld(b * 32 + 16 + 4 * i + o) * s, g1 = ld(b * 32 + 16 + 4 * i + o + 2) * s;
+    const int kb = k0 + b * 32;
+    const float e0 = ld(kb + 4 * i + o) * s, e1 = ld(kb + 4 * i + o + 2) * s;
+    const float g0 = ld(kb + 16 + 4 * i + o) * s, g1 = ld(kb + 16 + 4 * i + o + 2) * s;
     float sum = (e0 + e1) + (g0 + g1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
@@ -121,8 +125,8 @@ struct CsArgs {
   int K;
   int S;                 // K-slices per tile
   int nst;               // stages per item (ceil(K / 512) / S)
-  int tail;              // 1 when the last stage of a row holds one unit (K % 512 == 256): the rest reads as zeros
   int ntiles;
+  int span_units;        // 256-element units of the activation row a CTA arranges at most
   const void* x;         // the activation row
   int x_bf16;
   float* misc;           // [0] = 2^24 / scale, for the K-slice reduction
@@ -144,9 +148,8 @@ gemv_cs_q4_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap) {
   uint8_t* ring = cs_smem + (size_t)warp * CS_NST * G::STAGE;
   uint64_t* bars = reinterpret_cast<uint64_t*>(cs_smem + (size_t)CS_WARPS * CS_NST * G::STAGE) + warp * CS_NST;
   uint4* xq = reinterpret_cast<uint4*>(cs_smem + G::RING_BYTES);
-  const int Kpad = a.K + (a.tail ? 256 : 0);
-  float* sx8 = reinterpret_cast<float*>(xq + (size_t)(Kpad >> 8) * 64);
-  float* red = sx8 + (Kpad >> 5);
+  float* sx8 = reinterpret_cast<float*>(xq + (size_t)a.span_units * 64);
+  float* red = sx8 + a.span_units * 8;
   pdl_trigger();  // the next kernel of the stream may start its own weight fetch
   if (threadIdx.x == 0) s_abort = 0;
   if (lane == 0) {
@@ -155,18 +158,23 @@ gemv_cs_q4_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap) {
   }
   __syncthreads();
 
+  // item = slice * ntiles + tile (slice-major): consecutive items share their K-slice
   const int64_t nitems = (int64_t)a.ntiles * a.S;
   const int64_t gw = (int64_t)blockIdx.x * CS_WARPS + warp;
   const int64_t nwarps = (int64_t)gridDim.x * CS_WARPS;
   const int64_t item_lo = nitems * gw / nwarps, item_hi = nitems * (gw + 1) / nwarps;  // balanced split
   const int nst = a.nst;
   const int total = item_lo < item_hi ? (int)(item_hi - item_lo) * nst : 0;
+  // the slices this CTA's sixteen warps touch, and the units of the activation row they cover
+  const int64_t cta_lo = nitems * ((int64_t)blockIdx.x * CS_WARPS) / nwarps;
+  const int64_t cta_hi = nitems * ((int64_t)(blockIdx.x + 1) * CS_WARPS) / nwarps;
+  const int sl_first = (int)(cta_lo / a.ntiles), sl_last = cta_hi > cta_lo ? (int)((cta_hi - 1) / a.ntiles) : sl_first;
+  const int U_base = sl_first * nst * 2;
 
   // copy role: lanes 0..3 each fetch one box (unit lane >> 1, rows 8 * (lane & 1) ..) of the stage.
   // The copy cursor (tile, slice, stage, slot) runs CS_NST stages ahead of the math and advances
   // without divisions.
-  const int S = a.S;
-  const int tile_lo = (int)(item_lo / S), sl_lo = (int)(item_lo - (int64_t)tile_lo * S);
+  const int sl_lo = (int)(item_lo / a.ntiles), tile_lo = (int)(item_lo - (int64_t)sl_lo * a.ntiles);
   int c_left = total, c_tile = tile_lo, c_sl = sl_lo, c_st = 0, c_slot = 0;
   auto issue = [&]() {
     if (c_left <= 0) return;
@@ -182,7 +190,7 @@ gemv_cs_q4_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap) {
     if (++c_slot == CS_NST) c_slot = 0;
     if (++c_st == nst) {
       c_st = 0;
-      if (++c_sl == S) c_sl = 0, c_tile++;
+      if (++c_tile == a.ntiles) c_tile = 0, c_sl++;
     }
   };
 #pragma unroll
@@ -192,8 +200,8 @@ gemv_cs_q4_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap) {
   // flight. Everything else (the activation row, the scratch words) does.
   pdl_wait();
   // while the first stages are in flight: arrange the activation row in shared memory
-  const float out_scale =
-      cs_stage_x(a.x, a.x_bf16, a.K, Kpad, reinterpret_cast<uint2*>(xq), sx8, red, ENC == E_Q4_0 ? 8.0f : 1.0f);
+  const float out_scale = cs_stage_x(a.x, a.x_bf16, a.K, U_base * 256, (sl_last - sl_first + 1) * nst * 512,
+                                     reinterpret_cast<uint2*>(xq), sx8, red, ENC == E_Q4_0 ? 8.0f : 1.0f);
   if (blockIdx.x == 0 && threadIdx.x == 0) a.misc[0] = out_scale;
   __syncthreads();
   if (total == 0) return;
@@ -217,7 +225,7 @@ gemv_cs_q4_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap) {
       const uint32_t* r1 = r0 + G::BOX / 4;
 #pragma unroll
       for (int pr = 0; pr < CS_PAIRS; pr++) {
-      const int U0 = ((sl * nst + st) * CS_PAIRS + pr) * 2;  // first 256-element unit of this pair
+      const int U0 = ((sl * nst + st) * CS_PAIRS + pr) * 2 - U_base;  // first unit of this pair within the arranged span
       // the pair goes to registers first; after the last pair the slot can be refilled before the math
       uint32_t w0[2][LW], w1[2][LW];
 #pragma unroll
@@ -305,7 +313,7 @@ gemv_cs_q4_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap) {
       }
     }
     acc0 = acc1 = 0.f;
-    if (++sl == S) sl = 0, tile++;
+    if (++tile == a.ntiles) tile = 0, sl++;
   }
 }
 
@@ -325,20 +333,13 @@ cs_reduce_kernel(const float* __restrict__ partial, int S, int64_t N, const floa
 }
 
 struct CsPlan {
-  int S, nst, ntiles, grid;
+  int S, nst, ntiles, grid, span_units;
   size_t smem, off_err, off_part, bytes;
 };
 
-size_t cs_smem_bytes(int enc, int K) {
-  const size_t ring = enc == E_Q4_0 ? CsGeo<E_Q4_0>::RING_BYTES : CsGeo<E_Q4_1>::RING_BYTES;
-  const int Kpad = (K + CS_KSTAGE - 1) / CS_KSTAGE * CS_KSTAGE;
-  return ring + (size_t)(Kpad >> 8) * 1024 + (size_t)(Kpad >> 5) * 4 + 128;
-}
-
-bool cs_shape_ok(const WRef& w, int M) {
+bool cs_basic_ok(const WRef& w, int M) {
   return M == 1 && (w.enc == E_Q4_0 || w.enc == E_Q4_1) && w.rows >= 1 && w.cols >= CS_KSTAGE &&
-         w.cols % (CS_KSTAGE / 2) == 0 && cs_smem_bytes(w.enc, (int)w.cols) <= (size_t)CS_MAX_SMEM &&
-         (reinterpret_cast<uintptr_t>(w.data) & 15) == 0;
+         w.cols % (CS_KSTAGE / 2) == 0 && (reinterpret_cast<uintptr_t>(w.data) & 15) == 0;
 }
 
 void cs_plan(const WRef& w, CsPlan* p) {
@@ -357,10 +358,26 @@ void cs_plan(const WRef& w, CsPlan* p) {
   p->nst = stages / S;
   const int64_t items = (int64_t)p->ntiles * S;
   p->grid = (int)std::min<int64_t>(sms, (items + CS_WARPS - 1) / CS_WARPS);
-  p->smem = cs_smem_bytes(w.enc, K);
+  // the widest span of K-slices one CTA's items touch (items are slice-major)
+  const int64_t nwarps = (int64_t)p->grid * CS_WARPS;
+  int span = 1;
+  for (int b = 0; b < p->grid; b++) {
+    const int64_t lo = items * ((int64_t)b * CS_WARPS) / nwarps, hi = items * ((int64_t)(b + 1) * CS_WARPS) / nwarps;
+    if (hi > lo) span = std::max(span, (int)((hi - 1) / p->ntiles - lo / p->ntiles) + 1);
+  }
+  p->span_units = span * p->nst * 2;
+  const size_t ring = w.enc == E_Q4_0 ? CsGeo<E_Q4_0>::RING_BYTES : CsGeo<E_Q4_1>::RING_BYTES;
+  p->smem = ring + (size_t)p->span_units * (1024 + 32) + 128;
   p->off_err = 0;       // [64] 2^24 / scale
   p->off_part = 256;
   p->bytes = 256 + (S > 1 ? (size_t)S * w.rows * 4 : 0);
+}
+
+bool cs_shape_ok(const WRef& w, int M) {
+  if (!cs_basic_ok(w, M)) return false;
+  CsPlan p;
+  cs_plan(w, &p);
+  return p.smem <= (size_t)CS_MAX_SMEM;
 }
 
 }  // namespace
@@ -400,7 +417,7 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
   CUtensorMap wmap;
   if (make_row_box_map(w.data, w.row_bytes(), w.rows, w.enc == E_Q4_0 ? CsGeo<E_Q4_0>::UW : CsGeo<E_Q4_1>::UW, 8, &wmap))
     return 1;
-  a.S = p.S, a.nst = p.nst, a.ntiles = p.ntiles, a.tail = (w.cols % CS_KSTAGE) ? 1 : 0;
+  a.S = p.S, a.nst = p.nst, a.ntiles = p.ntiles, a.span_units = p.span_units;
   a.x = x, a.x_bf16 = x_type == E_BF16 ? 1 : 0;
   a.error = device_error_word();
   if (!a.error) return 1;

@@ -51,6 +51,9 @@ __global__ void __launch_bounds__(TP_THREADS, 1) tp_exchange_kernel(const PeerAr
   __shared__ float s_inv;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_trigger();  // a product launched next may begin fetching its weights
+  // launched as a programmatic dependent: everything above and the launch itself overlap the tail
+  // of the product before; its partial rows (and this kernel's own epoch word) are there after the wait
+  pdl_wait();
   const unsigned e = a.epochs[blockIdx.x] + 1;
   // arrival: this rank's partial rows were written by the kernel before this one
   if (tid < a.world) {
@@ -62,7 +65,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1) tp_exchange_kernel(const PeerAr
     for (; it < a.spins; it++) {
       seen = ld_acquire_sys(mine);
       if ((int)(seen - e) >= 0) break;
-      __nanosleep(200);
+      __nanosleep(32);
     }
     if ((int)(seen - e) < 0) *a.error = 1 + tid;  // peer `tid` did not arrive
   }
@@ -134,7 +137,7 @@ int launch_tp_exchange(const TpPeer& p, int slot, int64_t rows, int H, float* hi
   a.rank = p.rank, a.world = p.world, a.rows = (int)rows, a.H = H;
   a.spins = p.spin_limit > 0 ? p.spin_limit : TP_SPINS;
   const int grid = (int)std::min<int64_t>(rows, TP_PEER_BLOCKS);
-  tp_exchange_kernel<<<grid, TP_THREADS, 0, st>>>(a);
+  DYN_CUDA(launch_pdl(tp_exchange_kernel, dim3(grid), dim3(TP_THREADS), 0, st, a));
   count_launch();
   DYN_CUDA(cudaGetLastError());
   return 0;

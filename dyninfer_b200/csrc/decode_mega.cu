@@ -1144,8 +1144,8 @@ __device__ __forceinline__ void decode_mega_body(const MegaArgs& a) {
     return;
   }
   // -------------------------------- consumers -------------------------------------------------
-  int64_t token = __ldcg(a.io + 0), pos = __ldcg(a.io + 1);
-  const int64_t seq = __ldcg(a.io + 2);
+  int64_t token = a.inline_io ? a.in_token : __ldcg(a.io + 0), pos = a.inline_io ? a.in_pos : __ldcg(a.io + 1);
+  const int64_t seq = a.inline_io ? a.in_seq : __ldcg(a.io + 2);
   const int64_t qd = (int64_t)a.nh * a.d;
   const int hid_lo = (int)hdr->hid_lo;
   float* res = sm.misc + MK_OFF_RES;
@@ -1292,6 +1292,7 @@ __device__ __forceinline__ void decode_mega_body(const MegaArgs& a) {
       *next_tok = (int)tok;
       if (cta == 0) {
         a.io[3] = tok;
+        if (a.out_host) a.out_host[0] = tok;
         if (a.advance) {
           a.io[0] = tok;
           a.io[1] = pos + 1;
@@ -1312,6 +1313,7 @@ __device__ __forceinline__ void decode_mega_body(const MegaArgs& a) {
   }  // tokens of the launch
   if (tid == 0 && *sm.abort) {
     atomicExch(a.error, *sm.abort);
+    if (a.out_host) a.out_host[1] = *sm.abort;
     // let any bulk copy still in flight land before the CTA's shared memory is released
     const long long t0 = clock64();
     while (clock64() - t0 < (1LL << 22)) {

@@ -120,8 +120,14 @@ struct MegaArgs {
   int64_t* hist;
   int64_t* hist_count;
   int64_t hist_cap;
+  // One-token calls pass the token, position and sequence as launch parameters and get the result
+  // written straight into pinned host memory (no copy before or after the launch): inline_io = 1,
+  // out_host = device address of two host words (produced token, error code of an expired wait).
+  int inline_io;
+  int64_t in_token, in_pos, in_seq;
+  int64_t* out_host;
   int advance;  // 1: feed the produced token back and advance the position on the device
-  int opts;     // bit 0: no L2 prefetch of cached keys / values, bit 1: none of norm vectors (measurement switches)
+  int opts;     // bit 1: no L2 prefetch of the next layer's norm vectors (measurement switch)
   int steps;    // tokens decoded by this launch (> 1 needs advance); epochs: steps * (layers + 2)
   int* error;   // set non-zero when a bounded wait gave up
   int max_split;

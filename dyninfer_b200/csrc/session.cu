@@ -567,6 +567,7 @@ void fill_mega_args(Session* s, MegaArgs* a, int advance, int steps = 1) {
   a->layer_stride = (uint64_t)c.batch * c.kv_heads * (uint64_t)a->cap * c.head_dim * s->kv_elem;
   a->kv_type = s->kv_type;
   a->io = s->io_dev;
+  a->inline_io = 0, a->in_token = a->in_pos = a->in_seq = 0, a->out_host = nullptr;
   a->hist = s->hist_dev, a->hist_count = s->hist_count_dev, a->hist_cap = (int64_t)s->hist_cap;
   a->advance = advance;
   a->error = reinterpret_cast<int*>(s->io_dev + 4);
@@ -1330,11 +1331,14 @@ int dyninfer_cuda_session_invoke_paged_chunk_slot(dyninfer_cuda_session_t* s, co
     s->stage_host[0] = tokens[0];
     s->stage_host[1] = start_pos;
     s->stage_host[2] = slot;
+    // token, position and slot travel as launch parameters; the kernel writes the produced token
+    // (and the code of an expired wait) into the pinned staging words itself
     MegaArgs ma;
     fill_mega_args(s, &ma, 0);
-    DYN_CUDA(cudaMemcpyAsync(s->io_dev, s->stage_host, 24, cudaMemcpyHostToDevice, s->stream));
+    ma.inline_io = 1, ma.in_token = tokens[0], ma.in_pos = start_pos, ma.in_seq = slot;
+    DYN_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&ma.out_host), s->stage_host + 3, 0));
+    s->stage_host[4] = 0;
     if (launch_decode_mega(ma, s->mega_grid, s->mega_smem, s->stream)) return 1;
-    DYN_CUDA(cudaMemcpyAsync(s->stage_host + 3, s->io_dev + 3, 16, cudaMemcpyDeviceToHost, s->stream));
   } else if (rows == 1) {
     if (!s->decode_graph && capture(s, false, &s->decode_graph, &s->graph_nodes)) return 1;
     s->stage_host[0] = tokens[0];

@@ -480,4 +480,15 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    # A rank that fails must take the job down at once: left to normal interpreter shutdown it can
+    # block in the teardown of its communicators while the other ranks wait for it in a collective.
+    try:
+        main()
+    except SystemExit:
+        raise
+    except BaseException:
+        import traceback
+        traceback.print_exc()
+        sys.stderr.flush()
+        sys.stdout.flush()
+        os._exit(1)

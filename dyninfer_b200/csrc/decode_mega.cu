@@ -776,9 +776,14 @@ __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, cons
     }
   }
   const float scale = 1.0f / sqrtf((float)d);
+  static_assert(MK_CT == 256, "the thread maps below assume 256 consumer threads");
   const int kl = tid / TPK, part = tid - kl * TPK;  // key within the batch, piece phase
-  const int npair = d >> 1, kg = tid / npair, dp = tid - kg * npair;  // value pass: dim pair, key group
-  const int kpg = BK / (MK_CT / npair);                                // keys per group
+  // value pass: dim pair and key group (head dim 128 or 64: shifts, not divisions -- this code is cold
+  // every time it runs)
+  const int lognp = d == 128 ? 6 : 5;
+  const int npair = 1 << lognp, kg = tid >> lognp, dp = tid & (npair - 1);
+  const int ngroups = MK_CT >> lognp;   // 4 or 8 key groups
+  const int kpg = BK >> (8 - lognp);    // keys per group
   const int npiece = rowbytes >> 4;
   float m_run = -3.40282347e38f, l_run = 0.f, acc0 = 0.f, acc1 = 0.f;
   int bi = 0;
@@ -870,7 +875,6 @@ __device__ __forceinline__ void phase_attention_t(const MegaArgs& a, int l, cons
   wacc[kg * 128 + 2 * dp + 1] = acc1;
   consumer_sync();
   prof.stamp(15);
-  const int ngroups = MK_CT / npair;
   const int64_t pbase = ((int64_t)h * a.max_split + sp) * (d + 4);
   if (tid < d) {
     float o = 0.f;

@@ -370,12 +370,19 @@ __device__ __forceinline__ void item_store(const float (&sv)[8], int layout, int
     for (int j = 0; j < 8; j++) f[j] = sv[j];
     *run0 = sa, *run1 = sb;
   }
-  __half hi[8], lo[8];
+  __half hi[8], lo[8];  // 16-bit storage: f16, or bf16 bit patterns for the plain-bf16 layout
 #pragma unroll
   for (int j = 0; j < 8; j++) {
-    const __half h = __float2half_rn(f[j]);
-    hi[j] = h;
-    lo[j] = __float2half_rn(f[j] - __half2float(h));
+    if (layout == XL_BF16N) {
+      const __nv_bfloat16 h = __float2bfloat16_rn(f[j]);
+      const __nv_bfloat16 l = __float2bfloat16_rn(f[j] - __bfloat162float(h));
+      hi[j] = __ushort_as_half(__bfloat16_as_ushort(h));
+      lo[j] = __ushort_as_half(__bfloat16_as_ushort(l));
+    } else {
+      const __half h = __float2half_rn(f[j]);
+      hi[j] = h;
+      lo[j] = __float2half_rn(f[j] - __half2float(h));
+    }
   }
   uint4* dst = reinterpret_cast<uint4*>(sm.xf + ((size_t)(kb * 2) * 4 + t) * 8);
   dst[0] = *reinterpret_cast<uint4*>(hi);
@@ -541,6 +548,11 @@ __device__ __forceinline__ void run_unit_t(int aux, int group_shift, const uint8
     blk_q8_0<0, true>(p0 + u * 68, p1 + u * 68, xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc, sm.isx[kb]);
     blk_q8_0<2, true>(p0 + u * 68 + 34, p1 + u * 68 + 34, xf0 + (size_t)(kb + 1) * 64, sm.sx32[kb + 1],
                       0.f, t, acc, sm.isx[kb + 1]);
+  } else if (ENC == E_BF16 || ENC == E_F16) {
+    // a unit is one block of 32 plain weights; the activations carry the block's own power-of-two
+    // scale (isx = 2^24 / scale), the weights are true values
+    const int kb = kb0 + u;
+    blk_plain16<ENC == E_BF16, true>(p0 + u * 64, p1 + u * 64, xf0 + (size_t)kb * 64, t, acc, sm.isx[kb] * GV_2M24);
   } else if (ENC == E_MLX_U4) {
     const int kb = kb0 + u;
     const int gi = u >> group_shift;
@@ -576,6 +588,8 @@ __device__ __forceinline__ void run_unit(int enc, int aux, int group_shift, cons
     case E_Q4_1: run_unit_t<E_Q4_1>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc); break;
     case E_Q8_0: run_unit_t<E_Q8_0>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc); break;
     case E_MLX_U4: run_unit_t<E_MLX_U4>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc); break;
+    case E_BF16: run_unit_t<E_BF16>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc); break;
+    case E_F16: run_unit_t<E_F16>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc); break;
     default: run_unit_t<E_Q6_K>(aux, group_shift, p0, p1, a0, a1, apitch16, u, kb0, sm, lane, acc); break;
   }
 }
@@ -1373,6 +1387,8 @@ HostPlan host_plan(const WRef& w) {
     case E_Q4_1: p.ubytes = 20, p.ukb = 1, p.units_total = K / 32; break;
     case E_Q8_0: p.ubytes = 68, p.ukb = 2, p.units_total = K / 64; break;
     case E_MLX_U4: p.ubytes = 16, p.ukb = 1, p.units_total = K / 32; break;
+    case E_BF16:
+    case E_F16: p.ubytes = 64, p.ukb = 1, p.units_total = K / 32; break;
     default: p.ubytes = 0, p.ukb = 2, p.units_total = K / 64, p.unit_q6 = 1; break;  // quarters
   }
   return p;
@@ -1622,6 +1638,8 @@ bool mega_supports_weight(const WRef& w) {
     case E_Q8_0: return w.cols % 256 == 0;
     case E_Q4_1: return w.cols % 128 == 0;
     case E_Q6_K: return w.cols % 1024 == 0;
+    case E_BF16:  // plain 16-bit matrices (a tied bf16 embedding table as the head)
+    case E_F16: return w.cols % 512 == 0;
     case E_MLX_U4:  // scales and biases are copied with one alignment rule: they must agree modulo 16
       return w.cols % 256 == 0 && (w.group == 32 || w.group == 64 || w.group == 128) &&
              ((reinterpret_cast<uintptr_t>(w.scales) ^ reinterpret_cast<uintptr_t>(w.biases)) & 15) == 0;

@@ -37,17 +37,27 @@ __device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // ---- activation staging ---------------------------------------------------------------
 // Fragment layouts (per 32-element block kb, column c, lane quarter t = lane & 3), 8 halfs:
 //   NIBBLE (Q4_0, Q4_1): x[4t] x[4t+2] x[16+4t]/16 x[16+4t+2]/16 x[4t+1] x[4t+3]
 //                        x[16+4t+1]/16 x[16+4t+3]/16
 //   MLXW   (MLX u4)    : x[8t] x[8t+4] x[8t+1]/16 x[8t+5]/16 x[8t+2] x[8t+6] x[8t+3]/16 x[8t+7]/16
 //   BYTES  (Q8_0, Q6_K): x[4t] x[4t+1] x[4t+2] x[4t+3] x[16+4t] ... x[16+4t+3]
+//   BF16N  (plain bf16): the order of BYTES, the fragments held as bf16 (hi + lo) instead of f16
 // The /16 compensates high nibbles that are used in place (as 16*q).
-enum { XL_NIBBLE = 0, XL_MLXW = 1, XL_BYTES = 2 };
+enum { XL_NIBBLE = 0, XL_MLXW = 1, XL_BYTES = 2, XL_BF16N = 3 };
 
 __host__ __device__ inline int xl_for_encoding(int enc) {
-  return (enc == E_Q4_0 || enc == E_Q4_1) ? XL_NIBBLE : (enc == E_MLX_U4 ? XL_MLXW : XL_BYTES);
+  return (enc == E_Q4_0 || enc == E_Q4_1) ? XL_NIBBLE
+                                         : (enc == E_MLX_U4 ? XL_MLXW : (enc == E_BF16 ? XL_BF16N : XL_BYTES));
 }
 
 __device__ __forceinline__ int xl_index(int layout, int t, int i) {
@@ -196,6 +206,35 @@ __device__ __forceinline__ void blk_q8_0(const uint8_t* p0, const uint8_t* p1, c
                   __byte_perm(w1, 0, 0x4342), hlf ? b.z : b.x, hlf ? b.w : b.y);
   }
   unit_apply<HILO>(acc, c, ldh_f32(p0) * bs, ldh_f32(p1) * bs, 128.0f * GV_2M24, sxa, sxb);
+}
+
+// One block of 32 plain 16-bit weights (64 bytes, 4-byte aligned): bf16 weights against bf16
+// activation fragments (layout BF16N), f16 weights against f16 fragments (layout BYTES). The
+// weights are the A operand as they lie in memory: lane quarter t owns elements 4t .. 4t+3 of
+// each half of the block. scale: what turns the tile sums back into true units.
+template <bool BF16, bool HILO>
+__device__ __forceinline__ void blk_plain16(const uint8_t* p0, const uint8_t* p1, const __half* xfp, int t,
+                                            TileAcc<HILO>& acc, float scale) {
+  const uint4 b = *reinterpret_cast<const uint4*>(xfp);
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int hlf = 0; hlf < 2; hlf++) {
+    const uint2 w0 = *reinterpret_cast<const uint2*>(p0 + 32 * hlf + 8 * t);
+    const uint2 w1 = *reinterpret_cast<const uint2*>(p1 + 32 * hlf + 8 * t);
+    if (BF16)
+      mma_bf16_16816(c, w0.x, w1.x, w0.y, w1.y, hlf ? b.z : b.x, hlf ? b.w : b.y);
+    else
+      mma_f16_16816(c, w0.x, w1.x, w0.y, w1.y, hlf ? b.z : b.x, hlf ? b.w : b.y);
+  }
+  if (HILO) {
+    acc.v[0] = fmaf(scale, c[0] + c[1], acc.v[0]);
+    acc.v[1] = fmaf(scale, c[2] + c[3], acc.v[1]);
+  } else {
+    acc.v[0] = fmaf(scale, c[0], acc.v[0]);
+    acc.v[1] = fmaf(scale, c[1], acc.v[1]);
+    acc.v[2] = fmaf(scale, c[2], acc.v[2]);
+    acc.v[3] = fmaf(scale, c[3], acc.v[3]);
+  }
 }
 
 template <bool HILO>

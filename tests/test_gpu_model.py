@@ -106,7 +106,7 @@ def test_tiny_qwen3_logits_and_greedy(native_lib, oracle, tmp_path, flavor, kv, 
     """Seeded Qwen3-shaped model (2 layers): prompt of 16 ids, 32 greedy steps.
     logits max-abs <= 1e-2, cosine >= 0.9999, identical greedy tokens except near-ties."""
     # the persistent kernel needs 1024-wide Q6_K rows: its cases run on the smallest shapes it takes
-    cfg = synth.TINY if kernel == "graph" or flavor == "mlx_u4" else (synth.SMALL_D64 if kv == "f32" else synth.SMALL_D128)
+    cfg = synth.TINY if kernel == "graph" else (synth.SMALL_D64 if kv == "f32" else synth.SMALL_D128)
     if flavor == "mlx_u4":
         path = synth.write_qwen3_mlx(str(tmp_path / "mlx"), cfg, seed=11)
     else:
@@ -119,8 +119,9 @@ def test_tiny_qwen3_logits_and_greedy(native_lib, oracle, tmp_path, flavor, kv, 
     steps = 32
     want_logits, want_toks, margins = oracle_run(oracle, cat, prompt, steps, kv_round=2 if kv == "bf16" else 0)
     with model.create_session(SessionConfig(max_sequence_length=512)) as s:
-        # the path under test is the one that runs (bf16 embeddings keep MLX models on the operator path)
-        assert s.uses_persistent_kernel() == (kernel == "persistent" and flavor != "mlx_u4")
+        # the path under test is the one that runs (the MLX model's head is its tied bf16 embedding table:
+        # plain 16-bit tile steps inside the persistent kernel)
+        assert s.uses_persistent_kernel() == (kernel == "persistent")
         lg = s.prefill(prompt).values
         assert np.abs(lg - want_logits[0]).max() <= 1e-2 and helpers.cosine(lg, want_logits[0]) >= 0.9999
         toks = [int(np.argmax(lg))]

@@ -554,12 +554,22 @@ __device__ __forceinline__ void run_unit_t(int aux, int group_shift, const uint8
     const int kb = kb0 + u;
     blk_plain16<ENC == E_BF16, true>(p0 + u * 64, p1 + u * 64, xf0 + (size_t)kb * 64, t, acc, sm.isx[kb] * GV_2M24);
   } else if (ENC == E_MLX_U4) {
-    const int kb = kb0 + u;
-    const int gi = u >> group_shift;
-    const float bs = sm.isx[kb];
-    blk_mlx<true>(p0 + u * 16, p1 + u * 16, aux_load(a0, aux, gi) * bs, aux_load(a1, aux, gi) * bs,
-                  aux_load(a0 + apitch16, aux, gi) * bs, aux_load(a1 + apitch16, aux, gi) * bs,
-                  xf0 + (size_t)kb * 64, sm.sx32[kb], 0.f, t, acc);
+    // a unit is two 32-blocks (32 bytes per row); with groups of 64 or 128 they share scale and bias
+    const int kb = kb0 + 2 * u;
+    const int gi = (2 * u) >> group_shift, gj = (2 * u + 1) >> group_shift;
+    const float s0 = aux_load(a0, aux, gi), s1 = aux_load(a1, aux, gi);
+    const float b0 = aux_load(a0 + apitch16, aux, gi), b1 = aux_load(a1 + apitch16, aux, gi);
+    const float bs = sm.isx[kb], bt = sm.isx[kb + 1];
+    blk_mlx<true>(p0 + u * 32, p1 + u * 32, s0 * bs, s1 * bs, b0 * bs, b1 * bs, xf0 + (size_t)kb * 64, sm.sx32[kb],
+                  0.f, t, acc);
+    if (gj == gi) {
+      blk_mlx<true>(p0 + u * 32 + 16, p1 + u * 32 + 16, s0 * bt, s1 * bt, b0 * bt, b1 * bt,
+                    xf0 + (size_t)(kb + 1) * 64, sm.sx32[kb + 1], 0.f, t, acc);
+    } else {
+      blk_mlx<true>(p0 + u * 32 + 16, p1 + u * 32 + 16, aux_load(a0, aux, gj) * bt, aux_load(a1, aux, gj) * bt,
+                    aux_load(a0 + apitch16, aux, gj) * bt, aux_load(a1 + apitch16, aux, gj) * bt,
+                    xf0 + (size_t)(kb + 1) * 64, sm.sx32[kb + 1], 0.f, t, acc);
+    }
   } else {
     // Q6_K quarter: superblock u / 4 of the chunk, half n, sub-block s
     const int sb = u >> 2, n = (u >> 1) & 1, s = u & 1;
@@ -1082,7 +1092,7 @@ __device__ __forceinline__ void run_phase(const MegaArgs& a, const Smem& sm, Wal
   if (MK_OPT_LOCAL && (enc == E_Q4_0 || enc == E_Q4_1 || enc == E_Q8_0 || enc == E_MLX_U4)) {
     float* mine = sm.misc + MK_OFF_RED + 32 + (w.nlocal & 1u) * MK_CW;  // consecutive per-warp stages alternate
     w.nlocal++;
-    stage_local(src, nw, nw_type, n_in, (enc == E_Q4_0 || enc == E_Q8_0) ? 2 : 1, xl_for_encoding(enc), sm, mine + warp,
+    stage_local(src, nw, nw_type, n_in, (enc == E_Q4_0 || enc == E_Q8_0 || enc == E_MLX_U4) ? 2 : 1, xl_for_encoding(enc), sm, mine + warp,
                 lane, warp);
     if (nw) ssq = mine;
   } else {
@@ -1098,6 +1108,8 @@ __device__ __forceinline__ void run_phase(const MegaArgs& a, const Smem& sm, Wal
 #if !defined(MK_SIZE_PROBE) || MK_SIZE_PROBE < 2
   else if (enc == E_Q6_K)
     run_phase_t<E_Q6_K>(a, sm, w, nr, ep, ssq, n_in, res, hid_lo, tid, lane, warp, prof, sid);
+  else if (enc == E_MLX_U4)  // MLX models: every layer product is of this kind
+    run_phase_t<E_MLX_U4>(a, sm, w, nr, ep, ssq, n_in, res, hid_lo, tid, lane, warp, prof, sid);
 #endif
 #ifndef MK_SIZE_PROBE
   else
@@ -1386,7 +1398,7 @@ HostPlan host_plan(const WRef& w) {
     case E_Q4_0: p.ubytes = 36, p.ukb = 2, p.units_total = K / 64; break;
     case E_Q4_1: p.ubytes = 20, p.ukb = 1, p.units_total = K / 32; break;
     case E_Q8_0: p.ubytes = 68, p.ukb = 2, p.units_total = K / 64; break;
-    case E_MLX_U4: p.ubytes = 16, p.ukb = 1, p.units_total = K / 32; break;
+    case E_MLX_U4: p.ubytes = 32, p.ukb = 2, p.units_total = K / 64; break;
     case E_BF16:
     case E_F16: p.ubytes = 64, p.ukb = 1, p.units_total = K / 32; break;
     default: p.ubytes = 0, p.ukb = 2, p.units_total = K / 64, p.unit_q6 = 1; break;  // quarters
@@ -1406,7 +1418,7 @@ void add_tile_chunks(const WRef& w, int64_t r, int n, int acc, std::vector<MegaC
   int su = p.units_total < 16 ? p.units_total : 16;
   for (int cand = 16; cand <= p.units_total && cand <= 240; cand += 16) {
     const int pitch = host_bank_pitch(seg_bytes(p, cand) + 20);
-    const int ap = w.enc == E_MLX_U4 ? ((cand * 32 / w.group) * ael + 31) / 16 * 16 : 0;
+    const int ap = w.enc == E_MLX_U4 ? ((cand * p.ukb * 32 / w.group) * ael + 31) / 16 * 16 : 0;
     const size_t need = ap ? (size_t)16 * pitch + 32 * (size_t)ap : (size_t)n * pitch;
     if (need <= (size_t)MK_SLOT && pitch < 65536) su = cand;
   }
@@ -1437,12 +1449,12 @@ void add_tile_chunks(const WRef& w, int64_t r, int n, int acc, std::vector<MegaC
       c.contig = (uint32_t)((c.al + (size_t)n * c.rb + 15) / 16 * 16);
     }
     if (w.enc == E_MLX_U4) {
-      const int64_t arow = (int64_t)(w.cols / w.group) * ael, ao = (int64_t)(u0 * 32 / w.group) * ael;
+      const int64_t arow = (int64_t)(w.cols / w.group) * ael, ao = (int64_t)(u0 * p.ukb * 32 / w.group) * ael;
       c.sc = w.scales + r * arow + ao;
       c.bi = w.biases + r * arow + ao;
       c.arb = (uint32_t)arow;
-      c.aseg = (uint16_t)((nu * 32 / w.group) * ael);
-      c.apitch = (uint16_t)(((su * 32 / w.group) * ael + 31) / 16 * 16);
+      c.aseg = (uint16_t)((nu * p.ukb * 32 / w.group) * ael);
+      c.apitch = (uint16_t)(((su * p.ukb * 32 / w.group) * ael + 31) / 16 * 16);
       c.aal = (uint8_t)(reinterpret_cast<uintptr_t>(c.sc) & 15);
       c.aal_step = (uint8_t)(c.arb & 15u);
       for (int i = 0; i < n; i++) c.tx += 2u * (((((uint32_t)c.aal + (uint32_t)i * c.aal_step) & 15u) + c.aseg + 15u) & ~15u);

@@ -61,6 +61,7 @@ struct FaArgs {
   const void* vcache;
   float* ctx;         // [rows, nh * d]
   int64_t rows, nh, nkv, cap, base_pos, seq;
+  int64_t ldq;        // floats between consecutive rows of q
 };
 
 template <int KV>
@@ -84,8 +85,8 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const FaArgs a) 
   // Q fragments (hi, lo) for the 8 k-steps over the head dim
   uint32_t qh[8][4], ql[8][4];
   {
-    const float* q0 = a.q + (r0c * a.nh + h) * FA_D;
-    const float* q1 = a.q + (r1c * a.nh + h) * FA_D;
+    const float* q0 = a.q + r0c * a.ldq + h * FA_D;
+    const float* q1 = a.q + r1c * a.ldq + h * FA_D;
 #pragma unroll
     for (int kk = 0; kk < 8; kk++) {
       const float2 a0 = *reinterpret_cast<const float2*>(q0 + 16 * kk + 2 * t);
@@ -224,6 +225,7 @@ int launch_attention_prefill(const AttnArgs& a, int64_t base_pos, int64_t seq, c
   FaArgs f;
   f.q = a.q, f.kcache = a.kcache, f.vcache = a.vcache, f.ctx = a.ctx;
   f.rows = a.rows, f.nh = a.nh, f.nkv = a.nkv, f.cap = a.cap, f.base_pos = base_pos, f.seq = seq;
+  f.ldq = a.ldq ? a.ldq : a.nh * FA_D;
   const dim3 grid((unsigned)a.nh, (unsigned)((a.rows + FA_BR - 1) / FA_BR));
   if (a.kv_type == E_BF16)
     attention_prefill_kernel<E_BF16><<<grid, 128, 0, s>>>(f);

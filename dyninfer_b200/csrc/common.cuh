@@ -226,6 +226,7 @@ int launch_rms_norm(const float* x, const void* w, int w_type, int64_t rows, int
 int launch_rope(float* x, int64_t s_rows, int64_t heads, int64_t d, int64_t start_pos,
                 const FreqTable& ft, cudaStream_t s);
 int launch_silu_mul(const float* gate, const float* up, int64_t n, float* y, cudaStream_t s);
+int launch_silu_mul_rows(const float* gate_up, int64_t rows, int64_t inter, float* y, cudaStream_t s);
 
 struct QkvPrepArgs {
   float* q;        // [rows, nh, d]   normalised + rotated in place
@@ -242,6 +243,9 @@ struct QkvPrepArgs {
   int64_t rows, nh, nkv, d, cap;
   int kv_type, has_norm, has_rope;
   float eps;
+  // floats between consecutive rows of q / k / v (0: dense, nh*d / nkv*d): the three may be column
+  // ranges of one [rows, nh*d + 2*nkv*d] matrix, the output of the fused [q; k; v] product
+  int64_t ldq = 0, ldk = 0, ldv = 0;
 };
 int launch_qkv_prepare(const QkvPrepArgs& a, const FreqTable& ft, cudaStream_t s);
 
@@ -258,6 +262,7 @@ struct AttnArgs {
   // >= 0: the rows are consecutive positions uniform_base + row of sequence uniform_seq even though
   // row_pos / row_seq are given (prefill chunks); lets the tensor-core prefill kernel take them
   int64_t uniform_base = -1, uniform_seq = 0;
+  int64_t ldq = 0;  // floats between consecutive rows of q (0: dense, nh*d)
 };
 int launch_attention(const AttnArgs& a, cudaStream_t s);
 size_t attention_split_scratch_bytes(int64_t rows, int64_t nh, int64_t d, int nsplit);

@@ -140,6 +140,29 @@ __global__ void silu_mul_kernel(const float* __restrict__ g, const float* __rest
   }
 }
 
+// y[r, i] = silu(gu[r, i]) * gu[r, I + i] for the rows of a fused [gate; up] product ([rows, 2 I])
+__global__ void silu_mul_rows_kernel(const float* __restrict__ gu, int64_t rows, int64_t I, float* __restrict__ y) {
+  pdl_trigger();
+  const int64_t n = rows * I;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / I, c = i - r * I;
+    const float gv = gu[r * 2 * I + c];
+    y[i] = (gv / (1.0f + expf(-gv))) * gu[r * 2 * I + I + c];
+  }
+}
+
+int launch_silu_mul_rows(const float* gu, int64_t rows, int64_t I, float* y, cudaStream_t s) {
+  if (rows * I == 0) return 0;
+  int64_t blocks = (rows * I + 255) / 256;
+  const int64_t cap = (int64_t)std::max(1, sm_count()) * 8;
+  if (blocks > cap) blocks = cap;
+  silu_mul_rows_kernel<<<(unsigned)blocks, 256, 0, s>>>(gu, rows, I, y);
+  count_launch();
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
 int launch_silu_mul(const float* gate, const float* up, int64_t n, float* y, cudaStream_t s) {
   if (n == 0) return 0;
   int64_t blocks = (n + 255) / 256;
@@ -187,13 +210,13 @@ __global__ void __launch_bounds__(128) qkv_prepare_kernel(QkvPrepArgs a, FreqTab
   const int kind = hh < a.nh ? 0 : (hh < a.nh + a.nkv ? 1 : 2);
   const int64_t head = kind == 0 ? hh : (kind == 1 ? hh - a.nh : hh - a.nh - a.nkv);
   if (kind == 2) {
-    const float* src = a.v + (r * a.nkv + head) * d;
+    const float* src = a.v + r * (a.ldv ? a.ldv : a.nkv * d) + head * d;
     T* dst = reinterpret_cast<T*>(a.vcache) + ((seq * a.nkv + head) * a.cap + pos) * d;
     for (int64_t i = threadIdx.x; i < d; i += blockDim.x) dst[i] = KvT<KV>::enc(src[i]);
     return;
   }
-  float* qv = a.q + (r * a.nh + head) * d;
-  const float* src = kind == 0 ? qv : a.k + (r * a.nkv + head) * d;
+  float* qv = a.q + r * (a.ldq ? a.ldq : a.nh * d) + head * d;
+  const float* src = kind == 0 ? qv : a.k + r * (a.ldk ? a.ldk : a.nkv * d) + head * d;
   const void* nw = kind == 0 ? a.q_norm_w : a.k_norm_w;
   float inv = 1.f;
   if (a.has_norm) {
@@ -261,7 +284,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_kernel(AttnArgs a) {
   const int64_t pos = a.row_pos ? a.row_pos[r] : a.base_pos + r;
   const int64_t seq = a.row_seq ? a.row_seq[r] : 0;
   const float scale = 1.0f / sqrtf((float)d);
-  const float* qv = a.q + (r * a.nh + h) * d;
+  const float* qv = a.q + r * (a.ldq ? a.ldq : a.nh * d) + h * d;
   const T* kb = reinterpret_cast<const T*>(a.kcache) + (seq * a.nkv + kvh) * a.cap * d;
   const T* vb = reinterpret_cast<const T*>(a.vcache) + (seq * a.nkv + kvh) * a.cap * d;
   float qreg[ATT_DPL], acc[ATT_DPL];
@@ -342,7 +365,7 @@ attention_split_kernel(AttnArgs a, float* __restrict__ part, int nsplit) {
   float qreg[DPL], acc[DPL];
 #pragma unroll
   for (int j = 0; j < DPL; j++) {
-    qreg[j] = live ? a.q[(r * a.nh + h) * d + e0 + j] : 0.f;
+    qreg[j] = live ? a.q[r * (a.ldq ? a.ldq : a.nh * d) + h * d + e0 + j] : 0.f;
     acc[j] = 0.f;
   }
   struct __align__(sizeof(T) * DPL) Row {  // one vector load per lane and cached row

@@ -78,7 +78,7 @@ struct dyninfer_cuda_session_t {
   int64_t max_rows = 0;
   float *hidden = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ctx = nullptr,
         *act = nullptr, *up = nullptr, *logits = nullptr;
-  float *qkv1 = nullptr, *gu1 = nullptr;  // one row of [q | k | v] and of [gate | up] for the fused products
+  float *qkv1 = nullptr, *gu1 = nullptr;  // rows of [q | k | v] and of [gate | up] for the fused products
   int64_t *tokens_dev = nullptr, *row_pos_dev = nullptr, *row_seq_dev = nullptr,
           *out_token_dev = nullptr, *hist_dev = nullptr, *hist_count_dev = nullptr;
   size_t hist_cap = 0;
@@ -348,12 +348,16 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
     if (!normed &&
         launch_rms_norm(s->hidden, L.attn_norm.ptr, L.attn_norm.type, rows, H, c.eps, s->xn, st))
       return 1;
-    // one row: matrices laid back to back in the arena are one product into [q | k | v]
+    // matrices laid back to back in the arena are one product into rows of [q | k | v] (or of
+    // [q | k], v apart): one activation pass and one launch instead of three
     float *qp = s->q, *kp = s->k, *vp = s->v;
-    if (rows == 1 && L.qkv_parts >= 2) {
-      qp = s->qkv1, kp = qp + qd, vp = kp + kvd;
-      if (launch_linear(L.qkv, s->xn, E_F32, 1, qp, nullptr, st)) return 1;
-      if (L.qkv_parts == 2 && launch_linear(L.v, s->xn, E_F32, 1, vp, nullptr, st)) return 1;
+    int64_t ldq = 0, ldk = 0, ldv = 0;
+    if (L.qkv_parts >= 2) {
+      qp = s->qkv1, kp = qp + qd;
+      ldq = ldk = L.qkv_parts == 3 ? qd + 2 * kvd : qd + kvd;
+      if (launch_linear(L.qkv, s->xn, E_F32, rows, qp, nullptr, st)) return 1;
+      if (L.qkv_parts == 3) vp = kp + kvd, ldv = ldq;
+      else if (launch_linear(L.v, s->xn, E_F32, rows, vp, nullptr, st)) return 1;
     } else {
       if (launch_linear(L.q, s->xn, E_F32, rows, qp, nullptr, st)) return 1;
       if (launch_linear(L.k, s->xn, E_F32, rows, kp, nullptr, st)) return 1;
@@ -368,6 +372,7 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
     pa.rows = rows, pa.nh = c.heads, pa.nkv = c.kv_heads, pa.d = c.head_dim, pa.cap = cap;
     pa.kv_type = s->kv_type, pa.has_norm = c.qk_norm ? 1 : 0, pa.has_rope = c.rope ? 1 : 0;
     pa.eps = c.eps;
+    pa.ldq = ldq, pa.ldk = ldk, pa.ldv = ldv;
     if (launch_qkv_prepare(pa, s->freq, st)) return 1;
     AttnArgs aa{};
     aa.q = qp, aa.kcache = pa.kcache, aa.vcache = pa.vcache;
@@ -375,6 +380,7 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
     aa.ctx = s->ctx;
     aa.rows = rows, aa.nh = c.heads, aa.nkv = c.kv_heads, aa.d = c.head_dim, aa.cap = cap;
     aa.kv_type = s->kv_type;
+    aa.ldq = ldq;
     aa.uniform_base = chunk_start, aa.uniform_seq = chunk_slot;  // a prefill chunk: consecutive positions
     if (launch_attention(aa, st)) return 1;
     bool ffn_normed = false;
@@ -389,10 +395,10 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
     const bool fast_gemv = (rows == 1 && gemv_cs_workspace_bytes(L.gate, 1) && gemv_cs_workspace_bytes(L.up, 1)) ||
                            (rows <= 4 && gemv_mma_workspace_bytes(L.gate, E_F32, (int)rows) &&
                             gemv_mma_workspace_bytes(L.up, E_F32, (int)rows));
-    if (rows == 1 && L.gate_up.data && gemv_cs_workspace_bytes(L.gate_up, 1)) {
-      // [gate; up] as one product, then the activation
-      if (launch_linear(L.gate_up, s->xn, E_F32, 1, s->gu1, nullptr, st)) return 1;
-      if (launch_silu_mul(s->gu1, s->gu1 + c.inter, c.inter, s->act, st)) return 1;
+    if (L.gate_up.data && (rows == 1 ? gemv_cs_workspace_bytes(L.gate_up, 1) != 0 : rows > 4 || fast_gemv)) {
+      // [gate; up] as one product into rows of [gate | up], then the activation
+      if (launch_linear(L.gate_up, s->xn, E_F32, rows, s->gu1, nullptr, st)) return 1;
+      if (launch_silu_mul_rows(s->gu1, rows, c.inter, s->act, st)) return 1;
     } else if (L.gate.enc == L.up.enc && rows <= 4 && !fast_gemv) {
       if (launch_linear_swiglu(L.gate, L.up, s->xn, rows, s->act, st)) return 1;
     } else {
@@ -1051,7 +1057,7 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
   cudaSetDevice(s->device);
   if (s->stream) cudaStreamSynchronize(s->stream);
   destroy_graphs(s);
-  void* dev[] = {s->arena, s->kcache, s->vcache, s->hidden, s->xn, s->q, s->k, s->v, s->ctx, s->act, s->up,
+  void* dev[] = {s->arena, s->kcache, s->vcache, s->hidden, s->xn, s->ctx, s->act,
                  s->logits, s->tokens_dev, s->row_pos_dev, s->row_seq_dev, s->out_token_dev,
                  s->hist_dev, s->hist_count_dev, s->argmax_scratch, s->mega_layers, s->io_dev,
                  s->prof_dev, s->trace_dev, s->prog_dev, s->ll_dev, s->batch_logits, s->batch_tokens_dev, s->tp_part, s->tp_logits,
@@ -1106,20 +1112,19 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
   if (!s->kv_configured) {
     if (dev_alloc(s, (void**)&s->hidden, (size_t)rows * c.hidden * 4) ||
         dev_alloc(s, (void**)&s->xn, (size_t)rows * c.hidden * 4) ||
-        dev_alloc(s, (void**)&s->q, (size_t)rows * qd * 4) ||
-        dev_alloc(s, (void**)&s->k, (size_t)rows * kvd * 4) ||
-        dev_alloc(s, (void**)&s->v, (size_t)rows * kvd * 4) ||
         dev_alloc(s, (void**)&s->ctx, (size_t)rows * qd * 4) ||
         dev_alloc(s, (void**)&s->act, (size_t)rows * c.inter * 4) ||
-        dev_alloc(s, (void**)&s->up, (size_t)rows * c.inter * 4) ||
-        dev_alloc(s, (void**)&s->qkv1, (size_t)(qd + 2 * kvd) * 4) ||
-        dev_alloc(s, (void**)&s->gu1, (size_t)2 * c.inter * 4) ||
+        dev_alloc(s, (void**)&s->qkv1, (size_t)rows * (qd + 2 * kvd) * 4) ||
+        dev_alloc(s, (void**)&s->gu1, (size_t)rows * 2 * c.inter * 4) ||
         (c.tp_world > 1 && dev_alloc(s, (void**)&s->tp_part, (size_t)rows * c.hidden * 4)) ||
         dev_alloc(s, (void**)&s->tokens_dev, (size_t)rows * 8) ||
         dev_alloc(s, (void**)&s->row_pos_dev, (size_t)rows * 8) ||
         dev_alloc(s, (void**)&s->row_seq_dev, (size_t)rows * 8) ||
         host_alloc(s, (void**)&s->stage_host, (size_t)(8 + 3 * rows) * 8))
       return 1;
+    // the separate-product path writes dense q, k, v and `up` into the same buffers
+    s->q = s->qkv1, s->k = s->q + rows * qd, s->v = s->k + rows * kvd;
+    s->up = s->gu1;
     s->max_rows = rows;
   } else {
     DYN_CHECK(rows <= s->max_rows, "chunk_size %zu exceeds the scratch sized at first configuration",

@@ -3,8 +3,9 @@
 //
 // One CTA computes a 128 (weight rows) x BN (activation rows, <= 256) tile of y^T:
 //   * warps 0..15 dequantise (four groups of four, one pipeline stage each): for every 64-wide K chunk they decode the raw checkpoint blocks of
-//     the tile's 128 rows with the exact decoders of codec.cuh (lanes along K, so a row's bytes
-//     are read contiguously), round to f16 and store them as the A operand in the canonical
+//     the tile's 128 rows (Q4_0, Q4_1, Q8_0, Q6_K and MLX-U4 with word fetches issued a step ahead and
+//     packed f16 / f32 arithmetic that rounds like the decoders of codec.cuh; the other encodings
+//     through those decoders), round to f16 and store them as the A operand in the canonical
 //     K-major 128-byte-swizzled layout (8-row groups of 1024 bytes, 16-byte chunk c of row r at
 //     position c ^ (r & 7));
 //   * one thread of warp 16 fetches the matching activation chunk (f16, prepared once per call) as the
@@ -144,6 +145,50 @@ struct ChunkItems {
     }
   }
 };
+
+// The A producers' chunk loop for the encodings below: group `grp` converts chunks grp, grp + 4, ...
+// Each chunk is converted in SUB steps; the raw words of the next step (of the group's next chunk
+// after the last one) are fetched before the current step is converted, so global loads stay in
+// flight during the conversion and while the group waits for its stage to drain. fetch(kc, sub, buf)
+// loads, convert(kc, sub, buf, abase) stores the step's f16 weights into the stage.
+template <int NR, int SUB, class Fetch, class Convert>
+__device__ __forceinline__ void tg_produce_chunks(int grp, int nk, int nslot, uint8_t* smem, uint32_t stage_bytes,
+                                                  uint64_t* empty_bar, uint64_t* full_bar, int* s_abort, int lane,
+                                                  Fetch fetch, Convert convert) {
+  constexpr int U = SUB == 1 ? 2 : 1;  // chunks per loop body, so that the buffer index is static
+  static_assert(SUB == 1 || SUB % 2 == 0, "steps per chunk: one or an even number");
+  uint32_t buf[2][NR];
+  if (grp < nk) fetch(grp, 0, buf[0]);
+  bool live = true;
+  for (int kc0 = grp; kc0 < nk && live; kc0 += U * TG_GROUPS) {
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int kc = kc0 + u * TG_GROUPS;
+      if (kc >= nk) break;
+      const int slot = kc % nslot;
+      uint8_t* abase = smem + (size_t)slot * stage_bytes;
+#pragma unroll
+      for (int sub = 0; sub < SUB; sub++) {
+        const int b = (u * SUB + sub) & 1;
+        if (sub + 1 < SUB)
+          fetch(kc, sub + 1, buf[b ^ 1]);
+        else if (kc + TG_GROUPS < nk)
+          fetch(kc + TG_GROUPS, 0, buf[b ^ 1]);
+        if (sub == 0 && kc >= nslot &&
+            !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / nslot - 1) & 1u, TG_SPINS, s_abort)) {
+          if (!*s_abort) *s_abort = 1;
+          live = false;
+          break;
+        }
+        convert(kc, sub, buf[b], abase);
+      }
+      if (!live) break;
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_bar + slot);
+    }
+  }
+}
 
 template <int ENC>
 __global__ void __launch_bounds__(TG_THREADS, 1)
@@ -347,6 +392,171 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
           if (lane == 0) mbar_arrive(full_bar + slot);
         }
       }
+    } else if constexpr (ENC == E_Q8_0) {
+      // Q8_0: a row's chunk is two 34-byte blocks = 17 aligned words (rows are multiples of 68 bytes).
+      // Lane = (row sub-index, piece l8 of 8 weights): the lanes of a row fetch words 2 l8 and 2 l8 + 1
+      // (lane 7 also word 16) and pass the neighbour's first word on by shuffle. Block 0 keeps its scale
+      // in the low half of word 0 and its quants from byte 2, block 1 its scale in the high half of
+      // word 8 and its quants from word 9. int8 -> f16: byte ^ 0x80 under 0x64 is 1024 + 128 + q;
+      // subtracting 1152 is exact and the product with d rounds once, like rounding the f32 value.
+      constexpr int NJ = TG_BM / (TG_GWARPS * 4);
+      const int l8 = lane & 7, rsub = lane >> 3, base8 = lane & ~7, blk2 = l8 >> 2;
+      const int64_t rw = a.w.row_bytes() / 4;
+      const uint32_t* roww[NJ];
+#pragma unroll
+      for (int j = 0; j < NJ; j++) {
+        int64_t row = n0 + wg * 4 + rsub + 16 * j;
+        if (row > N - 1) row = N - 1;
+        roww[j] = reinterpret_cast<const uint32_t*>(a.w.data) + row * rw + 2 * l8;
+      }
+      const __half2 c1152 = __floats2half2_rn(1152.f, 1152.f);
+      auto fetch = [&](int kc, int, uint32_t (&q)[3 * NJ]) {
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+          const uint32_t* p = roww[j] + (int64_t)(kbase + kc) * 17;
+          q[3 * j] = p[0];
+          q[3 * j + 1] = p[1];
+          q[3 * j + 2] = l8 == 7 ? p[2] : 0u;
+        }
+      };
+      auto convert = [&](int, int, uint32_t (&q)[3 * NJ], uint8_t* abase) {
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+          const int r = wg * 4 + rsub + 16 * j;
+          const uint32_t wa = q[3 * j], wb = q[3 * j + 1];
+          const uint32_t nx = __shfl_sync(0xffffffffu, wa, base8 + ((l8 + 1) & 7));
+          const uint32_t dw = __shfl_sync(0xffffffffu, wa, base8 + (blk2 ? 4 : 0));
+          const uint32_t nxt = l8 == 7 ? q[3 * j + 2] : nx;
+          const uint32_t lo = (blk2 ? wb : __funnelshift_r(wa, wb, 16)) ^ 0x80808080u;
+          const uint32_t hi = (blk2 ? nxt : __funnelshift_r(wb, nx, 16)) ^ 0x80808080u;
+          const __half dh = __ushort_as_half((unsigned short)(blk2 ? dw >> 16 : dw & 0xffffu));
+          const __half2 d2 = __halves2half2(dh, dh);
+          uint32_t pr[4] = {__byte_perm(lo, 0x64646464u, 0x4140), __byte_perm(lo, 0x64646464u, 0x4342),
+                            __byte_perm(hi, 0x64646464u, 0x4140), __byte_perm(hi, 0x64646464u, 0x4342)};
+          uint4 out;
+          uint32_t* o = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const __half2 v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&pr[e]), c1152), d2);
+            o[e] = *reinterpret_cast<const uint32_t*>(&v);
+          }
+          *reinterpret_cast<uint4*>(abase + r * 128 + ((l8 ^ (r & 7)) << 4)) = out;
+        }
+      };
+      tg_produce_chunks<3 * NJ, 1>(grp, nk, nslot, smem, stage_bytes, empty_bar, full_bar, &s_abort, lane, fetch, convert);
+    } else if constexpr (ENC == E_Q4_1) {
+      // Q4_1: a row's chunk is two 20-byte blocks = 10 aligned words; word 0 of a block is (d, m), words
+      // 1..4 its quants. Lane = (row sub-index, block, quarter t): one quant word + the (d, m) word -> the
+      // weights 4t..4t+3 (low nibbles) and 16+4t..16+4t+3 (high nibbles). nibble | 0x6400 = 1024 + q or
+      // 1024 + 16 q; both reduce to q exactly, and the f16 fused multiply-add q * d + m rounds once.
+      constexpr int NJ = TG_BM / (TG_GWARPS * 4);
+      const int blk2 = (lane >> 2) & 1, t = lane & 3, rsub = lane >> 3;
+      const int64_t rw = a.w.row_bytes() / 4;
+      const uint32_t* roww[NJ];
+#pragma unroll
+      for (int j = 0; j < NJ; j++) {
+        int64_t row = n0 + wg * 4 + rsub + 16 * j;
+        if (row > N - 1) row = N - 1;
+        roww[j] = reinterpret_cast<const uint32_t*>(a.w.data) + row * rw + blk2 * 5;
+      }
+      const __half2 c1024 = __floats2half2_rn(1024.f, 1024.f), c64n = __floats2half2_rn(-64.f, -64.f);
+      const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
+      auto fetch = [&](int kc, int, uint32_t (&q)[2 * NJ]) {
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+          const uint32_t* p = roww[j] + (int64_t)(kbase + kc) * 10;
+          q[2 * j] = p[1 + t];
+          q[2 * j + 1] = p[0];
+        }
+      };
+      auto convert = [&](int, int, uint32_t (&q)[2 * NJ], uint8_t* abase) {
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+          const int r = wg * 4 + rsub + 16 * j;
+          const uint32_t w = q[2 * j], dm = q[2 * j + 1];
+          const __half dh = __ushort_as_half((unsigned short)(dm & 0xffffu));
+          const __half mh = __ushort_as_half((unsigned short)(dm >> 16));
+          const __half2 d2 = __halves2half2(dh, dh), m2 = __halves2half2(mh, mh);
+          uint32_t l02 = (w & 0x000F000Fu) | 0x64006400u, l13 = ((w >> 8) & 0x000F000Fu) | 0x64006400u;
+          uint32_t h02 = (w & 0x00F000F0u) | 0x64006400u, h13 = ((w >> 8) & 0x00F000F0u) | 0x64006400u;
+          __half2 v;
+          v = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&l02), c1024), d2, m2);
+          l02 = *reinterpret_cast<uint32_t*>(&v);
+          v = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&l13), c1024), d2, m2);
+          l13 = *reinterpret_cast<uint32_t*>(&v);
+          v = __hfma2(__hfma2(*reinterpret_cast<__half2*>(&h02), c16th, c64n), d2, m2);
+          h02 = *reinterpret_cast<uint32_t*>(&v);
+          v = __hfma2(__hfma2(*reinterpret_cast<__half2*>(&h13), c16th, c64n), d2, m2);
+          h13 = *reinterpret_cast<uint32_t*>(&v);
+          const uint2 lo = make_uint2(__byte_perm(l02, l13, 0x5410), __byte_perm(l02, l13, 0x7632));
+          const uint2 hi = make_uint2(__byte_perm(h02, h13, 0x5410), __byte_perm(h02, h13, 0x7632));
+          const int klo = blk2 * 32 + 4 * t, khi = klo + 16;
+          uint8_t* rowbase = abase + r * 128;
+          *reinterpret_cast<uint2*>(rowbase + (((klo >> 3) ^ (r & 7)) << 4) + (klo & 7) * 2) = lo;
+          *reinterpret_cast<uint2*>(rowbase + (((khi >> 3) ^ (r & 7)) << 4) + (khi & 7) * 2) = hi;
+        }
+      };
+      tg_produce_chunks<2 * NJ, 1>(grp, nk, nslot, smem, stage_bytes, empty_bar, full_bar, &s_abort, lane, fetch, convert);
+    } else if constexpr (ENC == E_Q6_K) {
+      // Q6_K: a 64-wide chunk is one quarter (n, h) of a 210-byte block: nibble h of ql bytes
+      // 64 n .. 64 n + 63 and bit field 2 h + p of qh bytes 32 n .. 32 n + 31 (p = 0: the chunk's first 32
+      // weights, p = 1: the last 32). Lane = (row sub-index, j4): 4 ql bytes at 4 j4 and at 32 + 4 j4,
+      // 4 qh bytes, the two sub-block scales and d -> weights 4 j4..+3 and 32 + 4 j4..+3. Blocks are only
+      // 2-byte aligned, so every word is fetched as two halves. A chunk is converted two rows at a
+      // time. q - 32 is made exact in f32 (byte under 0x4B000000 = 2^23 + q) and multiplied by the exact
+      // f32 product scale * d: one f32 rounding of (q - 32) * scale * d, the value the decoder defines.
+      constexpr int NJ = TG_BM / (TG_GWARPS * 4), RB = 2, SUB = NJ / RB;
+      const int j4 = lane & 7, rsub = lane >> 3;
+      const int64_t rb = a.w.row_bytes();
+      auto row_of = [&](int j) {
+        int64_t row = n0 + wg * 4 + rsub + 16 * j;
+        return row > N - 1 ? N - 1 : row;
+      };
+      auto fetch = [&](int kc, int sub, uint32_t (&q)[9 * RB]) {
+        const int64_t k0 = (int64_t)(kbase + kc) * TG_BK;
+        const int64_t blk = k0 >> 8;
+        const int n = (int)(k0 >> 7) & 1, h = (int)(k0 >> 6) & 1;
+#pragma unroll
+        for (int i = 0; i < RB; i++) {
+          const uint8_t* b = a.w.data + row_of(sub * RB + i) * rb + blk * 210;
+          const unsigned short* ql = reinterpret_cast<const unsigned short*>(b + n * 64 + 4 * j4);
+          const unsigned short* qh = reinterpret_cast<const unsigned short*>(b + 128 + n * 32 + 4 * j4);
+          const uint8_t* sc = b + 192 + n * 8 + h * 4 + (j4 >> 2);
+          q[9 * i] = ql[0], q[9 * i + 1] = ql[1];
+          q[9 * i + 2] = ql[16], q[9 * i + 3] = ql[17];
+          q[9 * i + 4] = qh[0], q[9 * i + 5] = qh[1];
+          q[9 * i + 6] = sc[0], q[9 * i + 7] = sc[2];
+          q[9 * i + 8] = *reinterpret_cast<const unsigned short*>(b + 208);
+        }
+      };
+      auto convert = [&](int kc, int sub, uint32_t (&q)[9 * RB], uint8_t* abase) {
+        const int h = (kbase + kc) & 1;
+#pragma unroll
+        for (int i = 0; i < RB; i++) {
+          const int r = wg * 4 + rsub + 16 * (sub * RB + i);
+          const uint32_t ql0 = q[9 * i] | (q[9 * i + 1] << 16), ql1 = q[9 * i + 2] | (q[9 * i + 3] << 16);
+          const uint32_t qh = (q[9 * i + 4] | (q[9 * i + 5] << 16)) >> (4 * h);
+          const float d = __half2float(__ushort_as_half((unsigned short)q[9 * i + 8]));
+          const float sd0 = __fmul_rn((float)(int)(int8_t)q[9 * i + 6], d);
+          const float sd1 = __fmul_rn((float)(int)(int8_t)q[9 * i + 7], d);
+          const uint32_t v0 = ((ql0 >> (4 * h)) & 0x0F0F0F0Fu) | ((qh & 0x03030303u) << 4);
+          const uint32_t v1 = ((ql1 >> (4 * h)) & 0x0F0F0F0Fu) | (((qh >> 2) & 0x03030303u) << 4);
+          auto four = [&](uint32_t v, float sd) {
+            float f[4];
+            f[0] = __fmul_rn(__uint_as_float(__byte_perm(v, 0x4B000000u, 0x7440)) - 8388640.f, sd);
+            f[1] = __fmul_rn(__uint_as_float(__byte_perm(v, 0x4B000000u, 0x7441)) - 8388640.f, sd);
+            f[2] = __fmul_rn(__uint_as_float(__byte_perm(v, 0x4B000000u, 0x7442)) - 8388640.f, sd);
+            f[3] = __fmul_rn(__uint_as_float(__byte_perm(v, 0x4B000000u, 0x7443)) - 8388640.f, sd);
+            const __half2 a01 = __floats2half2_rn(f[0], f[1]), a23 = __floats2half2_rn(f[2], f[3]);
+            return make_uint2(*reinterpret_cast<const uint32_t*>(&a01), *reinterpret_cast<const uint32_t*>(&a23));
+          };
+          const int klo = 4 * j4, khi = 32 + 4 * j4;
+          uint8_t* rowbase = abase + r * 128;
+          *reinterpret_cast<uint2*>(rowbase + (((klo >> 3) ^ (r & 7)) << 4) + (klo & 7) * 2) = four(v0, sd0);
+          *reinterpret_cast<uint2*>(rowbase + (((khi >> 3) ^ (r & 7)) << 4) + (khi & 7) * 2) = four(v1, sd1);
+        }
+      };
+      tg_produce_chunks<9 * RB, SUB>(grp, nk, nslot, smem, stage_bytes, empty_bar, full_bar, &s_abort, lane, fetch, convert);
     } else {
       constexpr int RPP = 32 / CI::IPR;  // rows per warp pass
       const int it = lane % CI::IPR, rsub = lane / CI::IPR;
@@ -477,6 +687,10 @@ bool tg_shape_ok(const WRef& w, int64_t M) {
     default: return false;
   }
   if (w.enc == E_MLX_U4 && (w.group < 8 || w.cols % w.group)) return false;
+  // the word-fetching producers read aligned 32-bit words (Q6_K: 16-bit halves)
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(w.data);
+  if ((w.enc == E_Q4_0 || w.enc == E_Q4_1 || w.enc == E_Q8_0 || w.enc == E_MLX_U4) && (addr & 3)) return false;
+  if (w.enc == E_Q6_K && (addr & 1)) return false;
   return M >= 1 && w.rows >= 1 && w.cols >= TG_BK && w.cols % ((w.enc == E_Q6_K || w.enc == E_Q4_K || w.enc == E_Q5_K) ? 256 : TG_BK) == 0;
 }
 

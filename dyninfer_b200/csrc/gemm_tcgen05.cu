@@ -2,18 +2,18 @@
 // and every product with many activation rows: y[m, n] = sum_k x[m, k] * w[n, k], f32 accumulate.
 //
 // One CTA computes a 128 (weight rows) x BN (activation rows, <= 256) tile of y^T:
-//   * warps 0..15 dequantise (four groups of four, one pipeline stage each): for every 64-wide K chunk they decode the raw checkpoint blocks of
+//   * sixteen warps dequantise (four groups of four, one pipeline stage each): for every 64-wide K chunk they decode the raw checkpoint blocks of
 //     the tile's 128 rows (Q4_0, Q4_1, Q8_0, Q6_K and MLX-U4 with word fetches issued a step ahead and
 //     packed f16 / f32 arithmetic that rounds like the decoders of codec.cuh; the other encodings
 //     through those decoders), round to f16 and store them as the A operand in the canonical
 //     K-major 128-byte-swizzled layout (8-row groups of 1024 bytes, 16-byte chunk c of row r at
 //     position c ^ (r & 7));
-//   * one thread of warp 16 fetches the matching activation chunk (f16, prepared once per call) as the
+//   * one thread of another warp fetches the matching activation chunk (f16, prepared once per call) as the
 //     B operand with a 2-D TMA tile copy (cp.async.bulk.tensor, hardware 128-byte swizzle);
-//   * one thread of warp 17 issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16, four per
+//   * one thread of a third issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16, four per
 //     chunk) with the accumulator in tensor memory, and releases each stage with tcgen05.commit;
-//   * warps 0..3 read the accumulator back with tcgen05.ld (lane = weight row) and write y with
-//     coalesced stores.
+//   * all warps (after their pipeline roles) read the accumulator back with tcgen05.ld (lane = weight row,
+//     a warp reads the lanes of its own SM partition) and write y with coalesced stores.
 // Stages hand over through mbarriers; every wait is bounded and reports through an error word, and
 // the tensor memory is always released before the CTA exits.
 //
@@ -36,7 +36,20 @@ constexpr int TG_BK = 64;           // K elements per stage: 128 bytes of f16 pe
 constexpr int TG_GROUPS = 4;         // producer groups; group g fills stage g with chunks g, g + 4, ...
 constexpr int TG_GWARPS = 4;         // warps per group
 constexpr int TG_A_WARPS = TG_GROUPS * TG_GWARPS, TG_B_WARPS = 1;
-constexpr int TG_THREADS = (TG_A_WARPS + TG_B_WARPS + 1) * 32;
+// Warp roles. A warp issues from the scheduler of SM partition (warp index mod 4). The MMA-issuing thread is
+// the pipeline's serial section, and next to four always-ready conversion warps it was given an issue slot
+// only every ~13 cycles (measured: ~750 cycles per chunk for ~60 instructions). So partition 1 holds one
+// conversion warp instead of four: warp 1 issues the MMAs, warp 5 the activation copies, warps 9 and 13
+// only wait at the final barrier; the sixteen conversion warps are the other warps of 0..19 (twenty warps
+// keep 96 registers per thread).
+constexpr int TG_MMA_WARP = 1, TG_B_WARP = 5;
+constexpr int TG_WARPS = 20;
+constexpr int TG_THREADS = TG_WARPS * 32;
+__host__ __device__ constexpr bool tg_converts(int warp) { return (warp & 3) != 1 || warp > 13; }
+__host__ __device__ constexpr int tg_conversion_index(int warp) { return warp - ((warp + 2) / 4 < 4 ? (warp + 2) / 4 : 4); }
+static_assert(TG_WARPS % 4 == 0, "the epilogue spreads column blocks over TG_WARPS / 4 warps per partition");
+static_assert(tg_conversion_index(TG_WARPS - 1) == TG_A_WARPS - 1 && tg_conversion_index(17) == 13 && tg_conversion_index(16) == 12,
+              "sixteen conversion warps");
 constexpr int TG_MAX_SLOTS = 2 * TG_GROUPS;  // a group owns one pipeline slot, or two when they fit
 constexpr int TG_A_BYTES = TG_BM * 128;
 constexpr long long TG_SPINS = 1LL << 24;
@@ -157,6 +170,7 @@ __device__ __forceinline__ void tg_produce_chunks(int grp, int nk, int nslot, ui
                                                   Fetch fetch, Convert convert) {
   constexpr int U = SUB == 1 ? 2 : 1;  // chunks per loop body, so that the buffer index is static
   static_assert(SUB == 1 || SUB % 2 == 0, "steps per chunk: one or an even number");
+  const int slot_shift = nslot == TG_GROUPS ? 2 : 3;
   uint32_t buf[2][NR];
   if (grp < nk) fetch(grp, 0, buf[0]);
   bool live = true;
@@ -165,7 +179,7 @@ __device__ __forceinline__ void tg_produce_chunks(int grp, int nk, int nslot, ui
     for (int u = 0; u < U; u++) {
       const int kc = kc0 + u * TG_GROUPS;
       if (kc >= nk) break;
-      const int slot = kc % nslot;
+      const int slot = (kc & (nslot - 1));
       uint8_t* abase = smem + (size_t)slot * stage_bytes;
 #pragma unroll
       for (int sub = 0; sub < SUB; sub++) {
@@ -175,7 +189,7 @@ __device__ __forceinline__ void tg_produce_chunks(int grp, int nk, int nslot, ui
         else if (kc + TG_GROUPS < nk)
           fetch(kc + TG_GROUPS, 0, buf[b ^ 1]);
         if (sub == 0 && kc >= nslot &&
-            !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / nslot - 1) & 1u, TG_SPINS, s_abort)) {
+            !mbar_wait_bounded(empty_bar + slot, (unsigned)((kc >> slot_shift) - 1) & 1u, TG_SPINS, s_abort)) {
           if (!*s_abort) *s_abort = 1;
           live = false;
           break;
@@ -195,9 +209,12 @@ __global__ void __launch_bounds__(TG_THREADS, 1)
 dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) uint8_t tg_smem[];
   __shared__ uint64_t full_bar[TG_MAX_SLOTS], empty_bar[TG_MAX_SLOTS], accum_bar;
-  const int nslot = a.nslot;  // TG_GROUPS or 2 * TG_GROUPS; chunk kc uses slot kc % nslot and belongs to group kc % TG_GROUPS
+  const int nslot = a.nslot;  // TG_GROUPS or 2 * TG_GROUPS (powers of two); chunk kc uses slot kc mod nslot and belongs to group kc mod TG_GROUPS
+  const int slot_shift = nslot == TG_GROUPS ? 2 : 3;
+  static_assert(TG_GROUPS == 4, "slot_shift assumes four or eight slots");
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
+  __shared__ float s_inv[256];  // inverse activation-row scales of this tile
   using C = Codec<ENC>;
   using CI = ChunkItems<ENC>;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -218,7 +235,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
     mbar_init(&accum_bar, 1);
     mbar_fence_init();
   }
-  if (warp == TG_A_WARPS + TG_B_WARPS) {  // the MMA warp owns the tensor memory allocation
+  if (warp == TG_MMA_WARP) {  // the MMA warp owns the tensor memory allocation
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
                  "r"((uint32_t)a.tmem_cols)
                  : "memory");
@@ -229,11 +246,12 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
   tc_fence_after();
   const uint32_t tmem_d = tmem_base_s;
 
-  if (warp < TG_A_WARPS) {
+  if (tg_converts(warp)) {
     // ---------------- A producers: dequantise 128 rows x 64 k per stage --------------------------
     // Four groups of four warps; group g produces chunks g, g + 4, ... into stage g, so the fixed
     // costs of a hand-over (proxy fence, barrier round trip) of up to four chunks overlap.
-    const int grp = warp / TG_GWARPS, wg = warp % TG_GWARPS;
+    const int pw = tg_conversion_index(warp);
+    const int grp = pw / TG_GWARPS, wg = pw % TG_GWARPS;
     if constexpr (ENC == E_Q4_0) {
       // Fast path. Lane = (row sub-index, block of the chunk, quarter t): 4 quant bytes + the block
       // scale -> 8 weights. The raw bytes of the group's next chunk are fetched before the current
@@ -279,9 +297,9 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
           const int kc = kc0 + u * TG_GROUPS;
           if (kc >= nk) break;
           if (kc + TG_GROUPS < nk) fetch(kc + TG_GROUPS, qa[u ^ 1], qb[u ^ 1]);
-          const int slot = kc % nslot;
+          const int slot = (kc & (nslot - 1));
           uint8_t* abase = smem + (size_t)slot * stage_bytes;
-          if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / nslot - 1) & 1u, TG_SPINS, &s_abort)) {
+          if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, (unsigned)((kc >> slot_shift) - 1) & 1u, TG_SPINS, &s_abort)) {
             if (!s_abort) s_abort = 1;
             live = false;
             break;
@@ -359,9 +377,9 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
           const int kc = kc0 + u * TG_GROUPS;
           if (kc >= nk) break;
           if (kc + TG_GROUPS < nk) fetch(kc + TG_GROUPS, qw[u ^ 1], ax[u ^ 1]);
-          const int slot = kc % nslot;
+          const int slot = (kc & (nslot - 1));
           uint8_t* abase = smem + (size_t)slot * stage_bytes;
-          if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / nslot - 1) & 1u, TG_SPINS, &s_abort)) {
+          if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, (unsigned)((kc >> slot_shift) - 1) & 1u, TG_SPINS, &s_abort)) {
             if (!s_abort) s_abort = 1;
             live = false;
             break;
@@ -561,9 +579,9 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
       constexpr int RPP = 32 / CI::IPR;  // rows per warp pass
       const int it = lane % CI::IPR, rsub = lane / CI::IPR;
       for (int kc = grp; kc < nk; kc += TG_GROUPS) {
-        const int slot = kc % nslot;
+        const int slot = (kc & (nslot - 1));
         uint8_t* abase = smem + (size_t)slot * stage_bytes;
-        if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / nslot - 1) & 1u, TG_SPINS, &s_abort)) {
+        if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, (unsigned)((kc >> slot_shift) - 1) & 1u, TG_SPINS, &s_abort)) {
           if (!s_abort) s_abort = 1;
           break;
         }
@@ -595,69 +613,106 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
         if (lane == 0) mbar_arrive(full_bar + slot);
       }
     }
-  } else if (warp < TG_A_WARPS + TG_B_WARPS) {
+  } else if (warp == TG_B_WARP) {
     // ---------------- B producer: one TMA tile (bn rows x 64 k, swizzled by the hardware) per stage -----
     if (lane == 0) {
+      int slot = 0;
+      unsigned phase = 1;  // parity of the drain that frees a slot for its next chunk; the first round waits for none
+      uint8_t* dst = smem + TG_A_BYTES;
       for (int kc = 0; kc < nk; kc++) {
-        const int slot = kc % nslot;
-        if (kc >= nslot &&
-            !mbar_wait_bounded(empty_bar + slot, (unsigned)(kc / nslot - 1) & 1u, TG_SPINS, &s_abort)) {
+        if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, phase, TG_SPINS, &s_abort)) {
           if (!s_abort) s_abort = 1;
           break;
         }
         mbar_expect_tx(full_bar + slot, (unsigned)bn * 128u);
-        tma_load_2d(smem + (size_t)slot * stage_bytes + TG_A_BYTES, &xmap, (kbase + kc) * TG_BK, (int)m0, full_bar + slot);
+        tma_load_2d(dst, &xmap, (kbase + kc) * TG_BK, (int)m0, full_bar + slot);
+        slot++, dst += stage_bytes;
+        if (slot == nslot) slot = 0, dst = smem + TG_A_BYTES, phase ^= 1u;
       }
     }
-  } else {
+  } else if (warp == TG_MMA_WARP) {
     // ---------------- MMA issue: one thread ---------------------------------------------------------
     if (lane == 0) {
+      // This one thread is the pipeline's serial section: every instruction between two chunks' MMAs
+      // delays all of them, so slot, phase and the operand descriptors advance by additions only (no
+      // division by the runtime slot count, no descriptor rebuilt per MMA: 16 K elements further along
+      // a swizzled K-major row is +32 bytes = +2 in the descriptor's address field).
       const uint32_t idesc = umma_idesc(bn);
+      const uint32_t smem0 = smem_u32(smem);
+      uint32_t aaddr = smem0, accumulate = 0u;
+      int slot = 0;
+      unsigned phase = 0;
       bool ok = true;
       for (int kc = 0; kc < nk && ok; kc++) {
-        const int slot = kc % nslot;
-        ok = mbar_wait_bounded(full_bar + slot, (unsigned)(kc / nslot) & 1u, TG_SPINS, &s_abort);
+        ok = mbar_wait_bounded(full_bar + slot, phase, TG_SPINS, &s_abort);
         if (!ok) {
           if (!s_abort) s_abort = 2;
           break;
         }
         tc_fence_after();
-        const uint32_t aaddr = smem_u32(smem + (size_t)slot * stage_bytes);
-        const uint32_t baddr = aaddr + TG_A_BYTES;
+        const uint64_t adesc = umma_desc(aaddr), bdesc = umma_desc(aaddr + TG_A_BYTES);
 #pragma unroll
-        for (int k4 = 0; k4 < TG_BK / 16; k4++)
-          umma_f16(tmem_d, umma_desc(aaddr + k4 * 32), umma_desc(baddr + k4 * 32), idesc, (kc | k4) ? 1u : 0u);
+        for (int k4 = 0; k4 < TG_BK / 16; k4++) {
+          umma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc, accumulate);
+          accumulate = 1u;
+        }
         umma_commit(empty_bar + slot);  // frees the stage once these MMAs have read it
+        slot++, aaddr += stage_bytes;
+        if (slot == nslot) slot = 0, aaddr = smem0, phase ^= 1u;
       }
       umma_commit(&accum_bar);  // accumulator complete (also reached after a failed wait)
     }
   }
 
-  // ---------------- epilogue: warps 0..3, TMEM lane = weight row ------------------------------------
-  if (warp < 4) {
+  // ---------------- epilogue: every warp, TMEM lane = weight row ---------------------------------------
+  // A warp reads the 32 accumulator lanes of its SM partition (warp index mod 4), sixteen columns
+  // (activation rows) per tcgen05.ld, and stores them scaled: one store = 32 consecutive weight rows of
+  // one activation row = 128 bytes. The five warps of a partition take the sixteen-column blocks in
+  // turn: with one warp per partition every instruction of the store loop paid its full issue latency
+  // (measured ~150 cycles per column, 40 % of the kernel on a 256-column tile). Addresses advance by
+  // additions; the rows' inverse scales wait in shared memory; a block's residual values are all loaded
+  // before its first store (y may be the residual's own buffer).
+  {
+    __syncwarp();  // the issuing lanes of the MMA and copy warps rejoin here
+    for (int j = tid; j < bn; j += TG_THREADS) s_inv[j] = m0 + j < a.M ? __ldg(a.inv_s + m0 + j) : 0.f;
+    __syncthreads();
     const bool ok = mbar_wait_bounded(&accum_bar, 0, TG_SPINS, &s_abort);
     if (!ok && !s_abort) s_abort = 3;
     tc_fence_after();
+    const int quarter = warp & 3;
+    const int64_t n = n0 + quarter * 32 + lane;
     if (ok && !s_abort) {
-      const int64_t n = n0 + warp * 32 + lane;
-      for (int j0 = 0; j0 < bn; j0 += 8) {
-        uint32_t v[8];
-        const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)j0;
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                     : "r"(taddr));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const uint32_t tbase = tmem_d + ((uint32_t)(quarter * 32) << 16);
+      const bool split = gridDim.z > 1;
+      float* const out = (split ? a.partial + (int64_t)blockIdx.z * a.M * N : a.y) + m0 * N + n;
+      const float* const res = split || !a.residual ? nullptr : a.residual + m0 * N + n;
+      const int mleft = (int)min((int64_t)bn, a.M - m0);  // live activation rows of this tile
+      for (int j0 = (warp >> 2) * 16; j0 < mleft; j0 += (TG_WARPS / 4) * 16) {
+        uint32_t v[16];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+            : "r"(tbase + (uint32_t)j0));
+        float r[16];
+        if (res && n < N) {
+          const float* rp = res + (int64_t)j0 * N;
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const int64_t m = m0 + j0 + j;
-          if (m < a.M && n < N) {
-            float o = __uint_as_float(v[j]) * __ldg(a.inv_s + m);
-            if (gridDim.z > 1) {
-              a.partial[((int64_t)blockIdx.z * a.M + m) * N + n] = o;
-            } else {
-              if (a.residual) o += a.residual[m * N + n];
-              a.y[m * N + n] = o;
-            }
+          for (int j = 0; j < 16; j++) {
+            r[j] = j0 + j < mleft ? *rp : 0.f;
+            rp += N;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; j++) r[j] = 0.f;
+        }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (n < N) {
+          float* p = out + (int64_t)j0 * N;
+#pragma unroll
+          for (int j = 0; j < 16; j++) {
+            if (j0 + j < mleft) *p = __fadd_rn(__fmul_rn(__uint_as_float(v[j]), s_inv[j0 + j]), r[j]);
+            p += N;
           }
         }
       }
@@ -665,7 +720,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == TG_A_WARPS + TG_B_WARPS) {
+  if (warp == TG_MMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)a.tmem_cols)
                  : "memory");
   }

@@ -36,20 +36,21 @@ constexpr int TG_BK = 64;           // K elements per stage: 128 bytes of f16 pe
 constexpr int TG_GROUPS = 4;         // producer groups; group g fills stage g with chunks g, g + 4, ...
 constexpr int TG_GWARPS = 4;         // warps per group
 constexpr int TG_A_WARPS = TG_GROUPS * TG_GWARPS, TG_B_WARPS = 1;
-// Warp roles. A warp issues from the scheduler of SM partition (warp index mod 4). The MMA-issuing thread is
-// the pipeline's serial section, and next to four always-ready conversion warps it was given an issue slot
-// only every ~13 cycles (measured: ~750 cycles per chunk for ~60 instructions). So partition 1 holds one
-// conversion warp instead of four: warp 1 issues the MMAs, warp 5 the activation copies, warps 9 and 13
-// only wait at the final barrier; the sixteen conversion warps are the other warps of 0..19 (twenty warps
-// keep 96 registers per thread).
-constexpr int TG_MMA_WARP = 1, TG_B_WARP = 5;
-constexpr int TG_WARPS = 20;
+// Warp roles: warps 0..15 convert (group = warp / 4; with the A operand in tensor memory a warp converts
+// the 32 weight rows of its own TMEM lane quarter, warp mod 4), warp 16 issues the activation copies,
+// warp 17 the MMAs. (Moving the two service warps to an SM partition of their own changed nothing measurable.)
+constexpr int TG_B_WARP = TG_A_WARPS, TG_MMA_WARP = TG_A_WARPS + 1;
+constexpr int TG_WARPS = TG_A_WARPS + 2;
 constexpr int TG_THREADS = TG_WARPS * 32;
-__host__ __device__ constexpr bool tg_converts(int warp) { return (warp & 3) != 1 || warp > 13; }
-__host__ __device__ constexpr int tg_conversion_index(int warp) { return warp - ((warp + 2) / 4 < 4 ? (warp + 2) / 4 : 4); }
-static_assert(TG_WARPS % 4 == 0, "the epilogue spreads column blocks over TG_WARPS / 4 warps per partition");
-static_assert(tg_conversion_index(TG_WARPS - 1) == TG_A_WARPS - 1 && tg_conversion_index(17) == 13 && tg_conversion_index(16) == 12,
-              "sixteen conversion warps");
+__host__ __device__ constexpr bool tg_converts(int warp) { return warp < TG_A_WARPS; }
+__host__ __device__ constexpr int tg_conversion_index(int warp) { return warp; }
+// Encodings whose converted A operand goes to tensor memory instead of shared memory: the MMA then reads
+// only B from shared memory. With both operands there a 128 x 256 x 64 chunk moves 96 KB through the
+// shared-memory port (A stored + B copied in + both read by the MMAs) = 768 cycles at 128 bytes per
+// cycle, more than the chunk's 512 tensor-pipe cycles.
+__host__ __device__ constexpr bool tg_a_in_tmem(int enc) { return enc == E_Q4_0; }
+constexpr int TG_TMEM_A_COL = 256;        // first column of the A ring (32 columns per slot) behind the accumulator
+constexpr int TG_RAW_WORDS = 32 * 17;     // per-warp staging of raw row words (Q8_0: 17 words per row and chunk)
 constexpr int TG_MAX_SLOTS = 2 * TG_GROUPS;  // a group owns one pipeline slot, or two when they fit
 constexpr int TG_A_BYTES = TG_BM * 128;
 constexpr long long TG_SPINS = 1LL << 24;
@@ -74,6 +75,15 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The same with the A operand in tensor memory: lane = row, a 32-bit column holds two consecutive K elements.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -223,7 +233,9 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
   const int64_t n0 = (int64_t)blockIdx.x * TG_BM, m0 = (int64_t)blockIdx.y * bn;
   const int kbase = (int)blockIdx.z * a.nk_split;  // first chunk of this CTA's share of K
   const int nk = min(a.nk_split, (int)(K / TG_BK) - kbase);
-  const uint32_t stage_bytes = TG_A_BYTES + (uint32_t)bn * 128;
+  constexpr bool AT = tg_a_in_tmem(ENC);
+  constexpr uint32_t A_BYTES = AT ? 0u : (uint32_t)TG_A_BYTES;  // shared-memory bytes of a stage's A operand
+  const uint32_t stage_bytes = A_BYTES + (uint32_t)bn * 128;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tg_smem) + 1023) & ~uintptr_t(1023));
 
   if (tid == 0) {
@@ -252,7 +264,77 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
     // costs of a hand-over (proxy fence, barrier round trip) of up to four chunks overlap.
     const int pw = tg_conversion_index(warp);
     const int grp = pw / TG_GWARPS, wg = pw % TG_GWARPS;
-    if constexpr (ENC == E_Q4_0) {
+    if constexpr (ENC == E_Q4_0 && AT) {
+      // A operand in tensor memory. A warp converts the 32 rows of its lane quarter: thread = row, the
+      // chunk's 64 weights of a row = 32 packed columns, written with one tcgen05.st. The raw words of the
+      // next chunk are fetched a step ahead with coalesced loads (lane i of pass p holds word 32 p + i of
+      // the warp's 32 x 9 words) and turned to "thread = row" through a per-warp scratch in shared memory
+      // (row stride 9 words: conflict-free both ways).
+      const int quarter = warp & 3;
+      const int64_t rw = a.w.row_bytes() / 4;
+      uint32_t* raw = reinterpret_cast<uint32_t*>(smem + (size_t)nslot * stage_bytes) + warp * TG_RAW_WORDS;
+      const uint32_t* src[9];
+#pragma unroll
+      for (int it = 0; it < 9; it++) {
+        const int idx = it * 32 + lane;
+        int64_t row = n0 + quarter * 32 + idx / 9;
+        if (row > N - 1) row = N - 1;
+        src[it] = reinterpret_cast<const uint32_t*>(a.w.data) + row * rw + idx % 9;
+      }
+      const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f), c72 = __floats2half2_rn(72.f, 72.f);
+      const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
+      auto fetch = [&](int kc, int, uint32_t (&q)[9]) {
+#pragma unroll
+        for (int it = 0; it < 9; it++) q[it] = src[it][(int64_t)(kbase + kc) * 9];
+      };
+      auto convert = [&](int kc, int, uint32_t (&q)[9], uint8_t*) {
+#pragma unroll
+        for (int it = 0; it < 9; it++) raw[it * 32 + lane] = q[it];
+        __syncwarp();
+        uint32_t w[9];
+#pragma unroll
+        for (int i = 0; i < 9; i++) w[i] = raw[lane * 9 + i];
+        __syncwarp();
+        uint32_t out[32];
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+          const __half dh = __ushort_as_half((unsigned short)(b ? w[4] >> 16 : w[0] & 0xffffu));
+          const __half2 d2 = __halves2half2(dh, dh);
+#pragma unroll
+          for (int t = 0; t < 4; t++) {
+            const uint32_t x = b ? w[5 + t] : __funnelshift_r(w[t], w[t + 1], 16);
+            uint32_t l02 = (x & 0x000F000Fu) | 0x64006400u, l13 = ((x >> 8) & 0x000F000Fu) | 0x64006400u;
+            uint32_t h02 = (x & 0x00F000F0u) | 0x64006400u, h13 = ((x >> 8) & 0x00F000F0u) | 0x64006400u;
+            __half2 v;
+            v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l02), c1032), d2);
+            l02 = *reinterpret_cast<uint32_t*>(&v);
+            v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l13), c1032), d2);
+            l13 = *reinterpret_cast<uint32_t*>(&v);
+            v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h02), c16th), c72), d2);
+            h02 = *reinterpret_cast<uint32_t*>(&v);
+            v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h13), c16th), c72), d2);
+            h13 = *reinterpret_cast<uint32_t*>(&v);
+            // weights 4t..4t+3 (low nibbles) and 16+4t..16+4t+3 (high nibbles) of block b; column = weight / 2
+            out[b * 16 + 2 * t] = __byte_perm(l02, l13, 0x5410);
+            out[b * 16 + 2 * t + 1] = __byte_perm(l02, l13, 0x7632);
+            out[b * 16 + 8 + 2 * t] = __byte_perm(h02, h13, 0x5410);
+            out[b * 16 + 8 + 2 * t + 1] = __byte_perm(h02, h13, 0x7632);
+          }
+        }
+        const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + TG_TMEM_A_COL + (uint32_t)(kc & (nslot - 1)) * 32u;
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+            "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+            ::"r"(taddr), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]),
+              "r"(out[8]), "r"(out[9]), "r"(out[10]), "r"(out[11]), "r"(out[12]), "r"(out[13]), "r"(out[14]), "r"(out[15]),
+              "r"(out[16]), "r"(out[17]), "r"(out[18]), "r"(out[19]), "r"(out[20]), "r"(out[21]), "r"(out[22]), "r"(out[23]),
+              "r"(out[24]), "r"(out[25]), "r"(out[26]), "r"(out[27]), "r"(out[28]), "r"(out[29]), "r"(out[30]), "r"(out[31])
+            : "memory");
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+      };
+      tg_produce_chunks<9, 1>(grp, nk, nslot, smem, stage_bytes, empty_bar, full_bar, &s_abort, lane, fetch, convert);
+    } else if constexpr (ENC == E_Q4_0) {
       // Fast path. Lane = (row sub-index, block of the chunk, quarter t): 4 quant bytes + the block
       // scale -> 8 weights. The raw bytes of the group's next chunk are fetched before the current
       // one is converted and stay in flight while the group waits for its stage to drain.
@@ -618,7 +700,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
     if (lane == 0) {
       int slot = 0;
       unsigned phase = 1;  // parity of the drain that frees a slot for its next chunk; the first round waits for none
-      uint8_t* dst = smem + TG_A_BYTES;
+      uint8_t* dst = smem + A_BYTES;
       for (int kc = 0; kc < nk; kc++) {
         if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, phase, TG_SPINS, &s_abort)) {
           if (!s_abort) s_abort = 1;
@@ -627,7 +709,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
         mbar_expect_tx(full_bar + slot, (unsigned)bn * 128u);
         tma_load_2d(dst, &xmap, (kbase + kc) * TG_BK, (int)m0, full_bar + slot);
         slot++, dst += stage_bytes;
-        if (slot == nslot) slot = 0, dst = smem + TG_A_BYTES, phase ^= 1u;
+        if (slot == nslot) slot = 0, dst = smem + A_BYTES, phase ^= 1u;
       }
     }
   } else if (warp == TG_MMA_WARP) {
@@ -650,10 +732,13 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
           break;
         }
         tc_fence_after();
-        const uint64_t adesc = umma_desc(aaddr), bdesc = umma_desc(aaddr + TG_A_BYTES);
+        const uint64_t adesc = umma_desc(aaddr), bdesc = umma_desc(aaddr + A_BYTES);
 #pragma unroll
         for (int k4 = 0; k4 < TG_BK / 16; k4++) {
-          umma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc, accumulate);
+          if constexpr (AT)
+            umma_f16_ts(tmem_d, tmem_d + TG_TMEM_A_COL + (uint32_t)slot * 32u + 8u * k4, bdesc + 2 * k4, idesc, accumulate);
+          else
+            umma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc, accumulate);
           accumulate = 1u;
         }
         umma_commit(empty_bar + slot);  // frees the stage once these MMAs have read it
@@ -667,7 +752,7 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
   // ---------------- epilogue: every warp, TMEM lane = weight row ---------------------------------------
   // A warp reads the 32 accumulator lanes of its SM partition (warp index mod 4), sixteen columns
   // (activation rows) per tcgen05.ld, and stores them scaled: one store = 32 consecutive weight rows of
-  // one activation row = 128 bytes. The five warps of a partition take the sixteen-column blocks in
+  // one activation row = 128 bytes. The four or five warps of a partition take the sixteen-column blocks in
   // turn: with one warp per partition every instruction of the store loop paid its full issue latency
   // (measured ~150 cycles per column, 40 % of the kernel on a 256-column tile). Addresses advance by
   // additions; the rows' inverse scales wait in shared memory; a block's residual values are all loaded
@@ -687,7 +772,8 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
       float* const out = (split ? a.partial + (int64_t)blockIdx.z * a.M * N : a.y) + m0 * N + n;
       const float* const res = split || !a.residual ? nullptr : a.residual + m0 * N + n;
       const int mleft = (int)min((int64_t)bn, a.M - m0);  // live activation rows of this tile
-      for (int j0 = (warp >> 2) * 16; j0 < mleft; j0 += (TG_WARPS / 4) * 16) {
+      const int quarter_warps = (TG_WARPS - quarter + 3) / 4;
+      for (int j0 = (warp >> 2) * 16; j0 < mleft; j0 += quarter_warps * 16) {
         uint32_t v[16];
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -864,10 +950,13 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
   if (tg_make_xmap(xh, Mpad, K, bn, &xmap)) return 1;
   a.nk_split = nk_split, a.partial = partial;
   const dim3 grid((unsigned)((w.rows + TG_BM - 1) / TG_BM), (unsigned)mtiles, (unsigned)splits);
-  const size_t stage_b = TG_A_BYTES + (size_t)bn * 128;
-  const int nslot = 2 * TG_GROUPS * stage_b + 1024 <= 200 * 1024 ? 2 * TG_GROUPS : TG_GROUPS;
+  const bool a_tmem = tg_a_in_tmem(w.enc);
+  const size_t stage_b = (a_tmem ? 0 : TG_A_BYTES) + (size_t)bn * 128;
+  const size_t raw_b = a_tmem ? (size_t)TG_A_WARPS * TG_RAW_WORDS * 4 : 0;  // per-warp scratch behind the stages
+  const int nslot = 2 * TG_GROUPS * stage_b + raw_b + 1024 <= 200 * 1024 ? 2 * TG_GROUPS : TG_GROUPS;
   a.nslot = nslot;
-  const size_t smem = (size_t)nslot * stage_b + 1024;
+  if (a_tmem) a.tmem_cols = 512;  // accumulator (<= 256 columns) + the A ring (32 columns per slot)
+  const size_t smem = (size_t)nslot * stage_b + raw_b + 1024;
   int rc = 1;
   switch (w.enc) {
     case E_Q4_0: rc = tg_launch<E_Q4_0>(a, xmap, grid, smem, s); break;

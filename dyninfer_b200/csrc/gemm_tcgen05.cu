@@ -5,9 +5,10 @@
 //   * sixteen warps dequantise (four groups of four, one pipeline stage each): for every 64-wide K chunk they decode the raw checkpoint blocks of
 //     the tile's 128 rows (Q4_0, Q4_1, Q8_0, Q6_K and MLX-U4 with word fetches issued a step ahead and
 //     packed f16 / f32 arithmetic that rounds like the decoders of codec.cuh; the other encodings
-//     through those decoders), round to f16 and store them as the A operand in the canonical
-//     K-major 128-byte-swizzled layout (8-row groups of 1024 bytes, 16-byte chunk c of row r at
-//     position c ^ (r & 7));
+//     through those decoders) and round to f16. Q4_0, Q4_1, Q8_0 and MLX-U4 write the A operand into
+//     tensor memory (tcgen05.st, thread = weight row, column = two consecutive K elements); the others
+//     store it in shared memory in the canonical K-major 128-byte-swizzled layout (8-row groups of
+//     1024 bytes, 16-byte chunk c of row r at position c ^ (r & 7));
 //   * one thread of another warp fetches the matching activation chunk (f16, prepared once per call) as the
 //     B operand with a 2-D TMA tile copy (cp.async.bulk.tensor, hardware 128-byte swizzle);
 //   * one thread of a third issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16, four per
@@ -48,7 +49,9 @@ __host__ __device__ constexpr int tg_conversion_index(int warp) { return warp; }
 // only B from shared memory. With both operands there a 128 x 256 x 64 chunk moves 96 KB through the
 // shared-memory port (A stored + B copied in + both read by the MMAs) = 768 cycles at 128 bytes per
 // cycle, more than the chunk's 512 tensor-pipe cycles.
-__host__ __device__ constexpr bool tg_a_in_tmem(int enc) { return enc == E_Q4_0; }
+__host__ __device__ constexpr bool tg_a_in_tmem(int enc) {
+  return enc == E_Q4_0 || enc == E_Q4_1 || enc == E_Q8_0 || enc == E_MLX_U4;
+}
 constexpr int TG_TMEM_A_COL = 256;        // first column of the A ring (32 columns per slot) behind the accumulator
 constexpr int TG_RAW_WORDS = 32 * 17;     // per-warp staging of raw row words (Q8_0: 17 words per row and chunk)
 constexpr int TG_MAX_SLOTS = 2 * TG_GROUPS;  // a group owns one pipeline slot, or two when they fit
@@ -264,339 +267,139 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
     // costs of a hand-over (proxy fence, barrier round trip) of up to four chunks overlap.
     const int pw = tg_conversion_index(warp);
     const int grp = pw / TG_GWARPS, wg = pw % TG_GWARPS;
-    if constexpr (ENC == E_Q4_0 && AT) {
+    if constexpr (AT) {
       // A operand in tensor memory. A warp converts the 32 rows of its lane quarter: thread = row, the
-      // chunk's 64 weights of a row = 32 packed columns, written with one tcgen05.st. The raw words of the
-      // next chunk are fetched a step ahead with coalesced loads (lane i of pass p holds word 32 p + i of
-      // the warp's 32 x 9 words) and turned to "thread = row" through a per-warp scratch in shared memory
-      // (row stride 9 words: conflict-free both ways).
+      // chunk's 64 weights of a row = 32 packed columns (column c = weights 2c, 2c + 1), written with one
+      // tcgen05.st. The raw words of the next chunk are fetched a step ahead with coalesced loads (lane i
+      // of pass p holds word 32 p + i of the warp's 32 rows x WPR words) and turned to "thread = row"
+      // through a per-warp scratch in shared memory (odd row stride: conflict-free both ways).
+      //   Q4_0  9 words: d | 16 quant bytes from byte 2; second block from byte 18 (d = high half of word 4)
+      //   Q4_1 10 words: (d, m), 4 quant words, twice
+      //   Q8_0 17 words: d | 32 int8 from byte 2; second block from byte 34 (d = high half of word 8)
+      //   MLX-U4 8 words (word j = weights 8j..8j+7, nibble k = bits [4k, 4k+4)) + the scale and bias of
+      //          the chunk's two 32-weight halves (groups are powers of two >= 32)
+      // The arithmetic is that of the shared-memory producers: q | 0x6400 = 1024 + q in f16, reduced to q
+      // exactly, then one rounding for q * d (+ m) or q * scale + bias.
+      constexpr int WPR = ENC == E_Q4_0 ? 9 : ENC == E_Q4_1 ? 10 : ENC == E_Q8_0 ? 17 : 8;
+      constexpr int RS = WPR | 1;
+      constexpr int NX = ENC == E_MLX_U4 ? 4 : 0;
+      static_assert(32 * RS <= TG_RAW_WORDS, "per-warp scratch");
       const int quarter = warp & 3;
-      const int64_t rw = a.w.row_bytes() / 4;
+      const int64_t rw = ENC == E_MLX_U4 ? K / 8 : a.w.row_bytes() / 4;
+      const uint32_t* wbase = reinterpret_cast<const uint32_t*>(a.w.data);
       uint32_t* raw = reinterpret_cast<uint32_t*>(smem + (size_t)nslot * stage_bytes) + warp * TG_RAW_WORDS;
-      const uint32_t* src[9];
-#pragma unroll
-      for (int it = 0; it < 9; it++) {
-        const int idx = it * 32 + lane;
-        int64_t row = n0 + quarter * 32 + idx / 9;
-        if (row > N - 1) row = N - 1;
-        src[it] = reinterpret_cast<const uint32_t*>(a.w.data) + row * rw + idx % 9;
+      const int64_t last = N - 1 - (n0 + quarter * 32);  // rows past the matrix repeat its last row (never stored)
+      // MLX: this thread's own row of scales and biases
+      const int ael = a.w.aux == E_F32 ? 4 : 2;
+      int gshift = 5;
+      const uint8_t *scp = nullptr, *bip = nullptr;
+      if constexpr (ENC == E_MLX_U4) {
+        while ((1 << gshift) < a.w.group) gshift++;
+        const int64_t row = n0 + quarter * 32 + (lane < last ? lane : last);
+        scp = a.w.scales + row * (K >> gshift) * ael;
+        bip = a.w.biases + row * (K >> gshift) * ael;
       }
-      const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f), c72 = __floats2half2_rn(72.f, 72.f);
-      const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
-      auto fetch = [&](int kc, int, uint32_t (&q)[9]) {
+      auto fetch = [&](int kc, int, uint32_t (&q)[WPR + NX]) {
+        const uint32_t* cb = wbase + (int64_t)(kbase + kc) * WPR;
 #pragma unroll
-        for (int it = 0; it < 9; it++) q[it] = src[it][(int64_t)(kbase + kc) * 9];
-      };
-      auto convert = [&](int kc, int, uint32_t (&q)[9], uint8_t*) {
-#pragma unroll
-        for (int it = 0; it < 9; it++) raw[it * 32 + lane] = q[it];
-        __syncwarp();
-        uint32_t w[9];
-#pragma unroll
-        for (int i = 0; i < 9; i++) w[i] = raw[lane * 9 + i];
-        __syncwarp();
-        uint32_t out[32];
-#pragma unroll
-        for (int b = 0; b < 2; b++) {
-          const __half dh = __ushort_as_half((unsigned short)(b ? w[4] >> 16 : w[0] & 0xffffu));
-          const __half2 d2 = __halves2half2(dh, dh);
-#pragma unroll
-          for (int t = 0; t < 4; t++) {
-            const uint32_t x = b ? w[5 + t] : __funnelshift_r(w[t], w[t + 1], 16);
-            uint32_t l02 = (x & 0x000F000Fu) | 0x64006400u, l13 = ((x >> 8) & 0x000F000Fu) | 0x64006400u;
-            uint32_t h02 = (x & 0x00F000F0u) | 0x64006400u, h13 = ((x >> 8) & 0x00F000F0u) | 0x64006400u;
-            __half2 v;
-            v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l02), c1032), d2);
-            l02 = *reinterpret_cast<uint32_t*>(&v);
-            v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l13), c1032), d2);
-            l13 = *reinterpret_cast<uint32_t*>(&v);
-            v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h02), c16th), c72), d2);
-            h02 = *reinterpret_cast<uint32_t*>(&v);
-            v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h13), c16th), c72), d2);
-            h13 = *reinterpret_cast<uint32_t*>(&v);
-            // weights 4t..4t+3 (low nibbles) and 16+4t..16+4t+3 (high nibbles) of block b; column = weight / 2
-            out[b * 16 + 2 * t] = __byte_perm(l02, l13, 0x5410);
-            out[b * 16 + 2 * t + 1] = __byte_perm(l02, l13, 0x7632);
-            out[b * 16 + 8 + 2 * t] = __byte_perm(h02, h13, 0x5410);
-            out[b * 16 + 8 + 2 * t + 1] = __byte_perm(h02, h13, 0x7632);
+        for (int it = 0; it < WPR; it++) {
+          const int idx = it * 32 + lane, r = idx / WPR;
+          q[it] = cb[(n0 + quarter * 32 + (r < last ? r : last)) * rw + (idx - r * WPR)];
+        }
+        if constexpr (ENC == E_MLX_U4) {
+          const int64_t k0 = (int64_t)(kbase + kc) * TG_BK;
+          q[WPR] = __float_as_uint(aux_load(scp, a.w.aux, k0 >> gshift));
+          q[WPR + 1] = __float_as_uint(aux_load(bip, a.w.aux, k0 >> gshift));
+          if (gshift > 5) {  // one group covers the whole chunk
+            q[WPR + 2] = q[WPR], q[WPR + 3] = q[WPR + 1];
+          } else {
+            q[WPR + 2] = __float_as_uint(aux_load(scp, a.w.aux, (k0 + 32) >> gshift));
+            q[WPR + 3] = __float_as_uint(aux_load(bip, a.w.aux, (k0 + 32) >> gshift));
           }
         }
+      };
+      const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f), c72 = __floats2half2_rn(72.f, 72.f);
+      const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f), c1024 = __floats2half2_rn(1024.f, 1024.f);
+      const __half2 c64n = __floats2half2_rn(-64.f, -64.f), c1152 = __floats2half2_rn(1152.f, 1152.f);
+      auto h2u = [](__half2 v) { return *reinterpret_cast<uint32_t*>(&v); };
+      auto u2h = [](uint32_t v) { return *reinterpret_cast<__half2*>(&v); };
+      auto convert = [&](int kc, int, uint32_t (&q)[WPR + NX], uint8_t*) {
+#pragma unroll
+        for (int it = 0; it < WPR; it++) {
+          const int idx = it * 32 + lane, r = idx / WPR;
+          raw[r * RS + (idx - r * WPR)] = q[it];
+        }
+        __syncwarp();
+        // one 32-weight half of the chunk at a time (its words w[0..NW) of the row): 16 columns per tcgen05.st
+        constexpr int NW = ENC == E_Q8_0 ? 9 : ENC == E_MLX_U4 ? 4 : 5, WSTEP = ENC == E_Q4_1 ? 5 : NW - (ENC == E_MLX_U4 ? 0 : 1);
         const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + TG_TMEM_A_COL + (uint32_t)(kc & (nslot - 1)) * 32u;
-        asm volatile(
-            "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-            "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-            ::"r"(taddr), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]),
-              "r"(out[8]), "r"(out[9]), "r"(out[10]), "r"(out[11]), "r"(out[12]), "r"(out[13]), "r"(out[14]), "r"(out[15]),
-              "r"(out[16]), "r"(out[17]), "r"(out[18]), "r"(out[19]), "r"(out[20]), "r"(out[21]), "r"(out[22]), "r"(out[23]),
-              "r"(out[24]), "r"(out[25]), "r"(out[26]), "r"(out[27]), "r"(out[28]), "r"(out[29]), "r"(out[30]), "r"(out[31])
-            : "memory");
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+          uint32_t w[NW];
+#pragma unroll
+          for (int i = 0; i < NW; i++) w[i] = raw[lane * RS + b * WSTEP + i];
+          uint32_t out[16];
+          if constexpr (ENC == E_Q4_0 || ENC == E_Q4_1) {
+            const uint32_t dm = ENC == E_Q4_1 ? w[0] : (b ? w[0] >> 16 : w[0] & 0xffffu);
+            const __half dh = __ushort_as_half((unsigned short)(dm & 0xffffu));
+            const __half mh = __ushort_as_half((unsigned short)(dm >> 16));
+            const __half2 d2 = __halves2half2(dh, dh), m2 = __halves2half2(mh, mh);
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+              const uint32_t x = ENC == E_Q4_1 || b ? w[1 + t] : __funnelshift_r(w[t], w[t + 1], 16);
+              uint32_t l02 = (x & 0x000F000Fu) | 0x64006400u, l13 = ((x >> 8) & 0x000F000Fu) | 0x64006400u;
+              uint32_t h02 = (x & 0x00F000F0u) | 0x64006400u, h13 = ((x >> 8) & 0x00F000F0u) | 0x64006400u;
+              if constexpr (ENC == E_Q4_0) {  // (q - 8) * d
+                l02 = h2u(__hmul2(__hsub2(u2h(l02), c1032), d2));
+                l13 = h2u(__hmul2(__hsub2(u2h(l13), c1032), d2));
+                h02 = h2u(__hmul2(__hsub2(__hmul2(u2h(h02), c16th), c72), d2));
+                h13 = h2u(__hmul2(__hsub2(__hmul2(u2h(h13), c16th), c72), d2));
+              } else {  // q * d + m
+                l02 = h2u(__hfma2(__hsub2(u2h(l02), c1024), d2, m2));
+                l13 = h2u(__hfma2(__hsub2(u2h(l13), c1024), d2, m2));
+                h02 = h2u(__hfma2(__hfma2(u2h(h02), c16th, c64n), d2, m2));
+                h13 = h2u(__hfma2(__hfma2(u2h(h13), c16th, c64n), d2, m2));
+              }
+              // weights 4t..4t+3 (low nibbles) and 16+4t..16+4t+3 (high nibbles) of the block
+              out[2 * t] = __byte_perm(l02, l13, 0x5410);
+              out[2 * t + 1] = __byte_perm(l02, l13, 0x7632);
+              out[8 + 2 * t] = __byte_perm(h02, h13, 0x5410);
+              out[8 + 2 * t + 1] = __byte_perm(h02, h13, 0x7632);
+            }
+          } else if constexpr (ENC == E_Q8_0) {
+            const __half dh = __ushort_as_half((unsigned short)(b ? w[0] >> 16 : w[0] & 0xffffu));
+            const __half2 d2 = __halves2half2(dh, dh);
+#pragma unroll
+            for (int t = 0; t < 8; t++) {
+              const uint32_t x = (b ? w[1 + t] : __funnelshift_r(w[t], w[t + 1], 16)) ^ 0x80808080u;
+              out[2 * t] = h2u(__hmul2(__hsub2(u2h(__byte_perm(x, 0x64646464u, 0x4140)), c1152), d2));
+              out[2 * t + 1] = h2u(__hmul2(__hsub2(u2h(__byte_perm(x, 0x64646464u, 0x4342)), c1152), d2));
+            }
+          } else {
+            const __half2 s2 = __float2half2_rn(__uint_as_float(q[WPR + 2 * b]));
+            const __half2 b2 = __float2half2_rn(__uint_as_float(q[WPR + 2 * b + 1]));
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const uint32_t x = w[j];
+              const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;  // nibbles 0,2,4,6 / 1,3,5,7
+#pragma unroll
+              for (int e = 0; e < 4; e++) {
+                const uint32_t pr = (__byte_perm(lo, hi, 0x0400 + 0x0101 * e) & 0x00FF00FFu) | 0x64006400u;  // (n 2e, n 2e+1)
+                out[4 * j + e] = h2u(__hfma2(__hsub2(u2h(pr), c1024), s2, b2));
+              }
+            }
+          }
+          asm volatile(
+              "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+              ::"r"(taddr + 16u * b), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]),
+                "r"(out[7]), "r"(out[8]), "r"(out[9]), "r"(out[10]), "r"(out[11]), "r"(out[12]), "r"(out[13]), "r"(out[14]), "r"(out[15])
+              : "memory");
+        }
+        __syncwarp();  // the scratch is read; the next chunk may overwrite it
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
       };
-      tg_produce_chunks<9, 1>(grp, nk, nslot, smem, stage_bytes, empty_bar, full_bar, &s_abort, lane, fetch, convert);
-    } else if constexpr (ENC == E_Q4_0) {
-      // Fast path. Lane = (row sub-index, block of the chunk, quarter t): 4 quant bytes + the block
-      // scale -> 8 weights. The raw bytes of the group's next chunk are fetched before the current
-      // one is converted and stay in flight while the group waits for its stage to drain.
-      // (q - 8) * d in f16: nibble | 0x6400 = 1024 + q (low) or 1024 + 16 q (high, used in place);
-      // subtracting 1032, or multiplying by 1/16 and subtracting 72, is exact; the product with d
-      // rounds once, exactly like rounding the f32 value.
-      constexpr int NJ = TG_BM / (TG_GWARPS * 4);  // rows per lane and chunk
-      const int blk2 = (lane >> 2) & 1, t = lane & 3, rsub = lane >> 3, l8 = lane & 7;
-      // A row's chunk is 36 bytes = 9 aligned words (rows are multiples of 36 bytes). The 8 lanes of
-      // a row fetch words 0..7 (lane 0 of the row also word 8) with 32-bit loads and pass them on by
-      // shuffle: a third of the load instructions and far fewer cache transactions than 2-byte loads.
-      const int64_t rw = a.w.row_bytes() / 4;
-      const uint32_t* roww[NJ];
-#pragma unroll
-      for (int j = 0; j < NJ; j++) {
-        int64_t row = n0 + wg * 4 + rsub + 16 * j;
-        if (row > N - 1) row = N - 1;
-        roww[j] = reinterpret_cast<const uint32_t*>(a.w.data) + row * rw;
-      }
-      uint32_t qa[2][NJ], qb[2][NJ];  // word l8 of the chunk; word 8 (lane 0 of each row only)
-      auto fetch = [&](int kc, uint32_t (&wa)[NJ], uint32_t (&wb)[NJ]) {
-#pragma unroll
-        for (int j = 0; j < NJ; j++) {
-          const uint32_t* p = roww[j] + (int64_t)(kbase + kc) * 9;
-          wa[j] = p[l8];
-          wb[j] = l8 == 0 ? p[8] : 0u;
-        }
-      };
-      // where this lane's 4 quant bytes and scale live among the 9 words:
-      //   block 0: scale = low half of word 0, quants = bytes 2+4t.. = words t, t+1 shifted by 16 bits
-      //   block 1: scale = high half of word 4, quants = word 5+t (word 8 for t = 3)
-      const int base8 = lane & ~7;
-      const int src_x = base8 + (blk2 ? ((5 + t) & 7) : t), src_y = base8 + ((t + 1) & 7);
-      const int src_d = base8 + (blk2 ? 4 : 0);
-      if (grp < nk) fetch(grp, qa[0], qb[0]);
-      const __half2 c1032 = __floats2half2_rn(1032.f, 1032.f), c72 = __floats2half2_rn(72.f, 72.f);
-      const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
-      bool live = true;
-      for (int kc0 = grp; kc0 < nk && live; kc0 += 2 * TG_GROUPS) {
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-          const int kc = kc0 + u * TG_GROUPS;
-          if (kc >= nk) break;
-          if (kc + TG_GROUPS < nk) fetch(kc + TG_GROUPS, qa[u ^ 1], qb[u ^ 1]);
-          const int slot = (kc & (nslot - 1));
-          uint8_t* abase = smem + (size_t)slot * stage_bytes;
-          if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, (unsigned)((kc >> slot_shift) - 1) & 1u, TG_SPINS, &s_abort)) {
-            if (!s_abort) s_abort = 1;
-            live = false;
-            break;
-          }
-#pragma unroll
-          for (int j = 0; j < NJ; j++) {
-            const int r = wg * 4 + rsub + 16 * j;
-            const uint32_t x = __shfl_sync(0xffffffffu, qa[u][j], src_x);
-            const uint32_t x8 = __shfl_sync(0xffffffffu, qb[u][j], base8);
-            const uint32_t y = __shfl_sync(0xffffffffu, qa[u][j], src_y);
-            const uint32_t dw = __shfl_sync(0xffffffffu, qa[u][j], src_d);
-            const uint32_t w = blk2 ? (t == 3 ? x8 : x) : __funnelshift_r(x, y, 16);
-            const __half dh = __ushort_as_half((unsigned short)(blk2 ? dw >> 16 : dw & 0xffffu));
-            const __half2 d2 = __halves2half2(dh, dh);
-            uint32_t l02 = (w & 0x000F000Fu) | 0x64006400u, l13 = ((w >> 8) & 0x000F000Fu) | 0x64006400u;
-            uint32_t h02 = (w & 0x00F000F0u) | 0x64006400u, h13 = ((w >> 8) & 0x00F000F0u) | 0x64006400u;
-            __half2 v;
-            v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l02), c1032), d2);
-            l02 = *reinterpret_cast<uint32_t*>(&v);
-            v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&l13), c1032), d2);
-            l13 = *reinterpret_cast<uint32_t*>(&v);
-            v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h02), c16th), c72), d2);
-            h02 = *reinterpret_cast<uint32_t*>(&v);
-            v = __hmul2(__hsub2(__hmul2(*reinterpret_cast<__half2*>(&h13), c16th), c72), d2);
-            h13 = *reinterpret_cast<uint32_t*>(&v);
-            // elements 4t..4t+3 (low nibbles) and 16+4t..16+4t+3 (high nibbles) of block blk2
-            const uint2 lo = make_uint2(__byte_perm(l02, l13, 0x5410), __byte_perm(l02, l13, 0x7632));
-            const uint2 hi = make_uint2(__byte_perm(h02, h13, 0x5410), __byte_perm(h02, h13, 0x7632));
-            const int klo = blk2 * 32 + 4 * t, khi = klo + 16;
-            uint8_t* rowbase = abase + r * 128;
-            *reinterpret_cast<uint2*>(rowbase + (((klo >> 3) ^ (r & 7)) << 4) + (klo & 7) * 2) = lo;
-            *reinterpret_cast<uint2*>(rowbase + (((khi >> 3) ^ (r & 7)) << 4) + (khi & 7) * 2) = hi;
-          }
-          fence_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(full_bar + slot);
-        }
-      }
-    } else if constexpr (ENC == E_MLX_U4) {
-      // Fast path for MLX affine U4 (word j of a row = elements 8j .. 8j+7, nibble k = bits [4k, 4k+4);
-      // w = q * scale + bias per group, mlx_affine.rs:284-290,590-600). Lane = (row sub-index, word j of
-      // the chunk's 8 words): one aligned word + the group's scale and bias -> 8 consecutive f16
-      // weights = one 16-byte store. nibble | 0x6400 = 1024 + q; subtracting 1024 is exact and the
-      // f16 fused multiply-add q * s + b rounds once.
-      constexpr int NJ = TG_BM / (TG_GWARPS * 4);
-      const int j = lane & 7, rsub = lane >> 3;
-      const int ael = a.w.aux == E_F32 ? 4 : 2;
-      const int64_t gpr = K / a.w.group;  // groups per row
-      const uint32_t* wordp[NJ];
-      const uint8_t *scp[NJ], *bip[NJ];
-#pragma unroll
-      for (int jj = 0; jj < NJ; jj++) {
-        int64_t row = n0 + wg * 4 + rsub + 16 * jj;
-        if (row > N - 1) row = N - 1;
-        wordp[jj] = reinterpret_cast<const uint32_t*>(a.w.data) + row * (K / 8) + j;
-        scp[jj] = a.w.scales + row * gpr * ael;
-        bip[jj] = a.w.biases + row * gpr * ael;
-      }
-      uint32_t qw[2][NJ];
-      float ax[2][NJ];  // even lanes hold the group's scale, odd lanes its bias (lane pairs share a group)
-      auto fetch = [&](int kc, uint32_t (&q)[NJ], float (&x_)[NJ]) {
-        const int64_t gi = ((int64_t)(kbase + kc) * TG_BK + 8 * j) / a.w.group;
-#pragma unroll
-        for (int jj = 0; jj < NJ; jj++) {
-          q[jj] = wordp[jj][(int64_t)(kbase + kc) * 8];
-          x_[jj] = aux_load((j & 1) ? bip[jj] : scp[jj], a.w.aux, gi);
-        }
-      };
-      if (grp < nk) fetch(grp, qw[0], ax[0]);
-      const __half2 c1024 = __floats2half2_rn(1024.f, 1024.f);
-      bool live = true;
-      for (int kc0 = grp; kc0 < nk && live; kc0 += 2 * TG_GROUPS) {
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-          const int kc = kc0 + u * TG_GROUPS;
-          if (kc >= nk) break;
-          if (kc + TG_GROUPS < nk) fetch(kc + TG_GROUPS, qw[u ^ 1], ax[u ^ 1]);
-          const int slot = (kc & (nslot - 1));
-          uint8_t* abase = smem + (size_t)slot * stage_bytes;
-          if (kc >= nslot && !mbar_wait_bounded(empty_bar + slot, (unsigned)((kc >> slot_shift) - 1) & 1u, TG_SPINS, &s_abort)) {
-            if (!s_abort) s_abort = 1;
-            live = false;
-            break;
-          }
-#pragma unroll
-          for (int jj = 0; jj < NJ; jj++) {
-            const int r = wg * 4 + rsub + 16 * jj;
-            const uint32_t w = qw[u][jj];
-            const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;   // nibbles 0,2,4,6 / 1,3,5,7
-            const __half2 s2 = __float2half2_rn(__shfl_sync(0xffffffffu, ax[u][jj], lane & ~1));
-            const __half2 b2 = __float2half2_rn(__shfl_sync(0xffffffffu, ax[u][jj], lane | 1));
-            uint32_t pr[4];
-            pr[0] = (__byte_perm(lo, hi, 0x0400) & 0x00FF00FFu) | 0x64006400u;      // (n0, n1)
-            pr[1] = (__byte_perm(lo, hi, 0x0501) & 0x00FF00FFu) | 0x64006400u;      // (n2, n3)
-            pr[2] = (__byte_perm(lo, hi, 0x0602) & 0x00FF00FFu) | 0x64006400u;      // (n4, n5)
-            pr[3] = (__byte_perm(lo, hi, 0x0703) & 0x00FF00FFu) | 0x64006400u;      // (n6, n7)
-            uint4 out;
-            uint32_t* o = reinterpret_cast<uint32_t*>(&out);
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-              const __half2 v = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&pr[e]), c1024), s2, b2);
-              o[e] = *reinterpret_cast<const uint32_t*>(&v);
-            }
-            *reinterpret_cast<uint4*>(abase + r * 128 + ((j ^ (r & 7)) << 4)) = out;
-          }
-          fence_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(full_bar + slot);
-        }
-      }
-    } else if constexpr (ENC == E_Q8_0) {
-      // Q8_0: a row's chunk is two 34-byte blocks = 17 aligned words (rows are multiples of 68 bytes).
-      // Lane = (row sub-index, piece l8 of 8 weights): the lanes of a row fetch words 2 l8 and 2 l8 + 1
-      // (lane 7 also word 16) and pass the neighbour's first word on by shuffle. Block 0 keeps its scale
-      // in the low half of word 0 and its quants from byte 2, block 1 its scale in the high half of
-      // word 8 and its quants from word 9. int8 -> f16: byte ^ 0x80 under 0x64 is 1024 + 128 + q;
-      // subtracting 1152 is exact and the product with d rounds once, like rounding the f32 value.
-      constexpr int NJ = TG_BM / (TG_GWARPS * 4);
-      const int l8 = lane & 7, rsub = lane >> 3, base8 = lane & ~7, blk2 = l8 >> 2;
-      const int64_t rw = a.w.row_bytes() / 4;
-      const uint32_t* roww[NJ];
-#pragma unroll
-      for (int j = 0; j < NJ; j++) {
-        int64_t row = n0 + wg * 4 + rsub + 16 * j;
-        if (row > N - 1) row = N - 1;
-        roww[j] = reinterpret_cast<const uint32_t*>(a.w.data) + row * rw + 2 * l8;
-      }
-      const __half2 c1152 = __floats2half2_rn(1152.f, 1152.f);
-      auto fetch = [&](int kc, int, uint32_t (&q)[3 * NJ]) {
-#pragma unroll
-        for (int j = 0; j < NJ; j++) {
-          const uint32_t* p = roww[j] + (int64_t)(kbase + kc) * 17;
-          q[3 * j] = p[0];
-          q[3 * j + 1] = p[1];
-          q[3 * j + 2] = l8 == 7 ? p[2] : 0u;
-        }
-      };
-      auto convert = [&](int, int, uint32_t (&q)[3 * NJ], uint8_t* abase) {
-#pragma unroll
-        for (int j = 0; j < NJ; j++) {
-          const int r = wg * 4 + rsub + 16 * j;
-          const uint32_t wa = q[3 * j], wb = q[3 * j + 1];
-          const uint32_t nx = __shfl_sync(0xffffffffu, wa, base8 + ((l8 + 1) & 7));
-          const uint32_t dw = __shfl_sync(0xffffffffu, wa, base8 + (blk2 ? 4 : 0));
-          const uint32_t nxt = l8 == 7 ? q[3 * j + 2] : nx;
-          const uint32_t lo = (blk2 ? wb : __funnelshift_r(wa, wb, 16)) ^ 0x80808080u;
-          const uint32_t hi = (blk2 ? nxt : __funnelshift_r(wb, nx, 16)) ^ 0x80808080u;
-          const __half dh = __ushort_as_half((unsigned short)(blk2 ? dw >> 16 : dw & 0xffffu));
-          const __half2 d2 = __halves2half2(dh, dh);
-          uint32_t pr[4] = {__byte_perm(lo, 0x64646464u, 0x4140), __byte_perm(lo, 0x64646464u, 0x4342),
-                            __byte_perm(hi, 0x64646464u, 0x4140), __byte_perm(hi, 0x64646464u, 0x4342)};
-          uint4 out;
-          uint32_t* o = reinterpret_cast<uint32_t*>(&out);
-#pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const __half2 v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&pr[e]), c1152), d2);
-            o[e] = *reinterpret_cast<const uint32_t*>(&v);
-          }
-          *reinterpret_cast<uint4*>(abase + r * 128 + ((l8 ^ (r & 7)) << 4)) = out;
-        }
-      };
-      tg_produce_chunks<3 * NJ, 1>(grp, nk, nslot, smem, stage_bytes, empty_bar, full_bar, &s_abort, lane, fetch, convert);
-    } else if constexpr (ENC == E_Q4_1) {
-      // Q4_1: a row's chunk is two 20-byte blocks = 10 aligned words; word 0 of a block is (d, m), words
-      // 1..4 its quants. Lane = (row sub-index, block, quarter t): one quant word + the (d, m) word -> the
-      // weights 4t..4t+3 (low nibbles) and 16+4t..16+4t+3 (high nibbles). nibble | 0x6400 = 1024 + q or
-      // 1024 + 16 q; both reduce to q exactly, and the f16 fused multiply-add q * d + m rounds once.
-      constexpr int NJ = TG_BM / (TG_GWARPS * 4);
-      const int blk2 = (lane >> 2) & 1, t = lane & 3, rsub = lane >> 3;
-      const int64_t rw = a.w.row_bytes() / 4;
-      const uint32_t* roww[NJ];
-#pragma unroll
-      for (int j = 0; j < NJ; j++) {
-        int64_t row = n0 + wg * 4 + rsub + 16 * j;
-        if (row > N - 1) row = N - 1;
-        roww[j] = reinterpret_cast<const uint32_t*>(a.w.data) + row * rw + blk2 * 5;
-      }
-      const __half2 c1024 = __floats2half2_rn(1024.f, 1024.f), c64n = __floats2half2_rn(-64.f, -64.f);
-      const __half2 c16th = __floats2half2_rn(0.0625f, 0.0625f);
-      auto fetch = [&](int kc, int, uint32_t (&q)[2 * NJ]) {
-#pragma unroll
-        for (int j = 0; j < NJ; j++) {
-          const uint32_t* p = roww[j] + (int64_t)(kbase + kc) * 10;
-          q[2 * j] = p[1 + t];
-          q[2 * j + 1] = p[0];
-        }
-      };
-      auto convert = [&](int, int, uint32_t (&q)[2 * NJ], uint8_t* abase) {
-#pragma unroll
-        for (int j = 0; j < NJ; j++) {
-          const int r = wg * 4 + rsub + 16 * j;
-          const uint32_t w = q[2 * j], dm = q[2 * j + 1];
-          const __half dh = __ushort_as_half((unsigned short)(dm & 0xffffu));
-          const __half mh = __ushort_as_half((unsigned short)(dm >> 16));
-          const __half2 d2 = __halves2half2(dh, dh), m2 = __halves2half2(mh, mh);
-          uint32_t l02 = (w & 0x000F000Fu) | 0x64006400u, l13 = ((w >> 8) & 0x000F000Fu) | 0x64006400u;
-          uint32_t h02 = (w & 0x00F000F0u) | 0x64006400u, h13 = ((w >> 8) & 0x00F000F0u) | 0x64006400u;
-          __half2 v;
-          v = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&l02), c1024), d2, m2);
-          l02 = *reinterpret_cast<uint32_t*>(&v);
-          v = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&l13), c1024), d2, m2);
-          l13 = *reinterpret_cast<uint32_t*>(&v);
-          v = __hfma2(__hfma2(*reinterpret_cast<__half2*>(&h02), c16th, c64n), d2, m2);
-          h02 = *reinterpret_cast<uint32_t*>(&v);
-          v = __hfma2(__hfma2(*reinterpret_cast<__half2*>(&h13), c16th, c64n), d2, m2);
-          h13 = *reinterpret_cast<uint32_t*>(&v);
-          const uint2 lo = make_uint2(__byte_perm(l02, l13, 0x5410), __byte_perm(l02, l13, 0x7632));
-          const uint2 hi = make_uint2(__byte_perm(h02, h13, 0x5410), __byte_perm(h02, h13, 0x7632));
-          const int klo = blk2 * 32 + 4 * t, khi = klo + 16;
-          uint8_t* rowbase = abase + r * 128;
-          *reinterpret_cast<uint2*>(rowbase + (((klo >> 3) ^ (r & 7)) << 4) + (klo & 7) * 2) = lo;
-          *reinterpret_cast<uint2*>(rowbase + (((khi >> 3) ^ (r & 7)) << 4) + (khi & 7) * 2) = hi;
-        }
-      };
-      tg_produce_chunks<2 * NJ, 1>(grp, nk, nslot, smem, stage_bytes, empty_bar, full_bar, &s_abort, lane, fetch, convert);
+      tg_produce_chunks<WPR + NX, 1>(grp, nk, nslot, smem, stage_bytes, empty_bar, full_bar, &s_abort, lane, fetch, convert);
     } else if constexpr (ENC == E_Q6_K) {
       // Q6_K: a 64-wide chunk is one quarter (n, h) of a 210-byte block: nibble h of ql bytes
       // 64 n .. 64 n + 63 and bit field 2 h + p of qh bytes 32 n .. 32 n + 31 (p = 0: the chunk's first 32
@@ -827,7 +630,8 @@ bool tg_shape_ok(const WRef& w, int64_t M) {
     case E_BF16: break;
     default: return false;
   }
-  if (w.enc == E_MLX_U4 && (w.group < 8 || w.cols % w.group)) return false;
+  // MLX-U4: a 64-wide chunk takes one scale and bias per 32-weight half
+  if (w.enc == E_MLX_U4 && (w.group < 32 || (w.group & (w.group - 1)) || w.cols % w.group)) return false;
   // the word-fetching producers read aligned 32-bit words (Q6_K: 16-bit halves)
   const uintptr_t addr = reinterpret_cast<uintptr_t>(w.data);
   if ((w.enc == E_Q4_0 || w.enc == E_Q4_1 || w.enc == E_Q8_0 || w.enc == E_MLX_U4) && (addr & 3)) return false;

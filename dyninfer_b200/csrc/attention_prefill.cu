@@ -3,9 +3,11 @@
 //
 // Same mathematics as the per-row kernel (kernels.rs:310-458: s = (q.k) * 1/sqrt(d), keys beyond the
 // row's position masked, online max / sum merge, out / sum at the end), restructured the usual
-// flash-attention way: one CTA = one query head x 64 consecutive rows, four warps x 16 rows; the
-// key / value rows of the head's KV plane stream through shared memory 64 keys at a time;
-// S = Q K^T and O += P V run on mma.sync.m16n8k16 with f32 accumulators. The cache entries are used
+// flash-attention way: one CTA = one query head x 64 consecutive rows, eight warps: warp w takes the
+// 16 rows of group w mod 4 and, of every pair of 64-key blocks, the block w / 4, so two blocks are
+// worked on at once; the pairs stream through shared memory with cp.async, the next pair in flight
+// while the current one is used (four K + V tiles resident). The two halves' running (max, sum, out)
+// are merged at the end. S = Q K^T and O += P V run on mma.sync.m16n8k16 with f32 accumulators. The cache entries are used
 // in their stored type (exact); the f32 operands Q and P enter as hi + lo pairs of that type
 // (two mma per tile), so the products carry ~16 significant bits of Q / P and the result stays
 // within ~1e-4 of the f32 evaluation.
@@ -19,6 +21,15 @@ constexpr int FA_D = 128;      // head dim handled by this kernel
 constexpr int FA_BR = 64;      // query rows per CTA
 constexpr int FA_BC = 64;      // keys per step
 constexpr int FA_PITCH = FA_D + 8;  // elements per shared-memory row (272 bytes: conflict-free fragment loads)
+constexpr int FA_THREADS = 256;
+constexpr int FA_TILE = FA_BC * FA_PITCH;            // elements of one K (or V) tile
+constexpr int FA_SMEM = 2 * 2 * 2 * FA_TILE * 2;     // buffers x blocks of a pair x (K, V) x 2 bytes
+
+__device__ __forceinline__ void fa_cp16(void* dst, const void* src, bool live) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int n = live ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
 
 template <int KV>
 struct Mma;
@@ -65,14 +76,15 @@ struct FaArgs {
 };
 
 template <int KV>
-__global__ void __launch_bounds__(128) attention_prefill_kernel(const FaArgs a) {
+__global__ void __launch_bounds__(FA_THREADS) attention_prefill_kernel(const FaArgs a) {
   using M = Mma<KV>;
   using T = typename M::T;
-  __shared__ __align__(16) T ks[FA_BC][FA_PITCH];
-  __shared__ __align__(16) T vs[FA_BC][FA_PITCH];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  extern __shared__ __align__(16) uint8_t fa_smem[];
+  T* const tiles = reinterpret_cast<T*>(fa_smem);  // [buffer][block of the pair][K, V][FA_BC][FA_PITCH]
+  const int tid = threadIdx.x, lane = tid & 31, warp8 = tid >> 5;
+  const int warp = warp8 & 3, half = warp8 >> 2;   // row group; which block of a pair
   const int g = lane >> 2, t = lane & 3;
-  const int64_t h = blockIdx.x, rb = blockIdx.y;
+  const int64_t h = blockIdx.x, rb = gridDim.y - 1 - blockIdx.y;  // the longest row blocks start first
   const int64_t kvh = h / (a.nh / a.nkv);
   const T* kplane = reinterpret_cast<const T*>(a.kcache) + (a.seq * a.nkv + kvh) * a.cap * FA_D;
   const T* vplane = reinterpret_cast<const T*>(a.vcache) + (a.seq * a.nkv + kvh) * a.cap * FA_D;
@@ -108,21 +120,30 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const FaArgs a) 
   int64_t cta_last = a.base_pos + rb * FA_BR + FA_BR - 1;
   if (cta_last > a.base_pos + a.rows - 1) cta_last = a.base_pos + a.rows - 1;
   const int64_t warp_last = a.base_pos + (row_lo + 15 < a.rows ? row_lo + 15 : a.rows - 1);
-  for (int64_t kb = 0; kb * FA_BC <= cta_last; kb++) {
-    __syncthreads();  // the previous block is no longer read
-    // 64 keys x 256 bytes each for K and V: 16-byte pieces, coalesced
-    for (int i = tid; i < FA_BC * (FA_D / 8); i += 128) {
-      const int key = i / (FA_D / 8), c = i % (FA_D / 8);
-      const int64_t gk = kb * FA_BC + key;   // < cap: the capacity is a multiple of the page size
-      // rows past the last written position may hold anything: they are masked, but 0 * NaN must not happen
+  const int64_t nkb = cta_last / FA_BC + 1, npairs = (nkb + 1) / 2;
+  // 2 blocks x (K, V) x 64 keys x 16 pieces of 16 bytes per pair, coalesced; rows past the last written
+  // position may hold anything: they are masked, but 0 * NaN must not happen, so they arrive as zeros
+  auto load_pair = [&](int64_t pr) {
+    T* dst = tiles + (pr & 1) * 4 * FA_TILE;
+    for (int i = tid; i < 2 * FA_BC * (FA_D / 8); i += FA_THREADS) {
+      const int blk = i / (FA_BC * (FA_D / 8)), key = (i / (FA_D / 8)) % FA_BC, c = i % (FA_D / 8);
+      const int64_t gk = (2 * pr + blk) * FA_BC + key;  // < cap for every written key
       const bool written = gk <= cta_last;
-      const uint4 z = make_uint4(0, 0, 0, 0);
-      *reinterpret_cast<uint4*>(&ks[key][c * 8]) =
-          written ? *reinterpret_cast<const uint4*>(kplane + gk * FA_D + c * 8) : z;
-      *reinterpret_cast<uint4*>(&vs[key][c * 8]) =
-          written ? *reinterpret_cast<const uint4*>(vplane + gk * FA_D + c * 8) : z;
+      const int64_t src = (written ? gk : 0) * FA_D + c * 8;
+      fa_cp16(dst + (blk * 2) * FA_TILE + key * FA_PITCH + c * 8, kplane + src, written);
+      fa_cp16(dst + (blk * 2 + 1) * FA_TILE + key * FA_PITCH + c * 8, vplane + src, written);
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  load_pair(0);
+  for (int64_t pr = 0; pr < npairs; pr++) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // pair pr has arrived for everyone, and nobody still reads the buffer the next pair goes to
+    if (pr + 1 < npairs) load_pair(pr + 1);
+    const int64_t kb = 2 * pr + half;
+    if (kb >= nkb) continue;
+    const T(*ks)[FA_PITCH] = reinterpret_cast<const T(*)[FA_PITCH]>(tiles + ((pr & 1) * 4 + half * 2) * FA_TILE);
+    const T(*vs)[FA_PITCH] = reinterpret_cast<const T(*)[FA_PITCH]>(tiles + ((pr & 1) * 4 + half * 2 + 1) * FA_TILE);
     if (kb * FA_BC > warp_last) continue;  // every key of the block lies after this warp's rows
     // ---- S = Q K^T for 16 rows x 64 keys
     float s[8][4];
@@ -197,6 +218,30 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const FaArgs a) 
       }
     }
   }
+  // ---- merge the two halves' running states (thread for thread: both cover the same rows and columns)
+  __syncthreads();  // the tiles are no longer read
+  float* const mg = reinterpret_cast<float*>(fa_smem) + (size_t)(warp * 32 + lane) * 68;
+  if (half == 1) {
+    mg[0] = m0, mg[1] = m1, mg[2] = l0, mg[3] = l1;
+#pragma unroll
+    for (int dt = 0; dt < 16; dt++)
+      *reinterpret_cast<float4*>(mg + 4 + 4 * dt) = make_float4(o[dt][0], o[dt][1], o[dt][2], o[dt][3]);
+  }
+  __syncthreads();
+  if (half == 1) return;
+  {
+    const float mb0 = mg[0], mb1 = mg[1];
+    const float mn0 = fmaxf(m0, mb0), mn1 = fmaxf(m1, mb1);
+    const float fa0 = expf(m0 - mn0), fb0 = expf(mb0 - mn0), fa1 = expf(m1 - mn1), fb1 = expf(mb1 - mn1);
+    l0 = l0 * fa0 + mg[2] * fb0;
+    l1 = l1 * fa1 + mg[3] * fb1;
+#pragma unroll
+    for (int dt = 0; dt < 16; dt++) {
+      const float4 ob = *reinterpret_cast<const float4*>(mg + 4 + 4 * dt);
+      o[dt][0] = o[dt][0] * fa0 + ob.x * fb0, o[dt][1] = o[dt][1] * fa0 + ob.y * fb0;
+      o[dt][2] = o[dt][2] * fa1 + ob.z * fb1, o[dt][3] = o[dt][3] * fa1 + ob.w * fb1;
+    }
+  }
   // ---- out / sum
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -227,10 +272,13 @@ int launch_attention_prefill(const AttnArgs& a, int64_t base_pos, int64_t seq, c
   f.rows = a.rows, f.nh = a.nh, f.nkv = a.nkv, f.cap = a.cap, f.base_pos = base_pos, f.seq = seq;
   f.ldq = a.ldq ? a.ldq : a.nh * FA_D;
   const dim3 grid((unsigned)a.nh, (unsigned)((a.rows + FA_BR - 1) / FA_BR));
-  if (a.kv_type == E_BF16)
-    attention_prefill_kernel<E_BF16><<<grid, 128, 0, s>>>(f);
-  else
-    attention_prefill_kernel<E_F16><<<grid, 128, 0, s>>>(f);
+  if (a.kv_type == E_BF16) {
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(attention_prefill_kernel<E_BF16>), FA_SMEM)) return 1;
+    attention_prefill_kernel<E_BF16><<<grid, FA_THREADS, FA_SMEM, s>>>(f);
+  } else {
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(attention_prefill_kernel<E_F16>), FA_SMEM)) return 1;
+    attention_prefill_kernel<E_F16><<<grid, FA_THREADS, FA_SMEM, s>>>(f);
+  }
   count_launch();
   DYN_CUDA(cudaGetLastError());
   *handled = true;

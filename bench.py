@@ -20,7 +20,8 @@ checkpoint (all linears Q4_0, tied Q6_K embedding / lm_head, GGUF v3), after a
             launch, timed alone with CUDA events over back-to-back launches (its 127.6 MB
             of weights exceed L2).
   cpu_baseline  the CPU restatement of the reference's direct path (oracle/) on the
-            host cores, on a bounded sample of the same workload.
+            host cores, on a bounded sample of the same workload (one-GPU run only; the same
+            sample checks the timed loop's first tokens, key `parity`).
 
 With N > 1 every rank runs an independent replica of the model on its own GPU
 (the 0.6B path does not shard; there is no data-path collective), so the value is
@@ -323,6 +324,8 @@ def tp_section(rank, world, local_rank, no_check=False):
         replicas.barrier()
     if not no_check:
         cores = use_all_host_threads()
+        if world > 1:
+            cores = min(cores, 8)      # the other ranks' runtime threads keep spinning on the same cores
         from oracle import oracle as orc
         from dyninfer_b200 import checkpoint as ck
         orc.build()
@@ -463,7 +466,9 @@ def main():
         }
         out["prefill"] = {"tokens": 2048, "chunk": model.chunk_size, "tokens_per_s": time_prefill(model),
                           "note": "tcgen05 dequant GEMM + tensor-core flash attention, bf16 KV"}
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
+            # the CPU baseline belongs to the one-GPU run: under a multi-rank launch the host cores are
+            # shared with the other ranks' runtime threads and the number would describe that contention
             steps, warm = 28, 4
             tps, cores, dt, cpu_toks, cpu_margins = cpu_decode(path, steps, warm=warm,
                                                                kv_round={"bf16": 2, "f16": 1, "f32": 0}[args.kv_dtype])

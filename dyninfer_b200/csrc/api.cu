@@ -51,8 +51,21 @@ int keep_scratch_pool_cached() {
 
 static thread_local void* g_scratch = nullptr;
 static thread_local size_t g_scratch_bytes = 0;
-void set_thread_scratch(void* ptr, size_t bytes) { g_scratch = ptr, g_scratch_bytes = ptr ? bytes : 0; }
-void* thread_scratch(size_t bytes) { return bytes <= g_scratch_bytes ? g_scratch : nullptr; }
+static thread_local size_t g_scratch_held = 0;
+void set_thread_scratch(void* ptr, size_t bytes) { g_scratch = ptr, g_scratch_bytes = ptr ? bytes : 0, g_scratch_held = 0; }
+void* thread_scratch(size_t bytes) {
+  return g_scratch_held + bytes <= g_scratch_bytes ? static_cast<uint8_t*>(g_scratch) + g_scratch_held : nullptr;
+}
+void thread_scratch_hold(size_t bytes) { g_scratch_held += (bytes + 255) / 256 * 256; }
+void thread_scratch_release_all() { g_scratch_held = 0; }
+
+static thread_local Deferred* g_defer = nullptr;
+void defer_request(Deferred* d) { g_defer = d; }
+Deferred* defer_take() {
+  Deferred* d = g_defer;
+  g_defer = nullptr;
+  return d;
+}
 
 bool pdl_enabled() {
   static const bool on = [] {

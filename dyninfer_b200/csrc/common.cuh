@@ -34,6 +34,42 @@ int keep_scratch_pool_cached();  // raise the default memory pool's release thre
 // allocator, so consecutive kernels of a captured graph are not separated by allocation nodes.
 void set_thread_scratch(void* ptr, size_t bytes);
 void* thread_scratch(size_t bytes);  // the region when it holds `bytes`, else nullptr
+// Keep the first `bytes` of the region out of the next products' reach (a product's K-slice sums wait
+// there for the kernel that adds them); release_all gives the whole region back.
+void thread_scratch_hold(size_t bytes);
+void thread_scratch_release_all();
+
+// The K-slice sums of a single-row product whose final addition is left to the caller's next kernel
+// (QKV prepare, SwiGLU), which saves the reduction launch: y[i] = scale[0] * sum_j partial[j][i],
+// j in ascending order, exactly what the product's own reduction kernel computes. S == 0: the product
+// wrote y itself (another kernel took it, or K was not split).
+struct Deferred {
+  const float* partial = nullptr;  // [S][N]
+  const float* scale = nullptr;    // device word
+  int S = 0;
+  int64_t N = 0;
+  size_t ws_bytes = 0;             // scratch the product occupies (hold it until the sums are consumed)
+};
+// While a DeferScope lives, the first column-split product launched on this thread with K split fills
+// `d` instead of launching its reduction.
+void defer_request(Deferred* d);
+Deferred* defer_take();
+struct DeferScope {
+  explicit DeferScope(Deferred* d) { *d = Deferred(); defer_request(d); }
+  ~DeferScope() { defer_request(nullptr); }
+};
+// A column range of deferred sums (or nothing: S == 0)
+struct DeferredCols {
+  const float* partial = nullptr;
+  const float* scale = nullptr;
+  int S = 0;
+  int64_t N = 0, col = 0;
+};
+inline DeferredCols deferred_cols(const Deferred& d, int64_t col) {
+  DeferredCols c;
+  c.partial = d.partial, c.scale = d.scale, c.S = d.S, c.N = d.N, c.col = col;
+  return c;
+}
 
 // Programmatic dependent launch (sm_90+). A kernel launched with launch_pdl may start while the
 // kernel before it in the stream is still running; it must not touch anything that kernel (or an
@@ -223,6 +259,8 @@ int launch_linear_swiglu(const WRef& wg, const WRef& wu, const float* x, int64_t
 
 int launch_rms_norm(const float* x, const void* w, int w_type, int64_t rows, int64_t width,
                     float eps, float* y, cudaStream_t s);
+// One row of [gate | up] (2 * inter values, deferred or in `gate_up`): y = silu(gate) * up
+int launch_silu_mul_deferred(const Deferred& d, const float* gate_up, int64_t inter, float* y, cudaStream_t s);
 int launch_rope(float* x, int64_t s_rows, int64_t heads, int64_t d, int64_t start_pos,
                 const FreqTable& ft, cudaStream_t s);
 int launch_silu_mul(const float* gate, const float* up, int64_t n, float* y, cudaStream_t s);
@@ -246,6 +284,8 @@ struct QkvPrepArgs {
   // floats between consecutive rows of q / k / v (0: dense, nh*d / nkv*d): the three may be column
   // ranges of one [rows, nh*d + 2*nkv*d] matrix, the output of the fused [q; k; v] product
   int64_t ldq = 0, ldk = 0, ldv = 0;
+  // one row only: q / k / v still lie as K-slice sums of their product (the reduced q is written to `q`)
+  DeferredCols dq, dk, dv;
 };
 int launch_qkv_prepare(const QkvPrepArgs& a, const FreqTable& ft, cudaStream_t s);
 

@@ -433,7 +433,10 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
   else
     DYN_CUDA(launch_pdl(gemv_cs_q4_kernel<E_Q4_1>, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a, wmap));
   count_launch(1);
-  if (p.S > 1) {
+  Deferred* defer = p.S > 1 && !residual ? defer_take() : nullptr;
+  if (defer) {
+    defer->partial = a.partial, defer->scale = a.misc, defer->S = p.S, defer->N = w.rows, defer->ws_bytes = p.bytes;
+  } else if (p.S > 1) {
     DYN_CUDA(launch_pdl(cs_reduce_kernel, dim3((unsigned)((w.rows + 255) / 256)), dim3(256), 0, s,
                         (const float*)a.partial, p.S, (int64_t)w.rows, (const float*)a.misc, y, residual));
     count_launch();

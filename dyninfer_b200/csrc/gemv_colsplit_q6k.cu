@@ -338,7 +338,10 @@ int launch_gemv_cs_q6k(const WRef& w, const void* x, int x_type, float* y, const
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(gemv_cs_q6k_kernel), Q6_MAX_SMEM)) return 1;
   DYN_CUDA(launch_pdl(gemv_cs_q6k_kernel, dim3(p.grid), dim3(Q6_WARPS * 32), p.smem, s, a));
   count_launch(1);
-  if (p.S > 1) {
+  Deferred* defer = p.S > 1 && !residual ? defer_take() : nullptr;
+  if (defer) {
+    defer->partial = a.partial, defer->scale = a.misc, defer->S = p.S, defer->N = w.rows, defer->ws_bytes = p.bytes;
+  } else if (p.S > 1) {
     DYN_CUDA(launch_pdl(q6_reduce_kernel, dim3((unsigned)((w.rows + 255) / 256)), dim3(256), 0, s, (const float*)a.partial,
                         p.S, (int64_t)w.rows, (const float*)a.misc, y, residual));
     count_launch();

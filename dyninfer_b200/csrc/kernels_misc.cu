@@ -98,6 +98,30 @@ int launch_rms_norm(const float* x, const void* w, int w_type, int64_t rows, int
   return 0;
 }
 
+// out[e] = sum over the S K-slices of partial[j][idx[e]], j ascending (the order of the products' own
+// reduction kernels), four slices' loads in flight at a time for all NE elements: a plain loop would wait
+// for one L2 round trip per slice and element.
+template <int NE>
+__device__ __forceinline__ void deferred_sums(const float* __restrict__ partial, int S, int64_t N,
+                                              const int64_t (&idx)[NE], const bool (&live)[NE], float (&out)[NE]) {
+#pragma unroll
+  for (int e = 0; e < NE; e++) out[e] = 0.f;
+  for (int j0 = 0; j0 < S; j0 += 4) {
+    float t[4][NE];
+#pragma unroll
+    for (int u = 0; u < 4; u++)
+#pragma unroll
+      for (int e = 0; e < NE; e++)
+        t[u][e] = (j0 + u < S && live[e]) ? partial[(int64_t)(j0 + u) * N + idx[e]] : 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; u++)
+      if (j0 + u < S) {
+#pragma unroll
+        for (int e = 0; e < NE; e++) out[e] += t[u][e];
+      }
+  }
+}
+
 // Rotate-half RoPE (kernels.rs:1053-1064): pair (i, i + d/2).
 __device__ __forceinline__ void rope_pair(float x1, float x2, float pos, float freq, float* lo,
                                           float* hi) {
@@ -163,6 +187,35 @@ int launch_silu_mul_rows(const float* gu, int64_t rows, int64_t I, float* y, cud
   return 0;
 }
 
+// One row of [gate | up] still lying as K-slice sums (or in gate_up when S == 0)
+__global__ void silu_mul_deferred_kernel(const float* __restrict__ partial, const float* __restrict__ scale, int S,
+                                         int64_t N, const float* __restrict__ gate_up, int64_t I, float* __restrict__ y) {
+  pdl_trigger();
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= I) return;
+  float g, u;
+  if (S) {
+    const int64_t idx[2] = {i, I + i};
+    const bool live[2] = {true, true};
+    float t[2];
+    deferred_sums<2>(partial, S, N, idx, live, t);
+    g = t[0] * scale[0], u = t[1] * scale[0];
+  } else {
+    g = gate_up[i], u = gate_up[I + i];
+  }
+  y[i] = (g / (1.0f + expf(-g))) * u;
+}
+
+int launch_silu_mul_deferred(const Deferred& d, const float* gate_up, int64_t inter, float* y, cudaStream_t s) {
+  if (inter == 0) return 0;
+  DYN_CHECK(!d.S || d.N == 2 * inter, "deferred sums of %lld rows against [gate | up] of %lld", (long long)d.N,
+            (long long)(2 * inter));
+  silu_mul_deferred_kernel<<<(unsigned)((inter + 255) / 256), 256, 0, s>>>(d.partial, d.scale, d.S, d.N, gate_up, inter, y);
+  count_launch();
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
 int launch_silu_mul(const float* gate, const float* up, int64_t n, float* y, cudaStream_t s) {
   if (n == 0) return 0;
   int64_t blocks = (n + 255) / 256;
@@ -209,14 +262,42 @@ __global__ void __launch_bounds__(128) qkv_prepare_kernel(QkvPrepArgs a, FreqTab
   const int64_t seq = a.row_seq ? a.row_seq[r] : 0;
   const int kind = hh < a.nh ? 0 : (hh < a.nh + a.nkv ? 1 : 2);
   const int64_t head = kind == 0 ? hh : (kind == 1 ? hh - a.nh : hh - a.nh - a.nkv);
+  // the head's values: from the product's output, or (one row) added up here from its K-slice sums
+  __shared__ float hv[256];
+  float* qv = a.q + r * (a.ldq ? a.ldq : a.nh * d) + head * d;
+  {
+    const DeferredCols& dc = kind == 0 ? a.dq : (kind == 1 ? a.dk : a.dv);
+    const float* in = kind == 0 ? qv
+                                : (kind == 1 ? a.k + r * (a.ldk ? a.ldk : a.nkv * d) + head * d
+                                             : a.v + r * (a.ldv ? a.ldv : a.nkv * d) + head * d);
+    if (dc.S) {
+      // up to four elements per thread (d <= 256, at least 32 or 64 threads)
+      int64_t idx[4];
+      bool live[4];
+      float t[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int64_t i = threadIdx.x + (int64_t)e * blockDim.x;
+        live[e] = i < d, idx[e] = dc.col + head * d + i;
+      }
+      deferred_sums<4>(dc.partial, dc.S, dc.N, idx, live, t);
+      const float sc = dc.scale[0];
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int64_t i = threadIdx.x + (int64_t)e * blockDim.x;
+        if (i < d) hv[i] = t[e] * sc;
+      }
+    } else {
+      for (int64_t i = threadIdx.x; i < d; i += blockDim.x) hv[i] = in[i];
+    }
+    __syncthreads();
+  }
   if (kind == 2) {
-    const float* src = a.v + r * (a.ldv ? a.ldv : a.nkv * d) + head * d;
     T* dst = reinterpret_cast<T*>(a.vcache) + ((seq * a.nkv + head) * a.cap + pos) * d;
-    for (int64_t i = threadIdx.x; i < d; i += blockDim.x) dst[i] = KvT<KV>::enc(src[i]);
+    for (int64_t i = threadIdx.x; i < d; i += blockDim.x) dst[i] = KvT<KV>::enc(hv[i]);
     return;
   }
-  float* qv = a.q + r * (a.ldq ? a.ldq : a.nh * d) + head * d;
-  const float* src = kind == 0 ? qv : a.k + r * (a.ldk ? a.ldk : a.nkv * d) + head * d;
+  const float* src = hv;
   const void* nw = kind == 0 ? a.q_norm_w : a.k_norm_w;
   float inv = 1.f;
   if (a.has_norm) {

@@ -587,12 +587,18 @@ int launch_attention(const AttnArgs& a, cudaStream_t s) {
     if (nsplit > by_cap) nsplit = by_cap;
     if (nsplit > 32) nsplit = 32;
     if (nsplit < 1) nsplit = 1;
-    if (keep_scratch_pool_cached()) return 1;
-    float* part = nullptr;
-    DYN_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&part), attention_split_scratch_bytes(a.rows, a.nh, a.d, nsplit), s));
+    // the slices' partial results: the caller's scratch region when it is large enough (a session's:
+    // no allocation nodes in a captured step), else the stream-ordered allocator
+    const size_t part_bytes = attention_split_scratch_bytes(a.rows, a.nh, a.d, nsplit);
+    float* part = reinterpret_cast<float*>(thread_scratch(part_bytes));
+    const bool pooled = part == nullptr;
+    if (pooled) {
+      if (keep_scratch_pool_cached()) return 1;
+      DYN_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&part), part_bytes, s));
+    }
     bool handled = false;
     const int rc = launch_attention_split(a, part, nsplit, s, &handled);
-    const cudaError_t fe = cudaFreeAsync(part, s);
+    const cudaError_t fe = pooled ? cudaFreeAsync(part, s) : cudaSuccess;
     if (rc) return rc;
     if (fe != cudaSuccess) return cuda_fail(fe, "cudaFreeAsync", __FILE__, __LINE__);
     if (handled) return 0;

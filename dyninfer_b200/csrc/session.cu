@@ -1023,9 +1023,15 @@ int dyninfer_cuda_session_create_with_file_params(
     for (const LayerW& L : s->layers) {
       const WRef* ws[7] = {&L.q, &L.k, &L.v, &L.o, &L.gate, &L.up, &L.down};
       for (const WRef* wp : ws) grow(*wp);
+      if (L.qkv_parts >= 2) grow(L.qkv);
+      if (L.gate_up.data) grow(L.gate_up);
     }
     if (need) {
       need = need * 3 + 1024;  // up to three products' K-slice sums wait for the kernel that adds them
+      for (int64_t r : {(int64_t)1, (int64_t)std::max(1, cfg.batch)}) {  // decode attention's slice results
+        const int64_t per = std::max<int64_t>(1, std::min<int64_t>(32, 592 / (r * cfg.heads)));
+        need = std::max(need, attention_split_scratch_bytes(r, cfg.heads, cfg.head_dim, (int)per));
+      }
       if (dev_alloc(s, &s->scratch, need)) return fail();
       s->scratch_bytes = need;
       set_thread_scratch(s->scratch, s->scratch_bytes);  // `scope` was entered before the region existed

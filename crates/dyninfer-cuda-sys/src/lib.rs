@@ -22,6 +22,9 @@ pub const DYNINFER_ENC_Q4_1: i32 = 4;
 pub const DYNINFER_ENC_Q8_0: i32 = 5;
 pub const DYNINFER_ENC_Q6_K: i32 = 6;
 pub const DYNINFER_ENC_MLX_U4: i32 = 7;
+pub const DYNINFER_ENC_Q4_K: i32 = 8;
+pub const DYNINFER_ENC_Q5_K: i32 = 9;
+pub const DYNINFER_ENC_IQ4_XS: i32 = 10;
 
 /// Opaque session: one KV cache, one parameter arena, one stream.
 #[repr(C)]

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("DYNINFER_CUDA_LIB") or os.path.join(HERE, "libdyninfer_cuda.so")
 
 ENC = {"plain.f32": 0, "plain.f16": 1, "plain.bf16": 2, "gguf.q4_0": 3, "gguf.q4_1": 4,
-       "gguf.q8_0": 5, "gguf.q6_k": 6, "mlx.affine.u4": 7, "gguf.q4_k": 8, "gguf.q5_k": 9}
+       "gguf.q8_0": 5, "gguf.q6_k": 6, "mlx.affine.u4": 7, "gguf.q4_k": 8, "gguf.q5_k": 9, "gguf.iq4_xs": 10}
 ENC_NAME = {v: k for k, v in ENC.items()}
 
 

@@ -35,6 +35,7 @@ GGML_TYPES = {
     12: ("gguf.q4_k", 256, 144),
     13: ("gguf.q5_k", 256, 176),
     14: ("gguf.q6_k", 256, 210),
+    23: ("gguf.iq4_xs", 256, 136),
     30: ("plain.bf16", 1, 2),
 }
 GGML_CODE = {v[0]: k for k, v in GGML_TYPES.items()}
@@ -44,7 +45,6 @@ GGML_SCHEMA_ONLY = {
     6: ("gguf.q5_0", 32, 22), 7: ("gguf.q5_1", 32, 24), 9: ("gguf.q8_1", 32, 36),
     10: ("gguf.q2_k", 256, 84), 11: ("gguf.q3_k", 256, 110), 15: ("gguf.q8_k", 256, 292),
     20: ("gguf.iq4_nl", 32, 18),
-    23: ("gguf.iq4_xs", 256, 136),
 }
 
 ST_DTYPES = {"F32": ("plain.f32", 4), "F16": ("plain.f16", 2), "BF16": ("plain.bf16", 2),

@@ -184,6 +184,41 @@ struct Codec<E_Q4_K> : KQuant45<E_Q4_K> {};
 template <>
 struct Codec<E_Q5_K> : KQuant45<E_Q5_K> {};
 
+// IQ4_XS (a non-linear 4-bit K-quant of UD-Q4_K_XL files; schema-only in the reference,
+// crates/dyninfer-checkpoint-gguf/src/types.rs, so the arithmetic follows GGML's published
+// dequantisation as the `gguf` Python package evaluates it in f32): 256 weights in 136 bytes:
+//   f16 d @0, u16 scales_h @2, 4 bytes scales_l @4, 128 index bytes @8.
+//   sub-block ib (32 weights, ib < 8): 6-bit scale ls = nibble (ib & 1) of scales_l[ib / 2] | bits
+//   [2 ib, 2 ib + 2) of scales_h << 4; weight 32 ib + j (j < 16) = low nibble of byte 16 ib + j,
+//   weight 32 ib + 16 + j its high nibble; w = (f32(d) * f32(ls - 32)) * f32(table[index]), each
+//   product rounded on its own.
+// A part is (ib, 4 consecutive j); group g = nibble.
+__device__ __forceinline__ float iq4_value(uint32_t idx) {
+  // -127 -104 -83 -65 -49 -35 -22 -10 | 1 13 25 38 53 69 89 113 as two's-complement bytes
+  const uint64_t lo = 0xF6EADDCFBFAD9881ull, hi = 0x7159453526190D01ull;
+  return (float)(int)(int8_t)(((idx & 8u) ? hi : lo) >> (8u * (idx & 7u)));
+}
+template <>
+struct Codec<E_IQ4_XS> {
+  static constexpr int BLOCK = 256, BYTES = 136, PARTS = 32, G = 2, CHUNK_DIV = 64;
+  __device__ static __forceinline__ int xoff(int part, int g) { return (part >> 2) * 32 + g * 16 + 4 * (part & 3); }
+  __device__ static __forceinline__ void decode(const RowPtr& r, int64_t blk, int part, float* w) {
+    const uint8_t* b = r.data + blk * BYTES;  // 136 is a multiple of 8: blocks stay word aligned
+    const int ib = part >> 2, j4 = part & 3;
+    const uint32_t head = *reinterpret_cast<const uint32_t*>(b);       // d | scales_h << 16
+    const uint32_t sl = *reinterpret_cast<const uint32_t*>(b + 4);
+    const uint32_t q = *reinterpret_cast<const uint32_t*>(b + 8 + 16 * ib + 4 * j4);
+    const uint32_t ls = ((sl >> (4 * ib)) & 15u) | ((((head >> 16) >> (2 * ib)) & 3u) << 4);
+    const float dl = __fmul_rn(f16_bits_to_f32(head & 0xffffu), (float)((int)ls - 32));
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint32_t byte = (q >> (8 * i)) & 0xffu;
+      w[i] = __fmul_rn(dl, iq4_value(byte & 15u));
+      w[4 + i] = __fmul_rn(dl, iq4_value(byte >> 4));
+    }
+  }
+};
+
 // MLX affine U4: ui32[N, K/8], lane k of a word = bits [4k, 4k+4); per group:
 // w = f32(q)*scale + bias. mlx_affine.rs:284-290,590-600. One word is one "block".
 template <>
@@ -246,6 +281,7 @@ struct Codec<E_BF16> {
     case E_MLX_U4: { constexpr int ENC = E_MLX_U4; __VA_ARGS__; } break; \
     case E_Q4_K: { constexpr int ENC = E_Q4_K; __VA_ARGS__; } break;     \
     case E_Q5_K: { constexpr int ENC = E_Q5_K; __VA_ARGS__; } break;     \
+    case E_IQ4_XS: { constexpr int ENC = E_IQ4_XS; __VA_ARGS__; } break; \
     default:                                            \
       dyn::set_error("unknown encoding %d", (int)(enc)); \
       return 1;                                         \

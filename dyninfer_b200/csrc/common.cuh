@@ -128,7 +128,8 @@ enum : int {
   E_MLX_U4 = DYNINFER_ENC_MLX_U4,
   E_Q4_K = DYNINFER_ENC_Q4_K,
   E_Q5_K = DYNINFER_ENC_Q5_K,
-  E_LAST = DYNINFER_ENC_Q5_K,
+  E_IQ4_XS = DYNINFER_ENC_IQ4_XS,
+  E_LAST = DYNINFER_ENC_IQ4_XS,
 };
 
 __host__ __device__ inline int enc_block_elems(int enc) {
@@ -140,6 +141,7 @@ __host__ __device__ inline int enc_block_elems(int enc) {
     case E_Q6_K:
     case E_Q4_K:
     case E_Q5_K:
+    case E_IQ4_XS:
       return 256;
     case E_MLX_U4:
       return 8;
@@ -166,6 +168,8 @@ __host__ __device__ inline int enc_block_bytes(int enc) {
       return 144;
     case E_Q5_K:
       return 176;
+    case E_IQ4_XS:
+      return 136;
     case E_MLX_U4:
       return 4;
     default:

@@ -625,6 +625,7 @@ bool tg_shape_ok(const WRef& w, int64_t M) {
     case E_Q6_K:
     case E_Q4_K:
     case E_Q5_K:
+    case E_IQ4_XS:
     case E_F32:
     case E_F16:
     case E_BF16: break;
@@ -636,7 +637,7 @@ bool tg_shape_ok(const WRef& w, int64_t M) {
   const uintptr_t addr = reinterpret_cast<uintptr_t>(w.data);
   if ((w.enc == E_Q4_0 || w.enc == E_Q4_1 || w.enc == E_Q8_0 || w.enc == E_MLX_U4) && (addr & 3)) return false;
   if (w.enc == E_Q6_K && (addr & 1)) return false;
-  return M >= 1 && w.rows >= 1 && w.cols >= TG_BK && w.cols % ((w.enc == E_Q6_K || w.enc == E_Q4_K || w.enc == E_Q5_K) ? 256 : TG_BK) == 0;
+  return M >= 1 && w.rows >= 1 && w.cols >= TG_BK && w.cols % (enc_block_elems(w.enc) == 256 ? 256 : TG_BK) == 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -769,6 +770,7 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
     case E_Q6_K: rc = tg_launch<E_Q6_K>(a, xmap, grid, smem, s); break;
     case E_Q4_K: rc = tg_launch<E_Q4_K>(a, xmap, grid, smem, s); break;
     case E_Q5_K: rc = tg_launch<E_Q5_K>(a, xmap, grid, smem, s); break;
+    case E_IQ4_XS: rc = tg_launch<E_IQ4_XS>(a, xmap, grid, smem, s); break;
     case E_MLX_U4: rc = tg_launch<E_MLX_U4>(a, xmap, grid, smem, s); break;
     case E_F32: rc = tg_launch<E_F32>(a, xmap, grid, smem, s); break;
     case E_F16: rc = tg_launch<E_F16>(a, xmap, grid, smem, s); break;

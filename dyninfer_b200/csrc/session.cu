@@ -158,6 +158,7 @@ int enc_from_name(const std::string& n) {
   if (n == "gguf.q6_k") return E_Q6_K;
   if (n == "gguf.q4_k") return E_Q4_K;
   if (n == "gguf.q5_k") return E_Q5_K;
+  if (n == "gguf.iq4_xs") return E_IQ4_XS;
   if (n == "mlx.affine.u4") return E_MLX_U4;
   return -1;
 }

@@ -143,7 +143,7 @@ class KernelRegistry:
 CUDA_SM100 = TargetConstraint(("cuda",), ("sm_100a", "sm_100"), ())
 # (encoding, elements per block along the input axis)
 CUDA_ENCODINGS = (("gguf.q4_0", 32), ("gguf.q4_1", 32), ("gguf.q8_0", 32), ("gguf.q6_k", 256),
-                  ("gguf.q4_k", 256), ("gguf.q5_k", 256),
+                  ("gguf.q4_k", 256), ("gguf.q5_k", 256), ("gguf.iq4_xs", 256),
                   ("mlx.affine.u4", 64), ("plain.bf16", 4), ("plain.f16", 4), ("plain.f32", 4))
 
 

@@ -153,6 +153,16 @@ def random_weight(enc: str, rows: int, cols: int, seed: int, group: int = 64):
         blk[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
         blk[:, 2:4] = dmin.view(np.uint8).reshape(-1, 2)
         return {"data": blk.reshape(-1)}
+    if enc == "gguf.iq4_xs":
+        # uniform 4-bit table indices and 6-bit sub-block scales; f16 d sized for std ~= 0.02:
+        # w = d * (ls - 32) * table[q], rms(ls - 32) ~= 18.5, rms(table) ~= 69 (d lands among the f16
+        # subnormals, as it does in real files)
+        nb = rows * cols // 256
+        blk = np.empty((nb, 136), dtype=np.uint8)
+        blk[:, 2:] = rng.integers(0, 256, size=(nb, 134), dtype=np.uint8)
+        d = (np.float32(0.02 / (18.5 * 69.0)) * rng.uniform(0.5, 1.5, size=nb).astype(np.float32)).astype(np.float16)
+        blk[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+        return {"data": blk.reshape(-1)}
     if enc == "mlx.affine.u4":
         packed = rng.integers(0, 2 ** 32, size=(rows, cols // 8), dtype=np.uint32)
         s = (np.float32(0.0043) * rng.uniform(0.5, 1.5, size=(rows, cols // group)).astype(np.float32))

@@ -25,7 +25,7 @@ COLUMN = ("attn_q", "attn_k", "attn_v", "ffn_gate", "ffn_up")
 ROW = ("attn_output", "ffn_down")
 
 # (elements per block, bytes per block) of the row-major encodings
-_BLOCK = {"gguf.q4_0": (32, 18), "gguf.q4_1": (32, 20), "gguf.q8_0": (32, 34), "gguf.q6_k": (256, 210), "gguf.q4_k": (256, 144), "gguf.q5_k": (256, 176),
+_BLOCK = {"gguf.q4_0": (32, 18), "gguf.q4_1": (32, 20), "gguf.q8_0": (32, 34), "gguf.q6_k": (256, 210), "gguf.q4_k": (256, 144), "gguf.q5_k": (256, 176), "gguf.iq4_xs": (256, 136),
           "plain.f32": (1, 4), "plain.f16": (1, 2), "plain.bf16": (1, 2)}
 
 

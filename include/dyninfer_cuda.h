@@ -47,7 +47,8 @@ enum {
   DYNINFER_ENC_Q6_K = 6,   /* gguf.q6_k: 256 el / 210 B */
   DYNINFER_ENC_MLX_U4 = 7, /* mlx.affine.u4: u32 words + scales + biases */
   DYNINFER_ENC_Q4_K = 8,   /* gguf.q4_k: 256 el / 144 B */
-  DYNINFER_ENC_Q5_K = 9    /* gguf.q5_k: 256 el / 176 B */
+  DYNINFER_ENC_Q5_K = 9,   /* gguf.q5_k: 256 el / 176 B */
+  DYNINFER_ENC_IQ4_XS = 10 /* gguf.iq4_xs: 256 el / 136 B */
 };
 
 /* One [rows, cols] parameter as the verbatim checkpoint bytes, resident in

@@ -9,7 +9,7 @@
  * reference file:line it follows.
  *
  * Pin status:
- *   - dequantisation of Q4_0 / Q4_1 / Q8_0 / Q6_K / Q4_K / Q5_K: pinned, bit for bit,
+ *   - dequantisation of Q4_0 / Q4_1 / Q8_0 / Q6_K / Q4_K / Q5_K / IQ4_XS: pinned, bit for bit,
  *     against the third-party `gguf` Python package and against the
  *     reference's own fixture packers restated in tests/fixtures_ref.py
  *     (crates/dyninfer-checkpoint-gguf/src/q4.rs:16-128).
@@ -45,7 +45,8 @@ enum {
   ORC_Q6_K = 6,
   ORC_MLX_U4 = 7,
   ORC_Q4_K = 8,
-  ORC_Q5_K = 9
+  ORC_Q5_K = 9,
+  ORC_IQ4_XS = 10
 };
 
 typedef struct {
@@ -134,6 +135,7 @@ ORC_API int64_t orc_block_elems(int enc) {
     case ORC_Q6_K:
     case ORC_Q4_K:
     case ORC_Q5_K:
+    case ORC_IQ4_XS:
       return 256;
     case ORC_MLX_U4:
       return 8;
@@ -160,6 +162,8 @@ ORC_API int64_t orc_block_bytes(int enc) {
       return 144;
     case ORC_Q5_K:
       return 176;
+    case ORC_IQ4_XS:
+      return 136;
     case ORC_MLX_U4:
       return 4;
     default:
@@ -269,6 +273,29 @@ static void dq_q45_k(const uint8_t* blk, float* out, int five) {
   }
 }
 
+/* IQ4_XS: schema-only in the reference (crates/dyninfer-checkpoint-gguf/src/types.rs), so this restates
+ * GGML's published dequantisation as the third-party `gguf` package evaluates it, in f32: f16 d at 0,
+ * u16 scales_h at 2, 4 bytes scales_l at 4, 128 index bytes at 8. Sub-block ib (32 weights): 6-bit scale
+ * ls = nibble (ib & 1) of scales_l[ib / 2] | bits [2 ib, 2 ib + 2) of scales_h << 4; weight 32 ib + j
+ * (j < 16) takes the low nibble of byte 16 ib + j, weight 32 ib + 16 + j its high nibble, as an index
+ * into the 16-entry table below; w = (d * (ls - 32)) * table[index], each product rounded on its own.
+ * Pinned by tests/golden/dequant_golden.npz. */
+static const int8_t iq4_table[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+static void dq_iq4_xs(const uint8_t* blk, float* out) {
+  const float d = f16_to_f32(rd16(blk));
+  const unsigned sh = rd16(blk + 2);
+  const uint8_t* sl = blk + 4;
+  const uint8_t* qs = blk + 8;
+  for (int ib = 0; ib < 8; ib++) {
+    const int ls = (int)(((sl[ib >> 1] >> (4 * (ib & 1))) & 15u) | (((sh >> (2 * ib)) & 3u) << 4));
+    const float dl = d * (float)(ls - 32);
+    for (int j = 0; j < 16; j++) {
+      out[32 * ib + j] = dl * (float)iq4_table[qs[16 * ib + j] & 15u];
+      out[32 * ib + 16 + j] = dl * (float)iq4_table[qs[16 * ib + j] >> 4];
+    }
+  }
+}
+
 ORC_API void orc_dequant_row(const orc_tensor* t, int64_t row, float* out) {
   const int64_t K = t->cols;
   switch (t->enc) {
@@ -304,6 +331,10 @@ ORC_API void orc_dequant_row(const orc_tensor* t, int64_t row, float* out) {
     case ORC_Q5_K: {
       const uint8_t* p = t->data + row * (K / 256) * 176;
       for (int64_t b = 0; b < K / 256; b++) dq_q45_k(p + b * 176, out + b * 256, 1);
+    } break;
+    case ORC_IQ4_XS: {
+      const uint8_t* p = t->data + row * (K / 256) * 136;
+      for (int64_t b = 0; b < K / 256; b++) dq_iq4_xs(p + b * 136, out + b * 256);
     } break;
     case ORC_MLX_U4: {
       /* packed ui32[N, K/8], lane k of a word is bits [4k, 4k+4); per group of

@@ -14,11 +14,11 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_build", "liboracle.so")
 
-F32, F16, BF16, Q4_0, Q4_1, Q8_0, Q6_K, MLX_U4, Q4_K, Q5_K = range(10)
+F32, F16, BF16, Q4_0, Q4_1, Q8_0, Q6_K, MLX_U4, Q4_K, Q5_K, IQ4_XS = range(11)
 ENC_BY_NAME = {
     "plain.f32": F32, "plain.f16": F16, "plain.bf16": BF16,
     "gguf.q4_0": Q4_0, "gguf.q4_1": Q4_1, "gguf.q8_0": Q8_0, "gguf.q6_k": Q6_K,
-    "mlx.affine.u4": MLX_U4, "gguf.q4_k": Q4_K, "gguf.q5_k": Q5_K,
+    "mlx.affine.u4": MLX_U4, "gguf.q4_k": Q4_K, "gguf.q5_k": Q5_K, "gguf.iq4_xs": IQ4_XS,
 }
 
 

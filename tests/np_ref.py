@@ -71,6 +71,24 @@ def dequant(enc, raw, rows, cols, scales=None, biases=None, group=64):
             dm = dmin * mn[:, j].astype(np.float32)
             w[:, j, :] = ds[:, None] * q.astype(np.float32) - dm[:, None]
         w = w.reshape(nb, 256)
+    elif enc == "gguf.iq4_xs":
+        # GGML's published layout (schema-only in the reference): d f16, scales_h u16, 4 bytes scales_l,
+        # 128 index bytes; sub-block scale = 6 bits - 32, value = 16-entry table
+        table = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.float32)
+        b = raw.reshape(-1, 136)
+        nb = b.shape[0]
+        d = _f16(b[:, 0:2])
+        sh = b[:, 2:4].copy().view(np.uint16).reshape(nb).astype(np.uint32)
+        sl = b[:, 4:8].astype(np.uint32)
+        qs = b[:, 8:136]
+        w = np.empty((nb, 8, 32), np.float32)
+        for ib in range(8):
+            ls = ((sl[:, ib // 2] >> (4 * (ib % 2))) & 15) | (((sh >> (2 * ib)) & 3) << 4)
+            dl = d * (ls.astype(np.int32) - 32).astype(np.float32)
+            q = qs[:, 16 * ib:16 * ib + 16]
+            w[:, ib, :16] = dl[:, None] * table[q & 15]
+            w[:, ib, 16:] = dl[:, None] * table[q >> 4]
+        w = w.reshape(nb, 256)
     elif enc == "mlx.affine.u4":
         words = raw.view(np.uint32).reshape(rows, cols // 8)
         q = np.stack([(words >> np.uint32(4 * k)) & np.uint32(15) for k in range(8)], axis=-1)

@@ -48,7 +48,7 @@ def test_argument_validation_precedes_any_launch(native_lib):
     assert rc != 0 and "model descriptor" in _lib.last_error()
     rc = native_lib.dyninfer_cuda_session_create_with_file_params(
         b"cuda", b'{"layers":1,"hidden":64,"intermediate":128,"heads":4,"head_dim":16,"vocab":32,'
-        b'"params":{"token_embd.weight":{"encoding":"gguf.iq4_xs","shape":[32,64]}}}', None, 0, None, 0, C.byref(h))
+        b'"params":{"token_embd.weight":{"encoding":"gguf.q3_k","shape":[32,64]}}}', None, 0, None, 0, C.byref(h))
     assert rc != 0 and "E_KERNEL_COVERAGE" in _lib.last_error()
     assert native_lib.dyninfer_cuda_session_invoke_paged_chunk(None, None, 0, 0, 0, None, None, None, 0) != 0
     assert native_lib.dyninfer_cuda_session_kv_page_count(None) == 0

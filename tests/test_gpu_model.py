@@ -81,11 +81,11 @@ def test_gqa_rope_qknorm_prefill_vs_decode(native_lib, oracle, tmp_path):
 
 
 def test_k_quant_tensors_in_a_mixed_model(native_lib, oracle, tmp_path):
-    """Q4_K and Q5_K linears (what Q4_K_M / UD-Q4_K_XL files mix with Q4_0 and Q6_K) through the
+    """Q4_K, Q5_K and IQ4_XS linears (what Q4_K_M / UD-Q4_K_XL files mix with Q4_0 and Q6_K) through the
     operator path: prompt in chunks (tensor-core GEMM), then single-row steps."""
     path = synth.write_qwen3_gguf(str(tmp_path / "kq.gguf"), synth.TINY, seed=13,
-                                  encodings={"attn_q": "gguf.q4_k", "attn_output": "gguf.q5_k", "ffn_gate": "gguf.q4_k",
-                                             "ffn_up": "gguf.q4_k", "ffn_down": "gguf.q5_k"})
+                                  encodings={"attn_q": "gguf.q4_k", "attn_k": "gguf.iq4_xs", "attn_output": "gguf.q5_k",
+                                             "ffn_gate": "gguf.q4_k", "ffn_up": "gguf.iq4_xs", "ffn_down": "gguf.q5_k"})
     cat = ck.open_catalog(path)
     prompt = np.random.default_rng(8).integers(0, synth.TINY["vocab"], size=40).tolist()
     want_logits, want_toks, margins = oracle_run(oracle, cat, prompt, 6)

@@ -10,7 +10,7 @@ from dyninfer_b200 import synth
 pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
-GGUF_ENCS = ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "gguf.q4_k", "gguf.q5_k"]
+GGUF_ENCS = ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "gguf.q4_k", "gguf.q5_k", "gguf.iq4_xs"]
 ENCS = GGUF_ENCS + ["mlx.affine.u4", "plain.bf16", "plain.f16", "plain.f32"]
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "dequant_golden.npz")
 

@@ -10,7 +10,7 @@ import np_ref
 from dyninfer_b200 import synth
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "dequant_golden.npz")
-GGUF_ENCS = ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "gguf.q4_k", "gguf.q5_k"]
+GGUF_ENCS = ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "gguf.q4_k", "gguf.q5_k", "gguf.iq4_xs"]
 
 
 @pytest.mark.parametrize("enc", GGUF_ENCS)

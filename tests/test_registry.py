@@ -41,8 +41,8 @@ def test_strict_rejection_reasons():
     r = reg.default_registry()
     cuda = reg.TargetProfile.cuda()
     # unregistered encoding -> E_KERNEL_COVERAGE, never a fallback
-    with pytest.raises(reg.KernelCoverageError, match="E_KERNEL_COVERAGE.*gguf.iq4_xs"):
-        r.require(reg.KernelRequest("blk.0.attn_q", "Linear", "gguf.iq4_xs", (1024, 1024)), cuda)
+    with pytest.raises(reg.KernelCoverageError, match="E_KERNEL_COVERAGE.*gguf.q3_k"):
+        r.require(reg.KernelRequest("blk.0.attn_q", "Linear", "gguf.q3_k", (1024, 1024)), cuda)
     # exact architecture match (kernel-registry lib.rs:627-740 `cuda.sm100`)
     rep = r.select(reg.KernelRequest("q", "Linear", "gguf.q4_0", (1024, 1024)), reg.TargetProfile.cuda("sm_90a"))
     assert rep.selected is None and any("architecture_mismatch" in w for _, ws in rep.rejected for w in ws)
@@ -65,7 +65,7 @@ def test_loader_rejects_uncovered_model_and_cpu_target(tmp_path):
     with pytest.raises(DynInferError, match="no CPU fallback"):
         ld.load(path, target="cpu")
     cat = ld.bind(path)
-    cat.parameters["blk.0.attn_q.weight"].encoding = "gguf.iq4_xs"
+    cat.parameters["blk.0.attn_q.weight"].encoding = "gguf.q3_k"
     rep = ld.kernel_coverage(cat, reg.TargetProfile.cuda())
     assert len(rep.missing) == 2          # prefill + decode
     with pytest.raises(reg.KernelCoverageError, match="E_KERNEL_COVERAGE"):

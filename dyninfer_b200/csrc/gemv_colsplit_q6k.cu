@@ -13,15 +13,21 @@
 // index is n*8 + h*4 + t. The activations stay in natural order (sub-block = 16 consecutive
 // elements), as two f16 arrays hi and lo in shared memory.
 //
-// Data movement: per warp a ring of two stages of 16 rows x 2 superblocks (420 bytes). Rows of
-// 210-byte superblocks are only 4-byte aligned, so each row copy (cp.async.bulk) starts at the
-// 16-byte boundary below its first byte and the lane adds the remainder when it reads; the second
-// superblock of a stage sits 2 bytes off the word grid and is read with funnel shifts. All waits
-// are bounded.
+// Data movement: per warp a ring of two stages of 16 rows x 2 superblocks (420 bytes). A stage's
+// 420 bytes of a row start anywhere on the 4-byte grid, so every copy starts at the 16-byte boundary
+// below the first byte (432 bytes per row) and the lane adds the remainder when it reads; the second
+// superblock of a stage sits 2 bytes off the word grid and is read with funnel shifts. The copies are
+// 2-D tensor copies where the layout allows a tensor map (row strides must be multiples of 16 bytes):
+// rows of a multiple of 16 bytes (K a multiple of 2048) as one box of 16 rows per stage; rows of
+// 8 mod 16 bytes (K = 1024, 5120: the lm_head) with an even row count as a matrix of ROW PAIRS, one box
+// of 8 pairs for the stage's even rows and one for its odd rows (in shared memory: even rows first) --
+// two requests to the copy engine instead of sixteen. Otherwise one cp.async.bulk per row. All waits are
+// bounded.
 #include <algorithm>
 
 #include "gemv_core.cuh"
 #include "ring.cuh"
+#include "tensor_map.cuh"
 
 namespace dyn {
 
@@ -49,6 +55,7 @@ struct Q6Args {
   const float* residual;
   float* partial;
   int* error;
+  int mode;  // how a stage is copied: 0 one bulk copy per row, 1 one box of 16 rows, 2 two boxes of 8 row pairs
 };
 
 // Activation row -> shared memory: xhi[K], 16 bytes of padding, xlo[K] (f16, natural order, scaled
@@ -159,7 +166,8 @@ __device__ __forceinline__ void q6_superblock(const uint8_t* b0, const uint8_t* 
   }
 }
 
-__global__ void __launch_bounds__(Q6_WARPS * 32, 1) gemv_cs_q6k_kernel(const Q6Args a) {
+__global__ void __launch_bounds__(Q6_WARPS * 32, 1)
+gemv_cs_q6k_kernel(const Q6Args a, const __grid_constant__ CUtensorMap wmap) {
   extern __shared__ __align__(128) uint8_t q6_smem[];
   __shared__ int s_abort;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -193,7 +201,18 @@ __global__ void __launch_bounds__(Q6_WARPS * 32, 1) gemv_cs_q6k_kernel(const Q6A
     c_left--;
     if (lane == 0) mbar_expect_tx(bars + c_slot, 16 * Q6_COPYB);
     __syncwarp();
-    if (lane < 16) {
+    if (a.mode) {
+      if (lane == 0) {
+        const int64_t coff = (int64_t)(c_sl * nst + c_st) * Q6_ROWB;
+        uint8_t* dst = ring + c_slot * Q6_STAGE;
+        if (a.mode == 1) {
+          tma_box_g2s(dst, &wmap, (int)((coff >> 4) << 2), c_tile * 16, bars + c_slot);
+        } else {
+          tma_box_g2s(dst, &wmap, (int)((coff >> 4) << 2), c_tile * 8, bars + c_slot);
+          tma_box_g2s(dst + 8 * Q6_PITCH, &wmap, (int)(((a.rb + coff) >> 4) << 2), c_tile * 8, bars + c_slot);
+        }
+      }
+    } else if (lane < 16) {
       int64_t row = (int64_t)c_tile * 16 + lane;
       if (row > last_row) row = last_row;
       const uint8_t* src = a.data + row * a.rb + (int64_t)(c_sl * nst + c_st) * Q6_ROWB;
@@ -237,8 +256,11 @@ __global__ void __launch_bounds__(Q6_WARPS * 32, 1) gemv_cs_q6k_kernel(const Q6A
       const uint32_t off0 = (uint32_t)(reinterpret_cast<uintptr_t>(a.data + r0c * a.rb + coff) & 15);
       const uint32_t off1 = (uint32_t)(reinterpret_cast<uintptr_t>(a.data + r1c * a.rb + coff) & 15);
       const uint8_t* base = ring + slot * Q6_STAGE;
-      const uint8_t* b0 = base + g * Q6_PITCH + off0;
-      const uint8_t* b1 = base + (g + 8) * Q6_PITCH + off1;
+      // rows g and g + 8 of the tile; pair mode keeps the tile's even rows in the first eight slots
+      const int sr0 = a.mode == 2 ? (g & 1) * 8 + (g >> 1) : g;
+      const int sr1 = a.mode == 2 ? sr0 + 4 : g + 8;
+      const uint8_t* b0 = base + sr0 * Q6_PITCH + off0;
+      const uint8_t* b1 = base + sr1 * Q6_PITCH + off1;
       const int kbase = (sl * nst + st) * Q6_KSTAGE;
       q6_superblock<0>(b0, b1, t, active, g, xhi, xlo, sx, kbase, acc0, acc1);
       q6_superblock<2>(b0 + 210, b1 + 210, t, active, g, xhi, xlo, sx, kbase + 256, acc0, acc1);
@@ -335,8 +357,19 @@ int launch_gemv_cs_q6k(const WRef& w, const void* x, int x_type, float* y, const
   a.misc = reinterpret_cast<float*>(ws + 64);
   a.partial = reinterpret_cast<float*>(ws + 256);
   a.y = y, a.residual = residual;
+  CUtensorMap wmap;
+  memset(&wmap, 0, sizeof wmap);
+  a.mode = 0;
+  static_assert(Q6_COPYB % 16 == 0 && Q6_PITCH == Q6_COPYB && (8 * Q6_PITCH) % 128 == 0, "boxes land row after row");
+  if (a.rb % 16 == 0) {
+    if (make_row_box_map(w.data, (size_t)a.rb, w.rows, Q6_COPYB / 4, 16, &wmap)) return 1;
+    a.mode = 1;
+  } else if (a.rb % 8 == 0 && w.rows % 2 == 0) {
+    if (make_row_box_map(w.data, (size_t)a.rb * 2, w.rows / 2, Q6_COPYB / 4, 8, &wmap)) return 1;
+    a.mode = 2;
+  }
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(gemv_cs_q6k_kernel), Q6_MAX_SMEM)) return 1;
-  DYN_CUDA(launch_pdl(gemv_cs_q6k_kernel, dim3(p.grid), dim3(Q6_WARPS * 32), p.smem, s, a));
+  DYN_CUDA(launch_pdl(gemv_cs_q6k_kernel, dim3(p.grid), dim3(Q6_WARPS * 32), p.smem, s, a, wmap));
   count_launch(1);
   Deferred* defer = p.S > 1 && !residual ? defer_take() : nullptr;
   if (defer) {

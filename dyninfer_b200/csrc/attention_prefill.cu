@@ -3,14 +3,19 @@
 //
 // Same mathematics as the per-row kernel (kernels.rs:310-458: s = (q.k) * 1/sqrt(d), keys beyond the
 // row's position masked, online max / sum merge, out / sum at the end), restructured the usual
-// flash-attention way: one CTA = one query head x 64 consecutive rows, eight warps: warp w takes the
-// 16 rows of group w mod 4 and, of every pair of 64-key blocks, the block w / 4, so two blocks are
-// worked on at once; the pairs stream through shared memory with cp.async, the next pair in flight
-// while the current one is used (four K + V tiles resident). The two halves' running (max, sum, out)
-// are merged at the end. S = Q K^T and O += P V run on mma.sync.m16n8k16 with f32 accumulators. The cache entries are used
+// flash-attention way: one CTA = one query head x 64 consecutive rows. The 64-key blocks stream through
+// shared memory with cp.async, the next group of blocks in flight while the current one is used.
+// Two shapes of CTA: when the grid is no larger than the GPU (a 512-row chunk of a 16-head model: 128
+// CTAs), eight warps -- warp w takes the 16 rows of group w mod 4 and, of every PAIR of blocks, block
+// w / 4, so two blocks are worked on at once and the two halves' running (max, sum, out) are merged at
+// the end (four K + V tiles resident, one CTA per SM); for larger grids four warps and one block at a
+// time (two tiles resident, two CTAs per SM). S = Q K^T and O += P V run on mma.sync.m16n8k16 with f32
+// accumulators. The cache entries are used
 // in their stored type (exact); the f32 operands Q and P enter as hi + lo pairs of that type
 // (two mma per tile), so the products carry ~16 significant bits of Q / P and the result stays
 // within ~1e-4 of the f32 evaluation.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace dyn {
@@ -21,9 +26,9 @@ constexpr int FA_D = 128;      // head dim handled by this kernel
 constexpr int FA_BR = 64;      // query rows per CTA
 constexpr int FA_BC = 64;      // keys per step
 constexpr int FA_PITCH = FA_D + 8;  // elements per shared-memory row (272 bytes: conflict-free fragment loads)
-constexpr int FA_THREADS = 256;
 constexpr int FA_TILE = FA_BC * FA_PITCH;            // elements of one K (or V) tile
-constexpr int FA_SMEM = 2 * 2 * 2 * FA_TILE * 2;     // buffers x blocks of a pair x (K, V) x 2 bytes
+constexpr int fa_threads(int halves) { return 128 * halves; }
+constexpr int fa_smem_bytes(int halves) { return 2 * halves * 2 * FA_TILE * 2; }  // buffers x blocks of a group x (K, V) x 2 bytes
 
 __device__ __forceinline__ void fa_cp16(void* dst, const void* src, bool live) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -75,14 +80,15 @@ struct FaArgs {
   int64_t ldq;        // floats between consecutive rows of q
 };
 
-template <int KV>
-__global__ void __launch_bounds__(FA_THREADS) attention_prefill_kernel(const FaArgs a) {
+template <int KV, int HALVES>
+__global__ void __launch_bounds__(fa_threads(HALVES)) attention_prefill_kernel(const FaArgs a) {
+  constexpr int FA_THREADS = fa_threads(HALVES);
   using M = Mma<KV>;
   using T = typename M::T;
   extern __shared__ __align__(16) uint8_t fa_smem[];
   T* const tiles = reinterpret_cast<T*>(fa_smem);  // [buffer][block of the pair][K, V][FA_BC][FA_PITCH]
   const int tid = threadIdx.x, lane = tid & 31, warp8 = tid >> 5;
-  const int warp = warp8 & 3, half = warp8 >> 2;   // row group; which block of a pair
+  const int warp = warp8 & 3, half = warp8 >> 2;   // row group; which block of a group
   const int g = lane >> 2, t = lane & 3;
   const int64_t h = blockIdx.x, rb = gridDim.y - 1 - blockIdx.y;  // the longest row blocks start first
   const int64_t kvh = h / (a.nh / a.nkv);
@@ -120,14 +126,14 @@ __global__ void __launch_bounds__(FA_THREADS) attention_prefill_kernel(const FaA
   int64_t cta_last = a.base_pos + rb * FA_BR + FA_BR - 1;
   if (cta_last > a.base_pos + a.rows - 1) cta_last = a.base_pos + a.rows - 1;
   const int64_t warp_last = a.base_pos + (row_lo + 15 < a.rows ? row_lo + 15 : a.rows - 1);
-  const int64_t nkb = cta_last / FA_BC + 1, npairs = (nkb + 1) / 2;
-  // 2 blocks x (K, V) x 64 keys x 16 pieces of 16 bytes per pair, coalesced; rows past the last written
+  const int64_t nkb = cta_last / FA_BC + 1, npairs = (nkb + HALVES - 1) / HALVES;
+  // HALVES blocks x (K, V) x 64 keys x 16 pieces of 16 bytes per group, coalesced; rows past the last written
   // position may hold anything: they are masked, but 0 * NaN must not happen, so they arrive as zeros
   auto load_pair = [&](int64_t pr) {
-    T* dst = tiles + (pr & 1) * 4 * FA_TILE;
-    for (int i = tid; i < 2 * FA_BC * (FA_D / 8); i += FA_THREADS) {
+    T* dst = tiles + (pr & 1) * 2 * HALVES * FA_TILE;
+    for (int i = tid; i < HALVES * FA_BC * (FA_D / 8); i += FA_THREADS) {
       const int blk = i / (FA_BC * (FA_D / 8)), key = (i / (FA_D / 8)) % FA_BC, c = i % (FA_D / 8);
-      const int64_t gk = (2 * pr + blk) * FA_BC + key;  // < cap for every written key
+      const int64_t gk = (HALVES * pr + blk) * FA_BC + key;  // < cap for every written key
       const bool written = gk <= cta_last;
       const int64_t src = (written ? gk : 0) * FA_D + c * 8;
       fa_cp16(dst + (blk * 2) * FA_TILE + key * FA_PITCH + c * 8, kplane + src, written);
@@ -140,10 +146,10 @@ __global__ void __launch_bounds__(FA_THREADS) attention_prefill_kernel(const FaA
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();  // pair pr has arrived for everyone, and nobody still reads the buffer the next pair goes to
     if (pr + 1 < npairs) load_pair(pr + 1);
-    const int64_t kb = 2 * pr + half;
+    const int64_t kb = HALVES * pr + half;
     if (kb >= nkb) continue;
-    const T(*ks)[FA_PITCH] = reinterpret_cast<const T(*)[FA_PITCH]>(tiles + ((pr & 1) * 4 + half * 2) * FA_TILE);
-    const T(*vs)[FA_PITCH] = reinterpret_cast<const T(*)[FA_PITCH]>(tiles + ((pr & 1) * 4 + half * 2 + 1) * FA_TILE);
+    const T(*ks)[FA_PITCH] = reinterpret_cast<const T(*)[FA_PITCH]>(tiles + ((pr & 1) * 2 * HALVES + half * 2) * FA_TILE);
+    const T(*vs)[FA_PITCH] = reinterpret_cast<const T(*)[FA_PITCH]>(tiles + ((pr & 1) * 2 * HALVES + half * 2 + 1) * FA_TILE);
     if (kb * FA_BC > warp_last) continue;  // every key of the block lies after this warp's rows
     // ---- S = Q K^T for 16 rows x 64 keys
     float s[8][4];
@@ -219,6 +225,7 @@ __global__ void __launch_bounds__(FA_THREADS) attention_prefill_kernel(const FaA
     }
   }
   // ---- merge the two halves' running states (thread for thread: both cover the same rows and columns)
+  if constexpr (HALVES == 2) {
   __syncthreads();  // the tiles are no longer read
   float* const mg = reinterpret_cast<float*>(fa_smem) + (size_t)(warp * 32 + lane) * 68;
   if (half == 1) {
@@ -241,6 +248,7 @@ __global__ void __launch_bounds__(FA_THREADS) attention_prefill_kernel(const FaA
       o[dt][0] = o[dt][0] * fa0 + ob.x * fb0, o[dt][1] = o[dt][1] * fa0 + ob.y * fb0;
       o[dt][2] = o[dt][2] * fa1 + ob.z * fb1, o[dt][3] = o[dt][3] * fa1 + ob.w * fb1;
     }
+  }
   }
   // ---- out / sum
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -272,13 +280,19 @@ int launch_attention_prefill(const AttnArgs& a, int64_t base_pos, int64_t seq, c
   f.rows = a.rows, f.nh = a.nh, f.nkv = a.nkv, f.cap = a.cap, f.base_pos = base_pos, f.seq = seq;
   f.ldq = a.ldq ? a.ldq : a.nh * FA_D;
   const dim3 grid((unsigned)a.nh, (unsigned)((a.rows + FA_BR - 1) / FA_BR));
-  if (a.kv_type == E_BF16) {
-    if (ensure_dynamic_smem(reinterpret_cast<const void*>(attention_prefill_kernel<E_BF16>), FA_SMEM)) return 1;
-    attention_prefill_kernel<E_BF16><<<grid, FA_THREADS, FA_SMEM, s>>>(f);
-  } else {
-    if (ensure_dynamic_smem(reinterpret_cast<const void*>(attention_prefill_kernel<E_F16>), FA_SMEM)) return 1;
-    attention_prefill_kernel<E_F16><<<grid, FA_THREADS, FA_SMEM, s>>>(f);
-  }
+  // a grid that fits the GPU in one round: eight warps and pairs of key blocks; larger: four warps, two CTAs per SM
+  const bool pairs = (int64_t)grid.x * grid.y <= std::max(1, sm_count());
+  auto run = [&](auto kernel, int halves) -> int {
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), fa_smem_bytes(halves))) return 1;
+    kernel<<<grid, fa_threads(halves), fa_smem_bytes(halves), s>>>(f);
+    return 0;
+  };
+  int rc;
+  if (a.kv_type == E_BF16)
+    rc = pairs ? run(attention_prefill_kernel<E_BF16, 2>, 2) : run(attention_prefill_kernel<E_BF16, 1>, 1);
+  else
+    rc = pairs ? run(attention_prefill_kernel<E_F16, 2>, 2) : run(attention_prefill_kernel<E_F16, 1>, 1);
+  if (rc) return 1;
   count_launch();
   DYN_CUDA(cudaGetLastError());
   *handled = true;

@@ -225,7 +225,7 @@ def test_attention_vs_oracle(native_lib, oracle, dtype, s, start, d, nh, nkv):
 
 
 @pytest.mark.parametrize("dtype", ["bf16", "f16"])
-@pytest.mark.parametrize("s,start,nh,nkv", [(100, 37, 4, 2), (64, 0, 2, 2), (130, 500, 4, 1)])
+@pytest.mark.parametrize("s,start,nh,nkv", [(100, 37, 4, 2), (64, 0, 2, 2), (130, 500, 4, 1), (200, 100, 40, 8)])
 def test_attention_prefill_tensor_core(native_lib, oracle, dtype, s, start, nh, nkv):
     """32 or more consecutive rows of one sequence on a 2-byte cache take the tensor-core
     flash-attention kernel (head dim 128): ragged row blocks, GQA, a start position in the middle

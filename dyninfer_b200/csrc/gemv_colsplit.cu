@@ -77,8 +77,10 @@ constexpr int CS_MAX_SMEM = 226 * 1024;  // dynamic shared memory the kernel may
 // are numbered slice-major, so a CTA works inside one or two slices and the arrangement costs
 // 1/S of the row instead of all of it); the scale comes from the whole row, so that every CTA
 // uses the same one. xq and sx8 are indexed from the start of the span.
+// mlx: a block's 32-bit word i holds elements 8i .. 8i+7, nibble k = element 8i + k, so step 2i+o pairs
+//   b0 = (x[8i+2o], x[8i+2o+4]), b1 = (x[8i+2o+1], x[8i+2o+5]) / 16.
 __device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf16, int K, int k0, int kspan, uint2* xq,
-                                            float* sx8, float* red, float sum_factor) {
+                                            float* sx8, float* red, float sum_factor, bool mlx = false) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   auto ld = [&](int i) -> float {
     if (i >= K) return 0.f;
@@ -99,8 +101,9 @@ __device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf
     const int b = j >> 3, st = j & 7, i = st >> 1, o = st & 1;
     const int U = b >> 3, r = b & 7, t = r >> 1, e = r & 1;
     const int kb = k0 + b * 32;
-    const float e0 = ld(kb + 4 * i + o) * s, e1 = ld(kb + 4 * i + o + 2) * s;
-    const float g0 = ld(kb + 16 + 4 * i + o) * s, g1 = ld(kb + 16 + 4 * i + o + 2) * s;
+    const int ia = mlx ? 8 * i + 2 * o : 4 * i + o, da = mlx ? 4 : 2, ib = mlx ? ia + 1 : ia + 16;
+    const float e0 = ld(kb + ia) * s, e1 = ld(kb + ia + da) * s;
+    const float g0 = ld(kb + ib) * s, g1 = ld(kb + ib + da) * s;
     float sum = (e0 + e1) + (g0 + g1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
@@ -134,6 +137,9 @@ struct CsArgs {
   const float* residual;
   float* partial;        // [S][N] when S > 1
   int* error;
+  // MLX-U4 only: aux element type is f16 (else bf16); bytes of scales (= of biases) per row and stage;
+  // group of 32 (else 64) weights per scale
+  int aux_f16, sb, group32;
 };
 
 template <int ENC>
@@ -317,6 +323,176 @@ gemv_cs_q4_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap) {
   }
 }
 
+// ---- MLX affine U4 ---------------------------------------------------------------------------
+// The same scheme for MLX-U4 rows (ui32[N, K/8], word j = weights 8j..8j+7, nibble k = bits [4k, 4k+4);
+// bf16 / f16 scales and biases per group of 64 or 32 weights, w = q * scale + bias,
+// mlx_affine.rs:284-290,590-600). A 32-weight block is four words; lane quarter t takes blocks 2t and
+// 2t + 1 of a 256-weight unit = words 8t .. 8t+7 = two 16-byte pieces of the row's 128 bytes. A stage is
+// two units x 16 rows: four tensor copies of 8 rows x 128 bytes, 128-byte swizzled so that the lanes'
+// 16-byte loads of one piece from eight rows fall into different banks, plus one box of the stage's
+// scales and one of its biases (16 rows x 16 or 32 bytes). The row's product is
+// sum_groups scale * sum(q x) + bias * sum(x): the second term uses the per-block sums of the arranged row.
+constexpr int CM_WSTAGE = 4096;  // weight bytes of a stage: 4 boxes of 8 rows x 128 bytes
+
+__global__ void __launch_bounds__(CS_WARPS * 32, 1)
+gemv_cs_mlx_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
+                   const __grid_constant__ CUtensorMap bmap) {
+  extern __shared__ __align__(128) uint8_t cs_smem_mlx[];
+  __shared__ int s_abort;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(cs_smem_mlx) + 1023) & ~uintptr_t(1023));
+  const int aux_stage = 2 * 16 * a.sb;  // scales then biases
+  uint8_t* ring = smem + (size_t)warp * CS_NST * CM_WSTAGE;
+  uint8_t* aring = smem + (size_t)CS_WARPS * CS_NST * CM_WSTAGE + (size_t)warp * CS_NST * aux_stage;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)CS_WARPS * CS_NST * (CM_WSTAGE + aux_stage)) + warp * CS_NST;
+  uint4* xq = reinterpret_cast<uint4*>(smem + (size_t)CS_WARPS * CS_NST * (CM_WSTAGE + aux_stage + 8));
+  float* sx8 = reinterpret_cast<float*>(xq + (size_t)a.span_units * 64);
+  float* red = sx8 + a.span_units * 8;
+  pdl_trigger();  // the next kernel of the stream may start its own weight fetch
+  if (threadIdx.x == 0) s_abort = 0;
+  if (lane == 0) {
+    for (int i = 0; i < CS_NST; i++) mbar_init(bars + i, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const int64_t nitems = (int64_t)a.ntiles * a.S;
+  const int64_t gw = (int64_t)blockIdx.x * CS_WARPS + warp;
+  const int64_t nwarps = (int64_t)gridDim.x * CS_WARPS;
+  const int64_t item_lo = nitems * gw / nwarps, item_hi = nitems * (gw + 1) / nwarps;
+  const int nst = a.nst;
+  const int total = item_lo < item_hi ? (int)(item_hi - item_lo) * nst : 0;
+  const int64_t cta_lo = nitems * ((int64_t)blockIdx.x * CS_WARPS) / nwarps;
+  const int64_t cta_hi = nitems * ((int64_t)(blockIdx.x + 1) * CS_WARPS) / nwarps;
+  const int sl_first = (int)(cta_lo / a.ntiles), sl_last = cta_hi > cta_lo ? (int)((cta_hi - 1) / a.ntiles) : sl_first;
+  const int U_base = sl_first * nst * 2;
+
+  const int sl_lo = (int)(item_lo / a.ntiles), tile_lo = (int)(item_lo - (int64_t)sl_lo * a.ntiles);
+  int c_left = total, c_tile = tile_lo, c_sl = sl_lo, c_st = 0, c_slot = 0;
+  auto issue = [&]() {
+    if (c_left <= 0) return;
+    c_left--;
+    if (lane == 0) mbar_expect_tx(bars + c_slot, CM_WSTAGE + aux_stage);  // boxes count in full, zeros included
+    __syncwarp();
+    const int stage = c_sl * nst + c_st;
+    if (lane < 4) {  // weights: unit lane >> 1, rows 8 * (lane & 1) ..
+      tma_box_g2s(ring + c_slot * CM_WSTAGE + lane * 1024, &wmap, (stage * 2 + (lane >> 1)) * 32, c_tile * 16 + (lane & 1) * 8,
+                  bars + c_slot);
+    } else if (lane < 6) {  // the stage's scales / biases of the tile's 16 rows
+      tma_box_g2s(aring + c_slot * aux_stage + (lane - 4) * 16 * a.sb, lane == 4 ? &smap : &bmap, stage * (a.sb / 4),
+                  c_tile * 16, bars + c_slot);
+    }
+    if (++c_slot == CS_NST) c_slot = 0;
+    if (++c_st == nst) {
+      c_st = 0;
+      if (++c_tile == a.ntiles) c_tile = 0, c_sl++;
+    }
+  };
+#pragma unroll
+  for (int q = 0; q < CS_NST; q++) issue();
+
+  pdl_wait();
+  const float out_scale = cs_stage_x(a.x, a.x_bf16, a.K, U_base * 256, (sl_last - sl_first + 1) * nst * 512,
+                                     reinterpret_cast<uint2*>(xq), sx8, red, 1.0f, true);
+  if (blockIdx.x == 0 && threadIdx.x == 0) a.misc[0] = out_scale;
+  __syncthreads();
+  if (total == 0) return;
+  const bool active = (g >> 1) == t;
+  auto aux_f32 = [&](const uint8_t* p) -> float {
+    const uint32_t bits = *reinterpret_cast<const uint16_t*>(p);
+    return a.aux_f16 ? __half2float(__ushort_as_half((unsigned short)bits)) : __uint_as_float(bits << 16);
+  };
+  float acc0 = 0.f, acc1 = 0.f;
+  int tile = tile_lo, sl = sl_lo, slot = 0;
+  unsigned parity = 0;
+  for (int64_t item = item_lo; item < item_hi; item++) {
+    for (int st = 0; st < nst; st++) {
+      if (!mbar_wait_bounded_sleepy(bars + slot, parity, CS_SPINS, &s_abort, 2000u)) {
+        if (!s_abort) {
+          s_abort = 1;
+          report_wait_expired(a.error, DEV_ERR_GEMV_RING);
+        }
+        return;  // warp-uniform: every lane polls the same barrier
+      }
+      const uint8_t* base = ring + slot * CM_WSTAGE;
+      const uint8_t* ab = aring + slot * aux_stage;
+      const int U0 = (sl * nst + st) * 2 - U_base;
+      // words 8t .. 8t+7 of rows g (box rows 0..7) and g + 8 (the next box) of both units; and the
+      // lane's scales and biases (rows g, g + 8; group of blocks 2t, 2t+1 or one per block)
+      uint32_t w0[2][8], w1[2][8];
+      float sc0[4], sc1[4], bi0[4], bi1[4];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          const int piece = ((2 * t + h) ^ g) << 4;
+          const uint4 v0 = *reinterpret_cast<const uint4*>(base + (2 * u) * 1024 + g * 128 + piece);
+          const uint4 v1 = *reinterpret_cast<const uint4*>(base + (2 * u + 1) * 1024 + g * 128 + piece);
+          w0[u][4 * h] = v0.x, w0[u][4 * h + 1] = v0.y, w0[u][4 * h + 2] = v0.z, w0[u][4 * h + 3] = v0.w;
+          w1[u][4 * h] = v1.x, w1[u][4 * h + 1] = v1.y, w1[u][4 * h + 2] = v1.z, w1[u][4 * h + 3] = v1.w;
+          const int si = a.group32 ? u * 8 + 2 * t + h : u * 4 + t;
+          sc0[2 * u + h] = aux_f32(ab + g * a.sb + 2 * si);
+          sc1[2 * u + h] = aux_f32(ab + (g + 8) * a.sb + 2 * si);
+          bi0[2 * u + h] = aux_f32(ab + 16 * a.sb + g * a.sb + 2 * si);
+          bi1[2 * u + h] = aux_f32(ab + 16 * a.sb + (g + 8) * a.sb + 2 * si);
+        }
+      }
+      __syncwarp();
+      issue();
+      if (++slot == CS_NST) slot = 0, parity ^= 1u;
+      const uint4* bp = xq + (size_t)U0 * 64 + g;   // group gi, word i: + gi * 32 + i * 8
+      const float* sxp = sx8 + U0 * 8 + 2 * t;
+      float c[4][4];
+#pragma unroll
+      for (int gi = 0; gi < 4; gi++) c[gi][0] = c[gi][1] = c[gi][2] = c[gi][3] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        uint32_t q0[4], q1[4];
+        uint4 bf[4];
+#pragma unroll
+        for (int gi = 0; gi < 4; gi++) {
+          q0[gi] = w0[gi >> 1][4 * (gi & 1) + i];
+          q1[gi] = w1[gi >> 1][4 * (gi & 1) + i];
+          bf[gi] = active ? bp[gi * 32 + i * 8] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int gi = 0; gi < 4; gi++)
+          mma_f16_16816(c[gi], q0[gi] & 0x000F000Fu, q1[gi] & 0x000F000Fu, q0[gi] & 0x00F000F0u,
+                        q1[gi] & 0x00F000F0u, bf[gi].x, bf[gi].y);
+#pragma unroll
+        for (int gi = 0; gi < 4; gi++) {
+          const uint32_t s0 = q0[gi] >> 8, s1 = q1[gi] >> 8;
+          mma_f16_16816(c[gi], s0 & 0x000F000Fu, s1 & 0x000F000Fu, s0 & 0x00F000F0u, s1 & 0x00F000F0u,
+                        bf[gi].z, bf[gi].w);
+        }
+      }
+#pragma unroll
+      for (int gi = 0; gi < 4; gi++) {
+        const float sx = sxp[(gi >> 1) * 8 + (gi & 1)];
+        acc0 = fmaf(sc0[gi], c[gi][0] + c[gi][1], fmaf(bi0[gi], sx, acc0));
+        acc1 = fmaf(sc1[gi], c[gi][2] + c[gi][3], fmaf(bi1[gi], sx, acc1));
+      }
+    }
+    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+    if (t == 0) {
+      const int64_t row0 = (int64_t)tile * 16 + g, row1 = row0 + 8;
+      if (a.S == 1) {
+        if (row0 < a.N) a.y[row0] = acc0 * out_scale + (a.residual ? a.residual[row0] : 0.f);
+        if (row1 < a.N) a.y[row1] = acc1 * out_scale + (a.residual ? a.residual[row1] : 0.f);
+      } else {
+        if (row0 < a.N) a.partial[(int64_t)sl * a.N + row0] = acc0;
+        if (row1 < a.N) a.partial[(int64_t)sl * a.N + row1] = acc1;
+      }
+    }
+    acc0 = acc1 = 0.f;
+    if (++tile == a.ntiles) tile = 0, sl++;
+  }
+}
+
 // partial sums over the K-slices, fixed order
 __global__ void __launch_bounds__(256)
 cs_reduce_kernel(const float* __restrict__ partial, int S, int64_t N, const float* __restrict__ misc,
@@ -338,9 +514,15 @@ struct CsPlan {
 };
 
 bool cs_basic_ok(const WRef& w, int M) {
+  if (w.enc == E_MLX_U4)  // whole stages; groups of 64 or 32; 2-byte scales and biases; 16-byte aligned arrays
+    return M == 1 && w.rows >= 1 && w.cols >= CS_KSTAGE && w.cols % CS_KSTAGE == 0 && (w.group == 64 || w.group == 32) &&
+           (w.aux == E_BF16 || w.aux == E_F16) && w.scales && w.biases &&
+           ((reinterpret_cast<uintptr_t>(w.data) | reinterpret_cast<uintptr_t>(w.scales) |
+             reinterpret_cast<uintptr_t>(w.biases)) & 15) == 0;
   return M == 1 && (w.enc == E_Q4_0 || w.enc == E_Q4_1) && w.rows >= 1 && w.cols >= CS_KSTAGE &&
          w.cols % (CS_KSTAGE / 2) == 0 && (reinterpret_cast<uintptr_t>(w.data) & 15) == 0;
 }
+int cs_mlx_sb(const WRef& w) { return w.group == 32 ? 32 : 16; }  // bytes of scales per row and stage
 
 void cs_plan(const WRef& w, CsPlan* p) {
   const int K = (int)w.cols, stages = (K + CS_KSTAGE - 1) / CS_KSTAGE;
@@ -366,7 +548,9 @@ void cs_plan(const WRef& w, CsPlan* p) {
     if (hi > lo) span = std::max(span, (int)((hi - 1) / p->ntiles - lo / p->ntiles) + 1);
   }
   p->span_units = span * p->nst * 2;
-  const size_t ring = w.enc == E_Q4_0 ? CsGeo<E_Q4_0>::RING_BYTES : CsGeo<E_Q4_1>::RING_BYTES;
+  const size_t ring = w.enc == E_MLX_U4
+                          ? 1024 + (size_t)CS_WARPS * CS_NST * (CM_WSTAGE + 2 * 16 * cs_mlx_sb(w) + 8)  // 1024: alignment slack
+                          : (w.enc == E_Q4_0 ? CsGeo<E_Q4_0>::RING_BYTES : CsGeo<E_Q4_1>::RING_BYTES);
   p->smem = ring + (size_t)p->span_units * (1024 + 32) + 128;
   p->off_err = 0;       // [64] 2^24 / scale
   p->off_part = 256;
@@ -413,6 +597,39 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
   cs_plan(w, &p);
   CsArgs a;
   a.N = w.rows, a.K = (int)w.cols;
+  a.aux_f16 = 0, a.sb = 0, a.group32 = 0;
+  if (w.enc == E_MLX_U4) {
+    // weights as [rows][K / 8] words in boxes of 8 rows x 128 bytes (swizzled); scales and biases as
+    // [rows][K / group] 2-byte values in boxes of 16 rows x one stage's worth
+    CUtensorMap wm, sm, bm;
+    const int sb = cs_mlx_sb(w);
+    const size_t aux_row = (size_t)(w.cols / w.group) * 2;
+    if (make_row_box_map(w.data, (size_t)w.cols / 2, w.rows, 32, 8, &wm, true) ||
+        make_row_box_map(w.scales, aux_row, w.rows, sb / 4, 16, &sm) || make_row_box_map(w.biases, aux_row, w.rows, sb / 4, 16, &bm))
+      return 1;
+    a.S = p.S, a.nst = p.nst, a.ntiles = p.ntiles, a.span_units = p.span_units;
+    a.x = x, a.x_bf16 = x_type == E_BF16 ? 1 : 0;
+    a.aux_f16 = w.aux == E_F16 ? 1 : 0, a.sb = sb, a.group32 = w.group == 32 ? 1 : 0;
+    a.error = device_error_word();
+    if (!a.error) return 1;
+    a.misc = reinterpret_cast<float*>(ws + p.off_err + 64);
+    a.partial = reinterpret_cast<float*>(ws + p.off_part);
+    a.y = y, a.residual = residual;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(gemv_cs_mlx_kernel), CS_MAX_SMEM)) return 1;
+    DYN_CUDA(launch_pdl(gemv_cs_mlx_kernel, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a, wm, sm, bm));
+    count_launch(1);
+    Deferred* defer = p.S > 1 && !residual ? defer_take() : nullptr;
+    if (defer) {
+      defer->partial = a.partial, defer->scale = a.misc, defer->S = p.S, defer->N = w.rows, defer->ws_bytes = p.bytes;
+    } else if (p.S > 1) {
+      DYN_CUDA(launch_pdl(cs_reduce_kernel, dim3((unsigned)((w.rows + 255) / 256)), dim3(256), 0, s,
+                          (const float*)a.partial, p.S, (int64_t)w.rows, (const float*)a.misc, y, residual));
+      count_launch();
+    }
+    DYN_CUDA(cudaGetLastError());
+    *handled = true;
+    return 0;
+  }
   // the matrix as [rows][row bytes / 4] words; boxes of 8 rows x one unit
   CUtensorMap wmap;
   if (make_row_box_map(w.data, w.row_bytes(), w.rows, w.enc == E_Q4_0 ? CsGeo<E_Q4_0>::UW : CsGeo<E_Q4_1>::UW, 8, &wmap))

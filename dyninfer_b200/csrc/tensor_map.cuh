@@ -20,9 +20,11 @@ __device__ __forceinline__ void tma_box_g2s(void* dst, const CUtensorMap* map, i
 }
 
 // Map of `rows` rows of `row_bytes` bytes (a multiple of 16, base 16-byte aligned) with boxes of
-// box_rows x box_words words, dense in shared memory, no swizzle, zeros outside the matrix.
+// box_rows x box_words words, dense in shared memory, zeros outside the matrix. swizzle128 (boxes of
+// exactly 32 words = 128 bytes per row, destination 1024-byte aligned): the 16-byte piece c of box row r
+// lands at piece c ^ (r & 7), so that lanes reading the same piece of eight rows hit different banks.
 inline int make_row_box_map(const uint8_t* data, size_t row_bytes, int64_t rows, int box_words, int box_rows,
-                            CUtensorMap* out) {
+                            CUtensorMap* out, bool swizzle128 = false) {
   typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -41,7 +43,8 @@ inline int make_row_box_map(const uint8_t* data, size_t row_bytes, int64_t rows,
   const cuuint32_t box[2] = {(cuuint32_t)box_words, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(data), dims, strides, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   DYN_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d", (int)r);
   return 0;

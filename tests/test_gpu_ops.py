@@ -103,7 +103,7 @@ def test_linear_ragged_and_full_shapes(native_lib, oracle, enc, n, k):
     assert helpers.rel_err(got, oracle.linear(ow, x, fast=True)) < 1e-4
 
 
-@pytest.mark.parametrize("enc", ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k"])
+@pytest.mark.parametrize("enc", ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "mlx.affine.u4"])
 @pytest.mark.parametrize("n,k", [(33, 512), (1000, 3072), (4096, 12288), (12288, 4096), (40, 768), (5120, 6400)])
 def test_linear_single_row_column_split(native_lib, oracle, enc, n, k):
     """One activation row (the decode shape) on the column-split tensor-core kernels: ragged last
@@ -121,6 +121,25 @@ def test_linear_single_row_column_split(native_lib, oracle, enc, n, k):
     x[0, ::7] = 0.0                                    # zeros and a huge dynamic range in one row
     x[0, 5] = 3.0e4
     x[0, 6] = 1.0e-6
+    got = ops.linear(dw, torch.from_numpy(x).cuda()).cpu().numpy()
+    assert helpers.rel_err(got, oracle.linear(ow, x, fast=True)) < 2e-5
+
+
+@pytest.mark.parametrize("group,aux", [(32, "bf16"), (64, "f16"), (128, "bf16")])
+def test_linear_single_row_mlx_groups_and_f16_aux(native_lib, oracle, group, aux):
+    """MLX-U4 single rows with groups of 32 (one scale per block), f16 scales and biases, and groups of
+    128 (outside the column-split kernel's rules: another kernel takes it), against the oracle."""
+    from dyninfer_b200 import ops
+    n, k = 520, 2048
+    t = synth.random_weight("mlx.affine.u4", n, k, 77, group=group)
+    sc, bi, aux_name = t["scales"], t["biases"], "plain.bf16"
+    if aux == "f16":
+        sc = synth.bf16_bits_to_f32(sc).astype(np.float16)
+        bi = synth.bf16_bits_to_f32(bi).astype(np.float16)
+        aux_name = "plain.f16"
+    dw = ops.DeviceWeight("mlx.affine.u4", n, k, t["packed"], sc, bi, aux_name, group)
+    ow = oracle.Weight("mlx.affine.u4", n, k, t["packed"], sc, bi, aux_name, group)
+    x = np.random.default_rng(group).normal(size=(1, k)).astype(np.float32)
     got = ops.linear(dw, torch.from_numpy(x).cuda()).cpu().numpy()
     assert helpers.rel_err(got, oracle.linear(ow, x, fast=True)) < 2e-5
 

@@ -50,10 +50,12 @@ __host__ __device__ constexpr int tg_conversion_index(int warp) { return warp; }
 // shared-memory port (A stored + B copied in + both read by the MMAs) = 768 cycles at 128 bytes per
 // cycle, more than the chunk's 512 tensor-pipe cycles.
 __host__ __device__ constexpr bool tg_a_in_tmem(int enc) {
-  return enc == E_Q4_0 || enc == E_Q4_1 || enc == E_Q8_0 || enc == E_MLX_U4;
+  return enc == E_Q4_0 || enc == E_Q4_1 || enc == E_Q8_0 || enc == E_MLX_U4 || enc == E_Q4_K || enc == E_Q5_K ||
+         enc == E_IQ4_XS;
 }
+__host__ __device__ constexpr bool tg_kquant(int enc) { return enc == E_Q4_K || enc == E_Q5_K || enc == E_IQ4_XS; }
 constexpr int TG_TMEM_A_COL = 256;        // first column of the A ring (32 columns per slot) behind the accumulator
-constexpr int TG_RAW_WORDS = 32 * 17;     // per-warp staging of raw row words (Q8_0: 17 words per row and chunk)
+constexpr int TG_RAW_WORDS = 32 * 21;     // per-warp staging of raw row words (Q5_K: 20 words per row and chunk, odd stride)
 constexpr int TG_MAX_SLOTS = 2 * TG_GROUPS;  // a group owns one pipeline slot, or two when they fit
 constexpr int TG_A_BYTES = TG_BM * 128;
 constexpr long long TG_SPINS = 1LL << 24;
@@ -267,7 +269,101 @@ dqgemm_tc_kernel(const TgArgs a, const __grid_constant__ CUtensorMap xmap) {
     // costs of a hand-over (proxy fence, barrier round trip) of up to four chunks overlap.
     const int pw = tg_conversion_index(warp);
     const int grp = pw / TG_GWARPS, wg = pw % TG_GWARPS;
-    if constexpr (AT) {
+    if constexpr (AT && tg_kquant(ENC)) {
+      // 256-weight blocks (Q4_K, Q5_K, IQ4_XS) with the A operand in tensor memory, thread = row as below.
+      // A 64-wide chunk is one quarter of a block: the block's header words (d, dmin / scales) plus the
+      // quarter's 32 index bytes (Q5_K: plus the block's 32 high-bit bytes):
+      //   Q4_K   12 words: 4 header + quant words 4 + 8 jj ..; Q5_K 20 words: 4 header + 8 high-bit + 12 + 8 jj ..
+      //   IQ4_XS 10 words: 2 header + index words 2 + 8 c ..
+      // The values are computed in f32 exactly as the decoders of codec.cuh do (each product and the
+      // difference rounded on its own; index -> f32 through 0x4B000000 | q), then rounded to f16.
+      constexpr int HW = ENC == E_Q4_K ? 4 : ENC == E_Q5_K ? 12 : 2;      // words taken from the block's start
+      constexpr int WPR = HW + 8, RS = WPR | 1, BW = Codec<ENC>::BYTES / 4;
+      static_assert(32 * RS <= TG_RAW_WORDS, "per-warp scratch");
+      const int quarter = warp & 3;
+      const int64_t rw = a.w.row_bytes() / 4;
+      const uint32_t* wbase = reinterpret_cast<const uint32_t*>(a.w.data);
+      uint32_t* raw = reinterpret_cast<uint32_t*>(smem + (size_t)nslot * stage_bytes) + warp * TG_RAW_WORDS;
+      const int64_t last = N - 1 - (n0 + quarter * 32);
+      auto fetch = [&](int kc, int, uint32_t (&q)[WPR]) {
+        const int64_t k0 = (int64_t)(kbase + kc) * TG_BK;
+        const uint32_t* cb = wbase + (k0 >> 8) * BW;
+        const int qoff = HW + 8 * (int)((k0 >> 6) & 3) - HW;  // quarter's index words start HW + 8 * quarter words in
+#pragma unroll
+        for (int it = 0; it < WPR; it++) {
+          const int idx = it * 32 + lane, r = idx / WPR, w = idx - r * WPR;
+          q[it] = cb[(n0 + quarter * 32 + (r < last ? r : last)) * rw + (w < HW ? w : w + qoff)];
+        }
+      };
+      auto h2u = [](__half2 v) { return *reinterpret_cast<uint32_t*>(&v); };
+      auto convert = [&](int kc, int, uint32_t (&q)[WPR], uint8_t*) {
+#pragma unroll
+        for (int it = 0; it < WPR; it++) {
+          const int idx = it * 32 + lane, r = idx / WPR;
+          raw[r * RS + (idx - r * WPR)] = q[it];
+        }
+        __syncwarp();
+        const uint32_t* me = raw + lane * RS;
+        const int jj = (kbase + kc) & 3;  // which quarter of the block
+        const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + TG_TMEM_A_COL + (uint32_t)(kc & (nslot - 1)) * 32u;
+        const uint32_t h0 = me[0];
+        const float d = f16_bits_to_f32(h0 & 0xffffu);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          uint32_t out[16];
+          if constexpr (ENC == E_IQ4_XS) {
+            const int ib = 2 * jj + h;
+            const uint32_t ls = ((me[1] >> (4 * ib)) & 15u) | ((((h0 >> 16) >> (2 * ib)) & 3u) << 4);
+            const float dl = __fmul_rn(d, (float)((int)ls - 32));
+#pragma unroll
+            for (int wq = 0; wq < 4; wq++) {
+              const uint32_t x = me[HW + 4 * h + wq];
+              float lo[4], hi[4];
+#pragma unroll
+              for (int i = 0; i < 4; i++) {
+                const uint32_t byte = (x >> (8 * i)) & 0xffu;
+                lo[i] = __fmul_rn(dl, iq4_value(byte & 15u));
+                hi[i] = __fmul_rn(dl, iq4_value(byte >> 4));
+              }
+              out[2 * wq] = h2u(__floats2half2_rn(lo[0], lo[1])), out[2 * wq + 1] = h2u(__floats2half2_rn(lo[2], lo[3]));
+              out[8 + 2 * wq] = h2u(__floats2half2_rn(hi[0], hi[1])), out[8 + 2 * wq + 1] = h2u(__floats2half2_rn(hi[2], hi[3]));
+            }
+          } else {
+            // sub-block j = 2 jj + h: 6-bit scale and minimum out of the 12 packed bytes (words 1..3)
+            const int j = 2 * jj + h;
+            auto sb = [&](int i) { return (me[1 + (i >> 2)] >> (8 * (i & 3))) & 0xffu; };
+            uint32_t sc, mn;
+            if (j < 4) {
+              sc = sb(j) & 63u, mn = sb(j + 4) & 63u;
+            } else {
+              sc = (sb(j + 4) & 15u) | ((sb(j - 4) >> 6) << 4);
+              mn = (sb(j + 4) >> 4) | ((sb(j) >> 6) << 4);
+            }
+            const float ds = __fmul_rn(d, (float)sc), dm = __fmul_rn(f16_bits_to_f32(h0 >> 16), (float)mn);
+#pragma unroll
+            for (int wq = 0; wq < 8; wq++) {
+              uint32_t v = (me[HW + wq] >> (4 * h)) & 0x0F0F0F0Fu;
+              if constexpr (ENC == E_Q5_K) v |= ((me[4 + wq] >> j) & 0x01010101u) << 4;
+              float f[4];
+              f[0] = __fsub_rn(__fmul_rn(ds, __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7440)) - 8388608.f), dm);
+              f[1] = __fsub_rn(__fmul_rn(ds, __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7441)) - 8388608.f), dm);
+              f[2] = __fsub_rn(__fmul_rn(ds, __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7442)) - 8388608.f), dm);
+              f[3] = __fsub_rn(__fmul_rn(ds, __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7443)) - 8388608.f), dm);
+              out[2 * wq] = h2u(__floats2half2_rn(f[0], f[1])), out[2 * wq + 1] = h2u(__floats2half2_rn(f[2], f[3]));
+            }
+          }
+          asm volatile(
+              "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+              ::"r"(taddr + 16u * h), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]),
+                "r"(out[7]), "r"(out[8]), "r"(out[9]), "r"(out[10]), "r"(out[11]), "r"(out[12]), "r"(out[13]), "r"(out[14]), "r"(out[15])
+              : "memory");
+        }
+        __syncwarp();  // the scratch is read; the next chunk may overwrite it
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+      };
+      tg_produce_chunks<WPR, 1>(grp, nk, nslot, smem, stage_bytes, empty_bar, full_bar, &s_abort, lane, fetch, convert);
+    } else if constexpr (AT) {
       // A operand in tensor memory. A warp converts the 32 rows of its lane quarter: thread = row, the
       // chunk's 64 weights of a row = 32 packed columns (column c = weights 2c, 2c + 1), written with one
       // tcgen05.st. The raw words of the next chunk are fetched a step ahead with coalesced loads (lane i
@@ -635,7 +731,8 @@ bool tg_shape_ok(const WRef& w, int64_t M) {
   if (w.enc == E_MLX_U4 && (w.group < 32 || (w.group & (w.group - 1)) || w.cols % w.group)) return false;
   // the word-fetching producers read aligned 32-bit words (Q6_K: 16-bit halves)
   const uintptr_t addr = reinterpret_cast<uintptr_t>(w.data);
-  if ((w.enc == E_Q4_0 || w.enc == E_Q4_1 || w.enc == E_Q8_0 || w.enc == E_MLX_U4) && (addr & 3)) return false;
+  if ((w.enc == E_Q4_0 || w.enc == E_Q4_1 || w.enc == E_Q8_0 || w.enc == E_MLX_U4 || tg_kquant(w.enc)) && (addr & 3))
+    return false;
   if (w.enc == E_Q6_K && (addr & 1)) return false;
   return M >= 1 && w.rows >= 1 && w.cols >= TG_BK && w.cols % (enc_block_elems(w.enc) == 256 ? 256 : TG_BK) == 0;
 }

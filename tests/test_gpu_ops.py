@@ -166,11 +166,12 @@ def test_linear_many_rows_tensor_core(native_lib, oracle, enc, m, n, k):
         assert helpers.rel_err(got[r], want[r]) < 1e-3
 
 
-@pytest.mark.parametrize("enc", ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "mlx.affine.u4"])
+@pytest.mark.parametrize("enc", ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "gguf.q4_k", "gguf.q5_k",
+                                 "gguf.iq4_xs", "mlx.affine.u4"])
 def test_tensor_core_operand_is_the_rounded_weight(native_lib, oracle, enc):
     """Identity activations read the dequant-GEMM's A operand back: y[k, n] = f16(w[n, k]). Every
     element of every 64-wide chunk and both halves of a 256-element block must land in its place.
-    Q4_0, Q8_0 and Q6_K round the decoder's f32 value once (bit-exact); Q4_1 rounds q*d + m once where
+    Q4_0, Q8_0, Q6_K, Q4_K, Q5_K and IQ4_XS round the decoder's f32 value once (bit-exact); Q4_1 rounds q*d + m once where
     the decoder rounds twice (one f16 unit); MLX-U4 takes its scale and bias as f16 (2^-10 relative)."""
     from dyninfer_b200 import ops
     n, k = 200, 512
@@ -178,7 +179,7 @@ def test_tensor_core_operand_is_the_rounded_weight(native_lib, oracle, enc):
     got = ops.linear(dw, torch.eye(k).cuda()).cpu().numpy().T            # [n, k]
     w = oracle.dequant(ow)
     want = w.astype(np.float16).astype(np.float32)
-    if enc in ("gguf.q4_0", "gguf.q8_0", "gguf.q6_k"):
+    if enc in ("gguf.q4_0", "gguf.q8_0", "gguf.q6_k", "gguf.q4_k", "gguf.q5_k", "gguf.iq4_xs"):
         assert np.array_equal(got, want)                                  # -0.0 == +0.0
     elif enc == "gguf.q4_1":
         ulp = np.spacing(np.abs(want).astype(np.float16)).astype(np.float32)

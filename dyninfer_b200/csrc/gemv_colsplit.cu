@@ -77,10 +77,13 @@ constexpr int CS_MAX_SMEM = 226 * 1024;  // dynamic shared memory the kernel may
 // are numbered slice-major, so a CTA works inside one or two slices and the arrangement costs
 // 1/S of the row instead of all of it); the scale comes from the whole row, so that every CTA
 // uses the same one. xq and sx8 are indexed from the start of the span.
-// mlx: a block's 32-bit word i holds elements 8i .. 8i+7, nibble k = element 8i + k, so step 2i+o pairs
-//   b0 = (x[8i+2o], x[8i+2o+4]), b1 = (x[8i+2o+1], x[8i+2o+5]) / 16.
+// order 1 (MLX-U4): a block's 32-bit word i holds elements 8i .. 8i+7, nibble k = element 8i + k, so step
+//   2i+o pairs b0 = (x[8i+2o], x[8i+2o+4]), b1 = (x[8i+2o+1], x[8i+2o+5]) / 16.
+// order 2 (Q4_K): a 32-element sub-block is one nibble plane of 32 bytes; step s = 2i+o takes the plane's
+//   elements of word s: b0 = (x[4s], x[4s+2]), b1 = (x[4s+1], x[4s+3]), all of them / 16 for the odd
+//   sub-blocks (the high-nibble plane).
 __device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf16, int K, int k0, int kspan, uint2* xq,
-                                            float* sx8, float* red, float sum_factor, bool mlx = false) {
+                                            float* sx8, float* red, float sum_factor, int order = 0) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   auto ld = [&](int i) -> float {
     if (i >= K) return 0.f;
@@ -101,7 +104,8 @@ __device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf
     const int b = j >> 3, st = j & 7, i = st >> 1, o = st & 1;
     const int U = b >> 3, r = b & 7, t = r >> 1, e = r & 1;
     const int kb = k0 + b * 32;
-    const int ia = mlx ? 8 * i + 2 * o : 4 * i + o, da = mlx ? 4 : 2, ib = mlx ? ia + 1 : ia + 16;
+    const int ia = order == 1 ? 8 * i + 2 * o : (order == 2 ? 4 * st : 4 * i + o), da = order == 1 ? 4 : 2;
+    const int ib = order == 0 ? ia + 16 : ia + 1;
     const float e0 = ld(kb + ia) * s, e1 = ld(kb + ia + da) * s;
     const float g0 = ld(kb + ib) * s, g1 = ld(kb + ib + da) * s;
     float sum = (e0 + e1) + (g0 + g1);
@@ -109,11 +113,12 @@ __device__ __forceinline__ float cs_stage_x(const void* __restrict__ x, int x_bf
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     sum += __shfl_xor_sync(0xffffffffu, sum, 4);
     if (st == 0) sx8[b] = sum_factor * GV_2M24 * sum;
-    const float f0 = g0 * 0.0625f, f1 = g1 * 0.0625f;
-    const __half h0 = __float2half_rn(e0), h1 = __float2half_rn(e1);
+    const float m0 = order == 2 && e ? 0.0625f : 1.0f, m1 = order == 2 && !e ? 1.0f : 0.0625f;
+    const float f0 = g0 * m1, f1 = g1 * m1, d0 = e0 * m0, d1 = e1 * m0;
+    const __half h0 = __float2half_rn(d0), h1 = __float2half_rn(d1);
     const __half h2 = __float2half_rn(f0), h3 = __float2half_rn(f1);
     const __half2 hi0 = __halves2half2(h0, h1), hi1 = __halves2half2(h2, h3);
-    const __half2 lo0 = __halves2half2(__float2half_rn(e0 - __half2float(h0)), __float2half_rn(e1 - __half2float(h1)));
+    const __half2 lo0 = __halves2half2(__float2half_rn(d0 - __half2float(h0)), __float2half_rn(d1 - __half2float(h1)));
     const __half2 lo1 = __halves2half2(__float2half_rn(f0 - __half2float(h2)), __float2half_rn(f1 - __half2float(h3)));
     uint2* dst = xq + ((size_t)(((U * 2 + e) * 4 + i) * 8 + 2 * t) * 2 + o);  // uint2 units; hl adds 2
     dst[0] = make_uint2(*reinterpret_cast<const uint32_t*>(&hi0), *reinterpret_cast<const uint32_t*>(&hi1));
@@ -394,7 +399,7 @@ gemv_cs_mlx_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap, con
 
   pdl_wait();
   const float out_scale = cs_stage_x(a.x, a.x_bf16, a.K, U_base * 256, (sl_last - sl_first + 1) * nst * 512,
-                                     reinterpret_cast<uint2*>(xq), sx8, red, 1.0f, true);
+                                     reinterpret_cast<uint2*>(xq), sx8, red, 1.0f, 1);
   if (blockIdx.x == 0 && threadIdx.x == 0) a.misc[0] = out_scale;
   __syncthreads();
   if (total == 0) return;
@@ -493,6 +498,169 @@ gemv_cs_mlx_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap, con
   }
 }
 
+// ---- Q4_K ------------------------------------------------------------------------------------
+// The same scheme for Q4_K (256-weight blocks of 144 bytes: f16 d, f16 dmin, 12 bytes of 6-bit scales and
+// minimums, 128 nibble bytes; weight 64 jj + 32 h + l = nibble h of byte 32 jj + l, sub-block j = 2 jj + h,
+// w = (d sc_j) q - dmin m_j; arithmetic after GGML's published dequantisation, see codec.cuh). A block is one
+// 256-weight unit of 36 words, the box geometry is Q4_0's. Lane quarter t takes the 32 nibble bytes jj = t
+// (two 16-byte loads) and the block's four header words: the low-nibble plane is sub-block 2t, the high
+// plane sub-block 2t + 1, each with its own accumulator; one mma covers four weights of ONE plane
+// (a0/a1 = bytes 0 and 2 of a word, a2/a3 = bytes 1 and 3), so both planes together issue as many mma as a
+// Q4_0 unit. The row's product is sum_j (d sc_j) sum(q x) - (dmin m_j) sum(x).
+__global__ void __launch_bounds__(CS_WARPS * 32, 1)
+gemv_cs_q4k_kernel(const CsArgs a, const __grid_constant__ CUtensorMap wmap) {
+  using G = CsGeo<E_Q4_0>;
+  extern __shared__ __align__(128) uint8_t cs_smem_q4k[];
+  __shared__ int s_abort;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  uint8_t* ring = cs_smem_q4k + (size_t)warp * CS_NST * G::STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(cs_smem_q4k + (size_t)CS_WARPS * CS_NST * G::STAGE) + warp * CS_NST;
+  uint4* xq = reinterpret_cast<uint4*>(cs_smem_q4k + G::RING_BYTES);
+  float* sx8 = reinterpret_cast<float*>(xq + (size_t)a.span_units * 64);
+  float* red = sx8 + a.span_units * 8;
+  pdl_trigger();  // the next kernel of the stream may start its own weight fetch
+  if (threadIdx.x == 0) s_abort = 0;
+  if (lane == 0) {
+    for (int i = 0; i < CS_NST; i++) mbar_init(bars + i, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const int64_t nitems = (int64_t)a.ntiles * a.S;
+  const int64_t gw = (int64_t)blockIdx.x * CS_WARPS + warp;
+  const int64_t nwarps = (int64_t)gridDim.x * CS_WARPS;
+  const int64_t item_lo = nitems * gw / nwarps, item_hi = nitems * (gw + 1) / nwarps;
+  const int nst = a.nst;
+  const int total = item_lo < item_hi ? (int)(item_hi - item_lo) * nst : 0;
+  const int64_t cta_lo = nitems * ((int64_t)blockIdx.x * CS_WARPS) / nwarps;
+  const int64_t cta_hi = nitems * ((int64_t)(blockIdx.x + 1) * CS_WARPS) / nwarps;
+  const int sl_first = (int)(cta_lo / a.ntiles), sl_last = cta_hi > cta_lo ? (int)((cta_hi - 1) / a.ntiles) : sl_first;
+  const int U_base = sl_first * nst * 2;
+
+  const int sl_lo = (int)(item_lo / a.ntiles), tile_lo = (int)(item_lo - (int64_t)sl_lo * a.ntiles);
+  int c_left = total, c_tile = tile_lo, c_sl = sl_lo, c_st = 0, c_slot = 0;
+  auto issue = [&]() {
+    if (c_left <= 0) return;
+    c_left--;
+    if (lane == 0) mbar_expect_tx(bars + c_slot, G::STAGE);  // boxes count in full, zeros included
+    __syncwarp();
+    if (lane < 4) {
+      const int u = lane >> 1, hf = lane & 1;
+      tma_box_g2s(ring + c_slot * G::STAGE + lane * G::BOX, &wmap, ((c_sl * nst + c_st) * 2 + u) * G::UW, c_tile * 16 + hf * 8,
+                  bars + c_slot);
+    }
+    if (++c_slot == CS_NST) c_slot = 0;
+    if (++c_st == nst) {
+      c_st = 0;
+      if (++c_tile == a.ntiles) c_tile = 0, c_sl++;
+    }
+  };
+#pragma unroll
+  for (int q = 0; q < CS_NST; q++) issue();
+
+  pdl_wait();
+  const float out_scale = cs_stage_x(a.x, a.x_bf16, a.K, U_base * 256, (sl_last - sl_first + 1) * nst * 512,
+                                     reinterpret_cast<uint2*>(xq), sx8, red, 1.0f, 2);
+  if (blockIdx.x == 0 && threadIdx.x == 0) a.misc[0] = out_scale;
+  __syncthreads();
+  if (total == 0) return;
+  const bool active = (g >> 1) == t;
+  // d * sc_j and dmin * m_j of sub-block j out of a block's four header words
+  auto scale_min = [](const uint4& h, int j, float* ds, float* dm) {
+    const uint32_t sw[3] = {h.y, h.z, h.w};
+    auto sb = [&](int i) { return (sw[i >> 2] >> (8 * (i & 3))) & 0xffu; };
+    uint32_t sc, mn;
+    if (j < 4) {
+      sc = sb(j) & 63u, mn = sb(j + 4) & 63u;
+    } else {
+      sc = (sb(j + 4) & 15u) | ((sb(j - 4) >> 6) << 4);
+      mn = (sb(j + 4) >> 4) | ((sb(j) >> 6) << 4);
+    }
+    const __half2 dd = *reinterpret_cast<const __half2*>(&h.x);
+    *ds = __low2float(dd) * (float)sc;
+    *dm = __high2float(dd) * (float)mn;
+  };
+  float acc0 = 0.f, acc1 = 0.f;
+  int tile = tile_lo, sl = sl_lo, slot = 0;
+  unsigned parity = 0;
+  for (int64_t item = item_lo; item < item_hi; item++) {
+    for (int st = 0; st < nst; st++) {
+      if (!mbar_wait_bounded_sleepy(bars + slot, parity, CS_SPINS, &s_abort, 2000u)) {
+        if (!s_abort) {
+          s_abort = 1;
+          report_wait_expired(a.error, DEV_ERR_GEMV_RING);
+        }
+        return;  // warp-uniform: every lane polls the same barrier
+      }
+      // box (unit u, rows 8 hf ..) sits at (2 u + hf) * BOX; row g of a box at g * 144 bytes
+      const uint8_t* base = ring + slot * G::STAGE;
+      const int U0 = (sl * nst + st) * 2 - U_base;
+      uint4 hd0[2], hd1[2], qa0[2], qb0[2], qa1[2], qb1[2];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const uint8_t* r0 = base + (2 * u) * G::BOX + g * 144;
+        const uint8_t* r1 = base + (2 * u + 1) * G::BOX + g * 144;
+        hd0[u] = *reinterpret_cast<const uint4*>(r0), hd1[u] = *reinterpret_cast<const uint4*>(r1);
+        qa0[u] = *reinterpret_cast<const uint4*>(r0 + 16 + 32 * t), qb0[u] = *reinterpret_cast<const uint4*>(r0 + 32 + 32 * t);
+        qa1[u] = *reinterpret_cast<const uint4*>(r1 + 16 + 32 * t), qb1[u] = *reinterpret_cast<const uint4*>(r1 + 32 + 32 * t);
+      }
+      __syncwarp();
+      issue();
+      if (++slot == CS_NST) slot = 0, parity ^= 1u;
+      const uint4* bp = xq + (size_t)U0 * 64 + g;   // (unit u, plane e), step pair m: + (2 u + e) * 32 + m * 8
+      const float* sxp = sx8 + U0 * 8 + 2 * t;
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const uint32_t w0[8] = {qa0[u].x, qa0[u].y, qa0[u].z, qa0[u].w, qb0[u].x, qb0[u].y, qb0[u].z, qb0[u].w};
+        const uint32_t w1[8] = {qa1[u].x, qa1[u].y, qa1[u].z, qa1[u].w, qb1[u].x, qb1[u].y, qb1[u].z, qb1[u].w};
+        float c[2][4];
+#pragma unroll
+        for (int e = 0; e < 2; e++) c[e][0] = c[e][1] = c[e][2] = c[e][3] = 0.f;
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+          uint4 bf[2];
+#pragma unroll
+          for (int e = 0; e < 2; e++) bf[e] = active ? bp[(2 * u + e) * 32 + m * 8] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int o = 0; o < 2; o++) {
+            const uint32_t x0 = w0[2 * m + o], x1 = w1[2 * m + o];
+            mma_f16_16816(c[0], x0 & 0x000F000Fu, x1 & 0x000F000Fu, (x0 >> 8) & 0x000F000Fu, (x1 >> 8) & 0x000F000Fu,
+                          o ? bf[0].z : bf[0].x, o ? bf[0].w : bf[0].y);
+            mma_f16_16816(c[1], x0 & 0x00F000F0u, x1 & 0x00F000F0u, (x0 >> 8) & 0x00F000F0u, (x1 >> 8) & 0x00F000F0u,
+                          o ? bf[1].z : bf[1].x, o ? bf[1].w : bf[1].y);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          float ds0, dm0, ds1, dm1;
+          scale_min(hd0[u], 2 * t + e, &ds0, &dm0);
+          scale_min(hd1[u], 2 * t + e, &ds1, &dm1);
+          const float sx = sxp[u * 8 + e];
+          acc0 = fmaf(ds0, c[e][0] + c[e][1], fmaf(-dm0, sx, acc0));
+          acc1 = fmaf(ds1, c[e][2] + c[e][3], fmaf(-dm1, sx, acc1));
+        }
+      }
+    }
+    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+    if (t == 0) {
+      const int64_t row0 = (int64_t)tile * 16 + g, row1 = row0 + 8;
+      if (a.S == 1) {
+        if (row0 < a.N) a.y[row0] = acc0 * out_scale + (a.residual ? a.residual[row0] : 0.f);
+        if (row1 < a.N) a.y[row1] = acc1 * out_scale + (a.residual ? a.residual[row1] : 0.f);
+      } else {
+        if (row0 < a.N) a.partial[(int64_t)sl * a.N + row0] = acc0;
+        if (row1 < a.N) a.partial[(int64_t)sl * a.N + row1] = acc1;
+      }
+    }
+    acc0 = acc1 = 0.f;
+    if (++tile == a.ntiles) tile = 0, sl++;
+  }
+}
+
 // partial sums over the K-slices, fixed order
 __global__ void __launch_bounds__(256)
 cs_reduce_kernel(const float* __restrict__ partial, int S, int64_t N, const float* __restrict__ misc,
@@ -519,7 +687,7 @@ bool cs_basic_ok(const WRef& w, int M) {
            (w.aux == E_BF16 || w.aux == E_F16) && w.scales && w.biases &&
            ((reinterpret_cast<uintptr_t>(w.data) | reinterpret_cast<uintptr_t>(w.scales) |
              reinterpret_cast<uintptr_t>(w.biases)) & 15) == 0;
-  return M == 1 && (w.enc == E_Q4_0 || w.enc == E_Q4_1) && w.rows >= 1 && w.cols >= CS_KSTAGE &&
+  return M == 1 && (w.enc == E_Q4_0 || w.enc == E_Q4_1 || w.enc == E_Q4_K) && w.rows >= 1 && w.cols >= CS_KSTAGE &&
          w.cols % (CS_KSTAGE / 2) == 0 && (reinterpret_cast<uintptr_t>(w.data) & 15) == 0;
 }
 int cs_mlx_sb(const WRef& w) { return w.group == 32 ? 32 : 16; }  // bytes of scales per row and stage
@@ -550,7 +718,7 @@ void cs_plan(const WRef& w, CsPlan* p) {
   p->span_units = span * p->nst * 2;
   const size_t ring = w.enc == E_MLX_U4
                           ? 1024 + (size_t)CS_WARPS * CS_NST * (CM_WSTAGE + 2 * 16 * cs_mlx_sb(w) + 8)  // 1024: alignment slack
-                          : (w.enc == E_Q4_0 ? CsGeo<E_Q4_0>::RING_BYTES : CsGeo<E_Q4_1>::RING_BYTES);
+                          : (w.enc == E_Q4_1 ? CsGeo<E_Q4_1>::RING_BYTES : CsGeo<E_Q4_0>::RING_BYTES);  // Q4_K: Q4_0's boxes
   p->smem = ring + (size_t)p->span_units * (1024 + 32) + 128;
   p->off_err = 0;       // [64] 2^24 / scale
   p->off_part = 256;
@@ -632,7 +800,7 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
   }
   // the matrix as [rows][row bytes / 4] words; boxes of 8 rows x one unit
   CUtensorMap wmap;
-  if (make_row_box_map(w.data, w.row_bytes(), w.rows, w.enc == E_Q4_0 ? CsGeo<E_Q4_0>::UW : CsGeo<E_Q4_1>::UW, 8, &wmap))
+  if (make_row_box_map(w.data, w.row_bytes(), w.rows, w.enc == E_Q4_1 ? CsGeo<E_Q4_1>::UW : CsGeo<E_Q4_0>::UW, 8, &wmap))
     return 1;
   a.S = p.S, a.nst = p.nst, a.ntiles = p.ntiles, a.span_units = p.span_units;
   a.x = x, a.x_bf16 = x_type == E_BF16 ? 1 : 0;
@@ -641,11 +809,14 @@ int launch_gemv_cs(const WRef& w, const void* x, int x_type, int M, float* y, co
   a.misc = reinterpret_cast<float*>(ws + p.off_err + 64);
   a.partial = reinterpret_cast<float*>(ws + p.off_part);
   a.y = y, a.residual = residual;
-  if (ensure_dynamic_smem(reinterpret_cast<const void*>(w.enc == E_Q4_0 ? gemv_cs_q4_kernel<E_Q4_0>
-                                                                       : gemv_cs_q4_kernel<E_Q4_1>),
+  if (ensure_dynamic_smem(w.enc == E_Q4_K   ? reinterpret_cast<const void*>(gemv_cs_q4k_kernel)
+                          : w.enc == E_Q4_0 ? reinterpret_cast<const void*>(gemv_cs_q4_kernel<E_Q4_0>)
+                                            : reinterpret_cast<const void*>(gemv_cs_q4_kernel<E_Q4_1>),
                           CS_MAX_SMEM))
     return 1;
-  if (w.enc == E_Q4_0)
+  if (w.enc == E_Q4_K)
+    DYN_CUDA(launch_pdl(gemv_cs_q4k_kernel, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a, wmap));
+  else if (w.enc == E_Q4_0)
     DYN_CUDA(launch_pdl(gemv_cs_q4_kernel<E_Q4_0>, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a, wmap));
   else
     DYN_CUDA(launch_pdl(gemv_cs_q4_kernel<E_Q4_1>, dim3(p.grid), dim3(CS_WARPS * 32), p.smem, s, a, wmap));

@@ -103,7 +103,7 @@ def test_linear_ragged_and_full_shapes(native_lib, oracle, enc, n, k):
     assert helpers.rel_err(got, oracle.linear(ow, x, fast=True)) < 1e-4
 
 
-@pytest.mark.parametrize("enc", ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "mlx.affine.u4"])
+@pytest.mark.parametrize("enc", ["gguf.q4_0", "gguf.q4_1", "gguf.q8_0", "gguf.q6_k", "gguf.q4_k", "mlx.affine.u4"])
 @pytest.mark.parametrize("n,k", [(33, 512), (1000, 3072), (4096, 12288), (12288, 4096), (40, 768), (5120, 6400)])
 def test_linear_single_row_column_split(native_lib, oracle, enc, n, k):
     """One activation row (the decode shape) on the column-split tensor-core kernels: ragged last

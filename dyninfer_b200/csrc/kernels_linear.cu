@@ -125,9 +125,10 @@ int launch_linear(const WRef& w, const void* x, int x_type, int64_t m, float* y,
   DYN_CHECK(m >= 1, "linear: m must be >= 1");
   // more rows than one pass of the tensor-core GEMV takes (4 with f32 activations, 8 with bf16):
   // dequant-in-shared-memory tensor-core GEMM, one pass over the weights for all rows
-  // (below 17 rows only for the encodings whose GEMM producer is cheap enough to beat repeated GEMV
+  // (below 17 rows only for the encodings with a word-fetching GEMM producer, which beats repeated GEMV
   // passes: the GEMM's dequantisation cost does not shrink with the row count)
-  const bool cheap_producer = w.enc == E_Q4_0 || w.enc == E_MLX_U4;
+  const bool cheap_producer = w.enc == E_Q4_0 || w.enc == E_Q4_1 || w.enc == E_Q8_0 || w.enc == E_Q6_K ||
+                              w.enc == E_Q4_K || w.enc == E_Q5_K || w.enc == E_IQ4_XS || w.enc == E_MLX_U4;
   if (m > 16 || (cheap_producer && m > (x_type == E_BF16 ? 8 : 4))) {
     bool handled = false;
     if (launch_dqgemm_tc(w, x, x_type, m, y, residual, s, &handled)) return 1;

@@ -265,6 +265,7 @@ __global__ void __launch_bounds__(128) qkv_prepare_kernel(QkvPrepArgs a, FreqTab
   // the head's values: from the product's output, or (one row) added up here from its K-slice sums
   __shared__ float hv[256];
   float* qv = a.q + r * (a.ldq ? a.ldq : a.nh * d) + head * d;
+  const float* src;
   {
     const DeferredCols& dc = kind == 0 ? a.dq : (kind == 1 ? a.dk : a.dv);
     const float* in = kind == 0 ? qv
@@ -287,17 +288,17 @@ __global__ void __launch_bounds__(128) qkv_prepare_kernel(QkvPrepArgs a, FreqTab
         const int64_t i = threadIdx.x + (int64_t)e * blockDim.x;
         if (i < d) hv[i] = t[e] * sc;
       }
+      __syncthreads();
+      src = hv;
     } else {
-      for (int64_t i = threadIdx.x; i < d; i += blockDim.x) hv[i] = in[i];
+      src = in;  // read in place, as the multi-row steps always do
     }
-    __syncthreads();
   }
   if (kind == 2) {
     T* dst = reinterpret_cast<T*>(a.vcache) + ((seq * a.nkv + head) * a.cap + pos) * d;
-    for (int64_t i = threadIdx.x; i < d; i += blockDim.x) dst[i] = KvT<KV>::enc(hv[i]);
+    for (int64_t i = threadIdx.x; i < d; i += blockDim.x) dst[i] = KvT<KV>::enc(src[i]);
     return;
   }
-  const float* src = hv;
   const void* nw = kind == 0 ? a.q_norm_w : a.k_norm_w;
   float inv = 1.f;
   if (a.has_norm) {

@@ -239,8 +239,24 @@ int launch_gather(const WRef& w, const int64_t* tokens, int64_t count, float* ou
 int launch_linear(const WRef& w, const void* x, int x_type, int64_t m, float* y,
                   const float* residual, cudaStream_t s);
 // Tensor-core GEMV for few activation rows (gemv_mma.cu); *handled tells whether it ran.
+// Optional hand-overs around the dequant GEMM, for callers that fuse its neighbours (a session's prefill
+// chunks): activations already in the GEMM's own form (f16 rows scaled by a power of two per row, the
+// inverse scales beside them; rows_alloc >= dqgemm_tc_padded_rows), and a place where a K-split product
+// leaves its sums [splits][M][N] instead of running its own reduction (the caller's next kernel adds them
+// in ascending split order, then the residual: what tg_split_reduce_kernel computes).
+struct TgIo {
+  const __half* xh = nullptr;
+  const float* inv_s = nullptr;
+  int64_t rows_alloc = 0;
+  float* partial = nullptr;
+  size_t partial_bytes = 0;
+  int splits = 0;  // out: > 1 when the sums were left in `partial` (y untouched)
+};
 int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float* y, const float* residual,
-                     cudaStream_t s, bool* handled);
+                     cudaStream_t s, bool* handled, TgIo* io = nullptr);
+// Whether launch_dqgemm_tc takes the product, and the activation rows its tiling pads M to.
+bool dqgemm_tc_takes(const WRef& w, int64_t M);
+int64_t dqgemm_tc_padded_rows(const WRef& w, int64_t M);
 bool gemv_cs_q8_0_shape_ok(const WRef& w, int M);
 size_t gemv_cs_q8_0_workspace_bytes(const WRef& w, int M);
 int launch_gemv_cs_q8_0(const WRef& w, const void* x, int x_type, float* y, const float* residual, uint8_t* ws,
@@ -263,6 +279,15 @@ int launch_linear_swiglu(const WRef& wg, const WRef& wu, const float* x, int64_t
 
 int launch_rms_norm(const float* x, const void* w, int w_type, int64_t rows, int64_t width,
                     float eps, float* y, cudaStream_t s);
+// Rows of a prefill chunk / batched step feeding the dequant GEMM, one launch instead of three or four:
+//   v = (splits ? sum over the K-split sums partial[z][row][:] : x[row][:]) + residual[row][:]  -> hidden (if given)
+//   y = RMSNorm(v) * w, written as the GEMM's activation operand: xh[row][:] = f16(y * 2^k), inv_s[row] = 2^-k.
+// Bit for bit what tg_split_reduce_kernel, rms_norm_kernel and the GEMM's activation pass produce in turn.
+int launch_norm_prepare(const float* x, const float* partial, int splits, const float* residual, float* hidden,
+                        const void* w, int w_type, int64_t rows, int64_t width, float eps, __half* xh, float* inv_s,
+                        cudaStream_t s);
+// The same for the SwiGLU: rows of [gate | up] -> silu(gate) * up as the GEMM's activation operand.
+int launch_silu_prepare(const float* gate_up, int64_t rows, int64_t inter, __half* xh, float* inv_s, cudaStream_t s);
 // One row of [gate | up] (2 * inter values, deferred or in `gate_up`): y = silu(gate) * up
 int launch_silu_mul_deferred(const Deferred& d, const float* gate_up, int64_t inter, float* y, cudaStream_t s);
 int launch_rope(float* x, int64_t s_rows, int64_t heads, int64_t d, int64_t start_pos,

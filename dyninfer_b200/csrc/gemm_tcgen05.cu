@@ -803,21 +803,21 @@ struct TgScratch {
 
 }  // namespace
 
-// Tensor-core dequant GEMM. *handled = false when the encoding or shape does not qualify.
-int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float* y, const float* residual,
-                     cudaStream_t s, bool* handled) {
-  *handled = false;
-  if (!tg_shape_ok(w, M)) return 0;
-  const int64_t K = w.cols;
+namespace {
+struct TgPlan {
+  int64_t mtiles, Mpad;
+  int bn, cols, splits, nk_split;
+};
+// activation rows per CTA: as many as fit one accumulator (256), rounded up to the MMA granule.
+// Few weight-row tiles would leave most SMs idle: K is split first (at least 4 chunks = 256 elements
+// per CTA, at most 8 ways; the CTAs of a split dequantise disjoint parts of the tile, a second pass
+// adds their sums), and only a product whose K cannot be split gets narrower activation tiles, down
+// to 32 rows (each of those re-dequantises the whole weight tile: measured 116 us against 91 us with
+// the K split on 4096 x 12288 x 512)
+TgPlan tg_plan(const WRef& w, int64_t M) {
   const int sms = std::max(1, sm_count());
-  // activation rows per CTA: as many as fit one accumulator (256), rounded up to the MMA granule.
-  // Few weight-row tiles would leave most SMs idle: K is split first (at least 4 chunks = 256 elements
-  // per CTA, at most 8 ways; the CTAs of a split dequantise disjoint parts of the tile, a second pass
-  // adds their sums), and only a product whose K cannot be split gets narrower activation tiles, down
-  // to 32 rows (each of those re-dequantises the whole weight tile: measured 116 us against 91 us with
-  // the K split on 4096 x 12288 x 512)
   const int64_t ntiles = (w.rows + TG_BM - 1) / TG_BM;
-  const int nk_all = (int)(K / TG_BK);
+  const int nk_all = (int)(w.cols / TG_BK);
   auto k_splits = [&](int64_t ctas) {
     int sp = 1;
     while (sp < 8 && ctas * (sp * 2) <= sms && nk_all / (sp * 2) >= 4) sp *= 2;
@@ -826,30 +826,56 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
   int64_t cap_rows = 256;
   if (k_splits(ntiles * ((M + 255) / 256)) == 1)
     while (cap_rows > 32 && ntiles * ((M + cap_rows / 2 - 1) / (cap_rows / 2)) <= sms) cap_rows /= 2;  // stay within one wave
-  const int64_t mtiles = (M + cap_rows - 1) / cap_rows;
-  int bn = (int)((M + mtiles - 1) / mtiles);
-  bn = (bn + 15) / 16 * 16;
-  const int64_t Mpad = mtiles * bn;
-  int cols = 32;
-  while (cols < bn) cols *= 2;
-  int splits = k_splits(ntiles * mtiles);
-  const int nk_split = (nk_all + splits - 1) / splits;
-  splits = (nk_all + nk_split - 1) / nk_split;
-  const size_t xh_bytes = ((size_t)Mpad * K * 2 + 255) / 256 * 256;
-  const size_t inv_bytes = ((size_t)Mpad * 4 + 255) / 256 * 256;
-  const size_t part_bytes = splits > 1 ? (size_t)splits * M * w.rows * 4 : 0;
+  TgPlan p;
+  p.mtiles = (M + cap_rows - 1) / cap_rows;
+  p.bn = (int)((M + p.mtiles - 1) / p.mtiles);
+  p.bn = (p.bn + 15) / 16 * 16;
+  p.Mpad = p.mtiles * p.bn;
+  p.cols = 32;
+  while (p.cols < p.bn) p.cols *= 2;
+  p.splits = k_splits(ntiles * p.mtiles);
+  p.nk_split = (nk_all + p.splits - 1) / p.splits;
+  p.splits = (nk_all + p.nk_split - 1) / p.nk_split;
+  return p;
+}
+}  // namespace
+
+bool dqgemm_tc_takes(const WRef& w, int64_t M) { return tg_shape_ok(w, M); }
+int64_t dqgemm_tc_padded_rows(const WRef& w, int64_t M) { return tg_shape_ok(w, M) ? tg_plan(w, M).Mpad : 0; }
+
+// Tensor-core dequant GEMM. *handled = false when the encoding or shape does not qualify.
+int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float* y, const float* residual,
+                     cudaStream_t s, bool* handled, TgIo* io) {
+  *handled = false;
+  if (io) io->splits = 0;
+  if (!tg_shape_ok(w, M)) return 0;
+  const int64_t K = w.cols;
+  const TgPlan pl = tg_plan(w, M);
+  const int64_t mtiles = pl.mtiles, Mpad = pl.Mpad;
+  const int bn = pl.bn, cols = pl.cols, nk_split = pl.nk_split;
+  int splits = pl.splits;
+  const bool prepared = io && io->xh;
+  DYN_CHECK(!prepared || Mpad <= io->rows_alloc, "dequant GEMM: %lld prepared rows, %lld needed", (long long)(io ? io->rows_alloc : 0),
+            (long long)Mpad);
+  const size_t part_need = splits > 1 ? (size_t)splits * M * w.rows * 4 : 0;
+  const bool part_out = io && io->partial && part_need && part_need <= io->partial_bytes;  // the caller adds the sums
+  const size_t xh_bytes = prepared ? 0 : ((size_t)Mpad * K * 2 + 255) / 256 * 256;
+  const size_t inv_bytes = prepared ? 0 : ((size_t)Mpad * 4 + 255) / 256 * 256;
+  const size_t part_bytes = part_out ? 0 : part_need;
   TgScratch ws(s);
-  if (ws.take(xh_bytes + inv_bytes + part_bytes)) return 1;
-  __half* xh = reinterpret_cast<__half*>(ws.ptr);
-  float* inv_s = reinterpret_cast<float*>(ws.ptr + xh_bytes);
-  float* partial = splits > 1 ? reinterpret_cast<float*>(ws.ptr + xh_bytes + inv_bytes) : nullptr;
+  if (xh_bytes + inv_bytes + part_bytes && ws.take(xh_bytes + inv_bytes + part_bytes)) return 1;
+  const __half* xh = prepared ? io->xh : reinterpret_cast<__half*>(ws.ptr);
+  const float* inv_s = prepared ? io->inv_s : reinterpret_cast<float*>(ws.ptr + xh_bytes);
+  float* partial = part_out ? io->partial : (splits > 1 ? reinterpret_cast<float*>(ws.ptr + xh_bytes + inv_bytes) : nullptr);
   int* err = device_error_word();
   if (!err) return 1;
-  tg_prepare_x_kernel<<<(unsigned)Mpad, 256, 0, s>>>(x, x_type == E_BF16 ? 1 : 0, M, K, xh, inv_s);
+  if (!prepared)
+    tg_prepare_x_kernel<<<(unsigned)Mpad, 256, 0, s>>>(x, x_type == E_BF16 ? 1 : 0, M, K, reinterpret_cast<__half*>(ws.ptr),
+                                                       reinterpret_cast<float*>(ws.ptr + xh_bytes));
   TgArgs a;
   a.w = w, a.xh = xh, a.inv_s = inv_s, a.M = M, a.bn = bn, a.tmem_cols = cols, a.y = y, a.residual = residual, a.error = err;
   CUtensorMap xmap;
-  if (tg_make_xmap(xh, Mpad, K, bn, &xmap)) return 1;
+  if (tg_make_xmap(const_cast<__half*>(xh), Mpad, K, bn, &xmap)) return 1;
   a.nk_split = nk_split, a.partial = partial;
   const dim3 grid((unsigned)((w.rows + TG_BM - 1) / TG_BM), (unsigned)mtiles, (unsigned)splits);
   const bool a_tmem = tg_a_in_tmem(w.enc);
@@ -875,8 +901,10 @@ int launch_dqgemm_tc(const WRef& w, const void* x, int x_type, int64_t M, float*
     default: break;
   }
   if (rc) return rc;
-  count_launch(2);
-  if (splits > 1) {
+  count_launch(prepared ? 1 : 2);
+  if (part_out) {
+    io->splits = splits;
+  } else if (splits > 1) {
     const int64_t count = M * w.rows;
     tg_split_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, s>>>(partial, splits, count, y, residual);
     count_launch();

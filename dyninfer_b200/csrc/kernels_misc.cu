@@ -122,6 +122,121 @@ __device__ __forceinline__ void deferred_sums(const float* __restrict__ partial,
   }
 }
 
+// ---- producers of the dequant GEMM's activation operand ------------------------------------------
+// max |v| over the block -> the power-of-two scale that puts it in [2^12, 2^13) (the GEMM's activation
+// pass: no overflow, ordinary entries stay out of the f16 subnormals) and its inverse
+__device__ __forceinline__ void f16_row_scale(float mx, float* red, float* sc, float* inv) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  mx = warp_max(mx);
+  __syncthreads();
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = 0.f;
+  for (int i = 0; i < nw; i++) mx = fmaxf(mx, red[i]);
+  int e = 0;
+  if (mx > 0.f && mx < 3.0e38f) frexpf(mx, &e);
+  *sc = ldexpf(1.0f, 13 - e);
+  *inv = ldexpf(1.0f, e - 13);
+}
+
+template <int PER>
+__global__ void __launch_bounds__(256)
+norm_prepare_kernel(const float* __restrict__ x, const float* __restrict__ partial, int S, int64_t rows,
+                    const float* residual, float* hidden, const void* __restrict__ w, int w_type, int64_t width,
+                    float eps, __half* __restrict__ xh, float* __restrict__ inv_s) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  float v[PER], wv[PER];
+#pragma unroll
+  for (int k = 0; k < PER; k++) {
+    const int64_t i = threadIdx.x + (int64_t)k * blockDim.x;
+    float t = 0.f;
+    if (i < width) {
+      if (S) {
+        for (int z = 0; z < S; z++) t += partial[((int64_t)z * rows + row) * width + i];
+      } else {
+        t = x[row * width + i];
+      }
+    }
+    v[k] = t;
+  }
+  if (residual) {
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+      const int64_t i = threadIdx.x + (int64_t)k * blockDim.x;
+      if (i < width) v[k] += residual[row * width + i];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < PER; k++) {
+    const int64_t i = threadIdx.x + (int64_t)k * blockDim.x;
+    wv[k] = i < width ? aux_load(reinterpret_cast<const uint8_t*>(w), w_type, i) : 0.f;
+    if (hidden && i < width) hidden[row * width + i] = v[k];
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < PER; k++) ss = fmaf(v[k], v[k], ss);  // absent elements add +0
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  float mx = 0.f;
+#pragma unroll
+  for (int k = 0; k < PER; k++) {
+    v[k] = __fmul_rn(__fmul_rn(v[k], inv), wv[k]);
+    mx = fmaxf(mx, fabsf(v[k]));
+  }
+  float sc, is;
+  f16_row_scale(mx, red, &sc, &is);
+  if (threadIdx.x == 0) inv_s[row] = is;
+#pragma unroll
+  for (int k = 0; k < PER; k++) {
+    const int64_t i = threadIdx.x + (int64_t)k * blockDim.x;
+    if (i < width) xh[row * width + i] = __float2half_rn(v[k] * sc);
+  }
+}
+
+int launch_norm_prepare(const float* x, const float* partial, int splits, const float* residual, float* hidden,
+                        const void* w, int w_type, int64_t rows, int64_t width, float eps, __half* xh, float* inv_s,
+                        cudaStream_t s) {
+  if (rows == 0) return 0;
+  const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 32);  // rms_norm_kernel's: same summation order
+  DYN_CHECK(width <= 32 * threads, "row of %lld elements is too wide for the fused RMSNorm", (long long)width);
+  const int S = splits > 1 ? splits : 0;
+  if (width <= 8 * threads)
+    norm_prepare_kernel<8><<<(unsigned)rows, threads, 0, s>>>(x, partial, S, rows, residual, hidden, w, w_type, width, eps, xh, inv_s);
+  else if (width <= 16 * threads)
+    norm_prepare_kernel<16><<<(unsigned)rows, threads, 0, s>>>(x, partial, S, rows, residual, hidden, w, w_type, width, eps, xh, inv_s);
+  else
+    norm_prepare_kernel<32><<<(unsigned)rows, threads, 0, s>>>(x, partial, S, rows, residual, hidden, w, w_type, width, eps, xh, inv_s);
+  count_launch();
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
+__global__ void __launch_bounds__(256)
+silu_prepare_kernel(const float* __restrict__ gu, int64_t I, __half* __restrict__ xh, float* __restrict__ inv_s) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const float* g = gu + row * 2 * I;
+  auto val = [&](int64_t i) {
+    const float gv = g[i];
+    return (gv / (1.0f + expf(-gv))) * g[I + i];
+  };
+  float mx = 0.f;
+  for (int64_t i = threadIdx.x; i < I; i += blockDim.x) mx = fmaxf(mx, fabsf(val(i)));
+  float sc, is;
+  f16_row_scale(mx, red, &sc, &is);
+  if (threadIdx.x == 0) inv_s[row] = is;
+  for (int64_t i = threadIdx.x; i < I; i += blockDim.x) xh[row * I + i] = __float2half_rn(val(i) * sc);
+}
+
+int launch_silu_prepare(const float* gate_up, int64_t rows, int64_t inter, __half* xh, float* inv_s, cudaStream_t s) {
+  if (rows == 0 || inter == 0) return 0;
+  silu_prepare_kernel<<<(unsigned)rows, 256, 0, s>>>(gate_up, inter, xh, inv_s);
+  count_launch();
+  DYN_CUDA(cudaGetLastError());
+  return 0;
+}
+
 // Rotate-half RoPE (kernels.rs:1053-1064): pair (i, i + d/2).
 __device__ __forceinline__ void rope_pair(float x1, float x2, float pos, float freq, float* lo,
                                           float* hi) {

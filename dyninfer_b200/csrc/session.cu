@@ -78,6 +78,12 @@ struct dyninfer_cuda_session_t {
   int64_t max_rows = 0;
   float *hidden = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ctx = nullptr,
         *act = nullptr, *up = nullptr, *logits = nullptr;
+  // many-row steps: the dequant GEMM's activation operand written by the norm / SwiGLU kernels, and the
+  // K-split sums of o / down waiting for the residual + norm kernel
+  __half* xh = nullptr;
+  float *xinv = nullptr, *gpart = nullptr;
+  int64_t xh_rows = 0, xh_cols = 0;
+  size_t gpart_bytes = 0;
   float *qkv1 = nullptr, *gu1 = nullptr;  // rows of [q | k | v] and of [gate | up] for the fused products
   int64_t *tokens_dev = nullptr, *row_pos_dev = nullptr, *row_seq_dev = nullptr,
           *out_token_dev = nullptr, *hist_dev = nullptr, *hist_count_dev = nullptr;
@@ -357,8 +363,101 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
     if (d->S) thread_scratch_hold(d->ws_bytes);
     return 0;
   };
+  // Many rows on one GPU (prefill chunks, wide batched steps), every product on the dequant GEMM: RMSNorm
+  // and SwiGLU write the GEMM's activation operand themselves (f16 rows + inverse scales) and the K-split
+  // sums of o / down are added inside the following residual + RMSNorm kernel -- 11 instead of 16 launches
+  // per layer and five passes over the activations fewer, with the same bits as the separate kernels.
+  bool fuse_n = rows > 16 && !tp && s->xh && H <= 8192;
+  for (int l = 0; l < c.layers && fuse_n; l++) {
+    const LayerW& L = s->layers[l];
+    const WRef* ws[8] = {L.qkv_parts >= 2 ? &L.qkv : &L.q, L.qkv_parts >= 2 ? nullptr : &L.k, L.qkv_parts == 3 ? nullptr : &L.v,
+                         &L.o, L.gate_up.data ? &L.gate_up : &L.gate, L.gate_up.data ? nullptr : &L.up, &L.down, nullptr};
+    for (const WRef* w : ws)
+      if (w && !(dqgemm_tc_takes(*w, rows) && dqgemm_tc_padded_rows(*w, rows) <= s->xh_rows)) fuse_n = false;
+    if (H > s->xh_cols || c.inter > s->xh_cols) fuse_n = false;
+  }
+  bool xh_ready = false;  // xh already holds this layer's normalised rows (written by the layer before)
+  auto gemm = [&](const WRef& w, const float* x, bool prepared, float* y, const float* residual, TgIo* io) -> int {
+    TgIo local;
+    if (!io) io = &local;
+    if (prepared) io->xh = s->xh, io->inv_s = s->xinv, io->rows_alloc = s->xh_rows;
+    bool handled = false;
+    if (launch_dqgemm_tc(w, x, E_F32, rows, y, residual, st, &handled, io)) return 1;
+    DYN_CHECK(handled, "dequant GEMM refused a product it had accepted");
+    return 0;
+  };
   for (int l = 0; l < c.layers; l++) {
     const LayerW& L = s->layers[l];
+    if (fuse_n) {
+      if (!xh_ready && launch_norm_prepare(s->hidden, nullptr, 0, nullptr, nullptr, L.attn_norm.ptr, L.attn_norm.type, rows, H,
+                                           c.eps, s->xh, s->xinv, st))
+        return 1;
+      xh_ready = false;
+      float *qp = s->q, *kp = s->k, *vp = s->v;
+      int64_t ldq = 0, ldk = 0, ldv = 0;
+      if (L.qkv_parts >= 2) {
+        qp = s->qkv1, kp = qp + qd;
+        ldq = ldk = L.qkv_parts == 3 ? qd + 2 * kvd : qd + kvd;
+        if (gemm(L.qkv, nullptr, true, qp, nullptr, nullptr)) return 1;
+        if (L.qkv_parts == 3) vp = kp + kvd, ldv = ldq;
+        else if (gemm(L.v, nullptr, true, vp, nullptr, nullptr)) return 1;
+      } else if (gemm(L.q, nullptr, true, qp, nullptr, nullptr) || gemm(L.k, nullptr, true, kp, nullptr, nullptr) ||
+                 gemm(L.v, nullptr, true, vp, nullptr, nullptr)) {
+        return 1;
+      }
+      QkvPrepArgs pa{};
+      pa.q = qp, pa.k = kp, pa.v = vp;
+      pa.kcache = s->kcache + (size_t)l * layer_stride;
+      pa.vcache = s->vcache + (size_t)l * layer_stride;
+      pa.q_norm_w = L.q_norm.ptr, pa.k_norm_w = L.k_norm.ptr, pa.norm_w_type = L.q_norm.type;
+      pa.row_pos = s->row_pos_dev, pa.row_seq = s->row_seq_dev, pa.base_pos = 0;
+      pa.rows = rows, pa.nh = c.heads, pa.nkv = c.kv_heads, pa.d = c.head_dim, pa.cap = cap;
+      pa.kv_type = s->kv_type, pa.has_norm = c.qk_norm ? 1 : 0, pa.has_rope = c.rope ? 1 : 0;
+      pa.eps = c.eps;
+      pa.ldq = ldq, pa.ldk = ldk, pa.ldv = ldv;
+      if (launch_qkv_prepare(pa, s->freq, st)) return 1;
+      AttnArgs aa{};
+      aa.q = qp, aa.kcache = pa.kcache, aa.vcache = pa.vcache;
+      aa.row_pos = s->row_pos_dev, aa.row_seq = s->row_seq_dev, aa.base_pos = 0;
+      aa.ctx = s->ctx;
+      aa.rows = rows, aa.nh = c.heads, aa.nkv = c.kv_heads, aa.d = c.head_dim, aa.cap = cap;
+      aa.kv_type = s->kv_type;
+      aa.ldq = ldq;
+      aa.uniform_base = chunk_start, aa.uniform_seq = chunk_slot;
+      if (launch_attention(aa, st)) return 1;
+      // o: hidden += W ctx, then the FFN norm straight into the GEMM's operand
+      TgIo io_o;
+      io_o.partial = s->gpart, io_o.partial_bytes = s->gpart_bytes;
+      if (gemm(L.o, s->ctx, false, s->hidden, s->hidden, &io_o)) return 1;
+      if (io_o.splits > 1 ? launch_norm_prepare(nullptr, s->gpart, io_o.splits, s->hidden, s->hidden, L.ffn_norm.ptr,
+                                                L.ffn_norm.type, rows, H, c.eps, s->xh, s->xinv, st)
+                          : launch_norm_prepare(s->hidden, nullptr, 0, nullptr, nullptr, L.ffn_norm.ptr, L.ffn_norm.type, rows,
+                                                H, c.eps, s->xh, s->xinv, st))
+        return 1;
+      bool act_prepared = false;
+      if (L.gate_up.data) {
+        if (gemm(L.gate_up, nullptr, true, s->gu1, nullptr, nullptr) ||
+            launch_silu_prepare(s->gu1, rows, c.inter, s->xh, s->xinv, st))
+          return 1;
+        act_prepared = true;
+      } else {
+        if (gemm(L.gate, nullptr, true, s->act, nullptr, nullptr) || gemm(L.up, nullptr, true, s->up, nullptr, nullptr) ||
+            launch_silu_mul(s->act, s->up, rows * c.inter, s->act, st))
+          return 1;
+      }
+      // down: hidden += W act; with another layer to come, its attention norm rides on the addition
+      TgIo io_d;
+      if (l + 1 < c.layers) io_d.partial = s->gpart, io_d.partial_bytes = s->gpart_bytes;
+      if (gemm(L.down, act_prepared ? nullptr : s->act, act_prepared, s->hidden, s->hidden, &io_d)) return 1;
+      if (io_d.splits > 1) {
+        const NormW& nw = s->layers[l + 1].attn_norm;
+        if (launch_norm_prepare(nullptr, s->gpart, io_d.splits, s->hidden, s->hidden, nw.ptr, nw.type, rows, H, c.eps, s->xh,
+                                s->xinv, st))
+          return 1;
+        xh_ready = true;
+      }
+      continue;
+    }
     if (!normed &&
         launch_rms_norm(s->hidden, L.attn_norm.ptr, L.attn_norm.type, rows, H, c.eps, s->xn, st))
       return 1;
@@ -1105,7 +1204,7 @@ void dyninfer_cuda_session_destroy(dyninfer_cuda_session_t* s) {
                  s->logits, s->tokens_dev, s->row_pos_dev, s->row_seq_dev, s->out_token_dev,
                  s->hist_dev, s->hist_count_dev, s->argmax_scratch, s->mega_layers, s->io_dev,
                  s->prof_dev, s->trace_dev, s->prog_dev, s->ll_dev, s->batch_logits, s->batch_tokens_dev, s->tp_part, s->tp_logits,
-                 s->tp_gather, s->scratch, s->qkv1, s->gu1};
+                 s->tp_gather, s->scratch, s->qkv1, s->gu1, s->xh, s->xinv, s->gpart};
   for (void* p : dev)
     if (p) cudaFree(p);
   if (s->logits_host) cudaFreeHost(s->logits_host);
@@ -1158,6 +1257,10 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
         dev_alloc(s, (void**)&s->xn, (size_t)rows * c.hidden * 4) ||
         dev_alloc(s, (void**)&s->ctx, (size_t)rows * qd * 4) ||
         dev_alloc(s, (void**)&s->act, (size_t)rows * c.inter * 4) ||
+        (c.tp_world == 1 && rows > 16 &&
+         (dev_alloc(s, (void**)&s->xh, (size_t)(rows + rows / 2 + 64) * std::max(c.hidden, c.inter) * 2) ||
+          dev_alloc(s, (void**)&s->xinv, (size_t)(rows + rows / 2 + 64) * 4) ||
+          dev_alloc(s, (void**)&s->gpart, (size_t)8 * rows * c.hidden * 4))) ||
         dev_alloc(s, (void**)&s->qkv1, (size_t)rows * (qd + 2 * kvd) * 4) ||
         dev_alloc(s, (void**)&s->gu1, (size_t)rows * 2 * c.inter * 4) ||
         (c.tp_world > 1 && dev_alloc(s, (void**)&s->tp_part, (size_t)rows * c.hidden * 4)) ||
@@ -1166,6 +1269,7 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
         dev_alloc(s, (void**)&s->row_seq_dev, (size_t)rows * 8) ||
         host_alloc(s, (void**)&s->stage_host, (size_t)(8 + 3 * rows) * 8))
       return 1;
+    if (s->xh) s->xh_rows = rows + rows / 2 + 64, s->xh_cols = std::max(c.hidden, c.inter), s->gpart_bytes = (size_t)8 * rows * c.hidden * 4;
     // the separate-product path writes dense q, k, v and `up` into the same buffers
     s->q = s->qkv1, s->k = s->q + rows * qd, s->v = s->k + rows * kvd;
     s->up = s->gu1;

@@ -61,9 +61,10 @@ struct DeferScope {
 // A column range of deferred sums (or nothing: S == 0)
 struct DeferredCols {
   const float* partial = nullptr;
-  const float* scale = nullptr;
+  const float* scale = nullptr;  // nullptr: the sums are already scaled (the dequant GEMM's)
   int S = 0;
   int64_t N = 0, col = 0;
+  int64_t rows = 1;  // rows per slice: slice j of row r starts at partial + (j * rows + r) * N
 };
 inline DeferredCols deferred_cols(const Deferred& d, int64_t col) {
   DeferredCols c;
@@ -313,7 +314,8 @@ struct QkvPrepArgs {
   // floats between consecutive rows of q / k / v (0: dense, nh*d / nkv*d): the three may be column
   // ranges of one [rows, nh*d + 2*nkv*d] matrix, the output of the fused [q; k; v] product
   int64_t ldq = 0, ldk = 0, ldv = 0;
-  // one row only: q / k / v still lie as K-slice sums of their product (the reduced q is written to `q`)
+  // q / k / v still lie as K-slice sums of their product (the reduced q is written to `q`): a single row's
+  // streaming GEMV, or all rows of a K-split dequant GEMM
   DeferredCols dq, dk, dv;
 };
 int launch_qkv_prepare(const QkvPrepArgs& a, const FreqTable& ft, cudaStream_t s);

@@ -102,7 +102,7 @@ int launch_rms_norm(const float* x, const void* w, int w_type, int64_t rows, int
 // reduction kernels), four slices' loads in flight at a time for all NE elements: a plain loop would wait
 // for one L2 round trip per slice and element.
 template <int NE>
-__device__ __forceinline__ void deferred_sums(const float* __restrict__ partial, int S, int64_t N,
+__device__ __forceinline__ void deferred_sums(const float* __restrict__ partial, int S, int64_t N,  // N: floats between slices
                                               const int64_t (&idx)[NE], const bool (&live)[NE], float (&out)[NE]) {
 #pragma unroll
   for (int e = 0; e < NE; e++) out[e] = 0.f;
@@ -396,8 +396,8 @@ __global__ void __launch_bounds__(128) qkv_prepare_kernel(QkvPrepArgs a, FreqTab
         const int64_t i = threadIdx.x + (int64_t)e * blockDim.x;
         live[e] = i < d, idx[e] = dc.col + head * d + i;
       }
-      deferred_sums<4>(dc.partial, dc.S, dc.N, idx, live, t);
-      const float sc = dc.scale[0];
+      deferred_sums<4>(dc.partial + r * dc.N, dc.S, dc.rows * dc.N, idx, live, t);
+      const float sc = dc.scale ? dc.scale[0] : 1.0f;
 #pragma unroll
       for (int e = 0; e < 4; e++) {
         const int64_t i = threadIdx.x + (int64_t)e * blockDim.x;

@@ -365,7 +365,8 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
   };
   // Many rows on one GPU (prefill chunks, wide batched steps), every product on the dequant GEMM: RMSNorm
   // and SwiGLU write the GEMM's activation operand themselves (f16 rows + inverse scales) and the K-split
-  // sums of o / down are added inside the following residual + RMSNorm kernel -- 11 instead of 16 launches
+  // sums of o / down are added inside the following residual + RMSNorm kernel, those of a single [q; k; v]
+  // product inside QKV prepare -- 10 instead of 16 launches
   // per layer and five passes over the activations fewer, with the same bits as the separate kernels.
   bool fuse_n = rows > 16 && !tp && s->xh && H <= 8192;
   for (int l = 0; l < c.layers && fuse_n; l++) {
@@ -395,10 +396,12 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
       xh_ready = false;
       float *qp = s->q, *kp = s->k, *vp = s->v;
       int64_t ldq = 0, ldk = 0, ldv = 0;
+      TgIo io_q;  // one [q; k; v] product: its K-split sums are added inside QKV prepare
       if (L.qkv_parts >= 2) {
         qp = s->qkv1, kp = qp + qd;
         ldq = ldk = L.qkv_parts == 3 ? qd + 2 * kvd : qd + kvd;
-        if (gemm(L.qkv, nullptr, true, qp, nullptr, nullptr)) return 1;
+        if (L.qkv_parts == 3) io_q.partial = s->gpart, io_q.partial_bytes = s->gpart_bytes;
+        if (gemm(L.qkv, nullptr, true, qp, nullptr, &io_q)) return 1;
         if (L.qkv_parts == 3) vp = kp + kvd, ldv = ldq;
         else if (gemm(L.v, nullptr, true, vp, nullptr, nullptr)) return 1;
       } else if (gemm(L.q, nullptr, true, qp, nullptr, nullptr) || gemm(L.k, nullptr, true, kp, nullptr, nullptr) ||
@@ -415,6 +418,12 @@ int enqueue_forward(Session* s, int64_t rows, int64_t logits_row, bool all_rows 
       pa.kv_type = s->kv_type, pa.has_norm = c.qk_norm ? 1 : 0, pa.has_rope = c.rope ? 1 : 0;
       pa.eps = c.eps;
       pa.ldq = ldq, pa.ldk = ldk, pa.ldv = ldv;
+      if (io_q.splits > 1) {
+        DeferredCols dc;
+        dc.partial = s->gpart, dc.S = io_q.splits, dc.N = qd + 2 * kvd, dc.rows = rows;
+        pa.dq = dc, pa.dk = dc, pa.dv = dc;
+        pa.dk.col = qd, pa.dv.col = qd + kvd;
+      }
       if (launch_qkv_prepare(pa, s->freq, st)) return 1;
       AttnArgs aa{};
       aa.q = qp, aa.kcache = pa.kcache, aa.vcache = pa.vcache;
@@ -1260,7 +1269,7 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
         (c.tp_world == 1 && rows > 16 &&
          (dev_alloc(s, (void**)&s->xh, (size_t)(rows + rows / 2 + 64) * std::max(c.hidden, c.inter) * 2) ||
           dev_alloc(s, (void**)&s->xinv, (size_t)(rows + rows / 2 + 64) * 4) ||
-          dev_alloc(s, (void**)&s->gpart, (size_t)8 * rows * c.hidden * 4))) ||
+          dev_alloc(s, (void**)&s->gpart, (size_t)8 * rows * std::max<int64_t>(c.hidden, qd + 2 * kvd) * 4))) ||
         dev_alloc(s, (void**)&s->qkv1, (size_t)rows * (qd + 2 * kvd) * 4) ||
         dev_alloc(s, (void**)&s->gu1, (size_t)rows * 2 * c.inter * 4) ||
         (c.tp_world > 1 && dev_alloc(s, (void**)&s->tp_part, (size_t)rows * c.hidden * 4)) ||
@@ -1269,7 +1278,7 @@ int dyninfer_cuda_session_configure_paged_kv(dyninfer_cuda_session_t* s, size_t 
         dev_alloc(s, (void**)&s->row_seq_dev, (size_t)rows * 8) ||
         host_alloc(s, (void**)&s->stage_host, (size_t)(8 + 3 * rows) * 8))
       return 1;
-    if (s->xh) s->xh_rows = rows + rows / 2 + 64, s->xh_cols = std::max(c.hidden, c.inter), s->gpart_bytes = (size_t)8 * rows * c.hidden * 4;
+    if (s->xh) s->xh_rows = rows + rows / 2 + 64, s->xh_cols = std::max(c.hidden, c.inter), s->gpart_bytes = (size_t)8 * rows * std::max<int64_t>(c.hidden, qd + 2 * kvd) * 4;
     // the separate-product path writes dense q, k, v and `up` into the same buffers
     s->q = s->qkv1, s->k = s->q + rows * qd, s->v = s->k + rows * kvd;
     s->up = s->gu1;

@@ -25,6 +25,22 @@ def test_qwen3_0_6b_coverage_counts():
     rep.require_complete()
 
 
+def test_k_quant_and_iq4_xs_files_are_covered():
+    """A file that mixes Q4_K, Q5_K, IQ4_XS and Q6_K linears (the Q4_K_M / UD-Q4_K_XL kind) is fully covered on
+    the cuda target; the container knows their block geometry."""
+    cfg = dict(synth.QWEN3_0_6B, qk_norm=True, rope=True)
+    p = _params(cfg, enc="gguf.q4_k")
+    for l in range(cfg["layers"]):
+        p[f"blk.{l}.attn_k.weight"] = ("gguf.iq4_xs", p[f"blk.{l}.attn_k.weight"][1])
+        p[f"blk.{l}.ffn_down.weight"] = ("gguf.q5_k", p[f"blk.{l}.ffn_down.weight"][1])
+    rep = reg.dry_run_coverage(cfg, p, reg.TargetProfile.cuda())
+    assert rep.requests == 1240 and not rep.missing
+    ids = {k for _, _, k in rep.selected}
+    assert {"gguf.q4_k.matmul.cuda_sm100", "gguf.q5_k.matmul.cuda_sm100", "gguf.iq4_xs.matmul.cuda_sm100"} <= ids
+    assert ck.GGML_TYPES[23] == ("gguf.iq4_xs", 256, 136) and ck.GGML_TYPES[12] == ("gguf.q4_k", 256, 144)
+    assert ck.GGML_CODE["gguf.iq4_xs"] == 23 and 23 not in ck.GGML_SCHEMA_ONLY
+
+
 def test_exact_backend_bonus_and_tie_break():
     r = reg.default_registry()
     rep = r.select(reg.KernelRequest("x", "RmsNorm"), reg.TargetProfile.cuda())

@@ -1,16 +1,18 @@
-// Dequant-in-shared-memory GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) for prefill
-// and every product with many activation rows: y[m, n] = sum_k x[m, k] * w[n, k], f32 accumulate.
+// Dequant GEMM on the 5th-generation tensor cores (tcgen05 + TMEM) for prefill and every product
+// with many activation rows: y[m, n] = sum_k x[m, k] * w[n, k], f32 accumulate.
 //
 // One CTA computes a 128 (weight rows) x BN (activation rows, <= 256) tile of y^T:
-//   * sixteen warps dequantise (four groups of four, one pipeline stage each): for every 64-wide K chunk they decode the raw checkpoint blocks of
-//     the tile's 128 rows (Q4_0, Q4_1, Q8_0, Q6_K and MLX-U4 with word fetches issued a step ahead and
-//     packed f16 / f32 arithmetic that rounds like the decoders of codec.cuh; the other encodings
-//     through those decoders) and round to f16. Q4_0, Q4_1, Q8_0 and MLX-U4 write the A operand into
-//     tensor memory (tcgen05.st, thread = weight row, column = two consecutive K elements); the others
-//     store it in shared memory in the canonical K-major 128-byte-swizzled layout (8-row groups of
-//     1024 bytes, 16-byte chunk c of row r at position c ^ (r & 7));
-//   * one thread of another warp fetches the matching activation chunk (f16, prepared once per call) as the
-//     B operand with a 2-D TMA tile copy (cp.async.bulk.tensor, hardware 128-byte swizzle);
+//   * sixteen warps dequantise (four groups of four, one pipeline stage each): for every 64-wide K chunk
+//     they decode the raw checkpoint blocks of the tile's 128 rows (every quantised encoding with word
+//     fetches issued a step ahead and packed f16 / f32 arithmetic that rounds like the decoders of
+//     codec.cuh; plain f32 / f16 / bf16 weights through those decoders) and round to f16. Q4_0, Q4_1,
+//     Q8_0, MLX-U4, Q4_K, Q5_K and IQ4_XS write the A operand into tensor memory (tcgen05.st, thread =
+//     weight row, column = two consecutive K elements); Q6_K and the plain types store it in shared
+//     memory in the canonical K-major 128-byte-swizzled layout (8-row groups of 1024 bytes, 16-byte
+//     chunk c of row r at position c ^ (r & 7));
+//   * one thread of another warp fetches the matching activation chunk (f16, prepared once per call, or
+//     by the caller's norm / SwiGLU kernel: TgIo) as the B operand with a 2-D TMA tile copy
+//     (cp.async.bulk.tensor, hardware 128-byte swizzle);
 //   * one thread of a third issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16, four per
 //     chunk) with the accumulator in tensor memory, and releases each stage with tcgen05.commit;
 //   * all warps (after their pipeline roles) read the accumulator back with tcgen05.ld (lane = weight row,

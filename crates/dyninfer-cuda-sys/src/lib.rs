@@ -259,4 +259,5 @@ unsafe extern "C" {
         out_needed: *mut usize,
     ) -> c_int;
     pub fn dyninfer_cuda_session_launch_count(session: *const dyninfer_cuda_session_t) -> u64;
+    pub fn dyninfer_cuda_session_timer(session: *mut dyninfer_cuda_session_t, stop: c_int, out_ms: *mut f32) -> c_int;
 }

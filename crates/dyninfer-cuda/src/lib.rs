@@ -356,6 +356,22 @@ impl Context {
         self.with_session(|s| Ok(unsafe { sys::dyninfer_cuda_session_decode_weight_bytes(s) }))
     }
 
+    /// Starts the device-side stopwatch on the session's stream (after the work queued so far).
+    pub fn timer_start(&self) -> Result<()> {
+        // SAFETY: valid handle; a null output is allowed when `stop` is 0.
+        self.with_session(|s| check(unsafe { sys::dyninfer_cuda_session_timer(s, 0, std::ptr::null_mut()) }))
+    }
+
+    /// Stops the stopwatch, waits for the stream and returns the milliseconds it spent since `timer_start`.
+    pub fn timer_stop(&self) -> Result<f32> {
+        self.with_session(|s| {
+            let mut ms = 0f32;
+            // SAFETY: `ms` outlives the call.
+            check(unsafe { sys::dyninfer_cuda_session_timer(s, 1, &mut ms) })?;
+            Ok(ms)
+        })
+    }
+
     pub fn uses_persistent_kernel(&self) -> Result<bool> {
         // SAFETY: valid handle; read only.
         self.with_session(|s| Ok(unsafe { sys::dyninfer_cuda_session_uses_persistent_kernel(s) } != 0))

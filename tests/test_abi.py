@@ -70,3 +70,31 @@ def test_product_package_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
                 text = open(os.path.join(dirpath, f), errors="replace").read()
                 assert "oracle" not in text.lower(), f"{f} mentions the oracle"
+
+
+def _header_enums():
+    src = open(os.path.join(ROOT, "include", "dyninfer_cuda.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return {k: int(v) for k, v in re.findall(r"\b(DYNINFER_ENC_[A-Z0-9_]+)\s*=\s*(\d+)", src)}
+
+
+def test_rust_ffi_crate_follows_the_header():
+    """The crate is source only (no Rust toolchain here), so its text is held to the header: every export
+    declared once in the extern block, every encoding constant with the header's value."""
+    rs = open(os.path.join(ROOT, "crates", "dyninfer-cuda-sys", "src", "lib.rs")).read()
+    rs = re.sub(r"//[^\n]*", "", rs)
+    fns = re.findall(r"\bpub fn (dyninfer_cuda_[a-z0-9_]+)\s*\(", rs)
+    assert sorted(fns) == _declared(), set(fns) ^ set(_declared())
+    consts = {k: int(v) for k, v in re.findall(r"pub const (DYNINFER_ENC_[A-Z0-9_]+): i32 = (\d+);", rs)}
+    assert consts == _header_enums()
+
+
+def test_python_encoding_ids_follow_the_header():
+    enums = _header_enums()
+    names = {"plain.f32": "F32", "plain.f16": "F16", "plain.bf16": "BF16", "gguf.q4_0": "Q4_0",
+             "gguf.q4_1": "Q4_1", "gguf.q8_0": "Q8_0", "gguf.q6_k": "Q6_K", "mlx.affine.u4": "MLX_U4",
+             "gguf.q4_k": "Q4_K", "gguf.q5_k": "Q5_K", "gguf.iq4_xs": "IQ4_XS"}
+    assert set(_lib.ENC) == set(names)
+    for enc, short in names.items():
+        assert _lib.ENC[enc] == enums["DYNINFER_ENC_" + short], enc
+    assert sorted(enums.values()) == list(range(len(enums)))

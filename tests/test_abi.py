@@ -98,3 +98,20 @@ def test_python_encoding_ids_follow_the_header():
     for enc, short in names.items():
         assert _lib.ENC[enc] == enums["DYNINFER_ENC_" + short], enc
     assert sorted(enums.values()) == list(range(len(enums)))
+
+
+def test_struct_fields_agree_in_header_rust_and_ctypes():
+    """Field names and their order, struct by struct, in the three places that spell them out."""
+    hdr = open(os.path.join(ROOT, "include", "dyninfer_cuda.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    rs = open(os.path.join(ROOT, "crates", "dyninfer-cuda-sys", "src", "lib.rs")).read()
+    twins = {"dyninfer_cuda_weight_t": _lib.Weight, "dyninfer_cuda_parameter_file_t": _lib.ParameterFile,
+             "dyninfer_cuda_file_param_t": _lib.FileParam,
+             "dyninfer_cuda_allocator_statistics_t": _lib.AllocatorStatistics}
+    found = re.findall(r"typedef struct (\w+) \{(.*?)\}", hdr, flags=re.S)
+    assert {n for n, _ in found} == set(twins)
+    for name, body in found:
+        c_fields = [re.search(r"(\w+)\s*$", f.strip()).group(1) for f in body.split(";") if f.strip()]
+        rust_body = re.search(r"pub struct %s \{(.*?)\}" % name, rs, flags=re.S).group(1)
+        assert re.findall(r"pub (\w+):", rust_body) == c_fields, name
+        assert [f[0] for f in twins[name]._fields_] == c_fields, name

@@ -115,3 +115,13 @@ def test_struct_fields_agree_in_header_rust_and_ctypes():
         rust_body = re.search(r"pub struct %s \{(.*?)\}" % name, rs, flags=re.S).group(1)
         assert re.findall(r"pub (\w+):", rust_body) == c_fields, name
         assert [f[0] for f in twins[name]._fields_] == c_fields, name
+
+
+def test_safe_rust_crate_calls_only_declared_exports():
+    rs = open(os.path.join(ROOT, "crates", "dyninfer-cuda-sys", "src", "lib.rs")).read()
+    declared = set(re.findall(r"\bpub (?:fn|const|struct) (\w+)", rs))
+    src_dir = os.path.join(ROOT, "crates", "dyninfer-cuda", "src")
+    used = set()
+    for f in sorted(os.listdir(src_dir)):
+        used |= set(re.findall(r"\bsys::(\w+)", open(os.path.join(src_dir, f)).read()))
+    assert used and used <= declared, used - declared

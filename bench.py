@@ -4,15 +4,21 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 One step = one decode step (one generated token) of the seeded synthetic
-checkpoint (all linears Q4_0, tied Q6_K embedding / lm_head, GGUF v3), after a
-16-token prompt. Prints ONE JSON line on rank 0.
+checkpoint (all linears Q4_0, tied Q6_K embedding / lm_head, GGUF v3). The K timed
+steps are laid out the way the reference's perf runner lays out its iterations
+(crates/dyninfer-runtime/src/perf.rs:92-172): reset, prefill of the 16-token
+prompt (untimed), 32 greedy steps (timed), again until K steps are timed, so every
+timed step runs at the contexts of the named configuration (16 .. 48).
+Prints ONE JSON line on rank 0.
 
-  value     decode tok/s with everything resident in HBM: K launches of the persistent
-            decode kernel with the argmax fed back on the device, timed with CUDA
-            events on the session stream (max over ranks).
+  value     decode tok/s with everything resident in HBM: the persistent decode kernel
+            with the argmax fed back on the device (16 tokens per launch), timed with
+            CUDA events on the session stream, summed over the decode phases (max over
+            ranks).
   e2e       the same K steps through the public session call `decode_argmax`
             (C ABI `dyninfer_cuda_session_invoke_paged_chunk`): host token in from
-            pinned memory, argmax token out, every step.
+            pinned memory, argmax token out, every step; host clock around each decode
+            phase with a device synchronisation on both sides.
   roofline  the persistent decode kernel (the only kernel in the timed region): the
             weight bytes one token reads / its average launch time, against the
             measured HBM copy bandwidth. `roofline_lm_head_gemv` adds the largest
@@ -46,6 +52,7 @@ sys.path.insert(0, ROOT)
 
 WORKLOAD = "qwen3-0.6b-shape q4_0 (tied q6_k lm_head), batch 1, prompt 16, greedy decode"
 PROMPT_LEN = 16
+GEN_STEPS = 32           # greedy steps per generation of the named configuration
 SEED = 20240
 
 
@@ -399,29 +406,52 @@ def main():
         replicas.barrier()
         torch.cuda.synchronize()
 
+    def phases(n):
+        """n steps as decode phases of at most GEN_STEPS steps, each after its own prompt."""
+        return [GEN_STEPS] * (n // GEN_STEPS) + ([n % GEN_STEPS] if n % GEN_STEPS else [])
+
+    def begin_generation():
+        session.reset()
+        return session.prefill_argmax(prompt)
+
     # ---- device-resident arm
-    toks_w, _ = session.decode_loop(first, W)
     if args.decode_only:
+        toks_w, _ = session.decode_loop(first, W)
         _, ms = session.decode_loop(int(toks_w[-1]), K)
         print(json.dumps({"decode_only": True, "steps": K, "ms_per_step": ms / K}), flush=True)
         session.close()
         return
+    for n in phases(max(W, GEN_STEPS)):               # warm-up: at least one whole generation
+        session.decode_loop(begin_generation(), n)
     barrier()
-    launches0 = session.launch_count()
+    ms, gpu_launches, generations = 0.0, 0, []
     with ClockSampler(local_rank) as clocks:
-        toks, ms = session.decode_loop(int(toks_w[-1]), K)
+        for n in phases(K):
+            tok0 = begin_generation()
+            torch.cuda.synchronize()
+            launches0 = session.launch_count()
+            toks, ms_phase = session.decode_loop(tok0, n)
+            gpu_launches += session.launch_count() - launches0
+            ms += ms_phase
+            generations.append([int(tok0)] + [int(t) for t in toks])
         barrier()
-        gpu_launches = session.launch_count() - launches0
         # ---- end-to-end arm through the public per-token call
-        nxt = int(toks[-1])
-        for _ in range(W):
-            nxt = session.decode_argmax(nxt)
+        for n in phases(max(W, GEN_STEPS)):
+            nxt = begin_generation()
+            for _ in range(n):
+                nxt = session.decode_argmax(nxt)
         barrier()
-        t0 = time.perf_counter()
-        for _ in range(K):
-            nxt = session.decode_argmax(nxt)
-        torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
+        e2e_s, e2e_same = 0.0, True
+        for n in phases(K):
+            nxt = begin_generation()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(n):
+                nxt = session.decode_argmax(nxt)
+            torch.cuda.synchronize()
+            e2e_s += time.perf_counter() - t0
+            if n == len(generations[0]) - 1:            # the per-token call must end where the device loop did
+                e2e_same = e2e_same and int(nxt) == generations[0][-1]
     ms, e2e_ms = replicas.max_over_ranks([ms, e2e_s * 1e3], device="cuda")   # slowest rank decides
     e2e_s = e2e_ms / 1e3
     weight_bytes = session.decode_weight_bytes()
@@ -439,12 +469,14 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "kv_dtype": args.kv_dtype, "parallelism": f"replicas x{world}",
+                       "protocol": f"the reference perf runner's iterations: reset, prefill {PROMPT_LEN} (untimed), "
+                                   f"{GEN_STEPS} greedy steps (timed); {len(generations)} decode phases",
                        "l2": "inputs larger than L2: each step streams %.1f MB of weights" % (weight_bytes / 1e6),
                        "weight_bytes_per_step": weight_bytes},
             "weight_gbs": world * weight_bytes * K / (ms * 1e-3) / 1e9,
             "weight_hbm_frac_of_%s" % peak_kind: weight_bytes * K / (ms * 1e-3) / 1e9 / hbm_peak,
             "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 24,
-                    "d2h_bytes_per_step": 8},
+                    "d2h_bytes_per_step": 8, "last_token_equals_device_loop": bool(e2e_same)},
             "gpu_launches": int(gpu_launches),
             "clocks": clocks.summary(),
             # dominant kernel: the persistent decode kernel, the only kernel of the timed region; one
@@ -477,7 +509,11 @@ def main():
                 "sample": f"{steps} decode steps of the same model after the same {PROMPT_LEN}-token prompt "
                           f"({dt:.1f} s), CPU restatement of the reference's direct path"}
             # the same run checks the timed loop: its first tokens against the restatement's
-            out["parity"] = parity_against(cpu_toks, cpu_margins, [first] + [int(t) for t in toks_w] + [int(t) for t in toks])
+            out["parity"] = parity_against(cpu_toks, cpu_margins, generations[0])
+            # every timed generation repeats the first one token for token
+            full = [g for g in generations if len(g) == len(generations[0])]
+            out["parity"]["generations_identical"] = all(g == full[0] for g in full)
+            out["parity"]["ok"] = bool(out["parity"]["ok"] and out["parity"]["generations_identical"])
         if tp is not None:
             out["tp"] = tp
         print(json.dumps(out), flush=True)

@@ -120,6 +120,11 @@ class ClockSampler:
 MEGA_DRAM_TRAFFIC = 381_600_640 + 4_658_560
 
 
+def phases(n):
+    """n decode steps as decode phases of at most GEN_STEPS steps, each after its own prompt."""
+    return [GEN_STEPS] * (n // GEN_STEPS) + ([n % GEN_STEPS] if n % GEN_STEPS else [])
+
+
 def checkpoint_path():
     d = os.environ.get("DYNINFER_BENCH_DIR") or os.path.join(tempfile.gettempdir(), "dyninfer_b200_bench")
     os.makedirs(d, exist_ok=True)
@@ -405,10 +410,6 @@ def main():
     def barrier():
         replicas.barrier()
         torch.cuda.synchronize()
-
-    def phases(n):
-        """n steps as decode phases of at most GEN_STEPS steps, each after its own prompt."""
-        return [GEN_STEPS] * (n // GEN_STEPS) + ([n % GEN_STEPS] if n % GEN_STEPS else [])
 
     def begin_generation():
         session.reset()

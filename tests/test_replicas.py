@@ -47,3 +47,19 @@ def test_single_process_is_identity():
     assert replicas.max_over_ranks([1.5, 2.5]) == [1.5, 2.5]
     assert replicas.whole_job_rate(100, 50.0, 1) == 2000.0
     replicas.barrier()
+
+
+def test_bench_lays_its_timed_steps_out_as_generations():
+    """The bench times K steps as decode phases of the named configuration (32 greedy steps after the
+    16-token prompt), the way the reference's perf runner repeats its iterations."""
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    import bench
+    assert bench.GEN_STEPS == 32 and bench.PROMPT_LEN == 16
+    assert bench.phases(256) == [32] * 8
+    assert bench.phases(2) == [2] and bench.phases(32) == [32]
+    assert bench.phases(40) == [32, 8] and bench.phases(0) == []
+    for k in (1, 5, 31, 33, 100, 257):
+        p = bench.phases(k)
+        assert sum(p) == k and all(0 < n <= 32 for n in p)

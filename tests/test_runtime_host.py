@@ -30,6 +30,8 @@ class RecordingLibrary:
         self.descriptor = None
         self.keys = None
         self.fail_next_invoke = None
+        self.slot_invokes = []     # (slot, tokens, last, start_pos, want_logits)
+        self.batch_steps = []      # ([(slot, token, position)], want_logits)
 
     def dyninfer_cuda_last_error(self):
         return (self.fail_next_invoke or "").encode()
@@ -85,6 +87,27 @@ class RecordingLibrary:
             out_logits._obj.contents = self._logits
             out_count._obj.value = VOCAB
         out_token._obj.value = token
+        return 0
+
+
+    def dyninfer_cuda_session_invoke_paged_chunk_slot(self, h, tokens, n, last, start, slot, out_logits, out_count,
+                                                      out_token, want_logits):
+        self.slot_invokes.append((int(slot), [int(tokens[i]) for i in range(n)], int(last), int(start),
+                                  int(want_logits)))
+        out_token._obj.value = self.script(start + last) + int(slot)
+        if want_logits:
+            out_logits._obj.contents = self._logits
+            out_count._obj.value = VOCAB
+        return 0
+
+    def dyninfer_cuda_session_decode_batch(self, h, tokens, positions, slots, n, out_tokens, out_logits, want_logits):
+        rows = [(int(slots[i]), int(tokens[i]), int(positions[i])) for i in range(n)]
+        self.batch_steps.append((rows, int(want_logits)))
+        for i, (slot, _, pos) in enumerate(rows):
+            out_tokens[i] = self.script(pos) + slot
+        if want_logits:
+            self._batch_logits = (C.c_float * (n * VOCAB))(*[float(i // VOCAB) for i in range(n * VOCAB)])
+            out_logits._obj.contents = self._batch_logits
         return 0
 
 
@@ -246,3 +269,36 @@ def test_target_resolution_never_reaches_a_cpu():
     for bad in ("cpu", "local-task", "hip", "rocm:gfx1151"):
         with pytest.raises(DynInferError, match="no CPU fallback"):
             ModelLoader.resolve_target(bad)
+
+
+def test_batched_session_places_sequences_in_slots(model, fake):
+    with model.create_batched_session(SessionConfig(max_sequence_length=1024, batch_size=4)) as s:
+        assert fake.descriptor["batch"] == 4 and s.slots == 4
+        first = {slot: s.prefill_slot(slot, [slot + 1] * (600 if slot == 2 else 5)) for slot in range(4)}
+        assert s.positions == [5, 5, 600, 5]
+        # slot 2's prompt spans two chunk calls; every chunk is right padded to the chunk size
+        assert [(slot, len(t), last, start) for slot, t, last, start, _ in fake.slot_invokes] == \
+            [(0, 512, 4, 0), (1, 512, 4, 0), (2, 512, 511, 0), (2, 512, 87, 512), (3, 512, 4, 0)]
+        assert first == {0: fake.script(4), 1: fake.script(4) + 1, 2: fake.script(599) + 2, 3: fake.script(4) + 3}
+        # one step over a subset of the slots: rows in ascending slot order, each at its own position
+        nxt = s.step({3: 30, 0: 10, 2: 20})
+        rows, want = fake.batch_steps[-1]
+        assert rows == [(0, 10, 5), (2, 20, 600), (3, 30, 5)] and want == 0
+        assert nxt == {0: fake.script(5), 2: fake.script(600) + 2, 3: fake.script(5) + 3}
+        assert s.positions == [6, 5, 601, 6]
+        nxt, logits = s.step({1: 7}, want_logits=True)
+        assert fake.batch_steps[-1] == ([(1, 7, 5)], 1) and logits[1].shape == (VOCAB,) and set(nxt) == {1}
+        assert s.step({}) == {} and s.step({}, want_logits=True) == ({}, {})
+        with pytest.raises(DynInferError, match=r"slot 4 outside \[0, 4\)"):
+            s.prefill_slot(4, [1])
+        with pytest.raises(DynInferError, match=r"slot 9 outside \[0, 4\)"):
+            s.step({9: 1})
+        with pytest.raises(DynInferError, match=r"prefill length 0 outside \[1, 1024\]"):
+            s.prefill_slot(0, [])
+        s.positions[1] = 1024
+        with pytest.raises(DynInferError, match="slot 1: decode position 1024 exceeds session/KV limit 1024"):
+            s.step({1: 3})
+        s.reset()
+        assert s.positions == [0, 0, 0, 0]
+    with pytest.raises(DynInferError, match="batch_size must be >= 1"):
+        model.create_batched_session(SessionConfig(batch_size=0))

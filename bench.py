@@ -219,8 +219,8 @@ def run_reference_arm(args, rank):
     if rank != 0:
         return
     path = ensure_checkpoint()
-    steps = max(1, min(args.steps, 48))
     warm = max(1, min(args.warmup, 3))
+    steps = max(1, min(args.steps, GEN_STEPS - warm))     # one generation of the named configuration
     tps, cores, dt, _, _ = cpu_decode(path, steps, warm=warm)
     sample = (f"{steps} greedy decode steps of the full 28-layer model after the {PROMPT_LEN}-token prompt, "
               f"CPU restatement of the reference's direct path (the reference's own IREE llvm-cpu "

@@ -55,6 +55,16 @@ fn check(code: i32) -> Result<()> {
 }
 
 /// Number of usable CUDA devices. Fails (never falls back to a CPU) when there is none.
+/// Communicator id for a tensor-parallel group: created on rank 0 and handed to every rank (over
+/// whatever channel the launcher has) for `Context::with_tensor_parallel`.
+pub fn tp_unique_id() -> Result<Vec<u8>> {
+    // SAFETY: plain query.
+    let mut id = vec![0u8; unsafe { sys::dyninfer_cuda_tp_unique_id_bytes() }];
+    // SAFETY: `id` holds the advertised number of bytes.
+    check(unsafe { sys::dyninfer_cuda_tp_unique_id(id.as_mut_ptr(), id.len()) })?;
+    Ok(id)
+}
+
 pub fn device_count() -> Result<usize> {
     let mut n = 0;
     // SAFETY: plain out-parameter.
@@ -168,6 +178,9 @@ pub struct Context {
     model_descriptor: CString,
     ranges: Arc<FileRanges>,
     geometry: PagedKvGeometry,
+    /// Communicator id of the tensor-parallel group this context is one rank of (the descriptor
+    /// then carries `tp_rank` / `tp_world` and the ranges are the rank's slices).
+    tp_unique_id: Option<Vec<u8>>,
     session: Mutex<Option<NativeSession>>,
 }
 
@@ -185,8 +198,17 @@ impl Context {
                 .map_err(|e| runtime_error(format!("invalid model descriptor: {e}"), None))?,
             ranges,
             geometry,
+            tp_unique_id: None,
             session: Mutex::new(None),
         })
+    }
+
+    /// Makes this context one rank of a tensor-parallel group. `unique_id` is what `tp_unique_id()`
+    /// returned on rank 0, handed to every rank by the launcher; the group is joined when the native
+    /// session is created (every rank must then create its session: the call is collective).
+    pub fn with_tensor_parallel(mut self, unique_id: Vec<u8>) -> Self {
+        self.tp_unique_id = Some(unique_id);
+        self
     }
 
     /// Runs `f` with the native handle, creating and configuring the session on first use.
@@ -231,6 +253,10 @@ impl Context {
                 Some(h) if rc == 0 => NativeSession(h),
                 _ => return Err(native_error(rc)),
             };
+            if let Some(id) = &self.tp_unique_id {
+                // SAFETY: valid handle; `id` outlives the call. Must precede the KV configuration.
+                check(unsafe { sys::dyninfer_cuda_session_tp_init(handle.0.as_ptr(), id.as_ptr(), id.len()) })?;
+            }
             let g = self.geometry;
             // SAFETY: valid handle; plain integers.
             check(unsafe {
@@ -333,6 +359,105 @@ impl Context {
     pub fn invoke_paged_chunk(&self, tokens: &[i64], last: i64, start_pos: i64) -> Result<Vec<f32>> {
         let (logits, _) = self.invoke_paged_chunk_ex(tokens, last, start_pos, true)?;
         logits.ok_or_else(|| runtime_error("logits were requested but not returned", None))
+    }
+
+    /// `invoke_paged_chunk_ex` for KV slot `slot` of a session whose descriptor sets `"batch"` > 1.
+    /// Sequences in different slots are independent; each has its own positions.
+    pub fn invoke_paged_chunk_slot(
+        &self,
+        tokens: &[i64],
+        last: i64,
+        start_pos: i64,
+        slot: i64,
+        want_logits: bool,
+    ) -> Result<(Option<Vec<f32>>, i64)> {
+        self.with_session(|s| {
+            let mut view: *mut f32 = ptr::null_mut();
+            let mut count = 0usize;
+            let mut token = -1i64;
+            // SAFETY: as in `invoke_paged_chunk_ex`.
+            check(unsafe {
+                sys::dyninfer_cuda_session_invoke_paged_chunk_slot(
+                    s,
+                    tokens.as_ptr(),
+                    tokens.len(),
+                    last,
+                    start_pos,
+                    slot,
+                    if want_logits { &mut view } else { ptr::null_mut() },
+                    if want_logits { &mut count } else { ptr::null_mut() },
+                    &mut token,
+                    want_logits as i32,
+                )
+            })?;
+            let logits = if want_logits && !view.is_null() {
+                // SAFETY: `count` floats at `view` until the next invoke; copied under the lock.
+                Some(unsafe { std::slice::from_raw_parts(view, count) }.to_vec())
+            } else {
+                None
+            };
+            Ok((logits, token))
+        })
+    }
+
+    /// One decode step for several slots in one pass over the weights: row `i` feeds `tokens[i]` at
+    /// `positions[i]` into KV slot `slots[i]`. Returns the next token of every row and, when asked,
+    /// the logits as `tokens.len()` rows of `vocab` values.
+    pub fn decode_batch(
+        &self,
+        tokens: &[i64],
+        positions: &[i64],
+        slots: &[i64],
+        want_logits: bool,
+    ) -> Result<(Vec<i64>, Option<Vec<f32>>)> {
+        if tokens.len() != positions.len() || tokens.len() != slots.len() {
+            return Err(runtime_error("decode_batch: tokens, positions and slots differ in length", None));
+        }
+        let vocab = self.geometry.vocab_size;
+        self.with_session(|s| {
+            let mut out = vec![-1i64; tokens.len()];
+            let mut view: *mut f32 = ptr::null_mut();
+            // SAFETY: the three inputs and `out` hold `tokens.len()` entries each.
+            check(unsafe {
+                sys::dyninfer_cuda_session_decode_batch(
+                    s,
+                    tokens.as_ptr(),
+                    positions.as_ptr(),
+                    slots.as_ptr(),
+                    tokens.len(),
+                    out.as_mut_ptr(),
+                    if want_logits { &mut view } else { ptr::null_mut() },
+                    want_logits as i32,
+                )
+            })?;
+            let logits = if want_logits && !view.is_null() {
+                // SAFETY: session scratch of rows x vocab floats, valid until the next call; copied
+                // while the lock is held.
+                Some(unsafe { std::slice::from_raw_parts(view, tokens.len() * vocab) }.to_vec())
+            } else {
+                None
+            };
+            Ok((out, logits))
+        })
+    }
+
+    /// This rank's exchange-region handle for the fused peer-memory exchange (after the KV pool is
+    /// configured, i.e. after first use). The launcher gathers every rank's handle, in rank order.
+    pub fn tp_peer_handle(&self) -> Result<Vec<u8>> {
+        self.with_session(|s| {
+            // SAFETY: plain query.
+            let mut buf = vec![0u8; unsafe { sys::dyninfer_cuda_tp_peer_handle_bytes() }];
+            // SAFETY: `buf` holds the advertised number of bytes.
+            check(unsafe { sys::dyninfer_cuda_session_tp_peer_handle(s, buf.as_mut_ptr(), buf.len()) })?;
+            Ok(buf)
+        })
+    }
+
+    /// Maps the peers' exchange regions: `handles` = all ranks' handles concatenated in rank order.
+    /// Without this call the partial sums go through NCCL.
+    pub fn tp_peer_attach(&self, handles: &[u8]) -> Result<()> {
+        // SAFETY: valid handle; `handles` outlives the call.
+        self.with_session(|s| check(unsafe { sys::dyninfer_cuda_session_tp_peer_attach(s, handles.as_ptr(), handles.len()) }))
     }
 
     /// Device-resident greedy loop (no host round trip per token). Returns the tokens produced and

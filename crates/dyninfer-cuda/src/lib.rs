@@ -54,7 +54,6 @@ fn check(code: i32) -> Result<()> {
     if code == 0 { Ok(()) } else { Err(native_error(code)) }
 }
 
-/// Number of usable CUDA devices. Fails (never falls back to a CPU) when there is none.
 /// Communicator id for a tensor-parallel group: created on rank 0 and handed to every rank (over
 /// whatever channel the launcher has) for `Context::with_tensor_parallel`.
 pub fn tp_unique_id() -> Result<Vec<u8>> {
@@ -65,6 +64,7 @@ pub fn tp_unique_id() -> Result<Vec<u8>> {
     Ok(id)
 }
 
+/// Number of usable CUDA devices. Fails (never falls back to a CPU) when there is none.
 pub fn device_count() -> Result<usize> {
     let mut n = 0;
     // SAFETY: plain out-parameter.
